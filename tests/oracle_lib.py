@@ -1,0 +1,171 @@
+"""ctypes view of the CPU oracle (oracle/cusync_oracle.c) for the tests.
+
+Only tests, the smoke check and the bench's CPU-baseline leg may import this.
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ORACLE_DIR = os.path.join(ROOT, "oracle")
+ORACLE_SO = os.path.join(ORACLE_DIR, "_build", "libcusync_oracle.so")
+REF_POLICIES_SO = os.path.join(ORACLE_DIR, "_ref", "libcusync_ref_policies.so")
+REF_L1_DRIVER = os.path.join(ORACLE_DIR, "_ref", "ref_l1_driver")
+
+ORDER_IDENTITY, ORDER_TRANSPOSE_XY = 0, 1
+NOSYNC, ROWSYNC, TILESYNC, STRIDEDSYNC, CONV2DTILESYNC, CONSECUTIVESYNC = range(6)
+EPI_NONE, EPI_GELU_ERF, EPI_RELU = 0, 1, 2
+OPT_NO_ATOMIC_ADD = 1
+
+
+class Dim3(C.Structure):
+    _fields_ = [("x", C.c_uint32), ("y", C.c_uint32), ("z", C.c_uint32)]
+
+    def tup(self):
+        return (self.x, self.y, self.z)
+
+
+class Policy(C.Structure):
+    _fields_ = [("kind", C.c_int32), ("order", C.c_int32), ("tile_m", C.c_uint32),
+                ("tile_n", C.c_uint32), ("wait_value", C.c_uint32), ("post_value", C.c_uint32),
+                ("p0", C.c_uint32), ("p1", C.c_uint32)]
+
+
+def _build():
+    src = [os.path.join(ORACLE_DIR, f) for f in ("cusync_oracle.c", "cusync_oracle.h")]
+    if os.path.exists(ORACLE_SO) and all(os.path.getmtime(ORACLE_SO) >= os.path.getmtime(s) for s in src):
+        return
+    subprocess.check_call(["make", "-C", ORACLE_DIR, "all"], stdout=subprocess.DEVNULL)
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is not None:
+        return _lib
+    _build()
+    L = C.CDLL(ORACLE_SO)
+    u32, i32, vp = C.c_uint32, C.c_int, C.c_void_p
+    L.orc_block_index.restype = u32
+    L.orc_block_index.argtypes = [i32, Dim3, Dim3]
+    L.orc_tile_to_block.restype = Dim3
+    L.orc_tile_to_block.argtypes = [i32, Dim3]
+    L.orc_order_tile_index.restype = u32
+    L.orc_order_tile_index.argtypes = [i32, Dim3, Dim3]
+    for name in ("wait_value", "post_value", "tile_index"):
+        f = getattr(L, "orc_policy_" + name)
+        f.restype = u32
+        f.argtypes = [C.POINTER(Policy), Dim3, Dim3]
+    L.orc_policy_is_sync.restype = i32
+    L.orc_policy_is_sync.argtypes = [C.POINTER(Policy), Dim3, Dim3]
+    L.orc_build_tile_order.restype = i32
+    L.orc_build_tile_order.argtypes = [i32, Dim3, vp]
+    L.orc_producer_semaphores.restype = i32
+    L.orc_producer_semaphores.argtypes = [C.POINTER(Policy), Dim3, u32, u32, i32, u32, vp, u32]
+    L.orc_consumer_tile_waits.restype = u32
+    L.orc_consumer_tile_waits.argtypes = [C.POINTER(Policy), Dim3, u32, u32, u32, u32, vp, vp, u32]
+    L.orc_gemm_f16.restype = None
+    L.orc_gemm_f16.argtypes = [i32, i32, i32, vp, i32, vp, i32, vp, i32, i32]
+    L.orc_gemm_dual_silu_mul_f16.restype = None
+    L.orc_gemm_dual_silu_mul_f16.argtypes = [i32, i32, i32, vp, i32, vp, vp, i32, vp, i32]
+    L.orc_gemm_f32.restype = None
+    L.orc_gemm_f32.argtypes = [i32, i32, i32, vp, vp, vp]
+    L.orc_conv2d_3x3_nhwc_f16.restype = None
+    L.orc_conv2d_3x3_nhwc_f16.argtypes = [i32, i32, i32, i32, i32, vp, vp, vp, i32]
+    L.orc_attention_decode_f16.restype = None
+    L.orc_attention_decode_f16.argtypes = [i32, i32, i32, i32, vp, i32, vp, vp, vp, i32]
+    L.orc_max_rel_err_f16.restype = C.c_double
+    L.orc_max_rel_err_f16.argtypes = [C.c_size_t, vp, vp, C.c_double]
+    L.orc_num_threads.restype = i32
+    _lib = L
+    return L
+
+
+def _p(a):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def policy(kind, order=ORDER_TRANSPOSE_XY, tile_m=1, tile_n=1, wait_value=1, post_value=1, p0=0, p1=0):
+    return Policy(kind, order, tile_m, tile_n, wait_value, post_value, p0, p1)
+
+
+def tile_order(order, grid):
+    n = grid[0] * grid[1] * grid[2]
+    out = np.zeros((n, 3), dtype=np.uint32)
+    bad = lib().orc_build_tile_order(order, Dim3(*grid), _p(out))
+    return out, bad
+
+
+def producer_semaphores(pol, grid, tile_m, tile_n, opts, iters, num_sems=None):
+    n = num_sems if num_sems is not None else grid[0] * grid[1] * grid[2]
+    sems = np.zeros(n, dtype=np.uint32)
+    oob = lib().orc_producer_semaphores(C.byref(pol), Dim3(*grid), tile_m, tile_n, opts, iters, _p(sems), n)
+    return sems, oob
+
+
+def consumer_tile_waits(pol, prod_grid, row_off, k_extent, block_k, it):
+    cap = (k_extent + block_k - 1) // block_k
+    idx = np.zeros(cap, dtype=np.uint32)
+    exp = np.zeros(cap, dtype=np.uint32)
+    n = lib().orc_consumer_tile_waits(C.byref(pol), Dim3(*prod_grid), row_off, k_extent, block_k, it,
+                                      _p(idx), _p(exp), cap)
+    return idx[:n], exp[:n]
+
+
+def gemm_f16(a, b, epilogue=EPI_NONE):
+    """a[M,K], b[K,N] float16 numpy -> float16 [M,N]."""
+    assert a.dtype == np.float16 and b.dtype == np.float16
+    a = np.ascontiguousarray(a); b = np.ascontiguousarray(b)
+    M, K = a.shape; K2, N = b.shape
+    assert K == K2
+    c = np.empty((M, N), dtype=np.float16)
+    lib().orc_gemm_f16(M, N, K, _p(a), K, _p(b), N, _p(c), N, epilogue)
+    return c
+
+
+def gemm_dual_silu_mul_f16(a, b1, b2):
+    a = np.ascontiguousarray(a); b1 = np.ascontiguousarray(b1); b2 = np.ascontiguousarray(b2)
+    M, K = a.shape; _, N = b1.shape
+    g = np.empty((M, N), dtype=np.float16)
+    lib().orc_gemm_dual_silu_mul_f16(M, N, K, _p(a), K, _p(b1), _p(b2), N, _p(g), N)
+    return g
+
+
+def gemm_f32(a, b):
+    a = np.ascontiguousarray(a, dtype=np.float32); b = np.ascontiguousarray(b, dtype=np.float32)
+    M, K = a.shape; _, N = b.shape
+    c = np.empty((M, N), dtype=np.float32)
+    lib().orc_gemm_f32(M, N, K, _p(a), _p(b), _p(c))
+    return c
+
+
+def conv2d_3x3_nhwc_f16(x, w, relu):
+    x = np.ascontiguousarray(x); w = np.ascontiguousarray(w)
+    N, H, W, Cc = x.shape; K = w.shape[0]
+    assert w.shape == (K, 3, 3, Cc)
+    y = np.empty((N, H, W, K), dtype=np.float16)
+    lib().orc_conv2d_3x3_nhwc_f16(N, H, W, Cc, K, _p(x), _p(w), _p(y), int(relu))
+    return y
+
+
+def attention_decode_f16(q, k, v):
+    """q[B,heads,d], k/v[B,S,heads,d] -> o[B,heads,d]."""
+    q = np.ascontiguousarray(q); k = np.ascontiguousarray(k); v = np.ascontiguousarray(v)
+    B, S, heads, d = k.shape
+    o = np.empty((B, heads, d), dtype=np.float16)
+    lib().orc_attention_decode_f16(B, S, heads, d, _p(q), heads * d, _p(k), _p(v), _p(o), heads * d)
+    return o
+
+
+def max_rel_err(got, ref, floor_frac=1e-2):
+    got = np.ascontiguousarray(got, dtype=np.float16); ref = np.ascontiguousarray(ref, dtype=np.float16)
+    assert got.shape == ref.shape
+    return lib().orc_max_rel_err_f16(got.size, _p(got), _p(ref), floor_frac)
+
+
+def num_threads():
+    return lib().orc_num_threads()
