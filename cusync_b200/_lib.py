@@ -1,0 +1,123 @@
+"""ctypes binding of libcusync_b200.so (the C ABI declared in include/cusync_b200.h).
+
+The library is hand-written sm_100a CUDA; there is no fallback.  If the shared
+object is missing this module raises at import of the symbol table, and every
+compute call needs a CUDA device.
+"""
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libcusync_b200.so")
+
+# status codes (include/cusync_b200.h)
+ERROR_NOT_PRODUCER, ERROR_NOT_CONSUMER, ERROR_NOT_INITIALIZED, ERROR_INVALID_LINEAR_BLOCK_INDEX, \
+    ERROR_CUDA, SUCCESS, ERROR_TIMEOUT, ERROR_INVALID_ARGUMENT, ERROR_UNSUPPORTED = range(9)
+ERROR_NAMES = ["CuSyncErrorNotProducer", "CuSyncErrorNotConsumer", "CuSyncErrorNotInitialized",
+               "CuSyncErrorInvalidLinearBlockIndex", "CuSyncErrorCUDAError", "CuSyncSuccess",
+               "CuSyncErrorTimeout", "CuSyncErrorInvalidArgument", "CuSyncErrorUnsupported"]
+
+OPT_NONE, OPT_NO_ATOMIC_ADD, OPT_AVOID_WAIT_KERNEL, OPT_AVOID_CUSTOM_ORDER, OPT_REORDER_TILE_LOADS = 0, 1, 2, 4, 8
+ORDER_IDENTITY, ORDER_TRANSPOSE_XY = 0, 1
+POLICY_NOSYNC, POLICY_ROWSYNC, POLICY_TILESYNC, POLICY_STRIDEDTILESYNC, POLICY_CONV2DTILESYNC, \
+    POLICY_CONSECUTIVETILESYNC = range(6)
+EPILOGUE_NONE, EPILOGUE_GELU_ERF, EPILOGUE_RELU, EPILOGUE_SILU_MUL_DUAL = range(4)
+B_ROW_MAJOR_KN, B_ROW_MAJOR_NK = 0, 1
+
+
+class Dim3(C.Structure):
+    _fields_ = [("x", C.c_uint32), ("y", C.c_uint32), ("z", C.c_uint32)]
+
+
+class Policy(C.Structure):
+    _fields_ = [("kind", C.c_int32), ("order", C.c_int32), ("tile_m", C.c_uint32), ("tile_n", C.c_uint32),
+                ("wait_value", C.c_uint32), ("post_value", C.c_uint32), ("p0", C.c_uint32), ("p1", C.c_uint32)]
+
+
+class Status(C.Structure):
+    _fields_ = [("code", C.c_uint32), ("where", C.c_uint32), ("tile_x", C.c_uint32), ("tile_y", C.c_uint32),
+                ("tile_z", C.c_uint32), ("sem_index", C.c_uint32), ("seen", C.c_uint32), ("expected", C.c_uint32)]
+
+
+class StageView(C.Structure):
+    _fields_ = [("grid", Dim3), ("prod_grid", Dim3), ("tile_size", Dim3), ("iter", C.c_uint32),
+                ("opts", C.c_int32), ("order", C.c_int32), ("reserved", C.c_int32),
+                ("in_policy", Policy), ("out_policy", Policy),
+                ("tile_order", C.c_void_p), ("tile_counter", C.c_void_p), ("started", C.c_void_p),
+                ("sems_post", C.c_void_p), ("sems_wait", C.c_void_p), ("status", C.c_void_p),
+                ("timeout_ns", C.c_uint64)]
+
+
+class GemmDesc(C.Structure):
+    _fields_ = [("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32),
+                ("a", C.c_void_p), ("lda", C.c_int64),
+                ("b", C.c_void_p), ("ldb", C.c_int64),
+                ("b2", C.c_void_p),
+                ("d", C.c_void_p), ("ldd", C.c_int64),
+                ("b_layout", C.c_int32), ("epilogue", C.c_int32), ("tile_n", C.c_int32), ("max_ctas", C.c_int32),
+                ("stage", C.c_void_p)]
+
+
+# name -> (restype, argtypes); every function include/cusync_b200.h declares
+_vp, _i, _u32, _u64 = C.c_void_p, C.c_int, C.c_uint32, C.c_uint64
+SIGNATURES = {
+    "cusync_stage_create": (_i, [C.POINTER(_vp), Dim3, Dim3, _i, C.POINTER(Policy), C.POINTER(Policy), _i]),
+    "cusync_stage_destroy": (_i, [_vp]),
+    "cusync_stage_link": (_i, [_vp, _vp]),
+    "cusync_stage_increment_iter": (_i, [_vp]),
+    "cusync_stage_reset": (_i, [_vp, _vp]),
+    "cusync_stage_get_view": (_i, [_vp, C.POINTER(StageView)]),
+    "cusync_stage_set_timeout_ns": (_i, [_vp, _u64]),
+    "cusync_stage_invoke_wait_kernel": (_i, [_vp, _vp]),
+    "cusync_stage_note_launch": (_i, [_vp, _u32]),
+    "cusync_wait_kernel": (_i, [_vp, _u32, _vp, _vp, _u64]),
+    "cusync_stage_read_tile_order": (_i, [_vp, _vp, _u32]),
+    "cusync_stage_read_semaphores": (_i, [_vp, _vp, _u32]),
+    "cusync_stage_read_status": (_i, [_vp, C.POINTER(Status)]),
+    "cusync_stage_num_tiles": (_u32, [_vp]),
+    "cusync_stage_iter": (_u32, [_vp]),
+    "cusync_gemm_default_tile_n": (_i, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
+    "cusync_gemm_plan_create": (_i, [C.POINTER(_vp), C.POINTER(GemmDesc)]),
+    "cusync_gemm_plan_destroy": (_i, [_vp]),
+    "cusync_gemm_plan_update": (_i, [_vp, _vp, _vp, _vp, _vp]),
+    "cusync_gemm_run": (_i, [_vp, _vp]),
+    "cusync_gemm_plan_num_ctas": (_u32, [_vp]),
+    "cusync_b200_version": (C.c_char_p, []),
+    "cusync_b200_sm_count": (_i, []),
+}
+
+_lib = None
+
+
+class CuSyncLibraryError(RuntimeError):
+    pass
+
+
+def lib():
+    """Loads the shared library.  There is no CPU or PyTorch fallback behind it."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise CuSyncLibraryError(
+            "libcusync_b200.so is not built (%s). Run `python -m cusync_b200.build`; "
+            "there is no fallback implementation." % LIB_PATH)
+    L = C.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        f = getattr(L, name)
+        f.restype = res
+        f.argtypes = args
+    _lib = L
+    return L
+
+
+class CuSyncError(RuntimeError):
+    def __init__(self, code, what):
+        self.code = code
+        name = ERROR_NAMES[code] if 0 <= code < len(ERROR_NAMES) else str(code)
+        super().__init__("%s: %s" % (what, name))
+
+
+def check(code, what):
+    if code != SUCCESS:
+        raise CuSyncError(code, what)

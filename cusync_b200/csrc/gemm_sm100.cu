@@ -1,0 +1,797 @@
+// Tile-synchronised GEMM for sm_100a: D = epilogue(A * B), fp16 operands, fp32
+// accumulation in tensor memory, fp16 output.
+//
+// Replaces the reference's CuSync-augmented CUTLASS 2.x GEMM
+// (gemm/kernel/cusyncgemm.h:207-399 and the main loops in
+// gemm/threadblock/cusyncmma_multistage.h:943-1200, which are mma.sync +
+// cp.async) with a persistent, warp-specialised kernel:
+//
+//   warp 0  lane 0   tile scheduler + TMA loader.  Draws a ticket from the
+//                    stage's counter, looks the tile up in the schedule buffer
+//                    (CuStage::tile, cusync_device_defs.h:77-103), and streams
+//                    K-blocks of A and B into a shared-memory ring.  The
+//                    CONSUMER WAIT sits here: before the TMA load of an A
+//                    K-block whose producer tile is not known to be finished,
+//                    it evaluates the input policy and spins on the semaphore
+//                    (CuStage::wait, cusync_device_defs.h:33-50).  B (weights)
+//                    is issued before the wait, which is the reference's
+//                    ReorderTileLoads optimisation (cusyncmma_multistage.h:1076-1084).
+//   warp 1  lane 0   issues tcgen05.mma (128 x BN x 16, kind::f16) into one of
+//                    two TMEM accumulator buffers.
+//   warp 2           allocates / frees tensor memory.
+//   warps 4-7        epilogue: tcgen05.ld -> fp32 math (GELU / ReLU / SiLU*mul)
+//                    -> fp16 -> swizzled shared staging -> TMA store.  After
+//                    the stores have fully completed, ONE thread publishes the
+//                    tile with red.release.gpu (CuStage::post,
+//                    cusync_device_defs.h:55-72).
+//
+// No TMA multicast is used anywhere.  Every wait in the kernel is bounded: on
+// expiry the waiter records why in the stage's status words, raises a
+// block-wide abort flag, and the block drains its copies, frees its tensor
+// memory and returns.
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <new>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int kBlockM = 128;        // UMMA M
+constexpr int kBlockK = 64;         // one 128-byte swizzle row of fp16
+constexpr int kUmmaK = 16;
+constexpr int kThreads = 256;
+constexpr int kSchedSlots = 4;
+constexpr int kEpilogueWarp0 = 4;
+constexpr int kStoreCols = 64;      // columns per TMA store box (128 bytes)
+constexpr uint32_t kSmemLimit = 232448;  // 227 KB
+
+// ---------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ void fence_barrier_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(smem_u32(src)), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                         uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor for tcgen05.mma: 128-byte swizzle, Blackwell
+// descriptor version 1.  Offsets are given in bytes.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= 1ull << 46;   // descriptor version
+  d |= 2ull << 61;   // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor, kind::f16: D = f32, A = B = f16, A K-major.
+__host__ __device__ constexpr uint32_t make_idesc(int umma_n, bool b_mn_major) {
+  return (1u << 4) | (0u << 7) | (0u << 10) | (0u << 15) | ((b_mn_major ? 1u : 0u) << 16) |
+         (static_cast<uint32_t>(umma_n >> 3) << 17) | (static_cast<uint32_t>(kBlockM >> 4) << 24);
+}
+
+// ---------------------------------------------------------------------------
+// Kernel parameters
+// ---------------------------------------------------------------------------
+struct GemmParams {
+  int32_t m, n, k;
+  int32_t tiles_n, tiles_m, num_tiles;
+  int32_t num_k_blocks;
+  int32_t epilogue;
+  int32_t b_kmajor;            // 1: B given as [n,k] row-major
+  int32_t is_producer, is_consumer;
+  uint32_t b_lbo, b_sbo, b_kstep;  // B shared-memory descriptor: leading / stride offsets, bytes per UMMA K step
+  cusync_stage_view_t stage;   // by-value copy, like params_.custage in the reference
+};
+
+template <int BN, bool DUAL>
+struct Cfg {
+  static constexpr int kNumB = DUAL ? 2 : 1;
+  static constexpr int kABytes = kBlockM * kBlockK * 2;
+  static constexpr int kBBytes = BN * kBlockK * 2;
+  static constexpr int kStageBytes = kABytes + kNumB * kBBytes;
+  static constexpr int kStagingBytes = 4 * 2 * 32 * 128;   // 4 warps x 2 buffers x 32 rows x 128 B
+  static constexpr int kBarrierBytes = 1024;
+  static constexpr int kStages =
+      ((int)kSmemLimit - 1024 /*alignment slack*/ - kStagingBytes - kBarrierBytes) / kStageBytes > 8
+          ? 8
+          : ((int)kSmemLimit - 1024 - kStagingBytes - kBarrierBytes) / kStageBytes;
+  static constexpr int kAccCols = BN * kNumB;               // fp32 columns per accumulator buffer
+  static constexpr int kTmemCols = 2 * kAccCols < 32 ? 32 : 2 * kAccCols;
+  static constexpr uint32_t kSmemBytes = 1024 + kStages * kStageBytes + kStagingBytes + kBarrierBytes;
+  static_assert(kTmemCols <= 512, "accumulators exceed tensor memory");
+  static_assert((kTmemCols & (kTmemCols - 1)) == 0, "TMEM columns must be a power of two");
+  static_assert(kSmemBytes <= kSmemLimit, "shared memory over budget");
+  static_assert(kStages >= 3, "pipeline too shallow");
+};
+
+struct Barriers {
+  uint64_t full[8];
+  uint64_t empty[8];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint64_t sched_full[kSchedSlots];
+  uint64_t sched_empty[kSchedSlots];
+  uint64_t drain;
+  uint64_t post;                        // 4 epilogue warps -> the posting thread
+  int32_t sched_tile[kSchedSlots][4];   // {n tile, m tile, valid, unused}
+  uint32_t tmem_base;
+  volatile uint32_t abort;
+};
+static_assert(sizeof(Barriers) <= 1024, "barrier block too large");
+
+struct WaitCtx {
+  volatile uint32_t* abort;
+  uint32_t* status;
+  uint64_t timeout_ns;
+};
+
+// Bounded mbarrier wait.  Returns false when the block is aborting or the
+// bound expired (then it raises the abort flag itself).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& ctx) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = cusync::globalTimerNs();
+  uint32_t polls = 0;
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++polls & 31u) == 0u) {
+      if (*ctx.abort) return false;
+      if (cusync::globalTimerNs() - t0 > ctx.timeout_ns) {
+        *ctx.abort = 1u;
+        cusync::recordTimeout(ctx.status, 2u, blockIdx.x, threadIdx.x, parity, smem_u32(bar), 0u, 0u);
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f)); }
+__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
+
+__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// ---------------------------------------------------------------------------
+// The kernel
+// ---------------------------------------------------------------------------
+template <int BN, bool DUAL>
+__global__ void __launch_bounds__(kThreads, 1)
+cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                   const __grid_constant__ CUtensorMap tmB2, const __grid_constant__ CUtensorMap tmD,
+                   const GemmParams p) {
+  using C = Cfg<BN, DUAL>;
+  extern __shared__ uint8_t smem_raw[];
+  // 128-byte swizzle patterns repeat every 1024 bytes: align the ring to that.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* ring = smem;
+  uint8_t* staging = smem + C::kStages * C::kStageBytes;
+  Barriers* bars = reinterpret_cast<Barriers*>(staging + C::kStagingBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const cusync_stage_view_t& st = p.stage;
+  WaitCtx ctx{&bars->abort, st.status, 2 * st.timeout_ns + 1000000000ull};
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < C::kStages; i++) { mbar_init(&bars->full[i], 1); mbar_init(&bars->empty[i], 1); }
+    for (int i = 0; i < 2; i++) { mbar_init(&bars->tmem_full[i], 1); mbar_init(&bars->tmem_empty[i], 4); }
+    for (int i = 0; i < kSchedSlots; i++) { mbar_init(&bars->sched_full[i], 1); mbar_init(&bars->sched_empty[i], 5); }
+    mbar_init(&bars->drain, 1);
+    mbar_init(&bars->post, 4);
+    bars->abort = 0u;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+    // "Kernel started" words the wait kernel polls: [0] follows the reference
+    // (block 0 stores iter, cusync_device_defs.h:78-83); [1] counts resident blocks.
+    if (p.is_producer) {
+      if (blockIdx.x == 0) cusync::storeRelease(st.started, st.iter);
+      cusync::addRelease(st.started + 1, 1u);
+    }
+  }
+  if (warp == 0 && lane == 0) {
+    prefetch_tensormap(&tmA); prefetch_tensormap(&tmB); prefetch_tensormap(&tmD);
+    if (DUAL) prefetch_tensormap(&tmB2);
+  }
+  if (warp == 2) {
+    tmem_alloc(&bars->tmem_base, C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    // =====================================================================
+    // Scheduler + TMA loader
+    // =====================================================================
+    if (lane == 0) {
+      uint32_t fills = 0, sched_it = 0;
+      bool ok = true;
+      const uint32_t total_draws = static_cast<uint32_t>(p.num_tiles) + gridDim.x;
+      while (ok) {
+        const uint32_t slot = sched_it % kSchedSlots, sph = (sched_it / kSchedSlots) & 1u;
+        if (!mbar_wait(&bars->sched_empty[slot], sph ^ 1u, ctx)) { ok = false; break; }
+        const uint32_t ticket = atomicAdd(st.tile_counter, 1u);
+        // Every block draws exactly one ticket past the end, so the draw
+        // numbered total_draws-1 is the launch's last: it re-arms the counter
+        // (the reference resets on the last tile, cusync_device_defs.h:87-90).
+        if (ticket == total_draws - 1u) atomicExch(st.tile_counter, 0u);
+        const bool valid = ticket < static_cast<uint32_t>(p.num_tiles);
+        cusync_dim3_t t = {0, 0, 0};
+        if (valid) t = st.tile_order[ticket];
+        bars->sched_tile[slot][0] = static_cast<int32_t>(t.x);
+        bars->sched_tile[slot][1] = static_cast<int32_t>(t.y);
+        bars->sched_tile[slot][2] = valid ? 1 : 0;
+        mbar_arrive(&bars->sched_full[slot]);
+        sched_it++;
+        if (!valid) break;
+
+        const int n_off = static_cast<int>(t.x) * BN;
+        const int m_off = static_cast<int>(t.y) * kBlockM;
+        for (int kb = 0; kb < p.num_k_blocks; kb++) {
+          const uint32_t s = fills % C::kStages, ph = (fills / C::kStages) & 1u;
+          if (!mbar_wait(&bars->empty[s], ph ^ 1u, ctx)) { ok = false; break; }
+          uint8_t* sa = ring + s * C::kStageBytes;
+          uint8_t* sb = sa + C::kABytes;
+          mbar_expect_tx(&bars->full[s], C::kStageBytes);
+          const int k_off = kb * kBlockK;
+          // Weights first: they never depend on the producer kernel.
+          if (p.b_kmajor) {
+            tma_load_2d(sb, &tmB, &bars->full[s], k_off, n_off);
+            if (DUAL) tma_load_2d(sb + C::kBBytes, &tmB2, &bars->full[s], k_off, n_off);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; j++)
+              tma_load_2d(sb + j * (kBlockK * 128), &tmB, &bars->full[s], n_off + j * 64, k_off);
+            if (DUAL) {
+#pragma unroll
+              for (int j = 0; j < BN / 64; j++)
+                tma_load_2d(sb + C::kBBytes + j * (kBlockK * 128), &tmB2, &bars->full[s], n_off + j * 64, k_off);
+            }
+          }
+          // Consumer wait, at the load of the dependent A K-block.
+          if (p.is_consumer) {
+            const uint32_t tz = kb == 0 ? 1u : 0u;
+            if (cusync::eval::isSync(st.in_policy, static_cast<uint32_t>(k_off), tz)) {
+              const uint32_t idx = cusync::eval::tileIndex(st.in_policy, static_cast<uint32_t>(m_off),
+                                                           static_cast<uint32_t>(k_off), st.prod_grid.x,
+                                                           st.prod_grid.y);
+              const uint32_t expected = st.iter * cusync::eval::waitValue(st.in_policy);
+              uint32_t seen = 0;
+              if (!cusync::spinUntilAtLeast(st.sems_wait + idx, expected, st.timeout_ns, &seen)) {
+                bars->abort = 1u;
+                cusync::recordTimeout(st.status, 1u, static_cast<uint32_t>(m_off), static_cast<uint32_t>(k_off), tz,
+                                      idx, seen, expected);
+                // The stage was armed: give it its A bytes anyway so the
+                // barrier completes and the drain below terminates.
+                tma_load_2d(sa, &tmA, &bars->full[s], k_off, m_off);
+                fills++;
+                ok = false;
+                break;
+              }
+              // Order the acquire (generic proxy) before the TMA read (async proxy).
+              fence_proxy_async();
+            }
+          }
+          tma_load_2d(sa, &tmA, &bars->full[s], k_off, m_off);
+          fills++;
+        }
+      }
+      if (!ok) {
+        // Abort path: wait (bounded) for every copy still in flight before the
+        // block's shared memory goes away.
+        bars->abort = 1u;
+        const uint32_t live = fills < static_cast<uint32_t>(C::kStages) ? fills : static_cast<uint32_t>(C::kStages);
+        for (uint32_t j = 0; j < live; j++) {
+          const uint32_t f = fills - 1u - j;
+          const uint32_t s = f % C::kStages, ph = (f / C::kStages) & 1u;
+          const uint64_t t0 = cusync::globalTimerNs();
+          while (!mbar_try_wait(&bars->full[s], ph)) {
+            if (cusync::globalTimerNs() - t0 > 1000000000ull) break;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // =====================================================================
+    // MMA issuer
+    // =====================================================================
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(BN, !p.b_kmajor);
+      const uint32_t b_lbo = p.b_lbo, b_sbo = p.b_sbo, b_kstep = p.b_kstep;
+      uint32_t drains = 0, sched_it = 0, acc_it = 0;
+      bool ok = true;
+      bool issued = false;
+      while (ok) {
+        const uint32_t slot = sched_it % kSchedSlots, sph = (sched_it / kSchedSlots) & 1u;
+        if (!mbar_wait(&bars->sched_full[slot], sph, ctx)) { ok = false; break; }
+        const int valid = bars->sched_tile[slot][2];
+        mbar_arrive(&bars->sched_empty[slot]);
+        sched_it++;
+        if (!valid) break;
+        const uint32_t acc = acc_it & 1u, aph = (acc_it >> 1) & 1u;
+        if (!mbar_wait(&bars->tmem_empty[acc], aph ^ 1u, ctx)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * C::kAccCols;
+        for (int kb = 0; kb < p.num_k_blocks; kb++) {
+          const uint32_t s = drains % C::kStages, ph = (drains / C::kStages) & 1u;
+          if (!mbar_wait(&bars->full[s], ph, ctx)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(ring + s * C::kStageBytes);
+          const uint32_t sb = sa + C::kABytes;
+#pragma unroll
+          for (int kk = 0; kk < kBlockK / kUmmaK; kk++) {
+            const uint64_t adesc = make_smem_desc(sa + kk * 32, 16u, 1024u);
+            const uint64_t bdesc = make_smem_desc(sb + kk * b_kstep, b_lbo, b_sbo);
+            const uint32_t accumulate = (kb > 0 || kk > 0) ? 1u : 0u;
+            umma_f16(d_tmem, adesc, bdesc, idesc, accumulate);
+            if (DUAL) {
+              const uint64_t b2desc = make_smem_desc(sb + C::kBBytes + kk * b_kstep, b_lbo, b_sbo);
+              umma_f16(d_tmem + BN, adesc, b2desc, idesc, accumulate);
+            }
+          }
+          umma_commit(&bars->empty[s]);   // frees the ring slot when these MMAs retire
+          issued = true;
+          drains++;
+        }
+        if (!ok) break;
+        umma_commit(&bars->tmem_full[acc]);
+        acc_it++;
+      }
+      if (!ok && issued) {
+        // Let outstanding MMAs retire before tensor memory is released.
+        umma_commit(&bars->drain);
+        const uint64_t t0 = cusync::globalTimerNs();
+        while (!mbar_try_wait(&bars->drain, 0u)) {
+          if (cusync::globalTimerNs() - t0 > 1000000000ull) break;
+        }
+      }
+    }
+  } else if (warp >= kEpilogueWarp0) {
+    // =====================================================================
+    // Epilogue
+    // =====================================================================
+    const int ew = warp - kEpilogueWarp0;              // == warp % 4: this warp's TMEM lane quarter
+    uint8_t* stage_buf = staging + ew * (2 * 32 * 128);
+    uint32_t sched_it = 0, acc_it = 0, store_it = 0, post_it = 0;
+    bool ok = true;
+    while (ok) {
+      const uint32_t slot = sched_it % kSchedSlots, sph = (sched_it / kSchedSlots) & 1u;
+      if (!mbar_wait(&bars->sched_full[slot], sph, ctx)) { ok = false; break; }
+      const int tile_n = bars->sched_tile[slot][0];
+      const int tile_m = bars->sched_tile[slot][1];
+      const int valid = bars->sched_tile[slot][2];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->sched_empty[slot]);
+      sched_it++;
+      if (!valid) break;
+      const uint32_t acc = acc_it & 1u, aph = (acc_it >> 1) & 1u;
+      if (!mbar_wait(&bars->tmem_full[acc], aph, ctx)) { ok = false; break; }
+      tc_fence_after();
+      const int n_off = tile_n * BN, m_off = tile_m * kBlockM;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + acc * C::kAccCols;
+
+      const bool rows_in = m_off + ew * 32 < p.m;       // else this warp's 32 rows are all padding
+#pragma unroll 1
+      for (int c = 0; c < BN / kStoreCols && rows_in; c++) {
+        if (n_off + c * kStoreCols >= p.n) break;       // chunk entirely past the matrix edge
+        uint8_t* buf = stage_buf + (store_it & 1u) * (32 * 128);
+        // The store that last read this buffer must be done reading it.
+        if (lane == 0) tma_store_wait_read<1>();
+        __syncwarp();
+        uint32_t packed[32];
+        if (!DUAL) {
+          uint32_t v[64];
+          tmem_ld_32x32b_x32(t_row + c * 64, v);
+          tmem_ld_32x32b_x32(t_row + c * 64 + 32, v + 32);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; j++) {
+            float x0 = __uint_as_float(v[2 * j]), x1 = __uint_as_float(v[2 * j + 1]);
+            if (p.epilogue == CUSYNC_EPILOGUE_GELU_ERF) { x0 = gelu_erf(x0); x1 = gelu_erf(x1); }
+            else if (p.epilogue == CUSYNC_EPILOGUE_RELU) { x0 = fmaxf(x0, 0.0f); x1 = fmaxf(x1, 0.0f); }
+            packed[j] = pack_half2(x0, x1);
+          }
+        } else {
+#pragma unroll
+          for (int h = 0; h < 2; h++) {
+            uint32_t a[32], b[32];
+            tmem_ld_32x32b_x32(t_row + c * 64 + h * 32, a);
+            tmem_ld_32x32b_x32(t_row + BN + c * 64 + h * 32, b);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+              float g0 = silu(__uint_as_float(a[2 * j])) * __uint_as_float(b[2 * j]);
+              float g1 = silu(__uint_as_float(a[2 * j + 1])) * __uint_as_float(b[2 * j + 1]);
+              packed[h * 16 + j] = pack_half2(g0, g1);
+            }
+          }
+        }
+        // Row `lane` of the 32 x 64 chunk, 16-byte pieces XOR-swizzled by row so
+        // the layout is the one a 128-byte-swizzle tensor map expects.
+        uint8_t* row = buf + lane * 128;
+#pragma unroll
+        for (int q = 0; q < 8; q++) {
+          uint4 val = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+          *reinterpret_cast<uint4*>(row + ((q ^ (lane & 7)) << 4)) = val;
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(&tmD, buf, n_off + c * kStoreCols, m_off + ew * 32);
+          tma_store_commit();
+        }
+        store_it++;
+      }
+      // Accumulator buffer is free for the MMA warp again.
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->tmem_empty[acc]);
+      acc_it++;
+
+      if (p.is_producer) {
+        // Publish the tile only after every store of it has fully completed:
+        // each warp's issuing lane waits for its own bulk stores, then arrives
+        // on `post`; the first epilogue warp's lane collects the four arrivals
+        // (bounded) and performs the single release.
+        if (lane == 0) {
+          tma_store_wait_all();
+          __threadfence();
+          mbar_arrive(&bars->post);
+          if (ew == 0) {
+            if (!mbar_wait(&bars->post, post_it & 1u, ctx)) ok = false;
+            else {
+              const uint32_t idx = cusync::eval::tileIndex(st.out_policy, static_cast<uint32_t>(m_off),
+                                                           static_cast<uint32_t>(n_off), st.grid.x, st.grid.y);
+              const uint32_t pv = cusync::eval::postValue(st.out_policy);
+              __threadfence();
+              if (st.opts & CUSYNC_OPT_NO_ATOMIC_ADD) cusync::storeRelease(st.sems_post + idx, pv * st.iter);
+              else                                    cusync::addRelease(st.sems_post + idx, pv);
+            }
+          }
+        }
+        post_it++;
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      }
+    }
+    if (lane == 0) tma_store_wait_all();
+  }
+
+  // Teardown (normal and abort paths alike).
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* sym = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+      q != cudaDriverEntryPointSuccess || sym == nullptr) {
+    (void)cudaGetLastError();
+    return nullptr;
+  }
+  fn = reinterpret_cast<EncodeTiledFn>(sym);
+  return fn;
+}
+
+// 2-D fp16 tensor map over a row-major [rows, cols] matrix with leading
+// dimension ld (elements); box = box_cols x box_rows, 128-byte swizzle.
+bool make_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_cols,
+              uint32_t box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const GemmParams);
+
+struct KernelEntry { KernelFn fn; uint32_t smem; };
+
+template <int BN, bool DUAL>
+KernelEntry entry() { return KernelEntry{cusync_gemm_kernel<BN, DUAL>, Cfg<BN, DUAL>::kSmemBytes}; }
+
+bool select_kernel(int tile_n, bool dual, KernelEntry* out) {
+  if (!dual) {
+    switch (tile_n) {
+      case 64:  *out = entry<64, false>(); return true;
+      case 128: *out = entry<128, false>(); return true;
+      case 256: *out = entry<256, false>(); return true;
+      default: return false;
+    }
+  }
+  switch (tile_n) {
+    case 64:  *out = entry<64, true>(); return true;
+    case 128: *out = entry<128, true>(); return true;
+    default: return false;
+  }
+}
+
+}  // namespace
+
+struct cusync_gemm_plan {
+  cusync_gemm_desc_t desc;
+  CUtensorMap tmA, tmB, tmB2, tmD;
+  GemmParams params;
+  KernelEntry kernel;
+  int tile_n;
+  uint32_t num_ctas;
+  cusync_stage_t* own_stage;   // created when the caller passes no stage
+  cusync_stage_t* stage;
+};
+
+namespace {
+
+int build_maps(cusync_gemm_plan* pl) {
+  const cusync_gemm_desc_t& d = pl->desc;
+  const bool dual = d.epilogue == CUSYNC_EPILOGUE_SILU_MUL_DUAL;
+  bool ok = make_map(&pl->tmA, d.a, d.m, d.k, d.lda, kBlockK, kBlockM);
+  if (d.b_layout == CUSYNC_B_ROW_MAJOR_NK) {
+    ok = ok && make_map(&pl->tmB, d.b, d.n, d.k, d.ldb, kBlockK, pl->tile_n);
+    if (dual) ok = ok && make_map(&pl->tmB2, d.b2, d.n, d.k, d.ldb, kBlockK, pl->tile_n);
+  } else {
+    ok = ok && make_map(&pl->tmB, d.b, d.k, d.n, d.ldb, 64, kBlockK);
+    if (dual) ok = ok && make_map(&pl->tmB2, d.b2, d.k, d.n, d.ldb, 64, kBlockK);
+  }
+  if (!dual) pl->tmB2 = pl->tmB;
+  ok = ok && make_map(&pl->tmD, d.d, d.m, d.n, d.ldd, kStoreCols, 32);
+  return ok ? CUSYNC_SUCCESS : CUSYNC_ERROR_CUDA;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace
+
+extern "C" {
+
+int cusync_gemm_default_tile_n(int32_t m, int32_t n, int32_t k, int32_t epilogue) {
+  (void)k;
+  if (epilogue == CUSYNC_EPILOGUE_SILU_MUL_DUAL) return m <= 128 ? 64 : 128;
+  if (m <= 128) return 64;        // weight-bandwidth bound: more, narrower tiles
+  if (n % 256 == 0 || n >= 2048) return 256;
+  return 128;
+}
+
+int cusync_gemm_plan_create(cusync_gemm_plan_t** out, const cusync_gemm_desc_t* desc) {
+  if (out == nullptr || desc == nullptr) return CUSYNC_ERROR_INVALID_ARGUMENT;
+  *out = nullptr;
+  const cusync_gemm_desc_t& d = *desc;
+  if (d.m <= 0 || d.n <= 0 || d.k <= 0 || d.a == nullptr || d.b == nullptr || d.d == nullptr)
+    return CUSYNC_ERROR_INVALID_ARGUMENT;
+  const bool dual = d.epilogue == CUSYNC_EPILOGUE_SILU_MUL_DUAL;
+  if (d.epilogue < CUSYNC_EPILOGUE_NONE || d.epilogue > CUSYNC_EPILOGUE_SILU_MUL_DUAL)
+    return CUSYNC_ERROR_INVALID_ARGUMENT;
+  if (dual && d.b2 == nullptr) return CUSYNC_ERROR_INVALID_ARGUMENT;
+  // TMA needs 16-byte aligned bases and row pitches; fp16 => multiples of 8 elements.
+  if (!aligned16(d.a) || !aligned16(d.b) || !aligned16(d.d) || (dual && !aligned16(d.b2)))
+    return CUSYNC_ERROR_UNSUPPORTED;
+  if (d.lda % 8 || d.ldb % 8 || d.ldd % 8 || d.lda < d.k || d.ldd < d.n) return CUSYNC_ERROR_UNSUPPORTED;
+  if (d.b_layout == CUSYNC_B_ROW_MAJOR_NK ? d.ldb < d.k : d.ldb < d.n) return CUSYNC_ERROR_UNSUPPORTED;
+  if (d.b_layout != CUSYNC_B_ROW_MAJOR_KN && d.b_layout != CUSYNC_B_ROW_MAJOR_NK)
+    return CUSYNC_ERROR_INVALID_ARGUMENT;
+
+  cusync_gemm_plan* pl = new (std::nothrow) cusync_gemm_plan();
+  if (!pl) return CUSYNC_ERROR_CUDA;
+  std::memset(pl, 0, sizeof(*pl));
+  pl->desc = d;
+  pl->tile_n = d.tile_n ? d.tile_n : cusync_gemm_default_tile_n(d.m, d.n, d.k, d.epilogue);
+  if (!select_kernel(pl->tile_n, dual, &pl->kernel)) { delete pl; return CUSYNC_ERROR_UNSUPPORTED; }
+
+  GemmParams& p = pl->params;
+  p.m = d.m; p.n = d.n; p.k = d.k;
+  p.tiles_n = (d.n + pl->tile_n - 1) / pl->tile_n;
+  p.tiles_m = (d.m + kBlockM - 1) / kBlockM;
+  p.num_tiles = p.tiles_n * p.tiles_m;
+  p.num_k_blocks = (d.k + kBlockK - 1) / kBlockK;
+  p.epilogue = d.epilogue;
+  p.b_kmajor = d.b_layout == CUSYNC_B_ROW_MAJOR_NK ? 1 : 0;
+  if (p.b_kmajor) {
+    // K-major, 128-byte swizzle: rows are 128 B apart, 8-row groups 1024 B apart; one UMMA K step
+    // (16 fp16) is 32 B along the row.  The leading offset is unused for swizzled K-major operands.
+    p.b_lbo = 16; p.b_sbo = 1024; p.b_kstep = 32;
+  } else {
+    // MN-major ([k,n] row-major), 128-byte swizzle: each TMA box holds 64 columns x kBlockK rows;
+    // 64-column groups are one box (kBlockK * 128 B) apart, 8-row K groups 1024 B apart, and one
+    // UMMA K step is 16 rows = 2048 B.
+    p.b_lbo = kBlockK * 128; p.b_sbo = 1024; p.b_kstep = kUmmaK * 128;
+  }
+  if (const char* dbg = getenv("CUSYNC_DEBUG_BDESC")) {
+    unsigned a = 0, b = 0, c = 0;
+    if (sscanf(dbg, "%u,%u,%u", &a, &b, &c) == 3) { p.b_lbo = a; p.b_sbo = b; p.b_kstep = c; }
+  }
+
+  pl->stage = d.stage;
+  if (pl->stage == nullptr) {
+    cusync_dim3_t grid = {static_cast<uint32_t>(p.tiles_n), static_cast<uint32_t>(p.tiles_m), 1};
+    cusync_dim3_t ts = {1, 1, 1};
+    int rc = cusync_stage_create(&pl->own_stage, grid, ts, CUSYNC_ORDER_TRANSPOSE_XY, nullptr, nullptr,
+                                 CUSYNC_OPT_NONE);
+    if (rc != CUSYNC_SUCCESS) { delete pl; return rc; }
+    pl->stage = pl->own_stage;
+  }
+  cusync_stage_view_t view;
+  cusync_stage_get_view(pl->stage, &view);
+  // The stage's grid is the tile grid (N tiles, M tiles, split-K = 1), as
+  // CuSyncGemmHorizontalThreadblockSwizzle lays it out.
+  if (view.grid.x != static_cast<uint32_t>(p.tiles_n) || view.grid.y != static_cast<uint32_t>(p.tiles_m) ||
+      view.grid.z != 1) {
+    if (pl->own_stage) cusync_stage_destroy(pl->own_stage);
+    delete pl;
+    return CUSYNC_ERROR_INVALID_ARGUMENT;
+  }
+  if (view.in_policy.kind != CUSYNC_POLICY_NOSYNC && view.sems_wait == nullptr) {
+    if (pl->own_stage) cusync_stage_destroy(pl->own_stage);
+    delete pl;
+    return CUSYNC_ERROR_NOT_INITIALIZED;   // consumer not wired to a producer yet
+  }
+
+  int sms = cusync_b200_sm_count();
+  if (sms <= 0) sms = 148;
+  uint32_t cap = d.max_ctas > 0 ? static_cast<uint32_t>(d.max_ctas) : static_cast<uint32_t>(sms);
+  pl->num_ctas = static_cast<uint32_t>(p.num_tiles) < cap ? static_cast<uint32_t>(p.num_tiles) : cap;
+
+  int rc = build_maps(pl);
+  if (rc == CUSYNC_SUCCESS &&
+      cudaFuncSetAttribute(reinterpret_cast<const void*>(pl->kernel.fn), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(pl->kernel.smem)) != cudaSuccess) {
+    (void)cudaGetLastError();
+    rc = CUSYNC_ERROR_CUDA;
+  }
+  if (rc != CUSYNC_SUCCESS) {
+    if (pl->own_stage) cusync_stage_destroy(pl->own_stage);
+    delete pl;
+    return rc;
+  }
+  *out = pl;
+  return CUSYNC_SUCCESS;
+}
+
+int cusync_gemm_plan_destroy(cusync_gemm_plan_t* pl) {
+  if (!pl) return CUSYNC_ERROR_NOT_INITIALIZED;
+  if (pl->own_stage) cusync_stage_destroy(pl->own_stage);
+  delete pl;
+  return CUSYNC_SUCCESS;
+}
+
+int cusync_gemm_plan_update(cusync_gemm_plan_t* pl, const void* a, const void* b, const void* b2, void* d) {
+  if (!pl) return CUSYNC_ERROR_NOT_INITIALIZED;
+  if (a) pl->desc.a = a;
+  if (b) pl->desc.b = b;
+  if (b2) pl->desc.b2 = b2;
+  if (d) pl->desc.d = d;
+  if (!aligned16(pl->desc.a) || !aligned16(pl->desc.b) || !aligned16(pl->desc.d)) return CUSYNC_ERROR_UNSUPPORTED;
+  return build_maps(pl);
+}
+
+uint32_t cusync_gemm_plan_num_ctas(const cusync_gemm_plan_t* pl) { return pl ? pl->num_ctas : 0; }
+
+int cusync_gemm_run(cusync_gemm_plan_t* pl, cusync_stream_t stream) {
+  if (!pl) return CUSYNC_ERROR_NOT_INITIALIZED;
+  GemmParams p = pl->params;
+  cusync_stage_get_view(pl->stage, &p.stage);   // picks up the current iter
+  p.is_producer = p.stage.out_policy.kind != CUSYNC_POLICY_NOSYNC;
+  p.is_consumer = p.stage.in_policy.kind != CUSYNC_POLICY_NOSYNC;
+  if (p.is_producer) cusync_stage_note_launch(pl->stage, pl->num_ctas);
+  pl->kernel.fn<<<pl->num_ctas, kThreads, pl->kernel.smem, reinterpret_cast<cudaStream_t>(stream)>>>(
+      pl->tmA, pl->tmB, pl->tmB2, pl->tmD, p);
+  return cudaGetLastError() == cudaSuccess ? CUSYNC_SUCCESS : CUSYNC_ERROR_CUDA;
+}
+
+}  // extern "C"

@@ -1,0 +1,226 @@
+// Stage objects of the C ABI: the device-side state a CuStage owns (schedule
+// buffer, ticket counter, semaphores, started words, timeout record), the
+// producer/consumer wiring, and the wait kernel.
+//
+// Replaces, for sm_100a: CuStage's constructor and buildScheduleBuffer
+// (src/include/cusync/cusync.h:125-198), CuSync::setProducerConsumerPair
+// (cusync.h:287-299) and waitKernel / invokeWaitKernel (src/cusync.cu:11-25).
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "common.cuh"
+
+struct cusync_stage {
+  cusync_stage_view_t view;      // host master copy; `iter` lives here
+  bool is_producer;
+  bool is_consumer;
+  bool linked;
+  uint32_t num_tiles;
+  uint32_t num_sems;             // entries of the semaphore array this stage owns
+  uint64_t blocks_launched;      // persistent-kernel blocks launched over all runs
+  bool     launch_noted;         // a persistent launch was noted for the current run
+  int device;
+};
+
+namespace {
+
+// One thread spins until *sem >= value, with back-off and a time bound.
+__global__ void waitKernel(const uint32_t* sem, uint32_t value, uint32_t* status, uint64_t timeout_ns) {
+  if (threadIdx.x != 0) return;
+  uint32_t seen = 0;
+  if (!cusync::spinUntilAtLeast(sem, value, timeout_ns, &seen))
+    cusync::recordTimeout(status, 3u, 0, 0, 0, 0, seen, value);
+}
+
+bool policy_ok(const cusync_policy_t* p) {
+  if (p == nullptr) return true;
+  if (p->kind < CUSYNC_POLICY_NOSYNC || p->kind > CUSYNC_POLICY_CONSECUTIVETILESYNC) return false;
+  if (p->kind == CUSYNC_POLICY_NOSYNC) return true;
+  if (p->tile_m == 0 || p->tile_n == 0) return false;
+  if (p->kind == CUSYNC_POLICY_CONV2DTILESYNC && p->p0 == 0) return false;
+  if (p->kind == CUSYNC_POLICY_STRIDEDTILESYNC && (p->p0 < p->tile_n || p->p1 == 0)) return false;
+  if (p->kind == CUSYNC_POLICY_CONSECUTIVETILESYNC && (p->p0 / 8) < p->tile_n) return false;
+  return true;
+}
+
+}  // namespace
+
+extern "C" {
+
+int cusync_stage_create(cusync_stage_t** out, cusync_dim3_t grid, cusync_dim3_t tile_size, int order,
+                        const cusync_policy_t* in_policy, const cusync_policy_t* out_policy, int opts) {
+  if (out == nullptr) return CUSYNC_ERROR_INVALID_ARGUMENT;
+  *out = nullptr;
+  if (grid.x == 0 || grid.y == 0 || grid.z == 0) return CUSYNC_ERROR_INVALID_ARGUMENT;
+  if (order != CUSYNC_ORDER_IDENTITY && order != CUSYNC_ORDER_TRANSPOSE_XY) return CUSYNC_ERROR_INVALID_ARGUMENT;
+  if (!policy_ok(in_policy) || !policy_ok(out_policy)) return CUSYNC_ERROR_INVALID_ARGUMENT;
+  uint64_t n64 = (uint64_t)grid.x * grid.y * grid.z;
+  if (n64 > (1ull << 30)) return CUSYNC_ERROR_INVALID_ARGUMENT;
+
+  cusync_stage* s = new (std::nothrow) cusync_stage();
+  if (s == nullptr) return CUSYNC_ERROR_CUDA;
+  std::memset(s, 0, sizeof(*s));
+  s->num_tiles = (uint32_t)n64;
+  s->view.grid = grid;
+  s->view.tile_size = tile_size;
+  s->view.iter = 1;
+  s->view.opts = opts;
+  s->view.order = order;
+  if (in_policy) s->view.in_policy = *in_policy;
+  if (out_policy) s->view.out_policy = *out_policy;
+  s->is_consumer = s->view.in_policy.kind != CUSYNC_POLICY_NOSYNC;
+  s->is_producer = s->view.out_policy.kind != CUSYNC_POLICY_NOSYNC;
+  s->view.timeout_ns = cusync::kDefaultSpinTimeoutNs;
+  if (cudaGetDevice(&s->device) != cudaSuccess) { delete s; return CUSYNC_ERROR_CUDA; }
+
+  // Schedule buffer: slot blockIndex(grid, block) holds block (x, y, z).  Both
+  // tile orders linearise the launch grid x-fastest; a slot written twice or a
+  // slot out of range is the invalid-linear-index error.
+  std::vector<cusync_dim3_t> order_host(s->num_tiles, cusync_dim3_t{s->num_tiles, 0, 0});
+  bool invalid = false;
+  for (uint32_t z = 0; z < grid.z; z++)
+    for (uint32_t y = 0; y < grid.y; y++)
+      for (uint32_t x = 0; x < grid.x; x++) {
+        uint32_t id = cusync::eval::blockIndex(grid.x, grid.y, x, y, z);
+        if (id >= s->num_tiles || order_host[id].x != s->num_tiles) { invalid = true; continue; }
+        order_host[id] = cusync_dim3_t{x, y, z};
+      }
+
+  // One allocation for the small words: ticket counter, started[2], status[8].
+  uint32_t* words = nullptr;
+  bool ok = cudaMalloc(&words, 16 * sizeof(uint32_t)) == cudaSuccess &&
+            cudaMemset(words, 0, 16 * sizeof(uint32_t)) == cudaSuccess &&
+            cudaMalloc(&s->view.tile_order, sizeof(cusync_dim3_t) * s->num_tiles) == cudaSuccess &&
+            cudaMemcpy(s->view.tile_order, order_host.data(), sizeof(cusync_dim3_t) * s->num_tiles,
+                       cudaMemcpyHostToDevice) == cudaSuccess;
+  if (ok && s->is_producer) {
+    s->num_sems = s->num_tiles;
+    ok = cudaMalloc(&s->view.sems_post, sizeof(uint32_t) * s->num_sems) == cudaSuccess &&
+         cudaMemset(s->view.sems_post, 0, sizeof(uint32_t) * s->num_sems) == cudaSuccess;
+  }
+  if (!ok) {
+    cudaFree(words); cudaFree(s->view.tile_order); cudaFree(s->view.sems_post);
+    delete s;
+    (void)cudaGetLastError();
+    return CUSYNC_ERROR_CUDA;
+  }
+  s->view.tile_counter = words;
+  s->view.started = words + 2;
+  s->view.status = words + 8;
+  *out = s;
+  return invalid ? CUSYNC_ERROR_INVALID_LINEAR_BLOCK_INDEX : CUSYNC_SUCCESS;
+}
+
+int cusync_stage_destroy(cusync_stage_t* s) {
+  if (s == nullptr) return CUSYNC_ERROR_NOT_INITIALIZED;
+  cudaFree(s->view.tile_counter);
+  cudaFree(s->view.tile_order);
+  cudaFree(s->view.sems_post);   // owned by the producer; consumers only alias it
+  delete s;
+  return CUSYNC_SUCCESS;
+}
+
+int cusync_stage_link(cusync_stage_t* prod, cusync_stage_t* cons) {
+  if (prod == nullptr || cons == nullptr) return CUSYNC_ERROR_NOT_INITIALIZED;
+  if (!prod->is_producer) return CUSYNC_ERROR_NOT_PRODUCER;
+  if (!cons->is_consumer) return CUSYNC_ERROR_NOT_CONSUMER;
+  if (prod->view.sems_post == nullptr) return CUSYNC_ERROR_NOT_INITIALIZED;
+  cons->view.prod_grid = prod->view.grid;
+  cons->view.sems_wait = prod->view.sems_post;
+  cons->linked = true;
+  return CUSYNC_SUCCESS;
+}
+
+int cusync_stage_increment_iter(cusync_stage_t* s) {
+  if (s == nullptr) return CUSYNC_ERROR_NOT_INITIALIZED;
+  s->view.iter += 1;
+  s->launch_noted = false;
+  return CUSYNC_SUCCESS;
+}
+
+int cusync_stage_reset(cusync_stage_t* s, cusync_stream_t stream) {
+  if (s == nullptr) return CUSYNC_ERROR_NOT_INITIALIZED;
+  cudaStream_t st = (cudaStream_t)stream;
+  bool ok = cudaMemsetAsync(s->view.tile_counter, 0, 16 * sizeof(uint32_t), st) == cudaSuccess;
+  if (ok && s->view.sems_post)
+    ok = cudaMemsetAsync(s->view.sems_post, 0, sizeof(uint32_t) * s->num_sems, st) == cudaSuccess;
+  s->view.iter = 1;
+  s->blocks_launched = 0;
+  s->launch_noted = false;
+  return ok ? CUSYNC_SUCCESS : CUSYNC_ERROR_CUDA;
+}
+
+int cusync_stage_get_view(const cusync_stage_t* s, cusync_stage_view_t* out) {
+  if (s == nullptr || out == nullptr) return CUSYNC_ERROR_NOT_INITIALIZED;
+  *out = s->view;
+  return CUSYNC_SUCCESS;
+}
+
+int cusync_stage_set_timeout_ns(cusync_stage_t* s, uint64_t ns) {
+  if (s == nullptr) return CUSYNC_ERROR_NOT_INITIALIZED;
+  s->view.timeout_ns = ns ? ns : cusync::kDefaultSpinTimeoutNs;
+  return CUSYNC_SUCCESS;
+}
+
+int cusync_stage_note_launch(cusync_stage_t* s, uint32_t num_blocks) {
+  if (s == nullptr) return CUSYNC_ERROR_NOT_INITIALIZED;
+  s->blocks_launched += num_blocks;
+  s->launch_noted = true;
+  return CUSYNC_SUCCESS;
+}
+
+int cusync_wait_kernel(uint32_t* semaphore, uint32_t given_value, cusync_stream_t stream, uint32_t* status,
+                       uint64_t timeout_ns) {
+  if (semaphore == nullptr) return CUSYNC_ERROR_NOT_INITIALIZED;
+  waitKernel<<<1, 1, 0, (cudaStream_t)stream>>>(semaphore, given_value, status, timeout_ns);
+  return cudaGetLastError() == cudaSuccess ? CUSYNC_SUCCESS : CUSYNC_ERROR_CUDA;
+}
+
+int cusync_stage_invoke_wait_kernel(cusync_stage_t* s, cusync_stream_t stream) {
+  if (s == nullptr) return CUSYNC_ERROR_NOT_INITIALIZED;
+  if (!s->is_producer) return CUSYNC_ERROR_NOT_PRODUCER;
+  if (s->view.opts & CUSYNC_OPT_AVOID_WAIT_KERNEL) return CUSYNC_SUCCESS;
+  if (s->launch_noted)   // persistent kernel: wait until every block of the launch is resident
+    return cusync_wait_kernel(s->view.started + 1, (uint32_t)s->blocks_launched, stream, s->view.status,
+                              s->view.timeout_ns);
+  return cusync_wait_kernel(s->view.started, s->view.iter, stream, s->view.status, s->view.timeout_ns);
+}
+
+int cusync_stage_read_tile_order(const cusync_stage_t* s, cusync_dim3_t* out, uint32_t count) {
+  if (s == nullptr || out == nullptr) return CUSYNC_ERROR_NOT_INITIALIZED;
+  if (count > s->num_tiles) return CUSYNC_ERROR_INVALID_ARGUMENT;
+  return cudaMemcpy(out, s->view.tile_order, sizeof(cusync_dim3_t) * count, cudaMemcpyDeviceToHost) == cudaSuccess
+             ? CUSYNC_SUCCESS : CUSYNC_ERROR_CUDA;
+}
+
+int cusync_stage_read_semaphores(const cusync_stage_t* s, uint32_t* out, uint32_t count) {
+  if (s == nullptr || out == nullptr) return CUSYNC_ERROR_NOT_INITIALIZED;
+  if (!s->is_producer) return CUSYNC_ERROR_NOT_PRODUCER;
+  if (count > s->num_sems) return CUSYNC_ERROR_INVALID_ARGUMENT;
+  return cudaMemcpy(out, s->view.sems_post, sizeof(uint32_t) * count, cudaMemcpyDeviceToHost) == cudaSuccess
+             ? CUSYNC_SUCCESS : CUSYNC_ERROR_CUDA;
+}
+
+int cusync_stage_read_status(const cusync_stage_t* s, cusync_status_t* out) {
+  if (s == nullptr || out == nullptr) return CUSYNC_ERROR_NOT_INITIALIZED;
+  return cudaMemcpy(out, s->view.status, sizeof(cusync_status_t), cudaMemcpyDeviceToHost) == cudaSuccess
+             ? CUSYNC_SUCCESS : CUSYNC_ERROR_CUDA;
+}
+
+uint32_t cusync_stage_num_tiles(const cusync_stage_t* s) { return s ? s->num_tiles : 0; }
+uint32_t cusync_stage_iter(const cusync_stage_t* s) { return s ? s->view.iter : 0; }
+
+const char* cusync_b200_version(void) { return "cusync_b200 0.1 (sm_100a)"; }
+
+int cusync_b200_sm_count(void) {
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return -1;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -1;
+  return n;
+}
+
+}  // extern "C"

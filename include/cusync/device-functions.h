@@ -1,0 +1,83 @@
+// Device-side primitives of the semaphore layer, written for sm_100a:
+//  * publish  = red.release.gpu (or st.release.gpu when a semaphore has a
+//    single poster) -- gpu scope is enough, both kernels run on one device;
+//  * observe  = ld.acquire.gpu in a loop with nanosleep back-off that gives up
+//    after a time bound and leaves a record, instead of spinning forever.
+// The reference's counterparts are globalVolatileLoad / globalLoad
+// (src/include/cusync/device-functions.h:14-32) and the loops in
+// cusync_device_defs.h:33-72.
+#pragma once
+
+#include <stdint.h>
+#include "../cusync_b200.h"
+#include "cusync_defines.h"
+
+#if defined(__CUDACC__) || defined(__NVCC__)
+
+namespace cusync {
+
+// Default bound of a device-side spin when the stage does not set one.
+static constexpr uint64_t kDefaultSpinTimeoutNs = 2000000000ull;
+
+CUSYNC_DEVICE uint32_t loadAcquire(const uint32_t* addr) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+
+CUSYNC_DEVICE uint32_t loadRelaxed(const uint32_t* addr) {
+  uint32_t v;
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+
+CUSYNC_DEVICE void addRelease(uint32_t* addr, uint32_t value) {
+  asm volatile("red.release.gpu.global.add.u32 [%0], %1;" :: "l"(addr), "r"(value) : "memory");
+}
+
+CUSYNC_DEVICE void storeRelease(uint32_t* addr, uint32_t value) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" :: "l"(addr), "r"(value) : "memory");
+}
+
+CUSYNC_DEVICE uint64_t globalTimerNs() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Names kept from the reference for code that calls them directly.
+CUSYNC_DEVICE uint32_t globalVolatileLoad(volatile uint32_t* addr) { return loadAcquire((const uint32_t*)addr); }
+CUSYNC_DEVICE uint32_t globalLoad(volatile uint32_t* addr) { return loadRelaxed((const uint32_t*)addr); }
+
+// First timeout wins the record; later ones leave it alone.
+CUSYNC_DEVICE void recordTimeout(uint32_t* status, uint32_t where, uint32_t tx, uint32_t ty, uint32_t tz,
+                                 uint32_t idx, uint32_t seen, uint32_t expected) {
+  if (status == nullptr) return;
+  if (atomicCAS(status, 0u, (uint32_t)CUSYNC_ERROR_TIMEOUT) == 0u) {
+    status[1] = where; status[2] = tx; status[3] = ty; status[4] = tz;
+    status[5] = idx; status[6] = seen; status[7] = expected;
+    __threadfence();
+  }
+}
+
+// Spin until *sem >= expected.  Returns false (after recording why) when the
+// bound expires.  Called by ONE thread; the caller broadcasts the outcome.
+CUSYNC_DEVICE bool spinUntilAtLeast(const uint32_t* sem, uint32_t expected, uint64_t timeoutNs,
+                                    uint32_t* seenOut) {
+  uint32_t v = loadAcquire(sem);
+  if (v >= expected) { *seenOut = v; return true; }
+  const uint64_t t0 = globalTimerNs();
+  const uint64_t bound = timeoutNs ? timeoutNs : kDefaultSpinTimeoutNs;
+  uint32_t backoff = 32;
+  while (true) {
+    __nanosleep(backoff);
+    if (backoff < 1024) backoff <<= 1;
+    v = loadAcquire(sem);
+    if (v >= expected) { *seenOut = v; return true; }
+    if (globalTimerNs() - t0 > bound) { *seenOut = v; return false; }
+  }
+}
+
+}  // namespace cusync
+
+#endif  // __CUDACC__

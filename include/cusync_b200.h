@@ -1,0 +1,226 @@
+/*
+ * cusync_b200 -- C ABI of the B200-native CuSync library (libcusync_b200.so).
+ *
+ * Plain C: opaque handles, POD descriptors, int status codes, caller-owned
+ * device memory, explicit streams.  The C++ template API in <cusync/cusync.h>
+ * (CuStage, CuSync, the sync policies, tile orders) is a thin layer over these
+ * entry points, and so is any foreign-language binding.
+ *
+ * Every entry point cites the interface of microsoft/cusync it replaces
+ * (paths relative to that project's root).
+ */
+#ifndef CUSYNC_B200_H
+#define CUSYNC_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(_WIN32)
+  #define CUSYNC_API
+#else
+  #define CUSYNC_API __attribute__((visibility("default")))
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* cusync_stream_t;   /* a cudaStream_t */
+
+typedef struct cusync_dim3 { uint32_t x, y, z; } cusync_dim3_t;
+
+/* Status codes.  The first six keep the reference's enumerator order
+ * (src/include/cusync/cusync.h:46-53): success is 5, not 0. */
+enum {
+  CUSYNC_ERROR_NOT_PRODUCER = 0,
+  CUSYNC_ERROR_NOT_CONSUMER = 1,
+  CUSYNC_ERROR_NOT_INITIALIZED = 2,
+  CUSYNC_ERROR_INVALID_LINEAR_BLOCK_INDEX = 3,
+  CUSYNC_ERROR_CUDA = 4,
+  CUSYNC_SUCCESS = 5,
+  /* additions */
+  CUSYNC_ERROR_TIMEOUT = 6,            /* a bounded device-side wait gave up */
+  CUSYNC_ERROR_INVALID_ARGUMENT = 7,
+  CUSYNC_ERROR_UNSUPPORTED = 8         /* shape/alignment outside what the kernels implement */
+};
+
+/* Optimizations bit set (src/include/cusync/cusync.h:69-75). */
+enum {
+  CUSYNC_OPT_NONE = 0,
+  CUSYNC_OPT_NO_ATOMIC_ADD = 1,
+  CUSYNC_OPT_AVOID_WAIT_KERNEL = 2,
+  CUSYNC_OPT_AVOID_CUSTOM_ORDER = 4,
+  CUSYNC_OPT_REORDER_TILE_LOADS = 8
+};
+
+/* Tile orders (src/include/cusync/tile-orders.h:50-76). */
+enum { CUSYNC_ORDER_IDENTITY = 0, CUSYNC_ORDER_TRANSPOSE_XY = 1 };
+
+/* Sync policies as data.  NOSYNC/ROWSYNC/TILESYNC/CONV2DTILESYNC:
+ * src/include/cusync/policies.h:18-210.  STRIDEDTILESYNC: StridedSync,
+ * src/ml-bench/transformer/mlp.cu:76-101.  CONSECUTIVETILESYNC:
+ * ConsecutiveSync, src/ml-bench/transformer/attention.cu:51-70. */
+enum {
+  CUSYNC_POLICY_NOSYNC = 0,
+  CUSYNC_POLICY_ROWSYNC = 1,
+  CUSYNC_POLICY_TILESYNC = 2,
+  CUSYNC_POLICY_STRIDEDTILESYNC = 3,
+  CUSYNC_POLICY_CONV2DTILESYNC = 4,
+  CUSYNC_POLICY_CONSECUTIVETILESYNC = 5
+};
+
+typedef struct cusync_policy {
+  int32_t  kind;        /* CUSYNC_POLICY_* */
+  int32_t  order;       /* CUSYNC_ORDER_* used to linearise the semaphore index */
+  uint32_t tile_m;      /* TileM template argument of the reference policy */
+  uint32_t tile_n;      /* TileN template argument */
+  uint32_t wait_value;  /* waitValue_ (ROW / TILE / CONV2D) */
+  uint32_t post_value;  /* postValue_ (ROW / TILE / CONV2D) */
+  uint32_t p0;          /* STRIDED: GridN, CONV2D: R*S, CONSECUTIVE: H */
+  uint32_t p1;          /* STRIDED: stride */
+} cusync_policy_t;
+
+/* Record a bounded wait leaves behind when it gives up. */
+typedef struct cusync_status {
+  uint32_t code;        /* 0 = nothing recorded, else CUSYNC_ERROR_TIMEOUT */
+  uint32_t where;       /* 1 semaphore wait, 2 pipeline barrier, 3 wait kernel */
+  uint32_t tile_x, tile_y, tile_z;
+  uint32_t sem_index;
+  uint32_t seen;
+  uint32_t expected;
+} cusync_status_t;
+
+/* What a kernel needs of a stage, passed by value in its parameters -- the
+ * role the by-value CuStage copy plays in the reference
+ * (gemm/device/cusyncgemm.h:352 `params_.custage`). */
+typedef struct cusync_stage_view {
+  cusync_dim3_t   grid;         /* tiles of this stage: (N tiles, M tiles, split-K) */
+  cusync_dim3_t   prod_grid;    /* the producer's grid, set by cusync_stage_link */
+  cusync_dim3_t   tile_size;
+  uint32_t        iter;         /* run counter, starts at 1 */
+  int32_t         opts;
+  int32_t         order;
+  int32_t         reserved;
+  cusync_policy_t in_policy;
+  cusync_policy_t out_policy;
+  cusync_dim3_t*  tile_order;   /* [numTiles] schedule buffer */
+  uint32_t*       tile_counter; /* ticket counter for tile_order */
+  uint32_t*       started;      /* [2]: [0] = iter stored by block 0 (reference protocol),
+                                   [1] = blocks started so far, all runs (persistent kernels) */
+  uint32_t*       sems_post;    /* semaphores this stage posts to (producer) */
+  uint32_t*       sems_wait;    /* semaphores this stage waits on (consumer) */
+  uint32_t*       status;       /* device copy of cusync_status_t */
+  uint64_t        timeout_ns;   /* bound of every device-side spin */
+} cusync_stage_view_t;
+
+typedef struct cusync_stage cusync_stage_t;
+
+/* ---- stages ------------------------------------------------------------- */
+
+/* CuStage::CuStage(grid, tileSize, inputPolicy, outputPolicy) incl.
+ * buildScheduleBuffer (cusync.h:125-157,176-198).  Allocates the schedule
+ * buffer, the ticket counter, and for a producer the semaphore array (one per
+ * tile, zeroed) and the started words.  Returns
+ * CUSYNC_ERROR_INVALID_LINEAR_BLOCK_INDEX when the order is not a bijection
+ * (the reference computes this error and drops it, cusync.h:184). */
+CUSYNC_API int cusync_stage_create(cusync_stage_t** out, cusync_dim3_t grid, cusync_dim3_t tile_size,
+                        int order, const cusync_policy_t* in_policy,
+                        const cusync_policy_t* out_policy, int opts);
+
+/* The reference never frees a stage's device memory (no destructor). */
+CUSYNC_API int cusync_stage_destroy(cusync_stage_t* stage);
+
+/* CuSync::setProducerConsumerPair (cusync.h:287-299). */
+CUSYNC_API int cusync_stage_link(cusync_stage_t* producer, cusync_stage_t* consumer);
+
+/* CuStage::incrementIter (cusync.h:212).  The handle is the single owner of
+ * `iter`; views taken afterwards carry the new value. */
+CUSYNC_API int cusync_stage_increment_iter(cusync_stage_t* stage);
+
+/* No counterpart: zero the semaphores, ticket and started words and set
+ * iter = 1, so a stage can be reused after an error. */
+CUSYNC_API int cusync_stage_reset(cusync_stage_t* stage, cusync_stream_t stream);
+
+/* The by-value copy a kernel takes (cusyncgemm.h:352). */
+CUSYNC_API int cusync_stage_get_view(const cusync_stage_t* stage, cusync_stage_view_t* out);
+
+/* Bound, in nanoseconds, of every device-side spin of kernels using this
+ * stage (the reference spins forever, cusync_device_defs.h:41-43). */
+CUSYNC_API int cusync_stage_set_timeout_ns(cusync_stage_t* stage, uint64_t ns);
+
+/* CuStage::invokeWaitKernel (cusync.h:203-209): enqueue on `stream` a
+ * one-thread kernel that returns once this producer's kernel has started. */
+CUSYNC_API int cusync_stage_invoke_wait_kernel(cusync_stage_t* producer, cusync_stream_t stream);
+
+/* Tells the stage that a persistent kernel of `num_blocks` blocks was
+ * launched for the current run; the next wait kernel then waits until all of
+ * them are resident instead of only block 0. */
+CUSYNC_API int cusync_stage_note_launch(cusync_stage_t* stage, uint32_t num_blocks);
+
+/* cusync::invokeWaitKernel(uint32_t*, uint32_t, cudaStream_t)
+ * (src/include/cusync/wait-kernel.h:10, src/cusync.cu:11-25).  `status` may
+ * be NULL; `timeout_ns` 0 selects the default bound. */
+CUSYNC_API int cusync_wait_kernel(uint32_t* semaphore, uint32_t given_value, cusync_stream_t stream,
+                       uint32_t* status, uint64_t timeout_ns);
+
+/* Test access, the role of the reference's friend class CuSyncTest
+ * (tests/cusync-test.h:8-44): copy the schedule buffer / the producer's
+ * semaphores / the timeout record to the host (synchronous). */
+CUSYNC_API int cusync_stage_read_tile_order(const cusync_stage_t* stage, cusync_dim3_t* out, uint32_t count);
+CUSYNC_API int cusync_stage_read_semaphores(const cusync_stage_t* stage, uint32_t* out, uint32_t count);
+CUSYNC_API int cusync_stage_read_status(const cusync_stage_t* stage, cusync_status_t* out);
+CUSYNC_API uint32_t cusync_stage_num_tiles(const cusync_stage_t* stage);
+CUSYNC_API uint32_t cusync_stage_iter(const cusync_stage_t* stage);
+
+/* ---- GEMM --------------------------------------------------------------- */
+
+enum { CUSYNC_EPILOGUE_NONE = 0, CUSYNC_EPILOGUE_GELU_ERF = 1, CUSYNC_EPILOGUE_RELU = 2,
+       CUSYNC_EPILOGUE_SILU_MUL_DUAL = 3 };
+enum { CUSYNC_B_ROW_MAJOR_KN = 0, CUSYNC_B_ROW_MAJOR_NK = 1 };
+
+/* D[m,n] = epilogue(A[m,k] * B[k,n]); fp16 operands, fp32 accumulate, fp16
+ * out.  Replaces cutlass::gemm::device::CuSyncGemm<...>::Arguments
+ * (gemm/device/cusyncgemm.h:293-350): custage, problem_size, ref_A, ref_B,
+ * ref_D.  alpha = 1 and beta = 0 as in every reference driver
+ * (src/ml-bench/transformer/mlp.cu:239-240); split-K is 1. */
+typedef struct cusync_gemm_desc {
+  int32_t m, n, k;
+  const void* a; int64_t lda;      /* row-major [m,k] */
+  const void* b; int64_t ldb;      /* row-major [k,n] (b_layout 0) or [n,k] (b_layout 1) */
+  const void* b2;                  /* second B of CUSYNC_EPILOGUE_SILU_MUL_DUAL, same layout/ldb */
+  void* d; int64_t ldd;            /* row-major [m,n] */
+  int32_t b_layout;
+  int32_t epilogue;
+  int32_t tile_n;                  /* 0 = choose; else 32, 64, 128 or 256.  Tile M is 128. */
+  int32_t max_ctas;                /* 0 = one per SM */
+  cusync_stage_t* stage;           /* NULL = no tile synchronisation (stream-ordered use) */
+} cusync_gemm_desc_t;
+
+typedef struct cusync_gemm_plan cusync_gemm_plan_t;
+
+/* Tile shape the library would pick for a GEMM (tile M is always 128); lets
+ * the caller size the CuStage grid the way
+ * CuSyncGemmHorizontalThreadblockSwizzle::get_tiled_shape does
+ * (gemm/threadblock/cusync_threadblock_swizzle.h:12-54). */
+CUSYNC_API int cusync_gemm_default_tile_n(int32_t m, int32_t n, int32_t k, int32_t epilogue);
+
+/* can_implement + get_workspace_size + initialize
+ * (gemm/device/cusyncgemm.h:364-456). */
+CUSYNC_API int cusync_gemm_plan_create(cusync_gemm_plan_t** out, const cusync_gemm_desc_t* desc);
+CUSYNC_API int cusync_gemm_plan_destroy(cusync_gemm_plan_t* plan);
+/* update / updateA / updateC / updateD (gemm/device/cusyncgemm.h:459-494). */
+CUSYNC_API int cusync_gemm_plan_update(cusync_gemm_plan_t* plan, const void* a, const void* b,
+                            const void* b2, void* d);
+/* run(bool overlap, int*, cudaStream_t) (gemm/device/cusyncgemm.h:525-563). */
+CUSYNC_API int cusync_gemm_run(cusync_gemm_plan_t* plan, cusync_stream_t stream);
+/* Blocks the launch uses (persistent grid). */
+CUSYNC_API uint32_t cusync_gemm_plan_num_ctas(const cusync_gemm_plan_t* plan);
+
+/* Library / device information. */
+CUSYNC_API const char* cusync_b200_version(void);
+CUSYNC_API int cusync_b200_sm_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CUSYNC_B200_H */
