@@ -1,0 +1,363 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: one GPT-3 175B MLP layer, one 8-way
+tensor-parallel shard, as a chain of two tile-synchronised GEMMs.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--policy rowsync|tilesync]
+    python bench.py --impl reference ...          # the CPU host-reference path, timed on the host cores
+
+A step is one MLP layer over one batch of synthetic input (X ~ N(0,1),
+weights ~ N(0,0.02), seeded): producer GEMM (+GELU) on one stream, wait kernel
+and consumer GEMM on another, semaphores between them; with N > 1 GPUs an NCCL
+all-reduce of the [B, 12288] output follows on the consumer stream.  One JSON
+line is printed by rank 0.  Time-like metric: microseconds per layer.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "gpt3_mlp_layer_latency"
+UNIT = "us"
+SWEEP_BATCHES = [1, 64, 256, 512, 1024, 2048]
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "tflops_burst": p["bf16_tflops"],
+                "tflops_sustained": p.get("bf16_tflops_sustained", p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops_burst": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 7:
+                continue
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, r[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_reference_us(batch, sample_rows, hidden, ffn):
+    """The CPU host-reference path (oracle restatement of ref_cpumatmul + GELU) on `sample_rows` rows of the
+    layer, all host threads; returns (microseconds scaled to `batch` rows, threads, seconds spent)."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import numpy as np
+    import oracle_lib as o
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((sample_rows, hidden), dtype=np.float32).astype(np.float16)
+    w1 = (rng.standard_normal((hidden, ffn), dtype=np.float32) * 0.02).astype(np.float16)
+    w2 = (rng.standard_normal((ffn, hidden), dtype=np.float32) * 0.02).astype(np.float16)
+    o.gemm_f16(x[:16], w1, o.EPI_GELU_ERF)   # warm the library and the thread pool
+    t0 = time.perf_counter()
+    h = o.gemm_f16(x, w1, o.EPI_GELU_ERF)
+    o.gemm_f16(h, w2)
+    dt = time.perf_counter() - t0
+    return dt * 1e6 * batch / sample_rows, o.num_threads(), dt
+
+
+def run_reference(args, rank, world):
+    """--impl reference: the reference's CPU check path for this layer, on the host cores.  Its CUTLASS GPU
+    kernels cannot be built (un-vendored, un-pinned CUTLASS submodule), so the CPU path is the oracle's
+    restatement of ref_cpumatmul (kind "port")."""
+    if rank != 0:
+        return
+    from cusync_b200 import mlp as M
+    hidden, ffn = M.GPT3_HIDDEN, M.GPT3_FFN
+    sample = min(args.batch, 1024)
+    times = []
+    for i in range(args.warmup + args.steps):
+        us, threads, _ = cpu_reference_us(args.batch, sample, hidden, ffn)
+        if i >= args.warmup:
+            times.append(us)
+    val = statistics.mean(times)
+    line = {"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": val / 1000.0, "higher_is_better": False,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": workload_config(args, None),
+            "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port",
+                             "sample": "%d of %d rows through both GEMMs, scaled to the full batch" % (sample, args.batch)},
+            "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, shard):
+    cfg = {"workload": "GPT-3 175B MLP, one 8-way tensor-parallel shard: X[%d,12288] * W1[12288,6144] -> GELU -> "
+                       "* W2[6144,12288]" % args.batch,
+           "batch": args.batch, "policy": args.policy,
+           "l2": "inputs larger than L2 (302 MB of weights per step vs 126 MB L2); no explicit flush",
+           "all_reduce": "NCCL sum of Y[B,12288] fp16 across ranks" if args.gpus > 1 else "none (1 GPU)"}
+    if shard is not None:
+        cfg.update({"tile_m": 128, "tile_n1": shard.tile_n1, "tile_n2": shard.tile_n2,
+                    "ctas1": shard.ctas1, "ctas2": shard.ctas2})
+    return cfg
+
+
+def time_steps(step_fn, start_stream, end_stream, steps, warmup, barrier):
+    """Runs warmup + steps; returns (total ms over the K timed steps, per-step ms list)."""
+    import torch
+    for _ in range(warmup):
+        step_fn()
+    torch.cuda.synchronize()
+    barrier()
+    torch.cuda.synchronize()
+    begins = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    for i in range(steps):
+        # steps are serialised (a step may not overwrite H while the previous consumer reads it), so the
+        # begin mark goes after the previous step's last kernel
+        if start_stream is not end_stream:
+            start_stream.wait_stream(end_stream)
+        begins[i].record(start_stream)
+        step_fn()
+        ends[i].record(end_stream)
+    torch.cuda.synchronize()
+    barrier()
+    total = begins[0].elapsed_time(ends[-1])
+    per = [b.elapsed_time(e) for b, e in zip(begins, ends)]
+    return total, per
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--batch", type=int, default=2048)
+    ap.add_argument("--policy", default="rowsync", choices=["rowsync", "tilesync"])
+    ap.add_argument("--impl", default="cusync", choices=["cusync", "reference"])
+    ap.add_argument("--no-sweep", action="store_true", help="skip the per-batch table")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "cusync" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from cusync_b200 import mlp as M
+    from cusync_b200 import _lib as L
+    L.lib()   # fail loudly here if the CUDA library is not built
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    peaks = load_peaks()
+    ps = torch.cuda.Stream(priority=-1)   # producer: high priority, launched first
+    cs = torch.cuda.Stream(priority=0)
+
+    def build(batch, policy):
+        x, w1, w2, v = M.make_inputs("gpt3", batch, dev, seed=rank)
+        return M.MLPShard("gpt3", batch, x, w1, w2, v, policy=policy)
+
+    shard = build(args.batch, args.policy)
+
+    def cusync_step():
+        # a step may not overwrite H while the previous consumer still reads it
+        ps.wait_stream(cs)
+        shard.run_cusync(ps, cs)
+        if world > 1:
+            with torch.cuda.stream(cs):
+                dist.all_reduce(shard.y)
+
+    def ordered_step():
+        shard.run_stream_ordered(cs)
+        if world > 1:
+            with torch.cuda.stream(cs):
+                dist.all_reduce(shard.y)
+
+    def reduce_max(v):
+        if world == 1:
+            return v
+        t = torch.tensor([v], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- headline: overlapped chain ------------------------------------------------------------
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    total_ms, per_ms = time_steps(cusync_step, ps, cs, args.steps, args.warmup, barrier)
+    clocks = sampler.stop() if rank == 0 else None
+    total_ms = reduce_max(total_ms)
+    ms_per_step = total_ms / args.steps
+    codes = shard.status_codes()
+    if codes != (0, 0):
+        raise SystemExit("a bounded wait expired during the timed region: %r" % (codes,))
+
+    # ---- same kernels serialised by stream order --------------------------------------------
+    ord_total, ord_per = time_steps(ordered_step, cs, cs, args.steps, args.warmup, barrier)
+    ord_ms = reduce_max(ord_total) / args.steps
+
+    # ---- per-kernel durations (stream-ordered, events on the launching stream) ----------------
+    flops2 = 2.0 * args.batch * M.GPT3_FFN * M.GPT3_HIDDEN
+    g1, g2 = [], []
+    for i in range(args.warmup + args.steps):
+        e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        e0.record(cs)
+        shard.run_single(1, cs)
+        e1.record(cs)
+        shard.run_single(2, cs)
+        e2.record(cs)
+        torch.cuda.synchronize()
+        if i >= args.warmup:
+            g1.append(e0.elapsed_time(e1)); g2.append(e1.elapsed_time(e2))
+    t1_ms, t2_ms = statistics.mean(g1), statistics.mean(g2)
+    tensor_bound = args.batch >= 256
+    if tensor_bound:
+        achieved = flops2 / (t2_ms * 1e-3) / 1e12
+        peak = peaks["tflops_sustained"]
+        roofline = {"bound": "tensor", "kernel": "cusync_gemm_kernel<%d> (GEMM2, consumer)" % shard.tile_n2,
+                    "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                    "peak_kind": "%s sustained bf16/fp16 cuBLAS" % peaks["source"],
+                    "frac_of_burst_peak": achieved / peaks["tflops_burst"], "traffic": None,
+                    "launch_ms": t2_ms, "gemm1_ms": t1_ms,
+                    "gemm1_tflops": flops2 / (t1_ms * 1e-3) / 1e12}
+    else:
+        bytes2 = 2.0 * (M.GPT3_FFN * M.GPT3_HIDDEN + args.batch * (M.GPT3_FFN + M.GPT3_HIDDEN))
+        achieved = bytes2 / (t2_ms * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "kernel": "cusync_gemm_kernel<%d> (GEMM2, consumer)" % shard.tile_n2,
+                    "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                    "peak_kind": "%s copy bandwidth" % peaks["source"], "traffic": None, "launch_ms": t2_ms,
+                    "gemm1_ms": t1_ms}
+
+    # ---- end to end through the C ABI with host buffers ---------------------------------------
+    xh = torch.empty((args.batch, M.GPT3_HIDDEN), dtype=torch.half).pin_memory()
+    xh.copy_(shard.x.cpu())
+    yh = torch.empty((args.batch, M.GPT3_HIDDEN), dtype=torch.half).pin_memory()
+
+    def e2e_step():
+        ps.wait_stream(cs)
+        with torch.cuda.stream(ps):
+            shard.x.copy_(xh, non_blocking=True)
+        shard.run_cusync(ps, cs)
+        with torch.cuda.stream(cs):
+            if world > 1:
+                dist.all_reduce(shard.y)
+            yh.copy_(shard.y, non_blocking=True)
+
+    e2e_total, _ = time_steps(e2e_step, ps, cs, args.steps, args.warmup, barrier)
+    e2e_us = reduce_max(e2e_total) / args.steps * 1000.0
+    io_bytes = args.batch * M.GPT3_HIDDEN * 2
+
+    # ---- per-batch table ------------------------------------------------------------------------
+    table = []
+    if not args.no_sweep and world == 1:
+        for b in SWEEP_BATCHES:
+            row = {"batch": b}
+            for pol in ("rowsync", "tilesync"):
+                s = build(b, pol)
+
+                def c_step(s=s):
+                    ps.wait_stream(cs)
+                    s.run_cusync(ps, cs)
+
+                def o_step(s=s):
+                    s.run_stream_ordered(cs)
+
+                _, c_per = time_steps(c_step, ps, cs, 20, 5, barrier)
+                _, o_per = time_steps(o_step, cs, cs, 20, 5, barrier)
+                c_us, o_us = statistics.median(c_per) * 1000, statistics.median(o_per) * 1000
+                row[pol + "_us"] = round(c_us, 2)
+                row["stream_ordered_us"] = round(o_us, 2)
+                row[pol + "_gain_pct"] = round(100.0 - c_us / o_us * 100.0, 2)
+                row["tile_n"] = [s.tile_n1, s.tile_n2]
+                if s.status_codes() != (0, 0):
+                    row["error"] = "bounded wait expired"
+                s.destroy()
+            row["tflops_best"] = round(shard.flops() / args.batch * b / (min(row["rowsync_us"], row["tilesync_us"],
+                                                                            row["stream_ordered_us"]) * 1e-6) / 1e12, 1)
+            table.append(row)
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    value_us = ms_per_step * 1000.0
+    line = {"metric": METRIC, "value": value_us, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": workload_config(args, shard),
+            "median_us": statistics.median(per_ms) * 1000.0,
+            "stream_ordered_us": ord_ms * 1000.0,
+            "gain_vs_stream_ordered_pct": 100.0 - ms_per_step / ord_ms * 100.0,
+            "layer_tflops": shard.flops() / (ms_per_step * 1e-3) / 1e12,
+            "layer_frac_of_sustained_peak": shard.flops() / (ms_per_step * 1e-3) / 1e12 / peaks["tflops_sustained"],
+            "roofline": roofline,
+            "e2e": {"value": e2e_us, "unit": UNIT, "h2d_bytes_per_step": io_bytes, "d2h_bytes_per_step": io_bytes},
+            "gpu_launches": 3 * args.steps,
+            "clocks": clocks,
+            "per_batch": table}
+    if not args.no_cpu:
+        sample = args.batch
+        us, threads, spent = cpu_reference_us(args.batch, sample, M.GPT3_HIDDEN, M.GPT3_FFN)
+        line["cpu_baseline"] = {"value": us, "unit": UNIT, "cores": threads, "kind": "port",
+                                "sample": "%d of %d rows through both GEMMs (%.1f s), scaled to the full batch"
+                                          % (sample, args.batch, spent)}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -58,6 +58,16 @@ class GemmDesc(C.Structure):
                 ("stage", C.c_void_p)]
 
 
+class MlpDesc(C.Structure):
+    _fields_ = [("model", C.c_int32), ("batch", C.c_int32), ("hidden", C.c_int32), ("ffn", C.c_int32),
+                ("policy", C.c_int32), ("opts", C.c_int32), ("tile_n1", C.c_int32), ("tile_n2", C.c_int32),
+                ("max_ctas", C.c_int32),
+                ("x", C.c_void_p), ("w1", C.c_void_p), ("v", C.c_void_p), ("w2", C.c_void_p),
+                ("h", C.c_void_p), ("y", C.c_void_p)]
+
+
+MLP_GPT3, MLP_LLAMA = 0, 1
+
 # name -> (restype, argtypes); every function include/cusync_b200.h declares
 _vp, _i, _u32, _u64 = C.c_void_p, C.c_int, C.c_uint32, C.c_uint64
 SIGNATURES = {
@@ -65,6 +75,8 @@ SIGNATURES = {
     "cusync_stage_destroy": (_i, [_vp]),
     "cusync_stage_link": (_i, [_vp, _vp]),
     "cusync_stage_increment_iter": (_i, [_vp]),
+    "cusync_stage_set_iter": (_i, [_vp, _u32]),
+    "cusync_stage_write_tile_order": (_i, [_vp, _vp, _u32]),
     "cusync_stage_reset": (_i, [_vp, _vp]),
     "cusync_stage_get_view": (_i, [_vp, C.POINTER(StageView)]),
     "cusync_stage_set_timeout_ns": (_i, [_vp, _u64]),
@@ -82,6 +94,14 @@ SIGNATURES = {
     "cusync_gemm_plan_update": (_i, [_vp, _vp, _vp, _vp, _vp]),
     "cusync_gemm_run": (_i, [_vp, _vp]),
     "cusync_gemm_plan_num_ctas": (_u32, [_vp]),
+    "cusync_mlp_create": (_i, [C.POINTER(_vp), C.POINTER(MlpDesc)]),
+    "cusync_mlp_destroy": (_i, [_vp]),
+    "cusync_mlp_run_stream_ordered": (_i, [_vp, _vp]),
+    "cusync_mlp_run_cusync": (_i, [_vp, _vp, _vp]),
+    "cusync_mlp_run_single": (_i, [_vp, _i, _vp]),
+    "cusync_mlp_update_io": (_i, [_vp, _vp, _vp]),
+    "cusync_mlp_stage": (_vp, [_vp, _i]),
+    "cusync_mlp_config": (_i, [_vp, C.POINTER(C.c_int32)]),
     "cusync_b200_version": (C.c_char_p, []),
     "cusync_b200_sm_count": (_i, []),
 }

@@ -1,0 +1,170 @@
+// Tensor-parallel MLP shard driver: two dependent GEMMs wired through CuSync
+// stages, plus the stream-ordered baseline built from the same kernels.
+// Host-only code over the library's own C ABI; it follows the flow of the
+// reference driver src/ml-bench/transformer/mlp.cu (stage typing :103-118,
+// grid/sync set-up :1026-1062, runBaselineGPT3 :411-491, runCuSyncGPT3 :645-716).
+#include <cstring>
+#include <new>
+
+#include "common.cuh"
+
+struct cusync_mlp {
+  cusync_mlp_desc_t desc;
+  int tile_n1, tile_n2;
+  cusync_stage_t* prod;
+  cusync_stage_t* cons;
+  cusync_gemm_plan_t* sync1;    // producer GEMM with its stage
+  cusync_gemm_plan_t* sync2;    // consumer GEMM with its stage
+  cusync_gemm_plan_t* plain1;   // same kernels without tile synchronisation
+  cusync_gemm_plan_t* plain2;
+};
+
+namespace {
+
+void fill_gemm1(const cusync_mlp_desc_t& d, int tile_n, cusync_stage_t* stage, cusync_gemm_desc_t* g) {
+  std::memset(g, 0, sizeof(*g));
+  g->m = d.batch; g->n = d.ffn; g->k = d.hidden;
+  g->a = d.x; g->lda = d.hidden;
+  g->b = d.w1; g->ldb = d.ffn;
+  g->b2 = d.model == CUSYNC_MLP_LLAMA ? d.v : nullptr;
+  g->d = d.h; g->ldd = d.ffn;
+  g->b_layout = CUSYNC_B_ROW_MAJOR_KN;
+  g->epilogue = d.model == CUSYNC_MLP_LLAMA ? CUSYNC_EPILOGUE_SILU_MUL_DUAL : CUSYNC_EPILOGUE_GELU_ERF;
+  g->tile_n = tile_n; g->max_ctas = d.max_ctas; g->stage = stage;
+}
+
+void fill_gemm2(const cusync_mlp_desc_t& d, int tile_n, cusync_stage_t* stage, cusync_gemm_desc_t* g) {
+  std::memset(g, 0, sizeof(*g));
+  g->m = d.batch; g->n = d.hidden; g->k = d.ffn;
+  g->a = d.h; g->lda = d.ffn;
+  g->b = d.w2; g->ldb = d.hidden;
+  g->d = d.y; g->ldd = d.hidden;
+  g->b_layout = CUSYNC_B_ROW_MAJOR_KN;
+  g->epilogue = CUSYNC_EPILOGUE_NONE;
+  g->tile_n = tile_n; g->max_ctas = d.max_ctas; g->stage = stage;
+}
+
+void destroy_all(cusync_mlp* m) {
+  if (m->sync1) cusync_gemm_plan_destroy(m->sync1);
+  if (m->sync2) cusync_gemm_plan_destroy(m->sync2);
+  if (m->plain1) cusync_gemm_plan_destroy(m->plain1);
+  if (m->plain2) cusync_gemm_plan_destroy(m->plain2);
+  if (m->prod) cusync_stage_destroy(m->prod);
+  if (m->cons) cusync_stage_destroy(m->cons);
+  delete m;
+}
+
+}  // namespace
+
+extern "C" {
+
+int cusync_mlp_create(cusync_mlp_t** out, const cusync_mlp_desc_t* desc) {
+  if (!out || !desc) return CUSYNC_ERROR_INVALID_ARGUMENT;
+  *out = nullptr;
+  const cusync_mlp_desc_t& d = *desc;
+  if (d.model != CUSYNC_MLP_GPT3 && d.model != CUSYNC_MLP_LLAMA) return CUSYNC_ERROR_INVALID_ARGUMENT;
+  if (d.batch <= 0 || d.hidden <= 0 || d.ffn <= 0) return CUSYNC_ERROR_INVALID_ARGUMENT;
+  if (!d.x || !d.w1 || !d.w2 || !d.h || !d.y || (d.model == CUSYNC_MLP_LLAMA && !d.v))
+    return CUSYNC_ERROR_INVALID_ARGUMENT;
+  if (d.policy != CUSYNC_POLICY_ROWSYNC && d.policy != CUSYNC_POLICY_TILESYNC) return CUSYNC_ERROR_INVALID_ARGUMENT;
+
+  cusync_mlp* m = new (std::nothrow) cusync_mlp();
+  if (!m) return CUSYNC_ERROR_CUDA;
+  std::memset(m, 0, sizeof(*m));
+  m->desc = d;
+  const int epi1 = d.model == CUSYNC_MLP_LLAMA ? CUSYNC_EPILOGUE_SILU_MUL_DUAL : CUSYNC_EPILOGUE_GELU_ERF;
+  m->tile_n1 = d.tile_n1 ? d.tile_n1 : cusync_gemm_default_tile_n(d.batch, d.ffn, d.hidden, epi1);
+  m->tile_n2 = d.tile_n2 ? d.tile_n2 : cusync_gemm_default_tile_n(d.batch, d.hidden, d.ffn, CUSYNC_EPILOGUE_NONE);
+
+  // Tile grids (N tiles, M tiles, 1) and the sync policy between the GEMMs.
+  const uint32_t tiles_m = static_cast<uint32_t>((d.batch + 127) / 128);
+  cusync_dim3_t grid1 = {static_cast<uint32_t>((d.ffn + m->tile_n1 - 1) / m->tile_n1), tiles_m, 1};
+  cusync_dim3_t grid2 = {static_cast<uint32_t>((d.hidden + m->tile_n2 - 1) / m->tile_n2), tiles_m, 1};
+  cusync_policy_t sync;
+  std::memset(&sync, 0, sizeof(sync));
+  sync.kind = d.policy;
+  sync.order = CUSYNC_ORDER_TRANSPOSE_XY;
+  sync.tile_m = 128;
+  sync.tile_n = static_cast<uint32_t>(m->tile_n1);
+  if (d.policy == CUSYNC_POLICY_ROWSYNC) { sync.wait_value = grid1.x; sync.post_value = 1; }   // mlp.cu:1032-1034
+  else                                   { sync.wait_value = 1; sync.post_value = 1; }
+  cusync_policy_t none;
+  std::memset(&none, 0, sizeof(none));
+  none.tile_m = none.tile_n = 1;
+  // NoAtomicAdd only where each semaphore has one poster (mlp.cu:9-14).
+  int opts = d.opts;
+  if (d.policy == CUSYNC_POLICY_ROWSYNC) opts &= ~CUSYNC_OPT_NO_ATOMIC_ADD;
+  cusync_dim3_t ts = {1, 1, 1};
+  int rc = cusync_stage_create(&m->prod, grid1, ts, CUSYNC_ORDER_TRANSPOSE_XY, &none, &sync, opts);
+  if (rc == CUSYNC_SUCCESS) rc = cusync_stage_create(&m->cons, grid2, ts, CUSYNC_ORDER_TRANSPOSE_XY, &sync, &none, opts);
+  if (rc == CUSYNC_SUCCESS) rc = cusync_stage_link(m->prod, m->cons);
+
+  cusync_gemm_desc_t g;
+  if (rc == CUSYNC_SUCCESS) { fill_gemm1(d, m->tile_n1, m->prod, &g); rc = cusync_gemm_plan_create(&m->sync1, &g); }
+  if (rc == CUSYNC_SUCCESS) { fill_gemm2(d, m->tile_n2, m->cons, &g); rc = cusync_gemm_plan_create(&m->sync2, &g); }
+  if (rc == CUSYNC_SUCCESS) { fill_gemm1(d, m->tile_n1, nullptr, &g); rc = cusync_gemm_plan_create(&m->plain1, &g); }
+  if (rc == CUSYNC_SUCCESS) { fill_gemm2(d, m->tile_n2, nullptr, &g); rc = cusync_gemm_plan_create(&m->plain2, &g); }
+  if (rc != CUSYNC_SUCCESS) { destroy_all(m); return rc; }
+  *out = m;
+  return CUSYNC_SUCCESS;
+}
+
+int cusync_mlp_destroy(cusync_mlp_t* m) {
+  if (!m) return CUSYNC_ERROR_NOT_INITIALIZED;
+  destroy_all(m);
+  return CUSYNC_SUCCESS;
+}
+
+int cusync_mlp_run_stream_ordered(cusync_mlp_t* m, cusync_stream_t stream) {
+  if (!m) return CUSYNC_ERROR_NOT_INITIALIZED;
+  int rc = cusync_gemm_run(m->plain1, stream);
+  if (rc == CUSYNC_SUCCESS) rc = cusync_gemm_run(m->plain2, stream);
+  return rc;
+}
+
+int cusync_mlp_run_single(cusync_mlp_t* m, int which, cusync_stream_t stream) {
+  if (!m) return CUSYNC_ERROR_NOT_INITIALIZED;
+  if (which != 1 && which != 2) return CUSYNC_ERROR_INVALID_ARGUMENT;
+  return cusync_gemm_run(which == 1 ? m->plain1 : m->plain2, stream);
+}
+
+int cusync_mlp_run_cusync(cusync_mlp_t* m, cusync_stream_t producer_stream, cusync_stream_t consumer_stream) {
+  if (!m) return CUSYNC_ERROR_NOT_INITIALIZED;
+  int rc = cusync_gemm_run(m->sync1, producer_stream);
+  if (rc == CUSYNC_SUCCESS) rc = cusync_stage_invoke_wait_kernel(m->prod, consumer_stream);
+  if (rc == CUSYNC_SUCCESS) rc = cusync_gemm_run(m->sync2, consumer_stream);
+  cusync_stage_increment_iter(m->prod);
+  cusync_stage_increment_iter(m->cons);
+  return rc;
+}
+
+int cusync_mlp_update_io(cusync_mlp_t* m, const void* x, void* y) {
+  if (!m) return CUSYNC_ERROR_NOT_INITIALIZED;
+  int rc = CUSYNC_SUCCESS;
+  if (x) {
+    m->desc.x = x;
+    rc = cusync_gemm_plan_update(m->sync1, x, nullptr, nullptr, nullptr);
+    if (rc == CUSYNC_SUCCESS) rc = cusync_gemm_plan_update(m->plain1, x, nullptr, nullptr, nullptr);
+  }
+  if (y && rc == CUSYNC_SUCCESS) {
+    m->desc.y = y;
+    rc = cusync_gemm_plan_update(m->sync2, nullptr, nullptr, nullptr, y);
+    if (rc == CUSYNC_SUCCESS) rc = cusync_gemm_plan_update(m->plain2, nullptr, nullptr, nullptr, y);
+  }
+  return rc;
+}
+
+cusync_stage_t* cusync_mlp_stage(cusync_mlp_t* m, int which) {
+  if (!m) return nullptr;
+  return which == 0 ? m->prod : m->cons;
+}
+
+int cusync_mlp_config(const cusync_mlp_t* m, int32_t* out4) {
+  if (!m || !out4) return CUSYNC_ERROR_NOT_INITIALIZED;
+  out4[0] = m->tile_n1; out4[1] = m->tile_n2;
+  out4[2] = static_cast<int32_t>(cusync_gemm_plan_num_ctas(m->sync1));
+  out4[3] = static_cast<int32_t>(cusync_gemm_plan_num_ctas(m->sync2));
+  return CUSYNC_SUCCESS;
+}
+
+}  // extern "C"

@@ -38,8 +38,8 @@ __global__ void waitKernel(const uint32_t* sem, uint32_t value, uint32_t* status
 
 bool policy_ok(const cusync_policy_t* p) {
   if (p == nullptr) return true;
-  if (p->kind < CUSYNC_POLICY_NOSYNC || p->kind > CUSYNC_POLICY_CONSECUTIVETILESYNC) return false;
-  if (p->kind == CUSYNC_POLICY_NOSYNC) return true;
+  if (p->kind < CUSYNC_POLICY_NOSYNC || p->kind > CUSYNC_POLICY_CUSTOM) return false;
+  if (p->kind == CUSYNC_POLICY_NOSYNC || p->kind == CUSYNC_POLICY_CUSTOM) return true;
   if (p->tile_m == 0 || p->tile_n == 0) return false;
   if (p->kind == CUSYNC_POLICY_CONV2DTILESYNC && p->p0 == 0) return false;
   if (p->kind == CUSYNC_POLICY_STRIDEDTILESYNC && (p->p0 < p->tile_n || p->p1 == 0)) return false;
@@ -140,6 +140,20 @@ int cusync_stage_increment_iter(cusync_stage_t* s) {
   s->view.iter += 1;
   s->launch_noted = false;
   return CUSYNC_SUCCESS;
+}
+
+int cusync_stage_set_iter(cusync_stage_t* s, uint32_t iter) {
+  if (s == nullptr) return CUSYNC_ERROR_NOT_INITIALIZED;
+  if (iter != s->view.iter) s->launch_noted = false;
+  s->view.iter = iter;
+  return CUSYNC_SUCCESS;
+}
+
+int cusync_stage_write_tile_order(cusync_stage_t* s, const cusync_dim3_t* order, uint32_t count) {
+  if (s == nullptr || order == nullptr) return CUSYNC_ERROR_NOT_INITIALIZED;
+  if (count != s->num_tiles) return CUSYNC_ERROR_INVALID_ARGUMENT;
+  return cudaMemcpy(s->view.tile_order, order, sizeof(cusync_dim3_t) * count, cudaMemcpyHostToDevice) == cudaSuccess
+             ? CUSYNC_SUCCESS : CUSYNC_ERROR_CUDA;
 }
 
 int cusync_stage_reset(cusync_stage_t* s, cusync_stream_t stream) {

@@ -1,0 +1,102 @@
+"""Tensor-parallel MLP shard on the CuSync GEMM chain (host-side driver).
+
+Mirrors the flow of the reference driver src/ml-bench/transformer/mlp.cu:
+MLPParameters (:209-330) -> stages + setProducerConsumerPair (:1026-1062) ->
+runBaseline* (:411-491) / runCuSync* (:645-716).  The work is done by
+cusync_mlp_* of the C ABI; torch only owns device memory, streams and, for
+N > 1 GPUs, the NCCL all-reduce of the row-parallel output.
+"""
+import ctypes as C
+
+from . import _lib as L
+from .api import _stream_ptr
+
+# (hidden, ffn-per-shard) of the models the reference benchmarks, one 8-way tensor-parallel shard
+GPT3_HIDDEN, GPT3_FFN = 12288, 4 * 12288 // 8          # mlp.cu:243-245
+LLAMA_HIDDEN = 8192
+LLAMA_FFN_REFERENCE = ((8192 // 3 + 127) // 128) * 128  # 2816, mlp.cu:247-250
+LLAMA_FFN = 2752                                        # 65.2B model: 22016 / 8
+
+POLICIES = {"rowsync": L.POLICY_ROWSYNC, "tilesync": L.POLICY_TILESYNC}
+
+
+class MLPShard:
+    """x[B,H] -> y[B,H] through W1 (and V) [H,F] and W2 [F,H]; fp16, fp32 accumulate."""
+
+    def __init__(self, model, batch, x, w1, w2, v=None, policy="rowsync", opts=0, tile_n1=0, tile_n2=0, max_ctas=0):
+        import torch
+        self.model = L.MLP_GPT3 if model == "gpt3" else L.MLP_LLAMA
+        self.batch, self.hidden, self.ffn = batch, w1.shape[0], w1.shape[1]
+        assert x.shape == (batch, self.hidden) and w2.shape == (self.ffn, self.hidden)
+        self.x, self.w1, self.w2, self.v = x, w1, w2, v
+        self.h = torch.empty((batch, self.ffn), device=x.device, dtype=torch.half)
+        self.y = torch.empty((batch, self.hidden), device=x.device, dtype=torch.half)
+        d = L.MlpDesc(self.model, batch, self.hidden, self.ffn, POLICIES[policy], opts, tile_n1, tile_n2, max_ctas,
+                      x.data_ptr(), w1.data_ptr(), v.data_ptr() if v is not None else None, w2.data_ptr(),
+                      self.h.data_ptr(), self.y.data_ptr())
+        self._h = C.c_void_p()
+        L.check(L.lib().cusync_mlp_create(C.byref(self._h), C.byref(d)), "cusync_mlp_create")
+        cfg = (C.c_int32 * 4)()
+        L.lib().cusync_mlp_config(self._h, cfg)
+        self.tile_n1, self.tile_n2, self.ctas1, self.ctas2 = list(cfg)
+
+    def run_stream_ordered(self, stream):
+        L.check(L.lib().cusync_mlp_run_stream_ordered(self._h, _stream_ptr(stream)), "run_stream_ordered")
+
+    def run_cusync(self, producer_stream, consumer_stream):
+        L.check(L.lib().cusync_mlp_run_cusync(self._h, _stream_ptr(producer_stream), _stream_ptr(consumer_stream)),
+                "run_cusync")
+
+    def run_single(self, which, stream):
+        L.check(L.lib().cusync_mlp_run_single(self._h, which, _stream_ptr(stream)), "run_single")
+
+    def update_io(self, x=None, y=None):
+        L.check(L.lib().cusync_mlp_update_io(self._h, x.data_ptr() if x is not None else None,
+                                             y.data_ptr() if y is not None else None), "update_io")
+        if x is not None:
+            self.x = x
+        if y is not None:
+            self.y = y
+
+    def _stage_status(self, which):
+        s = L.Status()
+        L.lib().cusync_stage_read_status(L.lib().cusync_mlp_stage(self._h, which), C.byref(s))
+        return s
+
+    def status_codes(self):
+        return self._stage_status(0).code, self._stage_status(1).code
+
+    def producer_semaphores(self):
+        import numpy as np
+        st = L.lib().cusync_mlp_stage(self._h, 0)
+        n = L.lib().cusync_stage_num_tiles(st)
+        out = np.zeros(n, dtype=np.uint32)
+        L.check(L.lib().cusync_stage_read_semaphores(st, out.ctypes.data_as(C.c_void_p), n), "read_semaphores")
+        return out
+
+    def flops(self):
+        mult = 3 if self.model == L.MLP_LLAMA else 2
+        return 2.0 * self.batch * self.hidden * self.ffn * mult
+
+    def destroy(self):
+        if self._h:
+            L.lib().cusync_mlp_destroy(self._h)
+            self._h = C.c_void_p()
+
+
+def make_inputs(model, batch, device, seed=0, ffn=None):
+    """Seeded synthetic inputs with the shapes and distributions of the benchmark configs:
+    X ~ N(0,1), weights ~ N(0, 0.02)."""
+    import torch
+    g = torch.Generator(device=device).manual_seed(seed)
+    if model == "gpt3":
+        hidden, f = GPT3_HIDDEN, ffn or GPT3_FFN
+    else:
+        hidden, f = LLAMA_HIDDEN, ffn or LLAMA_FFN
+    x = torch.randn((batch, hidden), generator=g, device=device, dtype=torch.float32).half()
+    w1 = (torch.randn((hidden, f), generator=g, device=device, dtype=torch.float32) * 0.02).half()
+    w2 = (torch.randn((f, hidden), generator=g, device=device, dtype=torch.float32) * 0.02).half()
+    v = None
+    if model != "gpt3":
+        v = (torch.randn((hidden, f), generator=g, device=device, dtype=torch.float32) * 0.02).half()
+    return x, w1, w2, v

@@ -66,7 +66,8 @@ enum {
   CUSYNC_POLICY_TILESYNC = 2,
   CUSYNC_POLICY_STRIDEDTILESYNC = 3,
   CUSYNC_POLICY_CONV2DTILESYNC = 4,
-  CUSYNC_POLICY_CONSECUTIVETILESYNC = 5
+  CUSYNC_POLICY_CONSECUTIVETILESYNC = 5,
+  CUSYNC_POLICY_CUSTOM = 6   /* user-written policy class; evaluated only by code compiled against <cusync/cusync.h> */
 };
 
 typedef struct cusync_policy {
@@ -136,6 +137,15 @@ CUSYNC_API int cusync_stage_link(cusync_stage_t* producer, cusync_stage_t* consu
 /* CuStage::incrementIter (cusync.h:212).  The handle is the single owner of
  * `iter`; views taken afterwards carry the new value. */
 CUSYNC_API int cusync_stage_increment_iter(cusync_stage_t* stage);
+
+/* Sets the run counter outright.  The C++ CuStage keeps a counter in every
+ * copy (as the reference does) and mirrors it here, so that incrementing the
+ * host object and the by-value copy inside a kernel handle (mlp.cu:709-712)
+ * does not count twice. */
+CUSYNC_API int cusync_stage_set_iter(cusync_stage_t* stage, uint32_t iter);
+
+/* Replaces the schedule buffer (user-defined tile orders of the C++ API). */
+CUSYNC_API int cusync_stage_write_tile_order(cusync_stage_t* stage, const cusync_dim3_t* order, uint32_t count);
 
 /* No counterpart: zero the semaphores, ticket and started words and set
  * iter = 1, so a stage can be reused after an error. */
@@ -215,6 +225,51 @@ CUSYNC_API int cusync_gemm_plan_update(cusync_gemm_plan_t* plan, const void* a, 
 CUSYNC_API int cusync_gemm_run(cusync_gemm_plan_t* plan, cusync_stream_t stream);
 /* Blocks the launch uses (persistent grid). */
 CUSYNC_API uint32_t cusync_gemm_plan_num_ctas(const cusync_gemm_plan_t* plan);
+
+/* ---- MLP driver ---------------------------------------------------------- */
+
+enum { CUSYNC_MLP_GPT3 = 0, CUSYNC_MLP_LLAMA = 1 };
+
+/* One tensor-parallel MLP shard, the workload of
+ * src/ml-bench/transformer/mlp.cu (MLPParameters :209-330):
+ *   GPT-3 : H = GELU(X * W1);            Y = H * W2
+ *   LLaMA : H = SiLU(X * W1) (.) (X * V); Y = H * W2   (the fused form of mlp-lib.cu:123-134)
+ * X[batch, hidden], W1 and V [hidden, ffn], W2 [ffn, hidden], H[batch, ffn],
+ * Y[batch, hidden]; all row-major fp16 on the device, caller-owned. */
+typedef struct cusync_mlp_desc {
+  int32_t model;                 /* CUSYNC_MLP_* */
+  int32_t batch, hidden, ffn;
+  int32_t policy;                /* CUSYNC_POLICY_ROWSYNC or CUSYNC_POLICY_TILESYNC between the two GEMMs */
+  int32_t opts;                  /* CUSYNC_OPT_* applied to both stages */
+  int32_t tile_n1, tile_n2;      /* 0 = choose */
+  int32_t max_ctas;              /* 0 = one per SM */
+  const void* x; const void* w1; const void* v; const void* w2;
+  void* h; void* y;
+} cusync_mlp_desc_t;
+
+typedef struct cusync_mlp cusync_mlp_t;
+
+/* MLPParameters + stage construction + setProducerConsumerPair + both
+ * GEMM initialisations (mlp.cu:1026-1062, 653-684). */
+CUSYNC_API int cusync_mlp_create(cusync_mlp_t** out, const cusync_mlp_desc_t* desc);
+CUSYNC_API int cusync_mlp_destroy(cusync_mlp_t* mlp);
+/* runBaselineGPT3 / runBaselineLLaMA, one iteration: the same two kernels,
+ * no tile synchronisation, back to back on one stream (mlp.cu:411-491). */
+CUSYNC_API int cusync_mlp_run_stream_ordered(cusync_mlp_t* mlp, cusync_stream_t stream);
+/* runCuSyncGPT3 / runCuSyncLLaMA, one iteration: producer GEMM on
+ * producer_stream, wait kernel + consumer GEMM on consumer_stream, then
+ * incrementIter on both stages (mlp.cu:691-712). */
+CUSYNC_API int cusync_mlp_run_cusync(cusync_mlp_t* mlp, cusync_stream_t producer_stream,
+                                     cusync_stream_t consumer_stream);
+/* One of the two un-synchronised kernels alone (1 = first GEMM, 2 = second), for per-kernel timing
+ * (the reference's baseline prints both, mlp.cu:463-488). */
+CUSYNC_API int cusync_mlp_run_single(cusync_mlp_t* mlp, int which, cusync_stream_t stream);
+/* New X / Y buffers for later runs (update, gemm/device/cusyncgemm.h:459-494). */
+CUSYNC_API int cusync_mlp_update_io(cusync_mlp_t* mlp, const void* x, void* y);
+/* Stage handles (0 = producer, 1 = consumer) for inspection. */
+CUSYNC_API cusync_stage_t* cusync_mlp_stage(cusync_mlp_t* mlp, int which);
+/* Tile widths and block counts in use: out[0..3] = tile_n1, tile_n2, ctas1, ctas2. */
+CUSYNC_API int cusync_mlp_config(const cusync_mlp_t* mlp, int32_t* out4);
 
 /* Library / device information. */
 CUSYNC_API const char* cusync_b200_version(void);
