@@ -78,7 +78,7 @@ class ClockSampler:
             except ValueError:
                 continue
             for name, val in zip(names, r[3:7]):
-                if val.lower().startswith("active"):
+                if val.lower().startswith("active") and not val.lower().startswith("not"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
                 "reasons": sorted(reasons), "samples": len(sm)}
@@ -167,7 +167,7 @@ def time_steps(step_fn, start_stream, end_stream, steps, warmup, barrier):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--batch", type=int, default=2048)
     ap.add_argument("--policy", default="rowsync", choices=["rowsync", "tilesync"])
@@ -232,12 +232,29 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    def interleaved(step_a, a_streams, step_b, b_streams, n, warm):
+        """Alternates the two arms step by step, so clock and power drift hits both alike.
+        Returns the per-step millisecond lists of A and B."""
+        for _ in range(warm):
+            step_a(); step_b()
+        torch.cuda.synchronize()
+        ev = []
+        for _ in range(n):
+            pair = []
+            for fn, (s0, s1) in ((step_a, a_streams), (step_b, b_streams)):
+                s0.wait_stream(cs); s0.wait_stream(ps)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(s0); fn(); e1.record(s1)
+                pair.append((e0, e1))
+            ev.append(pair)
+        torch.cuda.synchronize()
+        return [p[0][0].elapsed_time(p[0][1]) for p in ev], [p[1][0].elapsed_time(p[1][1]) for p in ev]
+
     # ---- headline: overlapped chain ------------------------------------------------------------
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
     total_ms, per_ms = time_steps(cusync_step, ps, cs, args.steps, args.warmup, barrier)
-    clocks = sampler.stop() if rank == 0 else None
     total_ms = reduce_max(total_ms)
     ms_per_step = total_ms / args.steps
     codes = shard.status_codes()
@@ -247,6 +264,9 @@ def main():
     # ---- same kernels serialised by stream order --------------------------------------------
     ord_total, ord_per = time_steps(ordered_step, cs, cs, args.steps, args.warmup, barrier)
     ord_ms = reduce_max(ord_total) / args.steps
+    # ... and both arms interleaved step by step (the fair comparison under clock drift)
+    il_c, il_o = interleaved(cusync_step, (ps, cs), ordered_step, (cs, cs), args.steps, 3)
+    il_c_us, il_o_us = statistics.median(il_c) * 1000.0, statistics.median(il_o) * 1000.0
 
     # ---- per-kernel durations (stream-ordered, events on the launching stream) ----------------
     flops2 = 2.0 * args.batch * M.GPT3_FFN * M.GPT3_HIDDEN
@@ -263,10 +283,11 @@ def main():
             g1.append(e0.elapsed_time(e1)); g2.append(e1.elapsed_time(e2))
     t1_ms, t2_ms = statistics.mean(g1), statistics.mean(g2)
     tensor_bound = args.batch >= 256
+    kernel_name = "cusync_gemm_kernel<%d> (GEMM2, the consumer)" % shard.tile_n2
     if tensor_bound:
         achieved = flops2 / (t2_ms * 1e-3) / 1e12
         peak = peaks["tflops_sustained"]
-        roofline = {"bound": "tensor", "kernel": "cusync_gemm_kernel<%d> (GEMM2, consumer)" % shard.tile_n2,
+        roofline = {"bound": "tensor", "kernel": kernel_name,
                     "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                     "peak_kind": "%s sustained bf16/fp16 cuBLAS" % peaks["source"],
                     "frac_of_burst_peak": achieved / peaks["tflops_burst"], "traffic": None,
@@ -275,7 +296,7 @@ def main():
     else:
         bytes2 = 2.0 * (M.GPT3_FFN * M.GPT3_HIDDEN + args.batch * (M.GPT3_FFN + M.GPT3_HIDDEN))
         achieved = bytes2 / (t2_ms * 1e-3) / 1e9
-        roofline = {"bound": "hbm", "kernel": "cusync_gemm_kernel<%d> (GEMM2, consumer)" % shard.tile_n2,
+        roofline = {"bound": "hbm", "kernel": kernel_name,
                     "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                     "peak_kind": "%s copy bandwidth" % peaks["source"], "traffic": None, "launch_ms": t2_ms,
                     "gemm1_ms": t1_ms}
@@ -314,19 +335,19 @@ def main():
                 def o_step(s=s):
                     s.run_stream_ordered(cs)
 
-                _, c_per = time_steps(c_step, ps, cs, 20, 5, barrier)
-                _, o_per = time_steps(o_step, cs, cs, 20, 5, barrier)
+                c_per, o_per = interleaved(c_step, (ps, cs), o_step, (cs, cs), 20, 5)
                 c_us, o_us = statistics.median(c_per) * 1000, statistics.median(o_per) * 1000
                 row[pol + "_us"] = round(c_us, 2)
-                row["stream_ordered_us"] = round(o_us, 2)
+                row[pol + "_stream_ordered_us"] = round(o_us, 2)
                 row[pol + "_gain_pct"] = round(100.0 - c_us / o_us * 100.0, 2)
                 row["tile_n"] = [s.tile_n1, s.tile_n2]
                 if s.status_codes() != (0, 0):
                     row["error"] = "bounded wait expired"
                 s.destroy()
-            row["tflops_best"] = round(shard.flops() / args.batch * b / (min(row["rowsync_us"], row["tilesync_us"],
-                                                                            row["stream_ordered_us"]) * 1e-6) / 1e12, 1)
+            best = min(row["rowsync_us"], row["tilesync_us"], row["rowsync_stream_ordered_us"])
+            row["tflops_best"] = round(shard.flops() / args.batch * b / (best * 1e-6) / 1e12, 1)
             table.append(row)
+    clocks = sampler.stop() if rank == 0 else None
 
     if rank != 0:
         if world > 1:
@@ -341,6 +362,9 @@ def main():
             "median_us": statistics.median(per_ms) * 1000.0,
             "stream_ordered_us": ord_ms * 1000.0,
             "gain_vs_stream_ordered_pct": 100.0 - ms_per_step / ord_ms * 100.0,
+            "interleaved": {"cusync_us": il_c_us, "stream_ordered_us": il_o_us,
+                            "gain_pct": 100.0 - il_c_us / il_o_us * 100.0,
+                            "how": "arms alternated step by step, medians over %d steps each" % args.steps},
             "layer_tflops": shard.flops() / (ms_per_step * 1e-3) / 1e12,
             "layer_frac_of_sustained_peak": shard.flops() / (ms_per_step * 1e-3) / 1e12 / peaks["tflops_sustained"],
             "roofline": roofline,

@@ -5,6 +5,6 @@ API over the library's C ABI."""
 from . import _lib
 from ._lib import CuSyncError, CuSyncLibraryError  # noqa: F401
 from .api import (CuStage, CuSync, NoSync, RowSync, TileSync, StridedTileSync, Conv2DTileSync,  # noqa: F401
-                  ConsecutiveTileSync, IdentityOrder, TransposeXYOrder, Optimizations, Gemm, GemmArguments,
+                  ConsecutiveTileSync, IdentityOrder, TransposeXYOrder, GroupedRowsOrder, Optimizations, Gemm, GemmArguments,
                   gemm_tiled_shape)
 from .mlp import MLPShard, make_inputs  # noqa: F401,E402

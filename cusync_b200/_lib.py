@@ -18,7 +18,12 @@ ERROR_NAMES = ["CuSyncErrorNotProducer", "CuSyncErrorNotConsumer", "CuSyncErrorN
                "CuSyncErrorTimeout", "CuSyncErrorInvalidArgument", "CuSyncErrorUnsupported"]
 
 OPT_NONE, OPT_NO_ATOMIC_ADD, OPT_AVOID_WAIT_KERNEL, OPT_AVOID_CUSTOM_ORDER, OPT_REORDER_TILE_LOADS = 0, 1, 2, 4, 8
-ORDER_IDENTITY, ORDER_TRANSPOSE_XY = 0, 1
+ORDER_IDENTITY, ORDER_TRANSPOSE_XY, ORDER_GROUPED_ROWS = 0, 1, 2
+
+
+def order_grouped(rows):
+    return ORDER_GROUPED_ROWS | (rows << 8)
+
 POLICY_NOSYNC, POLICY_ROWSYNC, POLICY_TILESYNC, POLICY_STRIDEDTILESYNC, POLICY_CONV2DTILESYNC, \
     POLICY_CONSECUTIVETILESYNC = range(6)
 EPILOGUE_NONE, EPILOGUE_GELU_ERF, EPILOGUE_RELU, EPILOGUE_SILU_MUL_DUAL = range(4)
@@ -61,7 +66,7 @@ class GemmDesc(C.Structure):
 class MlpDesc(C.Structure):
     _fields_ = [("model", C.c_int32), ("batch", C.c_int32), ("hidden", C.c_int32), ("ffn", C.c_int32),
                 ("policy", C.c_int32), ("opts", C.c_int32), ("tile_n1", C.c_int32), ("tile_n2", C.c_int32),
-                ("max_ctas", C.c_int32),
+                ("max_ctas", C.c_int32), ("group_rows2", C.c_int32),
                 ("x", C.c_void_p), ("w1", C.c_void_p), ("v", C.c_void_p), ("w2", C.c_void_p),
                 ("h", C.c_void_p), ("y", C.c_void_p)]
 
@@ -93,6 +98,7 @@ SIGNATURES = {
     "cusync_gemm_plan_destroy": (_i, [_vp]),
     "cusync_gemm_plan_update": (_i, [_vp, _vp, _vp, _vp, _vp]),
     "cusync_gemm_run": (_i, [_vp, _vp]),
+    "cusync_gemm_plan_set_trace": (_i, [_vp, _vp, _u32]),
     "cusync_gemm_plan_num_ctas": (_u32, [_vp]),
     "cusync_mlp_create": (_i, [C.POINTER(_vp), C.POINTER(MlpDesc)]),
     "cusync_mlp_destroy": (_i, [_vp]),
@@ -101,6 +107,7 @@ SIGNATURES = {
     "cusync_mlp_run_single": (_i, [_vp, _i, _vp]),
     "cusync_mlp_update_io": (_i, [_vp, _vp, _vp]),
     "cusync_mlp_stage": (_vp, [_vp, _i]),
+    "cusync_mlp_set_trace": (_i, [_vp, _vp, _u32, _vp, _u32]),
     "cusync_mlp_config": (_i, [_vp, C.POINTER(C.c_int32)]),
     "cusync_b200_version": (C.c_char_p, []),
     "cusync_b200_sm_count": (_i, []),

@@ -33,6 +33,13 @@ class TransposeXYOrder:
     kind = L.ORDER_TRANSPOSE_XY
 
 
+class GroupedRowsOrder:
+    """Addition: blocks taken in groups of `rows` grid rows, row index fastest inside a group."""
+
+    def __init__(self, rows):
+        self.kind = L.order_grouped(rows)
+
+
 def _order(o):
     return o if isinstance(o, int) else o.kind
 

@@ -19,7 +19,7 @@
 //   warp 1  lane 0   issues tcgen05.mma (128 x BN x 16, kind::f16) into one of
 //                    two TMEM accumulator buffers.
 //   warp 2           allocates / frees tensor memory.
-//   warps 4-7        epilogue: tcgen05.ld -> fp32 math (GELU / ReLU / SiLU*mul)
+//   warps 4-11       epilogue: tcgen05.ld -> fp32 math (GELU / ReLU / SiLU*mul)
 //                    -> fp16 -> swizzled shared staging -> TMA store.  After
 //                    the stores have fully completed, ONE thread publishes the
 //                    tile with red.release.gpu (CuStage::post,
@@ -45,9 +45,11 @@ namespace {
 constexpr int kBlockM = 128;        // UMMA M
 constexpr int kBlockK = 64;         // one 128-byte swizzle row of fp16
 constexpr int kUmmaK = 16;
-constexpr int kThreads = 256;
+constexpr int kThreads = 384;
+constexpr int kEpilogueWarps = 8;    // two per TMEM lane quarter: keeps every scheduler fed during the epilogue
 constexpr int kSchedSlots = 4;
 constexpr int kEpilogueWarp0 = 4;
+constexpr int kLookahead = 8;       // semaphores probed ahead of a consumer wait
 constexpr int kStoreCols = 64;      // columns per TMA store box (128 bytes)
 constexpr uint32_t kSmemLimit = 232448;  // 227 KB
 
@@ -176,6 +178,8 @@ struct GemmParams {
   int32_t b_kmajor;            // 1: B given as [n,k] row-major
   int32_t is_producer, is_consumer;
   uint32_t b_lbo, b_sbo, b_kstep;  // B shared-memory descriptor: leading / stride offsets, bytes per UMMA K step
+  unsigned long long* trace;       // optional per-tile timeline: 4 words per ticket (see cusync_gemm_plan_set_trace)
+  uint32_t trace_capacity;
   cusync_stage_view_t stage;   // by-value copy, like params_.custage in the reference
 };
 
@@ -185,7 +189,7 @@ struct Cfg {
   static constexpr int kABytes = kBlockM * kBlockK * 2;
   static constexpr int kBBytes = BN * kBlockK * 2;
   static constexpr int kStageBytes = kABytes + kNumB * kBBytes;
-  static constexpr int kStagingBytes = 4 * 2 * 32 * 128;   // 4 warps x 2 buffers x 32 rows x 128 B
+  static constexpr int kStagingBytes = kEpilogueWarps * 32 * 128;   // one 32-row x 128-byte buffer per epilogue warp
   static constexpr int kBarrierBytes = 1024;
   static constexpr int kStages =
       ((int)kSmemLimit - 1024 /*alignment slack*/ - kStagingBytes - kBarrierBytes) / kStageBytes > 8
@@ -208,8 +212,9 @@ struct Barriers {
   uint64_t sched_full[kSchedSlots];
   uint64_t sched_empty[kSchedSlots];
   uint64_t drain;
-  uint64_t post;                        // 4 epilogue warps -> the posting thread
-  int32_t sched_tile[kSchedSlots][4];   // {n tile, m tile, valid, unused}
+  uint64_t post;                        // epilogue warps -> the posting thread
+  int32_t sched_tile[kSchedSlots][4];   // {n tile, m tile, valid, ticket}
+  unsigned long long sched_time[kSchedSlots];   // globaltimer at the ticket draw (tracing only)
   uint32_t tmem_base;
   volatile uint32_t abort;
 };
@@ -271,10 +276,10 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < C::kStages; i++) { mbar_init(&bars->full[i], 1); mbar_init(&bars->empty[i], 1); }
-    for (int i = 0; i < 2; i++) { mbar_init(&bars->tmem_full[i], 1); mbar_init(&bars->tmem_empty[i], 4); }
-    for (int i = 0; i < kSchedSlots; i++) { mbar_init(&bars->sched_full[i], 1); mbar_init(&bars->sched_empty[i], 5); }
+    for (int i = 0; i < 2; i++) { mbar_init(&bars->tmem_full[i], 1); mbar_init(&bars->tmem_empty[i], kEpilogueWarps); }
+    for (int i = 0; i < kSchedSlots; i++) { mbar_init(&bars->sched_full[i], 1); mbar_init(&bars->sched_empty[i], 1 + kEpilogueWarps); }
     mbar_init(&bars->drain, 1);
-    mbar_init(&bars->post, 4);
+    mbar_init(&bars->post, kEpilogueWarps);
     bars->abort = 0u;
     fence_barrier_init();
     fence_proxy_async_smem();
@@ -306,6 +311,14 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       uint32_t fills = 0, sched_it = 0;
       bool ok = true;
       const uint32_t total_draws = static_cast<uint32_t>(p.num_tiles) + gridDim.x;
+      const uint32_t wait_target = p.is_consumer ? st.iter * cusync::eval::waitValue(st.in_policy) : 0u;
+      // Distance along K between two sync points of the input policy (0: it syncs once per tile).
+      uint32_t sync_stride = 0;
+      if (p.is_consumer) {
+        const int kind = st.in_policy.kind;
+        if (kind == CUSYNC_POLICY_TILESYNC || kind == CUSYNC_POLICY_STRIDEDTILESYNC) sync_stride = st.in_policy.tile_n;
+        else if (kind == CUSYNC_POLICY_CONV2DTILESYNC) sync_stride = st.in_policy.tile_n * st.in_policy.p0;
+      }
       while (ok) {
         const uint32_t slot = sched_it % kSchedSlots, sph = (sched_it / kSchedSlots) & 1u;
         if (!mbar_wait(&bars->sched_empty[slot], sph ^ 1u, ctx)) { ok = false; break; }
@@ -320,12 +333,15 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         bars->sched_tile[slot][0] = static_cast<int32_t>(t.x);
         bars->sched_tile[slot][1] = static_cast<int32_t>(t.y);
         bars->sched_tile[slot][2] = valid ? 1 : 0;
+        bars->sched_tile[slot][3] = static_cast<int32_t>(ticket);
+        if (p.trace) bars->sched_time[slot] = cusync::globalTimerNs();
         mbar_arrive(&bars->sched_full[slot]);
         sched_it++;
         if (!valid) break;
 
         const int n_off = static_cast<int>(t.x) * BN;
         const int m_off = static_cast<int>(t.y) * kBlockM;
+        uint32_t ready_end = 0;   // K offset below which this tile's producer tiles are known finished
         for (int kb = 0; kb < p.num_k_blocks; kb++) {
           const uint32_t s = fills % C::kStages, ph = (fills / C::kStages) & 1u;
           if (!mbar_wait(&bars->empty[s], ph ^ 1u, ctx)) { ok = false; break; }
@@ -350,22 +366,44 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           // Consumer wait, at the load of the dependent A K-block.
           if (p.is_consumer) {
             const uint32_t tz = kb == 0 ? 1u : 0u;
-            if (cusync::eval::isSync(st.in_policy, static_cast<uint32_t>(k_off), tz)) {
+            if (static_cast<uint32_t>(k_off) >= ready_end &&
+                cusync::eval::isSync(st.in_policy, static_cast<uint32_t>(k_off), tz)) {
               const uint32_t idx = cusync::eval::tileIndex(st.in_policy, static_cast<uint32_t>(m_off),
                                                            static_cast<uint32_t>(k_off), st.prod_grid.x,
                                                            st.prod_grid.y);
-              const uint32_t expected = st.iter * cusync::eval::waitValue(st.in_policy);
               uint32_t seen = 0;
-              if (!cusync::spinUntilAtLeast(st.sems_wait + idx, expected, st.timeout_ns, &seen)) {
+              if (!cusync::spinUntilAtLeast(st.sems_wait + idx, wait_target, st.timeout_ns, &seen)) {
                 bars->abort = 1u;
                 cusync::recordTimeout(st.status, 1u, static_cast<uint32_t>(m_off), static_cast<uint32_t>(k_off), tz,
-                                      idx, seen, expected);
+                                      idx, seen, wait_target);
                 // The stage was armed: give it its A bytes anyway so the
                 // barrier completes and the drain below terminates.
                 tma_load_2d(sa, &tmA, &bars->full[s], k_off, m_off);
                 fills++;
                 ok = false;
                 break;
+              }
+              // Look ahead: probe the semaphores of the next producer tiles along K with independent
+              // relaxed loads (one memory round trip for all of them) and remember how far the
+              // finished prefix reaches, so later K-blocks skip the wait.  The relaxed loads are
+              // made acquiring by the fence that follows.
+              if (sync_stride) {
+                uint32_t vals[kLookahead];
+#pragma unroll
+                for (int j = 0; j < kLookahead; j++) {
+                  const uint32_t kk = static_cast<uint32_t>(k_off) + (j + 1) * sync_stride;
+                  vals[j] = kk < static_cast<uint32_t>(p.k)
+                                ? cusync::loadRelaxed(st.sems_wait + cusync::eval::tileIndex(st.in_policy,
+                                      static_cast<uint32_t>(m_off), kk, st.prod_grid.x, st.prod_grid.y))
+                                : 0u;
+                }
+                uint32_t ahead = 0;
+#pragma unroll
+                for (int j = 0; j < kLookahead; j++) {
+                  if (ahead == static_cast<uint32_t>(j) && vals[j] >= wait_target) ahead++;
+                }
+                ready_end = static_cast<uint32_t>(k_off) + (ahead + 1) * sync_stride;
+                if (ahead) __threadfence();
               }
               // Order the acquire (generic proxy) before the TMA read (async proxy).
               fence_proxy_async();
@@ -449,9 +487,11 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     // =====================================================================
     // Epilogue
     // =====================================================================
-    const int ew = warp - kEpilogueWarp0;              // == warp % 4: this warp's TMEM lane quarter
-    uint8_t* stage_buf = staging + ew * (2 * 32 * 128);
-    uint32_t sched_it = 0, acc_it = 0, store_it = 0, post_it = 0;
+    const int ew = warp - kEpilogueWarp0;
+    const int quarter = ew & 3;                        // == warp % 4: the TMEM lanes this warp may read
+    const int half = ew >> 2;                          // which 64-column chunks of the tile it takes
+    uint8_t* buf = staging + ew * (32 * 128);
+    uint32_t sched_it = 0, acc_it = 0, post_it = 0;
     bool ok = true;
     while (ok) {
       const uint32_t slot = sched_it % kSchedSlots, sph = (sched_it / kSchedSlots) & 1u;
@@ -459,6 +499,8 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       const int tile_n = bars->sched_tile[slot][0];
       const int tile_m = bars->sched_tile[slot][1];
       const int valid = bars->sched_tile[slot][2];
+      const uint32_t ticket = static_cast<uint32_t>(bars->sched_tile[slot][3]);
+      const unsigned long long t_draw = p.trace ? bars->sched_time[slot] : 0ull;
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->sched_empty[slot]);
       sched_it++;
@@ -466,16 +508,16 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       const uint32_t acc = acc_it & 1u, aph = (acc_it >> 1) & 1u;
       if (!mbar_wait(&bars->tmem_full[acc], aph, ctx)) { ok = false; break; }
       tc_fence_after();
+      const unsigned long long t_mma_done = p.trace ? cusync::globalTimerNs() : 0ull;
       const int n_off = tile_n * BN, m_off = tile_m * kBlockM;
-      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + acc * C::kAccCols;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * C::kAccCols;
 
-      const bool rows_in = m_off + ew * 32 < p.m;       // else this warp's 32 rows are all padding
+      const bool rows_in = m_off + quarter * 32 < p.m;  // else this warp's 32 rows are all padding
 #pragma unroll 1
-      for (int c = 0; c < BN / kStoreCols && rows_in; c++) {
+      for (int c = half; c < BN / kStoreCols && rows_in; c += 2) {
         if (n_off + c * kStoreCols >= p.n) break;       // chunk entirely past the matrix edge
-        uint8_t* buf = stage_buf + (store_it & 1u) * (32 * 128);
-        // The store that last read this buffer must be done reading it.
-        if (lane == 0) tma_store_wait_read<1>();
+        // The store that last read this warp's buffer must be done reading it.
+        if (lane == 0) tma_store_wait_read<0>();
         __syncwarp();
         uint32_t packed[32];
         if (!DUAL) {
@@ -516,10 +558,9 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          tma_store_2d(&tmD, buf, n_off + c * kStoreCols, m_off + ew * 32);
+          tma_store_2d(&tmD, buf, n_off + c * kStoreCols, m_off + quarter * 32);
           tma_store_commit();
         }
-        store_it++;
       }
       // Accumulator buffer is free for the MMA warp again.
       tc_fence_before();
@@ -550,6 +591,13 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         }
         post_it++;
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      }
+      if (p.trace && ew == 0 && lane == 0 && ticket < p.trace_capacity) {
+        uint32_t smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        unsigned long long* rec = p.trace + 4ull * ticket;
+        rec[0] = t_draw; rec[1] = t_mma_done; rec[2] = cusync::globalTimerNs();
+        rec[3] = (static_cast<unsigned long long>(smid) << 32) | blockIdx.x;
       }
     }
     if (lane == 0) tma_store_wait_all();
@@ -781,6 +829,13 @@ int cusync_gemm_plan_update(cusync_gemm_plan_t* pl, const void* a, const void* b
 }
 
 uint32_t cusync_gemm_plan_num_ctas(const cusync_gemm_plan_t* pl) { return pl ? pl->num_ctas : 0; }
+
+int cusync_gemm_plan_set_trace(cusync_gemm_plan_t* pl, void* device_buffer, uint32_t capacity_tiles) {
+  if (!pl) return CUSYNC_ERROR_NOT_INITIALIZED;
+  pl->params.trace = static_cast<unsigned long long*>(device_buffer);
+  pl->params.trace_capacity = device_buffer ? capacity_tiles : 0;
+  return CUSYNC_SUCCESS;
+}
 
 int cusync_gemm_run(cusync_gemm_plan_t* pl, cusync_stream_t stream) {
   if (!pl) return CUSYNC_ERROR_NOT_INITIALIZED;

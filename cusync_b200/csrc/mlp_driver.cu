@@ -17,6 +17,7 @@ struct cusync_mlp {
   cusync_gemm_plan_t* sync2;    // consumer GEMM with its stage
   cusync_gemm_plan_t* plain1;   // same kernels without tile synchronisation
   cusync_gemm_plan_t* plain2;
+  cusync_stage_t* plain_stage2; // NoSync stage carrying the consumer's tile order for the baseline
 };
 
 namespace {
@@ -51,6 +52,7 @@ void destroy_all(cusync_mlp* m) {
   if (m->plain2) cusync_gemm_plan_destroy(m->plain2);
   if (m->prod) cusync_stage_destroy(m->prod);
   if (m->cons) cusync_stage_destroy(m->cons);
+  if (m->plain_stage2) cusync_stage_destroy(m->plain_stage2);
   delete m;
 }
 
@@ -96,14 +98,16 @@ int cusync_mlp_create(cusync_mlp_t** out, const cusync_mlp_desc_t* desc) {
   if (d.policy == CUSYNC_POLICY_ROWSYNC) opts &= ~CUSYNC_OPT_NO_ATOMIC_ADD;
   cusync_dim3_t ts = {1, 1, 1};
   int rc = cusync_stage_create(&m->prod, grid1, ts, CUSYNC_ORDER_TRANSPOSE_XY, &none, &sync, opts);
-  if (rc == CUSYNC_SUCCESS) rc = cusync_stage_create(&m->cons, grid2, ts, CUSYNC_ORDER_TRANSPOSE_XY, &sync, &none, opts);
+  const int order2 = d.group_rows2 > 0 ? CUSYNC_ORDER_GROUPED(d.group_rows2) : CUSYNC_ORDER_TRANSPOSE_XY;
+  if (rc == CUSYNC_SUCCESS) rc = cusync_stage_create(&m->cons, grid2, ts, order2, &sync, &none, opts);
   if (rc == CUSYNC_SUCCESS) rc = cusync_stage_link(m->prod, m->cons);
 
   cusync_gemm_desc_t g;
   if (rc == CUSYNC_SUCCESS) { fill_gemm1(d, m->tile_n1, m->prod, &g); rc = cusync_gemm_plan_create(&m->sync1, &g); }
   if (rc == CUSYNC_SUCCESS) { fill_gemm2(d, m->tile_n2, m->cons, &g); rc = cusync_gemm_plan_create(&m->sync2, &g); }
   if (rc == CUSYNC_SUCCESS) { fill_gemm1(d, m->tile_n1, nullptr, &g); rc = cusync_gemm_plan_create(&m->plain1, &g); }
-  if (rc == CUSYNC_SUCCESS) { fill_gemm2(d, m->tile_n2, nullptr, &g); rc = cusync_gemm_plan_create(&m->plain2, &g); }
+  if (rc == CUSYNC_SUCCESS) rc = cusync_stage_create(&m->plain_stage2, grid2, ts, order2, &none, &none, CUSYNC_OPT_NONE);
+  if (rc == CUSYNC_SUCCESS) { fill_gemm2(d, m->tile_n2, m->plain_stage2, &g); rc = cusync_gemm_plan_create(&m->plain2, &g); }
   if (rc != CUSYNC_SUCCESS) { destroy_all(m); return rc; }
   *out = m;
   return CUSYNC_SUCCESS;
@@ -157,6 +161,12 @@ int cusync_mlp_update_io(cusync_mlp_t* m, const void* x, void* y) {
 cusync_stage_t* cusync_mlp_stage(cusync_mlp_t* m, int which) {
   if (!m) return nullptr;
   return which == 0 ? m->prod : m->cons;
+}
+
+int cusync_mlp_set_trace(cusync_mlp_t* m, void* t1, uint32_t c1, void* t2, uint32_t c2) {
+  if (!m) return CUSYNC_ERROR_NOT_INITIALIZED;
+  cusync_gemm_plan_set_trace(m->sync1, t1, c1);
+  return cusync_gemm_plan_set_trace(m->sync2, t2, c2);
 }
 
 int cusync_mlp_config(const cusync_mlp_t* m, int32_t* out4) {

@@ -40,6 +40,7 @@ bool policy_ok(const cusync_policy_t* p) {
   if (p == nullptr) return true;
   if (p->kind < CUSYNC_POLICY_NOSYNC || p->kind > CUSYNC_POLICY_CUSTOM) return false;
   if (p->kind == CUSYNC_POLICY_NOSYNC || p->kind == CUSYNC_POLICY_CUSTOM) return true;
+  if (p->order != CUSYNC_ORDER_IDENTITY && p->order != CUSYNC_ORDER_TRANSPOSE_XY) return false;
   if (p->tile_m == 0 || p->tile_n == 0) return false;
   if (p->kind == CUSYNC_POLICY_CONV2DTILESYNC && p->p0 == 0) return false;
   if (p->kind == CUSYNC_POLICY_STRIDEDTILESYNC && (p->p0 < p->tile_n || p->p1 == 0)) return false;
@@ -56,7 +57,12 @@ int cusync_stage_create(cusync_stage_t** out, cusync_dim3_t grid, cusync_dim3_t 
   if (out == nullptr) return CUSYNC_ERROR_INVALID_ARGUMENT;
   *out = nullptr;
   if (grid.x == 0 || grid.y == 0 || grid.z == 0) return CUSYNC_ERROR_INVALID_ARGUMENT;
-  if (order != CUSYNC_ORDER_IDENTITY && order != CUSYNC_ORDER_TRANSPOSE_XY) return CUSYNC_ERROR_INVALID_ARGUMENT;
+  const int order_kind = order & 0xff;
+  const uint32_t group_rows = static_cast<uint32_t>(order) >> 8;
+  if (order_kind != CUSYNC_ORDER_IDENTITY && order_kind != CUSYNC_ORDER_TRANSPOSE_XY &&
+      order_kind != CUSYNC_ORDER_GROUPED_ROWS)
+    return CUSYNC_ERROR_INVALID_ARGUMENT;
+  if ((order_kind == CUSYNC_ORDER_GROUPED_ROWS) != (group_rows != 0)) return CUSYNC_ERROR_INVALID_ARGUMENT;
   if (!policy_ok(in_policy) || !policy_ok(out_policy)) return CUSYNC_ERROR_INVALID_ARGUMENT;
   uint64_t n64 = (uint64_t)grid.x * grid.y * grid.z;
   if (n64 > (1ull << 30)) return CUSYNC_ERROR_INVALID_ARGUMENT;
@@ -77,15 +83,18 @@ int cusync_stage_create(cusync_stage_t** out, cusync_dim3_t grid, cusync_dim3_t 
   s->view.timeout_ns = cusync::kDefaultSpinTimeoutNs;
   if (cudaGetDevice(&s->device) != cudaSuccess) { delete s; return CUSYNC_ERROR_CUDA; }
 
-  // Schedule buffer: slot blockIndex(grid, block) holds block (x, y, z).  Both
-  // tile orders linearise the launch grid x-fastest; a slot written twice or a
-  // slot out of range is the invalid-linear-index error.
+  // Schedule buffer: slot blockIndex(grid, block) holds block (x, y, z).  The
+  // reference's two orders linearise the launch grid x-fastest; the grouped
+  // order walks groups of rows.  A slot written twice or a slot out of range
+  // is the invalid-linear-index error.
   std::vector<cusync_dim3_t> order_host(s->num_tiles, cusync_dim3_t{s->num_tiles, 0, 0});
   bool invalid = false;
   for (uint32_t z = 0; z < grid.z; z++)
     for (uint32_t y = 0; y < grid.y; y++)
       for (uint32_t x = 0; x < grid.x; x++) {
-        uint32_t id = cusync::eval::blockIndex(grid.x, grid.y, x, y, z);
+        uint32_t id = order_kind == CUSYNC_ORDER_GROUPED_ROWS
+                          ? cusync::eval::groupedBlockIndex(group_rows, grid.x, grid.y, x, y, z)
+                          : cusync::eval::blockIndex(grid.x, grid.y, x, y, z);
         if (id >= s->num_tiles || order_host[id].x != s->num_tiles) { invalid = true; continue; }
         order_host[id] = cusync_dim3_t{x, y, z};
       }

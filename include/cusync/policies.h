@@ -68,7 +68,8 @@ struct RowSync : public detail::RecordPolicy<RowSync<TileM>> {
 // its K walk enters a new producer tile.
 template <typename TileOrder, uint32_t TileM, uint32_t TileN>
 struct TileSync : public detail::RecordPolicy<TileSync<TileOrder, TileM, TileN>> {
-  static_assert(TileOrder::kOrderKind >= 0, "TileSync needs a built-in tile order");
+  static_assert(TileOrder::kOrderKind == CUSYNC_ORDER_IDENTITY || TileOrder::kOrderKind == CUSYNC_ORDER_TRANSPOSE_XY,
+                "TileSync numbers its semaphores with IdentityOrder or TransposeXYOrder");
   uint32_t waitValue_, postValue_;
   CUSYNC_DEVICE_HOST TileSync() : waitValue_(1), postValue_(1) {}
   CUSYNC_DEVICE_HOST TileSync(uint32_t waitValue, uint32_t postValue) : waitValue_(waitValue), postValue_(postValue) {}
@@ -81,7 +82,8 @@ struct TileSync : public detail::RecordPolicy<TileSync<TileOrder, TileM, TileN>>
 // `stride`: the consumer's K tile needs both halves of a [X*W1 | X*V] output.
 template <typename TileOrder, uint32_t GridN, uint32_t TileM, uint32_t TileN, uint32_t stride>
 struct StridedTileSync : public detail::RecordPolicy<StridedTileSync<TileOrder, GridN, TileM, TileN, stride>> {
-  static_assert(TileOrder::kOrderKind >= 0, "StridedTileSync needs a built-in tile order");
+  static_assert(TileOrder::kOrderKind == CUSYNC_ORDER_IDENTITY || TileOrder::kOrderKind == CUSYNC_ORDER_TRANSPOSE_XY,
+                "StridedTileSync numbers its semaphores with IdentityOrder or TransposeXYOrder");
   CUSYNC_DEVICE_HOST StridedTileSync() {}
   CUSYNC_DEVICE_HOST cusync_policy_t desc() const {
     return cusync_policy_t{CUSYNC_POLICY_STRIDEDTILESYNC, TileOrder::kOrderKind, TileM, TileN, 0, 0, GridN, stride};
@@ -93,7 +95,8 @@ using StridedSync = StridedTileSync<TileOrder, GridN, TileM, TileN, stride>;
 // The (H/8)/TileN adjacent column tiles of one of Q, K, V share a semaphore.
 template <typename TileOrder, uint32_t H, uint32_t TileM, uint32_t TileN>
 struct ConsecutiveTileSync : public detail::RecordPolicy<ConsecutiveTileSync<TileOrder, H, TileM, TileN>> {
-  static_assert(TileOrder::kOrderKind >= 0, "ConsecutiveTileSync needs a built-in tile order");
+  static_assert(TileOrder::kOrderKind == CUSYNC_ORDER_IDENTITY || TileOrder::kOrderKind == CUSYNC_ORDER_TRANSPOSE_XY,
+                "ConsecutiveTileSync numbers its semaphores with IdentityOrder or TransposeXYOrder");
   CUSYNC_DEVICE_HOST ConsecutiveTileSync() {}
   CUSYNC_DEVICE_HOST cusync_policy_t desc() const {
     return cusync_policy_t{CUSYNC_POLICY_CONSECUTIVETILESYNC, TileOrder::kOrderKind, TileM, TileN, 0, 0, H, 0};
@@ -107,7 +110,8 @@ using ConsecutiveSync = ConsecutiveTileSync<TileOrder, H, TileM, TileN>;
 // column tile y / (R*S).
 template <typename TileOrder, uint32_t R, uint32_t S, uint32_t TileM, uint32_t TileN>
 struct Conv2DTileSync : public detail::RecordPolicy<Conv2DTileSync<TileOrder, R, S, TileM, TileN>> {
-  static_assert(TileOrder::kOrderKind >= 0, "Conv2DTileSync needs a built-in tile order");
+  static_assert(TileOrder::kOrderKind == CUSYNC_ORDER_IDENTITY || TileOrder::kOrderKind == CUSYNC_ORDER_TRANSPOSE_XY,
+                "Conv2DTileSync numbers its semaphores with IdentityOrder or TransposeXYOrder");
   uint32_t waitValue_, postValue_;
   CUSYNC_DEVICE_HOST Conv2DTileSync() : waitValue_(1), postValue_(1) {}
   CUSYNC_DEVICE_HOST Conv2DTileSync(uint32_t waitValue, uint32_t postValue)

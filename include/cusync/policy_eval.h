@@ -17,6 +17,16 @@ CUSYNC_DEVICE_HOST uint32_t blockIndex(uint32_t gx, uint32_t gy, uint32_t bx, ui
   return bx + by * gx + bz * gx * gy;
 }
 
+// Linear index of block (bx, by, bz) under the grouped-rows order: groups of `rows` grid rows, the row
+// index fastest inside a group, then the column; z outermost.
+CUSYNC_DEVICE_HOST uint32_t groupedBlockIndex(uint32_t rows, uint32_t gx, uint32_t gy, uint32_t bx, uint32_t by,
+                                              uint32_t bz) {
+  const uint32_t group = by / rows;
+  const uint32_t first = group * rows;
+  const uint32_t height = gy - first < rows ? gy - first : rows;   // the last group may be short
+  return bz * gx * gy + first * gx + bx * height + (by - first);
+}
+
 // Semaphore index of tile (tx, ty) under `order`: TransposeXY swaps the tile's
 // coordinates before linearising, Identity does not.
 CUSYNC_DEVICE_HOST uint32_t orderTileIndex(int order, uint32_t tx, uint32_t ty, uint32_t gx, uint32_t gy) {

@@ -46,4 +46,16 @@ struct IdentityOrder : public GenericTileOrder<IdentityOrder> {
   CUSYNC_DEVICE_HOST dim3 tileToBlock(const dim3& tile) { return dim3(tile.x, tile.y, tile.z); }
 };
 
+// Addition: blocks are taken in groups of Rows grid rows, row index fastest inside a group (see
+// CUSYNC_ORDER_GROUPED).  Tiles map to blocks like TransposeXYOrder.
+template <uint32_t Rows>
+struct GroupedRowsOrder : public GenericTileOrder<GroupedRowsOrder<Rows>> {
+  static_assert(Rows >= 1, "group height must be positive");
+  static constexpr int kOrderKind = CUSYNC_ORDER_GROUPED(Rows);
+  CUSYNC_DEVICE_HOST uint32_t blockIndex(const dim3& grid, const dim3& block) {
+    return eval::groupedBlockIndex(Rows, grid.x, grid.y, block.x, block.y, block.z);
+  }
+  CUSYNC_DEVICE_HOST dim3 tileToBlock(const dim3& tile) { return dim3(tile.y, tile.x, tile.z); }
+};
+
 }  // namespace cusync

@@ -54,7 +54,12 @@ enum {
 };
 
 /* Tile orders (src/include/cusync/tile-orders.h:50-76). */
-enum { CUSYNC_ORDER_IDENTITY = 0, CUSYNC_ORDER_TRANSPOSE_XY = 1 };
+enum { CUSYNC_ORDER_IDENTITY = 0, CUSYNC_ORDER_TRANSPOSE_XY = 1, CUSYNC_ORDER_GROUPED_ROWS = 2 };
+/* Addition for L2 locality on large-L2 parts: blocks are taken in groups of `rows` consecutive grid rows
+ * (M tiles); inside a group the row index runs fastest, then the column (N tile).  Blocks that run at the
+ * same time then share few weight (B) tiles and a bounded set of activation (A) row panels.  As a stage's
+ * schedule order only; a policy's `order` field stays IDENTITY or TRANSPOSE_XY. */
+#define CUSYNC_ORDER_GROUPED(rows) (CUSYNC_ORDER_GROUPED_ROWS | ((rows) << 8))
 
 /* Sync policies as data.  NOSYNC/ROWSYNC/TILESYNC/CONV2DTILESYNC:
  * src/include/cusync/policies.h:18-210.  STRIDEDTILESYNC: StridedSync,
@@ -223,6 +228,11 @@ CUSYNC_API int cusync_gemm_plan_update(cusync_gemm_plan_t* plan, const void* a, 
                             const void* b2, void* d);
 /* run(bool overlap, int*, cudaStream_t) (gemm/device/cusyncgemm.h:525-563). */
 CUSYNC_API int cusync_gemm_run(cusync_gemm_plan_t* plan, cusync_stream_t stream);
+/* Optional per-tile timeline, the only profiling hook beyond CUDA events: with a device buffer of
+ * 4 * capacity_tiles 64-bit words set, every tile writes, at index 4 * ticket,
+ * {globaltimer at the ticket draw, at the end of its MMAs, after its stores and post,
+ *  (SM id << 32) | block index}.  NULL switches it off (the default).  No counterpart in the reference. */
+CUSYNC_API int cusync_gemm_plan_set_trace(cusync_gemm_plan_t* plan, void* device_buffer, uint32_t capacity_tiles);
 /* Blocks the launch uses (persistent grid). */
 CUSYNC_API uint32_t cusync_gemm_plan_num_ctas(const cusync_gemm_plan_t* plan);
 
@@ -243,6 +253,7 @@ typedef struct cusync_mlp_desc {
   int32_t opts;                  /* CUSYNC_OPT_* applied to both stages */
   int32_t tile_n1, tile_n2;      /* 0 = choose */
   int32_t max_ctas;              /* 0 = one per SM */
+  int32_t group_rows2;           /* > 0: the consumer takes its tiles in CUSYNC_ORDER_GROUPED(group_rows2) order */
   const void* x; const void* w1; const void* v; const void* w2;
   void* h; void* y;
 } cusync_mlp_desc_t;
@@ -268,6 +279,8 @@ CUSYNC_API int cusync_mlp_run_single(cusync_mlp_t* mlp, int which, cusync_stream
 CUSYNC_API int cusync_mlp_update_io(cusync_mlp_t* mlp, const void* x, void* y);
 /* Stage handles (0 = producer, 1 = consumer) for inspection. */
 CUSYNC_API cusync_stage_t* cusync_mlp_stage(cusync_mlp_t* mlp, int which);
+/* Timeline buffers for the two synchronised GEMMs (see cusync_gemm_plan_set_trace). */
+CUSYNC_API int cusync_mlp_set_trace(cusync_mlp_t* mlp, void* trace1, uint32_t capacity1, void* trace2, uint32_t capacity2);
 /* Tile widths and block counts in use: out[0..3] = tile_n1, tile_n2, ctas1, ctas2. */
 CUSYNC_API int cusync_mlp_config(const cusync_mlp_t* mlp, int32_t* out4);
 

@@ -18,3 +18,6 @@ API uint32_t pe_block_index(uint32_t gx, uint32_t gy, uint32_t bx, uint32_t by, 
 API uint32_t pe_order_tile_index(int order, uint32_t tx, uint32_t ty, uint32_t gx, uint32_t gy) {
   return cusync::eval::orderTileIndex(order, tx, ty, gx, gy);
 }
+API uint32_t pe_grouped_block_index(uint32_t rows, uint32_t gx, uint32_t gy, uint32_t bx, uint32_t by, uint32_t bz) {
+  return cusync::eval::groupedBlockIndex(rows, gx, gy, bx, by, bz);
+}

@@ -131,3 +131,21 @@ def test_plan_create_rejects_bad_arguments_without_a_device():
     assert L.lib().cusync_gemm_plan_create(C.byref(plan), C.byref(d)) == L.ERROR_INVALID_ARGUMENT
     assert L.lib().cusync_stage_link(None, None) == L.ERROR_NOT_INITIALIZED
     assert L.lib().cusync_stage_increment_iter(None) == L.ERROR_NOT_INITIALIZED
+
+
+def test_grouped_rows_order_is_a_bijection_with_rows_fastest():
+    so = C.CDLL(bh.build_policy_eval_host())
+    so.pe_grouped_block_index.restype = C.c_uint32
+    so.pe_grouped_block_index.argtypes = [C.c_uint32] * 6
+    for rows, gx, gy, gz in ((6, 48, 16, 1), (4, 5, 7, 2), (16, 3, 16, 1), (1, 4, 3, 1), (5, 2, 3, 1)):
+        seen = {}
+        for z in range(gz):
+            for y in range(gy):
+                for x in range(gx):
+                    seen[so.pe_grouped_block_index(rows, gx, gy, x, y, z)] = (x, y, z)
+        assert sorted(seen) == list(range(gx * gy * gz))
+        # consecutive slots inside a group walk down the rows of one column
+        first_group = [seen[i] for i in range(min(rows, gy))]
+        assert first_group == [(0, y, 0) for y in range(min(rows, gy))]
+        if gx > 1:
+            assert seen[min(rows, gy)] == (1, 0, 0)
