@@ -760,10 +760,6 @@ int cusync_gemm_plan_create(cusync_gemm_plan_t** out, const cusync_gemm_desc_t* 
     // UMMA K step is 16 rows = 2048 B.
     p.b_lbo = kBlockK * 128; p.b_sbo = 1024; p.b_kstep = kUmmaK * 128;
   }
-  if (const char* dbg = getenv("CUSYNC_DEBUG_BDESC")) {
-    unsigned a = 0, b = 0, c = 0;
-    if (sscanf(dbg, "%u,%u,%u", &a, &b, &c) == 3) { p.b_lbo = a; p.b_sbo = b; p.b_kstep = c; }
-  }
 
   pl->stage = d.stage;
   if (pl->stage == nullptr) {
