@@ -12,10 +12,11 @@ LIB_PATH = os.path.join(HERE, "libcusync_b200.so")
 
 # status codes (include/cusync_b200.h)
 ERROR_NOT_PRODUCER, ERROR_NOT_CONSUMER, ERROR_NOT_INITIALIZED, ERROR_INVALID_LINEAR_BLOCK_INDEX, \
-    ERROR_CUDA, SUCCESS, ERROR_TIMEOUT, ERROR_INVALID_ARGUMENT, ERROR_UNSUPPORTED = range(9)
+    ERROR_CUDA, SUCCESS, ERROR_TIMEOUT, ERROR_INVALID_ARGUMENT, ERROR_UNSUPPORTED, ERROR_EXCEEDS_STATIC_SCRATCH = range(10)
 ERROR_NAMES = ["CuSyncErrorNotProducer", "CuSyncErrorNotConsumer", "CuSyncErrorNotInitialized",
                "CuSyncErrorInvalidLinearBlockIndex", "CuSyncErrorCUDAError", "CuSyncSuccess",
-               "CuSyncErrorTimeout", "CuSyncErrorInvalidArgument", "CuSyncErrorUnsupported"]
+               "CuSyncErrorTimeout", "CuSyncErrorInvalidArgument", "CuSyncErrorUnsupported",
+               "CuSyncErrorExceedsStaticScratch"]
 
 OPT_NONE, OPT_NO_ATOMIC_ADD, OPT_AVOID_WAIT_KERNEL, OPT_AVOID_CUSTOM_ORDER, OPT_REORDER_TILE_LOADS = 0, 1, 2, 4, 8
 ORDER_IDENTITY, ORDER_TRANSPOSE_XY, ORDER_GROUPED_ROWS = 0, 1, 2
@@ -98,6 +99,7 @@ SIGNATURES = {
     "cusync_gemm_plan_destroy": (_i, [_vp]),
     "cusync_gemm_plan_update": (_i, [_vp, _vp, _vp, _vp, _vp]),
     "cusync_gemm_run": (_i, [_vp, _vp]),
+    "cusync_gemm_run_noalloc": (_i, [C.POINTER(GemmDesc), _vp]),
     "cusync_gemm_plan_set_trace": (_i, [_vp, _vp, _u32]),
     "cusync_gemm_plan_num_ctas": (_u32, [_vp]),
     "cusync_mlp_create": (_i, [C.POINTER(_vp), C.POINTER(MlpDesc)]),

@@ -36,6 +36,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 #include <new>
 
 #include "common.cuh"
@@ -705,7 +706,139 @@ int build_maps(cusync_gemm_plan* pl) {
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// ---------------------------------------------------------------------------
+// Allocation-free GEMM entry point
+// ---------------------------------------------------------------------------
+// Some hosts of this library may not allocate device memory when they call it:
+// a serving runtime that handed the whole device to its own arena and forbids
+// cudaMalloc from plug-ins; a latency-critical loop in which cudaMalloc/cudaFree
+// would serialise with every stream of the device; a process that is already at
+// its memory limit.  The regular path (cusync_gemm_plan_create) allocates a
+// stage -- schedule buffer, ticket counter, status words -- with cudaMalloc.
+// cusync_gemm_run_noalloc runs the same un-synchronised GEMM kernel with that
+// scratch taken from the fixed array below instead.  The array is part of the
+// library image: every GPU that loads the library holds these ~97 KB until the
+// process exits, whether or not the entry point is ever called.
+constexpr uint32_t kNoAllocMaxTiles = 8192;   // 128 x tile_n output tiles per call, at most
+
+struct NoAllocScratch {
+  uint32_t words[64];                          // [0] ticket counter, [2..3] started, [8..15] status record
+  cusync_dim3_t tile_order[kNoAllocMaxTiles];  // schedule buffer
+};
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[sizeof(NoAllocScratch)];
+
+// Re-arms the shared scratch for one call: zero ticket counter and status
+// words (they keep the previous call's contents), write the row-major
+// schedule.  Device code may name the array directly.
+__global__ void noalloc_prepare_kernel(uint32_t tiles_n, uint32_t num_tiles) {
+  NoAllocScratch* sc = reinterpret_cast<NoAllocScratch*>(g_noalloc_scratch);
+  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < 64) sc->words[i] = 0u;
+  if (i < num_tiles) sc->tile_order[i] = cusync_dim3_t{i % tiles_n, i / tiles_n, 0u};
+}
+
+constexpr int kNoAllocMaxDevices = 64;
+std::mutex g_noalloc_mutex;
+NoAllocScratch* g_noalloc_device_ptr[kNoAllocMaxDevices] = {};
+
+// Device address of the scratch array on the CURRENT device.  In host code the
+// array's name is only a handle for the runtime, never an address a kernel
+// can use, so the address is looked up once per device with
+// cudaGetSymbolAddress (with that device current) and cached.
+int noalloc_scratch_for_current_device(NoAllocScratch** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoAllocMaxDevices) {
+    (void)cudaGetLastError();
+    return CUSYNC_ERROR_CUDA;
+  }
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (g_noalloc_device_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+    if (e != cudaSuccess || ptr == nullptr) {
+      (void)cudaGetLastError();
+      return CUSYNC_ERROR_CUDA;
+    }
+    g_noalloc_device_ptr[dev] = static_cast<NoAllocScratch*>(ptr);
+  }
+  *out = g_noalloc_device_ptr[dev];
+  return CUSYNC_SUCCESS;
+}
+
 }  // namespace
+
+extern "C" int cusync_gemm_run_noalloc(const cusync_gemm_desc_t* desc, cusync_stream_t stream) {
+  if (desc == nullptr) return CUSYNC_ERROR_INVALID_ARGUMENT;
+  const cusync_gemm_desc_t& d = *desc;
+  if (d.stage != nullptr) return CUSYNC_ERROR_INVALID_ARGUMENT;   // stages own allocated memory
+  if (d.m <= 0 || d.n <= 0 || d.k <= 0 || d.a == nullptr || d.b == nullptr || d.d == nullptr)
+    return CUSYNC_ERROR_INVALID_ARGUMENT;
+  if (d.epilogue < CUSYNC_EPILOGUE_NONE || d.epilogue > CUSYNC_EPILOGUE_SILU_MUL_DUAL)
+    return CUSYNC_ERROR_INVALID_ARGUMENT;
+  const bool dual = d.epilogue == CUSYNC_EPILOGUE_SILU_MUL_DUAL;
+  if (dual && d.b2 == nullptr) return CUSYNC_ERROR_INVALID_ARGUMENT;
+  if (d.b_layout != CUSYNC_B_ROW_MAJOR_KN && d.b_layout != CUSYNC_B_ROW_MAJOR_NK) return CUSYNC_ERROR_INVALID_ARGUMENT;
+  if (!aligned16(d.a) || !aligned16(d.b) || !aligned16(d.d) || (dual && !aligned16(d.b2)))
+    return CUSYNC_ERROR_UNSUPPORTED;
+  if (d.lda % 8 || d.ldb % 8 || d.ldd % 8 || d.lda < d.k || d.ldd < d.n) return CUSYNC_ERROR_UNSUPPORTED;
+  if (d.b_layout == CUSYNC_B_ROW_MAJOR_NK ? d.ldb < d.k : d.ldb < d.n) return CUSYNC_ERROR_UNSUPPORTED;
+
+  cusync_gemm_plan pl;                       // on the stack: tensor maps travel as kernel parameters
+  std::memset(&pl, 0, sizeof(pl));
+  pl.desc = d;
+  pl.tile_n = d.tile_n ? d.tile_n : cusync_gemm_default_tile_n(d.m, d.n, d.k, d.epilogue);
+  if (!select_kernel(pl.tile_n, dual, &pl.kernel)) return CUSYNC_ERROR_UNSUPPORTED;
+  GemmParams& p = pl.params;
+  p.m = d.m; p.n = d.n; p.k = d.k;
+  const int64_t tiles_n = (static_cast<int64_t>(d.n) + pl.tile_n - 1) / pl.tile_n;
+  const int64_t tiles_m = (static_cast<int64_t>(d.m) + kBlockM - 1) / kBlockM;
+  if (tiles_n * tiles_m > static_cast<int64_t>(kNoAllocMaxTiles))
+    return CUSYNC_ERROR_EXCEEDS_STATIC_SCRATCH;   // more output tiles than the fixed schedule buffer holds
+  p.tiles_n = static_cast<int32_t>(tiles_n);
+  p.tiles_m = static_cast<int32_t>(tiles_m);
+  p.num_tiles = p.tiles_n * p.tiles_m;
+  p.num_k_blocks = (d.k + kBlockK - 1) / kBlockK;
+  p.epilogue = d.epilogue;
+  p.b_kmajor = d.b_layout == CUSYNC_B_ROW_MAJOR_NK ? 1 : 0;
+  if (p.b_kmajor) { p.b_lbo = 16; p.b_sbo = 1024; p.b_kstep = 32; }
+  else            { p.b_lbo = kBlockK * 128; p.b_sbo = 1024; p.b_kstep = kUmmaK * 128; }
+
+  NoAllocScratch* scratch = nullptr;
+  int rc = noalloc_scratch_for_current_device(&scratch);
+  if (rc != CUSYNC_SUCCESS) return rc;
+  rc = build_maps(&pl);
+  if (rc != CUSYNC_SUCCESS) return rc;
+  if (cudaFuncSetAttribute(reinterpret_cast<const void*>(pl.kernel.fn), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(pl.kernel.smem)) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return CUSYNC_ERROR_CUDA;
+  }
+
+  cusync_stage_view_t& v = p.stage;          // a NoSync stage view over the static scratch
+  v.grid = cusync_dim3_t{static_cast<uint32_t>(p.tiles_n), static_cast<uint32_t>(p.tiles_m), 1};
+  v.tile_size = cusync_dim3_t{1, 1, 1};
+  v.iter = 1;
+  v.order = CUSYNC_ORDER_TRANSPOSE_XY;
+  v.in_policy.tile_m = v.in_policy.tile_n = v.out_policy.tile_m = v.out_policy.tile_n = 1;
+  v.tile_order = scratch->tile_order;
+  v.tile_counter = &scratch->words[0];
+  v.started = &scratch->words[2];
+  v.status = &scratch->words[8];
+  v.timeout_ns = cusync::kDefaultSpinTimeoutNs;
+  p.is_producer = 0; p.is_consumer = 0;
+
+  int sms = cusync_b200_sm_count();
+  if (sms <= 0) sms = 148;
+  const uint32_t cap = d.max_ctas > 0 ? static_cast<uint32_t>(d.max_ctas) : static_cast<uint32_t>(sms);
+  const uint32_t ctas = static_cast<uint32_t>(p.num_tiles) < cap ? static_cast<uint32_t>(p.num_tiles) : cap;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const uint32_t prep_threads = p.num_tiles > 64 ? static_cast<uint32_t>(p.num_tiles) : 64u;
+  noalloc_prepare_kernel<<<(prep_threads + 255) / 256, 256, 0, st>>>(static_cast<uint32_t>(p.tiles_n),
+                                                                     static_cast<uint32_t>(p.num_tiles));
+  pl.kernel.fn<<<ctas, kThreads, pl.kernel.smem, st>>>(pl.tmA, pl.tmB, pl.tmB2, pl.tmD, p);
+  return cudaGetLastError() == cudaSuccess ? CUSYNC_SUCCESS : CUSYNC_ERROR_CUDA;
+}
 
 extern "C" {
 

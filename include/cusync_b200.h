@@ -41,7 +41,8 @@ enum {
   /* additions */
   CUSYNC_ERROR_TIMEOUT = 6,            /* a bounded device-side wait gave up */
   CUSYNC_ERROR_INVALID_ARGUMENT = 7,
-  CUSYNC_ERROR_UNSUPPORTED = 8         /* shape/alignment outside what the kernels implement */
+  CUSYNC_ERROR_UNSUPPORTED = 8,        /* shape/alignment outside what the kernels implement */
+  CUSYNC_ERROR_EXCEEDS_STATIC_SCRATCH = 9  /* cusync_gemm_run_noalloc: more output tiles than its fixed scratch holds */
 };
 
 /* Optimizations bit set (src/include/cusync/cusync.h:69-75). */
@@ -228,6 +229,28 @@ CUSYNC_API int cusync_gemm_plan_update(cusync_gemm_plan_t* plan, const void* a, 
                             const void* b2, void* d);
 /* run(bool overlap, int*, cudaStream_t) (gemm/device/cusyncgemm.h:525-563). */
 CUSYNC_API int cusync_gemm_run(cusync_gemm_plan_t* plan, cusync_stream_t stream);
+/* Allocation-free GEMM.  It has no counterpart in the reference.
+ *
+ * For callers that must not allocate device memory at the point of the call: a plug-in inside a
+ * serving runtime that owns the whole device through its own arena and forbids cudaMalloc, a
+ * latency-critical loop where cudaMalloc / cudaFree would serialise against every stream of the
+ * device, a process already at its memory limit.  cusync_gemm_plan_create allocates a stage
+ * (schedule buffer, ticket counter, status words) with cudaMalloc; this entry point runs the same
+ * kernel, without tile synchronisation (desc->stage must be NULL), on scratch that lives in a fixed
+ * array inside the library image.  It calls no cudaMalloc, cudaFree or other allocating routine;
+ * inputs and the output are still the caller's buffers.
+ *
+ * Limit: at most 8192 output tiles per call (ceil(m / 128) * ceil(n / tile_n)); a larger problem is
+ * refused with CUSYNC_ERROR_EXCEEDS_STATIC_SCRATCH and nothing is launched.  The array costs about
+ * 97 KB of device memory on every GPU that loads the library, for the life of the process.
+ *
+ * The first call on each device looks up the array's device address (with that device current) and
+ * caches it; make that first call outside any stream capture.  All calls on a device share the one
+ * array, which keeps the last call's contents: each call re-arms it on `stream` before its kernel,
+ * so calls issued to one stream are safe back to back, while calls that can overlap on the GPU
+ * (different streams, no dependency) race on it and must be serialised by the caller. */
+CUSYNC_API int cusync_gemm_run_noalloc(const cusync_gemm_desc_t* desc, cusync_stream_t stream);
+
 /* Optional per-tile timeline, the only profiling hook beyond CUDA events: with a device buffer of
  * 4 * capacity_tiles 64-bit words set, every tile writes, at index 4 * ticket,
  * {globaltimer at the ticket draw, at the end of its MMAs, after its stores and post,
