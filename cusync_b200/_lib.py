@@ -61,13 +61,13 @@ class GemmDesc(C.Structure):
                 ("b2", C.c_void_p),
                 ("d", C.c_void_p), ("ldd", C.c_int64),
                 ("b_layout", C.c_int32), ("epilogue", C.c_int32), ("tile_n", C.c_int32), ("max_ctas", C.c_int32),
-                ("stage", C.c_void_p)]
+                ("cta_pair", C.c_int32), ("stage", C.c_void_p)]
 
 
 class MlpDesc(C.Structure):
     _fields_ = [("model", C.c_int32), ("batch", C.c_int32), ("hidden", C.c_int32), ("ffn", C.c_int32),
                 ("policy", C.c_int32), ("opts", C.c_int32), ("tile_n1", C.c_int32), ("tile_n2", C.c_int32),
-                ("max_ctas", C.c_int32), ("group_rows2", C.c_int32),
+                ("max_ctas", C.c_int32), ("cta_pair", C.c_int32), ("group_rows2", C.c_int32),
                 ("x", C.c_void_p), ("w1", C.c_void_p), ("v", C.c_void_p), ("w2", C.c_void_p),
                 ("h", C.c_void_p), ("y", C.c_void_p)]
 

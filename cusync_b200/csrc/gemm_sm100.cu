@@ -38,6 +38,7 @@
 #include <cstring>
 #include <mutex>
 #include <new>
+#include <vector>
 
 #include "common.cuh"
 
@@ -92,6 +93,12 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int c0, int c1) {
@@ -177,8 +184,11 @@ struct GemmParams {
   int32_t num_k_blocks;
   int32_t epilogue;
   int32_t b_kmajor;            // 1: B given as [n,k] row-major
+  int32_t b_chunked3d;         // [k,n] B: all 64-column chunks of a tile come with one 3-D TMA box
   int32_t is_producer, is_consumer;
   uint32_t b_lbo, b_sbo, b_kstep;  // B shared-memory descriptor: leading / stride offsets, bytes per UMMA K step
+  const cusync_dim3_t* pair_order; // CTA-pair kernel: schedule over 256-row pair tiles {n tile, pair row, 0}
+  int32_t num_pairs;
   unsigned long long* trace;       // optional per-tile timeline: 4 words per ticket (see cusync_gemm_plan_set_trace)
   uint32_t trace_capacity;
   cusync_stage_view_t stage;   // by-value copy, like params_.custage in the reference
@@ -252,6 +262,64 @@ __device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x));
 __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
   __half2 h = __floats2half2_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// Epilogue of one warp for one tile: its 32 accumulator rows (TMEM lanes of `t_row`), every second
+// 64-column chunk starting at `half`: tcgen05.ld -> fp32 epilogue math -> fp16 -> swizzled staging
+// buffer -> TMA store.  `row0` is the matrix row of the warp's first lane.
+template <int BN, bool DUAL>
+__device__ __forceinline__ void epilogue_store_rows(const GemmParams& p, const CUtensorMap* tmD, uint8_t* buf,
+                                                    uint32_t t_row, int n_off, int row0, int half, int lane) {
+  const bool rows_in = row0 < p.m;                      // else this warp's 32 rows are all padding
+#pragma unroll 1
+  for (int c = half; c < BN / kStoreCols && rows_in; c += 2) {
+    if (n_off + c * kStoreCols >= p.n) break;           // chunk entirely past the matrix edge
+    // The store that last read this warp's buffer must be done reading it.
+    if (lane == 0) tma_store_wait_read<0>();
+    __syncwarp();
+    uint32_t packed[32];
+    if (!DUAL) {
+      uint32_t v[64];
+      tmem_ld_32x32b_x32(t_row + c * 64, v);
+      tmem_ld_32x32b_x32(t_row + c * 64 + 32, v + 32);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; j++) {
+        float x0 = __uint_as_float(v[2 * j]), x1 = __uint_as_float(v[2 * j + 1]);
+        if (p.epilogue == CUSYNC_EPILOGUE_GELU_ERF) { x0 = gelu_erf(x0); x1 = gelu_erf(x1); }
+        else if (p.epilogue == CUSYNC_EPILOGUE_RELU) { x0 = fmaxf(x0, 0.0f); x1 = fmaxf(x1, 0.0f); }
+        packed[j] = pack_half2(x0, x1);
+      }
+    } else {
+#pragma unroll
+      for (int h = 0; h < 2; h++) {
+        uint32_t a[32], b[32];
+        tmem_ld_32x32b_x32(t_row + c * 64 + h * 32, a);
+        tmem_ld_32x32b_x32(t_row + BN + c * 64 + h * 32, b);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+          float g0 = silu(__uint_as_float(a[2 * j])) * __uint_as_float(b[2 * j]);
+          float g1 = silu(__uint_as_float(a[2 * j + 1])) * __uint_as_float(b[2 * j + 1]);
+          packed[h * 16 + j] = pack_half2(g0, g1);
+        }
+      }
+    }
+    // Row `lane` of the 32 x 64 chunk, 16-byte pieces XOR-swizzled by row so
+    // the layout is the one a 128-byte-swizzle tensor map expects.
+    uint8_t* row = buf + lane * 128;
+#pragma unroll
+    for (int q = 0; q < 8; q++) {
+      uint4 val = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+      *reinterpret_cast<uint4*>(row + ((q ^ (lane & 7)) << 4)) = val;
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_2d(tmD, buf, n_off + c * kStoreCols, row0);
+      tma_store_commit();
+    }
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -343,9 +411,12 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         const int n_off = static_cast<int>(t.x) * BN;
         const int m_off = static_cast<int>(t.y) * kBlockM;
         uint32_t ready_end = 0;   // K offset below which this tile's producer tiles are known finished
+        long long wait_empty = 0;
         for (int kb = 0; kb < p.num_k_blocks; kb++) {
           const uint32_t s = fills % C::kStages, ph = (fills / C::kStages) & 1u;
+          const long long c0 = p.trace ? clock64() : 0;
           if (!mbar_wait(&bars->empty[s], ph ^ 1u, ctx)) { ok = false; break; }
+          if (p.trace) wait_empty += clock64() - c0;
           uint8_t* sa = ring + s * C::kStageBytes;
           uint8_t* sb = sa + C::kABytes;
           mbar_expect_tx(&bars->full[s], C::kStageBytes);
@@ -354,6 +425,11 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           if (p.b_kmajor) {
             tma_load_2d(sb, &tmB, &bars->full[s], k_off, n_off);
             if (DUAL) tma_load_2d(sb + C::kBBytes, &tmB2, &bars->full[s], k_off, n_off);
+          } else if (p.b_chunked3d) {
+            // one box {64 columns, kBlockK rows, BN/64 chunks}: a TMA instruction costs the issuing
+            // thread over a hundred cycles, so fewer and larger boxes keep the loader ahead of the MMAs
+            tma_load_3d(sb, &tmB, &bars->full[s], 0, k_off, n_off / 64);
+            if (DUAL) tma_load_3d(sb + C::kBBytes, &tmB2, &bars->full[s], 0, k_off, n_off / 64);
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 64; j++)
@@ -413,6 +489,7 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           tma_load_2d(sa, &tmA, &bars->full[s], k_off, m_off);
           fills++;
         }
+        if (p.trace && ticket < p.trace_capacity) p.trace[8ull * ticket + 5] = static_cast<unsigned long long>(wait_empty);
       }
       if (!ok) {
         // Abort path: wait (bounded) for every copy still in flight before the
@@ -443,16 +520,22 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         const uint32_t slot = sched_it % kSchedSlots, sph = (sched_it / kSchedSlots) & 1u;
         if (!mbar_wait(&bars->sched_full[slot], sph, ctx)) { ok = false; break; }
         const int valid = bars->sched_tile[slot][2];
+        const uint32_t ticket = static_cast<uint32_t>(bars->sched_tile[slot][3]);
         mbar_arrive(&bars->sched_empty[slot]);
         sched_it++;
         if (!valid) break;
         const uint32_t acc = acc_it & 1u, aph = (acc_it >> 1) & 1u;
+        const long long t_tile0 = p.trace ? clock64() : 0;
         if (!mbar_wait(&bars->tmem_empty[acc], aph ^ 1u, ctx)) { ok = false; break; }
         tc_fence_after();
+        const long long t_acc = p.trace ? clock64() : 0;
+        long long wait_full = 0;
         const uint32_t d_tmem = tmem_base + acc * C::kAccCols;
         for (int kb = 0; kb < p.num_k_blocks; kb++) {
           const uint32_t s = drains % C::kStages, ph = (drains / C::kStages) & 1u;
+          const long long c0 = p.trace ? clock64() : 0;
           if (!mbar_wait(&bars->full[s], ph, ctx)) { ok = false; break; }
+          if (p.trace) wait_full += clock64() - c0;
           tc_fence_after();
           const uint32_t sa = smem_u32(ring + s * C::kStageBytes);
           const uint32_t sb = sa + C::kABytes;
@@ -473,6 +556,11 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         }
         if (!ok) break;
         umma_commit(&bars->tmem_full[acc]);
+        if (p.trace && ticket < p.trace_capacity) {
+          p.trace[8ull * ticket + 4] = static_cast<unsigned long long>(wait_full);
+          p.trace[8ull * ticket + 6] = static_cast<unsigned long long>(clock64() - t_tile0);
+          p.trace[8ull * ticket + 7] = static_cast<unsigned long long>(t_acc - t_tile0);
+        }
         acc_it++;
       }
       if (!ok && issued) {
@@ -513,56 +601,7 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       const int n_off = tile_n * BN, m_off = tile_m * kBlockM;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * C::kAccCols;
 
-      const bool rows_in = m_off + quarter * 32 < p.m;  // else this warp's 32 rows are all padding
-#pragma unroll 1
-      for (int c = half; c < BN / kStoreCols && rows_in; c += 2) {
-        if (n_off + c * kStoreCols >= p.n) break;       // chunk entirely past the matrix edge
-        // The store that last read this warp's buffer must be done reading it.
-        if (lane == 0) tma_store_wait_read<0>();
-        __syncwarp();
-        uint32_t packed[32];
-        if (!DUAL) {
-          uint32_t v[64];
-          tmem_ld_32x32b_x32(t_row + c * 64, v);
-          tmem_ld_32x32b_x32(t_row + c * 64 + 32, v + 32);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 32; j++) {
-            float x0 = __uint_as_float(v[2 * j]), x1 = __uint_as_float(v[2 * j + 1]);
-            if (p.epilogue == CUSYNC_EPILOGUE_GELU_ERF) { x0 = gelu_erf(x0); x1 = gelu_erf(x1); }
-            else if (p.epilogue == CUSYNC_EPILOGUE_RELU) { x0 = fmaxf(x0, 0.0f); x1 = fmaxf(x1, 0.0f); }
-            packed[j] = pack_half2(x0, x1);
-          }
-        } else {
-#pragma unroll
-          for (int h = 0; h < 2; h++) {
-            uint32_t a[32], b[32];
-            tmem_ld_32x32b_x32(t_row + c * 64 + h * 32, a);
-            tmem_ld_32x32b_x32(t_row + BN + c * 64 + h * 32, b);
-            tmem_ld_wait();
-#pragma unroll
-            for (int j = 0; j < 16; j++) {
-              float g0 = silu(__uint_as_float(a[2 * j])) * __uint_as_float(b[2 * j]);
-              float g1 = silu(__uint_as_float(a[2 * j + 1])) * __uint_as_float(b[2 * j + 1]);
-              packed[h * 16 + j] = pack_half2(g0, g1);
-            }
-          }
-        }
-        // Row `lane` of the 32 x 64 chunk, 16-byte pieces XOR-swizzled by row so
-        // the layout is the one a 128-byte-swizzle tensor map expects.
-        uint8_t* row = buf + lane * 128;
-#pragma unroll
-        for (int q = 0; q < 8; q++) {
-          uint4 val = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-          *reinterpret_cast<uint4*>(row + ((q ^ (lane & 7)) << 4)) = val;
-        }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          tma_store_2d(&tmD, buf, n_off + c * kStoreCols, m_off + quarter * 32);
-          tma_store_commit();
-        }
-      }
+      epilogue_store_rows<BN, DUAL>(p, &tmD, buf, t_row, n_off, m_off + quarter * 32, half, lane);
       // Accumulator buffer is free for the MMA warp again.
       tc_fence_before();
       __syncwarp();
@@ -596,7 +635,7 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       if (p.trace && ew == 0 && lane == 0 && ticket < p.trace_capacity) {
         uint32_t smid;
         asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-        unsigned long long* rec = p.trace + 4ull * ticket;
+        unsigned long long* rec = p.trace + 8ull * ticket;
         rec[0] = t_draw; rec[1] = t_mma_done; rec[2] = cusync::globalTimerNs();
         rec[3] = (static_cast<unsigned long long>(smid) << 32) | blockIdx.x;
       }
@@ -610,6 +649,474 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   if (warp == 2) {
     tc_fence_after();
     tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+
+// ---------------------------------------------------------------------------
+// CTA-pair variant: tcgen05.mma.cta_group::2
+// ---------------------------------------------------------------------------
+// Two CTAs of a cluster (the two SMs of a TPC) compute one 256 x 256 output tile.  CTA r owns rows
+// [r*128, r*128+128) of it: it loads its own A rows and HALF of the B tile (128 of the 256 columns),
+// and holds its 128 x 256 accumulator in its own tensor memory.  The leader (rank 0) issues one
+// M=256 MMA per K step that reads A and the B halves from both CTAs' shared memory.  Per CTA and
+// K-block that is 32 KB from L2 instead of 48 KB, and the ring holds six K-blocks instead of four.
+// No multicast loads: the only cluster-wide traffic is mbarrier signalling (TMA completion on the
+// leader's barrier, tcgen05.commit to both CTAs, remote arrives) and the scheduler's tile broadcast.
+// Semaphores stay per 128-row tile: each CTA waits for, and posts, its own rows.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait on a LOCAL barrier that a peer CTA may have signalled.
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, const WaitCtx& ctx) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const uint64_t t0 = cusync::globalTimerNs();
+  uint32_t polls = 0;
+  while (true) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if ((++polls & 31u) == 0u) {
+      if (*ctx.abort) return false;
+      if (cusync::globalTimerNs() - t0 > ctx.timeout_ns) {
+        *ctx.abort = 1u;
+        cusync::recordTimeout(ctx.status, 2u, blockIdx.x, threadIdx.x, parity, smem_u32(bar), 0u, 0u);
+        return false;
+      }
+    }
+  }
+}
+// TMA load whose completion may be signalled on the peer CTA's barrier (`bar_cluster_addr` is a
+// shared::cluster address); the data lands in this CTA's shared memory.
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int c0,
+                                                 int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int c0,
+                                                 int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on the barrier at this shared-memory offset in BOTH CTAs of the pair when the MMAs retire.
+__device__ __forceinline__ void umma_commit_pair_both(uint64_t* bar) {
+  const uint16_t mask = 3;
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(smem_u32(bar)), "h"(mask)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair_local(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+
+constexpr int kPairBN = 256;                       // tile width of the pair kernel
+// K depth of one ring stage of the pair kernel: two 64-element swizzle chunks.  A barrier wait, a commit and
+// each MMA issue cost the issuing thread of the order of a hundred cycles whatever the MMA's size, so a stage
+// carries eight MMAs (and two TMA boxes) per wait/commit instead of four to stay under the tensor time.
+constexpr int kPairBlockK = 128;
+constexpr int kPairChunkBytes = kBlockM * 128;     // one 64-deep chunk of 128 rows
+struct PairCfg {
+  static constexpr int kABytes = kBlockM * kPairBlockK * 2;            // this CTA's 128 A rows
+  static constexpr int kBHalfBytes = (kPairBN / 2) * kPairBlockK * 2;  // this CTA's half of the B tile
+  static constexpr int kStageBytes = kABytes + kBHalfBytes;
+  static constexpr int kStagingBytes = kEpilogueWarps * 32 * 128;
+  static constexpr int kBarrierBytes = 1024;
+  static constexpr int kStages = ((int)kSmemLimit - 1024 - kStagingBytes - kBarrierBytes) / kStageBytes;
+  static constexpr int kAccCols = kPairBN;
+  static constexpr int kTmemCols = 2 * kAccCols;
+  static constexpr uint32_t kSmemBytes = 1024 + kStages * kStageBytes + kStagingBytes + kBarrierBytes;
+  static_assert(kStages >= 3 && kStages <= 8, "ring depth out of range");
+  static_assert(kSmemBytes <= kSmemLimit, "shared memory over budget");
+};
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                        const __grid_constant__ CUtensorMap tmD, const GemmParams p) {
+  using C = PairCfg;
+  constexpr int BN = kPairBN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* ring = smem;
+  uint8_t* staging = smem + C::kStages * C::kStageBytes;
+  Barriers* bars = reinterpret_cast<Barriers*>(staging + C::kStagingBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();          // 0 = leader: draws tickets, issues the MMAs
+  const bool leader = rank == 0;
+  const cusync_stage_view_t& st = p.stage;
+  WaitCtx ctx{&bars->abort, st.status, 2 * st.timeout_ns + 1000000000ull};
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < C::kStages; i++) { mbar_init(&bars->full[i], 1); mbar_init(&bars->empty[i], 1); }
+    for (int i = 0; i < 2; i++) {
+      mbar_init(&bars->tmem_full[i], 1);
+      mbar_init(&bars->tmem_empty[i], 2 * kEpilogueWarps);           // leader's: epilogue warps of both CTAs
+    }
+    for (int i = 0; i < kSchedSlots; i++) {
+      mbar_init(&bars->sched_full[i], 1);
+      mbar_init(&bars->sched_empty[i], 2 * (1 + kEpilogueWarps));    // leader's: MMA + peer loader + all epilogue warps
+    }
+    mbar_init(&bars->drain, 1);
+    mbar_init(&bars->post, kEpilogueWarps);
+    bars->abort = 0u;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+    if (p.is_producer) {
+      if (blockIdx.x == 0) cusync::storeRelease(st.started, st.iter);
+      cusync::addRelease(st.started + 1, 1u);
+    }
+  }
+  if (warp == 0 && lane == 0) { prefetch_tensormap(&tmA); prefetch_tensormap(&tmB); prefetch_tensormap(&tmD); }
+  if (warp == 2) {
+    tmem_alloc_pair(&bars->tmem_base, C::kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();            // the peer's barriers are initialised before anything signals them
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  // Cluster addresses of the leader's barriers that the peer signals.
+  const uint32_t leader_full0 = map_to_cta(smem_u32(&bars->full[0]), 0);
+  const uint32_t leader_tmem_empty0 = map_to_cta(smem_u32(&bars->tmem_empty[0]), 0);
+  const uint32_t leader_sched_empty0 = map_to_cta(smem_u32(&bars->sched_empty[0]), 0);
+
+  if (warp == 0) {
+    // =====================================================================
+    // Scheduler (leader) + TMA loader (both CTAs)
+    // =====================================================================
+    if (lane == 0) {
+      uint32_t fills = 0, sched_it = 0;
+      bool ok = true;
+      const uint32_t total_draws = static_cast<uint32_t>(p.num_pairs) + gridDim.x / 2;
+      const uint32_t wait_target = p.is_consumer ? st.iter * cusync::eval::waitValue(st.in_policy) : 0u;
+      uint32_t sync_stride = 0;
+      if (p.is_consumer) {
+        const int kind = st.in_policy.kind;
+        if (kind == CUSYNC_POLICY_TILESYNC || kind == CUSYNC_POLICY_STRIDEDTILESYNC) sync_stride = st.in_policy.tile_n;
+        else if (kind == CUSYNC_POLICY_CONV2DTILESYNC) sync_stride = st.in_policy.tile_n * st.in_policy.p0;
+      }
+      const uint32_t peer_sched_tile0 = map_to_cta(smem_u32(&bars->sched_tile[0][0]), 1);
+      const uint32_t peer_sched_time0 = map_to_cta(smem_u32(&bars->sched_time[0]), 1);
+      const uint32_t peer_sched_full0 = map_to_cta(smem_u32(&bars->sched_full[0]), 1);
+      while (ok) {
+        const uint32_t slot = sched_it % kSchedSlots, sph = (sched_it / kSchedSlots) & 1u;
+        int32_t tn, tpm, valid;
+        if (leader) {
+          if (!mbar_wait_cluster(&bars->sched_empty[slot], sph ^ 1u, ctx)) { ok = false; break; }
+          const uint32_t ticket = atomicAdd(st.tile_counter, 1u);
+          if (ticket == total_draws - 1u) atomicExch(st.tile_counter, 0u);   // last draw of the launch
+          valid = ticket < static_cast<uint32_t>(p.num_pairs) ? 1 : 0;
+          cusync_dim3_t t = {0, 0, 0};
+          if (valid) t = p.pair_order[ticket];
+          tn = static_cast<int32_t>(t.x); tpm = static_cast<int32_t>(t.y);
+          const unsigned long long now = p.trace ? cusync::globalTimerNs() : 0ull;
+          bars->sched_tile[slot][0] = tn; bars->sched_tile[slot][1] = tpm;
+          bars->sched_tile[slot][2] = valid; bars->sched_tile[slot][3] = static_cast<int32_t>(ticket);
+          bars->sched_time[slot] = now;
+          // the same record into the peer's ring, then signal both
+          const uint32_t pt = peer_sched_tile0 + slot * 16;
+          st_cluster_u32(pt, static_cast<uint32_t>(tn)); st_cluster_u32(pt + 4, static_cast<uint32_t>(tpm));
+          st_cluster_u32(pt + 8, static_cast<uint32_t>(valid)); st_cluster_u32(pt + 12, ticket);
+          st_cluster_u32(peer_sched_time0 + slot * 8, static_cast<uint32_t>(now));
+          st_cluster_u32(peer_sched_time0 + slot * 8 + 4, static_cast<uint32_t>(now >> 32));
+          mbar_arrive(&bars->sched_full[slot]);
+          mbar_arrive_cluster(peer_sched_full0 + slot * 8);
+        } else {
+          if (!mbar_wait_cluster(&bars->sched_full[slot], sph, ctx)) { ok = false; break; }
+          tn = bars->sched_tile[slot][0]; tpm = bars->sched_tile[slot][1]; valid = bars->sched_tile[slot][2];
+          mbar_arrive_cluster(leader_sched_empty0 + slot * 8);
+        }
+        sched_it++;
+        if (!valid) break;
+
+        const int n_off = tn * BN;
+        const int m_off = tpm * (2 * kBlockM) + static_cast<int>(rank) * kBlockM;   // this CTA's 128 rows
+        const int nb_off = n_off + static_cast<int>(rank) * (BN / 2);               // this CTA's half of B
+        uint32_t ready_end = 0;
+        long long wait_empty = 0;
+        for (int kb = 0; kb < p.num_k_blocks; kb++) {
+          const uint32_t s = fills % C::kStages, ph = (fills / C::kStages) & 1u;
+          const long long c0 = p.trace ? clock64() : 0;
+          if (!mbar_wait_cluster(&bars->empty[s], ph ^ 1u, ctx)) { ok = false; break; }
+          if (p.trace) wait_empty += clock64() - c0;
+          uint8_t* sa = ring + s * C::kStageBytes;
+          uint8_t* sb = sa + C::kABytes;
+          const uint32_t full_addr = leader_full0 + s * 8;
+          // The leader's barrier collects the bytes of both CTAs.
+          if (leader) mbar_expect_tx(&bars->full[s], 2 * C::kStageBytes);
+          const int k_base = kb * kPairBlockK;
+          // B half: one 3-D box.  [k,n] weights: {64 columns, 128 k rows, 2 column chunks};
+          // [n,k] weights: {64 k, 128 n rows, 2 k chunks}.
+          if (p.b_kmajor) tma_load_3d_pair(sb, &tmB, full_addr, 0, nb_off, k_base / 64);
+          else            tma_load_3d_pair(sb, &tmB, full_addr, 0, k_base, nb_off / 64);
+          // The stage spans two 64-deep K chunks; each may open a new producer tile.
+#pragma unroll 1
+          for (int sub = 0; sub < kPairBlockK / kBlockK && ok; sub++) {
+          const int k_off = k_base + sub * kBlockK;
+          if (p.is_consumer && m_off < p.m && k_off < p.k) {
+            const uint32_t tz = (kb == 0 && sub == 0) ? 1u : 0u;
+            if (static_cast<uint32_t>(k_off) >= ready_end &&
+                cusync::eval::isSync(st.in_policy, static_cast<uint32_t>(k_off), tz)) {
+              const uint32_t idx = cusync::eval::tileIndex(st.in_policy, static_cast<uint32_t>(m_off),
+                                                           static_cast<uint32_t>(k_off), st.prod_grid.x,
+                                                           st.prod_grid.y);
+              uint32_t seen = 0;
+              if (!cusync::spinUntilAtLeast(st.sems_wait + idx, wait_target, st.timeout_ns, &seen)) {
+                bars->abort = 1u;
+                cusync::recordTimeout(st.status, 1u, static_cast<uint32_t>(m_off), static_cast<uint32_t>(k_off), tz,
+                                      idx, seen, wait_target);
+                ok = false;
+                break;
+              }
+              if (sync_stride) {
+                uint32_t vals[kLookahead];
+#pragma unroll
+                for (int j = 0; j < kLookahead; j++) {
+                  const uint32_t kk = static_cast<uint32_t>(k_off) + (j + 1) * sync_stride;
+                  vals[j] = kk < static_cast<uint32_t>(p.k)
+                                ? cusync::loadRelaxed(st.sems_wait + cusync::eval::tileIndex(st.in_policy,
+                                      static_cast<uint32_t>(m_off), kk, st.prod_grid.x, st.prod_grid.y))
+                                : 0u;
+                }
+                uint32_t ahead = 0;
+#pragma unroll
+                for (int j = 0; j < kLookahead; j++) {
+                  if (ahead == static_cast<uint32_t>(j) && vals[j] >= wait_target) ahead++;
+                }
+                ready_end = static_cast<uint32_t>(k_off) + (ahead + 1) * sync_stride;
+                if (ahead) __threadfence();
+              }
+              fence_proxy_async();
+            }
+          }
+          }
+          // A: {64 k, 128 rows, 2 k chunks}.  Issued on the abort path too, so that the armed barrier
+          // completes and the drain below terminates.
+          tma_load_3d_pair(sa, &tmA, full_addr, 0, m_off, k_base / 64);
+          fills++;
+          if (!ok) break;
+        }
+        if (p.trace) {
+          const uint32_t tk = static_cast<uint32_t>(bars->sched_tile[slot][3]);
+          if (2 * tk + rank < p.trace_capacity)
+            p.trace[8ull * (2 * tk + rank) + 5] = static_cast<unsigned long long>(wait_empty);
+        }
+      }
+      if (!ok) {
+        bars->abort = 1u;
+        if (leader) {
+          // wait (bounded) for the copies of both CTAs that were armed on this CTA's barriers
+          const uint32_t live = fills < static_cast<uint32_t>(C::kStages) ? fills : static_cast<uint32_t>(C::kStages);
+          for (uint32_t j = 0; j < live; j++) {
+            const uint32_t f = fills - 1u - j;
+            const uint32_t s = f % C::kStages, ph = (f / C::kStages) & 1u;
+            const uint64_t t0 = cusync::globalTimerNs();
+            while (!mbar_try_wait_cluster(&bars->full[s], ph)) {
+              if (cusync::globalTimerNs() - t0 > 1000000000ull) break;
+            }
+          }
+        } else {
+          // the peer's copies complete on the leader's barriers, which it cannot wait on: give
+          // them time to land before this CTA's shared memory goes away
+          const uint64_t t0 = cusync::globalTimerNs();
+          while (cusync::globalTimerNs() - t0 < 100000ull) __nanosleep(1000);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // =====================================================================
+    // MMA issuer (leader only)
+    // =====================================================================
+    if (lane == 0 && leader) {
+      // instruction descriptor: M = 256 across the pair, N = 256
+      const uint32_t idesc = (1u << 4) | ((p.b_kmajor ? 0u : 1u) << 16) | (static_cast<uint32_t>(BN >> 3) << 17) |
+                             (static_cast<uint32_t>((2 * kBlockM) >> 4) << 24);
+      const uint32_t b_lbo = p.b_lbo, b_sbo = p.b_sbo, b_kstep = p.b_kstep;
+      uint32_t drains = 0, sched_it = 0, acc_it = 0;
+      bool ok = true, issued = false;
+      while (ok) {
+        const uint32_t slot = sched_it % kSchedSlots, sph = (sched_it / kSchedSlots) & 1u;
+        if (!mbar_wait(&bars->sched_full[slot], sph, ctx)) { ok = false; break; }
+        const int valid = bars->sched_tile[slot][2];
+        const uint32_t ticket = static_cast<uint32_t>(bars->sched_tile[slot][3]);
+        mbar_arrive(&bars->sched_empty[slot]);
+        sched_it++;
+        if (!valid) break;
+        const uint32_t acc = acc_it & 1u, aph = (acc_it >> 1) & 1u;
+        const long long t_tile0 = p.trace ? clock64() : 0;
+        if (!mbar_wait_cluster(&bars->tmem_empty[acc], aph ^ 1u, ctx)) { ok = false; break; }
+        tc_fence_after();
+        const long long t_acc = p.trace ? clock64() : 0;
+        long long wait_full = 0;
+        const uint32_t d_tmem = tmem_base + acc * C::kAccCols;
+        for (int kb = 0; kb < p.num_k_blocks; kb++) {
+          const uint32_t s = drains % C::kStages, ph = (drains / C::kStages) & 1u;
+          const long long c0 = p.trace ? clock64() : 0;
+          if (!mbar_wait_cluster(&bars->full[s], ph, ctx)) { ok = false; break; }
+          if (p.trace) wait_full += clock64() - c0;
+          tc_fence_after();
+          const uint32_t sa = smem_u32(ring + s * C::kStageBytes);
+          const uint32_t sb = sa + C::kABytes;
+#pragma unroll
+          for (int kk = 0; kk < kPairBlockK / kUmmaK; kk++) {
+            // K-major operands: 64-deep chunks of 128 rows, 32 bytes per K step inside a chunk.
+            // [k,n] B: 2048 bytes (16 rows) per K step, column chunks one leading offset apart.
+            const uint32_t a_off = (kk >> 2) * kPairChunkBytes + (kk & 3) * 32;
+            const uint32_t b_off = p.b_kmajor ? a_off : kk * b_kstep;
+            const uint64_t adesc = make_smem_desc(sa + a_off, 16u, 1024u);
+            const uint64_t bdesc = make_smem_desc(sb + b_off, b_lbo, b_sbo);
+            umma_f16_pair(d_tmem, adesc, bdesc, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit_pair_both(&bars->empty[s]);     // frees the ring slot in both CTAs
+          issued = true;
+          drains++;
+        }
+        if (!ok) break;
+        umma_commit_pair_both(&bars->tmem_full[acc]);
+        if (p.trace && 2 * ticket < p.trace_capacity) {
+          p.trace[8ull * (2 * ticket) + 4] = static_cast<unsigned long long>(wait_full);
+          p.trace[8ull * (2 * ticket) + 6] = static_cast<unsigned long long>(clock64() - t_tile0);
+          p.trace[8ull * (2 * ticket) + 7] = static_cast<unsigned long long>(t_acc - t_tile0);
+        }
+        acc_it++;
+      }
+      if (!ok && issued) {
+        umma_commit_pair_local(&bars->drain);
+        const uint64_t t0 = cusync::globalTimerNs();
+        while (!mbar_try_wait(&bars->drain, 0u)) {
+          if (cusync::globalTimerNs() - t0 > 1000000000ull) break;
+        }
+      }
+    }
+  } else if (warp >= kEpilogueWarp0) {
+    // =====================================================================
+    // Epilogue (both CTAs, each for its own 128 rows)
+    // =====================================================================
+    const int ew = warp - kEpilogueWarp0;
+    const int quarter = ew & 3;
+    const int half = ew >> 2;
+    uint8_t* buf = staging + ew * (32 * 128);
+    uint32_t sched_it = 0, acc_it = 0, post_it = 0;
+    bool ok = true;
+    while (ok) {
+      const uint32_t slot = sched_it % kSchedSlots, sph = (sched_it / kSchedSlots) & 1u;
+      if (!mbar_wait_cluster(&bars->sched_full[slot], sph, ctx)) { ok = false; break; }
+      const int tile_n = bars->sched_tile[slot][0];
+      const int pair_m = bars->sched_tile[slot][1];
+      const int valid = bars->sched_tile[slot][2];
+      const uint32_t ticket = static_cast<uint32_t>(bars->sched_tile[slot][3]);
+      const unsigned long long t_draw = bars->sched_time[slot];
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(leader_sched_empty0 + slot * 8);
+      sched_it++;
+      if (!valid) break;
+      const uint32_t acc = acc_it & 1u, aph = (acc_it >> 1) & 1u;
+      if (!mbar_wait_cluster(&bars->tmem_full[acc], aph, ctx)) { ok = false; break; }
+      tc_fence_after();
+      const unsigned long long t_mma_done = p.trace ? cusync::globalTimerNs() : 0ull;
+      const int n_off = tile_n * BN;
+      const int m_off = pair_m * (2 * kBlockM) + static_cast<int>(rank) * kBlockM;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * C::kAccCols;
+
+      epilogue_store_rows<BN, false>(p, &tmD, buf, t_row, n_off, m_off + quarter * 32, half, lane);
+
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(leader_tmem_empty0 + acc * 8);
+      acc_it++;
+
+      if (p.is_producer && m_off < p.m) {     // a pair's second half may lie past the last row tile
+        if (lane == 0) {
+          tma_store_wait_all();
+          __threadfence();
+          mbar_arrive(&bars->post);
+          if (ew == 0) {
+            if (!mbar_wait(&bars->post, post_it & 1u, ctx)) ok = false;
+            else {
+              const uint32_t idx = cusync::eval::tileIndex(st.out_policy, static_cast<uint32_t>(m_off),
+                                                           static_cast<uint32_t>(n_off), st.grid.x, st.grid.y);
+              const uint32_t pv = cusync::eval::postValue(st.out_policy);
+              __threadfence();
+              if (st.opts & CUSYNC_OPT_NO_ATOMIC_ADD) cusync::storeRelease(st.sems_post + idx, pv * st.iter);
+              else                                    cusync::addRelease(st.sems_post + idx, pv);
+            }
+          }
+        }
+        post_it++;
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      }
+      if (p.trace && ew == 0 && lane == 0 && 2 * ticket + rank < p.trace_capacity) {
+        uint32_t smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        unsigned long long* rec = p.trace + 8ull * (2 * ticket + rank);
+        rec[0] = t_draw; rec[1] = t_mma_done; rec[2] = cusync::globalTimerNs();
+        rec[3] = (static_cast<unsigned long long>(smid) << 32) | blockIdx.x;
+      }
+    }
+    if (lane == 0) tma_store_wait_all();
+  }
+
+  // Teardown: nobody may leave while the peer can still signal its barriers or read its operands.
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, C::kTmemCols);
   }
 }
 
@@ -650,6 +1157,24 @@ bool make_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, 
   return r == CUDA_SUCCESS;
 }
 
+// 3-D view of a row-major [k, n] fp16 matrix whose n is a multiple of 64: {64 columns, k rows, n/64 column
+// chunks}; a box of {64, box_rows, box_chunks} lands in shared memory chunk after chunk, each chunk being
+// box_rows rows of 128 swizzled bytes -- the layout the MN-major UMMA descriptor walks with its leading offset.
+bool make_map_chunked(CUtensorMap* out, const void* base, uint64_t k, uint64_t n, uint64_t ld, uint32_t box_rows,
+                      uint32_t box_chunks) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  if (n % 64 != 0) return false;
+  cuuint64_t dims[3] = {64, k, n / 64};
+  cuuint64_t strides[2] = {ld * 2, 128};
+  cuuint32_t box[3] = {64, box_rows, box_chunks};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const GemmParams);
 
 struct KernelEntry { KernelFn fn; uint32_t smem; };
@@ -684,17 +1209,89 @@ struct cusync_gemm_plan {
   uint32_t num_ctas;
   cusync_stage_t* own_stage;   // created when the caller passes no stage
   cusync_stage_t* stage;
+  bool pair;                   // CTA-pair kernel (tcgen05 cta_group::2, 256 x 256 tiles per pair)
+  cusync_dim3_t* pair_order;   // device: schedule over pair tiles
 };
 
 namespace {
 
+// Whether cusync_gemm_plan_create picks the CTA-pair kernel when the caller leaves the choice open.
+bool pair_by_default(int m, int tile_n, bool dual) {
+  return !dual && tile_n == kPairBN && m > kBlockM;
+}
+
+// Pair mode: schedule over 256-row pair tiles (the stage's order applied to the pair grid), and the
+// number of clusters that can be resident at once.
+int setup_pair(cusync_gemm_plan* pl, const cusync_stage_view_t& view, uint32_t cta_cap) {
+  GemmParams& p = pl->params;
+  const uint32_t pair_rows = static_cast<uint32_t>((p.tiles_m + 1) / 2);
+  const uint32_t tiles_n = static_cast<uint32_t>(p.tiles_n);
+  const uint32_t num_pairs = pair_rows * tiles_n;
+  std::vector<cusync_dim3_t> order(num_pairs, cusync_dim3_t{num_pairs, 0, 0});
+  const int kind = view.order & 0xff;
+  uint32_t group = static_cast<uint32_t>(view.order) >> 8;
+  group = group > 1 ? group / 2 : 1;   // a group of R 128-row tiles is R/2 pair rows
+  for (uint32_t y = 0; y < pair_rows; y++)
+    for (uint32_t x = 0; x < tiles_n; x++) {
+      const uint32_t id = kind == CUSYNC_ORDER_GROUPED_ROWS
+                              ? cusync::eval::groupedBlockIndex(group, tiles_n, pair_rows, x, y, 0)
+                              : cusync::eval::blockIndex(tiles_n, pair_rows, x, y, 0);
+      if (id >= num_pairs || order[id].x != num_pairs) return CUSYNC_ERROR_INVALID_LINEAR_BLOCK_INDEX;
+      order[id] = cusync_dim3_t{x, y, 0};
+    }
+  if (cudaMalloc(&pl->pair_order, sizeof(cusync_dim3_t) * num_pairs) != cudaSuccess ||
+      cudaMemcpy(pl->pair_order, order.data(), sizeof(cusync_dim3_t) * num_pairs, cudaMemcpyHostToDevice) !=
+          cudaSuccess) {
+    (void)cudaGetLastError();
+    return CUSYNC_ERROR_CUDA;
+  }
+  p.pair_order = pl->pair_order;
+  p.num_pairs = static_cast<int32_t>(num_pairs);
+
+  // How many 2-CTA clusters fit on the device at once (one CTA per SM).
+  int max_clusters = 0;
+  cudaLaunchConfig_t cfg;
+  std::memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(2 * num_pairs, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = PairCfg::kSmemBytes;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr; cfg.numAttrs = 1;
+  if (cudaOccupancyMaxActiveClusters(&max_clusters, cusync_gemm_pair_kernel, &cfg) != cudaSuccess || max_clusters <= 0) {
+    (void)cudaGetLastError();
+    max_clusters = cusync_b200_sm_count() / 2;
+    if (max_clusters <= 0) max_clusters = 74;
+  }
+  uint32_t clusters = num_pairs < static_cast<uint32_t>(max_clusters) ? num_pairs : static_cast<uint32_t>(max_clusters);
+  if (cta_cap / 2 >= 1 && clusters > cta_cap / 2) clusters = cta_cap / 2;
+  pl->num_ctas = 2 * clusters;
+  return CUSYNC_SUCCESS;
+}
+
 int build_maps(cusync_gemm_plan* pl) {
   const cusync_gemm_desc_t& d = pl->desc;
   const bool dual = d.epilogue == CUSYNC_EPILOGUE_SILU_MUL_DUAL;
+  if (pl->pair) {
+    // Pair kernel: every operand box is 3-D, {64 contiguous elements, 128 rows, 2 chunks of 64}.
+    // A [m,k] and [n,k] weights are chunked along k; [k,n] weights along n.
+    bool okp = make_map_chunked(&pl->tmA, d.a, d.m, d.k, d.lda, kBlockM, kPairBlockK / 64);
+    if (d.b_layout == CUSYNC_B_ROW_MAJOR_NK) okp = okp && make_map_chunked(&pl->tmB, d.b, d.n, d.k, d.ldb, kPairBN / 2, kPairBlockK / 64);
+    else                                     okp = okp && make_map_chunked(&pl->tmB, d.b, d.k, d.n, d.ldb, kPairBlockK, kPairBN / 2 / 64);
+    pl->tmB2 = pl->tmB;
+    okp = okp && make_map(&pl->tmD, d.d, d.m, d.n, d.ldd, kStoreCols, 32);
+    return okp ? CUSYNC_SUCCESS : CUSYNC_ERROR_CUDA;
+  }
   bool ok = make_map(&pl->tmA, d.a, d.m, d.k, d.lda, kBlockK, kBlockM);
   if (d.b_layout == CUSYNC_B_ROW_MAJOR_NK) {
-    ok = ok && make_map(&pl->tmB, d.b, d.n, d.k, d.ldb, kBlockK, pl->tile_n);
-    if (dual) ok = ok && make_map(&pl->tmB2, d.b2, d.n, d.k, d.ldb, kBlockK, pl->tile_n);
+    const uint32_t b_rows = pl->pair ? pl->tile_n / 2 : pl->tile_n;   // a pair CTA loads half of the B tile
+    ok = ok && make_map(&pl->tmB, d.b, d.n, d.k, d.ldb, kBlockK, b_rows);
+    if (dual) ok = ok && make_map(&pl->tmB2, d.b2, d.n, d.k, d.ldb, kBlockK, b_rows);
+  } else if (pl->params.b_chunked3d) {
+    const uint32_t chunks = static_cast<uint32_t>(pl->pair ? pl->tile_n / 2 : pl->tile_n) / 64;
+    ok = ok && make_map_chunked(&pl->tmB, d.b, d.k, d.n, d.ldb, kBlockK, chunks);
+    if (dual) ok = ok && make_map_chunked(&pl->tmB2, d.b2, d.k, d.n, d.ldb, kBlockK, chunks);
   } else {
     ok = ok && make_map(&pl->tmB, d.b, d.k, d.n, d.ldb, 64, kBlockK);
     if (dual) ok = ok && make_map(&pl->tmB2, d.b2, d.k, d.n, d.ldb, 64, kBlockK);
@@ -874,15 +1471,26 @@ int cusync_gemm_plan_create(cusync_gemm_plan_t** out, const cusync_gemm_desc_t* 
   pl->desc = d;
   pl->tile_n = d.tile_n ? d.tile_n : cusync_gemm_default_tile_n(d.m, d.n, d.k, d.epilogue);
   if (!select_kernel(pl->tile_n, dual, &pl->kernel)) { delete pl; return CUSYNC_ERROR_UNSUPPORTED; }
+  if (d.cta_pair < 0 || d.cta_pair > 2) { delete pl; return CUSYNC_ERROR_INVALID_ARGUMENT; }
+  // The pair kernel fetches operands in 64-element chunks of whole rows: K, and N of [k,n] weights, must be
+  // multiples of 64 (a ragged last chunk would read past the end of a row).
+  const bool pair_ok = !dual && pl->tile_n == kPairBN && d.k % 64 == 0 &&
+                       (d.b_layout == CUSYNC_B_ROW_MAJOR_NK || d.n % 64 == 0);
+  if (d.cta_pair == 2 && !pair_ok) { delete pl; return CUSYNC_ERROR_UNSUPPORTED; }
+  pl->pair = d.cta_pair == 2 || (d.cta_pair == 0 && pair_ok && pair_by_default(d.m, pl->tile_n, dual));
+  if (pl->pair) pl->kernel = KernelEntry{nullptr, PairCfg::kSmemBytes};
 
   GemmParams& p = pl->params;
   p.m = d.m; p.n = d.n; p.k = d.k;
   p.tiles_n = (d.n + pl->tile_n - 1) / pl->tile_n;
   p.tiles_m = (d.m + kBlockM - 1) / kBlockM;
   p.num_tiles = p.tiles_n * p.tiles_m;
-  p.num_k_blocks = (d.k + kBlockK - 1) / kBlockK;
+  p.num_k_blocks = pl->pair ? (d.k + kPairBlockK - 1) / kPairBlockK : (d.k + kBlockK - 1) / kBlockK;
   p.epilogue = d.epilogue;
   p.b_kmajor = d.b_layout == CUSYNC_B_ROW_MAJOR_NK ? 1 : 0;
+  // [k,n] weights whose n is a whole number of 64-column chunks are fetched with one 3-D box per K-block
+  // (a ragged last chunk would read past the end of a row, so such matrices keep one 2-D box per chunk).
+  p.b_chunked3d = (!p.b_kmajor && d.n % 64 == 0 && pl->tile_n > 64) ? 1 : 0;
   if (p.b_kmajor) {
     // K-major, 128-byte swizzle: rows are 128 B apart, 8-row groups 1024 B apart; one UMMA K step
     // (16 fp16) is 32 B along the row.  The leading offset is unused for swizzled K-major operands.
@@ -891,7 +1499,7 @@ int cusync_gemm_plan_create(cusync_gemm_plan_t** out, const cusync_gemm_desc_t* 
     // MN-major ([k,n] row-major), 128-byte swizzle: each TMA box holds 64 columns x kBlockK rows;
     // 64-column groups are one box (kBlockK * 128 B) apart, 8-row K groups 1024 B apart, and one
     // UMMA K step is 16 rows = 2048 B.
-    p.b_lbo = kBlockK * 128; p.b_sbo = 1024; p.b_kstep = kUmmaK * 128;
+    p.b_lbo = (pl->pair ? kPairBlockK : kBlockK) * 128; p.b_sbo = 1024; p.b_kstep = kUmmaK * 128;
   }
 
   pl->stage = d.stage;
@@ -924,15 +1532,19 @@ int cusync_gemm_plan_create(cusync_gemm_plan_t** out, const cusync_gemm_desc_t* 
   uint32_t cap = d.max_ctas > 0 ? static_cast<uint32_t>(d.max_ctas) : static_cast<uint32_t>(sms);
   pl->num_ctas = static_cast<uint32_t>(p.num_tiles) < cap ? static_cast<uint32_t>(p.num_tiles) : cap;
 
-  int rc = build_maps(pl);
-  if (rc == CUSYNC_SUCCESS &&
-      cudaFuncSetAttribute(reinterpret_cast<const void*>(pl->kernel.fn), cudaFuncAttributeMaxDynamicSharedMemorySize,
+  int rc = CUSYNC_SUCCESS;
+  const void* kernel_fn = pl->pair ? reinterpret_cast<const void*>(cusync_gemm_pair_kernel)
+                                   : reinterpret_cast<const void*>(pl->kernel.fn);
+  if (cudaFuncSetAttribute(kernel_fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            static_cast<int>(pl->kernel.smem)) != cudaSuccess) {
     (void)cudaGetLastError();
     rc = CUSYNC_ERROR_CUDA;
   }
+  if (rc == CUSYNC_SUCCESS && pl->pair) rc = setup_pair(pl, view, cap);
+  if (rc == CUSYNC_SUCCESS) rc = build_maps(pl);
   if (rc != CUSYNC_SUCCESS) {
     if (pl->own_stage) cusync_stage_destroy(pl->own_stage);
+    cudaFree(pl->pair_order);
     delete pl;
     return rc;
   }
@@ -942,6 +1554,7 @@ int cusync_gemm_plan_create(cusync_gemm_plan_t** out, const cusync_gemm_desc_t* 
 
 int cusync_gemm_plan_destroy(cusync_gemm_plan_t* pl) {
   if (!pl) return CUSYNC_ERROR_NOT_INITIALIZED;
+  cudaFree(pl->pair_order);
   if (pl->own_stage) cusync_stage_destroy(pl->own_stage);
   delete pl;
   return CUSYNC_SUCCESS;
@@ -973,8 +1586,12 @@ int cusync_gemm_run(cusync_gemm_plan_t* pl, cusync_stream_t stream) {
   p.is_producer = p.stage.out_policy.kind != CUSYNC_POLICY_NOSYNC;
   p.is_consumer = p.stage.in_policy.kind != CUSYNC_POLICY_NOSYNC;
   if (p.is_producer) cusync_stage_note_launch(pl->stage, pl->num_ctas);
-  pl->kernel.fn<<<pl->num_ctas, kThreads, pl->kernel.smem, reinterpret_cast<cudaStream_t>(stream)>>>(
-      pl->tmA, pl->tmB, pl->tmB2, pl->tmD, p);
+  if (pl->pair)
+    cusync_gemm_pair_kernel<<<pl->num_ctas, kThreads, pl->kernel.smem, reinterpret_cast<cudaStream_t>(stream)>>>(
+        pl->tmA, pl->tmB, pl->tmD, p);
+  else
+    pl->kernel.fn<<<pl->num_ctas, kThreads, pl->kernel.smem, reinterpret_cast<cudaStream_t>(stream)>>>(
+        pl->tmA, pl->tmB, pl->tmB2, pl->tmD, p);
   return cudaGetLastError() == cudaSuccess ? CUSYNC_SUCCESS : CUSYNC_ERROR_CUDA;
 }
 

@@ -31,7 +31,7 @@ void fill_gemm1(const cusync_mlp_desc_t& d, int tile_n, cusync_stage_t* stage, c
   g->d = d.h; g->ldd = d.ffn;
   g->b_layout = CUSYNC_B_ROW_MAJOR_KN;
   g->epilogue = d.model == CUSYNC_MLP_LLAMA ? CUSYNC_EPILOGUE_SILU_MUL_DUAL : CUSYNC_EPILOGUE_GELU_ERF;
-  g->tile_n = tile_n; g->max_ctas = d.max_ctas; g->stage = stage;
+  g->tile_n = tile_n; g->max_ctas = d.max_ctas; g->cta_pair = d.cta_pair; g->stage = stage;
 }
 
 void fill_gemm2(const cusync_mlp_desc_t& d, int tile_n, cusync_stage_t* stage, cusync_gemm_desc_t* g) {
@@ -42,7 +42,7 @@ void fill_gemm2(const cusync_mlp_desc_t& d, int tile_n, cusync_stage_t* stage, c
   g->d = d.y; g->ldd = d.hidden;
   g->b_layout = CUSYNC_B_ROW_MAJOR_KN;
   g->epilogue = CUSYNC_EPILOGUE_NONE;
-  g->tile_n = tile_n; g->max_ctas = d.max_ctas; g->stage = stage;
+  g->tile_n = tile_n; g->max_ctas = d.max_ctas; g->cta_pair = d.cta_pair; g->stage = stage;
 }
 
 void destroy_all(cusync_mlp* m) {

@@ -209,6 +209,9 @@ typedef struct cusync_gemm_desc {
   int32_t epilogue;
   int32_t tile_n;                  /* 0 = choose; else 32, 64, 128 or 256.  Tile M is 128. */
   int32_t max_ctas;                /* 0 = one per SM */
+  int32_t cta_pair;                /* 0 = choose; 1 = one CTA per 128 x tile_n tile; 2 = CTA pairs (tcgen05
+                                      cta_group::2): two CTAs share a 256 x 256 tile, each loading half of B.
+                                      Needs tile_n 256 and a single B operand.  Semaphores stay per 128-row tile. */
   cusync_stage_t* stage;           /* NULL = no tile synchronisation (stream-ordered use) */
 } cusync_gemm_desc_t;
 
@@ -252,9 +255,12 @@ CUSYNC_API int cusync_gemm_run(cusync_gemm_plan_t* plan, cusync_stream_t stream)
 CUSYNC_API int cusync_gemm_run_noalloc(const cusync_gemm_desc_t* desc, cusync_stream_t stream);
 
 /* Optional per-tile timeline, the only profiling hook beyond CUDA events: with a device buffer of
- * 4 * capacity_tiles 64-bit words set, every tile writes, at index 4 * ticket,
+ * 8 * capacity_tiles 64-bit words set, every tile writes, at index 8 * ticket (CTA-pair kernel:
+ * 8 * (2 * ticket + rank)),
  * {globaltimer at the ticket draw, at the end of its MMAs, after its stores and post,
- *  (SM id << 32) | block index}.  NULL switches it off (the default).  No counterpart in the reference. */
+ *  (SM id << 32) | block index, SM cycles the MMA thread waited for operands, SM cycles the loader
+ *  waited for a free ring slot, SM cycles of the tile in the MMA thread, of which waiting for a free
+ *  accumulator}.  NULL switches it off (the default).  No counterpart in the reference. */
 CUSYNC_API int cusync_gemm_plan_set_trace(cusync_gemm_plan_t* plan, void* device_buffer, uint32_t capacity_tiles);
 /* Blocks the launch uses (persistent grid). */
 CUSYNC_API uint32_t cusync_gemm_plan_num_ctas(const cusync_gemm_plan_t* plan);
@@ -276,6 +282,7 @@ typedef struct cusync_mlp_desc {
   int32_t opts;                  /* CUSYNC_OPT_* applied to both stages */
   int32_t tile_n1, tile_n2;      /* 0 = choose */
   int32_t max_ctas;              /* 0 = one per SM */
+  int32_t cta_pair;              /* as cusync_gemm_desc_t.cta_pair, for both GEMMs */
   int32_t group_rows2;           /* > 0: the consumer takes its tiles in CUSYNC_ORDER_GROUPED(group_rows2) order */
   const void* x; const void* w1; const void* v; const void* w2;
   void* h; void* y;

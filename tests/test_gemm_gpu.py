@@ -25,7 +25,8 @@ def _rand(shape, seed, scale=1.0, dist="uniform"):
     return t.half().cuda()
 
 
-def _gemm(a, b, epi=L.EPILOGUE_NONE, tile_n=0, b_layout=L.B_ROW_MAJOR_KN, max_ctas=0, b2=None, stage=None):
+def _gemm(a, b, epi=L.EPILOGUE_NONE, tile_n=0, b_layout=L.B_ROW_MAJOR_KN, max_ctas=0, b2=None, stage=None,
+          cta_pair=0):
     M, K = a.shape
     N = b.shape[1]
     d = torch.full((M, N), float("nan"), device="cuda", dtype=torch.half)
@@ -36,7 +37,7 @@ def _gemm(a, b, epi=L.EPILOGUE_NONE, tile_n=0, b_layout=L.B_ROW_MAJOR_KN, max_ct
         bdev, b2dev = b, b2
     g = cs.Gemm()
     rc = g.initialize(cs.GemmArguments(stage, (M, N, K), a, bdev, d, epilogue=epi, ref_b2=b2dev, b_layout=b_layout,
-                                       tile_n=tile_n, max_ctas=max_ctas))
+                                       tile_n=tile_n, max_ctas=max_ctas, cta_pair=cta_pair))
     assert rc == L.SUCCESS, L.ERROR_NAMES[rc]
     assert g.run(stream=torch.cuda.current_stream()) == L.SUCCESS
     torch.cuda.synchronize()
@@ -85,6 +86,57 @@ def test_dual_gemm_silu_mul(M, N, K, tile_n, layout):
     assert o.max_rel_err(d.cpu().numpy(), ref) <= TOL
 
 
+@pytest.mark.parametrize("M,N,K", [
+    (256, 256, 64),       # one pair, one K block
+    (512, 1024, 1024),
+    (384, 512, 576),      # odd number of 128-row tiles: the last pair's second CTA has no rows; odd K chunks
+    (1000, 960, 320),     # ragged M, N not a multiple of the tile
+    (2048, 2048, 1024),
+])
+@pytest.mark.parametrize("layout", [L.B_ROW_MAJOR_KN, L.B_ROW_MAJOR_NK])
+def test_cta_pair_gemm_matches_oracle(M, N, K, layout):
+    a = _rand((M, K), 50)
+    b = _rand((K, N), 51)
+    d, n = _gemm(a, b, tile_n=256, b_layout=layout, cta_pair=2)
+    assert n % 2 == 0
+    ref = o.gemm_f16(a.cpu().numpy(), b.cpu().numpy())
+    assert o.max_rel_err(d.cpu().numpy(), ref) <= TOL
+
+
+def test_cta_pair_gemm_epilogue_and_few_clusters():
+    a = _rand((1024, 512), 52, dist="normal")
+    b = _rand((512, 2048), 53, scale=0.05, dist="normal")
+    ref = o.gemm_f16(a.cpu().numpy(), b.cpu().numpy(), o.EPI_GELU_ERF)
+    # 4 pair rows x 8 column tiles = 32 pair tiles on 3 clusters, run three times (ticket counter re-arms)
+    d = torch.empty((1024, 2048), device="cuda", dtype=torch.half)
+    g = cs.Gemm()
+    assert g.initialize(cs.GemmArguments(None, (1024, 2048, 512), a, b, d, epilogue=L.EPILOGUE_GELU_ERF, tile_n=256,
+                                         max_ctas=6, cta_pair=2)) == L.SUCCESS
+    assert g.num_ctas() == 6
+    for _ in range(3):
+        d.fill_(float("nan"))
+        assert g.run(stream=torch.cuda.current_stream()) == L.SUCCESS
+        torch.cuda.synchronize()
+        assert o.max_rel_err(d.cpu().numpy(), ref) <= TOL
+    g.destroy()
+
+
+def test_cta_pair_refuses_what_it_cannot_do():
+    # K (and N of [k,n] weights) must be whole 64-element chunks for the pair kernel; left to choose, the
+    # library falls back to one CTA per tile and still computes the right answer.
+    a = _rand((256, 520), 56); b = _rand((520, 1000), 57)
+    d = torch.empty((256, 1000), device="cuda", dtype=torch.half)
+    g = cs.Gemm()
+    assert g.initialize(cs.GemmArguments(None, (256, 1000, 520), a, b, d, tile_n=256, cta_pair=2)) == L.ERROR_UNSUPPORTED
+    d2, _ = _gemm(a, b, tile_n=256, cta_pair=0)
+    assert o.max_rel_err(d2.cpu().numpy(), o.gemm_f16(a.cpu().numpy(), b.cpu().numpy())) <= TOL
+    a = _rand((256, 256), 54); b = _rand((256, 256), 55)
+    d = torch.empty((256, 256), device="cuda", dtype=torch.half)
+    assert g.initialize(cs.GemmArguments(None, (256, 256, 256), a, b, d, tile_n=128, cta_pair=2)) == L.ERROR_UNSUPPORTED
+    assert g.initialize(cs.GemmArguments(None, (256, 256, 256), a, b, d, epilogue=L.EPILOGUE_SILU_MUL_DUAL, ref_b2=b,
+                                         tile_n=256, cta_pair=2)) == L.ERROR_UNSUPPORTED
+
+
 def test_persistent_scheduler_with_few_blocks_and_repeated_runs():
     # 64 tiles on 3 blocks: every block loops over many tickets; the ticket counter must re-arm itself.
     a = _rand((1024, 512), 8)
@@ -124,7 +176,7 @@ def test_linearity_at_full_gpt3_width():
 
 
 def _chain(policy_name, M, N1, K1, N2, tile_n1, tile_n2, iters, opts=0, epi1=L.EPILOGUE_NONE, max_ctas=0,
-           wait_kernel=True, seed=20):
+           wait_kernel=True, seed=20, cta_pair=0):
     a = _rand((M, K1), seed, dist="normal")
     w1 = _rand((K1, N1), seed + 1, scale=0.03, dist="normal")
     w2 = _rand((N1, N2), seed + 2, scale=0.03, dist="normal")
@@ -143,8 +195,9 @@ def _chain(policy_name, M, N1, K1, N2, tile_n1, tile_n2, iters, opts=0, epi1=L.E
     assert cs.CuSync.setProducerConsumerPair(prod, cons) == L.SUCCESS
     g1, g2 = cs.Gemm(), cs.Gemm()
     assert g1.initialize(cs.GemmArguments(prod, (M, N1, K1), a, w1, h, epilogue=epi1, tile_n=tile_n1,
-                                          max_ctas=max_ctas)) == L.SUCCESS
-    assert g2.initialize(cs.GemmArguments(cons, (M, N2, N1), h, w2, y, tile_n=tile_n2, max_ctas=max_ctas)) == L.SUCCESS
+                                          max_ctas=max_ctas, cta_pair=cta_pair)) == L.SUCCESS
+    assert g2.initialize(cs.GemmArguments(cons, (M, N2, N1), h, w2, y, tile_n=tile_n2, max_ctas=max_ctas,
+                                          cta_pair=cta_pair)) == L.SUCCESS
     ps, cst = torch.cuda.Stream(priority=-1), torch.cuda.Stream()
     oepi = {L.EPILOGUE_NONE: o.EPI_NONE, L.EPILOGUE_GELU_ERF: o.EPI_GELU_ERF}[epi1]
     href = o.gemm_f16(a.cpu().numpy(), w1.cpu().numpy(), oepi)
@@ -222,6 +275,16 @@ def test_chain_gelu_mismatched_tile_widths():
     # GPT-3-like slice: producer tile 256 wide with fused GELU, consumer K walk crosses producer tiles
     _chain("tile", 384, 1536, 1024, 768, 256, 128, iters=2, epi1=L.EPILOGUE_GELU_ERF)
     _chain("row", 384, 1536, 1024, 768, 256, 128, iters=2, epi1=L.EPILOGUE_GELU_ERF)
+
+
+@pytest.mark.parametrize("policy", ["row", "tile"])
+@pytest.mark.parametrize("opts", [0, L.OPT_NO_ATOMIC_ADD])
+def test_chain_with_cta_pairs(policy, opts):
+    if policy == "row" and opts:
+        pytest.skip("NoAtomicAdd needs one poster per semaphore (mlp.cu:9-14)")
+    # both GEMMs on CTA pairs, few clusters so consumers really wait; M = 640 -> 5 row tiles (odd)
+    _chain(policy, 640, 1024, 512, 1024, 256, 256, iters=3, opts=opts, max_ctas=4, cta_pair=2)
+    _chain(policy, 512, 1536, 1024, 768, 256, 256, iters=2, opts=opts, epi1=L.EPILOGUE_GELU_ERF, cta_pair=2)
 
 
 def test_chain_without_wait_kernel_small_grids():
