@@ -61,13 +61,13 @@ class GemmDesc(C.Structure):
                 ("b2", C.c_void_p),
                 ("d", C.c_void_p), ("ldd", C.c_int64),
                 ("b_layout", C.c_int32), ("epilogue", C.c_int32), ("tile_n", C.c_int32), ("max_ctas", C.c_int32),
-                ("cta_pair", C.c_int32), ("stage", C.c_void_p)]
+                ("split_k", C.c_int32), ("cta_pair", C.c_int32), ("stage", C.c_void_p)]
 
 
 class MlpDesc(C.Structure):
     _fields_ = [("model", C.c_int32), ("batch", C.c_int32), ("hidden", C.c_int32), ("ffn", C.c_int32),
                 ("policy", C.c_int32), ("opts", C.c_int32), ("tile_n1", C.c_int32), ("tile_n2", C.c_int32),
-                ("max_ctas", C.c_int32), ("cta_pair", C.c_int32), ("group_rows2", C.c_int32),
+                ("split_k1", C.c_int32), ("split_k2", C.c_int32), ("max_ctas", C.c_int32), ("cta_pair", C.c_int32), ("group_rows2", C.c_int32),
                 ("x", C.c_void_p), ("w1", C.c_void_p), ("v", C.c_void_p), ("w2", C.c_void_p),
                 ("h", C.c_void_p), ("y", C.c_void_p)]
 
@@ -95,6 +95,7 @@ SIGNATURES = {
     "cusync_stage_num_tiles": (_u32, [_vp]),
     "cusync_stage_iter": (_u32, [_vp]),
     "cusync_gemm_default_tile_n": (_i, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
+    "cusync_gemm_default_split_k": (_i, [C.c_int32] * 6),
     "cusync_gemm_plan_create": (_i, [C.POINTER(_vp), C.POINTER(GemmDesc)]),
     "cusync_gemm_plan_destroy": (_i, [_vp]),
     "cusync_gemm_plan_update": (_i, [_vp, _vp, _vp, _vp, _vp]),

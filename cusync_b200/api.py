@@ -203,7 +203,7 @@ class CuSync:
     setProducerConsumer = setProducerConsumerPair
 
 
-def gemm_tiled_shape(m, n, tile_m, tile_n, split_k=1):
+def gemm_tiled_shape(m, n, tile_m, tile_n, split_k=1):  # noqa: D401
     """CuSyncGemmHorizontalThreadblockSwizzle::get_tiled_shape + get_grid_shape
     (gemm/threadblock/cusync_threadblock_swizzle.h:12-54): the launch grid is (tilesN, tilesM, splitK)."""
     return ((n + tile_n - 1) // tile_n, (m + tile_m - 1) // tile_m, split_k)
@@ -214,7 +214,7 @@ class GemmArguments:
     (gemm/device/cusyncgemm.h:293-350).  ref_C is unused (beta = 0 in every reference driver)."""
 
     def __init__(self, custage, problem_size, ref_a, ref_b, ref_d, epilogue=L.EPILOGUE_NONE, ref_b2=None,
-                 b_layout=L.B_ROW_MAJOR_KN, tile_n=0, max_ctas=0, split_k_slices=1, cta_pair=0):
+                 b_layout=L.B_ROW_MAJOR_KN, tile_n=0, max_ctas=0, split_k_slices=0, cta_pair=0):
         self.custage, self.problem_size = custage, problem_size
         self.ref_a, self.ref_b, self.ref_b2, self.ref_d = ref_a, ref_b, ref_b2, ref_d
         self.epilogue, self.b_layout, self.tile_n, self.max_ctas = epilogue, b_layout, tile_n, max_ctas
@@ -250,12 +250,16 @@ class Gemm:
         d, ldd = _ref(args.ref_d)
         b2 = _ref(args.ref_b2)[0] if args.ref_b2 is not None else None
         return L.GemmDesc(m, n, k, a, lda, b, ldb, b2, d, ldd, args.b_layout, args.epilogue, args.tile_n,
-                          args.max_ctas, args.cta_pair, args.custage._h if args.custage is not None else None)
+                          args.max_ctas, args.split_k_slices, args.cta_pair, args.custage._h if args.custage is not None else None)
 
     def can_implement(self, args):
-        if args.split_k_slices != 1:
+        if args.split_k_slices < 0 or (args.split_k_slices > 1 and args.epilogue == L.EPILOGUE_SILU_MUL_DUAL):
             return L.ERROR_UNSUPPORTED
         return L.SUCCESS
+
+    @staticmethod
+    def default_split_k(m, n, k, epilogue=L.EPILOGUE_NONE, tile_n=0, cta_pair=0):
+        return L.lib().cusync_gemm_default_split_k(m, n, k, epilogue, tile_n, cta_pair)
 
     def initialize(self, args, workspace=None):
         if self.can_implement(args) != L.SUCCESS:

@@ -71,6 +71,10 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// Arrive on a barrier of any CTA of the cluster, given its shared::cluster address.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -187,6 +191,11 @@ struct GemmParams {
   int32_t b_chunked3d;         // [k,n] B: all 64-column chunks of a tile come with one 3-D TMA box
   int32_t is_producer, is_consumer;
   uint32_t b_lbo, b_sbo, b_kstep;  // B shared-memory descriptor: leading / stride offsets, bytes per UMMA K step
+  void* d; long long ldd;          // output matrix (split-K finalisation stores it without TMA)
+  int32_t split_k;                 // K slices per output tile (grid.z of the stage); 1 = none
+  int32_t k_blocks_per_split;      // ring stages per slice
+  float* splitk_ws;                // fp32 [tiles_m * 128, n] partial sums, all zero between launches
+  uint32_t* splitk_arrivals;       // per (m, n) tile: slices that have added their part
   const cusync_dim3_t* pair_order; // CTA-pair kernel: schedule over 256-row pair tiles {n tile, pair row, 0}
   int32_t num_pairs;
   unsigned long long* trace;       // optional per-tile timeline: 4 words per ticket (see cusync_gemm_plan_set_trace)
@@ -224,7 +233,11 @@ struct Barriers {
   uint64_t sched_empty[kSchedSlots];
   uint64_t drain;
   uint64_t post;                        // epilogue warps -> the posting thread
-  int32_t sched_tile[kSchedSlots][4];   // {n tile, m tile, valid, ticket}
+  uint64_t splitk_counted;              // posting thread -> epilogue warps: arrival counted, `splitk_last` valid
+  uint64_t splitk_done;                 // epilogue warps -> posting thread: finalisation stored
+  uint32_t splitk_last;
+  uint32_t pad0;
+  int32_t sched_tile[kSchedSlots][8];   // {n tile, m tile, valid, ticket, k slice, -, -, -}
   unsigned long long sched_time[kSchedSlots];   // globaltimer at the ticket draw (tracing only)
   uint32_t tmem_base;
   volatile uint32_t abort;
@@ -322,6 +335,100 @@ __device__ __forceinline__ void epilogue_store_rows(const GemmParams& p, const C
   }
 }
 
+
+__device__ __forceinline__ void red_add_v4_f32(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+// Split-K, phase 1: one warp adds its 32 accumulator rows (every second 64-column chunk from `half`)
+// into the fp32 workspace.  Rows and columns outside the matrix are skipped.
+template <int BN>
+__device__ __forceinline__ void splitk_accumulate_rows(const GemmParams& p, uint32_t t_row, int n_off, int row0,
+                                                       int half, int lane) {
+  const int row = row0 + lane;
+#pragma unroll 1
+  for (int c = half; c < BN / kStoreCols; c += 2) {
+    const int col0 = n_off + c * kStoreCols;
+    if (col0 >= p.n || row0 >= p.m) break;
+    uint32_t v[64];
+    tmem_ld_32x32b_x32(t_row + c * 64, v);
+    tmem_ld_32x32b_x32(t_row + c * 64 + 32, v + 32);
+    tmem_ld_wait();
+    if (row < p.m) {
+      float* dst = p.splitk_ws + static_cast<size_t>(row) * p.n + col0;
+#pragma unroll
+      for (int j = 0; j < 16; j++) {
+        if (col0 + 4 * j < p.n)      // n is a multiple of 8, so groups of four never straddle the edge
+          red_add_v4_f32(dst + 4 * j, __uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                         __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+      }
+    }
+  }
+}
+
+// Split-K, phase 2 (only in the block that brought the last slice): the 256 epilogue threads read the
+// summed tile back, zero it for the next launch, apply the epilogue and store fp16.
+template <int BN>
+__device__ __forceinline__ void splitk_finalize_tile(const GemmParams& p, __half* d, int64_t ldd, int n_off, int m_off,
+                                                     int tid) {
+  const int rows = p.m - m_off < kBlockM ? p.m - m_off : kBlockM;
+  constexpr int kVecPerRow = BN / 4;
+  for (int i = tid; i < rows * kVecPerRow; i += kEpilogueWarps * 32) {
+    const int r = i / kVecPerRow, c = (i % kVecPerRow) * 4;
+    const int col = n_off + c;
+    if (col >= p.n) continue;
+    float4* src = reinterpret_cast<float4*>(p.splitk_ws + static_cast<size_t>(m_off + r) * p.n + col);
+    float4 x = __ldcg(src);
+    __stcg(src, make_float4(0.f, 0.f, 0.f, 0.f));
+    if (p.epilogue == CUSYNC_EPILOGUE_GELU_ERF) { x.x = gelu_erf(x.x); x.y = gelu_erf(x.y); x.z = gelu_erf(x.z); x.w = gelu_erf(x.w); }
+    else if (p.epilogue == CUSYNC_EPILOGUE_RELU) { x.x = fmaxf(x.x, 0.f); x.y = fmaxf(x.y, 0.f); x.z = fmaxf(x.z, 0.f); x.w = fmaxf(x.w, 0.f); }
+    uint2 out = make_uint2(pack_half2(x.x, x.y), pack_half2(x.z, x.w));
+    *reinterpret_cast<uint2*>(d + static_cast<size_t>(m_off + r) * ldd + col) = out;
+  }
+}
+
+// Split-K epilogue of one tile for one epilogue warp; returns false if a bounded wait expired.
+// Every slice adds its part; the block that counts the last arrival finalises and publishes the tile
+// (the reference posts from the last K slice only, gemm/kernel/cusyncgemm.h:374-392).
+template <int BN>
+__device__ __forceinline__ bool splitk_epilogue(const GemmParams& p, Barriers* bars, const WaitCtx& ctx, uint32_t t_row,
+                                                int n_off, int m_off, int quarter, int half, int ew, int lane,
+                                                uint32_t phase, uint64_t* tmem_empty_local, uint32_t tmem_empty_cluster,
+                                                __half* d, int64_t ldd, bool* is_last) {
+  splitk_accumulate_rows<BN>(p, t_row, n_off, m_off + quarter * 32, half, lane);
+  // accumulator buffer is free for the MMA warp again
+  tc_fence_before();
+  __syncwarp();
+  if (lane == 0) {
+    if (tmem_empty_local) mbar_arrive(tmem_empty_local); else mbar_arrive_cluster(tmem_empty_cluster);
+    __threadfence();                 // this warp's adds are ordered before the arrival count
+    mbar_arrive(&bars->post);
+  }
+  bool ok = true;
+  if (ew == 0 && lane == 0) {
+    if (!mbar_wait(&bars->post, phase, ctx)) ok = false;
+    else if (m_off >= p.m) bars->splitk_last = 0u;     // a pair's second half past the last row tile
+    else {
+      const uint32_t tile = static_cast<uint32_t>(m_off / kBlockM) * static_cast<uint32_t>(p.tiles_n) +
+                            static_cast<uint32_t>(n_off / BN);
+      __threadfence();
+      const uint32_t before = atomicAdd(p.splitk_arrivals + tile, 1u);
+      const uint32_t last = before == static_cast<uint32_t>(p.split_k) - 1u ? 1u : 0u;
+      if (last) { p.splitk_arrivals[tile] = 0u; __threadfence(); }   // re-armed for the next launch
+      bars->splitk_last = last;
+    }
+    mbar_arrive(&bars->splitk_counted);
+  }
+  if (!mbar_wait(&bars->splitk_counted, phase, ctx)) ok = false;
+  const bool last = ok && bars->splitk_last != 0u;
+  __syncwarp();
+  if (last) splitk_finalize_tile<BN>(p, d, ldd, n_off, m_off, ew * 32 + lane);
+  __syncwarp();
+  if (lane == 0) { __threadfence(); mbar_arrive(&bars->splitk_done); }
+  *is_last = last;
+  return ok;
+}
+
 // ---------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------
@@ -349,6 +456,8 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     for (int i = 0; i < kSchedSlots; i++) { mbar_init(&bars->sched_full[i], 1); mbar_init(&bars->sched_empty[i], 1 + kEpilogueWarps); }
     mbar_init(&bars->drain, 1);
     mbar_init(&bars->post, kEpilogueWarps);
+    mbar_init(&bars->splitk_counted, 1);
+    mbar_init(&bars->splitk_done, kEpilogueWarps);
     bars->abort = 0u;
     fence_barrier_init();
     fence_proxy_async_smem();
@@ -403,6 +512,7 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         bars->sched_tile[slot][1] = static_cast<int32_t>(t.y);
         bars->sched_tile[slot][2] = valid ? 1 : 0;
         bars->sched_tile[slot][3] = static_cast<int32_t>(ticket);
+        bars->sched_tile[slot][4] = static_cast<int32_t>(t.z);
         if (p.trace) bars->sched_time[slot] = cusync::globalTimerNs();
         mbar_arrive(&bars->sched_full[slot]);
         sched_it++;
@@ -410,9 +520,13 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 
         const int n_off = static_cast<int>(t.x) * BN;
         const int m_off = static_cast<int>(t.y) * kBlockM;
+        // K slice of this work unit (the whole K walk without split-K)
+        const int kb_begin = static_cast<int>(t.z) * p.k_blocks_per_split;
+        const int kb_end = kb_begin + p.k_blocks_per_split < p.num_k_blocks ? kb_begin + p.k_blocks_per_split
+                                                                           : p.num_k_blocks;
         uint32_t ready_end = 0;   // K offset below which this tile's producer tiles are known finished
         long long wait_empty = 0;
-        for (int kb = 0; kb < p.num_k_blocks; kb++) {
+        for (int kb = kb_begin; kb < kb_end; kb++) {
           const uint32_t s = fills % C::kStages, ph = (fills / C::kStages) & 1u;
           const long long c0 = p.trace ? clock64() : 0;
           if (!mbar_wait(&bars->empty[s], ph ^ 1u, ctx)) { ok = false; break; }
@@ -442,7 +556,7 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           }
           // Consumer wait, at the load of the dependent A K-block.
           if (p.is_consumer) {
-            const uint32_t tz = kb == 0 ? 1u : 0u;
+            const uint32_t tz = kb == kb_begin ? 1u : 0u;
             if (static_cast<uint32_t>(k_off) >= ready_end &&
                 cusync::eval::isSync(st.in_policy, static_cast<uint32_t>(k_off), tz)) {
               const uint32_t idx = cusync::eval::tileIndex(st.in_policy, static_cast<uint32_t>(m_off),
@@ -521,6 +635,7 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         if (!mbar_wait(&bars->sched_full[slot], sph, ctx)) { ok = false; break; }
         const int valid = bars->sched_tile[slot][2];
         const uint32_t ticket = static_cast<uint32_t>(bars->sched_tile[slot][3]);
+        const int slice = bars->sched_tile[slot][4];
         mbar_arrive(&bars->sched_empty[slot]);
         sched_it++;
         if (!valid) break;
@@ -531,7 +646,10 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         const long long t_acc = p.trace ? clock64() : 0;
         long long wait_full = 0;
         const uint32_t d_tmem = tmem_base + acc * C::kAccCols;
-        for (int kb = 0; kb < p.num_k_blocks; kb++) {
+        const int kb_first = slice * p.k_blocks_per_split;
+        const int kb_count = kb_first + p.k_blocks_per_split < p.num_k_blocks ? p.k_blocks_per_split
+                                                                             : p.num_k_blocks - kb_first;
+        for (int kb = 0; kb < kb_count; kb++) {
           const uint32_t s = drains % C::kStages, ph = (drains / C::kStages) & 1u;
           const long long c0 = p.trace ? clock64() : 0;
           if (!mbar_wait(&bars->full[s], ph, ctx)) { ok = false; break; }
@@ -601,6 +719,27 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       const int n_off = tile_n * BN, m_off = tile_m * kBlockM;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * C::kAccCols;
 
+      if (!DUAL && p.split_k > 1) {
+        // Split-K: add this slice's part; the block that brings the last slice finalises and posts.
+        bool last = false;
+        ok = splitk_epilogue<BN>(p, bars, ctx, t_row, n_off, m_off, quarter, half, ew, lane, post_it & 1u,
+                                 &bars->tmem_empty[acc], 0u, static_cast<__half*>(p.d), p.ldd, &last);
+        acc_it++;
+        if (ew == 0 && lane == 0) {
+          if (!mbar_wait(&bars->splitk_done, post_it & 1u, ctx)) ok = false;
+          else if (last && p.is_producer) {
+            const uint32_t idx = cusync::eval::tileIndex(st.out_policy, static_cast<uint32_t>(m_off),
+                                                         static_cast<uint32_t>(n_off), st.grid.x, st.grid.y);
+            const uint32_t pv = cusync::eval::postValue(st.out_policy);
+            __threadfence();
+            if (st.opts & CUSYNC_OPT_NO_ATOMIC_ADD) cusync::storeRelease(st.sems_post + idx, pv * st.iter);
+            else                                    cusync::addRelease(st.sems_post + idx, pv);
+          }
+        }
+        post_it++;
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        continue;
+      }
       epilogue_store_rows<BN, DUAL>(p, &tmD, buf, t_row, n_off, m_off + quarter * 32, half, lane);
       // Accumulator buffer is free for the MMA warp again.
       tc_fence_before();
@@ -676,9 +815,6 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
 }
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 __device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
   asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
@@ -810,6 +946,8 @@ cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     }
     mbar_init(&bars->drain, 1);
     mbar_init(&bars->post, kEpilogueWarps);
+    mbar_init(&bars->splitk_counted, 1);
+    mbar_init(&bars->splitk_done, kEpilogueWarps);
     bars->abort = 0u;
     fence_barrier_init();
     fence_proxy_async_smem();
@@ -854,7 +992,7 @@ cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
       const uint32_t peer_sched_full0 = map_to_cta(smem_u32(&bars->sched_full[0]), 1);
       while (ok) {
         const uint32_t slot = sched_it % kSchedSlots, sph = (sched_it / kSchedSlots) & 1u;
-        int32_t tn, tpm, valid;
+        int32_t tn, tpm, valid, tz_slice = 0;
         if (leader) {
           if (!mbar_wait_cluster(&bars->sched_empty[slot], sph ^ 1u, ctx)) { ok = false; break; }
           const uint32_t ticket = atomicAdd(st.tile_counter, 1u);
@@ -862,15 +1000,17 @@ cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
           valid = ticket < static_cast<uint32_t>(p.num_pairs) ? 1 : 0;
           cusync_dim3_t t = {0, 0, 0};
           if (valid) t = p.pair_order[ticket];
-          tn = static_cast<int32_t>(t.x); tpm = static_cast<int32_t>(t.y);
+          tn = static_cast<int32_t>(t.x); tpm = static_cast<int32_t>(t.y); tz_slice = static_cast<int32_t>(t.z);
           const unsigned long long now = p.trace ? cusync::globalTimerNs() : 0ull;
           bars->sched_tile[slot][0] = tn; bars->sched_tile[slot][1] = tpm;
           bars->sched_tile[slot][2] = valid; bars->sched_tile[slot][3] = static_cast<int32_t>(ticket);
+          bars->sched_tile[slot][4] = tz_slice;
           bars->sched_time[slot] = now;
           // the same record into the peer's ring, then signal both
-          const uint32_t pt = peer_sched_tile0 + slot * 16;
+          const uint32_t pt = peer_sched_tile0 + slot * 32;
           st_cluster_u32(pt, static_cast<uint32_t>(tn)); st_cluster_u32(pt + 4, static_cast<uint32_t>(tpm));
           st_cluster_u32(pt + 8, static_cast<uint32_t>(valid)); st_cluster_u32(pt + 12, ticket);
+          st_cluster_u32(pt + 16, static_cast<uint32_t>(tz_slice));
           st_cluster_u32(peer_sched_time0 + slot * 8, static_cast<uint32_t>(now));
           st_cluster_u32(peer_sched_time0 + slot * 8 + 4, static_cast<uint32_t>(now >> 32));
           mbar_arrive(&bars->sched_full[slot]);
@@ -878,6 +1018,7 @@ cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         } else {
           if (!mbar_wait_cluster(&bars->sched_full[slot], sph, ctx)) { ok = false; break; }
           tn = bars->sched_tile[slot][0]; tpm = bars->sched_tile[slot][1]; valid = bars->sched_tile[slot][2];
+          tz_slice = bars->sched_tile[slot][4];
           mbar_arrive_cluster(leader_sched_empty0 + slot * 8);
         }
         sched_it++;
@@ -888,7 +1029,10 @@ cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         const int nb_off = n_off + static_cast<int>(rank) * (BN / 2);               // this CTA's half of B
         uint32_t ready_end = 0;
         long long wait_empty = 0;
-        for (int kb = 0; kb < p.num_k_blocks; kb++) {
+        const int kb_begin = tz_slice * p.k_blocks_per_split;
+        const int kb_end = kb_begin + p.k_blocks_per_split < p.num_k_blocks ? kb_begin + p.k_blocks_per_split
+                                                                           : p.num_k_blocks;
+        for (int kb = kb_begin; kb < kb_end; kb++) {
           const uint32_t s = fills % C::kStages, ph = (fills / C::kStages) & 1u;
           const long long c0 = p.trace ? clock64() : 0;
           if (!mbar_wait_cluster(&bars->empty[s], ph ^ 1u, ctx)) { ok = false; break; }
@@ -908,7 +1052,7 @@ cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
           for (int sub = 0; sub < kPairBlockK / kBlockK && ok; sub++) {
           const int k_off = k_base + sub * kBlockK;
           if (p.is_consumer && m_off < p.m && k_off < p.k) {
-            const uint32_t tz = (kb == 0 && sub == 0) ? 1u : 0u;
+            const uint32_t tz = (kb == kb_begin && sub == 0) ? 1u : 0u;
             if (static_cast<uint32_t>(k_off) >= ready_end &&
                 cusync::eval::isSync(st.in_policy, static_cast<uint32_t>(k_off), tz)) {
               const uint32_t idx = cusync::eval::tileIndex(st.in_policy, static_cast<uint32_t>(m_off),
@@ -993,6 +1137,7 @@ cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         if (!mbar_wait(&bars->sched_full[slot], sph, ctx)) { ok = false; break; }
         const int valid = bars->sched_tile[slot][2];
         const uint32_t ticket = static_cast<uint32_t>(bars->sched_tile[slot][3]);
+        const int slice = bars->sched_tile[slot][4];
         mbar_arrive(&bars->sched_empty[slot]);
         sched_it++;
         if (!valid) break;
@@ -1003,7 +1148,10 @@ cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         const long long t_acc = p.trace ? clock64() : 0;
         long long wait_full = 0;
         const uint32_t d_tmem = tmem_base + acc * C::kAccCols;
-        for (int kb = 0; kb < p.num_k_blocks; kb++) {
+        const int kb_first = slice * p.k_blocks_per_split;
+        const int kb_count = kb_first + p.k_blocks_per_split < p.num_k_blocks ? p.k_blocks_per_split
+                                                                             : p.num_k_blocks - kb_first;
+        for (int kb = 0; kb < kb_count; kb++) {
           const uint32_t s = drains % C::kStages, ph = (drains / C::kStages) & 1u;
           const long long c0 = p.trace ? clock64() : 0;
           if (!mbar_wait_cluster(&bars->full[s], ph, ctx)) { ok = false; break; }
@@ -1072,6 +1220,26 @@ cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
       const int m_off = pair_m * (2 * kBlockM) + static_cast<int>(rank) * kBlockM;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * C::kAccCols;
 
+      if (p.split_k > 1) {
+        bool last = false;
+        ok = splitk_epilogue<BN>(p, bars, ctx, t_row, n_off, m_off, quarter, half, ew, lane, post_it & 1u, nullptr,
+                                 leader_tmem_empty0 + acc * 8, static_cast<__half*>(p.d), p.ldd, &last);
+        acc_it++;
+        if (ew == 0 && lane == 0) {
+          if (!mbar_wait(&bars->splitk_done, post_it & 1u, ctx)) ok = false;
+          else if (last && p.is_producer) {
+            const uint32_t idx = cusync::eval::tileIndex(st.out_policy, static_cast<uint32_t>(m_off),
+                                                         static_cast<uint32_t>(n_off), st.grid.x, st.grid.y);
+            const uint32_t pv = cusync::eval::postValue(st.out_policy);
+            __threadfence();
+            if (st.opts & CUSYNC_OPT_NO_ATOMIC_ADD) cusync::storeRelease(st.sems_post + idx, pv * st.iter);
+            else                                    cusync::addRelease(st.sems_post + idx, pv);
+          }
+        }
+        post_it++;
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        continue;
+      }
       epilogue_store_rows<BN, false>(p, &tmD, buf, t_row, n_off, m_off + quarter * 32, half, lane);
 
       tc_fence_before();
@@ -1211,9 +1379,26 @@ struct cusync_gemm_plan {
   cusync_stage_t* stage;
   bool pair;                   // CTA-pair kernel (tcgen05 cta_group::2, 256 x 256 tiles per pair)
   cusync_dim3_t* pair_order;   // device: schedule over pair tiles
+  int split_k;
+  float* splitk_ws;            // device: fp32 partial sums [tiles_m * 128, n], zero between launches
+  uint32_t* splitk_arrivals;   // device: per-tile slice counters, zero between launches
 };
 
 namespace {
+
+// K slices per output tile when the caller leaves the choice open: enough to give every SM (or SM pair) a
+// work unit when the tile grid alone cannot, as long as a slice keeps at least 1024 of K.
+int auto_split_k(int m, int n, int k, int tile_n, bool dual, bool pair, int sms) {
+  if (dual || sms <= 0) return 1;
+  const int tiles_n = (n + tile_n - 1) / tile_n, tiles_m = (m + kBlockM - 1) / kBlockM;
+  const int units = pair ? tiles_n * ((tiles_m + 1) / 2) : tiles_n * tiles_m;
+  const int capacity = pair ? sms / 2 : sms;
+  int split = capacity / units;
+  const int max_by_k = k / 1024;
+  if (split > max_by_k) split = max_by_k;
+  if (split > 16) split = 16;
+  return split < 1 ? 1 : split;
+}
 
 // Whether cusync_gemm_plan_create picks the CTA-pair kernel when the caller leaves the choice open.
 bool pair_by_default(int m, int tile_n, bool dual) {
@@ -1226,19 +1411,21 @@ int setup_pair(cusync_gemm_plan* pl, const cusync_stage_view_t& view, uint32_t c
   GemmParams& p = pl->params;
   const uint32_t pair_rows = static_cast<uint32_t>((p.tiles_m + 1) / 2);
   const uint32_t tiles_n = static_cast<uint32_t>(p.tiles_n);
-  const uint32_t num_pairs = pair_rows * tiles_n;
+  const uint32_t split = static_cast<uint32_t>(pl->split_k);
+  const uint32_t num_pairs = pair_rows * tiles_n * split;   // work units: pair tile x K slice, slice outermost
   std::vector<cusync_dim3_t> order(num_pairs, cusync_dim3_t{num_pairs, 0, 0});
   const int kind = view.order & 0xff;
   uint32_t group = static_cast<uint32_t>(view.order) >> 8;
   group = group > 1 ? group / 2 : 1;   // a group of R 128-row tiles is R/2 pair rows
-  for (uint32_t y = 0; y < pair_rows; y++)
-    for (uint32_t x = 0; x < tiles_n; x++) {
-      const uint32_t id = kind == CUSYNC_ORDER_GROUPED_ROWS
-                              ? cusync::eval::groupedBlockIndex(group, tiles_n, pair_rows, x, y, 0)
-                              : cusync::eval::blockIndex(tiles_n, pair_rows, x, y, 0);
-      if (id >= num_pairs || order[id].x != num_pairs) return CUSYNC_ERROR_INVALID_LINEAR_BLOCK_INDEX;
-      order[id] = cusync_dim3_t{x, y, 0};
-    }
+  for (uint32_t z = 0; z < split; z++)
+    for (uint32_t y = 0; y < pair_rows; y++)
+      for (uint32_t x = 0; x < tiles_n; x++) {
+        const uint32_t id = kind == CUSYNC_ORDER_GROUPED_ROWS
+                                ? cusync::eval::groupedBlockIndex(group, tiles_n, pair_rows, x, y, z)
+                                : cusync::eval::blockIndex(tiles_n, pair_rows, x, y, z);
+        if (id >= num_pairs || order[id].x != num_pairs) return CUSYNC_ERROR_INVALID_LINEAR_BLOCK_INDEX;
+        order[id] = cusync_dim3_t{x, y, z};
+      }
   if (cudaMalloc(&pl->pair_order, sizeof(cusync_dim3_t) * num_pairs) != cudaSuccess ||
       cudaMemcpy(pl->pair_order, order.data(), sizeof(cusync_dim3_t) * num_pairs, cudaMemcpyHostToDevice) !=
           cudaSuccess) {
@@ -1396,6 +1583,8 @@ extern "C" int cusync_gemm_run_noalloc(const cusync_gemm_desc_t* desc, cusync_st
   p.tiles_m = static_cast<int32_t>(tiles_m);
   p.num_tiles = p.tiles_n * p.tiles_m;
   p.num_k_blocks = (d.k + kBlockK - 1) / kBlockK;
+  p.split_k = 1; p.k_blocks_per_split = p.num_k_blocks;
+  p.d = d.d; p.ldd = d.ldd;
   p.epilogue = d.epilogue;
   p.b_kmajor = d.b_layout == CUSYNC_B_ROW_MAJOR_NK ? 1 : 0;
   if (p.b_kmajor) { p.b_lbo = 16; p.b_sbo = 1024; p.b_kstep = 32; }
@@ -1442,9 +1631,20 @@ extern "C" {
 int cusync_gemm_default_tile_n(int32_t m, int32_t n, int32_t k, int32_t epilogue) {
   (void)k;
   if (epilogue == CUSYNC_EPILOGUE_SILU_MUL_DUAL) return m <= 128 ? 64 : 128;
-  if (m <= 128) return 64;        // weight-bandwidth bound: more, narrower tiles
+  // Every MMA issue costs the issuing thread about as much whatever its width, so wide tiles it is, also for
+  // a single row of tiles; split-K then spreads the weight stream over all SMs.
   if (n % 256 == 0 || n >= 2048) return 256;
-  return 128;
+  return m <= 128 ? 64 : 128;
+}
+
+int cusync_gemm_default_split_k(int32_t m, int32_t n, int32_t k, int32_t epilogue, int32_t tile_n, int32_t cta_pair) {
+  const bool dual = epilogue == CUSYNC_EPILOGUE_SILU_MUL_DUAL;
+  if (tile_n <= 0) tile_n = cusync_gemm_default_tile_n(m, n, k, epilogue);
+  const bool pair_ok = !dual && tile_n == kPairBN && k % 64 == 0;
+  const bool pair = cta_pair == 2 || (cta_pair == 0 && pair_ok && pair_by_default(m, tile_n, dual));
+  int sms = cusync_b200_sm_count();
+  if (sms <= 0) sms = 148;
+  return auto_split_k(m, n, k, tile_n, dual, pair, sms);
 }
 
 int cusync_gemm_plan_create(cusync_gemm_plan_t** out, const cusync_gemm_desc_t* desc) {
@@ -1480,12 +1680,23 @@ int cusync_gemm_plan_create(cusync_gemm_plan_t** out, const cusync_gemm_desc_t* 
   pl->pair = d.cta_pair == 2 || (d.cta_pair == 0 && pair_ok && pair_by_default(d.m, pl->tile_n, dual));
   if (pl->pair) pl->kernel = KernelEntry{nullptr, PairCfg::kSmemBytes};
 
+  int sms = cusync_b200_sm_count();
+  if (sms <= 0) sms = 148;
+  if (d.split_k < 0 || d.split_k > 64 || (dual && d.split_k > 1)) { delete pl; return CUSYNC_ERROR_UNSUPPORTED; }
+  pl->split_k = d.split_k > 0 ? d.split_k : auto_split_k(d.m, d.n, d.k, pl->tile_n, dual, pl->pair, sms);
+
   GemmParams& p = pl->params;
   p.m = d.m; p.n = d.n; p.k = d.k;
+  p.d = d.d; p.ldd = d.ldd;
   p.tiles_n = (d.n + pl->tile_n - 1) / pl->tile_n;
   p.tiles_m = (d.m + kBlockM - 1) / kBlockM;
-  p.num_tiles = p.tiles_n * p.tiles_m;
   p.num_k_blocks = pl->pair ? (d.k + kPairBlockK - 1) / kPairBlockK : (d.k + kBlockK - 1) / kBlockK;
+  // Slices of whole ring stages; drop slices that rounding left empty.
+  p.k_blocks_per_split = (p.num_k_blocks + pl->split_k - 1) / pl->split_k;
+  pl->split_k = (p.num_k_blocks + p.k_blocks_per_split - 1) / p.k_blocks_per_split;
+  if (d.split_k > 0 && pl->split_k != d.split_k) { delete pl; return CUSYNC_ERROR_UNSUPPORTED; }
+  p.split_k = pl->split_k;
+  p.num_tiles = p.tiles_n * p.tiles_m * pl->split_k;
   p.epilogue = d.epilogue;
   p.b_kmajor = d.b_layout == CUSYNC_B_ROW_MAJOR_NK ? 1 : 0;
   // [k,n] weights whose n is a whole number of 64-column chunks are fetched with one 3-D box per K-block
@@ -1504,7 +1715,8 @@ int cusync_gemm_plan_create(cusync_gemm_plan_t** out, const cusync_gemm_desc_t* 
 
   pl->stage = d.stage;
   if (pl->stage == nullptr) {
-    cusync_dim3_t grid = {static_cast<uint32_t>(p.tiles_n), static_cast<uint32_t>(p.tiles_m), 1};
+    cusync_dim3_t grid = {static_cast<uint32_t>(p.tiles_n), static_cast<uint32_t>(p.tiles_m),
+                          static_cast<uint32_t>(pl->split_k)};
     cusync_dim3_t ts = {1, 1, 1};
     int rc = cusync_stage_create(&pl->own_stage, grid, ts, CUSYNC_ORDER_TRANSPOSE_XY, nullptr, nullptr,
                                  CUSYNC_OPT_NONE);
@@ -1513,10 +1725,10 @@ int cusync_gemm_plan_create(cusync_gemm_plan_t** out, const cusync_gemm_desc_t* 
   }
   cusync_stage_view_t view;
   cusync_stage_get_view(pl->stage, &view);
-  // The stage's grid is the tile grid (N tiles, M tiles, split-K = 1), as
+  // The stage's grid is the tile grid (N tiles, M tiles, K slices), as
   // CuSyncGemmHorizontalThreadblockSwizzle lays it out.
   if (view.grid.x != static_cast<uint32_t>(p.tiles_n) || view.grid.y != static_cast<uint32_t>(p.tiles_m) ||
-      view.grid.z != 1) {
+      view.grid.z != static_cast<uint32_t>(pl->split_k)) {
     if (pl->own_stage) cusync_stage_destroy(pl->own_stage);
     delete pl;
     return CUSYNC_ERROR_INVALID_ARGUMENT;
@@ -1527,15 +1739,26 @@ int cusync_gemm_plan_create(cusync_gemm_plan_t** out, const cusync_gemm_desc_t* 
     return CUSYNC_ERROR_NOT_INITIALIZED;   // consumer not wired to a producer yet
   }
 
-  int sms = cusync_b200_sm_count();
-  if (sms <= 0) sms = 148;
   uint32_t cap = d.max_ctas > 0 ? static_cast<uint32_t>(d.max_ctas) : static_cast<uint32_t>(sms);
   pl->num_ctas = static_cast<uint32_t>(p.num_tiles) < cap ? static_cast<uint32_t>(p.num_tiles) : cap;
 
   int rc = CUSYNC_SUCCESS;
+  if (pl->split_k > 1) {
+    const size_t ws_bytes = static_cast<size_t>(p.tiles_m) * kBlockM * static_cast<size_t>(d.n) * sizeof(float);
+    const size_t cnt_bytes = static_cast<size_t>(p.tiles_m) * p.tiles_n * sizeof(uint32_t);
+    if (cudaMalloc(&pl->splitk_ws, ws_bytes) != cudaSuccess || cudaMemset(pl->splitk_ws, 0, ws_bytes) != cudaSuccess ||
+        cudaMalloc(&pl->splitk_arrivals, cnt_bytes) != cudaSuccess ||
+        cudaMemset(pl->splitk_arrivals, 0, cnt_bytes) != cudaSuccess) {
+      (void)cudaGetLastError();
+      rc = CUSYNC_ERROR_CUDA;
+    }
+    p.splitk_ws = pl->splitk_ws;
+    p.splitk_arrivals = pl->splitk_arrivals;
+  }
   const void* kernel_fn = pl->pair ? reinterpret_cast<const void*>(cusync_gemm_pair_kernel)
                                    : reinterpret_cast<const void*>(pl->kernel.fn);
-  if (cudaFuncSetAttribute(kernel_fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  if (rc == CUSYNC_SUCCESS &&
+      cudaFuncSetAttribute(kernel_fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            static_cast<int>(pl->kernel.smem)) != cudaSuccess) {
     (void)cudaGetLastError();
     rc = CUSYNC_ERROR_CUDA;
@@ -1544,7 +1767,7 @@ int cusync_gemm_plan_create(cusync_gemm_plan_t** out, const cusync_gemm_desc_t* 
   if (rc == CUSYNC_SUCCESS) rc = build_maps(pl);
   if (rc != CUSYNC_SUCCESS) {
     if (pl->own_stage) cusync_stage_destroy(pl->own_stage);
-    cudaFree(pl->pair_order);
+    cudaFree(pl->pair_order); cudaFree(pl->splitk_ws); cudaFree(pl->splitk_arrivals);
     delete pl;
     return rc;
   }
@@ -1554,7 +1777,7 @@ int cusync_gemm_plan_create(cusync_gemm_plan_t** out, const cusync_gemm_desc_t* 
 
 int cusync_gemm_plan_destroy(cusync_gemm_plan_t* pl) {
   if (!pl) return CUSYNC_ERROR_NOT_INITIALIZED;
-  cudaFree(pl->pair_order);
+  cudaFree(pl->pair_order); cudaFree(pl->splitk_ws); cudaFree(pl->splitk_arrivals);
   if (pl->own_stage) cusync_stage_destroy(pl->own_stage);
   delete pl;
   return CUSYNC_SUCCESS;
@@ -1565,7 +1788,7 @@ int cusync_gemm_plan_update(cusync_gemm_plan_t* pl, const void* a, const void* b
   if (a) pl->desc.a = a;
   if (b) pl->desc.b = b;
   if (b2) pl->desc.b2 = b2;
-  if (d) pl->desc.d = d;
+  if (d) { pl->desc.d = d; pl->params.d = d; }
   if (!aligned16(pl->desc.a) || !aligned16(pl->desc.b) || !aligned16(pl->desc.d)) return CUSYNC_ERROR_UNSUPPORTED;
   return build_maps(pl);
 }

@@ -11,6 +11,7 @@
 struct cusync_mlp {
   cusync_mlp_desc_t desc;
   int tile_n1, tile_n2;
+  int split_k1, split_k2;
   cusync_stage_t* prod;
   cusync_stage_t* cons;
   cusync_gemm_plan_t* sync1;    // producer GEMM with its stage
@@ -22,7 +23,7 @@ struct cusync_mlp {
 
 namespace {
 
-void fill_gemm1(const cusync_mlp_desc_t& d, int tile_n, cusync_stage_t* stage, cusync_gemm_desc_t* g) {
+void fill_gemm1(const cusync_mlp_desc_t& d, int tile_n, int split_k, cusync_stage_t* stage, cusync_gemm_desc_t* g) {
   std::memset(g, 0, sizeof(*g));
   g->m = d.batch; g->n = d.ffn; g->k = d.hidden;
   g->a = d.x; g->lda = d.hidden;
@@ -31,10 +32,10 @@ void fill_gemm1(const cusync_mlp_desc_t& d, int tile_n, cusync_stage_t* stage, c
   g->d = d.h; g->ldd = d.ffn;
   g->b_layout = CUSYNC_B_ROW_MAJOR_KN;
   g->epilogue = d.model == CUSYNC_MLP_LLAMA ? CUSYNC_EPILOGUE_SILU_MUL_DUAL : CUSYNC_EPILOGUE_GELU_ERF;
-  g->tile_n = tile_n; g->max_ctas = d.max_ctas; g->cta_pair = d.cta_pair; g->stage = stage;
+  g->tile_n = tile_n; g->max_ctas = d.max_ctas; g->split_k = split_k; g->cta_pair = d.cta_pair; g->stage = stage;
 }
 
-void fill_gemm2(const cusync_mlp_desc_t& d, int tile_n, cusync_stage_t* stage, cusync_gemm_desc_t* g) {
+void fill_gemm2(const cusync_mlp_desc_t& d, int tile_n, int split_k, cusync_stage_t* stage, cusync_gemm_desc_t* g) {
   std::memset(g, 0, sizeof(*g));
   g->m = d.batch; g->n = d.hidden; g->k = d.ffn;
   g->a = d.h; g->lda = d.ffn;
@@ -42,7 +43,7 @@ void fill_gemm2(const cusync_mlp_desc_t& d, int tile_n, cusync_stage_t* stage, c
   g->d = d.y; g->ldd = d.hidden;
   g->b_layout = CUSYNC_B_ROW_MAJOR_KN;
   g->epilogue = CUSYNC_EPILOGUE_NONE;
-  g->tile_n = tile_n; g->max_ctas = d.max_ctas; g->cta_pair = d.cta_pair; g->stage = stage;
+  g->tile_n = tile_n; g->max_ctas = d.max_ctas; g->split_k = split_k; g->cta_pair = d.cta_pair; g->stage = stage;
 }
 
 void destroy_all(cusync_mlp* m) {
@@ -78,10 +79,16 @@ int cusync_mlp_create(cusync_mlp_t** out, const cusync_mlp_desc_t* desc) {
   m->tile_n1 = d.tile_n1 ? d.tile_n1 : cusync_gemm_default_tile_n(d.batch, d.ffn, d.hidden, epi1);
   m->tile_n2 = d.tile_n2 ? d.tile_n2 : cusync_gemm_default_tile_n(d.batch, d.hidden, d.ffn, CUSYNC_EPILOGUE_NONE);
 
-  // Tile grids (N tiles, M tiles, 1) and the sync policy between the GEMMs.
+  m->split_k1 = d.split_k1 ? d.split_k1 : cusync_gemm_default_split_k(d.batch, d.ffn, d.hidden, epi1, m->tile_n1, d.cta_pair);
+  m->split_k2 = d.split_k2 ? d.split_k2
+                           : cusync_gemm_default_split_k(d.batch, d.hidden, d.ffn, CUSYNC_EPILOGUE_NONE, m->tile_n2, d.cta_pair);
+
+  // Tile grids (N tiles, M tiles, K slices) and the sync policy between the GEMMs.
   const uint32_t tiles_m = static_cast<uint32_t>((d.batch + 127) / 128);
-  cusync_dim3_t grid1 = {static_cast<uint32_t>((d.ffn + m->tile_n1 - 1) / m->tile_n1), tiles_m, 1};
-  cusync_dim3_t grid2 = {static_cast<uint32_t>((d.hidden + m->tile_n2 - 1) / m->tile_n2), tiles_m, 1};
+  cusync_dim3_t grid1 = {static_cast<uint32_t>((d.ffn + m->tile_n1 - 1) / m->tile_n1), tiles_m,
+                         static_cast<uint32_t>(m->split_k1)};
+  cusync_dim3_t grid2 = {static_cast<uint32_t>((d.hidden + m->tile_n2 - 1) / m->tile_n2), tiles_m,
+                         static_cast<uint32_t>(m->split_k2)};
   cusync_policy_t sync;
   std::memset(&sync, 0, sizeof(sync));
   sync.kind = d.policy;
@@ -103,11 +110,11 @@ int cusync_mlp_create(cusync_mlp_t** out, const cusync_mlp_desc_t* desc) {
   if (rc == CUSYNC_SUCCESS) rc = cusync_stage_link(m->prod, m->cons);
 
   cusync_gemm_desc_t g;
-  if (rc == CUSYNC_SUCCESS) { fill_gemm1(d, m->tile_n1, m->prod, &g); rc = cusync_gemm_plan_create(&m->sync1, &g); }
-  if (rc == CUSYNC_SUCCESS) { fill_gemm2(d, m->tile_n2, m->cons, &g); rc = cusync_gemm_plan_create(&m->sync2, &g); }
-  if (rc == CUSYNC_SUCCESS) { fill_gemm1(d, m->tile_n1, nullptr, &g); rc = cusync_gemm_plan_create(&m->plain1, &g); }
+  if (rc == CUSYNC_SUCCESS) { fill_gemm1(d, m->tile_n1, m->split_k1, m->prod, &g); rc = cusync_gemm_plan_create(&m->sync1, &g); }
+  if (rc == CUSYNC_SUCCESS) { fill_gemm2(d, m->tile_n2, m->split_k2, m->cons, &g); rc = cusync_gemm_plan_create(&m->sync2, &g); }
+  if (rc == CUSYNC_SUCCESS) { fill_gemm1(d, m->tile_n1, m->split_k1, nullptr, &g); rc = cusync_gemm_plan_create(&m->plain1, &g); }
   if (rc == CUSYNC_SUCCESS) rc = cusync_stage_create(&m->plain_stage2, grid2, ts, order2, &none, &none, CUSYNC_OPT_NONE);
-  if (rc == CUSYNC_SUCCESS) { fill_gemm2(d, m->tile_n2, m->plain_stage2, &g); rc = cusync_gemm_plan_create(&m->plain2, &g); }
+  if (rc == CUSYNC_SUCCESS) { fill_gemm2(d, m->tile_n2, m->split_k2, m->plain_stage2, &g); rc = cusync_gemm_plan_create(&m->plain2, &g); }
   if (rc != CUSYNC_SUCCESS) { destroy_all(m); return rc; }
   *out = m;
   return CUSYNC_SUCCESS;
@@ -169,11 +176,12 @@ int cusync_mlp_set_trace(cusync_mlp_t* m, void* t1, uint32_t c1, void* t2, uint3
   return cusync_gemm_plan_set_trace(m->sync2, t2, c2);
 }
 
-int cusync_mlp_config(const cusync_mlp_t* m, int32_t* out4) {
-  if (!m || !out4) return CUSYNC_ERROR_NOT_INITIALIZED;
-  out4[0] = m->tile_n1; out4[1] = m->tile_n2;
-  out4[2] = static_cast<int32_t>(cusync_gemm_plan_num_ctas(m->sync1));
-  out4[3] = static_cast<int32_t>(cusync_gemm_plan_num_ctas(m->sync2));
+int cusync_mlp_config(const cusync_mlp_t* m, int32_t* out6) {
+  if (!m || !out6) return CUSYNC_ERROR_NOT_INITIALIZED;
+  out6[0] = m->tile_n1; out6[1] = m->tile_n2;
+  out6[2] = static_cast<int32_t>(cusync_gemm_plan_num_ctas(m->sync1));
+  out6[3] = static_cast<int32_t>(cusync_gemm_plan_num_ctas(m->sync2));
+  out6[4] = m->split_k1; out6[5] = m->split_k2;
   return CUSYNC_SUCCESS;
 }
 

@@ -77,7 +77,8 @@ class Gemm {
   Gemm() : plan_(nullptr) {}
 
   static Status can_implement(const Arguments& a) {
-    if (a.split_k_slices != 1) return Status::kErrorNotSupported;
+    if (a.split_k_slices < 1) return Status::kErrorNotSupported;
+    if (a.split_k_slices > 1 && EpilogueKind == EpilogueSiluMulDual) return Status::kErrorNotSupported;
     if (a.epilogue.alpha != 1.0f || a.epilogue.beta != 0.0f) return Status::kErrorNotSupported;
     if (a.problem_size.m() <= 0 || a.problem_size.n() <= 0 || a.problem_size.k() <= 0)
       return Status::kErrorInvalidProblem;
@@ -103,6 +104,8 @@ class Gemm {
     d.epilogue = EpilogueKind;
     d.tile_n = TileN;
     d.max_ctas = 0;
+    d.split_k = a.split_k_slices;   // explicit, as in the reference: the stage grid's z must match
+    d.cta_pair = 0;
     d.stage = params_.custage.handle();
     int rc = cusync_gemm_plan_create(&plan_, &d);
     if (rc == CUSYNC_ERROR_UNSUPPORTED) return Status::kErrorNotSupported;

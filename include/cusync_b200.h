@@ -209,6 +209,10 @@ typedef struct cusync_gemm_desc {
   int32_t epilogue;
   int32_t tile_n;                  /* 0 = choose; else 32, 64, 128 or 256.  Tile M is 128. */
   int32_t max_ctas;                /* 0 = one per SM */
+  int32_t split_k;                 /* K slices per output tile (the stage grid's z): 0 = choose, 1 = none.  Slices add
+                                      their parts into an fp32 workspace owned by the plan; the last one to arrive applies
+                                      the epilogue, stores and posts (serial split-K of gemm/kernel/cusyncgemm.h:374-392,
+                                      without its ordering of the slices).  Not with CUSYNC_EPILOGUE_SILU_MUL_DUAL. */
   int32_t cta_pair;                /* 0 = choose; 1 = one CTA per 128 x tile_n tile; 2 = CTA pairs (tcgen05
                                       cta_group::2): two CTAs share a 256 x 256 tile, each loading half of B.
                                       Needs tile_n 256 and a single B operand.  Semaphores stay per 128-row tile. */
@@ -222,6 +226,9 @@ typedef struct cusync_gemm_plan cusync_gemm_plan_t;
  * CuSyncGemmHorizontalThreadblockSwizzle::get_tiled_shape does
  * (gemm/threadblock/cusync_threadblock_swizzle.h:12-54). */
 CUSYNC_API int cusync_gemm_default_tile_n(int32_t m, int32_t n, int32_t k, int32_t epilogue);
+/* K slices the library would pick (get_tiled_shape's third component); tile_n 0 and cta_pair 0 = its own choice. */
+CUSYNC_API int cusync_gemm_default_split_k(int32_t m, int32_t n, int32_t k, int32_t epilogue, int32_t tile_n,
+                                           int32_t cta_pair);
 
 /* can_implement + get_workspace_size + initialize
  * (gemm/device/cusyncgemm.h:364-456). */
@@ -281,6 +288,7 @@ typedef struct cusync_mlp_desc {
   int32_t policy;                /* CUSYNC_POLICY_ROWSYNC or CUSYNC_POLICY_TILESYNC between the two GEMMs */
   int32_t opts;                  /* CUSYNC_OPT_* applied to both stages */
   int32_t tile_n1, tile_n2;      /* 0 = choose */
+  int32_t split_k1, split_k2;    /* 0 = choose (mlp.cu's --split-k1 / --split-k2) */
   int32_t max_ctas;              /* 0 = one per SM */
   int32_t cta_pair;              /* as cusync_gemm_desc_t.cta_pair, for both GEMMs */
   int32_t group_rows2;           /* > 0: the consumer takes its tiles in CUSYNC_ORDER_GROUPED(group_rows2) order */
@@ -311,8 +319,8 @@ CUSYNC_API int cusync_mlp_update_io(cusync_mlp_t* mlp, const void* x, void* y);
 CUSYNC_API cusync_stage_t* cusync_mlp_stage(cusync_mlp_t* mlp, int which);
 /* Timeline buffers for the two synchronised GEMMs (see cusync_gemm_plan_set_trace). */
 CUSYNC_API int cusync_mlp_set_trace(cusync_mlp_t* mlp, void* trace1, uint32_t capacity1, void* trace2, uint32_t capacity2);
-/* Tile widths and block counts in use: out[0..3] = tile_n1, tile_n2, ctas1, ctas2. */
-CUSYNC_API int cusync_mlp_config(const cusync_mlp_t* mlp, int32_t* out4);
+/* Configuration in use: out[0..5] = tile_n1, tile_n2, ctas1, ctas2, split_k1, split_k2. */
+CUSYNC_API int cusync_mlp_config(const cusync_mlp_t* mlp, int32_t* out6);
 
 /* Library / device information. */
 CUSYNC_API const char* cusync_b200_version(void);

@@ -26,7 +26,7 @@ def _rand(shape, seed, scale=1.0, dist="uniform"):
 
 
 def _gemm(a, b, epi=L.EPILOGUE_NONE, tile_n=0, b_layout=L.B_ROW_MAJOR_KN, max_ctas=0, b2=None, stage=None,
-          cta_pair=0):
+          cta_pair=0, split_k=1, runs=1):
     M, K = a.shape
     N = b.shape[1]
     d = torch.full((M, N), float("nan"), device="cuda", dtype=torch.half)
@@ -37,10 +37,13 @@ def _gemm(a, b, epi=L.EPILOGUE_NONE, tile_n=0, b_layout=L.B_ROW_MAJOR_KN, max_ct
         bdev, b2dev = b, b2
     g = cs.Gemm()
     rc = g.initialize(cs.GemmArguments(stage, (M, N, K), a, bdev, d, epilogue=epi, ref_b2=b2dev, b_layout=b_layout,
-                                       tile_n=tile_n, max_ctas=max_ctas, cta_pair=cta_pair))
+                                       tile_n=tile_n, max_ctas=max_ctas, cta_pair=cta_pair,
+                                       split_k_slices=split_k))
     assert rc == L.SUCCESS, L.ERROR_NAMES[rc]
-    assert g.run(stream=torch.cuda.current_stream()) == L.SUCCESS
-    torch.cuda.synchronize()
+    for _ in range(runs):
+        d.fill_(float("nan"))
+        assert g.run(stream=torch.cuda.current_stream()) == L.SUCCESS
+        torch.cuda.synchronize()
     n = g.num_ctas()
     g.destroy()
     return d, n
@@ -111,7 +114,7 @@ def test_cta_pair_gemm_epilogue_and_few_clusters():
     d = torch.empty((1024, 2048), device="cuda", dtype=torch.half)
     g = cs.Gemm()
     assert g.initialize(cs.GemmArguments(None, (1024, 2048, 512), a, b, d, epilogue=L.EPILOGUE_GELU_ERF, tile_n=256,
-                                         max_ctas=6, cta_pair=2)) == L.SUCCESS
+                                         max_ctas=6, cta_pair=2, split_k_slices=1)) == L.SUCCESS
     assert g.num_ctas() == 6
     for _ in range(3):
         d.fill_(float("nan"))
@@ -137,6 +140,74 @@ def test_cta_pair_refuses_what_it_cannot_do():
                                          tile_n=256, cta_pair=2)) == L.ERROR_UNSUPPORTED
 
 
+@pytest.mark.parametrize("M,N,K,tile_n,split,pair", [
+    (1, 1024, 4096, 256, 4, 1),       # decode batch 1: one row, four K slices per tile
+    (64, 1536, 6144, 256, 0, 1),      # slices chosen by the library
+    (100, 1000, 2048 + 64, 128, 3, 1),  # ragged N, K not a multiple of the slices
+    (128, 512, 2048, 64, 2, 1),
+    (256, 512, 4096, 256, 4, 2),      # CTA pairs with split-K
+    (384, 768, 3072, 256, 3, 2),      # odd row-tile count: the last pair's second CTA only keeps the barriers going
+])
+@pytest.mark.parametrize("epi,oepi", [(L.EPILOGUE_NONE, o.EPI_NONE), (L.EPILOGUE_GELU_ERF, o.EPI_GELU_ERF)])
+def test_split_k_gemm_matches_oracle(M, N, K, tile_n, split, pair, epi, oepi):
+    a = _rand((M, K), 60, dist="normal")
+    b = _rand((K, N), 61, scale=0.03, dist="normal")
+    # three runs on one plan: the workspace and the slice counters must come back to zero by themselves
+    d, _ = _gemm(a, b, epi=epi, tile_n=tile_n, cta_pair=pair, split_k=split, runs=3)
+    ref = o.gemm_f16(a.cpu().numpy(), b.cpu().numpy(), oepi)
+    assert o.max_rel_err(d.cpu().numpy(), ref) <= TOL
+
+
+def test_split_k_defaults_and_limits():
+    assert cs.Gemm.default_split_k(64, 6144, 12288, L.EPILOGUE_GELU_ERF) >= 2
+    assert cs.Gemm.default_split_k(2048, 6144, 12288, L.EPILOGUE_GELU_ERF) == 1
+    assert cs.Gemm.default_split_k(64, 2752, 8192, L.EPILOGUE_SILU_MUL_DUAL) == 1
+    a = _rand((64, 4096), 62); b = _rand((4096, 256), 63)
+    d = torch.empty((64, 256), device="cuda", dtype=torch.half)
+    g = cs.Gemm()
+    assert g.initialize(cs.GemmArguments(None, (64, 256, 4096), a, b, d, epilogue=L.EPILOGUE_SILU_MUL_DUAL, ref_b2=b,
+                                         tile_n=64, split_k_slices=2)) == L.ERROR_UNSUPPORTED
+
+
+def test_chain_with_split_k_on_both_gemms():
+    # one row of tiles (M = 96): producer 4 column tiles x 3 K slices, consumer 2 column tiles x 2 K slices.
+    # Only the block that brings a tile's last slice posts, so every semaphore still counts one per run.
+    M, K1, N1, N2 = 96, 3072, 1024, 512
+    a = _rand((M, K1), 70, dist="normal")
+    w1 = _rand((K1, N1), 71, scale=0.03, dist="normal")
+    w2 = _rand((N1, N2), 72, scale=0.03, dist="normal")
+    h = torch.empty((M, N1), device="cuda", dtype=torch.half)
+    y = torch.empty((M, N2), device="cuda", dtype=torch.half)
+    for policy in ("row", "tile"):
+        grid1, grid2 = (4, 1, 3), (2, 1, 2)
+        sync = cs.RowSync(128, 4) if policy == "row" else cs.TileSync(cs.TransposeXYOrder, 128, 256)
+        prod = cs.CuStage(cs.TransposeXYOrder, grid1, (1, 1, 1), cs.NoSync(), sync)
+        cons = cs.CuStage(cs.TransposeXYOrder, grid2, (1, 1, 1), sync, cs.NoSync())
+        assert cs.CuSync.setProducerConsumerPair(prod, cons) == L.SUCCESS
+        g1, g2 = cs.Gemm(), cs.Gemm()
+        assert g1.initialize(cs.GemmArguments(prod, (M, N1, K1), a, w1, h, epilogue=L.EPILOGUE_GELU_ERF, tile_n=256,
+                                              split_k_slices=3)) == L.SUCCESS
+        assert g2.initialize(cs.GemmArguments(cons, (M, N2, N1), h, w2, y, tile_n=256, split_k_slices=2)) == L.SUCCESS
+        ps, cst = torch.cuda.Stream(priority=-1), torch.cuda.Stream()
+        href = o.gemm_f16(a.cpu().numpy(), w1.cpu().numpy(), o.EPI_GELU_ERF)
+        yref = o.gemm_f16(href, w2.cpu().numpy())
+        torch.cuda.synchronize()
+        for it in range(1, 4):
+            h.fill_(float("nan")); y.fill_(float("nan")); torch.cuda.synchronize()
+            g1.run(True, None, ps); prod.invokeWaitKernel(cst); g2.run(True, None, cst)
+            torch.cuda.synchronize()
+            assert prod.status().code == 0 and cons.status().code == 0
+            assert o.max_rel_err(h.cpu().numpy(), href) <= TOL
+            assert o.max_rel_err(y.cpu().numpy(), yref) <= TOL
+            sems = prod.semaphores()
+            if policy == "row":
+                assert sems[0] == 4 * it and (sems[1:] == 0).all()
+            else:
+                assert (sems[:4] == it).all() and (sems[4:] == 0).all()
+            prod.incrementIter(); cons.incrementIter()
+        g1.destroy(); g2.destroy(); prod.destroy(); cons.destroy()
+
+
 def test_persistent_scheduler_with_few_blocks_and_repeated_runs():
     # 64 tiles on 3 blocks: every block loops over many tickets; the ticket counter must re-arm itself.
     a = _rand((1024, 512), 8)
@@ -144,7 +215,7 @@ def test_persistent_scheduler_with_few_blocks_and_repeated_runs():
     ref = o.gemm_f16(a.cpu().numpy(), b.cpu().numpy())
     d = torch.empty((1024, 1024), device="cuda", dtype=torch.half)
     g = cs.Gemm()
-    assert g.initialize(cs.GemmArguments(None, (1024, 1024, 512), a, b, d, tile_n=128, max_ctas=3)) == L.SUCCESS
+    assert g.initialize(cs.GemmArguments(None, (1024, 1024, 512), a, b, d, tile_n=128, max_ctas=3, split_k_slices=1)) == L.SUCCESS
     assert g.num_ctas() == 3
     for _ in range(3):
         d.fill_(float("nan"))
@@ -195,9 +266,9 @@ def _chain(policy_name, M, N1, K1, N2, tile_n1, tile_n2, iters, opts=0, epi1=L.E
     assert cs.CuSync.setProducerConsumerPair(prod, cons) == L.SUCCESS
     g1, g2 = cs.Gemm(), cs.Gemm()
     assert g1.initialize(cs.GemmArguments(prod, (M, N1, K1), a, w1, h, epilogue=epi1, tile_n=tile_n1,
-                                          max_ctas=max_ctas, cta_pair=cta_pair)) == L.SUCCESS
+                                          max_ctas=max_ctas, cta_pair=cta_pair, split_k_slices=1)) == L.SUCCESS
     assert g2.initialize(cs.GemmArguments(cons, (M, N2, N1), h, w2, y, tile_n=tile_n2, max_ctas=max_ctas,
-                                          cta_pair=cta_pair)) == L.SUCCESS
+                                          cta_pair=cta_pair, split_k_slices=1)) == L.SUCCESS
     ps, cst = torch.cuda.Stream(priority=-1), torch.cuda.Stream()
     oepi = {L.EPILOGUE_NONE: o.EPI_NONE, L.EPILOGUE_GELU_ERF: o.EPI_GELU_ERF}[epi1]
     href = o.gemm_f16(a.cpu().numpy(), w1.cpu().numpy(), oepi)
@@ -242,8 +313,8 @@ def test_config1_two_dependent_gemms(policy):
     cons = cs.CuStage(cs.TransposeXYOrder, grid, (1, 1, 1), sync, cs.NoSync())
     assert cs.CuSync.setProducerConsumerPair(prod, cons) == L.SUCCESS
     g1, g2 = cs.Gemm(), cs.Gemm()
-    assert g1.initialize(cs.GemmArguments(prod, (M, 1024, 1024), a, b, c, tile_n=128)) == L.SUCCESS
-    assert g2.initialize(cs.GemmArguments(cons, (M, 1024, 1024), c, dd, e, tile_n=128)) == L.SUCCESS
+    assert g1.initialize(cs.GemmArguments(prod, (M, 1024, 1024), a, b, c, tile_n=128, split_k_slices=1)) == L.SUCCESS
+    assert g2.initialize(cs.GemmArguments(cons, (M, 1024, 1024), c, dd, e, tile_n=128, split_k_slices=1)) == L.SUCCESS
     ps, cst = torch.cuda.Stream(priority=-1), torch.cuda.Stream()
     cref = o.gemm_f16(a.cpu().numpy(), b.cpu().numpy())
     eref = o.gemm_f16(cref, dd.cpu().numpy())
@@ -304,7 +375,7 @@ def test_consumer_times_out_instead_of_hanging():
     assert cs.CuSync.setProducerConsumerPair(prod, cons) == L.SUCCESS
     cons.set_timeout_ns(30e6)
     g = cs.Gemm()
-    assert g.initialize(cs.GemmArguments(cons, (M, N, K), a, b, d, tile_n=128)) == L.SUCCESS
+    assert g.initialize(cs.GemmArguments(cons, (M, N, K), a, b, d, tile_n=128, split_k_slices=1)) == L.SUCCESS
     assert g.run(stream=torch.cuda.current_stream()) == L.SUCCESS
     torch.cuda.synchronize()      # returns: no hang
     st = cons.status()
@@ -314,7 +385,7 @@ def test_consumer_times_out_instead_of_hanging():
     # after reset the pair works: run the producer-side post by hand via a real producer GEMM
     x = _rand((M, 64), 32); w = _rand((64, 256), 33)
     g1 = cs.Gemm()
-    assert g1.initialize(cs.GemmArguments(prod, (M, 256, 64), x, w, a, tile_n=128)) == L.SUCCESS
+    assert g1.initialize(cs.GemmArguments(prod, (M, 256, 64), x, w, a, tile_n=128, split_k_slices=1)) == L.SUCCESS
     s2 = torch.cuda.Stream()
     g1.run(stream=torch.cuda.current_stream()); prod.invokeWaitKernel(s2); g.run(stream=s2)
     torch.cuda.synchronize()
@@ -329,10 +400,10 @@ def test_stage_grid_must_match_the_tile_grid():
     d = torch.empty((256, 256), device="cuda", dtype=torch.half)
     st = cs.CuStage(cs.TransposeXYOrder, (3, 2, 1), (1, 1, 1), cs.NoSync(), cs.TileSync(cs.TransposeXYOrder, 128, 128))
     g = cs.Gemm()
-    assert g.initialize(cs.GemmArguments(st, (256, 256, 256), a, b, d, tile_n=128)) == L.ERROR_INVALID_ARGUMENT
+    assert g.initialize(cs.GemmArguments(st, (256, 256, 256), a, b, d, tile_n=128, split_k_slices=1)) == L.ERROR_INVALID_ARGUMENT
     # an unlinked consumer is refused too
     c = cs.CuStage(cs.TransposeXYOrder, (2, 2, 1), (1, 1, 1), cs.TileSync(cs.TransposeXYOrder, 128, 128), cs.NoSync())
-    assert g.initialize(cs.GemmArguments(c, (256, 256, 256), a, b, d, tile_n=128)) == L.ERROR_NOT_INITIALIZED
+    assert g.initialize(cs.GemmArguments(c, (256, 256, 256), a, b, d, tile_n=128, split_k_slices=1)) == L.ERROR_NOT_INITIALIZED
     st.destroy(); c.destroy()
 
 
