@@ -111,6 +111,13 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void*
                "r"(smem_u32(src)), "r"(c0), "r"(c1)
                : "memory");
 }
+// Element-wise add of a shared-memory box into global memory, done by the TMA unit at the L2.
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, const void* src, int c0, int c1) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(smem_u32(src)), "r"(c0), "r"(c1)
+               : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void tma_store_wait_read() {
@@ -336,31 +343,33 @@ __device__ __forceinline__ void epilogue_store_rows(const GemmParams& p, const C
 }
 
 
-__device__ __forceinline__ void red_add_v4_f32(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
-
-// Split-K, phase 1: one warp adds its 32 accumulator rows (every second 64-column chunk from `half`)
-// into the fp32 workspace.  Rows and columns outside the matrix are skipped.
+// Split-K, phase 1: one warp adds its 32 accumulator rows (every second 64-column span from `half`, in two
+// 32-column boxes) into the fp32 workspace: tcgen05.ld -> swizzled staging buffer -> TMA reduce-add.  The
+// workspace map covers exactly m rows and n columns, so padding rows and columns are clipped by the TMA.
 template <int BN>
-__device__ __forceinline__ void splitk_accumulate_rows(const GemmParams& p, uint32_t t_row, int n_off, int row0,
-                                                       int half, int lane) {
-  const int row = row0 + lane;
+__device__ __forceinline__ void splitk_accumulate_rows(const GemmParams& p, const CUtensorMap* tmWS, uint8_t* buf,
+                                                       uint32_t t_row, int n_off, int row0, int half, int lane) {
+  if (row0 >= p.m) return;
 #pragma unroll 1
   for (int c = half; c < BN / kStoreCols; c += 2) {
-    const int col0 = n_off + c * kStoreCols;
-    if (col0 >= p.n || row0 >= p.m) break;
-    uint32_t v[64];
-    tmem_ld_32x32b_x32(t_row + c * 64, v);
-    tmem_ld_32x32b_x32(t_row + c * 64 + 32, v + 32);
-    tmem_ld_wait();
-    if (row < p.m) {
-      float* dst = p.splitk_ws + static_cast<size_t>(row) * p.n + col0;
+#pragma unroll 1
+    for (int h = 0; h < 2; h++) {
+      const int col0 = n_off + c * kStoreCols + h * 32;
+      if (col0 >= p.n) return;
+      if (lane == 0) tma_store_wait_read<0>();     // the previous box has left this warp's staging buffer
+      __syncwarp();
+      uint32_t v[32];
+      tmem_ld_32x32b_x32(t_row + c * 64 + h * 32, v);
+      tmem_ld_wait();
+      uint8_t* row = buf + lane * 128;             // 32 fp32 = 128 bytes per row, 16-byte pieces XOR-swizzled
 #pragma unroll
-      for (int j = 0; j < 16; j++) {
-        if (col0 + 4 * j < p.n)      // n is a multiple of 8, so groups of four never straddle the edge
-          red_add_v4_f32(dst + 4 * j, __uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
-                         __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+      for (int q = 0; q < 8; q++)
+        *reinterpret_cast<uint4*>(row + ((q ^ (lane & 7)) << 4)) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tma_reduce_add_2d(tmWS, buf, col0, row0);
+        tma_store_commit();
       }
     }
   }
@@ -373,17 +382,32 @@ __device__ __forceinline__ void splitk_finalize_tile(const GemmParams& p, __half
                                                      int tid) {
   const int rows = p.m - m_off < kBlockM ? p.m - m_off : kBlockM;
   constexpr int kVecPerRow = BN / 4;
-  for (int i = tid; i < rows * kVecPerRow; i += kEpilogueWarps * 32) {
-    const int r = i / kVecPerRow, c = (i % kVecPerRow) * 4;
-    const int col = n_off + c;
-    if (col >= p.n) continue;
-    float4* src = reinterpret_cast<float4*>(p.splitk_ws + static_cast<size_t>(m_off + r) * p.n + col);
-    float4 x = __ldcg(src);
-    __stcg(src, make_float4(0.f, 0.f, 0.f, 0.f));
-    if (p.epilogue == CUSYNC_EPILOGUE_GELU_ERF) { x.x = gelu_erf(x.x); x.y = gelu_erf(x.y); x.z = gelu_erf(x.z); x.w = gelu_erf(x.w); }
-    else if (p.epilogue == CUSYNC_EPILOGUE_RELU) { x.x = fmaxf(x.x, 0.f); x.y = fmaxf(x.y, 0.f); x.z = fmaxf(x.z, 0.f); x.w = fmaxf(x.w, 0.f); }
-    uint2 out = make_uint2(pack_half2(x.x, x.y), pack_half2(x.z, x.w));
-    *reinterpret_cast<uint2*>(d + static_cast<size_t>(m_off + r) * ldd + col) = out;
+  constexpr int kThreadsE = kEpilogueWarps * 32;
+  constexpr int kBatch = 8;                 // loads in flight per thread: the reads are L2 round trips
+  const int total = rows * kVecPerRow;
+  for (int base = tid; base < total; base += kThreadsE * kBatch) {
+    float4 x[kBatch];
+    float4* src[kBatch];
+#pragma unroll
+    for (int j = 0; j < kBatch; j++) {
+      const int i = base + j * kThreadsE;
+      const int r = i / kVecPerRow, c = (i % kVecPerRow) * 4;
+      const bool in = i < total && n_off + c < p.n;
+      src[j] = in ? reinterpret_cast<float4*>(p.splitk_ws + static_cast<size_t>(m_off + r) * p.n + n_off + c) : nullptr;
+      if (in) x[j] = __ldcg(src[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < kBatch; j++) {
+      if (src[j] == nullptr) continue;
+      const int i = base + j * kThreadsE;
+      const int r = i / kVecPerRow, c = (i % kVecPerRow) * 4;
+      __stcg(src[j], make_float4(0.f, 0.f, 0.f, 0.f));
+      float4 v = x[j];
+      if (p.epilogue == CUSYNC_EPILOGUE_GELU_ERF) { v.x = gelu_erf(v.x); v.y = gelu_erf(v.y); v.z = gelu_erf(v.z); v.w = gelu_erf(v.w); }
+      else if (p.epilogue == CUSYNC_EPILOGUE_RELU) { v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f); v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f); }
+      *reinterpret_cast<uint2*>(d + static_cast<size_t>(m_off + r) * ldd + n_off + c) =
+          make_uint2(pack_half2(v.x, v.y), pack_half2(v.z, v.w));
+    }
   }
 }
 
@@ -391,17 +415,19 @@ __device__ __forceinline__ void splitk_finalize_tile(const GemmParams& p, __half
 // Every slice adds its part; the block that counts the last arrival finalises and publishes the tile
 // (the reference posts from the last K slice only, gemm/kernel/cusyncgemm.h:374-392).
 template <int BN>
-__device__ __forceinline__ bool splitk_epilogue(const GemmParams& p, Barriers* bars, const WaitCtx& ctx, uint32_t t_row,
+__device__ __forceinline__ bool splitk_epilogue(const GemmParams& p, const CUtensorMap* tmWS, uint8_t* buf,
+                                                Barriers* bars, const WaitCtx& ctx, uint32_t t_row,
                                                 int n_off, int m_off, int quarter, int half, int ew, int lane,
                                                 uint32_t phase, uint64_t* tmem_empty_local, uint32_t tmem_empty_cluster,
                                                 __half* d, int64_t ldd, bool* is_last) {
-  splitk_accumulate_rows<BN>(p, t_row, n_off, m_off + quarter * 32, half, lane);
+  splitk_accumulate_rows<BN>(p, tmWS, buf, t_row, n_off, m_off + quarter * 32, half, lane);
   // accumulator buffer is free for the MMA warp again
   tc_fence_before();
   __syncwarp();
   if (lane == 0) {
     if (tmem_empty_local) mbar_arrive(tmem_empty_local); else mbar_arrive_cluster(tmem_empty_cluster);
-    __threadfence();                 // this warp's adds are ordered before the arrival count
+    tma_store_wait_all();            // this warp's reduce-adds have been performed ...
+    __threadfence();                 // ... and are ordered before the arrival count
     mbar_arrive(&bars->post);
   }
   bool ok = true;
@@ -436,7 +462,7 @@ template <int BN, bool DUAL>
 __global__ void __launch_bounds__(kThreads, 1)
 cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                    const __grid_constant__ CUtensorMap tmB2, const __grid_constant__ CUtensorMap tmD,
-                   const GemmParams p) {
+                   const __grid_constant__ CUtensorMap tmWS, const GemmParams p) {
   using C = Cfg<BN, DUAL>;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzle patterns repeat every 1024 bytes: align the ring to that.
@@ -722,7 +748,7 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       if (!DUAL && p.split_k > 1) {
         // Split-K: add this slice's part; the block that brings the last slice finalises and posts.
         bool last = false;
-        ok = splitk_epilogue<BN>(p, bars, ctx, t_row, n_off, m_off, quarter, half, ew, lane, post_it & 1u,
+        ok = splitk_epilogue<BN>(p, &tmWS, buf, bars, ctx, t_row, n_off, m_off, quarter, half, ew, lane, post_it & 1u,
                                  &bars->tmem_empty[acc], 0u, static_cast<__half*>(p.d), p.ldd, &last);
         acc_it++;
         if (ew == 0 && lane == 0) {
@@ -918,7 +944,8 @@ struct PairCfg {
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                        const __grid_constant__ CUtensorMap tmD, const GemmParams p) {
+                        const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmWS,
+                        const GemmParams p) {
   using C = PairCfg;
   constexpr int BN = kPairBN;
   extern __shared__ uint8_t smem_raw[];
@@ -1222,7 +1249,7 @@ cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
 
       if (p.split_k > 1) {
         bool last = false;
-        ok = splitk_epilogue<BN>(p, bars, ctx, t_row, n_off, m_off, quarter, half, ew, lane, post_it & 1u, nullptr,
+        ok = splitk_epilogue<BN>(p, &tmWS, buf, bars, ctx, t_row, n_off, m_off, quarter, half, ew, lane, post_it & 1u, nullptr,
                                  leader_tmem_empty0 + acc * 8, static_cast<__half*>(p.d), p.ldd, &last);
         acc_it++;
         if (ew == 0 && lane == 0) {
@@ -1343,7 +1370,22 @@ bool make_map_chunked(CUtensorMap* out, const void* base, uint64_t k, uint64_t n
   return r == CUDA_SUCCESS;
 }
 
-typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const GemmParams);
+// fp32 workspace of split-K: [rows, cols] row-major, boxes of 32 columns (128 bytes) x 32 rows.
+bool make_map_f32(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * 4};
+  cuuint32_t box[2] = {32, 32};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap,
+                         const GemmParams);
 
 struct KernelEntry { KernelFn fn; uint32_t smem; };
 
@@ -1370,7 +1412,7 @@ bool select_kernel(int tile_n, bool dual, KernelEntry* out) {
 
 struct cusync_gemm_plan {
   cusync_gemm_desc_t desc;
-  CUtensorMap tmA, tmB, tmB2, tmD;
+  CUtensorMap tmA, tmB, tmB2, tmD, tmWS;
   GemmParams params;
   KernelEntry kernel;
   int tile_n;
@@ -1393,11 +1435,20 @@ int auto_split_k(int m, int n, int k, int tile_n, bool dual, bool pair, int sms)
   const int tiles_n = (n + tile_n - 1) / tile_n, tiles_m = (m + kBlockM - 1) / kBlockM;
   const int units = pair ? tiles_n * ((tiles_m + 1) / 2) : tiles_n * tiles_m;
   const int capacity = pair ? sms / 2 : sms;
-  int split = capacity / units;
-  const int max_by_k = k / 1024;
-  if (split > max_by_k) split = max_by_k;
-  if (split > 16) split = 16;
-  return split < 1 ? 1 : split;
+  // Worth its fp32 workspace traffic only while the tile grid leaves more than half of the machine idle.
+  if (2 * units > capacity) return 1;
+  int max_split = k / 1024;
+  if (max_split > 16) max_split = 16;
+  // rounds of work units the machine runs, in units of an unsplit tile's time, plus a few per cent per extra
+  // slice for the workspace traffic
+  int best = 1;
+  double best_cost = 1e30;
+  for (int split = 1; split <= max_split; split++) {
+    const int rounds = (units * split + capacity - 1) / capacity;
+    const double cost = static_cast<double>(rounds) / split * (1.0 + 0.04 * (split - 1));
+    if (cost < best_cost - 1e-9) { best_cost = cost; best = split; }
+  }
+  return best;
 }
 
 // Whether cusync_gemm_plan_create picks the CTA-pair kernel when the caller leaves the choice open.
@@ -1622,7 +1673,7 @@ extern "C" int cusync_gemm_run_noalloc(const cusync_gemm_desc_t* desc, cusync_st
   const uint32_t prep_threads = p.num_tiles > 64 ? static_cast<uint32_t>(p.num_tiles) : 64u;
   noalloc_prepare_kernel<<<(prep_threads + 255) / 256, 256, 0, st>>>(static_cast<uint32_t>(p.tiles_n),
                                                                      static_cast<uint32_t>(p.num_tiles));
-  pl.kernel.fn<<<ctas, kThreads, pl.kernel.smem, st>>>(pl.tmA, pl.tmB, pl.tmB2, pl.tmD, p);
+  pl.kernel.fn<<<ctas, kThreads, pl.kernel.smem, st>>>(pl.tmA, pl.tmB, pl.tmB2, pl.tmD, pl.tmD, p);
   return cudaGetLastError() == cudaSuccess ? CUSYNC_SUCCESS : CUSYNC_ERROR_CUDA;
 }
 
@@ -1754,6 +1805,7 @@ int cusync_gemm_plan_create(cusync_gemm_plan_t** out, const cusync_gemm_desc_t* 
     }
     p.splitk_ws = pl->splitk_ws;
     p.splitk_arrivals = pl->splitk_arrivals;
+    if (rc == CUSYNC_SUCCESS && !make_map_f32(&pl->tmWS, pl->splitk_ws, d.m, d.n, d.n)) rc = CUSYNC_ERROR_CUDA;
   }
   const void* kernel_fn = pl->pair ? reinterpret_cast<const void*>(cusync_gemm_pair_kernel)
                                    : reinterpret_cast<const void*>(pl->kernel.fn);
@@ -1811,10 +1863,10 @@ int cusync_gemm_run(cusync_gemm_plan_t* pl, cusync_stream_t stream) {
   if (p.is_producer) cusync_stage_note_launch(pl->stage, pl->num_ctas);
   if (pl->pair)
     cusync_gemm_pair_kernel<<<pl->num_ctas, kThreads, pl->kernel.smem, reinterpret_cast<cudaStream_t>(stream)>>>(
-        pl->tmA, pl->tmB, pl->tmD, p);
+        pl->tmA, pl->tmB, pl->tmD, pl->tmWS, p);
   else
     pl->kernel.fn<<<pl->num_ctas, kThreads, pl->kernel.smem, reinterpret_cast<cudaStream_t>(stream)>>>(
-        pl->tmA, pl->tmB, pl->tmB2, pl->tmD, p);
+        pl->tmA, pl->tmB, pl->tmB2, pl->tmD, pl->tmWS, p);
   return cudaGetLastError() == cudaSuccess ? CUSYNC_SUCCESS : CUSYNC_ERROR_CUDA;
 }
 
