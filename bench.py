@@ -135,7 +135,9 @@ def workload_config(args, shard):
            "all_reduce": "NCCL sum of Y[B,12288] fp16 across ranks" if args.gpus > 1 else "none (1 GPU)"}
     if shard is not None:
         cfg.update({"tile_m": 128, "tile_n1": shard.tile_n1, "tile_n2": shard.tile_n2,
-                    "ctas1": shard.ctas1, "ctas2": shard.ctas2})
+                    "ctas1": shard.ctas1, "ctas2": shard.ctas2, "split_k1": shard.split_k1, "split_k2": shard.split_k2,
+                    "kernel": "CTA pairs (tcgen05 cta_group::2), 256x256 tile per pair" if args.batch > 128
+                              else "one CTA per 128x256 tile"})
     return cfg
 
 
@@ -195,6 +197,7 @@ def main():
     dev = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # keep stdout to the one JSON line
         dist.init_process_group("nccl", device_id=dev)
 
     def barrier():
@@ -283,7 +286,8 @@ def main():
             g1.append(e0.elapsed_time(e1)); g2.append(e1.elapsed_time(e2))
     t1_ms, t2_ms = statistics.mean(g1), statistics.mean(g2)
     tensor_bound = args.batch >= 256
-    kernel_name = "cusync_gemm_kernel<%d> (GEMM2, the consumer)" % shard.tile_n2
+    kernel_name = ("cusync_gemm_pair_kernel (GEMM2, the consumer)" if args.batch > 128
+                   else "cusync_gemm_kernel<%d,0> (GEMM2, the consumer)" % shard.tile_n2)
     if tensor_bound:
         achieved = flops2 / (t2_ms * 1e-3) / 1e12
         peak = peaks["tflops_sustained"]
@@ -341,6 +345,7 @@ def main():
                 row[pol + "_stream_ordered_us"] = round(o_us, 2)
                 row[pol + "_gain_pct"] = round(100.0 - c_us / o_us * 100.0, 2)
                 row["tile_n"] = [s.tile_n1, s.tile_n2]
+                row["split_k"] = [s.split_k1, s.split_k2]
                 if s.status_codes() != (0, 0):
                     row["error"] = "bounded wait expired"
                 s.destroy()
