@@ -6,5 +6,5 @@ from . import _lib
 from ._lib import CuSyncError, CuSyncLibraryError  # noqa: F401
 from .api import (CuStage, CuSync, NoSync, RowSync, TileSync, StridedTileSync, Conv2DTileSync,  # noqa: F401
                   ConsecutiveTileSync, IdentityOrder, TransposeXYOrder, GroupedRowsOrder, Optimizations, Gemm, GemmArguments,
-                  gemm_tiled_shape)
+                  gemm_tiled_shape, Conv2dFprop, Conv2dProblemSize)
 from .mlp import MLPShard, make_inputs  # noqa: F401,E402

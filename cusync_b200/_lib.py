@@ -64,6 +64,13 @@ class GemmDesc(C.Structure):
                 ("split_k", C.c_int32), ("cta_pair", C.c_int32), ("stage", C.c_void_p)]
 
 
+class Conv2dDesc(C.Structure):
+    _fields_ = [("n", C.c_int32), ("h", C.c_int32), ("w", C.c_int32), ("c", C.c_int32), ("k", C.c_int32),
+                ("r", C.c_int32), ("s", C.c_int32), ("stride", C.c_int32), ("pad", C.c_int32),
+                ("x", C.c_void_p), ("filter", C.c_void_p), ("y", C.c_void_p),
+                ("epilogue", C.c_int32), ("max_ctas", C.c_int32), ("stage", C.c_void_p)]
+
+
 class MlpDesc(C.Structure):
     _fields_ = [("model", C.c_int32), ("batch", C.c_int32), ("hidden", C.c_int32), ("ffn", C.c_int32),
                 ("policy", C.c_int32), ("opts", C.c_int32), ("tile_n1", C.c_int32), ("tile_n2", C.c_int32),
@@ -103,6 +110,11 @@ SIGNATURES = {
     "cusync_gemm_run_noalloc": (_i, [C.POINTER(GemmDesc), _vp]),
     "cusync_gemm_plan_set_trace": (_i, [_vp, _vp, _u32]),
     "cusync_gemm_plan_num_ctas": (_u32, [_vp]),
+    "cusync_conv2d_tile_rows": (_i, [C.c_int32]),
+    "cusync_conv2d_plan_create": (_i, [C.POINTER(_vp), C.POINTER(Conv2dDesc)]),
+    "cusync_conv2d_plan_destroy": (_i, [_vp]),
+    "cusync_conv2d_run": (_i, [_vp, _vp]),
+    "cusync_conv2d_plan_num_ctas": (_u32, [_vp]),
     "cusync_mlp_create": (_i, [C.POINTER(_vp), C.POINTER(MlpDesc)]),
     "cusync_mlp_destroy": (_i, [_vp]),
     "cusync_mlp_run_stream_ordered": (_i, [_vp, _vp]),

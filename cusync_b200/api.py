@@ -279,3 +279,47 @@ class Gemm:
         if self._plan:
             L.lib().cusync_gemm_plan_destroy(self._plan)
             self._plan = C.c_void_p()
+
+
+class Conv2dProblemSize:
+    """cutlass::conv::Conv2dProblemSize as resnet.cu builds it: input NHWC, filter KRSC, stride 1, pad 1."""
+
+    def __init__(self, n, h, w, c, k, r=3, s=3, pad=1, stride=1):
+        self.n, self.h, self.w, self.c, self.k, self.r, self.s, self.pad, self.stride = n, h, w, c, k, r, s, pad, stride
+
+    def tile_rows(self):
+        return L.lib().cusync_conv2d_tile_rows(self.w)
+
+    def grid(self):
+        """Stage grid (N tiles, M tiles, 1) of the implicit GEMM."""
+        return (self.k // 64, self.n * self.h // max(self.tile_rows(), 1), 1)
+
+    def tile_m(self):
+        """Output pixels per M tile: the TileM argument of the sync policies."""
+        return self.tile_rows() * self.w
+
+
+class Conv2dFprop:
+    """cutlass::conv::device::CuSyncImplicitGemmConvolution's call pattern (Arguments -> can_implement ->
+    initialize -> run) on the sm_100a implicit-GEMM kernel."""
+
+    def __init__(self):
+        self._plan = C.c_void_p()
+
+    def initialize(self, custage, problem, x, filt, y, epilogue=L.EPILOGUE_NONE, max_ctas=0):
+        self.destroy()
+        d = L.Conv2dDesc(problem.n, problem.h, problem.w, problem.c, problem.k, problem.r, problem.s, problem.stride,
+                         problem.pad, x.data_ptr(), filt.data_ptr(), y.data_ptr(), epilogue, max_ctas,
+                         custage._h if custage is not None else None)
+        return L.lib().cusync_conv2d_plan_create(C.byref(self._plan), C.byref(d))
+
+    def run(self, stream=None):
+        return L.lib().cusync_conv2d_run(self._plan, _stream_ptr(stream))
+
+    def num_ctas(self):
+        return L.lib().cusync_conv2d_plan_num_ctas(self._plan)
+
+    def destroy(self):
+        if self._plan:
+            L.lib().cusync_conv2d_plan_destroy(self._plan)
+            self._plan = C.c_void_p()

@@ -99,6 +99,13 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2,
+                                            int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
 __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
   asm volatile(
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
@@ -203,6 +210,10 @@ struct GemmParams {
   int32_t k_blocks_per_split;      // ring stages per slice
   float* splitk_ws;                // fp32 [tiles_m * 128, n] partial sums, all zero between launches
   uint32_t* splitk_arrivals;       // per (m, n) tile: slices that have added their part
+  // 3x3 convolution as implicit GEMM (CONV kernels): NHWC input [conv_n, conv_h, conv_w, conv_c]; an M tile
+  // is conv_rows whole image rows (conv_rows * conv_w <= 128 output pixels); K walks channel chunks of 64
+  // outermost and the nine filter taps innermost.
+  int32_t conv_n, conv_h, conv_w, conv_c, conv_rows, conv_tiles_per_image;
   const cusync_dim3_t* pair_order; // CTA-pair kernel: schedule over 256-row pair tiles {n tile, pair row, 0}
   int32_t num_pairs;
   unsigned long long* trace;       // optional per-tile timeline: 4 words per ticket (see cusync_gemm_plan_set_trace)
@@ -458,7 +469,7 @@ __device__ __forceinline__ bool splitk_epilogue(const GemmParams& p, const CUten
 // ---------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------
-template <int BN, bool DUAL>
+template <int BN, bool DUAL, bool CONV = false>
 __global__ void __launch_bounds__(kThreads, 1)
 cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                    const __grid_constant__ CUtensorMap tmB2, const __grid_constant__ CUtensorMap tmD,
@@ -545,7 +556,10 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         if (!valid) break;
 
         const int n_off = static_cast<int>(t.x) * BN;
-        const int m_off = static_cast<int>(t.y) * kBlockM;
+        // Row offset of the tile: 128 matrix rows, or for a convolution conv_rows image rows of output pixels.
+        const int m_off = CONV ? static_cast<int>(t.y) * p.conv_rows * p.conv_w : static_cast<int>(t.y) * kBlockM;
+        const int img = CONV ? static_cast<int>(t.y) / p.conv_tiles_per_image : 0;
+        const int h0 = CONV ? (static_cast<int>(t.y) % p.conv_tiles_per_image) * p.conv_rows : 0;
         // K slice of this work unit (the whole K walk without split-K)
         const int kb_begin = static_cast<int>(t.z) * p.k_blocks_per_split;
         const int kb_end = kb_begin + p.k_blocks_per_split < p.num_k_blocks ? kb_begin + p.k_blocks_per_split
@@ -559,10 +573,17 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           if (p.trace) wait_empty += clock64() - c0;
           uint8_t* sa = ring + s * C::kStageBytes;
           uint8_t* sb = sa + C::kABytes;
-          mbar_expect_tx(&bars->full[s], C::kStageBytes);
+          // A convolution's A box holds conv_rows * conv_w pixel rows of 128 bytes, not the full 128.
+          mbar_expect_tx(&bars->full[s], CONV ? static_cast<uint32_t>(p.conv_rows * p.conv_w * 128 + C::kNumB * C::kBBytes)
+                                              : static_cast<uint32_t>(C::kStageBytes));
           const int k_off = kb * kBlockK;
+          // Convolution: K block kb is channel chunk kb / 9, filter tap (r, s) = kb % 9; the filter is
+          // [k_out][r][s][c], so its K offset is tap * C + chunk * 64.
+          const int tap = CONV ? kb % 9 : 0, chunk = CONV ? kb / 9 : 0;
           // Weights first: they never depend on the producer kernel.
-          if (p.b_kmajor) {
+          if (CONV) {
+            tma_load_2d(sb, &tmB, &bars->full[s], tap * p.conv_c + chunk * kBlockK, n_off);
+          } else if (p.b_kmajor) {
             tma_load_2d(sb, &tmB, &bars->full[s], k_off, n_off);
             if (DUAL) tma_load_2d(sb + C::kBBytes, &tmB2, &bars->full[s], k_off, n_off);
           } else if (p.b_chunked3d) {
@@ -595,7 +616,8 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                                       idx, seen, wait_target);
                 // The stage was armed: give it its A bytes anyway so the
                 // barrier completes and the drain below terminates.
-                tma_load_2d(sa, &tmA, &bars->full[s], k_off, m_off);
+                if (CONV) tma_load_4d(sa, &tmA, &bars->full[s], chunk * kBlockK, tap % 3 - 1, h0 + tap / 3 - 1, img);
+                else      tma_load_2d(sa, &tmA, &bars->full[s], k_off, m_off);
                 fills++;
                 ok = false;
                 break;
@@ -622,11 +644,39 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 ready_end = static_cast<uint32_t>(k_off) + (ahead + 1) * sync_stride;
                 if (ahead) __threadfence();
               }
+              // A 3x3 stencil also reads the image rows just above and below the tile: they belong to
+              // the neighbouring producer tiles of the same image, which the reference's policy does
+              // not wait for (it relies on tile order); wait for them as well.
+              if (CONV) {
+                bool halo_ok = true;
+                for (int dm = -1; dm <= 1 && halo_ok; dm += 2) {
+                  const int nb = static_cast<int>(t.y) % p.conv_tiles_per_image + dm;
+                  if (nb < 0 || nb >= p.conv_tiles_per_image) continue;
+                  const uint32_t nidx = cusync::eval::tileIndex(
+                      st.in_policy, static_cast<uint32_t>(m_off + dm * p.conv_rows * p.conv_w),
+                      static_cast<uint32_t>(k_off), st.prod_grid.x, st.prod_grid.y);
+                  if (!cusync::spinUntilAtLeast(st.sems_wait + nidx, wait_target, st.timeout_ns, &seen)) {
+                    bars->abort = 1u;
+                    cusync::recordTimeout(st.status, 1u, static_cast<uint32_t>(m_off), static_cast<uint32_t>(k_off), 2u,
+                                          nidx, seen, wait_target);
+                    halo_ok = false;
+                  }
+                }
+                if (!halo_ok) {
+                  tma_load_4d(sa, &tmA, &bars->full[s], chunk * kBlockK, tap % 3 - 1, h0 + tap / 3 - 1, img);
+                  fills++;
+                  ok = false;
+                  break;
+                }
+              }
               // Order the acquire (generic proxy) before the TMA read (async proxy).
               fence_proxy_async();
             }
           }
-          tma_load_2d(sa, &tmA, &bars->full[s], k_off, m_off);
+          // Convolution: the box {64 channels, W pixels, conv_rows rows, 1 image} shifted by the tap; the
+          // TMA zero-fills what falls outside the image, which is the padding.
+          if (CONV) tma_load_4d(sa, &tmA, &bars->full[s], chunk * kBlockK, tap % 3 - 1, h0 + tap / 3 - 1, img);
+          else      tma_load_2d(sa, &tmA, &bars->full[s], k_off, m_off);
           fills++;
         }
         if (p.trace && ticket < p.trace_capacity) p.trace[8ull * ticket + 5] = static_cast<unsigned long long>(wait_empty);
@@ -742,9 +792,61 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       if (!mbar_wait(&bars->tmem_full[acc], aph, ctx)) { ok = false; break; }
       tc_fence_after();
       const unsigned long long t_mma_done = p.trace ? cusync::globalTimerNs() : 0ull;
-      const int n_off = tile_n * BN, m_off = tile_m * kBlockM;
+      const int n_off = tile_n * BN, m_off = CONV ? tile_m * p.conv_rows * p.conv_w : tile_m * kBlockM;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * C::kAccCols;
 
+      if (CONV) {
+        // One output pixel per lane: its BN channels are contiguous in NHWC, so each lane stores its own
+        // 128-byte pieces directly.  Rows past conv_rows * conv_w are padding of the 128-row MMA.
+        const int row = quarter * 32 + lane;
+        const bool row_in = row < p.conv_rows * p.conv_w;
+#pragma unroll 1
+        for (int c = half; c < BN / kStoreCols; c += 2) {
+          uint32_t v[64];
+          tmem_ld_32x32b_x32(t_row + c * 64, v);
+          tmem_ld_32x32b_x32(t_row + c * 64 + 32, v + 32);
+          tmem_ld_wait();
+          if (row_in) {
+            __half* dst = static_cast<__half*>(p.d) + static_cast<size_t>(m_off + row) * p.ldd + n_off + c * 64;
+#pragma unroll
+            for (int q = 0; q < 8; q++) {
+              uint32_t w[4];
+#pragma unroll
+              for (int e = 0; e < 4; e++) {
+                float x0 = __uint_as_float(v[8 * q + 2 * e]), x1 = __uint_as_float(v[8 * q + 2 * e + 1]);
+                if (p.epilogue == CUSYNC_EPILOGUE_RELU) { x0 = fmaxf(x0, 0.0f); x1 = fmaxf(x1, 0.0f); }
+                w[e] = pack_half2(x0, x1);
+              }
+              *reinterpret_cast<uint4*>(dst + 8 * q) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->tmem_empty[acc]);
+        acc_it++;
+        if (p.is_producer) {
+          // every lane's stores are ordered before lane 0's fence by the warp barrier above
+          if (lane == 0) {
+            __threadfence();
+            mbar_arrive(&bars->post);
+            if (ew == 0) {
+              if (!mbar_wait(&bars->post, post_it & 1u, ctx)) ok = false;
+              else {
+                const uint32_t idx = cusync::eval::tileIndex(st.out_policy, static_cast<uint32_t>(m_off),
+                                                             static_cast<uint32_t>(n_off), st.grid.x, st.grid.y);
+                const uint32_t pv = cusync::eval::postValue(st.out_policy);
+                __threadfence();
+                if (st.opts & CUSYNC_OPT_NO_ATOMIC_ADD) cusync::storeRelease(st.sems_post + idx, pv * st.iter);
+                else                                    cusync::addRelease(st.sems_post + idx, pv);
+              }
+            }
+          }
+          post_it++;
+          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        }
+        continue;
+      }
       if (!DUAL && p.split_k > 1) {
         // Split-K: add this slice's part; the block that brings the last slice finalises and posts.
         bool last = false;
@@ -1370,6 +1472,23 @@ bool make_map_chunked(CUtensorMap* out, const void* base, uint64_t k, uint64_t n
   return r == CUDA_SUCCESS;
 }
 
+// NHWC fp16 activation [n, h, w, c] as a 4-D tensor {c, w, h, n}; box = {64 channels, w pixels, box_rows image
+// rows, 1 image}, 128-byte swizzle.  In shared memory that is box_rows * w rows of 128 bytes: the K-major
+// operand layout, one output pixel per row.
+bool make_map_nhwc(CUtensorMap* out, const void* base, uint64_t n, uint64_t h, uint64_t w, uint64_t c,
+                   uint32_t box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  cuuint64_t dims[4] = {c, w, h, n};
+  cuuint64_t strides[3] = {c * 2, w * c * 2, h * w * c * 2};
+  cuuint32_t box[4] = {64, static_cast<cuuint32_t>(w), box_rows, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 // fp32 workspace of split-K: [rows, cols] row-major, boxes of 32 columns (128 bytes) x 32 rows.
 bool make_map_f32(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld) {
   EncodeTiledFn fn = encode_tiled_fn();
@@ -1869,5 +1988,90 @@ int cusync_gemm_run(cusync_gemm_plan_t* pl, cusync_stream_t stream) {
         pl->tmA, pl->tmB, pl->tmB2, pl->tmD, pl->tmWS, p);
   return cudaGetLastError() == cudaSuccess ? CUSYNC_SUCCESS : CUSYNC_ERROR_CUDA;
 }
+
+// ---------------------------------------------------------------------------
+// 3x3 convolution (implicit GEMM on the same kernel)
+// ---------------------------------------------------------------------------
+int cusync_conv2d_tile_rows(int32_t w) {
+  if (w <= 0 || w > kBlockM) return 0;
+  return kBlockM / w;     // whole image rows per 128-pixel M tile
+}
+
+int cusync_conv2d_plan_create(cusync_conv2d_plan_t** out, const cusync_conv2d_desc_t* desc) {
+  if (out == nullptr || desc == nullptr) return CUSYNC_ERROR_INVALID_ARGUMENT;
+  *out = nullptr;
+  const cusync_conv2d_desc_t& d = *desc;
+  if (d.n <= 0 || d.h <= 0 || d.w <= 0 || d.c <= 0 || d.k <= 0 || !d.x || !d.filter || !d.y)
+    return CUSYNC_ERROR_INVALID_ARGUMENT;
+  if (d.epilogue != CUSYNC_EPILOGUE_NONE && d.epilogue != CUSYNC_EPILOGUE_RELU) return CUSYNC_ERROR_INVALID_ARGUMENT;
+  if (d.r != 3 || d.s != 3 || d.stride != 1 || d.pad != 1) return CUSYNC_ERROR_UNSUPPORTED;
+  // channels in whole 64-element K chunks / 64-wide N tiles; an M tile is whole image rows
+  const int rows = cusync_conv2d_tile_rows(d.w);
+  if (d.c % 64 || d.k % 64 || rows == 0 || d.h % rows) return CUSYNC_ERROR_UNSUPPORTED;
+  if (!aligned16(d.x) || !aligned16(d.filter) || !aligned16(d.y)) return CUSYNC_ERROR_UNSUPPORTED;
+
+  cusync_gemm_plan* pl = new (std::nothrow) cusync_gemm_plan();
+  if (!pl) return CUSYNC_ERROR_CUDA;
+  std::memset(pl, 0, sizeof(*pl));
+  pl->tile_n = 64;
+  pl->split_k = 1;
+  pl->kernel = KernelEntry{cusync_gemm_kernel<64, false, true>, Cfg<64, false>::kSmemBytes};
+  GemmParams& p = pl->params;
+  p.m = d.n * d.h * d.w; p.n = d.k; p.k = 9 * d.c;
+  p.d = d.y; p.ldd = d.k;
+  p.tiles_n = d.k / 64;
+  p.conv_n = d.n; p.conv_h = d.h; p.conv_w = d.w; p.conv_c = d.c;
+  p.conv_rows = rows; p.conv_tiles_per_image = d.h / rows;
+  p.tiles_m = d.n * p.conv_tiles_per_image;
+  p.num_tiles = p.tiles_n * p.tiles_m;
+  p.num_k_blocks = 9 * (d.c / 64);
+  p.split_k = 1; p.k_blocks_per_split = p.num_k_blocks;
+  p.epilogue = d.epilogue;
+  p.b_kmajor = 1;                                  // filter [k_out][r][s][c] is an [n, k] matrix
+  p.b_lbo = 16; p.b_sbo = 1024; p.b_kstep = 32;
+
+  pl->stage = d.stage;
+  if (pl->stage == nullptr) {
+    cusync_dim3_t grid = {static_cast<uint32_t>(p.tiles_n), static_cast<uint32_t>(p.tiles_m), 1};
+    cusync_dim3_t ts = {1, 1, 1};
+    int rc = cusync_stage_create(&pl->own_stage, grid, ts, CUSYNC_ORDER_TRANSPOSE_XY, nullptr, nullptr, CUSYNC_OPT_NONE);
+    if (rc != CUSYNC_SUCCESS) { delete pl; return rc; }
+    pl->stage = pl->own_stage;
+  }
+  cusync_stage_view_t view;
+  cusync_stage_get_view(pl->stage, &view);
+  int rc = CUSYNC_SUCCESS;
+  if (view.grid.x != static_cast<uint32_t>(p.tiles_n) || view.grid.y != static_cast<uint32_t>(p.tiles_m) || view.grid.z != 1)
+    rc = CUSYNC_ERROR_INVALID_ARGUMENT;
+  else if (view.in_policy.kind != CUSYNC_POLICY_NOSYNC && view.sems_wait == nullptr)
+    rc = CUSYNC_ERROR_NOT_INITIALIZED;
+  int sms = cusync_b200_sm_count();
+  if (sms <= 0) sms = 148;
+  const uint32_t cap = d.max_ctas > 0 ? static_cast<uint32_t>(d.max_ctas) : static_cast<uint32_t>(sms);
+  pl->num_ctas = static_cast<uint32_t>(p.num_tiles) < cap ? static_cast<uint32_t>(p.num_tiles) : cap;
+  if (rc == CUSYNC_SUCCESS) {
+    bool ok = make_map_nhwc(&pl->tmA, d.x, d.n, d.h, d.w, d.c, static_cast<uint32_t>(rows)) &&
+              make_map(&pl->tmB, d.filter, d.k, 9ull * d.c, 9ull * d.c, kBlockK, 64);
+    pl->tmB2 = pl->tmB; pl->tmD = pl->tmB; pl->tmWS = pl->tmB;      // unused by the convolution path
+    if (!ok) rc = CUSYNC_ERROR_CUDA;
+  }
+  if (rc == CUSYNC_SUCCESS &&
+      cudaFuncSetAttribute(reinterpret_cast<const void*>(pl->kernel.fn), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(pl->kernel.smem)) != cudaSuccess) {
+    (void)cudaGetLastError();
+    rc = CUSYNC_ERROR_CUDA;
+  }
+  if (rc != CUSYNC_SUCCESS) {
+    if (pl->own_stage) cusync_stage_destroy(pl->own_stage);
+    delete pl;
+    return rc;
+  }
+  *out = pl;
+  return CUSYNC_SUCCESS;
+}
+
+int cusync_conv2d_plan_destroy(cusync_conv2d_plan_t* pl) { return cusync_gemm_plan_destroy(pl); }
+int cusync_conv2d_run(cusync_conv2d_plan_t* pl, cusync_stream_t stream) { return cusync_gemm_run(pl, stream); }
+uint32_t cusync_conv2d_plan_num_ctas(const cusync_conv2d_plan_t* pl) { return pl ? pl->num_ctas : 0; }
 
 }  // extern "C"

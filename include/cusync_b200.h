@@ -272,6 +272,35 @@ CUSYNC_API int cusync_gemm_plan_set_trace(cusync_gemm_plan_t* plan, void* device
 /* Blocks the launch uses (persistent grid). */
 CUSYNC_API uint32_t cusync_gemm_plan_num_ctas(const cusync_gemm_plan_t* plan);
 
+/* ---- 3x3 convolution ---------------------------------------------------- */
+
+/* y[n,h,w,k] = epilogue(conv(x[n,h,w,c], filter[k,r,s,c])), NHWC / KRSC fp16, fp32 accumulate: the forward
+ * convolution of cutlass::conv::device::CuSyncImplicitGemmConvolution
+ * (conv/device/cusyncimplicit_gemm_convolution.h:51-319) as the reference's resnet.cu / vgg.cu drive it.
+ * Implicit GEMM [n*h*w, 9c] x [9c, k]: the K walk is channel-chunk outermost, filter tap innermost, as
+ * Conv2DTileSync assumes (policies.h:160-210).  An M tile is cusync_conv2d_tile_rows(w) whole image rows
+ * (w <= 128), an N tile 64 output channels; the stage grid is (k / 64, n * h / rows, 1).  A consumer
+ * convolution also waits for the producer tiles holding the image rows just above and below its own.
+ * Supported: r = s = 3, stride 1, pad 1, c and k multiples of 64, h a multiple of the tile rows. */
+typedef struct cusync_conv2d_desc {
+  int32_t n, h, w, c, k;
+  int32_t r, s, stride, pad;
+  const void* x; const void* filter; void* y;
+  int32_t epilogue;                /* CUSYNC_EPILOGUE_NONE or CUSYNC_EPILOGUE_RELU */
+  int32_t max_ctas;
+  cusync_stage_t* stage;           /* NULL = no tile synchronisation */
+} cusync_conv2d_desc_t;
+
+typedef struct cusync_gemm_plan cusync_conv2d_plan_t;
+
+CUSYNC_API int cusync_conv2d_tile_rows(int32_t w);
+/* can_implement + initialize (conv/device/cusyncimplicit_gemm_convolution.h:100-265). */
+CUSYNC_API int cusync_conv2d_plan_create(cusync_conv2d_plan_t** out, const cusync_conv2d_desc_t* desc);
+CUSYNC_API int cusync_conv2d_plan_destroy(cusync_conv2d_plan_t* plan);
+/* run(stream) (conv/device/cusyncimplicit_gemm_convolution.h:283-297). */
+CUSYNC_API int cusync_conv2d_run(cusync_conv2d_plan_t* plan, cusync_stream_t stream);
+CUSYNC_API uint32_t cusync_conv2d_plan_num_ctas(const cusync_conv2d_plan_t* plan);
+
 /* ---- MLP driver ---------------------------------------------------------- */
 
 enum { CUSYNC_MLP_GPT3 = 0, CUSYNC_MLP_LLAMA = 1 };

@@ -1,0 +1,95 @@
+"""GPU parity tests of the 3x3 convolution (implicit GEMM on the sm_100a kernel) and of the two-convolution
+chain of BASELINE config 5, against the CPU oracle (orc_conv2d_3x3_nhwc_f16, which follows
+cutlass::reference::host::Conv2dFprop as called at volta_conv2d/resnet.cu:708-720).
+Tolerance: max relative error <= 1e-2 (resnet.cu:724), small elements compared absolutely."""
+import numpy as np
+import pytest
+
+import oracle_lib as o
+import cusync_b200 as cs
+from cusync_b200 import _lib as L
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+
+
+def _inputs(n, h, w, c, k, seed):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn((n, h, w, c), generator=g).half().cuda()
+    # He-normal filters: sigma = sqrt(2 / fan_in), fan_in = 9 c
+    f = (torch.randn((k, 3, 3, c), generator=g) * (2.0 / (9 * c)) ** 0.5).half().cuda()
+    return x, f
+
+
+@pytest.mark.parametrize("n,h,w,c,k", [
+    (1, 56, 56, 64, 64),      # config 5, N = 1
+    (2, 4, 56, 64, 64),       # two tiles per image: every tile touches a border
+    (3, 28, 28, 64, 128),     # four image rows per tile, two N tiles
+    (1, 8, 32, 128, 64),      # two channel chunks: 18 K blocks
+    (2, 2, 128, 64, 64),      # one image row per tile
+])
+@pytest.mark.parametrize("relu", [False, True])
+def test_conv3x3_matches_oracle(n, h, w, c, k, relu):
+    x, f = _inputs(n, h, w, c, k, 1)
+    y = torch.full((n, h, w, k), float("nan"), device="cuda", dtype=torch.half)
+    conv = cs.Conv2dFprop()
+    prob = cs.Conv2dProblemSize(n, h, w, c, k)
+    assert conv.initialize(None, prob, x, f, y, L.EPILOGUE_RELU if relu else L.EPILOGUE_NONE) == L.SUCCESS
+    assert conv.run(torch.cuda.current_stream()) == L.SUCCESS
+    torch.cuda.synchronize()
+    ref = o.conv2d_3x3_nhwc_f16(x.cpu().numpy(), f.cpu().numpy(), relu)
+    assert o.max_rel_err(y.cpu().numpy(), ref) <= TOL
+    conv.destroy()
+
+
+def test_conv_refuses_unsupported_shapes():
+    x, f = _inputs(1, 56, 56, 64, 64, 2)
+    y = torch.empty((1, 56, 56, 64), device="cuda", dtype=torch.half)
+    conv = cs.Conv2dFprop()
+    assert conv.initialize(None, cs.Conv2dProblemSize(1, 56, 56, 64, 64, r=5, s=5), x, f, y) == L.ERROR_UNSUPPORTED
+    assert conv.initialize(None, cs.Conv2dProblemSize(1, 56, 56, 48, 64), x, f, y) == L.ERROR_UNSUPPORTED
+    assert conv.initialize(None, cs.Conv2dProblemSize(1, 55, 56, 64, 64), x, f, y) == L.ERROR_UNSUPPORTED   # h % 2
+    assert conv.initialize(None, cs.Conv2dProblemSize(1, 8, 200, 64, 64), x, f, y) == L.ERROR_UNSUPPORTED   # w > 128
+
+
+@pytest.mark.parametrize("n", [1, 8, 32])
+@pytest.mark.parametrize("max_ctas", [0, 5])
+def test_config5_conv_chain_with_conv2dtilesync(n, max_ctas):
+    # BASELINE config 5: X [N,56,56,64] ~ N(0,1), both filters [64,3,3,64] He-normal, ReLU after each conv,
+    # producer TileSync / consumer Conv2DTileSync (resnet.cu:107-116, 773-782).
+    h = w = 56
+    c = k = 64
+    x, f1 = _inputs(n, h, w, c, k, 10)
+    _, f2 = _inputs(1, 2, 56, c, k, 11)
+    y1 = torch.empty((n, h, w, k), device="cuda", dtype=torch.half)
+    y2 = torch.empty((n, h, w, k), device="cuda", dtype=torch.half)
+    prob = cs.Conv2dProblemSize(n, h, w, c, k)
+    grid, tile_m = prob.grid(), prob.tile_m()
+    assert grid == (1, 28 * n, 1) and tile_m == 112
+    sync1 = cs.TileSync(cs.TransposeXYOrder, tile_m, 64)
+    sync2 = cs.Conv2DTileSync(cs.TransposeXYOrder, 3, 3, tile_m, 64)
+    prod = cs.CuStage(cs.TransposeXYOrder, grid, (1, 1, 1), cs.NoSync(), sync1)
+    cons = cs.CuStage(cs.TransposeXYOrder, grid, (1, 1, 1), sync2, cs.NoSync())
+    assert cs.CuSync.setProducerConsumerPair(prod, cons) == L.SUCCESS
+    c1, c2 = cs.Conv2dFprop(), cs.Conv2dFprop()
+    assert c1.initialize(prod, prob, x, f1, y1, L.EPILOGUE_RELU, max_ctas) == L.SUCCESS
+    assert c2.initialize(cons, prob, y1, f2, y2, L.EPILOGUE_RELU, max_ctas) == L.SUCCESS
+    ps, cst = torch.cuda.Stream(priority=-1), torch.cuda.Stream()
+    r1 = o.conv2d_3x3_nhwc_f16(x.cpu().numpy(), f1.cpu().numpy(), True)
+    r2 = o.conv2d_3x3_nhwc_f16(r1, f2.cpu().numpy(), True)
+    opol = o.policy(o.TILESYNC, 1, tile_m, 64, 1, 1)
+    torch.cuda.synchronize()
+    for it in range(1, 4):
+        y1.fill_(float("nan")); y2.fill_(float("nan")); torch.cuda.synchronize()   # poison
+        assert c1.run(ps) == L.SUCCESS
+        assert prod.invokeWaitKernel(cst) == L.SUCCESS
+        assert c2.run(cst) == L.SUCCESS
+        torch.cuda.synchronize()
+        assert prod.status().code == 0 and cons.status().code == 0
+        assert o.max_rel_err(y1.cpu().numpy(), r1) <= TOL
+        assert o.max_rel_err(y2.cpu().numpy(), r2) <= TOL
+        exp, oob = o.producer_semaphores(opol, grid, tile_m, 64, 0, it)
+        assert oob == 0 and (prod.semaphores() == exp).all()
+        prod.incrementIter(); cons.incrementIter()
+    c1.destroy(); c2.destroy(); prod.destroy(); cons.destroy()
