@@ -610,7 +610,26 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                                                            static_cast<uint32_t>(k_off), st.prod_grid.x,
                                                            st.prod_grid.y);
               uint32_t seen = 0;
-              if (!cusync::spinUntilAtLeast(st.sems_wait + idx, wait_target, st.timeout_ns, &seen)) {
+              // Convolution: the tile's own semaphore and those of its two halo neighbours are probed
+              // together first (one memory round trip instead of three); only what is still missing is
+              // then waited for.
+              bool conv_all_ready = false;
+              if (CONV) {
+                const int tin = static_cast<int>(t.y) % p.conv_tiles_per_image;
+                const int span = p.conv_rows * p.conv_w;
+                const uint32_t i_up = tin > 0 ? cusync::eval::tileIndex(st.in_policy, static_cast<uint32_t>(m_off - span),
+                                                    static_cast<uint32_t>(k_off), st.prod_grid.x, st.prod_grid.y) : idx;
+                const uint32_t i_dn = tin + 1 < p.conv_tiles_per_image
+                                          ? cusync::eval::tileIndex(st.in_policy, static_cast<uint32_t>(m_off + span),
+                                                static_cast<uint32_t>(k_off), st.prod_grid.x, st.prod_grid.y) : idx;
+                const uint32_t v0 = cusync::loadRelaxed(st.sems_wait + idx);
+                const uint32_t v1 = cusync::loadRelaxed(st.sems_wait + i_up);
+                const uint32_t v2 = cusync::loadRelaxed(st.sems_wait + i_dn);
+                conv_all_ready = v0 >= wait_target && v1 >= wait_target && v2 >= wait_target;
+                if (conv_all_ready) __threadfence();
+              }
+              if (!conv_all_ready &&
+                  !cusync::spinUntilAtLeast(st.sems_wait + idx, wait_target, st.timeout_ns, &seen)) {
                 bars->abort = 1u;
                 cusync::recordTimeout(st.status, 1u, static_cast<uint32_t>(m_off), static_cast<uint32_t>(k_off), tz,
                                       idx, seen, wait_target);
@@ -647,7 +666,7 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
               // A 3x3 stencil also reads the image rows just above and below the tile: they belong to
               // the neighbouring producer tiles of the same image, which the reference's policy does
               // not wait for (it relies on tile order); wait for them as well.
-              if (CONV) {
+              if (CONV && !conv_all_ready) {
                 bool halo_ok = true;
                 for (int dm = -1; dm <= 1 && halo_ok; dm += 2) {
                   const int nb = static_cast<int>(t.y) % p.conv_tiles_per_image + dm;
@@ -701,7 +720,11 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     // MMA issuer
     // =====================================================================
     if (lane == 0) {
-      const uint32_t idesc = make_idesc(BN, !p.b_kmajor);
+      // Dual-B tiles sit back to back in the ring (second operand right after the first, same chunking), so
+      // while both fit one instruction they are multiplied as a single 2*BN-wide B: accumulator columns
+      // [0, BN) are A*B, [BN, 2BN) are A*B2.
+      constexpr bool kFusedDual = DUAL && 2 * BN <= 256;
+      const uint32_t idesc = make_idesc(kFusedDual ? 2 * BN : BN, !p.b_kmajor);
       const uint32_t b_lbo = p.b_lbo, b_sbo = p.b_sbo, b_kstep = p.b_kstep;
       uint32_t drains = 0, sched_it = 0, acc_it = 0;
       bool ok = true;
@@ -739,7 +762,7 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             const uint64_t bdesc = make_smem_desc(sb + kk * b_kstep, b_lbo, b_sbo);
             const uint32_t accumulate = (kb > 0 || kk > 0) ? 1u : 0u;
             umma_f16(d_tmem, adesc, bdesc, idesc, accumulate);
-            if (DUAL) {
+            if (DUAL && !kFusedDual) {
               const uint64_t b2desc = make_smem_desc(sb + C::kBBytes + kk * b_kstep, b_lbo, b_sbo);
               umma_f16(d_tmem + BN, adesc, b2desc, idesc, accumulate);
             }
