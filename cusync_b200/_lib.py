@@ -71,6 +71,12 @@ class Conv2dDesc(C.Structure):
                 ("epilogue", C.c_int32), ("max_ctas", C.c_int32), ("stage", C.c_void_p)]
 
 
+class AttnDesc(C.Structure):
+    _fields_ = [("batch", C.c_int32), ("seq", C.c_int32), ("heads", C.c_int32), ("head_dim", C.c_int32),
+                ("qkv", C.c_void_p), ("ld_qkv", C.c_int64), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p),
+                ("out", C.c_void_p), ("ld_out", C.c_int64), ("kv_splits", C.c_int32), ("stage", C.c_void_p)]
+
+
 class MlpDesc(C.Structure):
     _fields_ = [("model", C.c_int32), ("batch", C.c_int32), ("hidden", C.c_int32), ("ffn", C.c_int32),
                 ("policy", C.c_int32), ("opts", C.c_int32), ("tile_n1", C.c_int32), ("tile_n2", C.c_int32),
@@ -115,6 +121,11 @@ SIGNATURES = {
     "cusync_conv2d_plan_destroy": (_i, [_vp]),
     "cusync_conv2d_run": (_i, [_vp, _vp]),
     "cusync_conv2d_plan_num_ctas": (_u32, [_vp]),
+    "cusync_attn_default_splits": (_i, [C.c_int32] * 3),
+    "cusync_attn_plan_create": (_i, [C.POINTER(_vp), C.POINTER(AttnDesc)]),
+    "cusync_attn_plan_destroy": (_i, [_vp]),
+    "cusync_attn_plan_splits": (_i, [_vp]),
+    "cusync_attn_run": (_i, [_vp, _vp]),
     "cusync_mlp_create": (_i, [C.POINTER(_vp), C.POINTER(MlpDesc)]),
     "cusync_mlp_destroy": (_i, [_vp]),
     "cusync_mlp_run_stream_ordered": (_i, [_vp, _vp]),

@@ -301,6 +301,33 @@ CUSYNC_API int cusync_conv2d_plan_destroy(cusync_conv2d_plan_t* plan);
 CUSYNC_API int cusync_conv2d_run(cusync_conv2d_plan_t* plan, cusync_stream_t stream);
 CUSYNC_API uint32_t cusync_conv2d_plan_num_ctas(const cusync_conv2d_plan_t* plan);
 
+/* ---- decode attention (a middle stage) ---------------------------------- */
+
+/* One query token per batch row attends, per head, over `seq` cached keys/values plus its own new key/value;
+ * scores scaled by 1/sqrt(head_dim), softmax in fp32, fp16 out.  It stands where the reference's attention
+ * chain has its two un-normalised GEMMs S = Q K^T and O = S V (src/ml-bench/transformer/attention.cu:105-118,
+ * 706-833): a stage that both waits (on the Q, K and V thirds of the QKV projection's row panel, ConsecutiveSync
+ * attention.cu:51-70) and posts (RowSync on its output's row panel, published when every row and head of the
+ * panel is written; use wait value 1 and post value 1).
+ * qkv[batch, 3 * heads * 128] = Q | K | V (row pitch ld_qkv), caches [batch, seq, heads, 128], out[batch, heads * 128].
+ * The stage grid is (heads, batch, kv_splits).  head_dim must be 128. */
+typedef struct cusync_attn_desc {
+  int32_t batch, seq, heads, head_dim;
+  const void* qkv; int64_t ld_qkv;
+  const void* k_cache; const void* v_cache;
+  void* out; int64_t ld_out;
+  int32_t kv_splits;               /* blocks per (row, head) over the key range: 0 = choose */
+  cusync_stage_t* stage;           /* NULL = no tile synchronisation */
+} cusync_attn_desc_t;
+
+typedef struct cusync_attn_plan cusync_attn_plan_t;
+
+CUSYNC_API int cusync_attn_default_splits(int32_t batch, int32_t seq, int32_t heads);
+CUSYNC_API int cusync_attn_plan_create(cusync_attn_plan_t** out, const cusync_attn_desc_t* desc);
+CUSYNC_API int cusync_attn_plan_destroy(cusync_attn_plan_t* plan);
+CUSYNC_API int cusync_attn_plan_splits(const cusync_attn_plan_t* plan);
+CUSYNC_API int cusync_attn_run(cusync_attn_plan_t* plan, cusync_stream_t stream);
+
 /* ---- MLP driver ---------------------------------------------------------- */
 
 enum { CUSYNC_MLP_GPT3 = 0, CUSYNC_MLP_LLAMA = 1 };

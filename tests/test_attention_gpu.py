@@ -1,0 +1,107 @@
+"""GPU parity tests of the decode-attention middle stage and of the three-stage attention block of BASELINE
+config 4 (QKV projection -> attention over a K/V cache -> output projection) against the CPU oracle.
+The reference's attention chain has no softmax and pins only the stage wiring (attention.cu:105-118); the
+arithmetic here is checked against orc_attention_decode_f16 (parity unpinned by any reference test)."""
+import numpy as np
+import pytest
+
+import oracle_lib as o
+import cusync_b200 as cs
+from cusync_b200 import _lib as L
+from cusync_b200.attention import AttentionBlock, DecodeAttention
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+
+
+def _randn(shape, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).half().cuda()
+
+
+def _oracle_attention(qkv, kc, vc, heads):
+    B = qkv.shape[0]
+    hd = heads * 128
+    q = qkv[:, :hd].reshape(B, heads, 128)
+    knew = qkv[:, hd:2 * hd].reshape(B, 1, heads, 128)
+    vnew = qkv[:, 2 * hd:].reshape(B, 1, heads, 128)
+    k = np.concatenate([kc, knew], axis=1)
+    v = np.concatenate([vc, vnew], axis=1)
+    return o.attention_decode_f16(q, k, v).reshape(B, hd)
+
+
+@pytest.mark.parametrize("B,S,heads,splits", [(1, 512, 12, 0), (4, 2048, 12, 0), (3, 100, 2, 1), (2, 1000, 3, 7),
+                                              (5, 0, 2, 1), (130, 64, 1, 2)])
+def test_decode_attention_matches_oracle(B, S, heads, splits):
+    qkv = _randn((B, 3 * heads * 128), 1)
+    kc = _randn((B, S, heads, 128), 2)
+    vc = _randn((B, S, heads, 128), 3)
+    out = torch.full((B, heads * 128), float("nan"), device="cuda", dtype=torch.half)
+    a = DecodeAttention(None, qkv, kc if S else None, vc if S else None, out, heads, splits)
+    assert a.create_status == L.SUCCESS
+    for _ in range(2):      # split counters must re-arm themselves
+        out.fill_(float("nan"))
+        assert a.run(torch.cuda.current_stream()) == L.SUCCESS
+        torch.cuda.synchronize()
+        ref = _oracle_attention(qkv.cpu().numpy(), kc.cpu().numpy(), vc.cpu().numpy(), heads)
+        assert o.max_rel_err(out.cpu().numpy(), ref) <= TOL
+    a.destroy()
+
+
+@pytest.mark.parametrize("B,S", [(1, 512), (4, 1024), (2, 2048), (160, 128)])
+def test_config4_attention_block_chain(B, S):
+    heads, H = 12, 12288
+    x = _randn((B, H), 10)
+    w_qkv = _randn((H, 3 * heads * 128), 11, 0.02)
+    w_o = _randn((heads * 128, H), 12, 0.02)
+    kc = _randn((B, S, heads, 128), 13)
+    vc = _randn((B, S, heads, 128), 14)
+    blk = AttentionBlock(x, w_qkv, kc, vc, w_o, heads)
+    streams = (torch.cuda.Stream(priority=-1), torch.cuda.Stream(), torch.cuda.Stream())
+    qkv_ref = o.gemm_f16(x.cpu().numpy(), w_qkv.cpu().numpy())
+    torch.cuda.synchronize()
+    for it in range(1, 4):
+        blk.qkv.fill_(float("nan")); blk.o.fill_(float("nan")); blk.y.fill_(float("nan"))   # poison
+        torch.cuda.synchronize()
+        blk.run(streams)
+        torch.cuda.synchronize()
+        assert blk.status_codes() == (0, 0, 0)
+        qkv = blk.qkv.cpu().numpy()
+        assert o.max_rel_err(qkv, qkv_ref) <= TOL
+        o_gpu = blk.o.cpu().numpy()
+        assert o.max_rel_err(o_gpu, _oracle_attention(qkv, kc.cpu().numpy(), vc.cpu().numpy(), heads)) <= TOL
+        assert o.max_rel_err(blk.y.cpu().numpy(), o.gemm_f16(o_gpu, w_o.cpu().numpy())) <= TOL
+        # semaphores: three per row panel of the QKV stage (Q, K, V thirds), each reaching its 6 column tiles;
+        # one per row panel of the attention stage
+        tiles_m = (B + 127) // 128
+        group = 1536 // blk.config["tile_n"][0]
+        assert (blk.s1.semaphores()[:3 * tiles_m] == group * it).all()
+        assert (blk.s2.semaphores()[:tiles_m] == it).all()
+    blk.destroy()
+    # stream-ordered arm gives the same output
+    ref_blk = AttentionBlock(x, w_qkv, kc, vc, w_o, heads, synced=False)
+    ref_blk.run((torch.cuda.current_stream(),))
+    torch.cuda.synchronize()
+    o_gpu = ref_blk.o.cpu().numpy()
+    assert o.max_rel_err(ref_blk.y.cpu().numpy(), o.gemm_f16(o_gpu, w_o.cpu().numpy())) <= TOL
+    ref_blk.destroy()
+
+
+def test_attention_wait_times_out():
+    B, S, heads = 2, 64, 2
+    qkv = _randn((B, 3 * heads * 128), 20); kc = _randn((B, S, heads, 128), 21); vc = _randn((B, S, heads, 128), 22)
+    out = torch.zeros((B, heads * 128), device="cuda", dtype=torch.half)
+    sync = cs.RowSync(128, 1, 1)
+    prod = cs.CuStage(cs.TransposeXYOrder, (1, 1, 1), (1, 1, 1), cs.NoSync(), sync)
+    mid = cs.CuStage(cs.IdentityOrder, (heads, B, 1), (1, 1, 1), sync, cs.NoSync())
+    assert cs.CuSync.setProducerConsumerPair(prod, mid) == L.SUCCESS
+    mid.set_timeout_ns(20e6)
+    a = DecodeAttention(mid, qkv, kc, vc, out, heads, 1)
+    assert a.create_status == L.SUCCESS
+    assert a.run(torch.cuda.current_stream()) == L.SUCCESS
+    torch.cuda.synchronize()
+    st = mid.status()
+    assert st.code == L.ERROR_TIMEOUT and st.expected == 1 and st.seen == 0
+    assert (out == 0).all()
+    a.destroy(); prod.destroy(); mid.destroy()
