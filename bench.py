@@ -187,22 +187,18 @@ def main():
         return
 
     import torch
-    import torch.distributed as dist
     from cusync_b200 import mlp as M
+    from cusync_b200 import tp
     from cusync_b200 import _lib as L
     L.lib()   # fail loudly here if the CUDA library is not built
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # keep stdout to the one JSON line
-        dist.init_process_group("nccl", device_id=dev)
+    group = tp.TensorParallelGroup("nccl", dev)
 
     def barrier():
-        if world > 1:
-            dist.barrier()
+        group.barrier()
 
     peaks = load_peaks()
     ps = torch.cuda.Stream(priority=-1)   # producer: high priority, launched first
@@ -220,20 +216,16 @@ def main():
         shard.run_cusync(ps, cs)
         if world > 1:
             with torch.cuda.stream(cs):
-                dist.all_reduce(shard.y)
+                group.all_reduce_sum(shard.y)
 
     def ordered_step():
         shard.run_stream_ordered(cs)
         if world > 1:
             with torch.cuda.stream(cs):
-                dist.all_reduce(shard.y)
+                group.all_reduce_sum(shard.y)
 
     def reduce_max(v):
-        if world == 1:
-            return v
-        t = torch.tensor([v], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+        return group.max_over_ranks(v)
 
     def interleaved(step_a, a_streams, step_b, b_streams, n, warm):
         """Alternates the two arms step by step, so clock and power drift hits both alike.
@@ -316,8 +308,7 @@ def main():
             shard.x.copy_(xh, non_blocking=True)
         shard.run_cusync(ps, cs)
         with torch.cuda.stream(cs):
-            if world > 1:
-                dist.all_reduce(shard.y)
+            group.all_reduce_sum(shard.y)
             yh.copy_(shard.y, non_blocking=True)
 
     e2e_total, _ = time_steps(e2e_step, ps, cs, args.steps, args.warmup, barrier)
@@ -352,11 +343,85 @@ def main():
             best = min(row["rowsync_us"], row["tilesync_us"], row["rowsync_stream_ordered_us"])
             row["tflops_best"] = round(shard.flops() / args.batch * b / (best * 1e-6) / 1e12, 1)
             table.append(row)
+    # ---- the other workloads of the path: LLaMA MLP, 3x3 conv chain, attention block ------------------
+    extras = {}
+    if not args.no_sweep and world == 1:
+        import cusync_b200 as cs
+        from cusync_b200.attention import AttentionBlock
+        s3 = torch.cuda.Stream()
+
+        def ab(c_step, o_step):
+            c_per, o_per = interleaved(c_step, (ps, cs), o_step, (cs, cs), 20, 5)
+            c_us, o_us = statistics.median(c_per) * 1000, statistics.median(o_per) * 1000
+            return {"cusync_us": round(c_us, 2), "stream_ordered_us": round(o_us, 2),
+                    "gain_pct": round(100.0 - c_us / o_us * 100.0, 2)}
+
+        rows = []
+        for b in (1, 64, 512, 2048):     # config 3: LLaMA 65B MLP shard, fused SwiGLU dual GEMM, ffn 2752
+            x, w1, w2, v = M.make_inputs("llama", b, dev, seed=1)
+            sh = M.MLPShard("llama", b, x, w1, w2, v, policy="rowsync")
+
+            def c_step(sh=sh):
+                ps.wait_stream(cs); sh.run_cusync(ps, cs)
+            r = ab(c_step, lambda sh=sh: sh.run_stream_ordered(cs))
+            r.update({"batch": b, "tile_n": [sh.tile_n1, sh.tile_n2], "split_k": [sh.split_k1, sh.split_k2]})
+            rows.append(r); sh.destroy()
+        extras["llama_mlp_rowsync"] = rows
+
+        rows = []
+        for n in (1, 8, 32):             # config 5: two 3x3 convolutions, 56x56x64, ReLU, Conv2DTileSync
+            g = torch.Generator(device=dev).manual_seed(n)
+            xin = torch.randn((n, 56, 56, 64), generator=g, device=dev).half()
+            f1 = (torch.randn((64, 3, 3, 64), generator=g, device=dev) * (2.0 / 576) ** 0.5).half()
+            f2 = (torch.randn((64, 3, 3, 64), generator=g, device=dev) * (2.0 / 576) ** 0.5).half()
+            y1 = torch.empty_like(xin); y2 = torch.empty_like(xin)
+            prob = cs.Conv2dProblemSize(n, 56, 56, 64, 64)
+            grid, tm = prob.grid(), prob.tile_m()
+            prod = cs.CuStage(cs.TransposeXYOrder, grid, (1, 1, 1), cs.NoSync(), cs.TileSync(cs.TransposeXYOrder, tm, 64))
+            cons = cs.CuStage(cs.TransposeXYOrder, grid, (1, 1, 1), cs.Conv2DTileSync(cs.TransposeXYOrder, 3, 3, tm, 64),
+                              cs.NoSync())
+            L.check(cs.CuSync.setProducerConsumerPair(prod, cons), "conv link")
+            convs = [cs.Conv2dFprop() for _ in range(4)]
+            L.check(convs[0].initialize(prod, prob, xin, f1, y1, L.EPILOGUE_RELU), "conv1")
+            L.check(convs[1].initialize(cons, prob, y1, f2, y2, L.EPILOGUE_RELU), "conv2")
+            L.check(convs[2].initialize(None, prob, xin, f1, y1, L.EPILOGUE_RELU), "conv1 plain")
+            L.check(convs[3].initialize(None, prob, y1, f2, y2, L.EPILOGUE_RELU), "conv2 plain")
+
+            def c_step():
+                ps.wait_stream(cs); convs[0].run(ps); prod.invokeWaitKernel(cs); convs[1].run(cs)
+                prod.incrementIter(); cons.incrementIter()
+
+            def o_step():
+                convs[2].run(cs); convs[3].run(cs)
+            r = ab(c_step, o_step)
+            r["images"] = n
+            rows.append(r)
+            for c in convs:
+                c.destroy()
+            prod.destroy(); cons.destroy()
+        extras["resnet_conv3x3_chain_conv2dtilesync"] = rows
+
+        rows = []
+        for b, seq in ((1, 512), (1, 2048), (4, 2048)):   # config 4: attention block, 12 heads of 128
+            g = torch.Generator(device=dev).manual_seed(7)
+            xin = torch.randn((b, 12288), generator=g, device=dev).half()
+            wqkv = (torch.randn((12288, 4608), generator=g, device=dev) * 0.02).half()
+            wo = (torch.randn((1536, 12288), generator=g, device=dev) * 0.02).half()
+            kc = torch.randn((b, seq, 12, 128), generator=g, device=dev).half()
+            vc = torch.randn((b, seq, 12, 128), generator=g, device=dev).half()
+            blk = AttentionBlock(xin, wqkv, kc, vc, wo, 12)
+            ref = AttentionBlock(xin, wqkv, kc, vc, wo, 12, synced=False)
+
+            def c_step():
+                ps.wait_stream(s3); blk.run((ps, cs, s3)); cs.wait_stream(s3)
+            r = ab(c_step, lambda: ref.run((cs,)))
+            r.update({"batch": b, "context": seq, "config": blk.config})
+            rows.append(r); blk.destroy(); ref.destroy()
+        extras["gpt3_attention_block"] = rows
     clocks = sampler.stop() if rank == 0 else None
 
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
+        group.close()
         return
 
     value_us = ms_per_step * 1000.0
@@ -376,7 +441,8 @@ def main():
             "e2e": {"value": e2e_us, "unit": UNIT, "h2d_bytes_per_step": io_bytes, "d2h_bytes_per_step": io_bytes},
             "gpu_launches": 3 * args.steps,
             "clocks": clocks,
-            "per_batch": table}
+            "per_batch": table,
+            "other_workloads": extras}
     if not args.no_cpu:
         sample = args.batch
         us, threads, spent = cpu_reference_us(args.batch, sample, M.GPT3_HIDDEN, M.GPT3_FFN)
@@ -384,8 +450,7 @@ def main():
                                 "sample": "%d of %d rows through both GEMMs (%.1f s), scaled to the full batch"
                                           % (sample, args.batch, spent)}
     print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    group.close()
 
 
 if __name__ == "__main__":
