@@ -346,7 +346,7 @@ def main():
     # ---- the other workloads of the path: LLaMA MLP, 3x3 conv chain, attention block ------------------
     extras = {}
     if not args.no_sweep and world == 1:
-        import cusync_b200 as cs
+        import cusync_b200 as lib_
         from cusync_b200.attention import AttentionBlock
         s3 = torch.cuda.Stream()
 
@@ -375,13 +375,13 @@ def main():
             f1 = (torch.randn((64, 3, 3, 64), generator=g, device=dev) * (2.0 / 576) ** 0.5).half()
             f2 = (torch.randn((64, 3, 3, 64), generator=g, device=dev) * (2.0 / 576) ** 0.5).half()
             y1 = torch.empty_like(xin); y2 = torch.empty_like(xin)
-            prob = cs.Conv2dProblemSize(n, 56, 56, 64, 64)
+            prob = lib_.Conv2dProblemSize(n, 56, 56, 64, 64)
             grid, tm = prob.grid(), prob.tile_m()
-            prod = cs.CuStage(cs.TransposeXYOrder, grid, (1, 1, 1), cs.NoSync(), cs.TileSync(cs.TransposeXYOrder, tm, 64))
-            cons = cs.CuStage(cs.TransposeXYOrder, grid, (1, 1, 1), cs.Conv2DTileSync(cs.TransposeXYOrder, 3, 3, tm, 64),
-                              cs.NoSync())
-            L.check(cs.CuSync.setProducerConsumerPair(prod, cons), "conv link")
-            convs = [cs.Conv2dFprop() for _ in range(4)]
+            prod = lib_.CuStage(lib_.TransposeXYOrder, grid, (1, 1, 1), lib_.NoSync(), lib_.TileSync(lib_.TransposeXYOrder, tm, 64))
+            cons = lib_.CuStage(lib_.TransposeXYOrder, grid, (1, 1, 1), lib_.Conv2DTileSync(lib_.TransposeXYOrder, 3, 3, tm, 64),
+                              lib_.NoSync())
+            L.check(lib_.CuSync.setProducerConsumerPair(prod, cons), "conv link")
+            convs = [lib_.Conv2dFprop() for _ in range(4)]
             L.check(convs[0].initialize(prod, prob, xin, f1, y1, L.EPILOGUE_RELU), "conv1")
             L.check(convs[1].initialize(cons, prob, y1, f2, y2, L.EPILOGUE_RELU), "conv2")
             L.check(convs[2].initialize(None, prob, xin, f1, y1, L.EPILOGUE_RELU), "conv1 plain")
