@@ -101,20 +101,53 @@ cusync_attn_decode_kernel(const AttnParams p) {
   const int k0 = z * per, k1 = min(total, k0 + per);
   const int nkeys = max(k1 - k0, 0);
 
-  // ---- scores: each warp takes every fourth key; a lane holds 4 of the 128 elements -------------
+  // Thread layout for the two passes over the cache: 16 threads cover one key's 128 elements with a 16-byte
+  // load each (thread `sub` holds elements [8 sub, 8 sub + 8)); the block's 8 such groups take every eighth
+  // key; `kInFlight` keys per group are loaded before any is used, so 16 KB are in flight per block.
+  constexpr int kGroups = kAttnThreads / 16, kInFlight = 8;
+  const int grp = tid >> 4, sub = tid & 15;
+  float qf[8];
+#pragma unroll
+  for (int e = 0; e < 8; e++) qf[e] = q_s[8 * sub + e];
+  const size_t kv_row = static_cast<size_t>(p.heads) * kHeadDim;                     // elements between keys
+  const __half* knew = p.qkv + static_cast<size_t>(b) * p.ld_qkv + hd + h * kHeadDim + 8 * sub;
+  const __half* vnew = p.qkv + static_cast<size_t>(b) * p.ld_qkv + 2 * hd + h * kHeadDim + 8 * sub;
+  const __half* kbase = p.k_cache + (static_cast<size_t>(b) * p.seq * p.heads + h) * kHeadDim + 8 * sub;
+  const __half* vbase = p.v_cache + (static_cast<size_t>(b) * p.seq * p.heads + h) * kHeadDim + 8 * sub;
+
+  // ---- scores -----------------------------------------------------------------------------------
   float mx = -INFINITY;
-  for (int i = warp; i < nkeys; i += kAttnThreads / 32) {
-    const int s = k0 + i;
-    const __half* kp = s < p.seq ? p.k_cache + ((static_cast<size_t>(b) * p.seq + s) * p.heads + h) * kHeadDim
-                                 : p.qkv + static_cast<size_t>(b) * p.ld_qkv + hd + h * kHeadDim;
-    const uint2 raw = *reinterpret_cast<const uint2*>(kp + 4 * lane);
-    const __half2 k01 = *reinterpret_cast<const __half2*>(&raw.x), k23 = *reinterpret_cast<const __half2*>(&raw.y);
-    float d = q_s[4 * lane] * __low2float(k01) + q_s[4 * lane + 1] * __high2float(k01) +
-              q_s[4 * lane + 2] * __low2float(k23) + q_s[4 * lane + 3] * __high2float(k23);
-    d = warp_sum(d);
-    if (lane == 0) scores[i] = d;
-    mx = fmaxf(mx, d);
+  // the trip count is the same for every thread of the block (the shuffles below need whole warps)
+  for (int base = 0; base < nkeys; base += kGroups * kInFlight) {
+    const int i0 = base + grp;
+    uint4 raw[kInFlight];
+#pragma unroll
+    for (int j = 0; j < kInFlight; j++) {
+      const int i = i0 + j * kGroups;
+      if (i < nkeys) {
+        const int s = k0 + i;
+        raw[j] = *reinterpret_cast<const uint4*>(s < p.seq ? kbase + static_cast<size_t>(s) * kv_row : knew);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kInFlight; j++) {
+      const int i = i0 + j * kGroups;
+      float d = 0.f;
+      if (i < nkeys) {
+        const __half2* h2 = reinterpret_cast<const __half2*>(&raw[j]);
+#pragma unroll
+        for (int e = 0; e < 4; e++) d += qf[2 * e] * __low2float(h2[e]) + qf[2 * e + 1] * __high2float(h2[e]);
+      }
+      // sum over the 16 threads of the group (both halves of the warp take part in every shuffle)
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+      if (i < nkeys) {
+        if (sub == 0) scores[i] = d;
+        mx = fmaxf(mx, d);
+      }
+    }
   }
+  mx = warp_max(mx);
   if (lane == 0) red[warp] = mx;
   __syncthreads();
   mx = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
@@ -132,14 +165,41 @@ cusync_attn_decode_kernel(const AttnParams p) {
   __syncthreads();
   sum = red[4] + red[5] + red[6] + red[7];
 
-  // ---- values: thread t accumulates output element t; a key's 128 values are one coalesced row ---------
-  float acc = 0.f;
-  for (int i = 0; i < nkeys; i++) {
-    const int s = k0 + i;
-    const __half* vp = s < p.seq ? p.v_cache + ((static_cast<size_t>(b) * p.seq + s) * p.heads + h) * kHeadDim
-                                 : p.qkv + static_cast<size_t>(b) * p.ld_qkv + 2 * hd + h * kHeadDim;
-    acc += scores[i] * __half2float(vp[tid]);
+  // ---- values: group g accumulates its keys' contribution to elements [8 sub, 8 sub + 8) -----------
+  float pv[8];
+#pragma unroll
+  for (int e = 0; e < 8; e++) pv[e] = 0.f;
+  for (int base = 0; base < nkeys; base += kGroups * kInFlight) {
+    const int i0 = base + grp;
+    uint4 raw[kInFlight];
+#pragma unroll
+    for (int j = 0; j < kInFlight; j++) {
+      const int i = i0 + j * kGroups;
+      if (i < nkeys) {
+        const int s = k0 + i;
+        raw[j] = *reinterpret_cast<const uint4*>(s < p.seq ? vbase + static_cast<size_t>(s) * kv_row : vnew);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kInFlight; j++) {
+      const int i = i0 + j * kGroups;
+      if (i < nkeys) {
+        const float w = scores[i];
+        const __half2* h2 = reinterpret_cast<const __half2*>(&raw[j]);
+#pragma unroll
+        for (int e = 0; e < 4; e++) { pv[2 * e] += w * __low2float(h2[e]); pv[2 * e + 1] += w * __high2float(h2[e]); }
+      }
+    }
   }
+  // sum the 8 groups: pv_s[group][128] in shared memory, then thread t adds up element t
+  __syncthreads();                       // everyone is done reading scores[], which pv_s may overlap
+  float* pv_s = smem + kHeadDim + 8;     // reuses the score buffer when it is large enough, see host side
+#pragma unroll
+  for (int e = 0; e < 8; e++) pv_s[grp * kHeadDim + 8 * sub + e] = pv[e];
+  __syncthreads();
+  float acc = 0.f;
+#pragma unroll
+  for (int g2 = 0; g2 < kGroups; g2++) acc += pv_s[g2 * kHeadDim + tid];
 
   __half* orow = p.out + static_cast<size_t>(b) * p.ld_out + h * kHeadDim;
   bool wrote = false;
@@ -233,7 +293,10 @@ int cusync_attn_plan_create(cusync_attn_plan_t** out, const cusync_attn_desc_t* 
   if (d.batch <= 0 || d.seq < 0 || d.heads <= 0 || !d.qkv || !d.out || (d.seq > 0 && (!d.k_cache || !d.v_cache)))
     return CUSYNC_ERROR_INVALID_ARGUMENT;
   if (d.head_dim != kHeadDim || d.seq > 16384) return CUSYNC_ERROR_UNSUPPORTED;
-  if (d.ld_qkv < 3ll * d.heads * kHeadDim || d.ld_out < 1ll * d.heads * kHeadDim || d.ld_qkv % 4) return CUSYNC_ERROR_UNSUPPORTED;
+  // 16-byte loads of the query's key/value and of the cache rows
+  if (d.ld_qkv < 3ll * d.heads * kHeadDim || d.ld_out < 1ll * d.heads * kHeadDim || d.ld_qkv % 8) return CUSYNC_ERROR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(d.qkv) | reinterpret_cast<uintptr_t>(d.k_cache) | reinterpret_cast<uintptr_t>(d.v_cache)) & 15u)
+    return CUSYNC_ERROR_UNSUPPORTED;
   if (d.kv_splits < 0 || d.kv_splits > 64) return CUSYNC_ERROR_INVALID_ARGUMENT;
 
   cusync_attn_plan* pl = new (std::nothrow) cusync_attn_plan();
@@ -281,7 +344,7 @@ int cusync_attn_plan_create(cusync_attn_plan_t** out, const cusync_attn_desc_t* 
     p.panel_arrivals = pl->counters + n_split;
     p.partial = pl->partial;
     const int per = (d.seq + 1 + pl->splits - 1) / pl->splits;
-    pl->smem = (kHeadDim + 8 + per) * sizeof(float);
+    pl->smem = (kHeadDim + 8 + (per > 8 * kHeadDim ? per : 8 * kHeadDim)) * sizeof(float);
     if (rc == CUSYNC_SUCCESS && pl->smem > 48 * 1024 &&
         cudaFuncSetAttribute(cusync_attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(pl->smem)) != cudaSuccess) {
