@@ -61,7 +61,7 @@ class GemmDesc(C.Structure):
                 ("b2", C.c_void_p),
                 ("d", C.c_void_p), ("ldd", C.c_int64),
                 ("b_layout", C.c_int32), ("epilogue", C.c_int32), ("tile_n", C.c_int32), ("max_ctas", C.c_int32),
-                ("split_k", C.c_int32), ("cta_pair", C.c_int32), ("stage", C.c_void_p)]
+                ("split_k", C.c_int32), ("cta_pair", C.c_int32), ("tail_split", C.c_int32), ("stage", C.c_void_p)]
 
 
 class Conv2dDesc(C.Structure):
@@ -81,6 +81,8 @@ class MlpDesc(C.Structure):
     _fields_ = [("model", C.c_int32), ("batch", C.c_int32), ("hidden", C.c_int32), ("ffn", C.c_int32),
                 ("policy", C.c_int32), ("opts", C.c_int32), ("tile_n1", C.c_int32), ("tile_n2", C.c_int32),
                 ("split_k1", C.c_int32), ("split_k2", C.c_int32), ("max_ctas", C.c_int32), ("cta_pair", C.c_int32), ("group_rows2", C.c_int32),
+                ("tail_split_sync1", C.c_int32), ("tail_split_sync2", C.c_int32),
+                ("tail_split_plain1", C.c_int32), ("tail_split_plain2", C.c_int32),
                 ("x", C.c_void_p), ("w1", C.c_void_p), ("v", C.c_void_p), ("w2", C.c_void_p),
                 ("h", C.c_void_p), ("y", C.c_void_p)]
 
@@ -113,6 +115,7 @@ SIGNATURES = {
     "cusync_gemm_plan_destroy": (_i, [_vp]),
     "cusync_gemm_plan_update": (_i, [_vp, _vp, _vp, _vp, _vp]),
     "cusync_gemm_run": (_i, [_vp, _vp]),
+    "cusync_gemm_plan_tail_split": (_i, [_vp]),
     "cusync_gemm_run_noalloc": (_i, [C.POINTER(GemmDesc), _vp]),
     "cusync_gemm_plan_set_trace": (_i, [_vp, _vp, _u32]),
     "cusync_gemm_plan_num_ctas": (_u32, [_vp]),
@@ -135,6 +138,7 @@ SIGNATURES = {
     "cusync_mlp_stage": (_vp, [_vp, _i]),
     "cusync_mlp_set_trace": (_i, [_vp, _vp, _u32, _vp, _u32]),
     "cusync_mlp_config": (_i, [_vp, C.POINTER(C.c_int32)]),
+    "cusync_mlp_tail_splits": (_i, [_vp, C.POINTER(C.c_int32)]),
     "cusync_b200_version": (C.c_char_p, []),
     "cusync_b200_sm_count": (_i, []),
 }

@@ -214,12 +214,13 @@ class GemmArguments:
     (gemm/device/cusyncgemm.h:293-350).  ref_C is unused (beta = 0 in every reference driver)."""
 
     def __init__(self, custage, problem_size, ref_a, ref_b, ref_d, epilogue=L.EPILOGUE_NONE, ref_b2=None,
-                 b_layout=L.B_ROW_MAJOR_KN, tile_n=0, max_ctas=0, split_k_slices=0, cta_pair=0):
+                 b_layout=L.B_ROW_MAJOR_KN, tile_n=0, max_ctas=0, split_k_slices=0, cta_pair=0, tail_split=0):
         self.custage, self.problem_size = custage, problem_size
         self.ref_a, self.ref_b, self.ref_b2, self.ref_d = ref_a, ref_b, ref_b2, ref_d
         self.epilogue, self.b_layout, self.tile_n, self.max_ctas = epilogue, b_layout, tile_n, max_ctas
         self.cta_pair = cta_pair
         self.split_k_slices = split_k_slices
+        self.tail_split = tail_split   # K slices for the tiles of the last partial wave: 0 = choose, 1 = none
 
 
 def _ref(t):
@@ -250,7 +251,7 @@ class Gemm:
         d, ldd = _ref(args.ref_d)
         b2 = _ref(args.ref_b2)[0] if args.ref_b2 is not None else None
         return L.GemmDesc(m, n, k, a, lda, b, ldb, b2, d, ldd, args.b_layout, args.epilogue, args.tile_n,
-                          args.max_ctas, args.split_k_slices, args.cta_pair, args.custage._h if args.custage is not None else None)
+                          args.max_ctas, args.split_k_slices, args.cta_pair, args.tail_split, args.custage._h if args.custage is not None else None)
 
     def can_implement(self, args):
         if args.split_k_slices < 0 or (args.split_k_slices > 1 and args.epilogue == L.EPILOGUE_SILU_MUL_DUAL):
@@ -274,6 +275,9 @@ class Gemm:
 
     def num_ctas(self):
         return L.lib().cusync_gemm_plan_num_ctas(self._plan)
+
+    def tail_split(self):
+        return L.lib().cusync_gemm_plan_tail_split(self._plan)
 
     def destroy(self):
         if self._plan:

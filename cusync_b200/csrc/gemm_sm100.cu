@@ -196,6 +196,11 @@ __host__ __device__ constexpr uint32_t make_idesc(int umma_n, bool b_mn_major) {
 // ---------------------------------------------------------------------------
 // Kernel parameters
 // ---------------------------------------------------------------------------
+// One work unit of the CTA-pair kernel: K slice `slice` of `nslices` of the pair tile (x = N tile, y = pair row).
+// Tiles of the last, partial wave may be cut into more slices than the others (see setup_pair).  A split tile
+// owns `nslices` consecutive 256 x 256 fp32 slots of the workspace, starting at slot ws_tile * nslices.
+struct PairUnit { uint32_t x, y, slice_of, ws_tile; };   // slice_of = slice | nslices << 16
+
 struct GemmParams {
   int32_t m, n, k;
   int32_t tiles_n, tiles_m, num_tiles;
@@ -214,7 +219,7 @@ struct GemmParams {
   // is conv_rows whole image rows (conv_rows * conv_w <= 128 output pixels); K walks channel chunks of 64
   // outermost and the nine filter taps innermost.
   int32_t conv_n, conv_h, conv_w, conv_c, conv_rows, conv_tiles_per_image;
-  const cusync_dim3_t* pair_order; // CTA-pair kernel: schedule over 256-row pair tiles {n tile, pair row, 0}
+  const PairUnit* pair_order;      // CTA-pair kernel: schedule over work units (256-row pair tile x K slice)
   int32_t num_pairs;
   unsigned long long* trace;       // optional per-tile timeline: 4 words per ticket (see cusync_gemm_plan_set_trace)
   uint32_t trace_capacity;
@@ -255,7 +260,7 @@ struct Barriers {
   uint64_t splitk_done;                 // epilogue warps -> posting thread: finalisation stored
   uint32_t splitk_last;
   uint32_t pad0;
-  int32_t sched_tile[kSchedSlots][8];   // {n tile, m tile, valid, ticket, k slice, -, -, -}
+  int32_t sched_tile[kSchedSlots][8];   // {n tile, m tile, valid, ticket, k slice, k slices of the tile, -, -}
   unsigned long long sched_time[kSchedSlots];   // globaltimer at the ticket draw (tracing only)
   uint32_t tmem_base;
   volatile uint32_t abort;
@@ -422,6 +427,82 @@ __device__ __forceinline__ void splitk_finalize_tile(const GemmParams& p, __half
   }
 }
 
+// CTA-pair kernel, split tiles.  Every K slice of a split tile owns a 256 x 256 fp32 slot of the workspace
+// (first the leader CTA's 128 rows, then the peer's).  Inside a CTA's part the order is the one the epilogue
+// warps produce and consume: 32-row x 32-column boxes, box (row quarter, column block) at float4 index
+// ((quarter * 8 + block) * 8 + q) * 32 + lane for columns [4q, 4q + 4) of row `lane` of the box, so that both
+// the slices' stores and the finaliser's loads are 512 contiguous bytes per warp instruction.
+constexpr int kPairBN = 256;                                // tile width of the pair kernel
+constexpr int kPairSlotVec4 = 2 * kBlockM * kPairBN / 4;    // float4 per slot
+
+// Phase 1: one warp stores its 32 accumulator rows (every second 64-column span from `half`) straight from
+// registers: plain stores that L2 takes at write bandwidth (reduce-adds of all slices into one tile were
+// bound by the L2's atomic rate, and staging through shared memory by the per-box round trip).
+template <int BN>
+__device__ __forceinline__ void pair_store_partial_rows(float4* cta_part, uint32_t t_row, int quarter, int half, int lane) {
+#pragma unroll 1
+  for (int c = half; c < BN / kStoreCols; c += 2) {
+    uint32_t v[64];
+    tmem_ld_32x32b_x32(t_row + c * 64, v);
+    tmem_ld_32x32b_x32(t_row + c * 64 + 32, v + 32);
+    tmem_ld_wait();
+    float4* dst = cta_part + ((quarter * 8 + c * 2) * 8) * 32 + lane;
+#pragma unroll
+    for (int j = 0; j < 16; j++)
+      __stcg(dst + j * 32, make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                       __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3])));
+  }
+  __threadfence();     // every lane's stores are ordered before the arrival count that follows
+}
+
+// Phase 2 (only in the CTA that counted the last slice): each warp adds up the slices' slots for its own rows
+// and column spans, in slice order (so the sum does not depend on which slice came last), then does what the
+// unsplit epilogue does: epilogue math -> fp16 -> swizzled staging buffer -> TMA store.
+template <int BN>
+__device__ __forceinline__ void pair_finalize_partials(const GemmParams& p, const CUtensorMap* tmD, uint8_t* buf,
+                                                       const float4* cta_part0, uint32_t nslices, int n_off, int row0,
+                                                       int quarter, int half, int lane) {
+  const bool rows_in = row0 < p.m;
+#pragma unroll 1
+  for (int c = half; c < BN / kStoreCols && rows_in; c += 2) {
+    if (n_off + c * kStoreCols >= p.n) break;
+    float acc[64];
+#pragma unroll
+    for (int j = 0; j < 64; j++) acc[j] = 0.f;
+    const float4* src = cta_part0 + ((quarter * 8 + c * 2) * 8) * 32 + lane;
+#pragma unroll 1
+    for (uint32_t sl = 0; sl < nslices; sl++, src += kPairSlotVec4) {
+      float4 x[16];
+#pragma unroll
+      for (int j = 0; j < 16; j++) x[j] = __ldcg(src + j * 32);
+#pragma unroll
+      for (int j = 0; j < 16; j++) { acc[4 * j] += x[j].x; acc[4 * j + 1] += x[j].y; acc[4 * j + 2] += x[j].z; acc[4 * j + 3] += x[j].w; }
+    }
+    if (lane == 0) tma_store_wait_read<0>();     // the store that last read this warp's buffer is done with it
+    __syncwarp();
+    uint32_t packed[32];
+#pragma unroll
+    for (int j = 0; j < 32; j++) {
+      float x0 = acc[2 * j], x1 = acc[2 * j + 1];
+      if (p.epilogue == CUSYNC_EPILOGUE_GELU_ERF) { x0 = gelu_erf(x0); x1 = gelu_erf(x1); }
+      else if (p.epilogue == CUSYNC_EPILOGUE_RELU) { x0 = fmaxf(x0, 0.0f); x1 = fmaxf(x1, 0.0f); }
+      packed[j] = pack_half2(x0, x1);
+    }
+    uint8_t* row = buf + lane * 128;
+#pragma unroll
+    for (int q = 0; q < 8; q++)
+      *reinterpret_cast<uint4*>(row + ((q ^ (lane & 7)) << 4)) =
+          make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_2d(tmD, buf, n_off + c * kStoreCols, row0);
+      tma_store_commit();
+    }
+  }
+  if (lane == 0) tma_store_wait_all();           // the tile is in memory before the caller publishes it
+}
+
 // Split-K epilogue of one tile for one epilogue warp; returns false if a bounded wait expired.
 // Every slice adds its part; the block that counts the last arrival finalises and publishes the tile
 // (the reference posts from the last K slice only, gemm/kernel/cusyncgemm.h:374-392).
@@ -429,9 +510,15 @@ template <int BN>
 __device__ __forceinline__ bool splitk_epilogue(const GemmParams& p, const CUtensorMap* tmWS, uint8_t* buf,
                                                 Barriers* bars, const WaitCtx& ctx, uint32_t t_row,
                                                 int n_off, int m_off, int quarter, int half, int ew, int lane,
-                                                uint32_t phase, uint64_t* tmem_empty_local, uint32_t tmem_empty_cluster,
-                                                __half* d, int64_t ldd, bool* is_last) {
-  splitk_accumulate_rows<BN>(p, tmWS, buf, t_row, n_off, m_off + quarter * 32, half, lane);
+                                                uint32_t phase, uint32_t split_phase, uint32_t nslices,
+                                                uint64_t* tmem_empty_local, uint32_t tmem_empty_cluster,
+                                                __half* d, int64_t ldd, bool* is_last,
+                                                float4* ws_part0 = nullptr, uint32_t slice = 0,
+                                                const CUtensorMap* tmD = nullptr) {
+  // ws_part0 (CTA-pair kernel): this CTA's part of the tile's first workspace slot; slice `slice` stores
+  // into the slot `slice` slots further on.  Without it the slices reduce-add into one [m, n] tile.
+  if (ws_part0) { if (m_off < p.m) pair_store_partial_rows<BN>(ws_part0 + static_cast<size_t>(slice) * kPairSlotVec4, t_row, quarter, half, lane); }
+  else splitk_accumulate_rows<BN>(p, tmWS, buf, t_row, n_off, m_off + quarter * 32, half, lane);
   // accumulator buffer is free for the MMA warp again
   tc_fence_before();
   __syncwarp();
@@ -450,16 +537,19 @@ __device__ __forceinline__ bool splitk_epilogue(const GemmParams& p, const CUten
                             static_cast<uint32_t>(n_off / BN);
       __threadfence();
       const uint32_t before = atomicAdd(p.splitk_arrivals + tile, 1u);
-      const uint32_t last = before == static_cast<uint32_t>(p.split_k) - 1u ? 1u : 0u;
+      const uint32_t last = before == nslices - 1u ? 1u : 0u;
       if (last) { p.splitk_arrivals[tile] = 0u; __threadfence(); }   // re-armed for the next launch
       bars->splitk_last = last;
     }
     mbar_arrive(&bars->splitk_counted);
   }
-  if (!mbar_wait(&bars->splitk_counted, phase, ctx)) ok = false;
+  if (!mbar_wait(&bars->splitk_counted, split_phase, ctx)) ok = false;
   const bool last = ok && bars->splitk_last != 0u;
   __syncwarp();
-  if (last) splitk_finalize_tile<BN>(p, d, ldd, n_off, m_off, ew * 32 + lane);
+  if (last) {
+    if (ws_part0) pair_finalize_partials<BN>(p, tmD, buf, ws_part0, nslices, n_off, m_off + quarter * 32, quarter, half, lane);
+    else splitk_finalize_tile<BN>(p, d, ldd, n_off, m_off, ew * 32 + lane);
+  }
   __syncwarp();
   if (lane == 0) { __threadfence(); mbar_arrive(&bars->splitk_done); }
   *is_last = last;
@@ -874,7 +964,8 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         // Split-K: add this slice's part; the block that brings the last slice finalises and posts.
         bool last = false;
         ok = splitk_epilogue<BN>(p, &tmWS, buf, bars, ctx, t_row, n_off, m_off, quarter, half, ew, lane, post_it & 1u,
-                                 &bars->tmem_empty[acc], 0u, static_cast<__half*>(p.d), p.ldd, &last);
+                                 post_it & 1u, static_cast<uint32_t>(p.split_k), &bars->tmem_empty[acc], 0u,
+                                 static_cast<__half*>(p.d), p.ldd, &last);
         acc_it++;
         if (ew == 0 && lane == 0) {
           if (!mbar_wait(&bars->splitk_done, post_it & 1u, ctx)) ok = false;
@@ -1047,7 +1138,6 @@ __device__ __forceinline__ void umma_commit_pair_local(uint64_t* bar) {
                : "memory");
 }
 
-constexpr int kPairBN = 256;                       // tile width of the pair kernel
 // K depth of one ring stage of the pair kernel: two 64-element swizzle chunks.  A barrier wait, a commit and
 // each MMA issue cost the issuing thread of the order of a hundred cycles whatever the MMA's size, so a stage
 // carries eight MMAs (and two TMA boxes) per wait/commit instead of four to stay under the tensor time.
@@ -1144,25 +1234,28 @@ cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
       const uint32_t peer_sched_full0 = map_to_cta(smem_u32(&bars->sched_full[0]), 1);
       while (ok) {
         const uint32_t slot = sched_it % kSchedSlots, sph = (sched_it / kSchedSlots) & 1u;
-        int32_t tn, tpm, valid, tz_slice = 0;
+        int32_t tn, tpm, valid, tz_slice = 0, nslices = 1;
         if (leader) {
           if (!mbar_wait_cluster(&bars->sched_empty[slot], sph ^ 1u, ctx)) { ok = false; break; }
           const uint32_t ticket = atomicAdd(st.tile_counter, 1u);
           if (ticket == total_draws - 1u) atomicExch(st.tile_counter, 0u);   // last draw of the launch
           valid = ticket < static_cast<uint32_t>(p.num_pairs) ? 1 : 0;
-          cusync_dim3_t t = {0, 0, 0};
+          PairUnit t = {0, 0, 1u << 16, 0};
           if (valid) t = p.pair_order[ticket];
-          tn = static_cast<int32_t>(t.x); tpm = static_cast<int32_t>(t.y); tz_slice = static_cast<int32_t>(t.z);
+          tn = static_cast<int32_t>(t.x); tpm = static_cast<int32_t>(t.y);
+          tz_slice = static_cast<int32_t>(t.slice_of & 0xffffu); nslices = static_cast<int32_t>(t.slice_of >> 16);
           const unsigned long long now = p.trace ? cusync::globalTimerNs() : 0ull;
           bars->sched_tile[slot][0] = tn; bars->sched_tile[slot][1] = tpm;
           bars->sched_tile[slot][2] = valid; bars->sched_tile[slot][3] = static_cast<int32_t>(ticket);
-          bars->sched_tile[slot][4] = tz_slice;
+          bars->sched_tile[slot][4] = tz_slice; bars->sched_tile[slot][5] = nslices;
+          bars->sched_tile[slot][6] = static_cast<int32_t>(t.ws_tile);
           bars->sched_time[slot] = now;
           // the same record into the peer's ring, then signal both
           const uint32_t pt = peer_sched_tile0 + slot * 32;
           st_cluster_u32(pt, static_cast<uint32_t>(tn)); st_cluster_u32(pt + 4, static_cast<uint32_t>(tpm));
           st_cluster_u32(pt + 8, static_cast<uint32_t>(valid)); st_cluster_u32(pt + 12, ticket);
-          st_cluster_u32(pt + 16, static_cast<uint32_t>(tz_slice));
+          st_cluster_u32(pt + 16, static_cast<uint32_t>(tz_slice)); st_cluster_u32(pt + 20, static_cast<uint32_t>(nslices));
+          st_cluster_u32(pt + 24, t.ws_tile);
           st_cluster_u32(peer_sched_time0 + slot * 8, static_cast<uint32_t>(now));
           st_cluster_u32(peer_sched_time0 + slot * 8 + 4, static_cast<uint32_t>(now >> 32));
           mbar_arrive(&bars->sched_full[slot]);
@@ -1170,7 +1263,7 @@ cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         } else {
           if (!mbar_wait_cluster(&bars->sched_full[slot], sph, ctx)) { ok = false; break; }
           tn = bars->sched_tile[slot][0]; tpm = bars->sched_tile[slot][1]; valid = bars->sched_tile[slot][2];
-          tz_slice = bars->sched_tile[slot][4];
+          tz_slice = bars->sched_tile[slot][4]; nslices = bars->sched_tile[slot][5];
           mbar_arrive_cluster(leader_sched_empty0 + slot * 8);
         }
         sched_it++;
@@ -1181,9 +1274,9 @@ cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         const int nb_off = n_off + static_cast<int>(rank) * (BN / 2);               // this CTA's half of B
         uint32_t ready_end = 0;
         long long wait_empty = 0;
-        const int kb_begin = tz_slice * p.k_blocks_per_split;
-        const int kb_end = kb_begin + p.k_blocks_per_split < p.num_k_blocks ? kb_begin + p.k_blocks_per_split
-                                                                           : p.num_k_blocks;
+        const int kb_per_slice = (p.num_k_blocks + nslices - 1) / nslices;
+        const int kb_begin = tz_slice * kb_per_slice;
+        const int kb_end = kb_begin + kb_per_slice < p.num_k_blocks ? kb_begin + kb_per_slice : p.num_k_blocks;
         for (int kb = kb_begin; kb < kb_end; kb++) {
           const uint32_t s = fills % C::kStages, ph = (fills / C::kStages) & 1u;
           const long long c0 = p.trace ? clock64() : 0;
@@ -1290,6 +1383,7 @@ cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         const int valid = bars->sched_tile[slot][2];
         const uint32_t ticket = static_cast<uint32_t>(bars->sched_tile[slot][3]);
         const int slice = bars->sched_tile[slot][4];
+        const int nslices = bars->sched_tile[slot][5];
         mbar_arrive(&bars->sched_empty[slot]);
         sched_it++;
         if (!valid) break;
@@ -1300,9 +1394,9 @@ cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         const long long t_acc = p.trace ? clock64() : 0;
         long long wait_full = 0;
         const uint32_t d_tmem = tmem_base + acc * C::kAccCols;
-        const int kb_first = slice * p.k_blocks_per_split;
-        const int kb_count = kb_first + p.k_blocks_per_split < p.num_k_blocks ? p.k_blocks_per_split
-                                                                             : p.num_k_blocks - kb_first;
+        const int kb_per_slice = (p.num_k_blocks + nslices - 1) / nslices;
+        const int kb_first = slice * kb_per_slice;
+        const int kb_count = kb_first + kb_per_slice < p.num_k_blocks ? kb_per_slice : p.num_k_blocks - kb_first;
         for (int kb = 0; kb < kb_count; kb++) {
           const uint32_t s = drains % C::kStages, ph = (drains / C::kStages) & 1u;
           const long long c0 = p.trace ? clock64() : 0;
@@ -1350,7 +1444,7 @@ cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     const int quarter = ew & 3;
     const int half = ew >> 2;
     uint8_t* buf = staging + ew * (32 * 128);
-    uint32_t sched_it = 0, acc_it = 0, post_it = 0;
+    uint32_t sched_it = 0, acc_it = 0, post_it = 0, split_it = 0;
     bool ok = true;
     while (ok) {
       const uint32_t slot = sched_it % kSchedSlots, sph = (sched_it / kSchedSlots) & 1u;
@@ -1358,6 +1452,9 @@ cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
       const int tile_n = bars->sched_tile[slot][0];
       const int pair_m = bars->sched_tile[slot][1];
       const int valid = bars->sched_tile[slot][2];
+      const uint32_t nslices = static_cast<uint32_t>(bars->sched_tile[slot][5]);
+      const uint32_t ws_slot = static_cast<uint32_t>(bars->sched_tile[slot][6]) * nslices;   // the tile's first slot
+      const uint32_t slice = static_cast<uint32_t>(bars->sched_tile[slot][4]);
       const uint32_t ticket = static_cast<uint32_t>(bars->sched_tile[slot][3]);
       const unsigned long long t_draw = bars->sched_time[slot];
       __syncwarp();
@@ -1372,13 +1469,19 @@ cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
       const int m_off = pair_m * (2 * kBlockM) + static_cast<int>(rank) * kBlockM;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * C::kAccCols;
 
-      if (p.split_k > 1) {
+      if (nslices > 1u) {
+        // One K slice of the tile: add it to the workspace; the pair that brings the last slice finalises.
+        // `post` is also used by unsplit tiles, the two split-K barriers only here: separate phase counters.
         bool last = false;
-        ok = splitk_epilogue<BN>(p, &tmWS, buf, bars, ctx, t_row, n_off, m_off, quarter, half, ew, lane, post_it & 1u, nullptr,
-                                 leader_tmem_empty0 + acc * 8, static_cast<__half*>(p.d), p.ldd, &last);
+        ok = splitk_epilogue<BN>(p, &tmWS, buf, bars, ctx, t_row, n_off, m_off, quarter, half, ew, lane, post_it & 1u,
+                                 split_it & 1u, nslices, nullptr, leader_tmem_empty0 + acc * 8,
+                                 static_cast<__half*>(p.d), p.ldd, &last,
+                                 reinterpret_cast<float4*>(p.splitk_ws) + static_cast<size_t>(ws_slot) * kPairSlotVec4 +
+                                     rank * (kPairSlotVec4 / 2),
+                                 slice, &tmD);
         acc_it++;
         if (ew == 0 && lane == 0) {
-          if (!mbar_wait(&bars->splitk_done, post_it & 1u, ctx)) ok = false;
+          if (!mbar_wait(&bars->splitk_done, split_it & 1u, ctx)) ok = false;
           else if (last && p.is_producer) {
             const uint32_t idx = cusync::eval::tileIndex(st.out_policy, static_cast<uint32_t>(m_off),
                                                          static_cast<uint32_t>(n_off), st.grid.x, st.grid.y);
@@ -1389,7 +1492,15 @@ cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
           }
         }
         post_it++;
+        split_it++;
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (p.trace && ew == 0 && lane == 0 && 2 * ticket + rank < p.trace_capacity) {
+          uint32_t smid;
+          asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+          unsigned long long* rec = p.trace + 8ull * (2 * ticket + rank);
+          rec[0] = t_draw; rec[1] = t_mma_done; rec[2] = cusync::globalTimerNs();
+          rec[3] = (static_cast<unsigned long long>(smid) << 32) | blockIdx.x;
+        }
         continue;
       }
       epilogue_store_rows<BN, false>(p, &tmD, buf, t_row, n_off, m_off + quarter * 32, half, lane);
@@ -1562,8 +1673,10 @@ struct cusync_gemm_plan {
   cusync_stage_t* own_stage;   // created when the caller passes no stage
   cusync_stage_t* stage;
   bool pair;                   // CTA-pair kernel (tcgen05 cta_group::2, 256 x 256 tiles per pair)
-  cusync_dim3_t* pair_order;   // device: schedule over pair tiles
+  PairUnit* pair_order;        // device: schedule over pair work units
   int split_k;
+  int tail_split;              // K slices of the tiles of the last, partial wave (pair kernel); 1 = none
+  size_t ws_slots;             // pair kernel: 256 x 256 fp32 workspace slots, one per (split tile, slice)
   float* splitk_ws;            // device: fp32 partial sums [tiles_m * 128, n], zero between launches
   uint32_t* splitk_arrivals;   // device: per-tile slice counters, zero between launches
 };
@@ -1605,8 +1718,8 @@ int setup_pair(cusync_gemm_plan* pl, const cusync_stage_view_t& view, uint32_t c
   const uint32_t pair_rows = static_cast<uint32_t>((p.tiles_m + 1) / 2);
   const uint32_t tiles_n = static_cast<uint32_t>(p.tiles_n);
   const uint32_t split = static_cast<uint32_t>(pl->split_k);
-  const uint32_t num_pairs = pair_rows * tiles_n * split;   // work units: pair tile x K slice, slice outermost
-  std::vector<cusync_dim3_t> order(num_pairs, cusync_dim3_t{num_pairs, 0, 0});
+  const uint32_t num_units = pair_rows * tiles_n * split;   // pair tile x uniform K slice, slice outermost
+  std::vector<PairUnit> order(num_units, PairUnit{num_units, 0, 0, 0});
   const int kind = view.order & 0xff;
   uint32_t group = static_cast<uint32_t>(view.order) >> 8;
   group = group > 1 ? group / 2 : 1;   // a group of R 128-row tiles is R/2 pair rows
@@ -1616,23 +1729,15 @@ int setup_pair(cusync_gemm_plan* pl, const cusync_stage_view_t& view, uint32_t c
         const uint32_t id = kind == CUSYNC_ORDER_GROUPED_ROWS
                                 ? cusync::eval::groupedBlockIndex(group, tiles_n, pair_rows, x, y, z)
                                 : cusync::eval::blockIndex(tiles_n, pair_rows, x, y, z);
-        if (id >= num_pairs || order[id].x != num_pairs) return CUSYNC_ERROR_INVALID_LINEAR_BLOCK_INDEX;
-        order[id] = cusync_dim3_t{x, y, z};
+        if (id >= num_units || order[id].x != num_units) return CUSYNC_ERROR_INVALID_LINEAR_BLOCK_INDEX;
+        order[id] = PairUnit{x, y, z | (split << 16), y * tiles_n + x};
       }
-  if (cudaMalloc(&pl->pair_order, sizeof(cusync_dim3_t) * num_pairs) != cudaSuccess ||
-      cudaMemcpy(pl->pair_order, order.data(), sizeof(cusync_dim3_t) * num_pairs, cudaMemcpyHostToDevice) !=
-          cudaSuccess) {
-    (void)cudaGetLastError();
-    return CUSYNC_ERROR_CUDA;
-  }
-  p.pair_order = pl->pair_order;
-  p.num_pairs = static_cast<int32_t>(num_pairs);
 
   // How many 2-CTA clusters fit on the device at once (one CTA per SM).
   int max_clusters = 0;
   cudaLaunchConfig_t cfg;
   std::memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = dim3(2 * num_pairs, 1, 1);
+  cfg.gridDim = dim3(2 * num_units, 1, 1);
   cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = PairCfg::kSmemBytes;
   cudaLaunchAttribute attr;
@@ -1644,8 +1749,45 @@ int setup_pair(cusync_gemm_plan* pl, const cusync_stage_view_t& view, uint32_t c
     max_clusters = cusync_b200_sm_count() / 2;
     if (max_clusters <= 0) max_clusters = 74;
   }
-  uint32_t clusters = num_pairs < static_cast<uint32_t>(max_clusters) ? num_pairs : static_cast<uint32_t>(max_clusters);
-  if (cta_cap / 2 >= 1 && clusters > cta_cap / 2) clusters = cta_cap / 2;
+  uint32_t capacity = static_cast<uint32_t>(max_clusters);
+  if (cta_cap / 2 >= 1 && capacity > cta_cap / 2) capacity = cta_cap / 2;
+
+  // Tail split: the tiles left over after the last full wave of `capacity` pair tiles would keep only some
+  // of the pairs busy for a whole tile's time.  Cut each of them into K slices (the same fp32 workspace
+  // and last-arrival finalisation as uniform split-K), so that the tail is spread over all pairs.
+  pl->tail_split = 1;
+  pl->ws_slots = split > 1 ? static_cast<size_t>(pair_rows) * tiles_n * split : 0;
+  if (split == 1 && pl->desc.tail_split != 1) {
+    const uint32_t tail = num_units % capacity;
+    int best = 1;
+    if (pl->desc.tail_split > 1) best = tail ? pl->desc.tail_split : 1;
+    // Left to choose (0), the tail is not split: on B200 the split tail measured slower at every GPT-3 MLP
+    // shape (the main loop is bound by L2 -> SM operand traffic and the power cap, so idle SM pairs in the
+    // last wave are not free throughput, and the extra fp32 round trip through the workspace is not paid back).
+    if (best > 1) {
+      // whole ring stages per slice; no slice may be left empty by the rounding
+      const int per = (p.num_k_blocks + best - 1) / best;
+      best = (p.num_k_blocks + per - 1) / per;
+    }
+    if (best > 1 && tail) {
+      std::vector<PairUnit> cut(order.begin(), order.begin() + (num_units - tail));
+      for (uint32_t i = num_units - tail; i < num_units; i++)
+        for (uint32_t sl = 0; sl < static_cast<uint32_t>(best); sl++)
+          cut.push_back(PairUnit{order[i].x, order[i].y, sl | (static_cast<uint32_t>(best) << 16), i - (num_units - tail)});
+      order.swap(cut);
+      pl->tail_split = best;
+      pl->ws_slots = static_cast<size_t>(tail) * best;
+    }
+  }
+  const uint32_t num_pairs = static_cast<uint32_t>(order.size());
+  if (cudaMalloc(&pl->pair_order, sizeof(PairUnit) * num_pairs) != cudaSuccess ||
+      cudaMemcpy(pl->pair_order, order.data(), sizeof(PairUnit) * num_pairs, cudaMemcpyHostToDevice) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return CUSYNC_ERROR_CUDA;
+  }
+  p.pair_order = pl->pair_order;
+  p.num_pairs = static_cast<int32_t>(num_pairs);
+  uint32_t clusters = num_pairs < capacity ? num_pairs : capacity;
   pl->num_ctas = 2 * clusters;
   return CUSYNC_SUCCESS;
 }
@@ -1876,6 +2018,7 @@ int cusync_gemm_plan_create(cusync_gemm_plan_t** out, const cusync_gemm_desc_t* 
   int sms = cusync_b200_sm_count();
   if (sms <= 0) sms = 148;
   if (d.split_k < 0 || d.split_k > 64 || (dual && d.split_k > 1)) { delete pl; return CUSYNC_ERROR_UNSUPPORTED; }
+  if (d.tail_split < 0 || d.tail_split > 16) { delete pl; return CUSYNC_ERROR_INVALID_ARGUMENT; }
   pl->split_k = d.split_k > 0 ? d.split_k : auto_split_k(d.m, d.n, d.k, pl->tile_n, dual, pl->pair, sms);
 
   GemmParams& p = pl->params;
@@ -1936,8 +2079,21 @@ int cusync_gemm_plan_create(cusync_gemm_plan_t** out, const cusync_gemm_desc_t* 
   pl->num_ctas = static_cast<uint32_t>(p.num_tiles) < cap ? static_cast<uint32_t>(p.num_tiles) : cap;
 
   int rc = CUSYNC_SUCCESS;
-  if (pl->split_k > 1) {
-    const size_t ws_bytes = static_cast<size_t>(p.tiles_m) * kBlockM * static_cast<size_t>(d.n) * sizeof(float);
+  const void* kernel_fn = pl->pair ? reinterpret_cast<const void*>(cusync_gemm_pair_kernel)
+                                   : reinterpret_cast<const void*>(pl->kernel.fn);
+  if (rc == CUSYNC_SUCCESS &&
+      cudaFuncSetAttribute(kernel_fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(pl->kernel.smem)) != cudaSuccess) {
+    (void)cudaGetLastError();
+    rc = CUSYNC_ERROR_CUDA;
+  }
+  pl->tail_split = 1;
+  if (rc == CUSYNC_SUCCESS && pl->pair) rc = setup_pair(pl, view, cap);
+  if (rc == CUSYNC_SUCCESS && (pl->split_k > 1 || pl->tail_split > 1)) {
+    // 1-CTA kernel: one [m, n] fp32 tile set that the slices reduce-add into and the finaliser zeroes again;
+    // CTA-pair kernel: one 256 x 256 slot per slice of every split tile (needs no zeroing).
+    const size_t ws_bytes = pl->pair ? pl->ws_slots * (2 * kBlockM) * kPairBN * sizeof(float)
+                                     : static_cast<size_t>(p.tiles_m) * kBlockM * static_cast<size_t>(d.n) * sizeof(float);
     const size_t cnt_bytes = static_cast<size_t>(p.tiles_m) * p.tiles_n * sizeof(uint32_t);
     if (cudaMalloc(&pl->splitk_ws, ws_bytes) != cudaSuccess || cudaMemset(pl->splitk_ws, 0, ws_bytes) != cudaSuccess ||
         cudaMalloc(&pl->splitk_arrivals, cnt_bytes) != cudaSuccess ||
@@ -1947,17 +2103,11 @@ int cusync_gemm_plan_create(cusync_gemm_plan_t** out, const cusync_gemm_desc_t* 
     }
     p.splitk_ws = pl->splitk_ws;
     p.splitk_arrivals = pl->splitk_arrivals;
-    if (rc == CUSYNC_SUCCESS && !make_map_f32(&pl->tmWS, pl->splitk_ws, d.m, d.n, d.n)) rc = CUSYNC_ERROR_CUDA;
+    if (rc == CUSYNC_SUCCESS) {
+      // (the pair kernel writes its slots with plain stores and needs no map)
+      if (!pl->pair && !make_map_f32(&pl->tmWS, pl->splitk_ws, d.m, d.n, d.n)) rc = CUSYNC_ERROR_CUDA;
+    }
   }
-  const void* kernel_fn = pl->pair ? reinterpret_cast<const void*>(cusync_gemm_pair_kernel)
-                                   : reinterpret_cast<const void*>(pl->kernel.fn);
-  if (rc == CUSYNC_SUCCESS &&
-      cudaFuncSetAttribute(kernel_fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           static_cast<int>(pl->kernel.smem)) != cudaSuccess) {
-    (void)cudaGetLastError();
-    rc = CUSYNC_ERROR_CUDA;
-  }
-  if (rc == CUSYNC_SUCCESS && pl->pair) rc = setup_pair(pl, view, cap);
   if (rc == CUSYNC_SUCCESS) rc = build_maps(pl);
   if (rc != CUSYNC_SUCCESS) {
     if (pl->own_stage) cusync_stage_destroy(pl->own_stage);
@@ -1988,6 +2138,8 @@ int cusync_gemm_plan_update(cusync_gemm_plan_t* pl, const void* a, const void* b
 }
 
 uint32_t cusync_gemm_plan_num_ctas(const cusync_gemm_plan_t* pl) { return pl ? pl->num_ctas : 0; }
+
+int cusync_gemm_plan_tail_split(const cusync_gemm_plan_t* pl) { return pl && pl->tail_split > 1 ? pl->tail_split : 1; }
 
 int cusync_gemm_plan_set_trace(cusync_gemm_plan_t* pl, void* device_buffer, uint32_t capacity_tiles) {
   if (!pl) return CUSYNC_ERROR_NOT_INITIALIZED;

@@ -23,7 +23,8 @@ struct cusync_mlp {
 
 namespace {
 
-void fill_gemm1(const cusync_mlp_desc_t& d, int tile_n, int split_k, cusync_stage_t* stage, cusync_gemm_desc_t* g) {
+void fill_gemm1(const cusync_mlp_desc_t& d, int tile_n, int split_k, int tail_split, cusync_stage_t* stage,
+                cusync_gemm_desc_t* g) {
   std::memset(g, 0, sizeof(*g));
   g->m = d.batch; g->n = d.ffn; g->k = d.hidden;
   g->a = d.x; g->lda = d.hidden;
@@ -32,10 +33,12 @@ void fill_gemm1(const cusync_mlp_desc_t& d, int tile_n, int split_k, cusync_stag
   g->d = d.h; g->ldd = d.ffn;
   g->b_layout = CUSYNC_B_ROW_MAJOR_KN;
   g->epilogue = d.model == CUSYNC_MLP_LLAMA ? CUSYNC_EPILOGUE_SILU_MUL_DUAL : CUSYNC_EPILOGUE_GELU_ERF;
-  g->tile_n = tile_n; g->max_ctas = d.max_ctas; g->split_k = split_k; g->cta_pair = d.cta_pair; g->stage = stage;
+  g->tile_n = tile_n; g->max_ctas = d.max_ctas; g->split_k = split_k; g->cta_pair = d.cta_pair; g->tail_split = tail_split;
+  g->stage = stage;
 }
 
-void fill_gemm2(const cusync_mlp_desc_t& d, int tile_n, int split_k, cusync_stage_t* stage, cusync_gemm_desc_t* g) {
+void fill_gemm2(const cusync_mlp_desc_t& d, int tile_n, int split_k, int tail_split, cusync_stage_t* stage,
+                cusync_gemm_desc_t* g) {
   std::memset(g, 0, sizeof(*g));
   g->m = d.batch; g->n = d.hidden; g->k = d.ffn;
   g->a = d.h; g->lda = d.ffn;
@@ -43,7 +46,8 @@ void fill_gemm2(const cusync_mlp_desc_t& d, int tile_n, int split_k, cusync_stag
   g->d = d.y; g->ldd = d.hidden;
   g->b_layout = CUSYNC_B_ROW_MAJOR_KN;
   g->epilogue = CUSYNC_EPILOGUE_NONE;
-  g->tile_n = tile_n; g->max_ctas = d.max_ctas; g->split_k = split_k; g->cta_pair = d.cta_pair; g->stage = stage;
+  g->tile_n = tile_n; g->max_ctas = d.max_ctas; g->split_k = split_k; g->cta_pair = d.cta_pair; g->tail_split = tail_split;
+  g->stage = stage;
 }
 
 void destroy_all(cusync_mlp* m) {
@@ -110,11 +114,11 @@ int cusync_mlp_create(cusync_mlp_t** out, const cusync_mlp_desc_t* desc) {
   if (rc == CUSYNC_SUCCESS) rc = cusync_stage_link(m->prod, m->cons);
 
   cusync_gemm_desc_t g;
-  if (rc == CUSYNC_SUCCESS) { fill_gemm1(d, m->tile_n1, m->split_k1, m->prod, &g); rc = cusync_gemm_plan_create(&m->sync1, &g); }
-  if (rc == CUSYNC_SUCCESS) { fill_gemm2(d, m->tile_n2, m->split_k2, m->cons, &g); rc = cusync_gemm_plan_create(&m->sync2, &g); }
-  if (rc == CUSYNC_SUCCESS) { fill_gemm1(d, m->tile_n1, m->split_k1, nullptr, &g); rc = cusync_gemm_plan_create(&m->plain1, &g); }
+  if (rc == CUSYNC_SUCCESS) { fill_gemm1(d, m->tile_n1, m->split_k1, d.tail_split_sync1, m->prod, &g); rc = cusync_gemm_plan_create(&m->sync1, &g); }
+  if (rc == CUSYNC_SUCCESS) { fill_gemm2(d, m->tile_n2, m->split_k2, d.tail_split_sync2, m->cons, &g); rc = cusync_gemm_plan_create(&m->sync2, &g); }
+  if (rc == CUSYNC_SUCCESS) { fill_gemm1(d, m->tile_n1, m->split_k1, d.tail_split_plain1, nullptr, &g); rc = cusync_gemm_plan_create(&m->plain1, &g); }
   if (rc == CUSYNC_SUCCESS) rc = cusync_stage_create(&m->plain_stage2, grid2, ts, order2, &none, &none, CUSYNC_OPT_NONE);
-  if (rc == CUSYNC_SUCCESS) { fill_gemm2(d, m->tile_n2, m->split_k2, m->plain_stage2, &g); rc = cusync_gemm_plan_create(&m->plain2, &g); }
+  if (rc == CUSYNC_SUCCESS) { fill_gemm2(d, m->tile_n2, m->split_k2, d.tail_split_plain2, m->plain_stage2, &g); rc = cusync_gemm_plan_create(&m->plain2, &g); }
   if (rc != CUSYNC_SUCCESS) { destroy_all(m); return rc; }
   *out = m;
   return CUSYNC_SUCCESS;
@@ -182,6 +186,13 @@ int cusync_mlp_config(const cusync_mlp_t* m, int32_t* out6) {
   out6[2] = static_cast<int32_t>(cusync_gemm_plan_num_ctas(m->sync1));
   out6[3] = static_cast<int32_t>(cusync_gemm_plan_num_ctas(m->sync2));
   out6[4] = m->split_k1; out6[5] = m->split_k2;
+  return CUSYNC_SUCCESS;
+}
+
+int cusync_mlp_tail_splits(const cusync_mlp_t* m, int32_t* out4) {
+  if (!m || !out4) return CUSYNC_ERROR_NOT_INITIALIZED;
+  out4[0] = cusync_gemm_plan_tail_split(m->sync1); out4[1] = cusync_gemm_plan_tail_split(m->sync2);
+  out4[2] = cusync_gemm_plan_tail_split(m->plain1); out4[3] = cusync_gemm_plan_tail_split(m->plain2);
   return CUSYNC_SUCCESS;
 }
 

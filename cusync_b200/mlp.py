@@ -24,7 +24,7 @@ class MLPShard:
     """x[B,H] -> y[B,H] through W1 (and V) [H,F] and W2 [F,H]; fp16, fp32 accumulate."""
 
     def __init__(self, model, batch, x, w1, w2, v=None, policy="rowsync", opts=0, tile_n1=0, tile_n2=0, max_ctas=0,
-                 group_rows2=0, cta_pair=0, split_k1=0, split_k2=0):
+                 group_rows2=0, cta_pair=0, split_k1=0, split_k2=0, tail_split=(0, 0, 0, 0)):
         import torch
         self.model = L.MLP_GPT3 if model == "gpt3" else L.MLP_LLAMA
         self.batch, self.hidden, self.ffn = batch, w1.shape[0], w1.shape[1]
@@ -33,13 +33,17 @@ class MLPShard:
         self.h = torch.empty((batch, self.ffn), device=x.device, dtype=torch.half)
         self.y = torch.empty((batch, self.hidden), device=x.device, dtype=torch.half)
         d = L.MlpDesc(self.model, batch, self.hidden, self.ffn, POLICIES[policy], opts, tile_n1, tile_n2, split_k1,
-                      split_k2, max_ctas, cta_pair, group_rows2, x.data_ptr(), w1.data_ptr(), v.data_ptr() if v is not None else None, w2.data_ptr(),
+                      split_k2, max_ctas, cta_pair, group_rows2, tail_split[0], tail_split[1], tail_split[2], tail_split[3],
+                      x.data_ptr(), w1.data_ptr(), v.data_ptr() if v is not None else None, w2.data_ptr(),
                       self.h.data_ptr(), self.y.data_ptr())
         self._h = C.c_void_p()
         L.check(L.lib().cusync_mlp_create(C.byref(self._h), C.byref(d)), "cusync_mlp_create")
         cfg = (C.c_int32 * 6)()
         L.lib().cusync_mlp_config(self._h, cfg)
         self.tile_n1, self.tile_n2, self.ctas1, self.ctas2, self.split_k1, self.split_k2 = list(cfg)
+        ts = (C.c_int32 * 4)()
+        L.lib().cusync_mlp_tail_splits(self._h, ts)
+        self.tail_splits = tuple(ts)   # (synchronised GEMM 1, 2, stream-ordered GEMM 1, 2)
 
     def run_stream_ordered(self, stream):
         L.check(L.lib().cusync_mlp_run_stream_ordered(self._h, _stream_ptr(stream)), "run_stream_ordered")

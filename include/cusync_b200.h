@@ -216,6 +216,11 @@ typedef struct cusync_gemm_desc {
   int32_t cta_pair;                /* 0 = choose; 1 = one CTA per 128 x tile_n tile; 2 = CTA pairs (tcgen05
                                       cta_group::2): two CTAs share a 256 x 256 tile, each loading half of B.
                                       Needs tile_n 256 and a single B operand.  Semaphores stay per 128-row tile. */
+  int32_t tail_split;              /* CTA-pair kernel without uniform split-K: K slices for the tiles of the last,
+                                      partial wave, so that the tail occupies every SM pair (the remedy the reference
+                                      gets from Stream-K, src/ml-bench/transformer/mlp.cu:137-207).  0 = choose
+                                      (today: none, it measured slower), 1 = none, 2..16 = forced.  The stage grid is unchanged (z = 1); a split tile
+                                      posts once, from the pair that adds its last slice. */
   cusync_stage_t* stage;           /* NULL = no tile synchronisation (stream-ordered use) */
 } cusync_gemm_desc_t;
 
@@ -239,6 +244,8 @@ CUSYNC_API int cusync_gemm_plan_update(cusync_gemm_plan_t* plan, const void* a, 
                             const void* b2, void* d);
 /* run(bool overlap, int*, cudaStream_t) (gemm/device/cusyncgemm.h:525-563). */
 CUSYNC_API int cusync_gemm_run(cusync_gemm_plan_t* plan, cusync_stream_t stream);
+/* K slices the plan uses for the tiles of its last partial wave (1 = none). */
+CUSYNC_API int cusync_gemm_plan_tail_split(const cusync_gemm_plan_t* plan);
 /* Allocation-free GEMM.  It has no counterpart in the reference.
  *
  * For callers that must not allocate device memory at the point of the call: a plug-in inside a
@@ -348,6 +355,8 @@ typedef struct cusync_mlp_desc {
   int32_t max_ctas;              /* 0 = one per SM */
   int32_t cta_pair;              /* as cusync_gemm_desc_t.cta_pair, for both GEMMs */
   int32_t group_rows2;           /* > 0: the consumer takes its tiles in CUSYNC_ORDER_GROUPED(group_rows2) order */
+  int32_t tail_split_sync1, tail_split_sync2;    /* cusync_gemm_desc_t.tail_split of the two synchronised GEMMs ... */
+  int32_t tail_split_plain1, tail_split_plain2;  /* ... and of the two stream-ordered ones: 0 = choose, 1 = none */
   const void* x; const void* w1; const void* v; const void* w2;
   void* h; void* y;
 } cusync_mlp_desc_t;
@@ -377,6 +386,8 @@ CUSYNC_API cusync_stage_t* cusync_mlp_stage(cusync_mlp_t* mlp, int which);
 CUSYNC_API int cusync_mlp_set_trace(cusync_mlp_t* mlp, void* trace1, uint32_t capacity1, void* trace2, uint32_t capacity2);
 /* Configuration in use: out[0..5] = tile_n1, tile_n2, ctas1, ctas2, split_k1, split_k2. */
 CUSYNC_API int cusync_mlp_config(const cusync_mlp_t* mlp, int32_t* out6);
+/* Tail splits in use: out[0..3] = synchronised GEMM 1, 2, stream-ordered GEMM 1, 2. */
+CUSYNC_API int cusync_mlp_tail_splits(const cusync_mlp_t* mlp, int32_t* out4);
 
 /* Library / device information. */
 CUSYNC_API const char* cusync_b200_version(void);

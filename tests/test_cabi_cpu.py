@@ -121,13 +121,13 @@ def test_default_tile_n_table():
 def test_plan_create_rejects_bad_arguments_without_a_device():
     bh.build_library()
     plan = C.c_void_p()
-    d = L.GemmDesc(0, 16, 16, 16, 16, 16, 16, None, 16, 16, 0, 0, 0, 0, 0, 0, None)
+    d = L.GemmDesc(0, 16, 16, 16, 16, 16, 16, None, 16, 16, 0, 0, 0, 0, 0, 0, 0, None)
     assert L.lib().cusync_gemm_plan_create(C.byref(plan), C.byref(d)) == L.ERROR_INVALID_ARGUMENT
-    d = L.GemmDesc(128, 128, 128, 0x1000, 100, 0x2000, 128, None, 0x3000, 128, 0, 0, 0, 0, 0, 0, None)   # lda % 8 != 0
+    d = L.GemmDesc(128, 128, 128, 0x1000, 100, 0x2000, 128, None, 0x3000, 128, 0, 0, 0, 0, 0, 0, 0, None)   # lda % 8 != 0
     assert L.lib().cusync_gemm_plan_create(C.byref(plan), C.byref(d)) == L.ERROR_UNSUPPORTED
-    d = L.GemmDesc(128, 128, 128, 0x1008, 128, 0x2000, 128, None, 0x3000, 128, 0, 0, 0, 0, 0, 0, None)   # misaligned A
+    d = L.GemmDesc(128, 128, 128, 0x1008, 128, 0x2000, 128, None, 0x3000, 128, 0, 0, 0, 0, 0, 0, 0, None)   # misaligned A
     assert L.lib().cusync_gemm_plan_create(C.byref(plan), C.byref(d)) == L.ERROR_UNSUPPORTED
-    d = L.GemmDesc(128, 128, 128, 0x1000, 128, 0x2000, 128, None, 0x3000, 128, 0, 3, 0, 0, 0, 0, None)   # dual without b2
+    d = L.GemmDesc(128, 128, 128, 0x1000, 128, 0x2000, 128, None, 0x3000, 128, 0, 3, 0, 0, 0, 0, 0, None)   # dual without b2
     assert L.lib().cusync_gemm_plan_create(C.byref(plan), C.byref(d)) == L.ERROR_INVALID_ARGUMENT
     assert L.lib().cusync_stage_link(None, None) == L.ERROR_NOT_INITIALIZED
     assert L.lib().cusync_stage_increment_iter(None) == L.ERROR_NOT_INITIALIZED

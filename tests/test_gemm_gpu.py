@@ -26,7 +26,7 @@ def _rand(shape, seed, scale=1.0, dist="uniform"):
 
 
 def _gemm(a, b, epi=L.EPILOGUE_NONE, tile_n=0, b_layout=L.B_ROW_MAJOR_KN, max_ctas=0, b2=None, stage=None,
-          cta_pair=0, split_k=1, runs=1):
+          cta_pair=0, split_k=1, runs=1, tail_split=0):
     M, K = a.shape
     N = b.shape[1]
     d = torch.full((M, N), float("nan"), device="cuda", dtype=torch.half)
@@ -38,7 +38,7 @@ def _gemm(a, b, epi=L.EPILOGUE_NONE, tile_n=0, b_layout=L.B_ROW_MAJOR_KN, max_ct
     g = cs.Gemm()
     rc = g.initialize(cs.GemmArguments(stage, (M, N, K), a, bdev, d, epilogue=epi, ref_b2=b2dev, b_layout=b_layout,
                                        tile_n=tile_n, max_ctas=max_ctas, cta_pair=cta_pair,
-                                       split_k_slices=split_k))
+                                       split_k_slices=split_k, tail_split=tail_split))
     assert rc == L.SUCCESS, L.ERROR_NAMES[rc]
     for _ in range(runs):
         d.fill_(float("nan"))
@@ -117,6 +117,33 @@ def test_cta_pair_gemm_epilogue_and_few_clusters():
                                          max_ctas=6, cta_pair=2, split_k_slices=1)) == L.SUCCESS
     assert g.num_ctas() == 6
     for _ in range(3):
+        d.fill_(float("nan"))
+        assert g.run(stream=torch.cuda.current_stream()) == L.SUCCESS
+        torch.cuda.synchronize()
+        assert o.max_rel_err(d.cpu().numpy(), ref) <= TOL
+    g.destroy()
+
+
+@pytest.mark.parametrize("M,N,K,max_ctas,tail_split,expect", [
+    (1024, 2048, 2048, 6, 3, 3),     # 32 pair tiles on 3 clusters: 2 left over, cut into 3 slices each
+    (1024, 2048, 2048, 6, 0, 1),     # left to the library: no split (it measured slower)
+    (1000, 960, 1024, 6, 2, 2),      # ragged edges; 16 pair tiles on 3 clusters: 1 left over, 2 slices forced
+    (1024, 2048, 2048, 6, 1, 1),     # switched off
+    (512, 1024, 1024, 4, 4, 1),      # 8 pair tiles on 2 clusters: nothing left over, nothing to split
+])
+@pytest.mark.parametrize("layout", [L.B_ROW_MAJOR_KN, L.B_ROW_MAJOR_NK])
+def test_tail_split_gemm_matches_oracle(M, N, K, max_ctas, tail_split, expect, layout):
+    a = _rand((M, K), 61, dist="normal")
+    b = _rand((K, N), 62, scale=0.05, dist="normal")
+    ref = o.gemm_f16(a.cpu().numpy(), b.cpu().numpy(), o.EPI_GELU_ERF)
+    bdev = b.t().contiguous() if layout == L.B_ROW_MAJOR_NK else b
+    d = torch.empty((M, N), device="cuda", dtype=torch.half)
+    g = cs.Gemm()
+    assert g.initialize(cs.GemmArguments(None, (M, N, K), a, bdev, d, epilogue=L.EPILOGUE_GELU_ERF, b_layout=layout,
+                                         tile_n=256, max_ctas=max_ctas, cta_pair=2, split_k_slices=1,
+                                         tail_split=tail_split)) == L.SUCCESS
+    assert g.tail_split() == expect
+    for _ in range(3):           # the workspace and the arrival counters re-arm themselves
         d.fill_(float("nan"))
         assert g.run(stream=torch.cuda.current_stream()) == L.SUCCESS
         torch.cuda.synchronize()
@@ -231,14 +258,16 @@ def test_linearity_at_full_gpt3_width():
     M, K, N = 256, 12288, 6144
     a = _rand((M, K), 10, dist="normal", scale=0.5)
     b = _rand((K, N), 11, scale=0.02, dist="normal")
-    d1, _ = _gemm(a, b, tile_n=256)
-    d2, _ = _gemm(a * 2, b, tile_n=256)
+    # (24 pair tiles, each cut into 3 K slices: the slices' partial sums are added in slice order whichever
+    # finishes last, so the results stay bit-reproducible)
+    d1, _ = _gemm(a, b, tile_n=256, tail_split=3)
+    d2, _ = _gemm(a * 2, b, tile_n=256, tail_split=3)
     # exact wherever the result is a normal fp16 number (subnormal outputs round differently after doubling)
     normal = d1.abs() >= 2.0 ** -13
     assert torch.equal(d2[normal], (d1 * 2)[normal])
     assert (d2.float() - 2 * d1.float()).abs().max().item() <= 2.0 ** -23
     perm = torch.randperm(M, generator=torch.Generator().manual_seed(0)).cuda()
-    d3, _ = _gemm(a[perm].contiguous(), b, tile_n=256)
+    d3, _ = _gemm(a[perm].contiguous(), b, tile_n=256, tail_split=3)
     assert torch.equal(d3, d1[perm])
     # 64 sampled rows carried through the oracle
     rows = torch.arange(0, M, 4)
@@ -247,7 +276,7 @@ def test_linearity_at_full_gpt3_width():
 
 
 def _chain(policy_name, M, N1, K1, N2, tile_n1, tile_n2, iters, opts=0, epi1=L.EPILOGUE_NONE, max_ctas=0,
-           wait_kernel=True, seed=20, cta_pair=0):
+           wait_kernel=True, seed=20, cta_pair=0, tail_split=0):
     a = _rand((M, K1), seed, dist="normal")
     w1 = _rand((K1, N1), seed + 1, scale=0.03, dist="normal")
     w2 = _rand((N1, N2), seed + 2, scale=0.03, dist="normal")
@@ -266,9 +295,12 @@ def _chain(policy_name, M, N1, K1, N2, tile_n1, tile_n2, iters, opts=0, epi1=L.E
     assert cs.CuSync.setProducerConsumerPair(prod, cons) == L.SUCCESS
     g1, g2 = cs.Gemm(), cs.Gemm()
     assert g1.initialize(cs.GemmArguments(prod, (M, N1, K1), a, w1, h, epilogue=epi1, tile_n=tile_n1,
-                                          max_ctas=max_ctas, cta_pair=cta_pair, split_k_slices=1)) == L.SUCCESS
+                                          max_ctas=max_ctas, cta_pair=cta_pair, split_k_slices=1,
+                                          tail_split=tail_split)) == L.SUCCESS
     assert g2.initialize(cs.GemmArguments(cons, (M, N2, N1), h, w2, y, tile_n=tile_n2, max_ctas=max_ctas,
-                                          cta_pair=cta_pair, split_k_slices=1)) == L.SUCCESS
+                                          cta_pair=cta_pair, split_k_slices=1, tail_split=tail_split)) == L.SUCCESS
+    if tail_split > 1:
+        assert g1.tail_split() == tail_split and g2.tail_split() == tail_split
     ps, cst = torch.cuda.Stream(priority=-1), torch.cuda.Stream()
     oepi = {L.EPILOGUE_NONE: o.EPI_NONE, L.EPILOGUE_GELU_ERF: o.EPI_GELU_ERF}[epi1]
     href = o.gemm_f16(a.cpu().numpy(), w1.cpu().numpy(), oepi)
@@ -356,6 +388,16 @@ def test_chain_with_cta_pairs(policy, opts):
     # both GEMMs on CTA pairs, few clusters so consumers really wait; M = 640 -> 5 row tiles (odd)
     _chain(policy, 640, 1024, 512, 1024, 256, 256, iters=3, opts=opts, max_ctas=4, cta_pair=2)
     _chain(policy, 512, 1536, 1024, 768, 256, 256, iters=2, opts=opts, epi1=L.EPILOGUE_GELU_ERF, cta_pair=2)
+
+
+@pytest.mark.parametrize("policy", ["row", "tile"])
+def test_chain_with_tail_split_on_both_gemms(policy):
+    # 3 pair rows x 4 column tiles = 12 pair tiles on 5 clusters: the last 2 tiles of either GEMM are cut
+    # into K slices; a split producer tile posts once (from the pair that adds the last slice), a split
+    # consumer tile waits slice by slice.
+    _chain(policy, 640, 1024, 1024, 1024, 256, 256, iters=3, max_ctas=10, cta_pair=2, tail_split=2)
+    _chain(policy, 768, 1024, 2048, 1024, 256, 256, iters=2, max_ctas=10, cta_pair=2, tail_split=4,
+           epi1=L.EPILOGUE_GELU_ERF)
 
 
 def test_chain_without_wait_kernel_small_grids():

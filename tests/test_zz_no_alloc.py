@@ -32,7 +32,7 @@ def _desc(a, b, d, epi, tile_n, b2=None):
     M, K = a.shape
     N = b.shape[1]
     return L.GemmDesc(M, N, K, a.data_ptr(), K, b.data_ptr(), N, b2.data_ptr() if b2 is not None else None,
-                      d.data_ptr(), N, L.B_ROW_MAJOR_KN, epi, tile_n, 0, 1, 1, None)
+                      d.data_ptr(), N, L.B_ROW_MAJOR_KN, epi, tile_n, 0, 1, 1, 0, None)
 
 
 def _plan_based(a, b, epi, tile_n, b2=None):
@@ -90,12 +90,12 @@ def test_noalloc_refuses_more_tiles_than_its_scratch_and_stage_handles():
     d = torch.zeros((128, 128), device="cuda", dtype=torch.half)
     # 12800 x 6464 with 128 x 64 tiles = 100 x 101 = 10100 tiles > 8192: refused before anything is touched
     big = L.GemmDesc(12800, 6464, 64, a.data_ptr(), 64, b.data_ptr(), 6464, None, d.data_ptr(), 6464,
-                     L.B_ROW_MAJOR_KN, L.EPILOGUE_NONE, 64, 0, 0, 0, None)
+                     L.B_ROW_MAJOR_KN, L.EPILOGUE_NONE, 64, 0, 0, 0, 0, None)
     assert L.lib().cusync_gemm_run_noalloc(C.byref(big), stream) == L.ERROR_EXCEEDS_STATIC_SCRATCH
     torch.cuda.synchronize()
     assert (d == 0).all()
     st = cs.CuStage(cs.TransposeXYOrder, (1, 1, 1), (1, 1, 1), cs.NoSync(), cs.NoSync())
     with_stage = L.GemmDesc(128, 128, 64, a.data_ptr(), 64, b.data_ptr(), 128, None, d.data_ptr(), 128,
-                            L.B_ROW_MAJOR_KN, L.EPILOGUE_NONE, 128, 0, 0, 0, st._h)
+                            L.B_ROW_MAJOR_KN, L.EPILOGUE_NONE, 128, 0, 0, 0, 0, st._h)
     assert L.lib().cusync_gemm_run_noalloc(C.byref(with_stage), stream) == L.ERROR_INVALID_ARGUMENT
     st.destroy()
