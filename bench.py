@@ -374,31 +374,18 @@ def main():
             xin = torch.randn((n, 56, 56, 64), generator=g, device=dev).half()
             f1 = (torch.randn((64, 3, 3, 64), generator=g, device=dev) * (2.0 / 576) ** 0.5).half()
             f2 = (torch.randn((64, 3, 3, 64), generator=g, device=dev) * (2.0 / 576) ** 0.5).half()
-            y1 = torch.empty_like(xin); y2 = torch.empty_like(xin)
-            prob = lib_.Conv2dProblemSize(n, 56, 56, 64, 64)
-            grid, tm = prob.grid(), prob.tile_m()
-            prod = lib_.CuStage(lib_.TransposeXYOrder, grid, (1, 1, 1), lib_.NoSync(), lib_.TileSync(lib_.TransposeXYOrder, tm, 64))
-            cons = lib_.CuStage(lib_.TransposeXYOrder, grid, (1, 1, 1), lib_.Conv2DTileSync(lib_.TransposeXYOrder, 3, 3, tm, 64),
-                              lib_.NoSync())
-            L.check(lib_.CuSync.setProducerConsumerPair(prod, cons), "conv link")
-            convs = [lib_.Conv2dFprop() for _ in range(4)]
-            L.check(convs[0].initialize(prod, prob, xin, f1, y1, L.EPILOGUE_RELU), "conv1")
-            L.check(convs[1].initialize(cons, prob, y1, f2, y2, L.EPILOGUE_RELU), "conv2")
-            L.check(convs[2].initialize(None, prob, xin, f1, y1, L.EPILOGUE_RELU), "conv1 plain")
-            L.check(convs[3].initialize(None, prob, y1, f2, y2, L.EPILOGUE_RELU), "conv2 plain")
+            chain = lib_.ConvChain(xin, [f1, f2], relu=True)     # cusync_conv_chain_*: the resnet.cu flow in C
 
             def c_step():
-                ps.wait_stream(cs); convs[0].run(ps); prod.invokeWaitKernel(cs); convs[1].run(cs)
-                prod.incrementIter(); cons.incrementIter()
+                ps.wait_stream(cs); chain.run_cusync([ps, cs])
 
             def o_step():
-                convs[2].run(cs); convs[3].run(cs)
+                chain.run_stream_ordered(cs)
             r = ab(c_step, o_step)
             r["images"] = n
+            r["wait_kernel"] = chain.uses_wait_kernels
             rows.append(r)
-            for c in convs:
-                c.destroy()
-            prod.destroy(); cons.destroy()
+            chain.destroy()
         extras["resnet_conv3x3_chain_conv2dtilesync"] = rows
 
         rows = []

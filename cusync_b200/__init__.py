@@ -8,3 +8,4 @@ from .api import (CuStage, CuSync, NoSync, RowSync, TileSync, StridedTileSync, C
                   ConsecutiveTileSync, IdentityOrder, TransposeXYOrder, GroupedRowsOrder, Optimizations, Gemm, GemmArguments,
                   gemm_tiled_shape, Conv2dFprop, Conv2dProblemSize)
 from .mlp import MLPShard, make_inputs  # noqa: F401,E402
+from .conv import ConvChain  # noqa: F401,E402

@@ -71,6 +71,12 @@ class Conv2dDesc(C.Structure):
                 ("epilogue", C.c_int32), ("max_ctas", C.c_int32), ("stage", C.c_void_p)]
 
 
+class ConvChainDesc(C.Structure):
+    _fields_ = [("num_convs", C.c_int32), ("n", C.c_int32), ("h", C.c_int32), ("w", C.c_int32), ("channels", C.c_int32),
+                ("relu", C.c_int32), ("max_ctas", C.c_int32),
+                ("filters", C.POINTER(C.c_void_p)), ("activations", C.POINTER(C.c_void_p))]
+
+
 class AttnDesc(C.Structure):
     _fields_ = [("batch", C.c_int32), ("seq", C.c_int32), ("heads", C.c_int32), ("head_dim", C.c_int32),
                 ("qkv", C.c_void_p), ("ld_qkv", C.c_int64), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p),
@@ -124,6 +130,12 @@ SIGNATURES = {
     "cusync_conv2d_plan_destroy": (_i, [_vp]),
     "cusync_conv2d_run": (_i, [_vp, _vp]),
     "cusync_conv2d_plan_num_ctas": (_u32, [_vp]),
+    "cusync_conv_chain_create": (_i, [C.POINTER(_vp), C.POINTER(ConvChainDesc)]),
+    "cusync_conv_chain_destroy": (_i, [_vp]),
+    "cusync_conv_chain_run_stream_ordered": (_i, [_vp, _vp]),
+    "cusync_conv_chain_run_cusync": (_i, [_vp, C.POINTER(_vp)]),
+    "cusync_conv_chain_stage": (_vp, [_vp, _i]),
+    "cusync_conv_chain_uses_wait_kernels": (_i, [_vp]),
     "cusync_attn_default_splits": (_i, [C.c_int32] * 3),
     "cusync_attn_plan_create": (_i, [C.POINTER(_vp), C.POINTER(AttnDesc)]),
     "cusync_attn_plan_destroy": (_i, [_vp]),

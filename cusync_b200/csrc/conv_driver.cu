@@ -1,0 +1,129 @@
+// Chain of 3x3 convolutions wired through CuSync stages, plus the stream-ordered baseline built from the same
+// kernels: the flow of the reference driver src/ml-bench/volta_conv2d/resnet.cu (stage typing :107-116, the
+// baseline loop that runs the convolutions back to back on one stream, and the CuSync loop that puts each
+// convolution on its own stream behind a wait kernel and increments the stages' iterations afterwards).
+// Host-only code over the library's own C ABI.  Doing the launches here keeps a whole chain at a handful of
+// microseconds of host time, which matters for these short kernels.
+#include <cstring>
+#include <new>
+
+#include "common.cuh"
+
+namespace { constexpr int kMaxConvs = 8; }
+
+struct cusync_conv_chain {
+  cusync_conv_chain_desc_t desc;
+  int num;
+  cusync_stage_t* stages[kMaxConvs];
+  cusync_conv2d_plan_t* sync[kMaxConvs];    // convolution i with its stage
+  cusync_conv2d_plan_t* plain[kMaxConvs];   // the same kernel without tile synchronisation
+  bool wait_kernels;                        // false: every stage fits on the device at once
+};
+
+namespace {
+
+void destroy_all(cusync_conv_chain* c) {
+  for (int i = 0; i < c->num; i++) {
+    if (c->sync[i]) cusync_conv2d_plan_destroy(c->sync[i]);
+    if (c->plain[i]) cusync_conv2d_plan_destroy(c->plain[i]);
+    if (c->stages[i]) cusync_stage_destroy(c->stages[i]);
+  }
+  delete c;
+}
+
+}  // namespace
+
+extern "C" {
+
+int cusync_conv_chain_create(cusync_conv_chain_t** out, const cusync_conv_chain_desc_t* desc) {
+  if (!out || !desc) return CUSYNC_ERROR_INVALID_ARGUMENT;
+  *out = nullptr;
+  const cusync_conv_chain_desc_t& d = *desc;
+  if (d.num_convs < 2 || d.num_convs > kMaxConvs || !d.filters || !d.activations) return CUSYNC_ERROR_INVALID_ARGUMENT;
+  if (d.n <= 0 || d.h <= 0 || d.w <= 0 || d.channels <= 0) return CUSYNC_ERROR_INVALID_ARGUMENT;
+  for (int i = 0; i < d.num_convs; i++)
+    if (!d.filters[i] || !d.activations[i] || !d.activations[i + 1]) return CUSYNC_ERROR_INVALID_ARGUMENT;
+  const int rows = cusync_conv2d_tile_rows(d.w);
+  if (rows == 0 || d.h % rows || d.channels % 64) return CUSYNC_ERROR_UNSUPPORTED;
+
+  cusync_conv_chain* c = new (std::nothrow) cusync_conv_chain();
+  if (!c) return CUSYNC_ERROR_CUDA;
+  std::memset(c, 0, sizeof(*c));
+  c->desc = d;
+  c->num = d.num_convs;
+
+  // Every convolution has the same tile grid: (K / 64, N * H / rows, 1); tiles are rows * W pixels by 64 channels.
+  const cusync_dim3_t grid = {static_cast<uint32_t>(d.channels / 64), static_cast<uint32_t>(d.n * (d.h / rows)), 1};
+  const cusync_dim3_t ts = {1, 1, 1};
+  const uint32_t tile_m = static_cast<uint32_t>(rows * d.w);
+  cusync_policy_t none, post, wait;
+  std::memset(&none, 0, sizeof(none));
+  none.tile_m = none.tile_n = 1;
+  std::memset(&post, 0, sizeof(post));
+  post.kind = CUSYNC_POLICY_TILESYNC; post.order = CUSYNC_ORDER_TRANSPOSE_XY;
+  post.tile_m = tile_m; post.tile_n = 64; post.wait_value = 1; post.post_value = 1;
+  wait = post;
+  wait.kind = CUSYNC_POLICY_CONV2DTILESYNC; wait.p0 = 9;          // R * S (resnet.cu:113-116)
+
+  int sms = cusync_b200_sm_count();
+  if (sms <= 0) sms = 148;
+  const uint32_t blocks = grid.x * grid.y;
+  c->wait_kernels = static_cast<uint64_t>(blocks) * d.num_convs > static_cast<uint64_t>(sms);
+  const int opts = c->wait_kernels ? CUSYNC_OPT_NONE : CUSYNC_OPT_AVOID_WAIT_KERNEL;   // cusync.h:61-62
+
+  int rc = CUSYNC_SUCCESS;
+  for (int i = 0; i < c->num && rc == CUSYNC_SUCCESS; i++)
+    rc = cusync_stage_create(&c->stages[i], grid, ts, CUSYNC_ORDER_TRANSPOSE_XY, i == 0 ? &none : &wait,
+                             i + 1 == c->num ? &none : &post, opts);
+  for (int i = 0; i + 1 < c->num && rc == CUSYNC_SUCCESS; i++) rc = cusync_stage_link(c->stages[i], c->stages[i + 1]);
+  for (int i = 0; i < c->num && rc == CUSYNC_SUCCESS; i++) {
+    cusync_conv2d_desc_t cd;
+    std::memset(&cd, 0, sizeof(cd));
+    cd.n = d.n; cd.h = d.h; cd.w = d.w; cd.c = d.channels; cd.k = d.channels;
+    cd.r = 3; cd.s = 3; cd.stride = 1; cd.pad = 1;
+    cd.x = d.activations[i]; cd.filter = d.filters[i]; cd.y = d.activations[i + 1];
+    cd.epilogue = d.relu ? CUSYNC_EPILOGUE_RELU : CUSYNC_EPILOGUE_NONE;
+    cd.max_ctas = d.max_ctas;
+    cd.stage = c->stages[i];
+    rc = cusync_conv2d_plan_create(&c->sync[i], &cd);
+    cd.stage = nullptr;
+    if (rc == CUSYNC_SUCCESS) rc = cusync_conv2d_plan_create(&c->plain[i], &cd);
+  }
+  if (rc != CUSYNC_SUCCESS) { destroy_all(c); return rc; }
+  *out = c;
+  return CUSYNC_SUCCESS;
+}
+
+int cusync_conv_chain_destroy(cusync_conv_chain_t* c) {
+  if (!c) return CUSYNC_ERROR_NOT_INITIALIZED;
+  destroy_all(c);
+  return CUSYNC_SUCCESS;
+}
+
+int cusync_conv_chain_run_stream_ordered(cusync_conv_chain_t* c, cusync_stream_t stream) {
+  if (!c) return CUSYNC_ERROR_NOT_INITIALIZED;
+  int rc = CUSYNC_SUCCESS;
+  for (int i = 0; i < c->num && rc == CUSYNC_SUCCESS; i++) rc = cusync_conv2d_run(c->plain[i], stream);
+  return rc;
+}
+
+int cusync_conv_chain_run_cusync(cusync_conv_chain_t* c, const cusync_stream_t* streams) {
+  if (!c || !streams) return CUSYNC_ERROR_NOT_INITIALIZED;
+  int rc = CUSYNC_SUCCESS;
+  for (int i = 0; i < c->num && rc == CUSYNC_SUCCESS; i++) {
+    // a dependent convolution is launched only once every block of its producer is resident
+    if (i > 0 && c->wait_kernels) rc = cusync_stage_invoke_wait_kernel(c->stages[i - 1], streams[i]);
+    if (rc == CUSYNC_SUCCESS) rc = cusync_conv2d_run(c->sync[i], streams[i]);
+  }
+  for (int i = 0; i < c->num; i++) cusync_stage_increment_iter(c->stages[i]);
+  return rc;
+}
+
+cusync_stage_t* cusync_conv_chain_stage(cusync_conv_chain_t* c, int which) {
+  if (!c || which < 0 || which >= c->num) return nullptr;
+  return c->stages[which];
+}
+
+int cusync_conv_chain_uses_wait_kernels(const cusync_conv_chain_t* c) { return c && c->wait_kernels ? 1 : 0; }
+
+}  // extern "C"

@@ -49,7 +49,7 @@ constexpr int kBlockK = 64;         // one 128-byte swizzle row of fp16
 constexpr int kUmmaK = 16;
 constexpr int kThreads = 384;
 constexpr int kEpilogueWarps = 8;    // two per TMEM lane quarter: keeps every scheduler fed during the epilogue
-constexpr int kSchedSlots = 4;
+constexpr int kSchedSlots = 8;
 constexpr int kEpilogueWarp0 = 4;
 constexpr int kLookahead = 8;       // semaphores probed ahead of a consumer wait
 constexpr int kStoreCols = 64;      // columns per TMA store box (128 bytes)
@@ -256,6 +256,7 @@ struct Barriers {
   uint64_t sched_empty[kSchedSlots];
   uint64_t drain;
   uint64_t post;                        // epilogue warps -> the posting thread
+  uint64_t post_slot[kSchedSlots];      // slab kernel: the same, one barrier per schedule slot
   uint64_t splitk_counted;              // posting thread -> epilogue warps: arrival counted, `splitk_last` valid
   uint64_t splitk_done;                 // epilogue warps -> posting thread: finalisation stored
   uint32_t splitk_last;
@@ -1104,10 +1105,10 @@ cusync_conv3x3_slab_kernel(const __grid_constant__ CUtensorMap tmX, const __grid
   if (threadIdx.x == 0) {
     for (int i = 0; i < kSlabStages; i++) { mbar_init(&bars->full[i], 1); mbar_init(&bars->empty[i], 1); }
     for (int i = 0; i < kSlabStages; i++) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], kEpilogueWarps); }
-    for (int i = 0; i < kSchedSlots; i++) { mbar_init(&bars->sched_full[i], 1); mbar_init(&bars->sched_empty[i], kSlabIssuers + kEpilogueWarps); }
+    for (int i = 0; i < kSchedSlots; i++) { mbar_init(&bars->sched_full[i], 1); mbar_init(&bars->sched_empty[i], kSlabIssuers + kEpilogueWarps + 1); }
     mbar_init(&bars->drain, 1);
     mbar_init(&bars->splitk_done, 1);     // the second MMA thread's drain barrier
-    mbar_init(&bars->post, kEpilogueWarps);
+    for (int i = 0; i < kSchedSlots; i++) mbar_init(&bars->post_slot[i], kEpilogueWarps);
     mbar_init(filt_full, 1);
     bars->abort = 0u;
     fence_barrier_init();
@@ -1166,6 +1167,28 @@ cusync_conv3x3_slab_kernel(const __grid_constant__ CUtensorMap tmX, const __grid
       }
       while (ok) {
         const bool valid = tk0 < num_tiles;
+        // Tile i's dependencies first: the fence that makes its (earlier) probes acquiring would otherwise
+        // also wait for the loads issued below for later tiles.
+        bool waited_ok = true;
+        if (valid && p.is_consumer) {
+          if (pr0 < wait_target || pr1 < wait_target || pr2 < wait_target) {
+            // not finished when probed: wait (bounded) for the tile itself and its two halo neighbours
+            uint32_t idx[3];
+            sem_indices(y0, &idx[0], &idx[1], &idx[2]);
+            for (int j = 0; j < 3 && waited_ok; j++) {
+              uint32_t seen = 0;
+              if (!cusync::spinUntilAtLeast(st.sems_wait + idx[j], wait_target, st.timeout_ns, &seen)) {
+                bars->abort = 1u;
+                cusync::recordTimeout(st.status, 1u, y0 * static_cast<uint32_t>(span), 0u, static_cast<uint32_t>(j), idx[j],
+                                      seen, wait_target);
+                waited_ok = false;
+              }
+            }
+          } else {
+            __threadfence();       // makes the relaxed probes acquiring
+          }
+          fence_proxy_async();     // acquire (generic proxy) before the TMA read (async proxy)
+        }
         uint32_t tk3 = 0, y2 = 0, pn0 = 0, pn1 = 0, pn2 = 0;
         if (valid) {
           // issue, for later tiles: the draw of i+3, the schedule entry of i+2, the probes of i+1
@@ -1193,30 +1216,10 @@ cusync_conv3x3_slab_kernel(const __grid_constant__ CUtensorMap tmX, const __grid
         mbar_arrive(&bars->sched_full[slot]);
         sched_it++;
         if (!valid) break;
+        if (!waited_ok) { ok = false; break; }
 
         const int img = static_cast<int>(y0) / p.conv_tiles_per_image;
         const int h0 = (static_cast<int>(y0) % p.conv_tiles_per_image) * p.conv_rows;
-        bool waited_ok = true;
-        if (p.is_consumer) {
-          if (pr0 < wait_target || pr1 < wait_target || pr2 < wait_target) {
-            // not finished when probed: wait (bounded) for the tile itself and its two halo neighbours
-            uint32_t idx[3];
-            sem_indices(y0, &idx[0], &idx[1], &idx[2]);
-            for (int j = 0; j < 3 && waited_ok; j++) {
-              uint32_t seen = 0;
-              if (!cusync::spinUntilAtLeast(st.sems_wait + idx[j], wait_target, st.timeout_ns, &seen)) {
-                bars->abort = 1u;
-                cusync::recordTimeout(st.status, 1u, y0 * static_cast<uint32_t>(span), 0u, static_cast<uint32_t>(j), idx[j],
-                                      seen, wait_target);
-                waited_ok = false;
-              }
-            }
-          } else {
-            __threadfence();       // makes the relaxed probes acquiring
-          }
-          fence_proxy_async();     // acquire (generic proxy) before the TMA read (async proxy)
-        }
-        if (!waited_ok) { ok = false; break; }
         const uint32_t s = fills % kSlabStages, ph = (fills / kSlabStages) & 1u;
         if (!mbar_wait(&bars->empty[s], ph ^ 1u, ctx)) { ok = false; break; }
         const uint32_t slab_bytes = static_cast<uint32_t>((p.conv_rows + 2) * wp * 128);
@@ -1361,27 +1364,11 @@ cusync_conv3x3_slab_kernel(const __grid_constant__ CUtensorMap tmX, const __grid
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
       acc_it++;
       if (p.is_producer) {
-        // every lane's stores are ordered before lane 0's fence by the warp barrier above
-        if (lane == 0) {
-          __threadfence();
-          // Epilogue warps run at their own pace: one that is a tile ahead must not arrive on `post`
-          // while the previous tile's phase is still open (its arrival would close that phase early).
-          if (!mbar_wait(&bars->post, (post_it & 1u) ^ 1u, ctx)) ok = false;
-          mbar_arrive(&bars->post);
-          if (ew == 0) {
-            if (!mbar_wait(&bars->post, post_it & 1u, ctx)) ok = false;
-            else {
-              const uint32_t idx = cusync::eval::tileIndex(st.out_policy, static_cast<uint32_t>(m_off), 0u, st.grid.x,
-                                                           st.grid.y);
-              const uint32_t pv = cusync::eval::postValue(st.out_policy);
-              __threadfence();
-              if (st.opts & CUSYNC_OPT_NO_ATOMIC_ADD) cusync::storeRelease(st.sems_post + idx, pv * st.iter);
-              else                                    cusync::addRelease(st.sems_post + idx, pv);
-            }
-          }
-        }
-        post_it++;
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        // Hand the tile to the posting thread (warp 2) and go on: the warp barrier above orders every lane's
+        // stores before lane 0's arrival, the arrival (release) before the poster's wait (acquire), and the
+        // poster's fence + release publish them device-wide.  The barrier belongs to the tile's schedule
+        // slot, which the poster gives back only after it has posted: no warp can be a phase ahead on it.
+        if (lane == 0) mbar_arrive(&bars->post_slot[slot]);
       }
       if (p.trace && ew == 0 && lane == 0 && ticket < p.trace_capacity) {
         uint32_t smid;
@@ -1389,6 +1376,37 @@ cusync_conv3x3_slab_kernel(const __grid_constant__ CUtensorMap tmX, const __grid
         unsigned long long* rec = p.trace + 8ull * ticket;
         rec[0] = t_draw; rec[1] = t_mma_done; rec[2] = cusync::globalTimerNs();
         rec[3] = (static_cast<unsigned long long>(smid) << 32) | blockIdx.x;
+      }
+    }
+  }
+
+  else if (warp == 2 && lane == 0) {
+    // =====================================================================
+    // Poster: publishes each finished tile (CuStage::post, cusync_device_defs.h:55-72) so that the epilogue
+    // warps do not sit out the device-wide fence.  Walks the schedule ring like everybody else.
+    // =====================================================================
+    uint32_t sched_it = 0;
+    bool ok = true;
+    while (ok) {
+      const uint32_t slot = sched_it % kSchedSlots, sph = (sched_it / kSchedSlots) & 1u;
+      if (!mbar_wait(&bars->sched_full[slot], sph, ctx)) { ok = false; break; }
+      const int tile_m = bars->sched_tile[slot][1];
+      const int valid = bars->sched_tile[slot][2];
+      sched_it++;
+      if (!valid || !p.is_producer) {
+        mbar_arrive(&bars->sched_empty[slot]);
+        if (!valid) break;
+        continue;
+      }
+      {
+        if (!mbar_wait(&bars->post_slot[slot], sph, ctx)) { ok = false; break; }
+        const uint32_t m_off = static_cast<uint32_t>(tile_m * p.conv_rows * p.conv_w);
+        const uint32_t idx = cusync::eval::tileIndex(st.out_policy, m_off, 0u, st.grid.x, st.grid.y);
+        const uint32_t pv = cusync::eval::postValue(st.out_policy);
+        __threadfence();
+        if (st.opts & CUSYNC_OPT_NO_ATOMIC_ADD) cusync::storeRelease(st.sems_post + idx, pv * st.iter);
+        else                                    cusync::addRelease(st.sems_post + idx, pv);
+        mbar_arrive(&bars->sched_empty[slot]);      // only now may the slot (and its post barrier) be reused
       }
     }
   }

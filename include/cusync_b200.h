@@ -308,6 +308,36 @@ CUSYNC_API int cusync_conv2d_plan_destroy(cusync_conv2d_plan_t* plan);
 CUSYNC_API int cusync_conv2d_run(cusync_conv2d_plan_t* plan, cusync_stream_t stream);
 CUSYNC_API uint32_t cusync_conv2d_plan_num_ctas(const cusync_conv2d_plan_t* plan);
 
+/* A chain of 3x3 convolutions with equal channel counts, the workload of
+ * src/ml-bench/volta_conv2d/resnet.cu (two convolutions) and vgg.cu (up to four):
+ * activations[0] -> conv(filters[0]) -> activations[1] -> ... -> activations[num_convs], NHWC fp16 on the device,
+ * caller-owned; ReLU after every convolution when `relu` is set.  Stage i posts TileSync<rows * w, 64> and stage
+ * i + 1 waits with Conv2DTileSync<3, 3, rows * w, 64> (resnet.cu:107-116). */
+typedef struct cusync_conv_chain_desc {
+  int32_t num_convs;               /* 2..8 */
+  int32_t n, h, w, channels;
+  int32_t relu;
+  int32_t max_ctas;                /* 0 = one block per SM */
+  const void* const* filters;      /* [num_convs] pointers to [channels, 3, 3, channels] */
+  void* const* activations;        /* [num_convs + 1] pointers to [n, h, w, channels] */
+} cusync_conv_chain_desc_t;
+
+typedef struct cusync_conv_chain cusync_conv_chain_t;
+
+/* Stage construction + setProducerConsumerPair + every convolution's initialisation (resnet.cu:659-700). */
+CUSYNC_API int cusync_conv_chain_create(cusync_conv_chain_t** out, const cusync_conv_chain_desc_t* desc);
+CUSYNC_API int cusync_conv_chain_destroy(cusync_conv_chain_t* chain);
+/* runBaseline, one iteration: the convolutions back to back on one stream, no tile synchronisation
+ * (resnet.cu:461-520). */
+CUSYNC_API int cusync_conv_chain_run_stream_ordered(cusync_conv_chain_t* chain, cusync_stream_t stream);
+/* runCuSync, one iteration: convolution i on streams[i], each dependent one behind a wait kernel unless all
+ * stages fit on the device at once, then incrementIter on every stage (resnet.cu:560-590).  streams: [num_convs]. */
+CUSYNC_API int cusync_conv_chain_run_cusync(cusync_conv_chain_t* chain, const cusync_stream_t* streams);
+/* Stage handle of convolution `which`, for inspection. */
+CUSYNC_API cusync_stage_t* cusync_conv_chain_stage(cusync_conv_chain_t* chain, int which);
+/* 1 when run_cusync launches wait kernels, 0 when every stage fits on the device at once (AvoidWaitKernel). */
+CUSYNC_API int cusync_conv_chain_uses_wait_kernels(const cusync_conv_chain_t* chain);
+
 /* ---- decode attention (a middle stage) ---------------------------------- */
 
 /* One query token per batch row attends, per head, over `seq` cached keys/values plus its own new key/value;

@@ -93,3 +93,43 @@ def test_config5_conv_chain_with_conv2dtilesync(n, max_ctas):
         assert oob == 0 and (prod.semaphores() == exp).all()
         prod.incrementIter(); cons.incrementIter()
     c1.destroy(); c2.destroy(); prod.destroy(); cons.destroy()
+
+
+@pytest.mark.parametrize("n,h,w,c,convs,max_ctas", [
+    (1, 56, 56, 64, 2, 0),     # config 5, N = 1: both grids resident at once, no wait kernel
+    (8, 56, 56, 64, 2, 0),     # config 5, N = 8: wait kernel before the consumer
+    (2, 28, 28, 64, 4, 6),     # vgg.cu-style chain of four, few blocks per stage, general-shape kernel rows
+    (1, 8, 32, 128, 3, 0),     # two channel chunks: the implicit-GEMM path between the stages
+])
+def test_conv_chain_driver(n, h, w, c, convs, max_ctas):
+    # cusync_conv_chain_*: the library's own driver for the chain (resnet.cu / vgg.cu flow)
+    g = torch.Generator().manual_seed(40 + n)
+    x = torch.randn((n, h, w, c), generator=g).half().cuda()
+    filters = [(torch.randn((c, 3, 3, c), generator=g) * (2.0 / (9 * c)) ** 0.5).half().cuda() for _ in range(convs)]
+    chain = cs.ConvChain(x, filters, relu=True, max_ctas=max_ctas)
+    blocks = n * (h // (128 // w)) * (c // 64)
+    assert chain.uses_wait_kernels == (blocks * convs > L.lib().cusync_b200_sm_count())
+    streams = [torch.cuda.Stream(priority=-1)] + [torch.cuda.Stream() for _ in range(convs - 1)]
+    for it in range(1, 4):
+        for out in chain.outputs:
+            out.fill_(float("nan"))                    # a consumer that reads ahead of its producer sees NaN
+        torch.cuda.synchronize()
+        chain.run_cusync(streams)
+        torch.cuda.synchronize()
+        assert chain.status_codes() == (0,) * convs
+        # every convolution against the oracle fed with the activation the GPU itself produced before it
+        # (an end-to-end reference would also compare the stages' different fp16 roundings)
+        acts = [x] + chain.outputs
+        for i, f in enumerate(filters):
+            ref = o.conv2d_3x3_nhwc_f16(acts[i].cpu().numpy(), f.cpu().numpy(), True)
+            assert not np.isnan(acts[i + 1].float().cpu().numpy()).any()
+            assert o.max_rel_err(acts[i + 1].cpu().numpy(), ref) <= TOL
+        for i in range(convs - 1):
+            assert (chain.semaphores(i) == it).all()   # every tile posted once per run
+    for out in chain.outputs:
+        out.fill_(float("nan"))
+    chain.run_stream_ordered(torch.cuda.current_stream())
+    torch.cuda.synchronize()
+    ref = o.conv2d_3x3_nhwc_f16(chain.outputs[-2].cpu().numpy(), filters[-1].cpu().numpy(), True)
+    assert o.max_rel_err(chain.y.cpu().numpy(), ref) <= TOL
+    chain.destroy()
