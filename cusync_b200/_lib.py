@@ -134,6 +134,7 @@ SIGNATURES = {
     "cusync_conv_chain_destroy": (_i, [_vp]),
     "cusync_conv_chain_run_stream_ordered": (_i, [_vp, _vp]),
     "cusync_conv_chain_run_cusync": (_i, [_vp, C.POINTER(_vp)]),
+    "cusync_conv_chain_run_cusync_replayable": (_i, [_vp, C.POINTER(_vp)]),
     "cusync_conv_chain_stage": (_vp, [_vp, _i]),
     "cusync_conv_chain_uses_wait_kernels": (_i, [_vp]),
     "cusync_attn_default_splits": (_i, [C.c_int32] * 3),

@@ -40,6 +40,12 @@ class ConvChain:
         arr = (C.c_void_p * len(streams))(*[_stream_ptr(s) for s in streams])
         L.check(L.lib().cusync_conv_chain_run_cusync(self._h, C.cast(arr, C.POINTER(C.c_void_p))), "run_cusync")
 
+    def run_cusync_replayable(self, streams):
+        """Reset + run, for recording into a CUDA graph captured on streams[0]; the caller joins the streams."""
+        arr = (C.c_void_p * len(streams))(*[_stream_ptr(s) for s in streams])
+        L.check(L.lib().cusync_conv_chain_run_cusync_replayable(self._h, C.cast(arr, C.POINTER(C.c_void_p))),
+                "run_cusync_replayable")
+
     def status_codes(self):
         out = []
         for i in range(len(self.filters)):

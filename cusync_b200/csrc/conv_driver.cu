@@ -4,6 +4,8 @@
 // convolution on its own stream behind a wait kernel and increments the stages' iterations afterwards).
 // Host-only code over the library's own C ABI.  Doing the launches here keeps a whole chain at a handful of
 // microseconds of host time, which matters for these short kernels.
+#include <cuda_runtime.h>
+
 #include <cstring>
 #include <new>
 
@@ -18,6 +20,7 @@ struct cusync_conv_chain {
   cusync_conv2d_plan_t* sync[kMaxConvs];    // convolution i with its stage
   cusync_conv2d_plan_t* plain[kMaxConvs];   // the same kernel without tile synchronisation
   bool wait_kernels;                        // false: every stage fits on the device at once
+  cudaEvent_t fork;                         // orders the resets of a replayable run before every stage
 };
 
 namespace {
@@ -28,6 +31,7 @@ void destroy_all(cusync_conv_chain* c) {
     if (c->plain[i]) cusync_conv2d_plan_destroy(c->plain[i]);
     if (c->stages[i]) cusync_stage_destroy(c->stages[i]);
   }
+  if (c->fork) cudaEventDestroy(c->fork);
   delete c;
 }
 
@@ -89,6 +93,11 @@ int cusync_conv_chain_create(cusync_conv_chain_t** out, const cusync_conv_chain_
     cd.stage = nullptr;
     if (rc == CUSYNC_SUCCESS) rc = cusync_conv2d_plan_create(&c->plain[i], &cd);
   }
+  if (rc == CUSYNC_SUCCESS && cudaEventCreateWithFlags(&c->fork, cudaEventDisableTiming) != cudaSuccess) {
+    (void)cudaGetLastError();
+    c->fork = nullptr;
+    rc = CUSYNC_ERROR_CUDA;
+  }
   if (rc != CUSYNC_SUCCESS) { destroy_all(c); return rc; }
   *out = c;
   return CUSYNC_SUCCESS;
@@ -116,6 +125,24 @@ int cusync_conv_chain_run_cusync(cusync_conv_chain_t* c, const cusync_stream_t* 
     if (rc == CUSYNC_SUCCESS) rc = cusync_conv2d_run(c->sync[i], streams[i]);
   }
   for (int i = 0; i < c->num; i++) cusync_stage_increment_iter(c->stages[i]);
+  return rc;
+}
+
+int cusync_conv_chain_run_cusync_replayable(cusync_conv_chain_t* c, const cusync_stream_t* streams) {
+  if (!c || !streams) return CUSYNC_ERROR_NOT_INITIALIZED;
+  // Every run starts from freshly zeroed semaphores at iteration 1, so the recorded work does not depend on
+  // how often it ran before.  The resets go to streams[0]; the other streams wait for them through an event
+  // (in a stream capture this is the fork).
+  int rc = CUSYNC_SUCCESS;
+  for (int i = 0; i < c->num && rc == CUSYNC_SUCCESS; i++) rc = cusync_stage_reset(c->stages[i], streams[0]);
+  if (rc != CUSYNC_SUCCESS) return rc;
+  if (cudaEventRecord(c->fork, reinterpret_cast<cudaStream_t>(streams[0])) != cudaSuccess) return CUSYNC_ERROR_CUDA;
+  for (int i = 1; i < c->num; i++)
+    if (cudaStreamWaitEvent(reinterpret_cast<cudaStream_t>(streams[i]), c->fork, 0) != cudaSuccess) return CUSYNC_ERROR_CUDA;
+  for (int i = 0; i < c->num && rc == CUSYNC_SUCCESS; i++) {
+    if (i > 0 && c->wait_kernels) rc = cusync_stage_invoke_wait_kernel(c->stages[i - 1], streams[i]);
+    if (rc == CUSYNC_SUCCESS) rc = cusync_conv2d_run(c->sync[i], streams[i]);
+  }
   return rc;
 }
 

@@ -1185,7 +1185,7 @@ cusync_conv3x3_slab_kernel(const __grid_constant__ CUtensorMap tmX, const __grid
               }
             }
           } else {
-            __threadfence();       // makes the relaxed probes acquiring
+            cusync::fenceAcqRel();  // makes the relaxed probes acquiring
           }
           fence_proxy_async();     // acquire (generic proxy) before the TMA read (async proxy)
         }
@@ -1403,7 +1403,7 @@ cusync_conv3x3_slab_kernel(const __grid_constant__ CUtensorMap tmX, const __grid
         const uint32_t m_off = static_cast<uint32_t>(tile_m * p.conv_rows * p.conv_w);
         const uint32_t idx = cusync::eval::tileIndex(st.out_policy, m_off, 0u, st.grid.x, st.grid.y);
         const uint32_t pv = cusync::eval::postValue(st.out_policy);
-        __threadfence();
+        cusync::fenceAcqRel();
         if (st.opts & CUSYNC_OPT_NO_ATOMIC_ADD) cusync::storeRelease(st.sems_post + idx, pv * st.iter);
         else                                    cusync::addRelease(st.sems_post + idx, pv);
         mbar_arrive(&bars->sched_empty[slot]);      // only now may the slot (and its post barrier) be reused

@@ -31,6 +31,10 @@ CUSYNC_DEVICE uint32_t loadRelaxed(const uint32_t* addr) {
   return v;
 }
 
+// Acquire/release fence at device scope.  Cheaper than __threadfence(), which is the sequentially
+// consistent fence: enough after relaxed semaphore probes (makes them acquiring) and before a release.
+CUSYNC_DEVICE void fenceAcqRel() { asm volatile("fence.acq_rel.gpu;" ::: "memory"); }
+
 CUSYNC_DEVICE void addRelease(uint32_t* addr, uint32_t value) {
   asm volatile("red.release.gpu.global.add.u32 [%0], %1;" :: "l"(addr), "r"(value) : "memory");
 }

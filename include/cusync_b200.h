@@ -333,6 +333,12 @@ CUSYNC_API int cusync_conv_chain_run_stream_ordered(cusync_conv_chain_t* chain, 
 /* runCuSync, one iteration: convolution i on streams[i], each dependent one behind a wait kernel unless all
  * stages fit on the device at once, then incrementIter on every stage (resnet.cu:560-590).  streams: [num_convs]. */
 CUSYNC_API int cusync_conv_chain_run_cusync(cusync_conv_chain_t* chain, const cusync_stream_t* streams);
+/* The same work in a form that can be recorded once and replayed (a CUDA graph captured on streams[0]; no
+ * counterpart in the reference): resets every stage (semaphores zero, iteration 1) on streams[0], makes the other
+ * streams wait for the resets, then launches as run_cusync does, without incrementIter.  The caller joins
+ * streams[1..] back into streams[0] before ending a capture.  These kernels run for tens of microseconds, less
+ * than the host needs to submit three launches, so replaying one graph is what keeps the GPU fed. */
+CUSYNC_API int cusync_conv_chain_run_cusync_replayable(cusync_conv_chain_t* chain, const cusync_stream_t* streams);
 /* Stage handle of convolution `which`, for inspection. */
 CUSYNC_API cusync_stage_t* cusync_conv_chain_stage(cusync_conv_chain_t* chain, int which);
 /* 1 when run_cusync launches wait kernels, 0 when every stage fits on the device at once (AvoidWaitKernel). */

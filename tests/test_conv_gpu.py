@@ -133,3 +133,37 @@ def test_conv_chain_driver(n, h, w, c, convs, max_ctas):
     ref = o.conv2d_3x3_nhwc_f16(chain.outputs[-2].cpu().numpy(), filters[-1].cpu().numpy(), True)
     assert o.max_rel_err(chain.y.cpu().numpy(), ref) <= TOL
     chain.destroy()
+
+
+@pytest.mark.parametrize("n", [1, 8])
+def test_conv_chain_replayed_from_a_cuda_graph(n):
+    # run_cusync_replayable recorded once (capture on the producer stream, the consumer stream forked by the
+    # driver's event and joined here), then replayed: every replay starts from reset stages.
+    h = w = 56
+    c = 64
+    g = torch.Generator().manual_seed(50 + n)
+    x = torch.randn((n, h, w, c), generator=g).half().cuda()
+    filters = [(torch.randn((c, 3, 3, c), generator=g) * (2.0 / (9 * c)) ** 0.5).half().cuda() for _ in range(2)]
+    chain = cs.ConvChain(x, filters, relu=True)
+    cap, side = torch.cuda.Stream(), torch.cuda.Stream()
+    chain.run_cusync([cap, side])          # warm-up outside the capture (module load, attribute calls)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=cap):
+        chain.run_cusync_replayable([cap, side])
+        cap.wait_stream(side)
+    r1 = o.conv2d_3x3_nhwc_f16(x.cpu().numpy(), filters[0].cpu().numpy(), True)
+    for _ in range(3):
+        for out in chain.outputs:
+            out.fill_(float("nan"))
+        torch.cuda.synchronize()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert chain.status_codes() == (0, 0)
+        assert o.max_rel_err(chain.outputs[0].cpu().numpy(), r1) <= TOL
+        r2 = o.conv2d_3x3_nhwc_f16(chain.outputs[0].cpu().numpy(), filters[1].cpu().numpy(), True)
+        assert not np.isnan(chain.y.float().cpu().numpy()).any()
+        assert o.max_rel_err(chain.y.cpu().numpy(), r2) <= TOL
+        assert (chain.semaphores(0) == 1).all()
+    del graph
+    chain.destroy()
