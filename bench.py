@@ -23,6 +23,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+REDUCE_CHUNKS = 4
 METRIC = "gpt3_mlp_layer_latency"
 UNIT = "us"
 SWEEP_BATCHES = [1, 64, 256, 512, 1024, 2048]
@@ -132,7 +133,10 @@ def workload_config(args, shard):
                        "* W2[6144,12288]" % args.batch,
            "batch": args.batch, "policy": args.policy,
            "l2": "inputs larger than L2 (302 MB of weights per step vs 126 MB L2); no explicit flush",
-           "all_reduce": "NCCL sum of Y[B,12288] fp16 across ranks" if args.gpus > 1 else "none (1 GPU)"}
+           "all_reduce": ("NCCL sum of Y[B,12288] fp16 across ranks" + (
+               "; overlapped arm: %d row blocks, each behind the RowSync semaphores of its 128-row tiles of the "
+               "second GEMM (%d of 148 SMs to the GEMMs)" % (args.reduce_chunks, args.gemm_ctas) if args.gpus > 1 and args.batch >= 512 and args.reduce == "overlapped" else ""))
+                         if args.gpus > 1 else "none (1 GPU)"}
     if shard is not None:
         cfg.update({"tile_m": 128, "tile_n1": shard.tile_n1, "tile_n2": shard.tile_n2,
                     "ctas1": shard.ctas1, "ctas2": shard.ctas2, "split_k1": shard.split_k1, "split_k2": shard.split_k2,
@@ -174,6 +178,12 @@ def main():
     ap.add_argument("--batch", type=int, default=2048)
     ap.add_argument("--policy", default="rowsync", choices=["rowsync", "tilesync"])
     ap.add_argument("--impl", default="cusync", choices=["cusync", "reference"])
+    ap.add_argument("--reduce", choices=("overlapped", "after"), default="after",
+                    help="multi-GPU: all-reduce Y after the second GEMM (default, the faster one here: NCCL needs "
+                         "more SMs for full NVLink bandwidth than the GEMMs can spare), or in row blocks behind "
+                         "the second GEMM's tiles")
+    ap.add_argument("--reduce-chunks", type=int, default=REDUCE_CHUNKS, help="row blocks of the overlapped all-reduce")
+    ap.add_argument("--gemm-ctas", type=int, default=128, help="blocks the GEMMs use when the all-reduce is overlapped")
     ap.add_argument("--no-sweep", action="store_true", help="skip the per-batch table")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
@@ -204,8 +214,16 @@ def main():
     ps = torch.cuda.Stream(priority=-1)   # producer: high priority, launched first
     cs = torch.cuda.Stream(priority=0)
 
+    comm = torch.cuda.Stream(priority=0)  # multi-GPU: the row-block all-reduces of the overlapped arm
+    # Multi-GPU: the second GEMM also posts its output by 128-row tile, so that the all-reduce runs block by
+    # block behind it; 20 SMs are left to the collective's kernels (128 blocks: 192 and 384 pair tiles are
+    # whole rounds of 64 pairs, so the GEMMs lose nothing at B = 2048).
+    overlap_reduce = world > 1 and args.batch >= 512 and args.reduce == "overlapped"
+
     def build(batch, policy):
         x, w1, w2, v = M.make_inputs("gpt3", batch, dev, seed=rank)
+        if overlap_reduce:
+            return M.MLPShard("gpt3", batch, x, w1, w2, v, policy=policy, post_rows=True, max_ctas=args.gemm_ctas)
         return M.MLPShard("gpt3", batch, x, w1, w2, v, policy=policy)
 
     shard = build(args.batch, args.policy)
@@ -214,7 +232,10 @@ def main():
         # a step may not overwrite H while the previous consumer still reads it
         ps.wait_stream(cs)
         shard.run_cusync(ps, cs)
-        if world > 1:
+        if overlap_reduce:
+            group.all_reduce_rows_overlapped(shard, comm, args.reduce_chunks)
+            cs.wait_stream(comm)
+        elif world > 1:
             with torch.cuda.stream(cs):
                 group.all_reduce_sum(shard.y)
 
@@ -244,6 +265,14 @@ def main():
             ev.append(pair)
         torch.cuda.synchronize()
         return [p[0][0].elapsed_time(p[0][1]) for p in ev], [p[1][0].elapsed_time(p[1][1]) for p in ev]
+
+    if overlap_reduce:
+        # the block-wise reduction must give what one all-reduce of the whole output gives
+        cusync_step(); torch.cuda.synchronize()
+        y_blocks = shard.y.clone()
+        ordered_step(); torch.cuda.synchronize()
+        if not torch.equal(y_blocks, shard.y):
+            raise SystemExit("row-block all-reduce differs from the whole-matrix all-reduce")
 
     # ---- headline: overlapped chain ------------------------------------------------------------
     sampler = ClockSampler(local_rank)

@@ -1167,6 +1167,7 @@ cusync_conv3x3_slab_kernel(const __grid_constant__ CUtensorMap tmX, const __grid
       }
       while (ok) {
         const bool valid = tk0 < num_tiles;
+        const long long lc0 = p.trace ? clock64() : 0;
         // Tile i's dependencies first: the fence that makes its (earlier) probes acquiring would otherwise
         // also wait for the loads issued below for later tiles.
         bool waited_ok = true;
@@ -1189,6 +1190,7 @@ cusync_conv3x3_slab_kernel(const __grid_constant__ CUtensorMap tmX, const __grid
           }
           fence_proxy_async();     // acquire (generic proxy) before the TMA read (async proxy)
         }
+        const long long lc1 = p.trace ? clock64() : 0;
         uint32_t tk3 = 0, y2 = 0, pn0 = 0, pn1 = 0, pn2 = 0;
         if (valid) {
           // issue, for later tiles: the draw of i+3, the schedule entry of i+2, the probes of i+1
@@ -1206,6 +1208,7 @@ cusync_conv3x3_slab_kernel(const __grid_constant__ CUtensorMap tmX, const __grid
           if (tk0 == total_draws - 1u || tk1 == total_draws - 1u || tk2 == total_draws - 1u)
             atomicExch(st.tile_counter, 0u);
         }
+        const long long lc2 = p.trace ? clock64() : 0;
         const uint32_t slot = sched_it % kSchedSlots, sph = (sched_it / kSchedSlots) & 1u;
         if (!mbar_wait(&bars->sched_empty[slot], sph ^ 1u, ctx)) { ok = false; break; }
         bars->sched_tile[slot][0] = 0;
@@ -1220,13 +1223,21 @@ cusync_conv3x3_slab_kernel(const __grid_constant__ CUtensorMap tmX, const __grid
 
         const int img = static_cast<int>(y0) / p.conv_tiles_per_image;
         const int h0 = (static_cast<int>(y0) % p.conv_tiles_per_image) * p.conv_rows;
+        const long long lc3 = p.trace ? clock64() : 0;
         const uint32_t s = fills % kSlabStages, ph = (fills / kSlabStages) & 1u;
         if (!mbar_wait(&bars->empty[s], ph ^ 1u, ctx)) { ok = false; break; }
+        const long long lc4 = p.trace ? clock64() : 0;
         const uint32_t slab_bytes = static_cast<uint32_t>((p.conv_rows + 2) * wp * 128);
         mbar_expect_tx(&bars->full[s], slab_bytes);
         // box {64 channels, W + 2 pixels, conv_rows + 2 rows, 1 image} from pixel (-1, h0 - 1)
         tma_load_4d(slabs + s * kSlabBytes, &tmX, &bars->full[s], 0, -1, h0 - 1, img);
         fills++;
+        if (p.trace && tk0 < p.trace_capacity) {
+          // loader's cycles for this tile: dependencies | prefetch issue | schedule slot | free slab | TMA issue
+          auto cap = [](long long v) { return static_cast<unsigned long long>(v < 0 ? 0 : (v > 4095 ? 4095 : v)); };
+          p.trace[8ull * tk0 + 5] = cap(lc1 - lc0) | (cap(lc2 - lc1) << 12) | (cap(lc3 - lc2) << 24) |
+                                    (cap(lc4 - lc3) << 36) | (cap(clock64() - lc4) << 48);
+        }
         tk0 = tk1; tk1 = tk2; tk2 = tk3; y0 = y1; y1 = y2; pr0 = pn0; pr1 = pn1; pr2 = pn2;
       }
       if (!ok) {

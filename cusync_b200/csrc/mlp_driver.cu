@@ -110,7 +110,15 @@ int cusync_mlp_create(cusync_mlp_t** out, const cusync_mlp_desc_t* desc) {
   cusync_dim3_t ts = {1, 1, 1};
   int rc = cusync_stage_create(&m->prod, grid1, ts, CUSYNC_ORDER_TRANSPOSE_XY, &none, &sync, opts);
   const int order2 = d.group_rows2 > 0 ? CUSYNC_ORDER_GROUPED(d.group_rows2) : CUSYNC_ORDER_TRANSPOSE_XY;
-  if (rc == CUSYNC_SUCCESS) rc = cusync_stage_create(&m->cons, grid2, ts, order2, &sync, &none, opts);
+  // post_rows: the consumer publishes Y by 128-row tile as well (RowSync counting its column tiles)
+  cusync_policy_t rows_out = none;
+  if (d.post_rows) {
+    rows_out.kind = CUSYNC_POLICY_ROWSYNC; rows_out.order = CUSYNC_ORDER_TRANSPOSE_XY;
+    rows_out.tile_m = 128; rows_out.tile_n = static_cast<uint32_t>(m->tile_n2);
+    rows_out.wait_value = grid2.x; rows_out.post_value = 1;
+  }
+  if (rc == CUSYNC_SUCCESS)
+    rc = cusync_stage_create(&m->cons, grid2, ts, order2, &sync, &rows_out, opts & ~CUSYNC_OPT_NO_ATOMIC_ADD);
   if (rc == CUSYNC_SUCCESS) rc = cusync_stage_link(m->prod, m->cons);
 
   cusync_gemm_desc_t g;
@@ -187,6 +195,18 @@ int cusync_mlp_config(const cusync_mlp_t* m, int32_t* out6) {
   out6[3] = static_cast<int32_t>(cusync_gemm_plan_num_ctas(m->sync2));
   out6[4] = m->split_k1; out6[5] = m->split_k2;
   return CUSYNC_SUCCESS;
+}
+
+int cusync_mlp_wait_rows(cusync_mlp_t* m, uint32_t first_tile, uint32_t num_tiles, cusync_stream_t stream) {
+  if (!m) return CUSYNC_ERROR_NOT_INITIALIZED;
+  if (!m->desc.post_rows) return CUSYNC_ERROR_NOT_PRODUCER;
+  cusync_stage_view_t v;
+  cusync_stage_get_view(m->cons, &v);
+  if (num_tiles == 0 || first_tile + num_tiles > v.grid.y) return CUSYNC_ERROR_INVALID_ARGUMENT;
+  // run_cusync has already incremented the iteration: the run to wait for is the previous one.  With split-K
+  // only the finishing slice of a tile posts, so a row is complete after grid.x posts per run.
+  const uint32_t runs = v.iter - 1u;
+  return cusync_wait_kernel_range(v.sems_post + first_tile, num_tiles, runs * v.grid.x, stream, v.status, v.timeout_ns);
 }
 
 int cusync_mlp_tail_splits(const cusync_mlp_t* m, int32_t* out4) {

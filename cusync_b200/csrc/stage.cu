@@ -36,6 +36,16 @@ __global__ void waitKernel(const uint32_t* sem, uint32_t value, uint32_t* status
     cusync::recordTimeout(status, 3u, 0, 0, 0, 0, seen, value);
 }
 
+// One thread per semaphore of a contiguous range; the kernel ends when every one has reached `value`.
+__global__ void waitRangeKernel(const uint32_t* sems, uint32_t count, uint32_t value, uint32_t* status,
+                                uint64_t timeout_ns) {
+  for (uint32_t i = threadIdx.x; i < count; i += blockDim.x) {
+    uint32_t seen = 0;
+    if (!cusync::spinUntilAtLeast(sems + i, value, timeout_ns, &seen))
+      cusync::recordTimeout(status, 3u, i, 0, 0, i, seen, value);
+  }
+}
+
 bool policy_ok(const cusync_policy_t* p) {
   if (p == nullptr) return true;
   if (p->kind < CUSYNC_POLICY_NOSYNC || p->kind > CUSYNC_POLICY_CUSTOM) return false;
@@ -200,6 +210,14 @@ int cusync_wait_kernel(uint32_t* semaphore, uint32_t given_value, cusync_stream_
                        uint64_t timeout_ns) {
   if (semaphore == nullptr) return CUSYNC_ERROR_NOT_INITIALIZED;
   waitKernel<<<1, 1, 0, (cudaStream_t)stream>>>(semaphore, given_value, status, timeout_ns);
+  return cudaGetLastError() == cudaSuccess ? CUSYNC_SUCCESS : CUSYNC_ERROR_CUDA;
+}
+
+int cusync_wait_kernel_range(uint32_t* semaphores, uint32_t count, uint32_t given_value, cusync_stream_t stream,
+                             uint32_t* status, uint64_t timeout_ns) {
+  if (semaphores == nullptr || count == 0) return CUSYNC_ERROR_NOT_INITIALIZED;
+  const uint32_t threads = count < 256u ? ((count + 31u) / 32u) * 32u : 256u;
+  waitRangeKernel<<<1, threads, 0, (cudaStream_t)stream>>>(semaphores, count, given_value, status, timeout_ns);
   return cudaGetLastError() == cudaSuccess ? CUSYNC_SUCCESS : CUSYNC_ERROR_CUDA;
 }
 

@@ -45,6 +45,21 @@ class TensorParallelGroup:
             self.dist.all_reduce(tensor)
         return tensor
 
+    def all_reduce_rows_overlapped(self, shard, comm_stream, chunks=4):
+        """Sum-all-reduce of shard.y in row blocks, each enqueued behind the 128-row tiles it covers instead of
+        behind the whole second GEMM (the shard was built with post_rows=True and run_cusync has just been called).
+        The collectives go to `comm_stream`; the caller joins it.  Row blocks are whole 128-row tiles, so every
+        element is summed exactly as by one all-reduce of the whole matrix."""
+        import torch
+        tiles = (shard.batch + 127) // 128
+        per = (tiles + chunks - 1) // chunks
+        for first in range(0, tiles, per):
+            n = min(per, tiles - first)
+            shard.wait_rows(first, n, comm_stream)
+            if self.world > 1:
+                with torch.cuda.stream(comm_stream):
+                    self.dist.all_reduce(shard.y[first * 128:min(shard.batch, (first + n) * 128)])
+
     def barrier(self):
         if self.world > 1:
             self.dist.barrier()

@@ -179,6 +179,12 @@ CUSYNC_API int cusync_stage_note_launch(cusync_stage_t* stage, uint32_t num_bloc
 CUSYNC_API int cusync_wait_kernel(uint32_t* semaphore, uint32_t given_value, cusync_stream_t stream,
                        uint32_t* status, uint64_t timeout_ns);
 
+/* The same for a contiguous range of semaphores: the kernel ends when each of `count` semaphores has reached
+ * `given_value`.  No counterpart in the reference; it is what lets a stream of another library (an NCCL
+ * all-reduce of some rows of the output) start behind the tiles it depends on instead of behind the kernel. */
+CUSYNC_API int cusync_wait_kernel_range(uint32_t* semaphores, uint32_t count, uint32_t given_value,
+                                        cusync_stream_t stream, uint32_t* status, uint64_t timeout_ns);
+
 /* Test access, the role of the reference's friend class CuSyncTest
  * (tests/cusync-test.h:8-44): copy the schedule buffer / the producer's
  * semaphores / the timeout record to the host (synchronous). */
@@ -274,7 +280,9 @@ CUSYNC_API int cusync_gemm_run_noalloc(const cusync_gemm_desc_t* desc, cusync_st
  * {globaltimer at the ticket draw, at the end of its MMAs, after its stores and post,
  *  (SM id << 32) | block index, SM cycles the MMA thread waited for operands, SM cycles the loader
  *  waited for a free ring slot, SM cycles of the tile in the MMA thread, of which waiting for a free
- *  accumulator}.  NULL switches it off (the default).  No counterpart in the reference. */
+ *  accumulator}.  (The 64 -> 64 channel convolution kernel packs into the sixth word the loader's cycles for the
+ *  tile instead, 12 bits each from bit 0: dependencies, prefetch issue, schedule slot, free slab, TMA issue.)
+ *  NULL switches it off (the default).  No counterpart in the reference. */
 CUSYNC_API int cusync_gemm_plan_set_trace(cusync_gemm_plan_t* plan, void* device_buffer, uint32_t capacity_tiles);
 /* Blocks the launch uses (persistent grid). */
 CUSYNC_API uint32_t cusync_gemm_plan_num_ctas(const cusync_gemm_plan_t* plan);
@@ -393,6 +401,10 @@ typedef struct cusync_mlp_desc {
   int32_t group_rows2;           /* > 0: the consumer takes its tiles in CUSYNC_ORDER_GROUPED(group_rows2) order */
   int32_t tail_split_sync1, tail_split_sync2;    /* cusync_gemm_desc_t.tail_split of the two synchronised GEMMs ... */
   int32_t tail_split_plain1, tail_split_plain2;  /* ... and of the two stream-ordered ones: 0 = choose, 1 = none */
+  int32_t post_rows;             /* 1: the second GEMM of run_cusync is a producer too: it posts RowSync semaphores, one
+                                    per 128-row tile of Y, counting its column tiles, so that whatever consumes Y (the
+                                    all-reduce of a tensor-parallel layer) can start row block by row block
+                                    (cusync_mlp_wait_rows) */
   const void* x; const void* w1; const void* v; const void* w2;
   void* h; void* y;
 } cusync_mlp_desc_t;
@@ -422,6 +434,10 @@ CUSYNC_API cusync_stage_t* cusync_mlp_stage(cusync_mlp_t* mlp, int which);
 CUSYNC_API int cusync_mlp_set_trace(cusync_mlp_t* mlp, void* trace1, uint32_t capacity1, void* trace2, uint32_t capacity2);
 /* Configuration in use: out[0..5] = tile_n1, tile_n2, ctas1, ctas2, split_k1, split_k2. */
 CUSYNC_API int cusync_mlp_config(const cusync_mlp_t* mlp, int32_t* out6);
+/* With desc.post_rows: enqueues on `stream` a wait for the 128-row tiles [first_tile, first_tile + num_tiles) of Y
+ * as written by the most recent run_cusync (call it after that run_cusync).  Work enqueued on `stream` afterwards
+ * sees those rows complete. */
+CUSYNC_API int cusync_mlp_wait_rows(cusync_mlp_t* mlp, uint32_t first_tile, uint32_t num_tiles, cusync_stream_t stream);
 /* Tail splits in use: out[0..3] = synchronised GEMM 1, 2, stream-ordered GEMM 1, 2. */
 CUSYNC_API int cusync_mlp_tail_splits(const cusync_mlp_t* mlp, int32_t* out4);
 

@@ -63,3 +63,49 @@ def test_mlp_layer_matches_oracle(model, batch, ffn, policy):
     torch.cuda.synchronize()
     assert o.max_rel_err(s.y[rows].cpu().numpy(), yref, floor_frac=5e-2) <= TOL
     s.destroy()
+
+
+@pytest.mark.parametrize("batch,max_ctas", [(1024, 128), (600, 0), (64, 0)])
+def test_output_rows_can_be_consumed_block_by_block(batch, max_ctas):
+    # post_rows: the second GEMM posts one RowSync semaphore per 128-row tile of Y; cusync_mlp_wait_rows lets
+    # another stream (in a tensor-parallel layer: the all-reduce) take row blocks as they complete.  Here the
+    # other stream copies each block right behind its wait; a block taken too early would carry the NaN poison.
+    from cusync_b200 import tp
+    dev = torch.device("cuda")
+    x, w1, w2, v = M.make_inputs("gpt3", batch, dev, seed=5)
+    s = M.MLPShard("gpt3", batch, x, w1, w2, v, policy="rowsync", post_rows=True, max_ctas=max_ctas)
+    ps, cs_, side = torch.cuda.Stream(priority=-1), torch.cuda.Stream(), torch.cuda.Stream()
+    tiles = (batch + 127) // 128
+    snap = torch.empty_like(s.y)
+    for it in range(1, 4):
+        s.h.fill_(float("nan")); s.y.fill_(float("nan")); snap.fill_(float("nan")); torch.cuda.synchronize()
+        s.run_cusync(ps, cs_)
+        per = max(tiles // 3, 1)
+        for first in range(0, tiles, per):
+            n = min(per, tiles - first)
+            s.wait_rows(first, n, side)
+            with torch.cuda.stream(side):
+                snap[first * 128:(first + n) * 128].copy_(s.y[first * 128:(first + n) * 128], non_blocking=True)
+        torch.cuda.synchronize()
+        assert s.status_codes() == (0, 0)
+        assert not torch.isnan(snap.float()).any()
+        assert torch.equal(snap, s.y)
+        # semaphore counts: every row tile of Y was posted once per column tile and run
+        st = L.lib().cusync_mlp_stage(s._h, 1)
+        sems = np.zeros(tiles, dtype=np.uint32)
+        import ctypes as C
+        assert L.lib().cusync_stage_read_semaphores(st, sems.ctypes.data_as(C.c_void_p), tiles) == L.SUCCESS
+        assert (sems == it * ((M.GPT3_HIDDEN + s.tile_n2 - 1) // s.tile_n2)).all()
+    # the helper used by the multi-GPU bench, on a world of one rank: waits only
+    g = tp.TensorParallelGroup("nccl", dev)
+    s.y.fill_(float("nan")); torch.cuda.synchronize()
+    s.run_cusync(ps, cs_)
+    g.all_reduce_rows_overlapped(s, side, 4)
+    side.synchronize()
+    assert not torch.isnan(s.y.float()).any()
+    torch.cuda.synchronize()
+    # without post_rows the call is refused
+    s2 = M.MLPShard("gpt3", batch, x, w1, w2, v, policy="rowsync")
+    with pytest.raises(L.CuSyncError):
+        s2.wait_rows(0, 1, side)
+    s2.destroy(); s.destroy()
