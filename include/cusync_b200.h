@@ -398,7 +398,7 @@ typedef struct cusync_mlp_desc {
   int32_t split_k1, split_k2;    /* 0 = choose (mlp.cu's --split-k1 / --split-k2) */
   int32_t max_ctas;              /* 0 = one per SM */
   int32_t cta_pair;              /* as cusync_gemm_desc_t.cta_pair, for both GEMMs */
-  int32_t group_rows2;           /* > 0: the consumer takes its tiles in CUSYNC_ORDER_GROUPED(group_rows2) order */
+  int32_t group_rows2;           /* the consumer's tile order: 0 = choose, 1 = plain, n > 1 = CUSYNC_ORDER_GROUPED(n) */
   int32_t tail_split_sync1, tail_split_sync2;    /* cusync_gemm_desc_t.tail_split of the two synchronised GEMMs ... */
   int32_t tail_split_plain1, tail_split_plain2;  /* ... and of the two stream-ordered ones: 0 = choose, 1 = none */
   int32_t post_rows;             /* 1: the second GEMM of run_cusync is a producer too: it posts RowSync semaphores, one
