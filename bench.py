@@ -393,14 +393,16 @@ def main():
         rows = []
         for b in (1, 64, 512, 2048):     # config 3: LLaMA 65B MLP shard, fused SwiGLU dual GEMM, ffn 2752
             x, w1, w2, v = M.make_inputs("llama", b, dev, seed=1)
-            sh = M.MLPShard("llama", b, x, w1, w2, v, policy="rowsync")
+            for pol in ("rowsync", "tilesync"):
+                sh = M.MLPShard("llama", b, x, w1, w2, v, policy=pol)
 
-            def c_step(sh=sh):
-                ps.wait_stream(cs); sh.run_cusync(ps, cs)
-            r = ab(c_step, lambda sh=sh: sh.run_stream_ordered(cs))
-            r.update({"batch": b, "tile_n": [sh.tile_n1, sh.tile_n2], "split_k": [sh.split_k1, sh.split_k2]})
-            rows.append(r); sh.destroy()
-        extras["llama_mlp_rowsync"] = rows
+                def c_step(sh=sh):
+                    ps.wait_stream(cs); sh.run_cusync(ps, cs)
+                r = ab(c_step, lambda sh=sh: sh.run_stream_ordered(cs))
+                r.update({"batch": b, "policy": pol, "tile_n": [sh.tile_n1, sh.tile_n2],
+                          "split_k": [sh.split_k1, sh.split_k2]})
+                rows.append(r); sh.destroy()
+        extras["llama_mlp"] = rows
 
         rows = []
         for n in (1, 8, 32):             # config 5: two 3x3 convolutions, 56x56x64, ReLU, Conv2DTileSync
@@ -421,6 +423,23 @@ def main():
             rows.append(r)
             chain.destroy()
         extras["resnet_conv3x3_chain_conv2dtilesync"] = rows
+
+        # vgg.cu-style chain of four 64-channel convolutions, one stream per convolution
+        g = torch.Generator(device=dev).manual_seed(44)
+        xin = torch.randn((8, 56, 56, 64), generator=g, device=dev).half()
+        fs = [(torch.randn((64, 3, 3, 64), generator=g, device=dev) * (2.0 / 576) ** 0.5).half() for _ in range(4)]
+        chain = lib_.ConvChain(xin, fs, relu=True)
+        side = [torch.cuda.Stream(), torch.cuda.Stream()]
+
+        def c4_step():
+            ps.wait_stream(cs); chain.run_cusync([ps, side[0], side[1], cs])
+
+        def o4_step():
+            chain.run_stream_ordered(cs)
+        r = ab(c4_step, o4_step)
+        r.update({"images": 8, "convs": 4})
+        extras["vgg_conv3x3_chain_of_4"] = [r]
+        chain.destroy()
 
         rows = []
         for b, seq in ((1, 512), (1, 2048), (4, 2048)):   # config 4: attention block, 12 heads of 128

@@ -88,7 +88,8 @@ class MlpDesc(C.Structure):
                 ("policy", C.c_int32), ("opts", C.c_int32), ("tile_n1", C.c_int32), ("tile_n2", C.c_int32),
                 ("split_k1", C.c_int32), ("split_k2", C.c_int32), ("max_ctas", C.c_int32), ("cta_pair", C.c_int32), ("group_rows2", C.c_int32),
                 ("tail_split_sync1", C.c_int32), ("tail_split_sync2", C.c_int32),
-                ("tail_split_plain1", C.c_int32), ("tail_split_plain2", C.c_int32), ("post_rows", C.c_int32),
+                ("tail_split_plain1", C.c_int32), ("tail_split_plain2", C.c_int32), ("group_rows1", C.c_int32),
+                ("post_rows", C.c_int32),
                 ("x", C.c_void_p), ("w1", C.c_void_p), ("v", C.c_void_p), ("w2", C.c_void_p),
                 ("h", C.c_void_p), ("y", C.c_void_p)]
 

@@ -42,1915 +42,12 @@
 
 #include "common.cuh"
 
+#include "sm100_device.cuh"
+#include "gemm_kernel_1cta.cuh"
+#include "conv3x3_slab_kernel.cuh"
+#include "gemm_kernel_pair.cuh"
+
 namespace {
-
-constexpr int kBlockM = 128;        // UMMA M
-constexpr int kBlockK = 64;         // one 128-byte swizzle row of fp16
-constexpr int kUmmaK = 16;
-constexpr int kThreads = 384;
-constexpr int kEpilogueWarps = 8;    // two per TMEM lane quarter: keeps every scheduler fed during the epilogue
-constexpr int kSchedSlots = 8;
-constexpr int kEpilogueWarp0 = 4;
-constexpr int kLookahead = 8;       // semaphores probed ahead of a consumer wait
-constexpr int kStoreCols = 64;      // columns per TMA store box (128 bytes)
-constexpr uint32_t kSmemLimit = 232448;  // 227 KB
-
-// ---------------------------------------------------------------------------
-// PTX wrappers
-// ---------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-// Arrive on a barrier of any CTA of the cluster, given its shared::cluster address.
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ void fence_barrier_init() {
-  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-}
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
-__device__ __forceinline__ void fence_proxy_async_smem() {
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
-      : "memory");
-}
-__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2,
-                                            int c3) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
-      : "memory");
-}
-__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
-      : "memory");
-}
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int c0, int c1) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
-                   reinterpret_cast<uint64_t>(map)),
-               "r"(smem_u32(src)), "r"(c0), "r"(c1)
-               : "memory");
-}
-// Element-wise add of a shared-memory box into global memory, done by the TMA unit at the L2.
-__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, const void* src, int c0, int c1) {
-  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
-                   reinterpret_cast<uint64_t>(map)),
-               "r"(smem_u32(src)), "r"(c0), "r"(c1)
-               : "memory");
-}
-__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void tma_store_wait_read() {
-  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
-}
-__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
-  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
-}
-
-__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)),
-               "r"(ncols)
-               : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                         uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
-}
-__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t* r) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor for tcgen05.mma: 128-byte swizzle, Blackwell
-// descriptor version 1.  Offsets are given in bytes.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
-  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
-  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
-  d |= 1ull << 46;   // descriptor version
-  d |= 2ull << 61;   // SWIZZLE_128B
-  return d;
-}
-
-// Instruction descriptor, kind::f16: D = f32, A = B = f16, A K-major.
-__host__ __device__ constexpr uint32_t make_idesc(int umma_n, bool b_mn_major) {
-  return (1u << 4) | (0u << 7) | (0u << 10) | (0u << 15) | ((b_mn_major ? 1u : 0u) << 16) |
-         (static_cast<uint32_t>(umma_n >> 3) << 17) | (static_cast<uint32_t>(kBlockM >> 4) << 24);
-}
-
-// ---------------------------------------------------------------------------
-// Kernel parameters
-// ---------------------------------------------------------------------------
-// One work unit of the CTA-pair kernel: K slice `slice` of `nslices` of the pair tile (x = N tile, y = pair row).
-// Tiles of the last, partial wave may be cut into more slices than the others (see setup_pair).  A split tile
-// owns `nslices` consecutive 256 x 256 fp32 slots of the workspace, starting at slot ws_tile * nslices.
-struct PairUnit { uint32_t x, y, slice_of, ws_tile; };   // slice_of = slice | nslices << 16
-
-struct GemmParams {
-  int32_t m, n, k;
-  int32_t tiles_n, tiles_m, num_tiles;
-  int32_t num_k_blocks;
-  int32_t epilogue;
-  int32_t b_kmajor;            // 1: B given as [n,k] row-major
-  int32_t b_chunked3d;         // [k,n] B: all 64-column chunks of a tile come with one 3-D TMA box
-  int32_t is_producer, is_consumer;
-  uint32_t b_lbo, b_sbo, b_kstep;  // B shared-memory descriptor: leading / stride offsets, bytes per UMMA K step
-  void* d; long long ldd;          // output matrix (split-K finalisation stores it without TMA)
-  int32_t split_k;                 // K slices per output tile (grid.z of the stage); 1 = none
-  int32_t k_blocks_per_split;      // ring stages per slice
-  float* splitk_ws;                // fp32 [tiles_m * 128, n] partial sums, all zero between launches
-  uint32_t* splitk_arrivals;       // per (m, n) tile: slices that have added their part
-  // 3x3 convolution as implicit GEMM (CONV kernels): NHWC input [conv_n, conv_h, conv_w, conv_c]; an M tile
-  // is conv_rows whole image rows (conv_rows * conv_w <= 128 output pixels); K walks channel chunks of 64
-  // outermost and the nine filter taps innermost.
-  int32_t conv_n, conv_h, conv_w, conv_c, conv_rows, conv_tiles_per_image;
-  const PairUnit* pair_order;      // CTA-pair kernel: schedule over work units (256-row pair tile x K slice)
-  int32_t num_pairs;
-  unsigned long long* trace;       // optional per-tile timeline: 4 words per ticket (see cusync_gemm_plan_set_trace)
-  uint32_t trace_capacity;
-  cusync_stage_view_t stage;   // by-value copy, like params_.custage in the reference
-};
-
-template <int BN, bool DUAL>
-struct Cfg {
-  static constexpr int kNumB = DUAL ? 2 : 1;
-  static constexpr int kABytes = kBlockM * kBlockK * 2;
-  static constexpr int kBBytes = BN * kBlockK * 2;
-  static constexpr int kStageBytes = kABytes + kNumB * kBBytes;
-  static constexpr int kStagingBytes = kEpilogueWarps * 32 * 128;   // one 32-row x 128-byte buffer per epilogue warp
-  static constexpr int kBarrierBytes = 1024;
-  static constexpr int kStages =
-      ((int)kSmemLimit - 1024 /*alignment slack*/ - kStagingBytes - kBarrierBytes) / kStageBytes > 8
-          ? 8
-          : ((int)kSmemLimit - 1024 - kStagingBytes - kBarrierBytes) / kStageBytes;
-  static constexpr int kAccCols = BN * kNumB;               // fp32 columns per accumulator buffer
-  static constexpr int kTmemCols = 2 * kAccCols < 32 ? 32 : 2 * kAccCols;
-  static constexpr uint32_t kSmemBytes = 1024 + kStages * kStageBytes + kStagingBytes + kBarrierBytes;
-  static_assert(kTmemCols <= 512, "accumulators exceed tensor memory");
-  static_assert((kTmemCols & (kTmemCols - 1)) == 0, "TMEM columns must be a power of two");
-  static_assert(kSmemBytes <= kSmemLimit, "shared memory over budget");
-  static_assert(kStages >= 3, "pipeline too shallow");
-};
-
-struct Barriers {
-  uint64_t full[8];
-  uint64_t empty[8];
-  uint64_t tmem_full[2];
-  uint64_t tmem_empty[2];
-  uint64_t sched_full[kSchedSlots];
-  uint64_t sched_empty[kSchedSlots];
-  uint64_t drain;
-  uint64_t post;                        // epilogue warps -> the posting thread
-  uint64_t post_slot[kSchedSlots];      // slab kernel: the same, one barrier per schedule slot
-  uint64_t splitk_counted;              // posting thread -> epilogue warps: arrival counted, `splitk_last` valid
-  uint64_t splitk_done;                 // epilogue warps -> posting thread: finalisation stored
-  uint32_t splitk_last;
-  uint32_t pad0;
-  int32_t sched_tile[kSchedSlots][8];   // {n tile, m tile, valid, ticket, k slice, k slices of the tile, -, -}
-  unsigned long long sched_time[kSchedSlots];   // globaltimer at the ticket draw (tracing only)
-  uint32_t tmem_base;
-  volatile uint32_t abort;
-};
-static_assert(sizeof(Barriers) <= 1024, "barrier block too large");
-
-struct WaitCtx {
-  volatile uint32_t* abort;
-  uint32_t* status;
-  uint64_t timeout_ns;
-};
-
-// Bounded mbarrier wait.  Returns false when the block is aborting or the
-// bound expired (then it raises the abort flag itself).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& ctx) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = cusync::globalTimerNs();
-  uint32_t polls = 0;
-  while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((++polls & 31u) == 0u) {
-      if (*ctx.abort) return false;
-      if (cusync::globalTimerNs() - t0 > ctx.timeout_ns) {
-        *ctx.abort = 1u;
-        cusync::recordTimeout(ctx.status, 2u, blockIdx.x, threadIdx.x, parity, smem_u32(bar), 0u, 0u);
-        return false;
-      }
-    }
-  }
-}
-
-__device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f)); }
-__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
-
-__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
-  __half2 h = __floats2half2_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&h);
-}
-
-// Epilogue of one warp for one tile: its 32 accumulator rows (TMEM lanes of `t_row`), every second
-// 64-column chunk starting at `half`: tcgen05.ld -> fp32 epilogue math -> fp16 -> swizzled staging
-// buffer -> TMA store.  `row0` is the matrix row of the warp's first lane.
-template <int BN, bool DUAL>
-__device__ __forceinline__ void epilogue_store_rows(const GemmParams& p, const CUtensorMap* tmD, uint8_t* buf,
-                                                    uint32_t t_row, int n_off, int row0, int half, int lane) {
-  const bool rows_in = row0 < p.m;                      // else this warp's 32 rows are all padding
-#pragma unroll 1
-  for (int c = half; c < BN / kStoreCols && rows_in; c += 2) {
-    if (n_off + c * kStoreCols >= p.n) break;           // chunk entirely past the matrix edge
-    // The store that last read this warp's buffer must be done reading it.
-    if (lane == 0) tma_store_wait_read<0>();
-    __syncwarp();
-    uint32_t packed[32];
-    if (!DUAL) {
-      uint32_t v[64];
-      tmem_ld_32x32b_x32(t_row + c * 64, v);
-      tmem_ld_32x32b_x32(t_row + c * 64 + 32, v + 32);
-      tmem_ld_wait();
-#pragma unroll
-      for (int j = 0; j < 32; j++) {
-        float x0 = __uint_as_float(v[2 * j]), x1 = __uint_as_float(v[2 * j + 1]);
-        if (p.epilogue == CUSYNC_EPILOGUE_GELU_ERF) { x0 = gelu_erf(x0); x1 = gelu_erf(x1); }
-        else if (p.epilogue == CUSYNC_EPILOGUE_RELU) { x0 = fmaxf(x0, 0.0f); x1 = fmaxf(x1, 0.0f); }
-        packed[j] = pack_half2(x0, x1);
-      }
-    } else {
-#pragma unroll
-      for (int h = 0; h < 2; h++) {
-        uint32_t a[32], b[32];
-        tmem_ld_32x32b_x32(t_row + c * 64 + h * 32, a);
-        tmem_ld_32x32b_x32(t_row + BN + c * 64 + h * 32, b);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 16; j++) {
-          float g0 = silu(__uint_as_float(a[2 * j])) * __uint_as_float(b[2 * j]);
-          float g1 = silu(__uint_as_float(a[2 * j + 1])) * __uint_as_float(b[2 * j + 1]);
-          packed[h * 16 + j] = pack_half2(g0, g1);
-        }
-      }
-    }
-    // Row `lane` of the 32 x 64 chunk, 16-byte pieces XOR-swizzled by row so
-    // the layout is the one a 128-byte-swizzle tensor map expects.
-    uint8_t* row = buf + lane * 128;
-#pragma unroll
-    for (int q = 0; q < 8; q++) {
-      uint4 val = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-      *reinterpret_cast<uint4*>(row + ((q ^ (lane & 7)) << 4)) = val;
-    }
-    fence_proxy_async_smem();
-    __syncwarp();
-    if (lane == 0) {
-      tma_store_2d(tmD, buf, n_off + c * kStoreCols, row0);
-      tma_store_commit();
-    }
-  }
-}
-
-
-// Split-K, phase 1: one warp adds its 32 accumulator rows (every second 64-column span from `half`, in two
-// 32-column boxes) into the fp32 workspace: tcgen05.ld -> swizzled staging buffer -> TMA reduce-add.  The
-// workspace map covers exactly m rows and n columns, so padding rows and columns are clipped by the TMA.
-template <int BN>
-__device__ __forceinline__ void splitk_accumulate_rows(const GemmParams& p, const CUtensorMap* tmWS, uint8_t* buf,
-                                                       uint32_t t_row, int n_off, int row0, int half, int lane) {
-  if (row0 >= p.m) return;
-#pragma unroll 1
-  for (int c = half; c < BN / kStoreCols; c += 2) {
-#pragma unroll 1
-    for (int h = 0; h < 2; h++) {
-      const int col0 = n_off + c * kStoreCols + h * 32;
-      if (col0 >= p.n) return;
-      if (lane == 0) tma_store_wait_read<0>();     // the previous box has left this warp's staging buffer
-      __syncwarp();
-      uint32_t v[32];
-      tmem_ld_32x32b_x32(t_row + c * 64 + h * 32, v);
-      tmem_ld_wait();
-      uint8_t* row = buf + lane * 128;             // 32 fp32 = 128 bytes per row, 16-byte pieces XOR-swizzled
-#pragma unroll
-      for (int q = 0; q < 8; q++)
-        *reinterpret_cast<uint4*>(row + ((q ^ (lane & 7)) << 4)) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) {
-        tma_reduce_add_2d(tmWS, buf, col0, row0);
-        tma_store_commit();
-      }
-    }
-  }
-}
-
-// Split-K, phase 2 (only in the block that brought the last slice): the 256 epilogue threads read the
-// summed tile back, zero it for the next launch, apply the epilogue and store fp16.
-template <int BN>
-__device__ __forceinline__ void splitk_finalize_tile(const GemmParams& p, __half* d, int64_t ldd, int n_off, int m_off,
-                                                     int tid) {
-  const int rows = p.m - m_off < kBlockM ? p.m - m_off : kBlockM;
-  constexpr int kVecPerRow = BN / 4;
-  constexpr int kThreadsE = kEpilogueWarps * 32;
-  constexpr int kBatch = 8;                 // loads in flight per thread: the reads are L2 round trips
-  const int total = rows * kVecPerRow;
-  for (int base = tid; base < total; base += kThreadsE * kBatch) {
-    float4 x[kBatch];
-    float4* src[kBatch];
-#pragma unroll
-    for (int j = 0; j < kBatch; j++) {
-      const int i = base + j * kThreadsE;
-      const int r = i / kVecPerRow, c = (i % kVecPerRow) * 4;
-      const bool in = i < total && n_off + c < p.n;
-      src[j] = in ? reinterpret_cast<float4*>(p.splitk_ws + static_cast<size_t>(m_off + r) * p.n + n_off + c) : nullptr;
-      if (in) x[j] = __ldcg(src[j]);
-    }
-#pragma unroll
-    for (int j = 0; j < kBatch; j++) {
-      if (src[j] == nullptr) continue;
-      const int i = base + j * kThreadsE;
-      const int r = i / kVecPerRow, c = (i % kVecPerRow) * 4;
-      __stcg(src[j], make_float4(0.f, 0.f, 0.f, 0.f));
-      float4 v = x[j];
-      if (p.epilogue == CUSYNC_EPILOGUE_GELU_ERF) { v.x = gelu_erf(v.x); v.y = gelu_erf(v.y); v.z = gelu_erf(v.z); v.w = gelu_erf(v.w); }
-      else if (p.epilogue == CUSYNC_EPILOGUE_RELU) { v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f); v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f); }
-      *reinterpret_cast<uint2*>(d + static_cast<size_t>(m_off + r) * ldd + n_off + c) =
-          make_uint2(pack_half2(v.x, v.y), pack_half2(v.z, v.w));
-    }
-  }
-}
-
-// CTA-pair kernel, split tiles.  Every K slice of a split tile owns a 256 x 256 fp32 slot of the workspace
-// (first the leader CTA's 128 rows, then the peer's).  Inside a CTA's part the order is the one the epilogue
-// warps produce and consume: 32-row x 32-column boxes, box (row quarter, column block) at float4 index
-// ((quarter * 8 + block) * 8 + q) * 32 + lane for columns [4q, 4q + 4) of row `lane` of the box, so that both
-// the slices' stores and the finaliser's loads are 512 contiguous bytes per warp instruction.
-constexpr int kPairBN = 256;                                // tile width of the pair kernel
-constexpr int kPairSlotVec4 = 2 * kBlockM * kPairBN / 4;    // float4 per slot
-
-// Phase 1: one warp stores its 32 accumulator rows (every second 64-column span from `half`) straight from
-// registers: plain stores that L2 takes at write bandwidth (reduce-adds of all slices into one tile were
-// bound by the L2's atomic rate, and staging through shared memory by the per-box round trip).
-template <int BN>
-__device__ __forceinline__ void pair_store_partial_rows(float4* cta_part, uint32_t t_row, int quarter, int half, int lane) {
-#pragma unroll 1
-  for (int c = half; c < BN / kStoreCols; c += 2) {
-    uint32_t v[64];
-    tmem_ld_32x32b_x32(t_row + c * 64, v);
-    tmem_ld_32x32b_x32(t_row + c * 64 + 32, v + 32);
-    tmem_ld_wait();
-    float4* dst = cta_part + ((quarter * 8 + c * 2) * 8) * 32 + lane;
-#pragma unroll
-    for (int j = 0; j < 16; j++)
-      __stcg(dst + j * 32, make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
-                                       __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3])));
-  }
-  __threadfence();     // every lane's stores are ordered before the arrival count that follows
-}
-
-// Phase 2 (only in the CTA that counted the last slice): each warp adds up the slices' slots for its own rows
-// and column spans, in slice order (so the sum does not depend on which slice came last), then does what the
-// unsplit epilogue does: epilogue math -> fp16 -> swizzled staging buffer -> TMA store.
-template <int BN>
-__device__ __forceinline__ void pair_finalize_partials(const GemmParams& p, const CUtensorMap* tmD, uint8_t* buf,
-                                                       const float4* cta_part0, uint32_t nslices, int n_off, int row0,
-                                                       int quarter, int half, int lane) {
-  const bool rows_in = row0 < p.m;
-#pragma unroll 1
-  for (int c = half; c < BN / kStoreCols && rows_in; c += 2) {
-    if (n_off + c * kStoreCols >= p.n) break;
-    float acc[64];
-#pragma unroll
-    for (int j = 0; j < 64; j++) acc[j] = 0.f;
-    const float4* src = cta_part0 + ((quarter * 8 + c * 2) * 8) * 32 + lane;
-#pragma unroll 1
-    for (uint32_t sl = 0; sl < nslices; sl++, src += kPairSlotVec4) {
-      float4 x[16];
-#pragma unroll
-      for (int j = 0; j < 16; j++) x[j] = __ldcg(src + j * 32);
-#pragma unroll
-      for (int j = 0; j < 16; j++) { acc[4 * j] += x[j].x; acc[4 * j + 1] += x[j].y; acc[4 * j + 2] += x[j].z; acc[4 * j + 3] += x[j].w; }
-    }
-    if (lane == 0) tma_store_wait_read<0>();     // the store that last read this warp's buffer is done with it
-    __syncwarp();
-    uint32_t packed[32];
-#pragma unroll
-    for (int j = 0; j < 32; j++) {
-      float x0 = acc[2 * j], x1 = acc[2 * j + 1];
-      if (p.epilogue == CUSYNC_EPILOGUE_GELU_ERF) { x0 = gelu_erf(x0); x1 = gelu_erf(x1); }
-      else if (p.epilogue == CUSYNC_EPILOGUE_RELU) { x0 = fmaxf(x0, 0.0f); x1 = fmaxf(x1, 0.0f); }
-      packed[j] = pack_half2(x0, x1);
-    }
-    uint8_t* row = buf + lane * 128;
-#pragma unroll
-    for (int q = 0; q < 8; q++)
-      *reinterpret_cast<uint4*>(row + ((q ^ (lane & 7)) << 4)) =
-          make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-    fence_proxy_async_smem();
-    __syncwarp();
-    if (lane == 0) {
-      tma_store_2d(tmD, buf, n_off + c * kStoreCols, row0);
-      tma_store_commit();
-    }
-  }
-  if (lane == 0) tma_store_wait_all();           // the tile is in memory before the caller publishes it
-}
-
-// Split-K epilogue of one tile for one epilogue warp; returns false if a bounded wait expired.
-// Every slice adds its part; the block that counts the last arrival finalises and publishes the tile
-// (the reference posts from the last K slice only, gemm/kernel/cusyncgemm.h:374-392).
-template <int BN>
-__device__ __forceinline__ bool splitk_epilogue(const GemmParams& p, const CUtensorMap* tmWS, uint8_t* buf,
-                                                Barriers* bars, const WaitCtx& ctx, uint32_t t_row,
-                                                int n_off, int m_off, int quarter, int half, int ew, int lane,
-                                                uint32_t phase, uint32_t split_phase, uint32_t nslices,
-                                                uint64_t* tmem_empty_local, uint32_t tmem_empty_cluster,
-                                                __half* d, int64_t ldd, bool* is_last,
-                                                float4* ws_part0 = nullptr, uint32_t slice = 0,
-                                                const CUtensorMap* tmD = nullptr) {
-  // ws_part0 (CTA-pair kernel): this CTA's part of the tile's first workspace slot; slice `slice` stores
-  // into the slot `slice` slots further on.  Without it the slices reduce-add into one [m, n] tile.
-  if (ws_part0) { if (m_off < p.m) pair_store_partial_rows<BN>(ws_part0 + static_cast<size_t>(slice) * kPairSlotVec4, t_row, quarter, half, lane); }
-  else splitk_accumulate_rows<BN>(p, tmWS, buf, t_row, n_off, m_off + quarter * 32, half, lane);
-  // accumulator buffer is free for the MMA warp again
-  tc_fence_before();
-  __syncwarp();
-  bool lane0_ok = true;
-  if (lane == 0) {
-    if (tmem_empty_local) mbar_arrive(tmem_empty_local); else mbar_arrive_cluster(tmem_empty_cluster);
-    tma_store_wait_all();            // this warp's reduce-adds have been performed ...
-    __threadfence();                 // ... and are ordered before the arrival count
-    // (a warp that ran ahead must not arrive while the previous tile's phase of `post` is still open)
-    if (!mbar_wait(&bars->post, phase ^ 1u, ctx)) lane0_ok = false;
-    mbar_arrive(&bars->post);
-  }
-  bool ok = lane0_ok;
-  if (ew == 0 && lane == 0) {
-    if (!mbar_wait(&bars->post, phase, ctx)) ok = false;
-    else if (m_off >= p.m) bars->splitk_last = 0u;     // a pair's second half past the last row tile
-    else {
-      const uint32_t tile = static_cast<uint32_t>(m_off / kBlockM) * static_cast<uint32_t>(p.tiles_n) +
-                            static_cast<uint32_t>(n_off / BN);
-      __threadfence();
-      const uint32_t before = atomicAdd(p.splitk_arrivals + tile, 1u);
-      const uint32_t last = before == nslices - 1u ? 1u : 0u;
-      if (last) { p.splitk_arrivals[tile] = 0u; __threadfence(); }   // re-armed for the next launch
-      bars->splitk_last = last;
-    }
-    mbar_arrive(&bars->splitk_counted);
-  }
-  if (!mbar_wait(&bars->splitk_counted, split_phase, ctx)) ok = false;
-  const bool last = ok && bars->splitk_last != 0u;
-  __syncwarp();
-  if (last) {
-    if (ws_part0) pair_finalize_partials<BN>(p, tmD, buf, ws_part0, nslices, n_off, m_off + quarter * 32, quarter, half, lane);
-    else splitk_finalize_tile<BN>(p, d, ldd, n_off, m_off, ew * 32 + lane);
-  }
-  __syncwarp();
-  if (lane == 0) { __threadfence(); mbar_arrive(&bars->splitk_done); }
-  *is_last = last;
-  return ok;
-}
-
-// ---------------------------------------------------------------------------
-// The kernel
-// ---------------------------------------------------------------------------
-template <int BN, bool DUAL, bool CONV = false>
-__global__ void __launch_bounds__(kThreads, 1)
-cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                   const __grid_constant__ CUtensorMap tmB2, const __grid_constant__ CUtensorMap tmD,
-                   const __grid_constant__ CUtensorMap tmWS, const GemmParams p) {
-  using C = Cfg<BN, DUAL>;
-  extern __shared__ uint8_t smem_raw[];
-  // 128-byte swizzle patterns repeat every 1024 bytes: align the ring to that.
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* ring = smem;
-  uint8_t* staging = smem + C::kStages * C::kStageBytes;
-  Barriers* bars = reinterpret_cast<Barriers*>(staging + C::kStagingBytes);
-
-  const int warp = threadIdx.x >> 5;
-  const int lane = threadIdx.x & 31;
-  const cusync_stage_view_t& st = p.stage;
-  WaitCtx ctx{&bars->abort, st.status, 2 * st.timeout_ns + 1000000000ull};
-
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < C::kStages; i++) { mbar_init(&bars->full[i], 1); mbar_init(&bars->empty[i], 1); }
-    for (int i = 0; i < 2; i++) { mbar_init(&bars->tmem_full[i], 1); mbar_init(&bars->tmem_empty[i], kEpilogueWarps); }
-    for (int i = 0; i < kSchedSlots; i++) { mbar_init(&bars->sched_full[i], 1); mbar_init(&bars->sched_empty[i], 1 + kEpilogueWarps); }
-    mbar_init(&bars->drain, 1);
-    mbar_init(&bars->post, kEpilogueWarps);
-    mbar_init(&bars->splitk_counted, 1);
-    mbar_init(&bars->splitk_done, kEpilogueWarps);
-    bars->abort = 0u;
-    fence_barrier_init();
-    fence_proxy_async_smem();
-    // "Kernel started" words the wait kernel polls: [0] follows the reference
-    // (block 0 stores iter, cusync_device_defs.h:78-83); [1] counts resident blocks.
-    if (p.is_producer) {
-      if (blockIdx.x == 0) cusync::storeRelease(st.started, st.iter);
-      cusync::addRelease(st.started + 1, 1u);
-    }
-  }
-  if (warp == 0 && lane == 0) {
-    prefetch_tensormap(&tmA); prefetch_tensormap(&tmB); prefetch_tensormap(&tmD);
-    if (DUAL) prefetch_tensormap(&tmB2);
-  }
-  if (warp == 2) {
-    tmem_alloc(&bars->tmem_base, C::kTmemCols);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = bars->tmem_base;
-
-  if (warp == 0) {
-    // =====================================================================
-    // Scheduler + TMA loader
-    // =====================================================================
-    if (lane == 0) {
-      uint32_t fills = 0, sched_it = 0;
-      bool ok = true;
-      const uint32_t total_draws = static_cast<uint32_t>(p.num_tiles) + gridDim.x;
-      const uint32_t wait_target = p.is_consumer ? st.iter * cusync::eval::waitValue(st.in_policy) : 0u;
-      // Distance along K between two sync points of the input policy (0: it syncs once per tile).
-      uint32_t sync_stride = 0;
-      if (p.is_consumer) {
-        const int kind = st.in_policy.kind;
-        if (kind == CUSYNC_POLICY_TILESYNC || kind == CUSYNC_POLICY_STRIDEDTILESYNC) sync_stride = st.in_policy.tile_n;
-        else if (kind == CUSYNC_POLICY_CONV2DTILESYNC) sync_stride = st.in_policy.tile_n * st.in_policy.p0;
-      }
-      while (ok) {
-        const uint32_t slot = sched_it % kSchedSlots, sph = (sched_it / kSchedSlots) & 1u;
-        if (!mbar_wait(&bars->sched_empty[slot], sph ^ 1u, ctx)) { ok = false; break; }
-        const uint32_t ticket = atomicAdd(st.tile_counter, 1u);
-        // Every block draws exactly one ticket past the end, so the draw
-        // numbered total_draws-1 is the launch's last: it re-arms the counter
-        // (the reference resets on the last tile, cusync_device_defs.h:87-90).
-        if (ticket == total_draws - 1u) atomicExch(st.tile_counter, 0u);
-        const bool valid = ticket < static_cast<uint32_t>(p.num_tiles);
-        cusync_dim3_t t = {0, 0, 0};
-        if (valid) t = st.tile_order[ticket];
-        bars->sched_tile[slot][0] = static_cast<int32_t>(t.x);
-        bars->sched_tile[slot][1] = static_cast<int32_t>(t.y);
-        bars->sched_tile[slot][2] = valid ? 1 : 0;
-        bars->sched_tile[slot][3] = static_cast<int32_t>(ticket);
-        bars->sched_tile[slot][4] = static_cast<int32_t>(t.z);
-        if (p.trace) bars->sched_time[slot] = cusync::globalTimerNs();
-        mbar_arrive(&bars->sched_full[slot]);
-        sched_it++;
-        if (!valid) break;
-
-        const int n_off = static_cast<int>(t.x) * BN;
-        // Row offset of the tile: 128 matrix rows, or for a convolution conv_rows image rows of output pixels.
-        const int m_off = CONV ? static_cast<int>(t.y) * p.conv_rows * p.conv_w : static_cast<int>(t.y) * kBlockM;
-        const int img = CONV ? static_cast<int>(t.y) / p.conv_tiles_per_image : 0;
-        const int h0 = CONV ? (static_cast<int>(t.y) % p.conv_tiles_per_image) * p.conv_rows : 0;
-        // K slice of this work unit (the whole K walk without split-K)
-        const int kb_begin = static_cast<int>(t.z) * p.k_blocks_per_split;
-        const int kb_end = kb_begin + p.k_blocks_per_split < p.num_k_blocks ? kb_begin + p.k_blocks_per_split
-                                                                           : p.num_k_blocks;
-        uint32_t ready_end = 0;   // K offset below which this tile's producer tiles are known finished
-        long long wait_empty = 0;
-        for (int kb = kb_begin; kb < kb_end; kb++) {
-          const uint32_t s = fills % C::kStages, ph = (fills / C::kStages) & 1u;
-          const long long c0 = p.trace ? clock64() : 0;
-          if (!mbar_wait(&bars->empty[s], ph ^ 1u, ctx)) { ok = false; break; }
-          if (p.trace) wait_empty += clock64() - c0;
-          uint8_t* sa = ring + s * C::kStageBytes;
-          uint8_t* sb = sa + C::kABytes;
-          // A convolution's A box holds conv_rows * conv_w pixel rows of 128 bytes, not the full 128.
-          mbar_expect_tx(&bars->full[s], CONV ? static_cast<uint32_t>(p.conv_rows * p.conv_w * 128 + C::kNumB * C::kBBytes)
-                                              : static_cast<uint32_t>(C::kStageBytes));
-          const int k_off = kb * kBlockK;
-          // Convolution: K block kb is channel chunk kb / 9, filter tap (r, s) = kb % 9; the filter is
-          // [k_out][r][s][c], so its K offset is tap * C + chunk * 64.
-          const int tap = CONV ? kb % 9 : 0, chunk = CONV ? kb / 9 : 0;
-          // Weights first: they never depend on the producer kernel.
-          if (CONV) {
-            tma_load_2d(sb, &tmB, &bars->full[s], tap * p.conv_c + chunk * kBlockK, n_off);
-          } else if (p.b_kmajor) {
-            tma_load_2d(sb, &tmB, &bars->full[s], k_off, n_off);
-            if (DUAL) tma_load_2d(sb + C::kBBytes, &tmB2, &bars->full[s], k_off, n_off);
-          } else if (p.b_chunked3d) {
-            // one box {64 columns, kBlockK rows, BN/64 chunks}: a TMA instruction costs the issuing
-            // thread over a hundred cycles, so fewer and larger boxes keep the loader ahead of the MMAs
-            tma_load_3d(sb, &tmB, &bars->full[s], 0, k_off, n_off / 64);
-            if (DUAL) tma_load_3d(sb + C::kBBytes, &tmB2, &bars->full[s], 0, k_off, n_off / 64);
-          } else {
-#pragma unroll
-            for (int j = 0; j < BN / 64; j++)
-              tma_load_2d(sb + j * (kBlockK * 128), &tmB, &bars->full[s], n_off + j * 64, k_off);
-            if (DUAL) {
-#pragma unroll
-              for (int j = 0; j < BN / 64; j++)
-                tma_load_2d(sb + C::kBBytes + j * (kBlockK * 128), &tmB2, &bars->full[s], n_off + j * 64, k_off);
-            }
-          }
-          // Consumer wait, at the load of the dependent A K-block.
-          if (p.is_consumer) {
-            const uint32_t tz = kb == kb_begin ? 1u : 0u;
-            if (static_cast<uint32_t>(k_off) >= ready_end &&
-                cusync::eval::isSync(st.in_policy, static_cast<uint32_t>(k_off), tz)) {
-              const uint32_t idx = cusync::eval::tileIndex(st.in_policy, static_cast<uint32_t>(m_off),
-                                                           static_cast<uint32_t>(k_off), st.prod_grid.x,
-                                                           st.prod_grid.y);
-              uint32_t seen = 0;
-              // Convolution: the tile's own semaphore and those of its two halo neighbours are probed
-              // together first (one memory round trip instead of three); only what is still missing is
-              // then waited for.
-              bool conv_all_ready = false;
-              if (CONV) {
-                const int tin = static_cast<int>(t.y) % p.conv_tiles_per_image;
-                const int span = p.conv_rows * p.conv_w;
-                const uint32_t i_up = tin > 0 ? cusync::eval::tileIndex(st.in_policy, static_cast<uint32_t>(m_off - span),
-                                                    static_cast<uint32_t>(k_off), st.prod_grid.x, st.prod_grid.y) : idx;
-                const uint32_t i_dn = tin + 1 < p.conv_tiles_per_image
-                                          ? cusync::eval::tileIndex(st.in_policy, static_cast<uint32_t>(m_off + span),
-                                                static_cast<uint32_t>(k_off), st.prod_grid.x, st.prod_grid.y) : idx;
-                const uint32_t v0 = cusync::loadRelaxed(st.sems_wait + idx);
-                const uint32_t v1 = cusync::loadRelaxed(st.sems_wait + i_up);
-                const uint32_t v2 = cusync::loadRelaxed(st.sems_wait + i_dn);
-                conv_all_ready = v0 >= wait_target && v1 >= wait_target && v2 >= wait_target;
-                if (conv_all_ready) __threadfence();
-              }
-              if (!conv_all_ready &&
-                  !cusync::spinUntilAtLeast(st.sems_wait + idx, wait_target, st.timeout_ns, &seen)) {
-                bars->abort = 1u;
-                cusync::recordTimeout(st.status, 1u, static_cast<uint32_t>(m_off), static_cast<uint32_t>(k_off), tz,
-                                      idx, seen, wait_target);
-                // The stage was armed: give it its A bytes anyway so the
-                // barrier completes and the drain below terminates.
-                if (CONV) tma_load_4d(sa, &tmA, &bars->full[s], chunk * kBlockK, tap % 3 - 1, h0 + tap / 3 - 1, img);
-                else      tma_load_2d(sa, &tmA, &bars->full[s], k_off, m_off);
-                fills++;
-                ok = false;
-                break;
-              }
-              // Look ahead: probe the semaphores of the next producer tiles along K with independent
-              // relaxed loads (one memory round trip for all of them) and remember how far the
-              // finished prefix reaches, so later K-blocks skip the wait.  The relaxed loads are
-              // made acquiring by the fence that follows.
-              if (sync_stride) {
-                uint32_t vals[kLookahead];
-#pragma unroll
-                for (int j = 0; j < kLookahead; j++) {
-                  const uint32_t kk = static_cast<uint32_t>(k_off) + (j + 1) * sync_stride;
-                  vals[j] = kk < static_cast<uint32_t>(p.k)
-                                ? cusync::loadRelaxed(st.sems_wait + cusync::eval::tileIndex(st.in_policy,
-                                      static_cast<uint32_t>(m_off), kk, st.prod_grid.x, st.prod_grid.y))
-                                : 0u;
-                }
-                uint32_t ahead = 0;
-#pragma unroll
-                for (int j = 0; j < kLookahead; j++) {
-                  if (ahead == static_cast<uint32_t>(j) && vals[j] >= wait_target) ahead++;
-                }
-                ready_end = static_cast<uint32_t>(k_off) + (ahead + 1) * sync_stride;
-                if (ahead) __threadfence();
-              }
-              // A 3x3 stencil also reads the image rows just above and below the tile: they belong to
-              // the neighbouring producer tiles of the same image, which the reference's policy does
-              // not wait for (it relies on tile order); wait for them as well.
-              if (CONV && !conv_all_ready) {
-                bool halo_ok = true;
-                for (int dm = -1; dm <= 1 && halo_ok; dm += 2) {
-                  const int nb = static_cast<int>(t.y) % p.conv_tiles_per_image + dm;
-                  if (nb < 0 || nb >= p.conv_tiles_per_image) continue;
-                  const uint32_t nidx = cusync::eval::tileIndex(
-                      st.in_policy, static_cast<uint32_t>(m_off + dm * p.conv_rows * p.conv_w),
-                      static_cast<uint32_t>(k_off), st.prod_grid.x, st.prod_grid.y);
-                  if (!cusync::spinUntilAtLeast(st.sems_wait + nidx, wait_target, st.timeout_ns, &seen)) {
-                    bars->abort = 1u;
-                    cusync::recordTimeout(st.status, 1u, static_cast<uint32_t>(m_off), static_cast<uint32_t>(k_off), 2u,
-                                          nidx, seen, wait_target);
-                    halo_ok = false;
-                  }
-                }
-                if (!halo_ok) {
-                  tma_load_4d(sa, &tmA, &bars->full[s], chunk * kBlockK, tap % 3 - 1, h0 + tap / 3 - 1, img);
-                  fills++;
-                  ok = false;
-                  break;
-                }
-              }
-              // Order the acquire (generic proxy) before the TMA read (async proxy).
-              fence_proxy_async();
-            }
-          }
-          // Convolution: the box {64 channels, W pixels, conv_rows rows, 1 image} shifted by the tap; the
-          // TMA zero-fills what falls outside the image, which is the padding.
-          if (CONV) tma_load_4d(sa, &tmA, &bars->full[s], chunk * kBlockK, tap % 3 - 1, h0 + tap / 3 - 1, img);
-          else      tma_load_2d(sa, &tmA, &bars->full[s], k_off, m_off);
-          fills++;
-        }
-        if (p.trace && ticket < p.trace_capacity) p.trace[8ull * ticket + 5] = static_cast<unsigned long long>(wait_empty);
-      }
-      if (!ok) {
-        // Abort path: wait (bounded) for every copy still in flight before the
-        // block's shared memory goes away.
-        bars->abort = 1u;
-        const uint32_t live = fills < static_cast<uint32_t>(C::kStages) ? fills : static_cast<uint32_t>(C::kStages);
-        for (uint32_t j = 0; j < live; j++) {
-          const uint32_t f = fills - 1u - j;
-          const uint32_t s = f % C::kStages, ph = (f / C::kStages) & 1u;
-          const uint64_t t0 = cusync::globalTimerNs();
-          while (!mbar_try_wait(&bars->full[s], ph)) {
-            if (cusync::globalTimerNs() - t0 > 1000000000ull) break;
-          }
-        }
-      }
-    }
-  } else if (warp == 1) {
-    // =====================================================================
-    // MMA issuer
-    // =====================================================================
-    if (lane == 0) {
-      // Dual-B tiles sit back to back in the ring (second operand right after the first, same chunking), so
-      // while both fit one instruction they are multiplied as a single 2*BN-wide B: accumulator columns
-      // [0, BN) are A*B, [BN, 2BN) are A*B2.
-      constexpr bool kFusedDual = DUAL && 2 * BN <= 256;
-      const uint32_t idesc = make_idesc(kFusedDual ? 2 * BN : BN, !p.b_kmajor);
-      const uint32_t b_lbo = p.b_lbo, b_sbo = p.b_sbo, b_kstep = p.b_kstep;
-      uint32_t drains = 0, sched_it = 0, acc_it = 0;
-      bool ok = true;
-      bool issued = false;
-      while (ok) {
-        const uint32_t slot = sched_it % kSchedSlots, sph = (sched_it / kSchedSlots) & 1u;
-        if (!mbar_wait(&bars->sched_full[slot], sph, ctx)) { ok = false; break; }
-        const int valid = bars->sched_tile[slot][2];
-        const uint32_t ticket = static_cast<uint32_t>(bars->sched_tile[slot][3]);
-        const int slice = bars->sched_tile[slot][4];
-        mbar_arrive(&bars->sched_empty[slot]);
-        sched_it++;
-        if (!valid) break;
-        const uint32_t acc = acc_it & 1u, aph = (acc_it >> 1) & 1u;
-        const long long t_tile0 = p.trace ? clock64() : 0;
-        if (!mbar_wait(&bars->tmem_empty[acc], aph ^ 1u, ctx)) { ok = false; break; }
-        tc_fence_after();
-        const long long t_acc = p.trace ? clock64() : 0;
-        long long wait_full = 0;
-        const uint32_t d_tmem = tmem_base + acc * C::kAccCols;
-        const int kb_first = slice * p.k_blocks_per_split;
-        const int kb_count = kb_first + p.k_blocks_per_split < p.num_k_blocks ? p.k_blocks_per_split
-                                                                             : p.num_k_blocks - kb_first;
-        for (int kb = 0; kb < kb_count; kb++) {
-          const uint32_t s = drains % C::kStages, ph = (drains / C::kStages) & 1u;
-          const long long c0 = p.trace ? clock64() : 0;
-          if (!mbar_wait(&bars->full[s], ph, ctx)) { ok = false; break; }
-          if (p.trace) wait_full += clock64() - c0;
-          tc_fence_after();
-          const uint32_t sa = smem_u32(ring + s * C::kStageBytes);
-          const uint32_t sb = sa + C::kABytes;
-#pragma unroll
-          for (int kk = 0; kk < kBlockK / kUmmaK; kk++) {
-            const uint64_t adesc = make_smem_desc(sa + kk * 32, 16u, 1024u);
-            const uint64_t bdesc = make_smem_desc(sb + kk * b_kstep, b_lbo, b_sbo);
-            const uint32_t accumulate = (kb > 0 || kk > 0) ? 1u : 0u;
-            umma_f16(d_tmem, adesc, bdesc, idesc, accumulate);
-            if (DUAL && !kFusedDual) {
-              const uint64_t b2desc = make_smem_desc(sb + C::kBBytes + kk * b_kstep, b_lbo, b_sbo);
-              umma_f16(d_tmem + BN, adesc, b2desc, idesc, accumulate);
-            }
-          }
-          umma_commit(&bars->empty[s]);   // frees the ring slot when these MMAs retire
-          issued = true;
-          drains++;
-        }
-        if (!ok) break;
-        umma_commit(&bars->tmem_full[acc]);
-        if (p.trace && ticket < p.trace_capacity) {
-          p.trace[8ull * ticket + 4] = static_cast<unsigned long long>(wait_full);
-          p.trace[8ull * ticket + 6] = static_cast<unsigned long long>(clock64() - t_tile0);
-          p.trace[8ull * ticket + 7] = static_cast<unsigned long long>(t_acc - t_tile0);
-        }
-        acc_it++;
-      }
-      if (!ok && issued) {
-        // Let outstanding MMAs retire before tensor memory is released.
-        umma_commit(&bars->drain);
-        const uint64_t t0 = cusync::globalTimerNs();
-        while (!mbar_try_wait(&bars->drain, 0u)) {
-          if (cusync::globalTimerNs() - t0 > 1000000000ull) break;
-        }
-      }
-    }
-  } else if (warp >= kEpilogueWarp0) {
-    // =====================================================================
-    // Epilogue
-    // =====================================================================
-    const int ew = warp - kEpilogueWarp0;
-    const int quarter = ew & 3;                        // == warp % 4: the TMEM lanes this warp may read
-    const int half = ew >> 2;                          // which 64-column chunks of the tile it takes
-    uint8_t* buf = staging + ew * (32 * 128);
-    uint32_t sched_it = 0, acc_it = 0, post_it = 0;
-    bool ok = true;
-    while (ok) {
-      const uint32_t slot = sched_it % kSchedSlots, sph = (sched_it / kSchedSlots) & 1u;
-      if (!mbar_wait(&bars->sched_full[slot], sph, ctx)) { ok = false; break; }
-      const int tile_n = bars->sched_tile[slot][0];
-      const int tile_m = bars->sched_tile[slot][1];
-      const int valid = bars->sched_tile[slot][2];
-      const uint32_t ticket = static_cast<uint32_t>(bars->sched_tile[slot][3]);
-      const unsigned long long t_draw = p.trace ? bars->sched_time[slot] : 0ull;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->sched_empty[slot]);
-      sched_it++;
-      if (!valid) break;
-      const uint32_t acc = acc_it & 1u, aph = (acc_it >> 1) & 1u;
-      if (!mbar_wait(&bars->tmem_full[acc], aph, ctx)) { ok = false; break; }
-      tc_fence_after();
-      const unsigned long long t_mma_done = p.trace ? cusync::globalTimerNs() : 0ull;
-      const int n_off = tile_n * BN, m_off = CONV ? tile_m * p.conv_rows * p.conv_w : tile_m * kBlockM;
-      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * C::kAccCols;
-
-      if (CONV) {
-        // One output pixel per lane: its BN channels are contiguous in NHWC, so each lane stores its own
-        // 128-byte pieces directly.  Rows past conv_rows * conv_w are padding of the 128-row MMA.
-        const int row = quarter * 32 + lane;
-        const bool row_in = row < p.conv_rows * p.conv_w;
-#pragma unroll 1
-        for (int c = half; c < BN / kStoreCols; c += 2) {
-          uint32_t v[64];
-          tmem_ld_32x32b_x32(t_row + c * 64, v);
-          tmem_ld_32x32b_x32(t_row + c * 64 + 32, v + 32);
-          tmem_ld_wait();
-          if (row_in) {
-            __half* dst = static_cast<__half*>(p.d) + static_cast<size_t>(m_off + row) * p.ldd + n_off + c * 64;
-#pragma unroll
-            for (int q = 0; q < 8; q++) {
-              uint32_t w[4];
-#pragma unroll
-              for (int e = 0; e < 4; e++) {
-                float x0 = __uint_as_float(v[8 * q + 2 * e]), x1 = __uint_as_float(v[8 * q + 2 * e + 1]);
-                if (p.epilogue == CUSYNC_EPILOGUE_RELU) { x0 = fmaxf(x0, 0.0f); x1 = fmaxf(x1, 0.0f); }
-                w[e] = pack_half2(x0, x1);
-              }
-              *reinterpret_cast<uint4*>(dst + 8 * q) = make_uint4(w[0], w[1], w[2], w[3]);
-            }
-          }
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->tmem_empty[acc]);
-        acc_it++;
-        if (p.is_producer) {
-          // every lane's stores are ordered before lane 0's fence by the warp barrier above
-          if (lane == 0) {
-            __threadfence();
-            // Epilogue warps run at their own pace: one that is a tile ahead must not arrive on `post`
-            // while the previous tile's phase is still open (its arrival would close that phase early).
-            if (!mbar_wait(&bars->post, (post_it & 1u) ^ 1u, ctx)) ok = false;
-            mbar_arrive(&bars->post);
-            if (ew == 0) {
-              if (!mbar_wait(&bars->post, post_it & 1u, ctx)) ok = false;
-              else {
-                const uint32_t idx = cusync::eval::tileIndex(st.out_policy, static_cast<uint32_t>(m_off),
-                                                             static_cast<uint32_t>(n_off), st.grid.x, st.grid.y);
-                const uint32_t pv = cusync::eval::postValue(st.out_policy);
-                __threadfence();
-                if (st.opts & CUSYNC_OPT_NO_ATOMIC_ADD) cusync::storeRelease(st.sems_post + idx, pv * st.iter);
-                else                                    cusync::addRelease(st.sems_post + idx, pv);
-              }
-            }
-          }
-          post_it++;
-          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-        }
-        if (p.trace && ew == 0 && lane == 0 && ticket < p.trace_capacity) {
-          uint32_t smid;
-          asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-          unsigned long long* rec = p.trace + 8ull * ticket;
-          rec[0] = t_draw; rec[1] = t_mma_done; rec[2] = cusync::globalTimerNs();
-          rec[3] = (static_cast<unsigned long long>(smid) << 32) | blockIdx.x;
-        }
-        continue;
-      }
-      if (!DUAL && p.split_k > 1) {
-        // Split-K: add this slice's part; the block that brings the last slice finalises and posts.
-        bool last = false;
-        ok = splitk_epilogue<BN>(p, &tmWS, buf, bars, ctx, t_row, n_off, m_off, quarter, half, ew, lane, post_it & 1u,
-                                 post_it & 1u, static_cast<uint32_t>(p.split_k), &bars->tmem_empty[acc], 0u,
-                                 static_cast<__half*>(p.d), p.ldd, &last);
-        acc_it++;
-        if (ew == 0 && lane == 0) {
-          if (!mbar_wait(&bars->splitk_done, post_it & 1u, ctx)) ok = false;
-          else if (last && p.is_producer) {
-            const uint32_t idx = cusync::eval::tileIndex(st.out_policy, static_cast<uint32_t>(m_off),
-                                                         static_cast<uint32_t>(n_off), st.grid.x, st.grid.y);
-            const uint32_t pv = cusync::eval::postValue(st.out_policy);
-            __threadfence();
-            if (st.opts & CUSYNC_OPT_NO_ATOMIC_ADD) cusync::storeRelease(st.sems_post + idx, pv * st.iter);
-            else                                    cusync::addRelease(st.sems_post + idx, pv);
-          }
-        }
-        post_it++;
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-        continue;
-      }
-      epilogue_store_rows<BN, DUAL>(p, &tmD, buf, t_row, n_off, m_off + quarter * 32, half, lane);
-      // Accumulator buffer is free for the MMA warp again.
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->tmem_empty[acc]);
-      acc_it++;
-
-      if (p.is_producer) {
-        // Publish the tile only after every store of it has fully completed:
-        // each warp's issuing lane waits for its own bulk stores, then arrives
-        // on `post`; the first epilogue warp's lane collects the four arrivals
-        // (bounded) and performs the single release.
-        if (lane == 0) {
-          tma_store_wait_all();
-          __threadfence();
-          // Epilogue warps run at their own pace: one that is a tile ahead must not arrive on `post`
-          // while the previous tile's phase is still open (its arrival would close that phase early).
-          if (!mbar_wait(&bars->post, (post_it & 1u) ^ 1u, ctx)) ok = false;
-          mbar_arrive(&bars->post);
-          if (ew == 0) {
-            if (!mbar_wait(&bars->post, post_it & 1u, ctx)) ok = false;
-            else {
-              const uint32_t idx = cusync::eval::tileIndex(st.out_policy, static_cast<uint32_t>(m_off),
-                                                           static_cast<uint32_t>(n_off), st.grid.x, st.grid.y);
-              const uint32_t pv = cusync::eval::postValue(st.out_policy);
-              __threadfence();
-              if (st.opts & CUSYNC_OPT_NO_ATOMIC_ADD) cusync::storeRelease(st.sems_post + idx, pv * st.iter);
-              else                                    cusync::addRelease(st.sems_post + idx, pv);
-            }
-          }
-        }
-        post_it++;
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      }
-      if (p.trace && ew == 0 && lane == 0 && ticket < p.trace_capacity) {
-        uint32_t smid;
-        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-        unsigned long long* rec = p.trace + 8ull * ticket;
-        rec[0] = t_draw; rec[1] = t_mma_done; rec[2] = cusync::globalTimerNs();
-        rec[3] = (static_cast<unsigned long long>(smid) << 32) | blockIdx.x;
-      }
-    }
-    if (lane == 0) tma_store_wait_all();
-  }
-
-  // Teardown (normal and abort paths alike).
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 2) {
-    tc_fence_after();
-    tmem_dealloc(tmem_base, C::kTmemCols);
-  }
-}
-
-
-// ---------------------------------------------------------------------------
-// 3x3 convolution, 64 -> 64 channels: the slab kernel
-// ---------------------------------------------------------------------------
-// The implicit-GEMM path above fetches one shifted copy of the input rows per filter tap (nine TMA boxes and
-// nine barrier round trips per tile) and re-reads the 3x3 filter for every tile.  For the layer the conv chain
-// is measured on (C = K = 64, src/ml-bench/volta_conv2d/ resnet sizes) both fit on chip:
-//
-//   * the whole filter (9 taps x 64 x 64 fp16 = 72 KB) is loaded ONCE per CTA and stays in shared memory;
-//   * per tile ONE 4-D TMA box brings the input slab: conv_rows + 2 image rows of W + 2 pixels (the halo is the
-//     box's out-of-range part, zero-filled = the padding), 64 channels = one 128-byte swizzle row per pixel;
-//   * the MMA's M index runs over the slab's pixels in memory order (padded width W + 2), so tap (r, s) is the
-//     same slab read from (r * (W + 2) + s) pixel rows further on: 36 tcgen05.mma per tile, back to back, with a
-//     shared-memory descriptor whose start address moves by whole 128-byte rows (the 128-byte swizzle is a
-//     function of the shared-memory address, so a start that is not a multiple of 8 rows needs nothing else;
-//     the descriptor's base-offset field stays 0 - setting it to the start row's phase gave wrong products).
-//     M rows that fall on the two padding columns of a slab row, or past conv_rows rows, are computed and dropped.
-//
-// Tile shape, stage grid, semaphores and policies are those of the general path: one tile = conv_rows whole image
-// rows, waits on its own and the two neighbouring producer tiles, posts once.
-//
-// The scheduler keeps three tickets in flight: the ticket draw, the schedule look-up and the semaphore probes of
-// a tile are three dependent memory round trips (about 2 us), as long as a whole tile's math here, so each is
-// issued one tile ahead of the next.  Every CTA therefore draws exactly three tickets past the end.
-constexpr int kSlabStages = 4;
-constexpr int kSlabBytes = 256 * 128;          // room for 256 pixel rows: the last tap reads up to row 2(W+2)+2+127
-constexpr int kSlabFilterBytes = 9 * 64 * 128; // nine taps of [64 n][64 c]
-constexpr int kSlabBN = 64;
-constexpr uint32_t kSlabSmemBytes = 1024 + kSlabStages * kSlabBytes + kSlabFilterBytes + 1024;
-constexpr int kSlabTicketsAhead = 3;
-constexpr int kSlabIssuers = 2;                // threads that issue MMAs, alternating tiles
-
-__global__ void __launch_bounds__(kThreads, 1)
-cusync_conv3x3_slab_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmF,
-                           const GemmParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* slabs = smem;
-  uint8_t* filt = smem + kSlabStages * kSlabBytes;
-  Barriers* bars = reinterpret_cast<Barriers*>(filt + kSlabFilterBytes);
-
-  const int warp = threadIdx.x >> 5;
-  const int lane = threadIdx.x & 31;
-  const cusync_stage_view_t& st = p.stage;
-  WaitCtx ctx{&bars->abort, st.status, 2 * st.timeout_ns + 1000000000ull};
-  const int wp = p.conv_w + 2;                         // padded slab width
-  uint64_t* filt_full = &bars->splitk_counted;         // (split-K is not used by this kernel)
-  // Four accumulators, one per slab stage: tile j of this CTA uses slab j % 4 and accumulator j % 4, and is
-  // issued by MMA thread j % 2 (see below).  Their barriers live in the upper half of the ring's arrays.
-  uint64_t* acc_full = &bars->full[kSlabStages];
-  uint64_t* acc_empty = &bars->empty[kSlabStages];
-
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < kSlabStages; i++) { mbar_init(&bars->full[i], 1); mbar_init(&bars->empty[i], 1); }
-    for (int i = 0; i < kSlabStages; i++) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], kEpilogueWarps); }
-    for (int i = 0; i < kSchedSlots; i++) { mbar_init(&bars->sched_full[i], 1); mbar_init(&bars->sched_empty[i], kSlabIssuers + kEpilogueWarps + 1); }
-    mbar_init(&bars->drain, 1);
-    mbar_init(&bars->splitk_done, 1);     // the second MMA thread's drain barrier
-    for (int i = 0; i < kSchedSlots; i++) mbar_init(&bars->post_slot[i], kEpilogueWarps);
-    mbar_init(filt_full, 1);
-    bars->abort = 0u;
-    fence_barrier_init();
-    fence_proxy_async_smem();
-    if (p.is_producer) {
-      if (blockIdx.x == 0) cusync::storeRelease(st.started, st.iter);
-      cusync::addRelease(st.started + 1, 1u);
-    }
-  }
-  if (warp == 0 && lane == 0) { prefetch_tensormap(&tmX); prefetch_tensormap(&tmF); }
-  if (warp == 2) {
-    tmem_alloc(&bars->tmem_base, kSlabStages * kSlabBN);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = bars->tmem_base;
-
-  if (warp == 0) {
-    // =====================================================================
-    // Scheduler + TMA loader
-    // =====================================================================
-    if (lane == 0) {
-      // The filter: nine boxes {64 c, 64 n}, tap t at K offset t * C of the [k_out][r][s][c] matrix.
-      mbar_expect_tx(filt_full, kSlabFilterBytes);
-      for (int tap = 0; tap < 9; tap++) tma_load_2d(filt + tap * (64 * 128), &tmF, filt_full, tap * p.conv_c, 0);
-
-      const uint32_t num_tiles = static_cast<uint32_t>(p.num_tiles);
-      const uint32_t total_draws = num_tiles + kSlabTicketsAhead * gridDim.x;
-      const uint32_t wait_target = p.is_consumer ? st.iter * cusync::eval::waitValue(st.in_policy) : 0u;
-      const int span = p.conv_rows * p.conv_w;           // output pixels per tile
-      uint32_t fills = 0, sched_it = 0;
-      bool ok = true;
-
-      // Pipeline registers: tickets of the tiles i, i+1, i+2; schedule entries of i and i+1; probes of i.
-      uint32_t tk0 = atomicAdd(st.tile_counter, 1u);
-      uint32_t tk1 = atomicAdd(st.tile_counter, 1u);
-      uint32_t tk2 = atomicAdd(st.tile_counter, 1u);
-      uint32_t y0 = tk0 < num_tiles ? st.tile_order[tk0].y : 0u;
-      uint32_t y1 = tk1 < num_tiles ? st.tile_order[tk1].y : 0u;
-      uint32_t pr0 = 0, pr1 = 0, pr2 = 0;                // semaphore values seen for tile i: own, above, below
-      auto sem_indices = [&](uint32_t ty, uint32_t* own, uint32_t* up, uint32_t* dn) {
-        const int tin = static_cast<int>(ty) % p.conv_tiles_per_image;
-        const uint32_t m_off = ty * static_cast<uint32_t>(span);
-        *own = cusync::eval::tileIndex(st.in_policy, m_off, 0u, st.prod_grid.x, st.prod_grid.y);
-        *up = tin > 0 ? cusync::eval::tileIndex(st.in_policy, m_off - span, 0u, st.prod_grid.x, st.prod_grid.y) : *own;
-        *dn = tin + 1 < p.conv_tiles_per_image
-                  ? cusync::eval::tileIndex(st.in_policy, m_off + span, 0u, st.prod_grid.x, st.prod_grid.y) : *own;
-      };
-      if (p.is_consumer && tk0 < num_tiles) {
-        uint32_t a, b, c;
-        sem_indices(y0, &a, &b, &c);
-        pr0 = cusync::loadRelaxed(st.sems_wait + a); pr1 = cusync::loadRelaxed(st.sems_wait + b);
-        pr2 = cusync::loadRelaxed(st.sems_wait + c);
-      }
-      while (ok) {
-        const bool valid = tk0 < num_tiles;
-        const long long lc0 = p.trace ? clock64() : 0;
-        // Tile i's dependencies first: the fence that makes its (earlier) probes acquiring would otherwise
-        // also wait for the loads issued below for later tiles.
-        bool waited_ok = true;
-        if (valid && p.is_consumer) {
-          if (pr0 < wait_target || pr1 < wait_target || pr2 < wait_target) {
-            // not finished when probed: wait (bounded) for the tile itself and its two halo neighbours
-            uint32_t idx[3];
-            sem_indices(y0, &idx[0], &idx[1], &idx[2]);
-            for (int j = 0; j < 3 && waited_ok; j++) {
-              uint32_t seen = 0;
-              if (!cusync::spinUntilAtLeast(st.sems_wait + idx[j], wait_target, st.timeout_ns, &seen)) {
-                bars->abort = 1u;
-                cusync::recordTimeout(st.status, 1u, y0 * static_cast<uint32_t>(span), 0u, static_cast<uint32_t>(j), idx[j],
-                                      seen, wait_target);
-                waited_ok = false;
-              }
-            }
-          } else {
-            cusync::fenceAcqRel();  // makes the relaxed probes acquiring
-          }
-          fence_proxy_async();     // acquire (generic proxy) before the TMA read (async proxy)
-        }
-        const long long lc1 = p.trace ? clock64() : 0;
-        uint32_t tk3 = 0, y2 = 0, pn0 = 0, pn1 = 0, pn2 = 0;
-        if (valid) {
-          // issue, for later tiles: the draw of i+3, the schedule entry of i+2, the probes of i+1
-          tk3 = atomicAdd(st.tile_counter, 1u);
-          y2 = tk2 < num_tiles ? st.tile_order[tk2].y : 0u;
-          if (p.is_consumer && tk1 < num_tiles) {
-            uint32_t a, b, c;
-            sem_indices(y1, &a, &b, &c);
-            pn0 = cusync::loadRelaxed(st.sems_wait + a); pn1 = cusync::loadRelaxed(st.sems_wait + b);
-            pn2 = cusync::loadRelaxed(st.sems_wait + c);
-          }
-        } else {
-          // the three tickets in hand are this block's draws past the end; the launch's last draw re-arms
-          // the counter (the reference resets on the last tile, cusync_device_defs.h:87-90)
-          if (tk0 == total_draws - 1u || tk1 == total_draws - 1u || tk2 == total_draws - 1u)
-            atomicExch(st.tile_counter, 0u);
-        }
-        const long long lc2 = p.trace ? clock64() : 0;
-        const uint32_t slot = sched_it % kSchedSlots, sph = (sched_it / kSchedSlots) & 1u;
-        if (!mbar_wait(&bars->sched_empty[slot], sph ^ 1u, ctx)) { ok = false; break; }
-        bars->sched_tile[slot][0] = 0;
-        bars->sched_tile[slot][1] = static_cast<int32_t>(y0);
-        bars->sched_tile[slot][2] = valid ? 1 : 0;
-        bars->sched_tile[slot][3] = static_cast<int32_t>(tk0);
-        if (p.trace) bars->sched_time[slot] = cusync::globalTimerNs();
-        mbar_arrive(&bars->sched_full[slot]);
-        sched_it++;
-        if (!valid) break;
-        if (!waited_ok) { ok = false; break; }
-
-        const int img = static_cast<int>(y0) / p.conv_tiles_per_image;
-        const int h0 = (static_cast<int>(y0) % p.conv_tiles_per_image) * p.conv_rows;
-        const long long lc3 = p.trace ? clock64() : 0;
-        const uint32_t s = fills % kSlabStages, ph = (fills / kSlabStages) & 1u;
-        if (!mbar_wait(&bars->empty[s], ph ^ 1u, ctx)) { ok = false; break; }
-        const long long lc4 = p.trace ? clock64() : 0;
-        const uint32_t slab_bytes = static_cast<uint32_t>((p.conv_rows + 2) * wp * 128);
-        mbar_expect_tx(&bars->full[s], slab_bytes);
-        // box {64 channels, W + 2 pixels, conv_rows + 2 rows, 1 image} from pixel (-1, h0 - 1)
-        tma_load_4d(slabs + s * kSlabBytes, &tmX, &bars->full[s], 0, -1, h0 - 1, img);
-        fills++;
-        if (p.trace && tk0 < p.trace_capacity) {
-          // loader's cycles for this tile: dependencies | prefetch issue | schedule slot | free slab | TMA issue
-          auto cap = [](long long v) { return static_cast<unsigned long long>(v < 0 ? 0 : (v > 4095 ? 4095 : v)); };
-          p.trace[8ull * tk0 + 5] = cap(lc1 - lc0) | (cap(lc2 - lc1) << 12) | (cap(lc3 - lc2) << 24) |
-                                    (cap(lc4 - lc3) << 36) | (cap(clock64() - lc4) << 48);
-        }
-        tk0 = tk1; tk1 = tk2; tk2 = tk3; y0 = y1; y1 = y2; pr0 = pn0; pr1 = pn1; pr2 = pn2;
-      }
-      if (!ok) {
-        bars->abort = 1u;
-        // wait (bounded) for the copies in flight before the block's shared memory goes away
-        const uint32_t live = fills < static_cast<uint32_t>(kSlabStages) ? fills : static_cast<uint32_t>(kSlabStages);
-        for (uint32_t j = 0; j < live; j++) {
-          const uint32_t f = fills - 1u - j;
-          const uint32_t s = f % kSlabStages, ph = (f / kSlabStages) & 1u;
-          const uint64_t t0 = cusync::globalTimerNs();
-          while (!mbar_try_wait(&bars->full[s], ph)) {
-            if (cusync::globalTimerNs() - t0 > 1000000000ull) break;
-          }
-        }
-      }
-      // the filter copy must have landed too
-      {
-        const uint64_t t0 = cusync::globalTimerNs();
-        while (!mbar_try_wait(filt_full, 0u)) {
-          if (cusync::globalTimerNs() - t0 > 1000000000ull) break;
-        }
-      }
-    }
-  } else if (warp == 1 || warp == 3) {
-    // =====================================================================
-    // MMA issuers.  A 128 x 64 x 16 MMA keeps the tensor pipe busy for about a third of the time one thread
-    // needs to issue it, so two threads issue: warp 1 the CTA's even tiles, warp 3 the odd ones, each into
-    // its own accumulators.  Both walk the whole schedule ring to stay in step.
-    // =====================================================================
-    if (lane == 0) {
-      const uint32_t me = warp == 1 ? 0u : 1u;
-      const uint32_t idesc = make_idesc(kSlabBN, false);
-      uint32_t drains = 0, sched_it = 0;
-      bool ok = mbar_wait(filt_full, 0u, ctx);
-      bool issued = false;
-      const uint32_t filt_addr = smem_u32(filt);
-      while (ok) {
-        const uint32_t slot = sched_it % kSchedSlots, sph = (sched_it / kSchedSlots) & 1u;
-        if (!mbar_wait(&bars->sched_full[slot], sph, ctx)) { ok = false; break; }
-        const int valid = bars->sched_tile[slot][2];
-        const uint32_t ticket = static_cast<uint32_t>(bars->sched_tile[slot][3]);
-        mbar_arrive(&bars->sched_empty[slot]);
-        sched_it++;
-        if (!valid) break;
-        const uint32_t s = drains % kSlabStages, ph = (drains / kSlabStages) & 1u;   // slab and accumulator of tile j
-        const bool mine = (drains & 1u) == me;
-        if (!mine) { drains++; continue; }
-        const uint32_t acc = s;
-        const long long t_tile0 = p.trace ? clock64() : 0;
-        if (!mbar_wait(&acc_empty[acc], ph ^ 1u, ctx)) { ok = false; break; }
-        const long long t_acc = p.trace ? clock64() : 0;
-        if (!mbar_wait(&bars->full[s], ph, ctx)) { ok = false; break; }
-        const long long t_full = p.trace ? clock64() : 0;
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * kSlabBN;
-        const uint32_t slab_addr = smem_u32(slabs + s * kSlabBytes);
-#pragma unroll 1
-        for (int tap = 0; tap < 9; tap++) {
-          const uint32_t a_row = static_cast<uint32_t>((tap / 3) * wp + tap % 3);     // first pixel row of this tap
-          const uint32_t a_addr = slab_addr + a_row * 128u;
-          const uint32_t b_addr = filt_addr + static_cast<uint32_t>(tap) * (64u * 128u);
-#pragma unroll
-          for (int kk = 0; kk < kBlockK / kUmmaK; kk++) {
-            const uint64_t adesc = make_smem_desc(a_addr + kk * 32, 16u, 1024u);
-            const uint64_t bdesc = make_smem_desc(b_addr + kk * 32, 16u, 1024u);
-            umma_f16(d_tmem, adesc, bdesc, idesc, (tap > 0 || kk > 0) ? 1u : 0u);
-          }
-        }
-        umma_commit(&bars->empty[s]);
-        umma_commit(&acc_full[acc]);
-        issued = true;
-        drains++;
-        if (p.trace && ticket < p.trace_capacity) {
-          p.trace[8ull * ticket + 4] = static_cast<unsigned long long>(t_full - t_acc);
-          p.trace[8ull * ticket + 6] = static_cast<unsigned long long>(clock64() - t_tile0);
-          p.trace[8ull * ticket + 7] = static_cast<unsigned long long>(t_acc - t_tile0);
-        }
-      }
-      if (!ok && issued) {
-        uint64_t* drain = me ? &bars->splitk_done : &bars->drain;
-        umma_commit(drain);
-        const uint64_t t0 = cusync::globalTimerNs();
-        while (!mbar_try_wait(drain, 0u)) {
-          if (cusync::globalTimerNs() - t0 > 1000000000ull) break;
-        }
-      }
-    }
-  } else if (warp >= kEpilogueWarp0) {
-    // =====================================================================
-    // Epilogue: lane = one M row = one slab pixel; warp (quarter, half) takes 32 of its 64 channels
-    // =====================================================================
-    const int ew = warp - kEpilogueWarp0;
-    const int quarter = ew & 3;
-    const int half = ew >> 2;
-    uint32_t sched_it = 0, acc_it = 0, post_it = 0;
-    bool ok = true;
-    const int mrow = quarter * 32 + lane;
-    const int prow = mrow / wp, pcol = mrow % wp;       // image row within the tile, column
-    const bool px_in = prow < p.conv_rows && pcol < p.conv_w;
-    while (ok) {
-      const uint32_t slot = sched_it % kSchedSlots, sph = (sched_it / kSchedSlots) & 1u;
-      if (!mbar_wait(&bars->sched_full[slot], sph, ctx)) { ok = false; break; }
-      const int tile_m = bars->sched_tile[slot][1];
-      const int valid = bars->sched_tile[slot][2];
-      const uint32_t ticket = static_cast<uint32_t>(bars->sched_tile[slot][3]);
-      const unsigned long long t_draw = p.trace ? bars->sched_time[slot] : 0ull;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->sched_empty[slot]);
-      sched_it++;
-      if (!valid) break;
-      const uint32_t acc = acc_it % kSlabStages, aph = (acc_it / kSlabStages) & 1u;
-      if (!mbar_wait(&acc_full[acc], aph, ctx)) { ok = false; break; }
-      tc_fence_after();
-      const unsigned long long t_mma_done = p.trace ? cusync::globalTimerNs() : 0ull;
-      const int m_off = tile_m * p.conv_rows * p.conv_w;      // first output pixel of the tile
-      uint32_t v[32];
-      tmem_ld_32x32b_x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kSlabBN + half * 32, v);
-      tmem_ld_wait();
-      if (px_in) {
-        __half* dst = static_cast<__half*>(p.d) + static_cast<size_t>(m_off + prow * p.conv_w + pcol) * p.ldd + half * 32;
-#pragma unroll
-        for (int q = 0; q < 4; q++) {
-          uint32_t w[4];
-#pragma unroll
-          for (int e = 0; e < 4; e++) {
-            float x0 = __uint_as_float(v[8 * q + 2 * e]), x1 = __uint_as_float(v[8 * q + 2 * e + 1]);
-            if (p.epilogue == CUSYNC_EPILOGUE_RELU) { x0 = fmaxf(x0, 0.0f); x1 = fmaxf(x1, 0.0f); }
-            w[e] = pack_half2(x0, x1);
-          }
-          *reinterpret_cast<uint4*>(dst + 8 * q) = make_uint4(w[0], w[1], w[2], w[3]);
-        }
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[acc]);
-      acc_it++;
-      if (p.is_producer) {
-        // Hand the tile to the posting thread (warp 2) and go on: the warp barrier above orders every lane's
-        // stores before lane 0's arrival, the arrival (release) before the poster's wait (acquire), and the
-        // poster's fence + release publish them device-wide.  The barrier belongs to the tile's schedule
-        // slot, which the poster gives back only after it has posted: no warp can be a phase ahead on it.
-        if (lane == 0) mbar_arrive(&bars->post_slot[slot]);
-      }
-      if (p.trace && ew == 0 && lane == 0 && ticket < p.trace_capacity) {
-        uint32_t smid;
-        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-        unsigned long long* rec = p.trace + 8ull * ticket;
-        rec[0] = t_draw; rec[1] = t_mma_done; rec[2] = cusync::globalTimerNs();
-        rec[3] = (static_cast<unsigned long long>(smid) << 32) | blockIdx.x;
-      }
-    }
-  }
-
-  else if (warp == 2 && lane == 0) {
-    // =====================================================================
-    // Poster: publishes each finished tile (CuStage::post, cusync_device_defs.h:55-72) so that the epilogue
-    // warps do not sit out the device-wide fence.  Walks the schedule ring like everybody else.
-    // =====================================================================
-    uint32_t sched_it = 0;
-    bool ok = true;
-    while (ok) {
-      const uint32_t slot = sched_it % kSchedSlots, sph = (sched_it / kSchedSlots) & 1u;
-      if (!mbar_wait(&bars->sched_full[slot], sph, ctx)) { ok = false; break; }
-      const int tile_m = bars->sched_tile[slot][1];
-      const int valid = bars->sched_tile[slot][2];
-      sched_it++;
-      if (!valid || !p.is_producer) {
-        mbar_arrive(&bars->sched_empty[slot]);
-        if (!valid) break;
-        continue;
-      }
-      {
-        if (!mbar_wait(&bars->post_slot[slot], sph, ctx)) { ok = false; break; }
-        const uint32_t m_off = static_cast<uint32_t>(tile_m * p.conv_rows * p.conv_w);
-        const uint32_t idx = cusync::eval::tileIndex(st.out_policy, m_off, 0u, st.grid.x, st.grid.y);
-        const uint32_t pv = cusync::eval::postValue(st.out_policy);
-        cusync::fenceAcqRel();
-        if (st.opts & CUSYNC_OPT_NO_ATOMIC_ADD) cusync::storeRelease(st.sems_post + idx, pv * st.iter);
-        else                                    cusync::addRelease(st.sems_post + idx, pv);
-        mbar_arrive(&bars->sched_empty[slot]);      // only now may the slot (and its post barrier) be reused
-      }
-    }
-  }
-
-  // Teardown (normal and abort paths alike).
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 2) {
-    tc_fence_after();
-    tmem_dealloc(tmem_base, kSlabStages * kSlabBN);
-  }
-}
-
-
-// ---------------------------------------------------------------------------
-// CTA-pair variant: tcgen05.mma.cta_group::2
-// ---------------------------------------------------------------------------
-// Two CTAs of a cluster (the two SMs of a TPC) compute one 256 x 256 output tile.  CTA r owns rows
-// [r*128, r*128+128) of it: it loads its own A rows and HALF of the B tile (128 of the 256 columns),
-// and holds its 128 x 256 accumulator in its own tensor memory.  The leader (rank 0) issues one
-// M=256 MMA per K step that reads A and the B halves from both CTAs' shared memory.  Per CTA and
-// K-block that is 32 KB from L2 instead of 48 KB, and the ring holds six K-blocks instead of four.
-// No multicast loads: the only cluster-wide traffic is mbarrier signalling (TMA completion on the
-// leader's barrier, tcgen05.commit to both CTAs, remote arrives) and the scheduler's tile broadcast.
-// Semaphores stay per 128-row tile: each CTA waits for, and posts, its own rows.
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
-  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait on a LOCAL barrier that a peer CTA may have signalled.
-__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, const WaitCtx& ctx) {
-  if (mbar_try_wait_cluster(bar, parity)) return true;
-  const uint64_t t0 = cusync::globalTimerNs();
-  uint32_t polls = 0;
-  while (true) {
-    if (mbar_try_wait_cluster(bar, parity)) return true;
-    if ((++polls & 31u) == 0u) {
-      if (*ctx.abort) return false;
-      if (cusync::globalTimerNs() - t0 > ctx.timeout_ns) {
-        *ctx.abort = 1u;
-        cusync::recordTimeout(ctx.status, 2u, blockIdx.x, threadIdx.x, parity, smem_u32(bar), 0u, 0u);
-        return false;
-      }
-    }
-  }
-}
-// TMA load whose completion may be signalled on the peer CTA's barrier (`bar_cluster_addr` is a
-// shared::cluster address); the data lands in this CTA's shared memory.
-__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int c0,
-                                                 int c1) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
-      : "memory");
-}
-__device__ __forceinline__ void tma_load_3d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int c0,
-                                                 int c1, int c2) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_alloc_pair(uint32_t* dst_smem, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)),
-               "r"(ncols)
-               : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish_pair() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                              uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// Arrive on the barrier at this shared-memory offset in BOTH CTAs of the pair when the MMAs retire.
-__device__ __forceinline__ void umma_commit_pair_both(uint64_t* bar) {
-  const uint16_t mask = 3;
-  asm volatile(
-      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-      ::"r"(smem_u32(bar)), "h"(mask)
-      : "memory");
-}
-__device__ __forceinline__ void umma_commit_pair_local(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
-}
-
-// K depth of one ring stage of the pair kernel: two 64-element swizzle chunks.  A barrier wait, a commit and
-// each MMA issue cost the issuing thread of the order of a hundred cycles whatever the MMA's size, so a stage
-// carries eight MMAs (and two TMA boxes) per wait/commit instead of four to stay under the tensor time.
-constexpr int kPairBlockK = 128;
-constexpr int kPairChunkBytes = kBlockM * 128;     // one 64-deep chunk of 128 rows
-struct PairCfg {
-  static constexpr int kABytes = kBlockM * kPairBlockK * 2;            // this CTA's 128 A rows
-  static constexpr int kBHalfBytes = (kPairBN / 2) * kPairBlockK * 2;  // this CTA's half of the B tile
-  static constexpr int kStageBytes = kABytes + kBHalfBytes;
-  static constexpr int kStagingBytes = kEpilogueWarps * 32 * 128;
-  static constexpr int kBarrierBytes = 1024;
-  static constexpr int kStages = ((int)kSmemLimit - 1024 - kStagingBytes - kBarrierBytes) / kStageBytes;
-  static constexpr int kAccCols = kPairBN;
-  static constexpr int kTmemCols = 2 * kAccCols;
-  static constexpr uint32_t kSmemBytes = 1024 + kStages * kStageBytes + kStagingBytes + kBarrierBytes;
-  static_assert(kStages >= 3 && kStages <= 8, "ring depth out of range");
-  static_assert(kSmemBytes <= kSmemLimit, "shared memory over budget");
-};
-
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
-cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                        const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmWS,
-                        const GemmParams p) {
-  using C = PairCfg;
-  constexpr int BN = kPairBN;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* ring = smem;
-  uint8_t* staging = smem + C::kStages * C::kStageBytes;
-  Barriers* bars = reinterpret_cast<Barriers*>(staging + C::kStagingBytes);
-
-  const int warp = threadIdx.x >> 5;
-  const int lane = threadIdx.x & 31;
-  const uint32_t rank = cluster_ctarank();          // 0 = leader: draws tickets, issues the MMAs
-  const bool leader = rank == 0;
-  const cusync_stage_view_t& st = p.stage;
-  WaitCtx ctx{&bars->abort, st.status, 2 * st.timeout_ns + 1000000000ull};
-
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < C::kStages; i++) { mbar_init(&bars->full[i], 1); mbar_init(&bars->empty[i], 1); }
-    for (int i = 0; i < 2; i++) {
-      mbar_init(&bars->tmem_full[i], 1);
-      mbar_init(&bars->tmem_empty[i], 2 * kEpilogueWarps);           // leader's: epilogue warps of both CTAs
-    }
-    for (int i = 0; i < kSchedSlots; i++) {
-      mbar_init(&bars->sched_full[i], 1);
-      mbar_init(&bars->sched_empty[i], 2 * (1 + kEpilogueWarps));    // leader's: MMA + peer loader + all epilogue warps
-    }
-    mbar_init(&bars->drain, 1);
-    mbar_init(&bars->post, kEpilogueWarps);
-    mbar_init(&bars->splitk_counted, 1);
-    mbar_init(&bars->splitk_done, kEpilogueWarps);
-    bars->abort = 0u;
-    fence_barrier_init();
-    fence_proxy_async_smem();
-    if (p.is_producer) {
-      if (blockIdx.x == 0) cusync::storeRelease(st.started, st.iter);
-      cusync::addRelease(st.started + 1, 1u);
-    }
-  }
-  if (warp == 0 && lane == 0) { prefetch_tensormap(&tmA); prefetch_tensormap(&tmB); prefetch_tensormap(&tmD); }
-  if (warp == 2) {
-    tmem_alloc_pair(&bars->tmem_base, C::kTmemCols);
-    tmem_relinquish_pair();
-  }
-  tc_fence_before();
-  __syncthreads();
-  cluster_sync_all();            // the peer's barriers are initialised before anything signals them
-  tc_fence_after();
-  const uint32_t tmem_base = bars->tmem_base;
-
-  // Cluster addresses of the leader's barriers that the peer signals.
-  const uint32_t leader_full0 = map_to_cta(smem_u32(&bars->full[0]), 0);
-  const uint32_t leader_tmem_empty0 = map_to_cta(smem_u32(&bars->tmem_empty[0]), 0);
-  const uint32_t leader_sched_empty0 = map_to_cta(smem_u32(&bars->sched_empty[0]), 0);
-
-  if (warp == 0) {
-    // =====================================================================
-    // Scheduler (leader) + TMA loader (both CTAs)
-    // =====================================================================
-    if (lane == 0) {
-      uint32_t fills = 0, sched_it = 0;
-      bool ok = true;
-      const uint32_t total_draws = static_cast<uint32_t>(p.num_pairs) + gridDim.x / 2;
-      const uint32_t wait_target = p.is_consumer ? st.iter * cusync::eval::waitValue(st.in_policy) : 0u;
-      uint32_t sync_stride = 0;
-      if (p.is_consumer) {
-        const int kind = st.in_policy.kind;
-        if (kind == CUSYNC_POLICY_TILESYNC || kind == CUSYNC_POLICY_STRIDEDTILESYNC) sync_stride = st.in_policy.tile_n;
-        else if (kind == CUSYNC_POLICY_CONV2DTILESYNC) sync_stride = st.in_policy.tile_n * st.in_policy.p0;
-      }
-      const uint32_t peer_sched_tile0 = map_to_cta(smem_u32(&bars->sched_tile[0][0]), 1);
-      const uint32_t peer_sched_time0 = map_to_cta(smem_u32(&bars->sched_time[0]), 1);
-      const uint32_t peer_sched_full0 = map_to_cta(smem_u32(&bars->sched_full[0]), 1);
-      while (ok) {
-        const uint32_t slot = sched_it % kSchedSlots, sph = (sched_it / kSchedSlots) & 1u;
-        int32_t tn, tpm, valid, tz_slice = 0, nslices = 1;
-        if (leader) {
-          if (!mbar_wait_cluster(&bars->sched_empty[slot], sph ^ 1u, ctx)) { ok = false; break; }
-          const uint32_t ticket = atomicAdd(st.tile_counter, 1u);
-          if (ticket == total_draws - 1u) atomicExch(st.tile_counter, 0u);   // last draw of the launch
-          valid = ticket < static_cast<uint32_t>(p.num_pairs) ? 1 : 0;
-          PairUnit t = {0, 0, 1u << 16, 0};
-          if (valid) t = p.pair_order[ticket];
-          tn = static_cast<int32_t>(t.x); tpm = static_cast<int32_t>(t.y);
-          tz_slice = static_cast<int32_t>(t.slice_of & 0xffffu); nslices = static_cast<int32_t>(t.slice_of >> 16);
-          const unsigned long long now = p.trace ? cusync::globalTimerNs() : 0ull;
-          bars->sched_tile[slot][0] = tn; bars->sched_tile[slot][1] = tpm;
-          bars->sched_tile[slot][2] = valid; bars->sched_tile[slot][3] = static_cast<int32_t>(ticket);
-          bars->sched_tile[slot][4] = tz_slice; bars->sched_tile[slot][5] = nslices;
-          bars->sched_tile[slot][6] = static_cast<int32_t>(t.ws_tile);
-          bars->sched_time[slot] = now;
-          // the same record into the peer's ring, then signal both
-          const uint32_t pt = peer_sched_tile0 + slot * 32;
-          st_cluster_u32(pt, static_cast<uint32_t>(tn)); st_cluster_u32(pt + 4, static_cast<uint32_t>(tpm));
-          st_cluster_u32(pt + 8, static_cast<uint32_t>(valid)); st_cluster_u32(pt + 12, ticket);
-          st_cluster_u32(pt + 16, static_cast<uint32_t>(tz_slice)); st_cluster_u32(pt + 20, static_cast<uint32_t>(nslices));
-          st_cluster_u32(pt + 24, t.ws_tile);
-          st_cluster_u32(peer_sched_time0 + slot * 8, static_cast<uint32_t>(now));
-          st_cluster_u32(peer_sched_time0 + slot * 8 + 4, static_cast<uint32_t>(now >> 32));
-          mbar_arrive(&bars->sched_full[slot]);
-          mbar_arrive_cluster(peer_sched_full0 + slot * 8);
-        } else {
-          if (!mbar_wait_cluster(&bars->sched_full[slot], sph, ctx)) { ok = false; break; }
-          tn = bars->sched_tile[slot][0]; tpm = bars->sched_tile[slot][1]; valid = bars->sched_tile[slot][2];
-          tz_slice = bars->sched_tile[slot][4]; nslices = bars->sched_tile[slot][5];
-          mbar_arrive_cluster(leader_sched_empty0 + slot * 8);
-        }
-        sched_it++;
-        if (!valid) break;
-
-        const int n_off = tn * BN;
-        const int m_off = tpm * (2 * kBlockM) + static_cast<int>(rank) * kBlockM;   // this CTA's 128 rows
-        const int nb_off = n_off + static_cast<int>(rank) * (BN / 2);               // this CTA's half of B
-        uint32_t ready_end = 0;
-        long long wait_empty = 0;
-        const int kb_per_slice = (p.num_k_blocks + nslices - 1) / nslices;
-        const int kb_begin = tz_slice * kb_per_slice;
-        const int kb_end = kb_begin + kb_per_slice < p.num_k_blocks ? kb_begin + kb_per_slice : p.num_k_blocks;
-        for (int kb = kb_begin; kb < kb_end; kb++) {
-          const uint32_t s = fills % C::kStages, ph = (fills / C::kStages) & 1u;
-          const long long c0 = p.trace ? clock64() : 0;
-          if (!mbar_wait_cluster(&bars->empty[s], ph ^ 1u, ctx)) { ok = false; break; }
-          if (p.trace) wait_empty += clock64() - c0;
-          uint8_t* sa = ring + s * C::kStageBytes;
-          uint8_t* sb = sa + C::kABytes;
-          const uint32_t full_addr = leader_full0 + s * 8;
-          // The leader's barrier collects the bytes of both CTAs.
-          if (leader) mbar_expect_tx(&bars->full[s], 2 * C::kStageBytes);
-          const int k_base = kb * kPairBlockK;
-          // B half: one 3-D box.  [k,n] weights: {64 columns, 128 k rows, 2 column chunks};
-          // [n,k] weights: {64 k, 128 n rows, 2 k chunks}.
-          if (p.b_kmajor) tma_load_3d_pair(sb, &tmB, full_addr, 0, nb_off, k_base / 64);
-          else            tma_load_3d_pair(sb, &tmB, full_addr, 0, k_base, nb_off / 64);
-          // The stage spans two 64-deep K chunks; each may open a new producer tile.
-#pragma unroll 1
-          for (int sub = 0; sub < kPairBlockK / kBlockK && ok; sub++) {
-          const int k_off = k_base + sub * kBlockK;
-          if (p.is_consumer && m_off < p.m && k_off < p.k) {
-            const uint32_t tz = (kb == kb_begin && sub == 0) ? 1u : 0u;
-            if (static_cast<uint32_t>(k_off) >= ready_end &&
-                cusync::eval::isSync(st.in_policy, static_cast<uint32_t>(k_off), tz)) {
-              const uint32_t idx = cusync::eval::tileIndex(st.in_policy, static_cast<uint32_t>(m_off),
-                                                           static_cast<uint32_t>(k_off), st.prod_grid.x,
-                                                           st.prod_grid.y);
-              uint32_t seen = 0;
-              if (!cusync::spinUntilAtLeast(st.sems_wait + idx, wait_target, st.timeout_ns, &seen)) {
-                bars->abort = 1u;
-                cusync::recordTimeout(st.status, 1u, static_cast<uint32_t>(m_off), static_cast<uint32_t>(k_off), tz,
-                                      idx, seen, wait_target);
-                ok = false;
-                break;
-              }
-              if (sync_stride) {
-                uint32_t vals[kLookahead];
-#pragma unroll
-                for (int j = 0; j < kLookahead; j++) {
-                  const uint32_t kk = static_cast<uint32_t>(k_off) + (j + 1) * sync_stride;
-                  vals[j] = kk < static_cast<uint32_t>(p.k)
-                                ? cusync::loadRelaxed(st.sems_wait + cusync::eval::tileIndex(st.in_policy,
-                                      static_cast<uint32_t>(m_off), kk, st.prod_grid.x, st.prod_grid.y))
-                                : 0u;
-                }
-                uint32_t ahead = 0;
-#pragma unroll
-                for (int j = 0; j < kLookahead; j++) {
-                  if (ahead == static_cast<uint32_t>(j) && vals[j] >= wait_target) ahead++;
-                }
-                ready_end = static_cast<uint32_t>(k_off) + (ahead + 1) * sync_stride;
-                if (ahead) __threadfence();
-              }
-              fence_proxy_async();
-            }
-          }
-          }
-          // A: {64 k, 128 rows, 2 k chunks}.  Issued on the abort path too, so that the armed barrier
-          // completes and the drain below terminates.
-          tma_load_3d_pair(sa, &tmA, full_addr, 0, m_off, k_base / 64);
-          fills++;
-          if (!ok) break;
-        }
-        if (p.trace) {
-          const uint32_t tk = static_cast<uint32_t>(bars->sched_tile[slot][3]);
-          if (2 * tk + rank < p.trace_capacity)
-            p.trace[8ull * (2 * tk + rank) + 5] = static_cast<unsigned long long>(wait_empty);
-        }
-      }
-      if (!ok) {
-        bars->abort = 1u;
-        if (leader) {
-          // wait (bounded) for the copies of both CTAs that were armed on this CTA's barriers
-          const uint32_t live = fills < static_cast<uint32_t>(C::kStages) ? fills : static_cast<uint32_t>(C::kStages);
-          for (uint32_t j = 0; j < live; j++) {
-            const uint32_t f = fills - 1u - j;
-            const uint32_t s = f % C::kStages, ph = (f / C::kStages) & 1u;
-            const uint64_t t0 = cusync::globalTimerNs();
-            while (!mbar_try_wait_cluster(&bars->full[s], ph)) {
-              if (cusync::globalTimerNs() - t0 > 1000000000ull) break;
-            }
-          }
-        } else {
-          // the peer's copies complete on the leader's barriers, which it cannot wait on: give
-          // them time to land before this CTA's shared memory goes away
-          const uint64_t t0 = cusync::globalTimerNs();
-          while (cusync::globalTimerNs() - t0 < 100000ull) __nanosleep(1000);
-        }
-      }
-    }
-  } else if (warp == 1) {
-    // =====================================================================
-    // MMA issuer (leader only)
-    // =====================================================================
-    if (lane == 0 && leader) {
-      // instruction descriptor: M = 256 across the pair, N = 256
-      const uint32_t idesc = (1u << 4) | ((p.b_kmajor ? 0u : 1u) << 16) | (static_cast<uint32_t>(BN >> 3) << 17) |
-                             (static_cast<uint32_t>((2 * kBlockM) >> 4) << 24);
-      const uint32_t b_lbo = p.b_lbo, b_sbo = p.b_sbo, b_kstep = p.b_kstep;
-      uint32_t drains = 0, sched_it = 0, acc_it = 0;
-      bool ok = true, issued = false;
-      while (ok) {
-        const uint32_t slot = sched_it % kSchedSlots, sph = (sched_it / kSchedSlots) & 1u;
-        if (!mbar_wait(&bars->sched_full[slot], sph, ctx)) { ok = false; break; }
-        const int valid = bars->sched_tile[slot][2];
-        const uint32_t ticket = static_cast<uint32_t>(bars->sched_tile[slot][3]);
-        const int slice = bars->sched_tile[slot][4];
-        const int nslices = bars->sched_tile[slot][5];
-        mbar_arrive(&bars->sched_empty[slot]);
-        sched_it++;
-        if (!valid) break;
-        const uint32_t acc = acc_it & 1u, aph = (acc_it >> 1) & 1u;
-        const long long t_tile0 = p.trace ? clock64() : 0;
-        if (!mbar_wait_cluster(&bars->tmem_empty[acc], aph ^ 1u, ctx)) { ok = false; break; }
-        tc_fence_after();
-        const long long t_acc = p.trace ? clock64() : 0;
-        long long wait_full = 0;
-        const uint32_t d_tmem = tmem_base + acc * C::kAccCols;
-        const int kb_per_slice = (p.num_k_blocks + nslices - 1) / nslices;
-        const int kb_first = slice * kb_per_slice;
-        const int kb_count = kb_first + kb_per_slice < p.num_k_blocks ? kb_per_slice : p.num_k_blocks - kb_first;
-        for (int kb = 0; kb < kb_count; kb++) {
-          const uint32_t s = drains % C::kStages, ph = (drains / C::kStages) & 1u;
-          const long long c0 = p.trace ? clock64() : 0;
-          if (!mbar_wait_cluster(&bars->full[s], ph, ctx)) { ok = false; break; }
-          if (p.trace) wait_full += clock64() - c0;
-          tc_fence_after();
-          const uint32_t sa = smem_u32(ring + s * C::kStageBytes);
-          const uint32_t sb = sa + C::kABytes;
-#pragma unroll
-          for (int kk = 0; kk < kPairBlockK / kUmmaK; kk++) {
-            // K-major operands: 64-deep chunks of 128 rows, 32 bytes per K step inside a chunk.
-            // [k,n] B: 2048 bytes (16 rows) per K step, column chunks one leading offset apart.
-            const uint32_t a_off = (kk >> 2) * kPairChunkBytes + (kk & 3) * 32;
-            const uint32_t b_off = p.b_kmajor ? a_off : kk * b_kstep;
-            const uint64_t adesc = make_smem_desc(sa + a_off, 16u, 1024u);
-            const uint64_t bdesc = make_smem_desc(sb + b_off, b_lbo, b_sbo);
-            umma_f16_pair(d_tmem, adesc, bdesc, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
-          }
-          umma_commit_pair_both(&bars->empty[s]);     // frees the ring slot in both CTAs
-          issued = true;
-          drains++;
-        }
-        if (!ok) break;
-        umma_commit_pair_both(&bars->tmem_full[acc]);
-        if (p.trace && 2 * ticket < p.trace_capacity) {
-          p.trace[8ull * (2 * ticket) + 4] = static_cast<unsigned long long>(wait_full);
-          p.trace[8ull * (2 * ticket) + 6] = static_cast<unsigned long long>(clock64() - t_tile0);
-          p.trace[8ull * (2 * ticket) + 7] = static_cast<unsigned long long>(t_acc - t_tile0);
-        }
-        acc_it++;
-      }
-      if (!ok && issued) {
-        umma_commit_pair_local(&bars->drain);
-        const uint64_t t0 = cusync::globalTimerNs();
-        while (!mbar_try_wait(&bars->drain, 0u)) {
-          if (cusync::globalTimerNs() - t0 > 1000000000ull) break;
-        }
-      }
-    }
-  } else if (warp >= kEpilogueWarp0) {
-    // =====================================================================
-    // Epilogue (both CTAs, each for its own 128 rows)
-    // =====================================================================
-    const int ew = warp - kEpilogueWarp0;
-    const int quarter = ew & 3;
-    const int half = ew >> 2;
-    uint8_t* buf = staging + ew * (32 * 128);
-    uint32_t sched_it = 0, acc_it = 0, post_it = 0, split_it = 0;
-    bool ok = true;
-    while (ok) {
-      const uint32_t slot = sched_it % kSchedSlots, sph = (sched_it / kSchedSlots) & 1u;
-      if (!mbar_wait_cluster(&bars->sched_full[slot], sph, ctx)) { ok = false; break; }
-      const int tile_n = bars->sched_tile[slot][0];
-      const int pair_m = bars->sched_tile[slot][1];
-      const int valid = bars->sched_tile[slot][2];
-      const uint32_t nslices = static_cast<uint32_t>(bars->sched_tile[slot][5]);
-      const uint32_t ws_slot = static_cast<uint32_t>(bars->sched_tile[slot][6]) * nslices;   // the tile's first slot
-      const uint32_t slice = static_cast<uint32_t>(bars->sched_tile[slot][4]);
-      const uint32_t ticket = static_cast<uint32_t>(bars->sched_tile[slot][3]);
-      const unsigned long long t_draw = bars->sched_time[slot];
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(leader_sched_empty0 + slot * 8);
-      sched_it++;
-      if (!valid) break;
-      const uint32_t acc = acc_it & 1u, aph = (acc_it >> 1) & 1u;
-      if (!mbar_wait_cluster(&bars->tmem_full[acc], aph, ctx)) { ok = false; break; }
-      tc_fence_after();
-      const unsigned long long t_mma_done = p.trace ? cusync::globalTimerNs() : 0ull;
-      const int n_off = tile_n * BN;
-      const int m_off = pair_m * (2 * kBlockM) + static_cast<int>(rank) * kBlockM;
-      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * C::kAccCols;
-
-      if (nslices > 1u) {
-        // One K slice of the tile: add it to the workspace; the pair that brings the last slice finalises.
-        // `post` is also used by unsplit tiles, the two split-K barriers only here: separate phase counters.
-        bool last = false;
-        ok = splitk_epilogue<BN>(p, &tmWS, buf, bars, ctx, t_row, n_off, m_off, quarter, half, ew, lane, post_it & 1u,
-                                 split_it & 1u, nslices, nullptr, leader_tmem_empty0 + acc * 8,
-                                 static_cast<__half*>(p.d), p.ldd, &last,
-                                 reinterpret_cast<float4*>(p.splitk_ws) + static_cast<size_t>(ws_slot) * kPairSlotVec4 +
-                                     rank * (kPairSlotVec4 / 2),
-                                 slice, &tmD);
-        acc_it++;
-        if (ew == 0 && lane == 0) {
-          if (!mbar_wait(&bars->splitk_done, split_it & 1u, ctx)) ok = false;
-          else if (last && p.is_producer) {
-            const uint32_t idx = cusync::eval::tileIndex(st.out_policy, static_cast<uint32_t>(m_off),
-                                                         static_cast<uint32_t>(n_off), st.grid.x, st.grid.y);
-            const uint32_t pv = cusync::eval::postValue(st.out_policy);
-            __threadfence();
-            if (st.opts & CUSYNC_OPT_NO_ATOMIC_ADD) cusync::storeRelease(st.sems_post + idx, pv * st.iter);
-            else                                    cusync::addRelease(st.sems_post + idx, pv);
-          }
-        }
-        post_it++;
-        split_it++;
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-        if (p.trace && ew == 0 && lane == 0 && 2 * ticket + rank < p.trace_capacity) {
-          uint32_t smid;
-          asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-          unsigned long long* rec = p.trace + 8ull * (2 * ticket + rank);
-          rec[0] = t_draw; rec[1] = t_mma_done; rec[2] = cusync::globalTimerNs();
-          rec[3] = (static_cast<unsigned long long>(smid) << 32) | blockIdx.x;
-        }
-        continue;
-      }
-      epilogue_store_rows<BN, false>(p, &tmD, buf, t_row, n_off, m_off + quarter * 32, half, lane);
-
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(leader_tmem_empty0 + acc * 8);
-      acc_it++;
-
-      if (p.is_producer && m_off < p.m) {     // a pair's second half may lie past the last row tile
-        if (lane == 0) {
-          tma_store_wait_all();
-          __threadfence();
-          // Epilogue warps run at their own pace: one that is a tile ahead must not arrive on `post`
-          // while the previous tile's phase is still open (its arrival would close that phase early).
-          if (!mbar_wait(&bars->post, (post_it & 1u) ^ 1u, ctx)) ok = false;
-          mbar_arrive(&bars->post);
-          if (ew == 0) {
-            if (!mbar_wait(&bars->post, post_it & 1u, ctx)) ok = false;
-            else {
-              const uint32_t idx = cusync::eval::tileIndex(st.out_policy, static_cast<uint32_t>(m_off),
-                                                           static_cast<uint32_t>(n_off), st.grid.x, st.grid.y);
-              const uint32_t pv = cusync::eval::postValue(st.out_policy);
-              __threadfence();
-              if (st.opts & CUSYNC_OPT_NO_ATOMIC_ADD) cusync::storeRelease(st.sems_post + idx, pv * st.iter);
-              else                                    cusync::addRelease(st.sems_post + idx, pv);
-            }
-          }
-        }
-        post_it++;
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      }
-      if (p.trace && ew == 0 && lane == 0 && 2 * ticket + rank < p.trace_capacity) {
-        uint32_t smid;
-        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-        unsigned long long* rec = p.trace + 8ull * (2 * ticket + rank);
-        rec[0] = t_draw; rec[1] = t_mma_done; rec[2] = cusync::globalTimerNs();
-        rec[3] = (static_cast<unsigned long long>(smid) << 32) | blockIdx.x;
-      }
-    }
-    if (lane == 0) tma_store_wait_all();
-  }
-
-  // Teardown: nobody may leave while the peer can still signal its barriers or read its operands.
-  tc_fence_before();
-  __syncthreads();
-  cluster_sync_all();
-  if (warp == 2) {
-    tc_fence_after();
-    tmem_dealloc_pair(tmem_base, C::kTmemCols);
-  }
-}
 
 // ---------------------------------------------------------------------------
 // Host side
@@ -2667,3 +764,4 @@ int cusync_conv2d_run(cusync_conv2d_plan_t* pl, cusync_stream_t stream) { return
 uint32_t cusync_conv2d_plan_num_ctas(const cusync_conv2d_plan_t* pl) { return pl ? pl->num_ctas : 0; }
 
 }  // extern "C"
+

@@ -24,7 +24,7 @@ class MLPShard:
     """x[B,H] -> y[B,H] through W1 (and V) [H,F] and W2 [F,H]; fp16, fp32 accumulate."""
 
     def __init__(self, model, batch, x, w1, w2, v=None, policy="rowsync", opts=0, tile_n1=0, tile_n2=0, max_ctas=0,
-                 group_rows2=0, cta_pair=0, split_k1=0, split_k2=0, tail_split=(0, 0, 0, 0), post_rows=False):
+                 group_rows2=0, cta_pair=0, split_k1=0, split_k2=0, tail_split=(0, 0, 0, 0), post_rows=False, group_rows1=0):
         import torch
         self.model = L.MLP_GPT3 if model == "gpt3" else L.MLP_LLAMA
         self.batch, self.hidden, self.ffn = batch, w1.shape[0], w1.shape[1]
@@ -33,7 +33,7 @@ class MLPShard:
         self.h = torch.empty((batch, self.ffn), device=x.device, dtype=torch.half)
         self.y = torch.empty((batch, self.hidden), device=x.device, dtype=torch.half)
         d = L.MlpDesc(self.model, batch, self.hidden, self.ffn, POLICIES[policy], opts, tile_n1, tile_n2, split_k1,
-                      split_k2, max_ctas, cta_pair, group_rows2, tail_split[0], tail_split[1], tail_split[2], tail_split[3], 1 if post_rows else 0,
+                      split_k2, max_ctas, cta_pair, group_rows2, tail_split[0], tail_split[1], tail_split[2], tail_split[3], group_rows1, 1 if post_rows else 0,
                       x.data_ptr(), w1.data_ptr(), v.data_ptr() if v is not None else None, w2.data_ptr(),
                       self.h.data_ptr(), self.y.data_ptr())
         self._h = C.c_void_p()

@@ -401,6 +401,7 @@ typedef struct cusync_mlp_desc {
   int32_t group_rows2;           /* the consumer's tile order: 0 = choose, 1 = plain, n > 1 = CUSYNC_ORDER_GROUPED(n) */
   int32_t tail_split_sync1, tail_split_sync2;    /* cusync_gemm_desc_t.tail_split of the two synchronised GEMMs ... */
   int32_t tail_split_plain1, tail_split_plain2;  /* ... and of the two stream-ordered ones: 0 = choose, 1 = none */
+  int32_t group_rows1;           /* the producer's tile order: 0 or 1 = plain, n > 1 = CUSYNC_ORDER_GROUPED(n) */
   int32_t post_rows;             /* 1: the second GEMM of run_cusync is a producer too: it posts RowSync semaphores, one
                                     per 128-row tile of Y, counting its column tiles, so that whatever consumes Y (the
                                     all-reduce of a tensor-parallel layer) can start row block by row block
