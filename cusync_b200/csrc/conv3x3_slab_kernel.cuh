@@ -26,15 +26,16 @@ namespace {
 // Tile shape, stage grid, semaphores and policies are those of the general path: one tile = conv_rows whole image
 // rows, waits on its own and the two neighbouring producer tiles, posts once.
 //
-// The scheduler keeps three tickets in flight: the ticket draw, the schedule look-up and the semaphore probes of
-// a tile are three dependent memory round trips (about 2 us), as long as a whole tile's math here, so each is
-// issued one tile ahead of the next.  Every CTA therefore draws exactly three tickets past the end.
+// The scheduler works in groups of four tickets, one group ahead: the ticket draw, the schedule look-up and the
+// semaphore probes of a tile are three dependent memory round trips (about 2 us, as long as two tiles' math
+// here), and the fence that makes the probes acquiring costs over a thousand cycles, so all of it is issued for
+// four tiles at once while the previous four are being loaded.  Every CTA draws exactly two groups past the end.
 constexpr int kSlabStages = 4;
 constexpr int kSlabBytes = 256 * 128;          // room for 256 pixel rows: the last tap reads up to row 2(W+2)+2+127
 constexpr int kSlabFilterBytes = 9 * 64 * 128; // nine taps of [64 n][64 c]
 constexpr int kSlabBN = 64;
 constexpr uint32_t kSlabSmemBytes = 1024 + kSlabStages * kSlabBytes + kSlabFilterBytes + 1024;
-constexpr int kSlabTicketsAhead = 3;
+constexpr int kSlabGroup = 4;                  // most tickets a block draws at a time
 constexpr int kSlabIssuers = 2;                // threads that issue MMAs, alternating tiles
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -93,107 +94,165 @@ cusync_conv3x3_slab_kernel(const __grid_constant__ CUtensorMap tmX, const __grid
       for (int tap = 0; tap < 9; tap++) tma_load_2d(filt + tap * (64 * 128), &tmF, filt_full, tap * p.conv_c, 0);
 
       const uint32_t num_tiles = static_cast<uint32_t>(p.num_tiles);
-      const uint32_t total_draws = num_tiles + kSlabTicketsAhead * gridDim.x;
+      // Tickets are drawn in groups, and a group ahead, only as far as the grid can afford: a block that holds
+      // tickets it is not yet working on keeps them from idle blocks.  With at most two tiles per block there is
+      // no drawing ahead; groups grow to kSlabGroup tickets from sixteen tiles per block.  Every block draws
+      // exactly one group that lies wholly past the end (two when it draws ahead), so the launch's last draw
+      // starts at last_base.
+      const bool ahead = num_tiles > 2u * gridDim.x;
+      uint32_t group = num_tiles / (4u * gridDim.x);
+      group = group < 1u ? 1u : (group > kSlabGroup ? kSlabGroup : group);
+      const uint32_t groups_total = (num_tiles + group - 1u) / group + (ahead ? 2u : 1u) * gridDim.x;
+      const uint32_t last_base = group * (groups_total - 1u);
       const uint32_t wait_target = p.is_consumer ? st.iter * cusync::eval::waitValue(st.in_policy) : 0u;
       const int span = p.conv_rows * p.conv_w;           // output pixels per tile
       uint32_t fills = 0, sched_it = 0;
       bool ok = true;
 
-      // Pipeline registers: tickets of the tiles i, i+1, i+2; schedule entries of i and i+1; probes of i.
-      uint32_t tk0 = atomicAdd(st.tile_counter, 1u);
-      uint32_t tk1 = atomicAdd(st.tile_counter, 1u);
-      uint32_t tk2 = atomicAdd(st.tile_counter, 1u);
-      uint32_t y0 = tk0 < num_tiles ? st.tile_order[tk0].y : 0u;
-      uint32_t y1 = tk1 < num_tiles ? st.tile_order[tk1].y : 0u;
-      uint32_t pr0 = 0, pr1 = 0, pr2 = 0;                // semaphore values seen for tile i: own, above, below
-      auto sem_indices = [&](uint32_t ty, uint32_t* own, uint32_t* up, uint32_t* dn) {
-        const int tin = static_cast<int>(ty) % p.conv_tiles_per_image;
-        const uint32_t m_off = ty * static_cast<uint32_t>(span);
-        *own = cusync::eval::tileIndex(st.in_policy, m_off, 0u, st.prod_grid.x, st.prod_grid.y);
-        *up = tin > 0 ? cusync::eval::tileIndex(st.in_policy, m_off - span, 0u, st.prod_grid.x, st.prod_grid.y) : *own;
-        *dn = tin + 1 < p.conv_tiles_per_image
-                  ? cusync::eval::tileIndex(st.in_policy, m_off + span, 0u, st.prod_grid.x, st.prod_grid.y) : *own;
+      // The policy's tile index is affine in the tile row (the column is always 0 here); when it is the row itself
+      // (any x-fastest or transposed order over a one-column producer grid) the three integer divisions per
+      // evaluation are skipped.
+      auto policy_index = [&](uint32_t row) {
+        return cusync::eval::tileIndex(st.in_policy, row * static_cast<uint32_t>(span), 0u, st.prod_grid.x, st.prod_grid.y);
       };
-      if (p.is_consumer && tk0 < num_tiles) {
-        uint32_t a, b, c;
-        sem_indices(y0, &a, &b, &c);
-        pr0 = cusync::loadRelaxed(st.sems_wait + a); pr1 = cusync::loadRelaxed(st.sems_wait + b);
-        pr2 = cusync::loadRelaxed(st.sems_wait + c);
+      const bool index_is_row = p.is_consumer && policy_index(0u) == 0u && policy_index(1u) == 1u &&
+                                policy_index(num_tiles - 1u) == num_tiles - 1u;
+      // semaphores a tile depends on: its own producer tile and the neighbours holding its halo rows
+      auto sem_indices = [&](uint32_t ty, uint32_t* idx) {
+        const int tin = static_cast<int>(ty) % p.conv_tiles_per_image;
+        if (index_is_row) {
+          idx[0] = ty;
+          idx[1] = tin > 0 ? ty - 1u : ty;
+          idx[2] = tin + 1 < p.conv_tiles_per_image ? ty + 1u : ty;
+          return;
+        }
+        idx[0] = policy_index(ty);
+        idx[1] = tin > 0 ? policy_index(ty - 1u) : idx[0];
+        idx[2] = tin + 1 < p.conv_tiles_per_image ? policy_index(ty + 1u) : idx[0];
+      };
+      // Probes the dependencies of a group of tiles with relaxed loads (all in flight together), then ONE fence
+      // makes them acquiring: the fence is the expensive part (over a thousand cycles here) and is paid once
+      // per group, a tile ahead of need.  ready[j] tells whether tile j may be loaded without waiting.
+      auto probe_group = [&](uint32_t base, const uint32_t* ys, bool* ready) {
+        uint32_t v[kSlabGroup][3];
+#pragma unroll
+        for (int j = 0; j < kSlabGroup; j++) {
+          if (j < static_cast<int>(group) && base + j < num_tiles) {
+            uint32_t idx[3];
+            sem_indices(ys[j], idx);
+#pragma unroll
+            for (int e = 0; e < 3; e++) v[j][e] = cusync::loadRelaxed(st.sems_wait + idx[e]);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < kSlabGroup; j++)
+          ready[j] = j < static_cast<int>(group) && base + j < num_tiles && v[j][0] >= wait_target &&
+                     v[j][1] >= wait_target && v[j][2] >= wait_target;
+        cusync::fenceAcqRel();
+        fence_proxy_async();     // acquire (generic proxy) before the TMA reads (async proxy)
+      };
+
+      // Pipeline: group 0 is being loaded, group 1 has its tickets (schedule entries and probes follow while
+      // group 0 is worked on), group 2 is drawn at the top of the iteration.
+      uint32_t base0 = atomicAdd(st.tile_counter, group);
+      uint32_t base1 = ahead ? atomicAdd(st.tile_counter, group) : 0u;
+      uint32_t y0[kSlabGroup], y1[kSlabGroup];
+      bool ready0[kSlabGroup], ready1[kSlabGroup];
+#pragma unroll
+      for (int j = 0; j < kSlabGroup; j++) {
+        y0[j] = j < static_cast<int>(group) && base0 + j < num_tiles ? st.tile_order[base0 + j].y : 0u;
+        ready0[j] = !p.is_consumer;
+        ready1[j] = !p.is_consumer;
       }
+      if (p.is_consumer && base0 < num_tiles) probe_group(base0, y0, ready0);
+
       while (ok) {
-        const bool valid = tk0 < num_tiles;
-        const long long lc0 = p.trace ? clock64() : 0;
-        // Tile i's dependencies first: the fence that makes its (earlier) probes acquiring would otherwise
-        // also wait for the loads issued below for later tiles.
-        bool waited_ok = true;
-        if (valid && p.is_consumer) {
-          if (pr0 < wait_target || pr1 < wait_target || pr2 < wait_target) {
+        if (base0 >= num_tiles) {
+          // this block's groups past the end are base0 and, when drawing ahead, base1; the launch's last draw
+          // re-arms the counter (the reference resets on the last tile, cusync_device_defs.h:87-90)
+          if (base0 == last_base || (ahead && base1 == last_base)) atomicExch(st.tile_counter, 0u);
+          const uint32_t slot = sched_it % kSchedSlots, sph = (sched_it / kSchedSlots) & 1u;
+          if (!mbar_wait(&bars->sched_empty[slot], sph ^ 1u, ctx)) { ok = false; break; }
+          bars->sched_tile[slot][2] = 0;
+          bars->sched_tile[slot][3] = static_cast<int32_t>(base0);
+          mbar_arrive(&bars->sched_full[slot]);
+          sched_it++;
+          break;
+        }
+        // for later groups: the draw of group 2 and the schedule entries of group 1 (both in flight while
+        // group 0 is loaded)
+        uint32_t base2 = 0u;
+        if (ahead) {
+          base2 = atomicAdd(st.tile_counter, group);
+#pragma unroll
+          for (int j = 0; j < kSlabGroup; j++)
+            y1[j] = j < static_cast<int>(group) && base1 + j < num_tiles ? st.tile_order[base1 + j].y : 0u;
+        }
+
+#pragma unroll 1
+        for (int j = 0; j < static_cast<int>(group) && ok; j++) {
+          const uint32_t ticket = base0 + j;
+          if (ticket >= num_tiles) break;
+          const long long lc0 = p.trace ? clock64() : 0;
+          const uint32_t ty = y0[j];
+          if (p.is_consumer && !ready0[j]) {
             // not finished when probed: wait (bounded) for the tile itself and its two halo neighbours
             uint32_t idx[3];
-            sem_indices(y0, &idx[0], &idx[1], &idx[2]);
-            for (int j = 0; j < 3 && waited_ok; j++) {
+            sem_indices(ty, idx);
+            for (int e = 0; e < 3 && ok; e++) {
               uint32_t seen = 0;
-              if (!cusync::spinUntilAtLeast(st.sems_wait + idx[j], wait_target, st.timeout_ns, &seen)) {
+              if (!cusync::spinUntilAtLeast(st.sems_wait + idx[e], wait_target, st.timeout_ns, &seen)) {
                 bars->abort = 1u;
-                cusync::recordTimeout(st.status, 1u, y0 * static_cast<uint32_t>(span), 0u, static_cast<uint32_t>(j), idx[j],
+                cusync::recordTimeout(st.status, 1u, ty * static_cast<uint32_t>(span), 0u, static_cast<uint32_t>(e), idx[e],
                                       seen, wait_target);
-                waited_ok = false;
+                ok = false;
               }
             }
-          } else {
-            cusync::fenceAcqRel();  // makes the relaxed probes acquiring
+            fence_proxy_async();
           }
-          fence_proxy_async();     // acquire (generic proxy) before the TMA read (async proxy)
-        }
-        const long long lc1 = p.trace ? clock64() : 0;
-        uint32_t tk3 = 0, y2 = 0, pn0 = 0, pn1 = 0, pn2 = 0;
-        if (valid) {
-          // issue, for later tiles: the draw of i+3, the schedule entry of i+2, the probes of i+1
-          tk3 = atomicAdd(st.tile_counter, 1u);
-          y2 = tk2 < num_tiles ? st.tile_order[tk2].y : 0u;
-          if (p.is_consumer && tk1 < num_tiles) {
-            uint32_t a, b, c;
-            sem_indices(y1, &a, &b, &c);
-            pn0 = cusync::loadRelaxed(st.sems_wait + a); pn1 = cusync::loadRelaxed(st.sems_wait + b);
-            pn2 = cusync::loadRelaxed(st.sems_wait + c);
-          }
-        } else {
-          // the three tickets in hand are this block's draws past the end; the launch's last draw re-arms
-          // the counter (the reference resets on the last tile, cusync_device_defs.h:87-90)
-          if (tk0 == total_draws - 1u || tk1 == total_draws - 1u || tk2 == total_draws - 1u)
-            atomicExch(st.tile_counter, 0u);
-        }
-        const long long lc2 = p.trace ? clock64() : 0;
-        const uint32_t slot = sched_it % kSchedSlots, sph = (sched_it / kSchedSlots) & 1u;
-        if (!mbar_wait(&bars->sched_empty[slot], sph ^ 1u, ctx)) { ok = false; break; }
-        bars->sched_tile[slot][0] = 0;
-        bars->sched_tile[slot][1] = static_cast<int32_t>(y0);
-        bars->sched_tile[slot][2] = valid ? 1 : 0;
-        bars->sched_tile[slot][3] = static_cast<int32_t>(tk0);
-        if (p.trace) bars->sched_time[slot] = cusync::globalTimerNs();
-        mbar_arrive(&bars->sched_full[slot]);
-        sched_it++;
-        if (!valid) break;
-        if (!waited_ok) { ok = false; break; }
+          const long long lc1 = p.trace ? clock64() : 0;
+          const uint32_t slot = sched_it % kSchedSlots, sph = (sched_it / kSchedSlots) & 1u;
+          if (!mbar_wait(&bars->sched_empty[slot], sph ^ 1u, ctx)) { ok = false; break; }
+          bars->sched_tile[slot][0] = 0;
+          bars->sched_tile[slot][1] = static_cast<int32_t>(ty);
+          bars->sched_tile[slot][2] = 1;
+          bars->sched_tile[slot][3] = static_cast<int32_t>(ticket);
+          if (p.trace) bars->sched_time[slot] = cusync::globalTimerNs();
+          mbar_arrive(&bars->sched_full[slot]);
+          sched_it++;
+          if (!ok) break;      // published, so that the other threads see the abort instead of a missing tile
 
-        const int img = static_cast<int>(y0) / p.conv_tiles_per_image;
-        const int h0 = (static_cast<int>(y0) % p.conv_tiles_per_image) * p.conv_rows;
-        const long long lc3 = p.trace ? clock64() : 0;
-        const uint32_t s = fills % kSlabStages, ph = (fills / kSlabStages) & 1u;
-        if (!mbar_wait(&bars->empty[s], ph ^ 1u, ctx)) { ok = false; break; }
-        const long long lc4 = p.trace ? clock64() : 0;
-        const uint32_t slab_bytes = static_cast<uint32_t>((p.conv_rows + 2) * wp * 128);
-        mbar_expect_tx(&bars->full[s], slab_bytes);
-        // box {64 channels, W + 2 pixels, conv_rows + 2 rows, 1 image} from pixel (-1, h0 - 1)
-        tma_load_4d(slabs + s * kSlabBytes, &tmX, &bars->full[s], 0, -1, h0 - 1, img);
-        fills++;
-        if (p.trace && tk0 < p.trace_capacity) {
-          // loader's cycles for this tile: dependencies | prefetch issue | schedule slot | free slab | TMA issue
-          auto cap = [](long long v) { return static_cast<unsigned long long>(v < 0 ? 0 : (v > 4095 ? 4095 : v)); };
-          p.trace[8ull * tk0 + 5] = cap(lc1 - lc0) | (cap(lc2 - lc1) << 12) | (cap(lc3 - lc2) << 24) |
-                                    (cap(lc4 - lc3) << 36) | (cap(clock64() - lc4) << 48);
+          const int img = static_cast<int>(ty) / p.conv_tiles_per_image;
+          const int h0 = (static_cast<int>(ty) % p.conv_tiles_per_image) * p.conv_rows;
+          const long long lc2 = p.trace ? clock64() : 0;
+          const uint32_t s = fills % kSlabStages, ph = (fills / kSlabStages) & 1u;
+          if (!mbar_wait(&bars->empty[s], ph ^ 1u, ctx)) { ok = false; break; }
+          const long long lc3 = p.trace ? clock64() : 0;
+          const uint32_t slab_bytes = static_cast<uint32_t>((p.conv_rows + 2) * wp * 128);
+          mbar_expect_tx(&bars->full[s], slab_bytes);
+          // box {64 channels, W + 2 pixels, conv_rows + 2 rows, 1 image} from pixel (-1, h0 - 1)
+          tma_load_4d(slabs + s * kSlabBytes, &tmX, &bars->full[s], 0, -1, h0 - 1, img);
+          fills++;
+          if (p.trace && ticket < p.trace_capacity) {
+            // loader's cycles for this tile: dependencies | schedule slot | free slab | TMA issue
+            auto cap = [](long long v) { return static_cast<unsigned long long>(v < 0 ? 0 : (v > 4095 ? 4095 : v)); };
+            p.trace[8ull * ticket + 5] = cap(lc1 - lc0) | (cap(lc2 - lc1) << 12) | (cap(lc3 - lc2) << 24) |
+                                         (cap(clock64() - lc3) << 36);
+          }
         }
-        tk0 = tk1; tk1 = tk2; tk2 = tk3; y0 = y1; y1 = y2; pr0 = pn0; pr1 = pn1; pr2 = pn2;
+        if (!ok) break;
+        if (!ahead) {
+          // the next group is drawn only now that this one is under way
+          base1 = atomicAdd(st.tile_counter, group);
+#pragma unroll
+          for (int j = 0; j < kSlabGroup; j++)
+            y1[j] = j < static_cast<int>(group) && base1 + j < num_tiles ? st.tile_order[base1 + j].y : 0u;
+        }
+        // group 1's dependencies, one group ahead of need
+        if (p.is_consumer && base1 < num_tiles) probe_group(base1, y1, ready1);
+        base0 = base1; base1 = base2;
+#pragma unroll
+        for (int j = 0; j < kSlabGroup; j++) { y0[j] = y1[j]; ready0[j] = ready1[j]; }
       }
       if (!ok) {
         bars->abort = 1u;

@@ -19,6 +19,7 @@ struct cusync_conv_chain {
   cusync_stage_t* stages[kMaxConvs];
   cusync_conv2d_plan_t* sync[kMaxConvs];    // convolution i with its stage
   cusync_conv2d_plan_t* plain[kMaxConvs];   // the same kernel without tile synchronisation
+  int sync_ctas;                            // blocks per synchronised convolution
   bool wait_kernels;                        // false: every stage fits on the device at once
   cudaEvent_t fork;                         // orders the resets of a replayable run before every stage
 };
@@ -71,9 +72,19 @@ int cusync_conv_chain_create(cusync_conv_chain_t** out, const cusync_conv_chain_
 
   int sms = cusync_b200_sm_count();
   if (sms <= 0) sms = 148;
-  const uint32_t blocks = grid.x * grid.y;
+  // Left to choose, small chains (at most two tiles per SM and convolution) share the device: each synchronised
+  // convolution gets sms / num_convs persistent blocks, so that every stage is resident from the start and the
+  // chain runs as a pipeline over the semaphores, with no wait kernels (the reference's AvoidWaitKernel case,
+  // cusync.h:61-62).  Larger chains give every convolution the whole device (measured faster from about ten
+  // images of 56 x 56 on); the next stage then becomes resident as the previous one's blocks retire.
+  const uint32_t tiles = grid.x * grid.y;
+  const uint32_t share = static_cast<uint32_t>(sms / d.num_convs) > 0 ? static_cast<uint32_t>(sms / d.num_convs) : 1u;
+  const uint32_t cap = d.max_ctas > 0 ? static_cast<uint32_t>(d.max_ctas)
+                                      : (tiles <= 2u * static_cast<uint32_t>(sms) ? share : static_cast<uint32_t>(sms));
+  const uint32_t blocks = tiles < cap ? tiles : cap;
+  c->sync_ctas = static_cast<int>(cap);
   c->wait_kernels = static_cast<uint64_t>(blocks) * d.num_convs > static_cast<uint64_t>(sms);
-  const int opts = c->wait_kernels ? CUSYNC_OPT_NONE : CUSYNC_OPT_AVOID_WAIT_KERNEL;   // cusync.h:61-62
+  const int opts = c->wait_kernels ? CUSYNC_OPT_NONE : CUSYNC_OPT_AVOID_WAIT_KERNEL;
 
   int rc = CUSYNC_SUCCESS;
   for (int i = 0; i < c->num && rc == CUSYNC_SUCCESS; i++)
@@ -87,9 +98,10 @@ int cusync_conv_chain_create(cusync_conv_chain_t** out, const cusync_conv_chain_
     cd.r = 3; cd.s = 3; cd.stride = 1; cd.pad = 1;
     cd.x = d.activations[i]; cd.filter = d.filters[i]; cd.y = d.activations[i + 1];
     cd.epilogue = d.relu ? CUSYNC_EPILOGUE_RELU : CUSYNC_EPILOGUE_NONE;
-    cd.max_ctas = d.max_ctas;
+    cd.max_ctas = c->sync_ctas;
     cd.stage = c->stages[i];
     rc = cusync_conv2d_plan_create(&c->sync[i], &cd);
+    cd.max_ctas = d.max_ctas;        // the stream-ordered convolutions each take the whole device
     cd.stage = nullptr;
     if (rc == CUSYNC_SUCCESS) rc = cusync_conv2d_plan_create(&c->plain[i], &cd);
   }

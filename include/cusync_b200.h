@@ -281,7 +281,7 @@ CUSYNC_API int cusync_gemm_run_noalloc(const cusync_gemm_desc_t* desc, cusync_st
  *  (SM id << 32) | block index, SM cycles the MMA thread waited for operands, SM cycles the loader
  *  waited for a free ring slot, SM cycles of the tile in the MMA thread, of which waiting for a free
  *  accumulator}.  (The 64 -> 64 channel convolution kernel packs into the sixth word the loader's cycles for the
- *  tile instead, 12 bits each from bit 0: dependencies, prefetch issue, schedule slot, free slab, TMA issue.)
+ *  tile instead, 12 bits each from bit 0: dependencies, schedule slot, free slab, TMA issue.)
  *  NULL switches it off (the default).  No counterpart in the reference. */
 CUSYNC_API int cusync_gemm_plan_set_trace(cusync_gemm_plan_t* plan, void* device_buffer, uint32_t capacity_tiles);
 /* Blocks the launch uses (persistent grid). */
@@ -325,7 +325,8 @@ typedef struct cusync_conv_chain_desc {
   int32_t num_convs;               /* 2..8 */
   int32_t n, h, w, channels;
   int32_t relu;
-  int32_t max_ctas;                /* 0 = one block per SM */
+  int32_t max_ctas;                /* blocks per convolution; 0 = choose: the synchronised convolutions of a small
+                                      chain share the SMs equally (all stages resident at once), otherwise one per SM */
   const void* const* filters;      /* [num_convs] pointers to [channels, 3, 3, channels] */
   void* const* activations;        /* [num_convs + 1] pointers to [n, h, w, channels] */
 } cusync_conv_chain_desc_t;

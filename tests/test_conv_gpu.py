@@ -108,7 +108,9 @@ def test_conv_chain_driver(n, h, w, c, convs, max_ctas):
     filters = [(torch.randn((c, 3, 3, c), generator=g) * (2.0 / (9 * c)) ** 0.5).half().cuda() for _ in range(convs)]
     chain = cs.ConvChain(x, filters, relu=True, max_ctas=max_ctas)
     blocks = n * (h // (128 // w)) * (c // 64)
-    assert chain.uses_wait_kernels == (blocks * convs > L.lib().cusync_b200_sm_count())
+    sms = L.lib().cusync_b200_sm_count()
+    per_stage = min(blocks, max_ctas if max_ctas else (sms // convs if blocks <= 2 * sms else sms))
+    assert chain.uses_wait_kernels == (per_stage * convs > sms)
     streams = [torch.cuda.Stream(priority=-1)] + [torch.cuda.Stream() for _ in range(convs - 1)]
     for it in range(1, 4):
         for out in chain.outputs:
