@@ -346,7 +346,7 @@ cusync_conv3x3_slab_kernel(const __grid_constant__ CUtensorMap tmX, const __grid
     const int ew = warp - kEpilogueWarp0;
     const int quarter = ew & 3;
     const int half = ew >> 2;
-    uint32_t sched_it = 0, acc_it = 0, post_it = 0;
+    uint32_t sched_it = 0, acc_it = 0;
     bool ok = true;
     const int mrow = quarter * 32 + lane;
     const int prow = mrow / wp, pcol = mrow % wp;       // image row within the tile, column
