@@ -68,7 +68,7 @@ class Conv2dDesc(C.Structure):
     _fields_ = [("n", C.c_int32), ("h", C.c_int32), ("w", C.c_int32), ("c", C.c_int32), ("k", C.c_int32),
                 ("r", C.c_int32), ("s", C.c_int32), ("stride", C.c_int32), ("pad", C.c_int32),
                 ("x", C.c_void_p), ("filter", C.c_void_p), ("y", C.c_void_p),
-                ("epilogue", C.c_int32), ("max_ctas", C.c_int32), ("stage", C.c_void_p)]
+                ("epilogue", C.c_int32), ("max_ctas", C.c_int32), ("kernel", C.c_int32), ("stage", C.c_void_p)]
 
 
 class ConvChainDesc(C.Structure):

@@ -310,10 +310,12 @@ class Conv2dFprop:
     def __init__(self):
         self._plan = C.c_void_p()
 
-    def initialize(self, custage, problem, x, filt, y, epilogue=L.EPILOGUE_NONE, max_ctas=0):
+    GENERAL, SLAB = 1, 2      # cusync_conv2d_desc_t.kernel
+
+    def initialize(self, custage, problem, x, filt, y, epilogue=L.EPILOGUE_NONE, max_ctas=0, kernel=0):
         self.destroy()
         d = L.Conv2dDesc(problem.n, problem.h, problem.w, problem.c, problem.k, problem.r, problem.s, problem.stride,
-                         problem.pad, x.data_ptr(), filt.data_ptr(), y.data_ptr(), epilogue, max_ctas,
+                         problem.pad, x.data_ptr(), filt.data_ptr(), y.data_ptr(), epilogue, max_ctas, kernel,
                          custage._h if custage is not None else None)
         return L.lib().cusync_conv2d_plan_create(C.byref(self._plan), C.byref(d))
 

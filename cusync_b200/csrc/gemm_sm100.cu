@@ -728,11 +728,12 @@ int cusync_conv2d_plan_create(cusync_conv2d_plan_t** out, const cusync_conv2d_de
   pl->num_ctas = static_cast<uint32_t>(p.num_tiles) < cap ? static_cast<uint32_t>(p.num_tiles) : cap;
   // The slab kernel serves the 64 -> 64 channel layer when a tile's padded rows still fit the 128-row MMA and
   // the consumer side waits once per tile (no input policy, or Conv2DTileSync over a one-column producer grid).
-  pl->conv_slab = rc == CUSYNC_SUCCESS && d.c == 64 && d.k == 64 && rows * (d.w + 2) <= kBlockM &&
-                  d.w + 2 <= 256 &&
-                  (view.in_policy.kind == CUSYNC_POLICY_NOSYNC ||
-                   (view.in_policy.kind == CUSYNC_POLICY_CONV2DTILESYNC && view.prod_grid.x == 1)) &&
-                  std::getenv("CUSYNC_CONV_GENERAL") == nullptr;
+  const bool slab_ok = d.c == 64 && d.k == 64 && rows * (d.w + 2) <= kBlockM && d.w + 2 <= 256 &&
+                       (view.in_policy.kind == CUSYNC_POLICY_NOSYNC ||
+                        (view.in_policy.kind == CUSYNC_POLICY_CONV2DTILESYNC && view.prod_grid.x == 1));
+  if (rc == CUSYNC_SUCCESS && (d.kernel < 0 || d.kernel > 2)) rc = CUSYNC_ERROR_INVALID_ARGUMENT;
+  if (rc == CUSYNC_SUCCESS && d.kernel == 2 && !slab_ok) rc = CUSYNC_ERROR_UNSUPPORTED;
+  pl->conv_slab = rc == CUSYNC_SUCCESS && slab_ok && d.kernel != 1;
   if (rc == CUSYNC_SUCCESS) {
     bool ok = (pl->conv_slab ? make_map_nhwc(&pl->tmA, d.x, d.n, d.h, d.w, d.c, static_cast<uint32_t>(rows + 2),
                                              static_cast<uint32_t>(d.w + 2))

@@ -303,6 +303,9 @@ typedef struct cusync_conv2d_desc {
   const void* x; const void* filter; void* y;
   int32_t epilogue;                /* CUSYNC_EPILOGUE_NONE or CUSYNC_EPILOGUE_RELU */
   int32_t max_ctas;
+  int32_t kernel;                  /* 0 = choose; 1 = the general implicit-GEMM kernel; 2 = the slab kernel (c = k = 64,
+                                      resident filter, one input slab per tile), CUSYNC_ERROR_UNSUPPORTED where it
+                                      does not apply */
   cusync_stage_t* stage;           /* NULL = no tile synchronisation */
 } cusync_conv2d_desc_t;
 

@@ -43,6 +43,36 @@ def test_conv3x3_matches_oracle(n, h, w, c, k, relu):
     conv.destroy()
 
 
+@pytest.mark.parametrize("kernel", [cs.Conv2dFprop.GENERAL, cs.Conv2dFprop.SLAB])
+@pytest.mark.parametrize("n,h,w", [(1, 56, 56), (2, 4, 56), (3, 28, 28), (2, 6, 62)])
+def test_both_conv_kernels_on_the_64_channel_layer(kernel, n, h, w):
+    # the 64 -> 64 channel layer runs on the slab kernel by default; the general implicit-GEMM kernel must give the
+    # same answer up to the oracle's tolerance (the two accumulate the taps in different orders)
+    x, f = _inputs(n, h, w, 64, 64, 3)
+    prob = cs.Conv2dProblemSize(n, h, w, 64, 64)
+    y = torch.full((n, h, w, 64), float("nan"), device="cuda", dtype=torch.half)
+    conv = cs.Conv2dFprop()
+    assert conv.initialize(None, prob, x, f, y, L.EPILOGUE_RELU, kernel=kernel) == L.SUCCESS
+    for _ in range(2):
+        y.fill_(float("nan"))
+        assert conv.run(torch.cuda.current_stream()) == L.SUCCESS
+        torch.cuda.synchronize()
+        ref = o.conv2d_3x3_nhwc_f16(x.cpu().numpy(), f.cpu().numpy(), True)
+        assert o.max_rel_err(y.cpu().numpy(), ref) <= TOL
+    conv.destroy()
+
+
+def test_slab_kernel_is_refused_where_it_does_not_apply():
+    x, f = _inputs(1, 8, 32, 128, 64, 4)
+    y = torch.empty((1, 8, 32, 64), device="cuda", dtype=torch.half)
+    conv = cs.Conv2dFprop()
+    prob = cs.Conv2dProblemSize(1, 8, 32, 128, 64)          # two channel chunks
+    assert conv.initialize(None, prob, x, f, y, kernel=cs.Conv2dFprop.SLAB) == L.ERROR_UNSUPPORTED
+    assert conv.initialize(None, prob, x, f, y, kernel=7) == L.ERROR_INVALID_ARGUMENT
+    assert conv.initialize(None, prob, x, f, y) == L.SUCCESS
+    conv.destroy()
+
+
 def test_conv_refuses_unsupported_shapes():
     x, f = _inputs(1, 56, 56, 64, 64, 2)
     y = torch.empty((1, 56, 56, 64), device="cuda", dtype=torch.half)
