@@ -473,14 +473,13 @@ def main():
             wo = (torch.randn((1536, 12288), generator=g, device=dev) * 0.02).half()
             kc = torch.randn((b, seq, 12, 128), generator=g, device=dev).half()
             vc = torch.randn((b, seq, 12, 128), generator=g, device=dev).half()
-            blk = AttentionBlock(xin, wqkv, kc, vc, wo, 12)
-            ref = AttentionBlock(xin, wqkv, kc, vc, wo, 12, synced=False)
+            blk = AttentionBlock(xin, wqkv, kc, vc, wo, 12)     # cusync_attn_block_*: the attention.cu flow in C
 
             def c_step():
                 ps.wait_stream(s3); blk.run((ps, cs, s3)); cs.wait_stream(s3)
-            r = ab(c_step, lambda: ref.run((cs,)))
+            r = ab(c_step, lambda: blk.run_stream_ordered(cs))
             r.update({"batch": b, "context": seq, "config": blk.config})
-            rows.append(r); blk.destroy(); ref.destroy()
+            rows.append(r); blk.destroy()
         extras["gpt3_attention_block"] = rows
     clocks = sampler.stop() if rank == 0 else None
 

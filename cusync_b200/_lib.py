@@ -83,6 +83,13 @@ class AttnDesc(C.Structure):
                 ("out", C.c_void_p), ("ld_out", C.c_int64), ("kv_splits", C.c_int32), ("stage", C.c_void_p)]
 
 
+class AttnBlockDesc(C.Structure):
+    _fields_ = [("batch", C.c_int32), ("seq", C.c_int32), ("hidden", C.c_int32), ("heads", C.c_int32),
+                ("out_features", C.c_int32), ("model_hidden", C.c_int32), ("kv_splits", C.c_int32),
+                ("x", C.c_void_p), ("w_qkv", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p),
+                ("w_o", C.c_void_p), ("qkv", C.c_void_p), ("attn_out", C.c_void_p), ("y", C.c_void_p)]
+
+
 class MlpDesc(C.Structure):
     _fields_ = [("model", C.c_int32), ("batch", C.c_int32), ("hidden", C.c_int32), ("ffn", C.c_int32),
                 ("policy", C.c_int32), ("opts", C.c_int32), ("tile_n1", C.c_int32), ("tile_n2", C.c_int32),
@@ -144,6 +151,12 @@ SIGNATURES = {
     "cusync_attn_plan_destroy": (_i, [_vp]),
     "cusync_attn_plan_splits": (_i, [_vp]),
     "cusync_attn_run": (_i, [_vp, _vp]),
+    "cusync_attn_block_create": (_i, [C.POINTER(_vp), C.POINTER(AttnBlockDesc)]),
+    "cusync_attn_block_destroy": (_i, [_vp]),
+    "cusync_attn_block_run_stream_ordered": (_i, [_vp, _vp]),
+    "cusync_attn_block_run_cusync": (_i, [_vp, C.POINTER(_vp)]),
+    "cusync_attn_block_stage": (_vp, [_vp, _i]),
+    "cusync_attn_block_config": (_i, [_vp, C.POINTER(C.c_int32)]),
     "cusync_mlp_create": (_i, [C.POINTER(_vp), C.POINTER(MlpDesc)]),
     "cusync_mlp_destroy": (_i, [_vp]),
     "cusync_mlp_run_stream_ordered": (_i, [_vp, _vp]),

@@ -383,6 +383,34 @@ CUSYNC_API int cusync_attn_plan_destroy(cusync_attn_plan_t* plan);
 CUSYNC_API int cusync_attn_plan_splits(const cusync_attn_plan_t* plan);
 CUSYNC_API int cusync_attn_run(cusync_attn_plan_t* plan, cusync_stream_t stream);
 
+/* The whole attention block of one tensor-parallel shard, the workload of src/ml-bench/transformer/attention.cu:
+ * qkv = x * w_qkv; attn_out = attention(qkv, caches); y = attn_out * w_o.  x[batch, hidden], w_qkv[hidden, 3 * heads
+ * * 128], w_o[heads * 128, out_features], row-major fp16 on the device, caller-owned, as are the intermediates
+ * qkv[batch, 3 * heads * 128] and attn_out[batch, heads * 128].  model_hidden is the H of ConsecutiveSync<H, ...>
+ * (attention.cu:105-110): the un-sharded hidden size. */
+typedef struct cusync_attn_block_desc {
+  int32_t batch, seq, hidden, heads, out_features, model_hidden;
+  int32_t kv_splits;               /* 0 = choose */
+  const void* x; const void* w_qkv; const void* k_cache; const void* v_cache; const void* w_o;
+  void* qkv; void* attn_out; void* y;
+} cusync_attn_block_desc_t;
+
+typedef struct cusync_attn_block cusync_attn_block_t;
+
+/* Stage construction, both setProducerConsumerPair calls and the three kernels' initialisation
+ * (attention.cu:706-790), for the synchronised chain and for the same kernels without synchronisation. */
+CUSYNC_API int cusync_attn_block_create(cusync_attn_block_t** out, const cusync_attn_block_desc_t* desc);
+CUSYNC_API int cusync_attn_block_destroy(cusync_attn_block_t* block);
+/* The three kernels back to back on one stream (the reference's baseline loop). */
+CUSYNC_API int cusync_attn_block_run_stream_ordered(cusync_attn_block_t* block, cusync_stream_t stream);
+/* runAttentionCuSync, one iteration (attention.cu:792-833): stage i on streams[i], a wait kernel before each
+ * dependent stage, incrementIter on all three afterwards.  streams: [3]. */
+CUSYNC_API int cusync_attn_block_run_cusync(cusync_attn_block_t* block, const cusync_stream_t* streams);
+/* Stage handles (0 = QKV projection, 1 = attention, 2 = output projection) for inspection. */
+CUSYNC_API cusync_stage_t* cusync_attn_block_stage(cusync_attn_block_t* block, int which);
+/* Configuration in use: out[0..4] = tile_n of the two GEMMs, their K slices, key-range splits of the attention. */
+CUSYNC_API int cusync_attn_block_config(const cusync_attn_block_t* block, int32_t* out5);
+
 /* ---- MLP driver ---------------------------------------------------------- */
 
 enum { CUSYNC_MLP_GPT3 = 0, CUSYNC_MLP_LLAMA = 1 };

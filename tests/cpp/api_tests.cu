@@ -13,6 +13,7 @@
 #include <vector>
 
 #include <cusync/cusync.h>
+#include <cusync/conv.h>
 #include <cusync/gemm.h>
 
 #define API extern "C" __attribute__((visibility("default")))
@@ -249,6 +250,66 @@ API int api_gemm_chain(int policy, int M, int N, int K, const void* hA, const vo
   using Sync = TileSync<TransposeXYOrder, 128, 128>;
   return runChain<Sync, CuStage<TransposeXYOrder, NoSync, Sync, NoAtomicAdd>, CuStage<TransposeXYOrder, Sync, NoSync>>(
       Sync(), M, N, K, hA, hB, hD, hC, hE, iters, sems_out);
+}
+
+// ---------------------------------------------------------------------------
+// Chain of two 3x3 convolutions through cusync::b200::Conv2dFprop, the reference's call pattern
+// (ml-bench/volta_conv2d/resnet.cu:107-116, 659-700): TileSync out of the first, Conv2DTileSync into the second,
+// ReLU after each.  Host NHWC / KRSC fp16 in, host fp16 out.  sems_out[N * H / rows].
+// ---------------------------------------------------------------------------
+API int api_conv_chain(int N, int H, int W, const void* hX, const void* hF1, const void* hF2, void* hY1, void* hY2,
+                       int iters, uint32_t* sems_out) {
+  using namespace cusync::b200;
+  constexpr int C = 64, TileM = 112;            // 56-wide images: two rows per tile
+  if (W != 56) return 64;
+  using Sync1 = TileSync<TransposeXYOrder, TileM, 64>;
+  using Sync2 = Conv2DTileSync<TransposeXYOrder, 3, 3, TileM, 64>;
+  using Prod = CuStage<TransposeXYOrder, NoSync, Sync1>;
+  using Cons = CuStage<TransposeXYOrder, Sync2, NoSync>;
+  using Conv1 = Conv2dFprop<Prod, EpilogueRelu>;
+  using Conv2 = Conv2dFprop<Cons, EpilogueRelu>;
+  const size_t act = (size_t)N * H * W * C * 2, filt = (size_t)C * 9 * C * 2;
+  half *X, *F1, *F2, *Y1, *Y2;
+  CUDA_CHECK(cudaMalloc(&X, act)); CUDA_CHECK(cudaMalloc(&Y1, act)); CUDA_CHECK(cudaMalloc(&Y2, act));
+  CUDA_CHECK(cudaMalloc(&F1, filt)); CUDA_CHECK(cudaMalloc(&F2, filt));
+  CUDA_CHECK(cudaMemcpy(X, hX, act, cudaMemcpyHostToDevice));
+  CUDA_CHECK(cudaMemcpy(F1, hF1, filt, cudaMemcpyHostToDevice));
+  CUDA_CHECK(cudaMemcpy(F2, hF2, filt, cudaMemcpyHostToDevice));
+  Conv2dProblemSize problem(N, H, W, C, C);
+  int rc = 0;
+  if (conv2dTileM(problem) != TileM) rc |= 1;
+  dim3 grid = conv2dGridShape(problem);
+  Prod prod(grid, {1, 1, 1}, NoSync(), Sync1());
+  Cons cons(grid, {1, 1, 1}, Sync2(), NoSync());
+  if (CuSync::setProducerConsumerPair(prod, cons) != CuSyncSuccess) rc |= 1;
+  typename Conv1::Arguments a1{prod, problem, X, F1, Y1, Y1, {1.f, 0.f}};
+  typename Conv2::Arguments a2{cons, problem, Y1, F2, Y2, Y2, {1.f, 0.f}};
+  Conv1 c1; Conv2 c2;
+  if (c1.can_implement(a1) != Status::kSuccess || c1.initialize(a1) != Status::kSuccess) rc |= 2;
+  if (c2.can_implement(a2) != Status::kSuccess || c2.initialize(a2) != Status::kSuccess) rc |= 4;
+  cudaStream_t ps, cs;
+  int lo, hi;
+  CUDA_CHECK(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+  CUDA_CHECK(cudaStreamCreateWithPriority(&ps, cudaStreamNonBlocking, hi));
+  CUDA_CHECK(cudaStreamCreateWithPriority(&cs, cudaStreamNonBlocking, lo));
+  for (int it = 0; it < iters && rc == 0; it++) {
+    CUDA_CHECK(cudaMemset(Y1, 0xff, act)); CUDA_CHECK(cudaMemset(Y2, 0xff, act));   // NaN poison
+    CUDA_CHECK(cudaDeviceSynchronize());
+    if (c1(ps) != Status::kSuccess) rc |= 8;
+    prod.invokeWaitKernel(cs);
+    if (c2(cs) != Status::kSuccess) rc |= 16;
+    CUDA_CHECK(cudaDeviceSynchronize());
+    prod.incrementIter(); cons.incrementIter();
+    c1.params_.custage.incrementIter(); c2.params_.custage.incrementIter();
+  }
+  CUDA_CHECK(cudaMemcpy(hY1, Y1, act, cudaMemcpyDeviceToHost));
+  CUDA_CHECK(cudaMemcpy(hY2, Y2, act, cudaMemcpyDeviceToHost));
+  if (sems_out) cusync_stage_read_semaphores(prod.handle(), sems_out, grid.x * grid.y);
+  if (prod.status().code || cons.status().code) rc |= 32;
+  c1.destroy(); c2.destroy(); prod.destroy(); cons.destroy();
+  cudaFree(X); cudaFree(F1); cudaFree(F2); cudaFree(Y1); cudaFree(Y2);
+  cudaStreamDestroy(ps); cudaStreamDestroy(cs);
+  return rc;
 }
 
 // ---------------------------------------------------------------------------

@@ -21,6 +21,7 @@ def api():
     so.api_simple_test.argtypes = [C.c_int, C.c_int, C.c_int]
     so.api_two_matmuls.argtypes = [C.c_int, C.c_float, C.c_float, C.c_void_p, C.c_void_p, C.c_int]
     so.api_gemm_chain.argtypes = [C.c_int] * 4 + [C.c_void_p] * 5 + [C.c_int, C.c_void_p]
+    so.api_conv_chain.argtypes = [C.c_int] * 3 + [C.c_void_p] * 5 + [C.c_int, C.c_void_p]
     so.api_custom_policy_and_order.argtypes = [C.c_int, C.c_void_p, C.c_void_p]
     so.api_wait_times_out.argtypes = [C.POINTER(L.Status), C.POINTER(C.c_float)]
     return so
@@ -69,6 +70,25 @@ def test_gemm_chain_through_the_cpp_handle(api, policy):
         assert list(sems[:2]) == [8 * iters] * 2 and (sems[2:] == 0).all()
     else:             # TileSync + NoAtomicAdd: every semaphore holds postValue * iter
         assert (sems == iters).all()
+
+
+def test_conv_chain_through_the_cpp_handle(api):
+    # resnet.cu's call pattern on <cusync/conv.h>: Conv2dFprop<CuStage<..., TileSync>> -> Conv2dFprop<CuStage<Conv2DTileSync, ...>>
+    N, H, W, Cc = 2, 56, 56, 64
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal((N, H, W, Cc)).astype(np.float16)
+    f1 = (rng.standard_normal((Cc, 3, 3, Cc)) * (2.0 / 576) ** 0.5).astype(np.float16)
+    f2 = (rng.standard_normal((Cc, 3, 3, Cc)) * (2.0 / 576) ** 0.5).astype(np.float16)
+    y1 = np.zeros_like(x); y2 = np.zeros_like(x)
+    tiles = N * H // 2
+    sems = np.zeros(tiles, np.uint32)
+    p = lambda a: a.ctypes.data_as(C.c_void_p)
+    iters = 2
+    assert api.api_conv_chain(N, H, W, p(x), p(f1), p(f2), p(y1), p(y2), iters, p(sems)) == 0
+    r1 = o.conv2d_3x3_nhwc_f16(x, f1, True)
+    assert o.max_rel_err(y1, r1) <= 1e-2
+    assert o.max_rel_err(y2, o.conv2d_3x3_nhwc_f16(y1, f2, True)) <= 1e-2
+    assert (sems == iters).all()
 
 
 def test_user_written_policy_and_tile_order(api):
