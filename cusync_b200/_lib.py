@@ -96,7 +96,7 @@ class MlpDesc(C.Structure):
                 ("split_k1", C.c_int32), ("split_k2", C.c_int32), ("max_ctas", C.c_int32), ("cta_pair", C.c_int32), ("group_rows2", C.c_int32),
                 ("tail_split_sync1", C.c_int32), ("tail_split_sync2", C.c_int32),
                 ("tail_split_plain1", C.c_int32), ("tail_split_plain2", C.c_int32), ("group_rows1", C.c_int32),
-                ("post_rows", C.c_int32),
+                ("x_rows", C.c_int32), ("post_rows", C.c_int32),
                 ("x", C.c_void_p), ("w1", C.c_void_p), ("v", C.c_void_p), ("w2", C.c_void_p),
                 ("h", C.c_void_p), ("y", C.c_void_p)]
 
@@ -119,6 +119,8 @@ SIGNATURES = {
     "cusync_stage_note_launch": (_i, [_vp, _u32]),
     "cusync_wait_kernel": (_i, [_vp, _u32, _vp, _vp, _u64]),
     "cusync_wait_kernel_range": (_i, [_vp, _u32, _u32, _vp, _vp, _u64]),
+    "cusync_stream_wait_values": (_i, [_vp, _u32, _u32, _vp]),
+    "cusync_stream_write_values": (_i, [_vp, _u32, _u32, _vp]),
     "cusync_stage_read_tile_order": (_i, [_vp, _vp, _u32]),
     "cusync_stage_read_semaphores": (_i, [_vp, _vp, _u32]),
     "cusync_stage_read_status": (_i, [_vp, C.POINTER(Status)]),
@@ -168,6 +170,7 @@ SIGNATURES = {
     "cusync_mlp_config": (_i, [_vp, C.POINTER(C.c_int32)]),
     "cusync_mlp_tail_splits": (_i, [_vp, C.POINTER(C.c_int32)]),
     "cusync_mlp_wait_rows": (_i, [_vp, _u32, _u32, _vp]),
+    "cusync_mlp_post_x_rows": (_i, [_vp, _u32, _u32, _vp]),
     "cusync_b200_version": (C.c_char_p, []),
     "cusync_b200_sm_count": (_i, []),
 }

@@ -12,6 +12,7 @@ struct cusync_mlp {
   cusync_mlp_desc_t desc;
   int tile_n1, tile_n2;
   int split_k1, split_k2;
+  cusync_stage_t* input;        // x_rows: producer-only stage standing for whatever brings X, posted by the caller
   cusync_stage_t* prod;
   cusync_stage_t* cons;
   cusync_gemm_plan_t* sync1;    // producer GEMM with its stage
@@ -56,6 +57,7 @@ void destroy_all(cusync_mlp* m) {
   if (m->sync2) cusync_gemm_plan_destroy(m->sync2);
   if (m->plain1) cusync_gemm_plan_destroy(m->plain1);
   if (m->plain2) cusync_gemm_plan_destroy(m->plain2);
+  if (m->input) cusync_stage_destroy(m->input);
   if (m->prod) cusync_stage_destroy(m->prod);
   if (m->cons) cusync_stage_destroy(m->cons);
   if (m->plain_stage1) cusync_stage_destroy(m->plain_stage1);
@@ -111,7 +113,18 @@ int cusync_mlp_create(cusync_mlp_t** out, const cusync_mlp_desc_t* desc) {
   if (d.policy == CUSYNC_POLICY_ROWSYNC) opts &= ~CUSYNC_OPT_NO_ATOMIC_ADD;
   cusync_dim3_t ts = {1, 1, 1};
   const int order1 = d.group_rows1 > 1 ? CUSYNC_ORDER_GROUPED(d.group_rows1) : CUSYNC_ORDER_TRANSPOSE_XY;
-  int rc = cusync_stage_create(&m->prod, grid1, ts, order1, &none, &sync, opts);
+  // x_rows: the first GEMM is a consumer as well, of a stage with one tile per 128 rows of X that the caller posts
+  cusync_policy_t rows_in = none;
+  int rc = CUSYNC_SUCCESS;
+  if (d.x_rows) {
+    rows_in.kind = CUSYNC_POLICY_ROWSYNC; rows_in.order = CUSYNC_ORDER_TRANSPOSE_XY;
+    rows_in.tile_m = 128; rows_in.tile_n = 1; rows_in.wait_value = 1; rows_in.post_value = 1;
+    const cusync_dim3_t grid0 = {1, tiles_m, 1};
+    rc = cusync_stage_create(&m->input, grid0, ts, CUSYNC_ORDER_TRANSPOSE_XY, &none, &rows_in, CUSYNC_OPT_NONE);
+  }
+  if (rc == CUSYNC_SUCCESS)
+    rc = cusync_stage_create(&m->prod, grid1, ts, order1, &rows_in, &sync, opts & ~(d.x_rows ? CUSYNC_OPT_NO_ATOMIC_ADD : 0));
+  if (rc == CUSYNC_SUCCESS && d.x_rows) rc = cusync_stage_link(m->input, m->prod);
   // Consumer tile order: left to choose, batches of at least 8 row tiles take their tiles in groups of 4 rows
   // (row fastest inside a group), which re-reads W2 once per group instead of once per row; measured 4 % faster
   // at B = 1024 and 2048, neutral below.
@@ -164,6 +177,7 @@ int cusync_mlp_run_cusync(cusync_mlp_t* m, cusync_stream_t producer_stream, cusy
   int rc = cusync_gemm_run(m->sync1, producer_stream);
   if (rc == CUSYNC_SUCCESS) rc = cusync_stage_invoke_wait_kernel(m->prod, consumer_stream);
   if (rc == CUSYNC_SUCCESS) rc = cusync_gemm_run(m->sync2, consumer_stream);
+  if (m->input) cusync_stage_increment_iter(m->input);
   cusync_stage_increment_iter(m->prod);
   cusync_stage_increment_iter(m->cons);
   return rc;
@@ -205,6 +219,16 @@ int cusync_mlp_config(const cusync_mlp_t* m, int32_t* out6) {
   return CUSYNC_SUCCESS;
 }
 
+int cusync_mlp_post_x_rows(cusync_mlp_t* m, uint32_t first_tile, uint32_t num_tiles, cusync_stream_t stream) {
+  if (!m) return CUSYNC_ERROR_NOT_INITIALIZED;
+  if (!m->input) return CUSYNC_ERROR_NOT_PRODUCER;
+  cusync_stage_view_t v;
+  cusync_stage_get_view(m->input, &v);
+  if (num_tiles == 0 || first_tile + num_tiles > v.grid.y) return CUSYNC_ERROR_INVALID_ARGUMENT;
+  // the value of the coming run: run r waits for its row semaphores to reach r
+  return cusync_stream_write_values(v.sems_post + first_tile, num_tiles, v.iter, stream);
+}
+
 int cusync_mlp_wait_rows(cusync_mlp_t* m, uint32_t first_tile, uint32_t num_tiles, cusync_stream_t stream) {
   if (!m) return CUSYNC_ERROR_NOT_INITIALIZED;
   if (!m->desc.post_rows) return CUSYNC_ERROR_NOT_PRODUCER;
@@ -214,7 +238,10 @@ int cusync_mlp_wait_rows(cusync_mlp_t* m, uint32_t first_tile, uint32_t num_tile
   // run_cusync has already incremented the iteration: the run to wait for is the previous one.  With split-K
   // only the finishing slice of a tile posts, so a row is complete after grid.x posts per run.
   const uint32_t runs = v.iter - 1u;
-  return cusync_wait_kernel_range(v.sems_post + first_tile, num_tiles, runs * v.grid.x, stream, v.status, v.timeout_ns);
+  int rc = cusync_stream_wait_values(v.sems_post + first_tile, num_tiles, runs * v.grid.x, stream);
+  if (rc == CUSYNC_ERROR_UNSUPPORTED)   // no stream memory operations: a wait kernel, which needs a free SM
+    rc = cusync_wait_kernel_range(v.sems_post + first_tile, num_tiles, runs * v.grid.x, stream, v.status, v.timeout_ns);
+  return rc;
 }
 
 int cusync_mlp_tail_splits(const cusync_mlp_t* m, int32_t* out4) {

@@ -5,6 +5,7 @@
 // Replaces, for sm_100a: CuStage's constructor and buildScheduleBuffer
 // (src/include/cusync/cusync.h:125-198), CuSync::setProducerConsumerPair
 // (cusync.h:287-299) and waitKernel / invokeWaitKernel (src/cusync.cu:11-25).
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include <cstdio>
@@ -44,6 +45,22 @@ __global__ void waitRangeKernel(const uint32_t* sems, uint32_t count, uint32_t v
     if (!cusync::spinUntilAtLeast(sems + i, value, timeout_ns, &seen))
       cusync::recordTimeout(status, 3u, i, 0, 0, i, seen, value);
   }
+}
+
+// Stream memory operations of the driver (cuStreamWaitValue32 / cuStreamWriteValue32): a stream waits for, or
+// writes, a 32-bit word without a kernel.  A kernel would need room on an SM, and the persistent GEMM blocks leave
+// none: a one-thread kernel enqueued while they are resident starts only when one of them retires.
+typedef CUresult (*StreamValueFn)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
+
+StreamValueFn stream_value_fn(const char* name) {
+  void* sym = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint(name, &sym, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess ||
+      sym == nullptr) {
+    (void)cudaGetLastError();
+    return nullptr;
+  }
+  return reinterpret_cast<StreamValueFn>(sym);
 }
 
 bool policy_ok(const cusync_policy_t* p) {
@@ -219,6 +236,28 @@ int cusync_wait_kernel_range(uint32_t* semaphores, uint32_t count, uint32_t give
   const uint32_t threads = count < 256u ? ((count + 31u) / 32u) * 32u : 256u;
   waitRangeKernel<<<1, threads, 0, (cudaStream_t)stream>>>(semaphores, count, given_value, status, timeout_ns);
   return cudaGetLastError() == cudaSuccess ? CUSYNC_SUCCESS : CUSYNC_ERROR_CUDA;
+}
+
+int cusync_stream_wait_values(uint32_t* semaphores, uint32_t count, uint32_t value, cusync_stream_t stream) {
+  if (semaphores == nullptr || count == 0) return CUSYNC_ERROR_NOT_INITIALIZED;
+  static StreamValueFn fn = stream_value_fn("cuStreamWaitValue32");
+  if (!fn) return CUSYNC_ERROR_UNSUPPORTED;
+  for (uint32_t i = 0; i < count; i++)
+    if (fn(reinterpret_cast<CUstream>(stream), reinterpret_cast<CUdeviceptr>(semaphores + i), value,
+           CU_STREAM_WAIT_VALUE_GEQ) != CUDA_SUCCESS)
+      return CUSYNC_ERROR_CUDA;
+  return CUSYNC_SUCCESS;
+}
+
+int cusync_stream_write_values(uint32_t* semaphores, uint32_t count, uint32_t value, cusync_stream_t stream) {
+  if (semaphores == nullptr || count == 0) return CUSYNC_ERROR_NOT_INITIALIZED;
+  static StreamValueFn fn = stream_value_fn("cuStreamWriteValue32");
+  if (!fn) return CUSYNC_ERROR_UNSUPPORTED;
+  for (uint32_t i = 0; i < count; i++)
+    if (fn(reinterpret_cast<CUstream>(stream), reinterpret_cast<CUdeviceptr>(semaphores + i), value,
+           CU_STREAM_WRITE_VALUE_DEFAULT) != CUDA_SUCCESS)
+      return CUSYNC_ERROR_CUDA;
+  return CUSYNC_SUCCESS;
 }
 
 int cusync_stage_invoke_wait_kernel(cusync_stage_t* s, cusync_stream_t stream) {

@@ -24,7 +24,7 @@ class MLPShard:
     """x[B,H] -> y[B,H] through W1 (and V) [H,F] and W2 [F,H]; fp16, fp32 accumulate."""
 
     def __init__(self, model, batch, x, w1, w2, v=None, policy="rowsync", opts=0, tile_n1=0, tile_n2=0, max_ctas=0,
-                 group_rows2=0, cta_pair=0, split_k1=0, split_k2=0, tail_split=(0, 0, 0, 0), post_rows=False, group_rows1=0):
+                 group_rows2=0, cta_pair=0, split_k1=0, split_k2=0, tail_split=(0, 0, 0, 0), post_rows=False, group_rows1=0, x_rows=False):
         import torch
         self.model = L.MLP_GPT3 if model == "gpt3" else L.MLP_LLAMA
         self.batch, self.hidden, self.ffn = batch, w1.shape[0], w1.shape[1]
@@ -33,7 +33,7 @@ class MLPShard:
         self.h = torch.empty((batch, self.ffn), device=x.device, dtype=torch.half)
         self.y = torch.empty((batch, self.hidden), device=x.device, dtype=torch.half)
         d = L.MlpDesc(self.model, batch, self.hidden, self.ffn, POLICIES[policy], opts, tile_n1, tile_n2, split_k1,
-                      split_k2, max_ctas, cta_pair, group_rows2, tail_split[0], tail_split[1], tail_split[2], tail_split[3], group_rows1, 1 if post_rows else 0,
+                      split_k2, max_ctas, cta_pair, group_rows2, tail_split[0], tail_split[1], tail_split[2], tail_split[3], group_rows1, 1 if x_rows else 0, 1 if post_rows else 0,
                       x.data_ptr(), w1.data_ptr(), v.data_ptr() if v is not None else None, w2.data_ptr(),
                       self.h.data_ptr(), self.y.data_ptr())
         self._h = C.c_void_p()
@@ -51,6 +51,11 @@ class MLPShard:
     def run_cusync(self, producer_stream, consumer_stream):
         L.check(L.lib().cusync_mlp_run_cusync(self._h, _stream_ptr(producer_stream), _stream_ptr(consumer_stream)),
                 "run_cusync")
+
+    def post_x_rows(self, first_tile, num_tiles, stream):
+        """x_rows=True: the 128-row tiles [first_tile, first_tile + num_tiles) of x are complete, for the NEXT
+        run_cusync, once what `stream` holds so far has run; call for every tile before each run_cusync."""
+        L.check(L.lib().cusync_mlp_post_x_rows(self._h, first_tile, num_tiles, _stream_ptr(stream)), "post_x_rows")
 
     def wait_rows(self, first_tile, num_tiles, stream):
         """After run_cusync (post_rows=True): work enqueued on `stream` afterwards sees the 128-row tiles

@@ -185,6 +185,17 @@ CUSYNC_API int cusync_wait_kernel(uint32_t* semaphore, uint32_t given_value, cus
 CUSYNC_API int cusync_wait_kernel_range(uint32_t* semaphores, uint32_t count, uint32_t given_value,
                                         cusync_stream_t stream, uint32_t* status, uint64_t timeout_ns);
 
+/* The same wait without a kernel (the driver's stream memory operations, cuStreamWaitValue32 with GEQ): `stream`
+ * holds until each of `count` semaphores has reached `value`.  A kernel needs room on an SM, and while the
+ * persistent GEMM blocks are resident there is none, so a wait kernel enqueued behind them starts only when
+ * they retire; this form does not depend on that.  Unbounded: no timeout record.  No counterpart. */
+CUSYNC_API int cusync_stream_wait_values(uint32_t* semaphores, uint32_t count, uint32_t value, cusync_stream_t stream);
+/* The posting counterpart (cuStreamWriteValue32): `stream` stores `value` into each of `count` semaphores once
+ * everything enqueued on it before has completed - the way something that is not a kernel of this library (a
+ * host-to-device copy, another library's kernel) acts as a producer stage.  A store, not an add: one poster per
+ * semaphore, values that only grow (the NoAtomicAdd protocol, policies of mlp.cu:9-14).  No counterpart. */
+CUSYNC_API int cusync_stream_write_values(uint32_t* semaphores, uint32_t count, uint32_t value, cusync_stream_t stream);
+
 /* Test access, the role of the reference's friend class CuSyncTest
  * (tests/cusync-test.h:8-44): copy the schedule buffer / the producer's
  * semaphores / the timeout record to the host (synchronous). */
@@ -434,6 +445,9 @@ typedef struct cusync_mlp_desc {
   int32_t tail_split_sync1, tail_split_sync2;    /* cusync_gemm_desc_t.tail_split of the two synchronised GEMMs ... */
   int32_t tail_split_plain1, tail_split_plain2;  /* ... and of the two stream-ordered ones: 0 = choose, 1 = none */
   int32_t group_rows1;           /* the producer's tile order: 0 or 1 = plain, n > 1 = CUSYNC_ORDER_GROUPED(n) */
+  int32_t x_rows;                /* 1: X arrives in row blocks while the layer runs (e.g. host-to-device copies on
+                                    another stream): the first GEMM of run_cusync waits, per 128-row tile, on a RowSync
+                                    semaphore that the caller posts with cusync_mlp_post_x_rows once per run */
   int32_t post_rows;             /* 1: the second GEMM of run_cusync is a producer too: it posts RowSync semaphores, one
                                     per 128-row tile of Y, counting its column tiles, so that whatever consumes Y (the
                                     all-reduce of a tensor-parallel layer) can start row block by row block
@@ -467,9 +481,15 @@ CUSYNC_API cusync_stage_t* cusync_mlp_stage(cusync_mlp_t* mlp, int which);
 CUSYNC_API int cusync_mlp_set_trace(cusync_mlp_t* mlp, void* trace1, uint32_t capacity1, void* trace2, uint32_t capacity2);
 /* Configuration in use: out[0..5] = tile_n1, tile_n2, ctas1, ctas2, split_k1, split_k2. */
 CUSYNC_API int cusync_mlp_config(const cusync_mlp_t* mlp, int32_t* out6);
-/* With desc.post_rows: enqueues on `stream` a wait for the 128-row tiles [first_tile, first_tile + num_tiles) of Y
- * as written by the most recent run_cusync (call it after that run_cusync).  Work enqueued on `stream` afterwards
- * sees those rows complete. */
+/* With desc.x_rows: enqueues on `stream` the post (a stream memory operation, no kernel) for the 128-row tiles
+ * [first_tile, first_tile + num_tiles) of X for the NEXT run_cusync; what was enqueued on `stream` before (the copy
+ * that brings those rows) is complete when the first GEMM sees the post.  Call it for every row tile before each
+ * run_cusync; the stream may well execute it after the GEMM has started.  The copy itself must not need an SM
+ * either (a host-to-device cudaMemcpyAsync does not; a copy kernel might wait for the GEMM's blocks to retire). */
+CUSYNC_API int cusync_mlp_post_x_rows(cusync_mlp_t* mlp, uint32_t first_tile, uint32_t num_tiles, cusync_stream_t stream);
+/* With desc.post_rows: makes `stream` wait (a stream memory operation, no kernel) for the 128-row tiles
+ * [first_tile, first_tile + num_tiles) of Y as written by the most recent run_cusync (call it after that
+ * run_cusync).  Work enqueued on `stream` afterwards sees those rows complete. */
 CUSYNC_API int cusync_mlp_wait_rows(cusync_mlp_t* mlp, uint32_t first_tile, uint32_t num_tiles, cusync_stream_t stream);
 /* Tail splits in use: out[0..3] = synchronised GEMM 1, 2, stream-ordered GEMM 1, 2. */
 CUSYNC_API int cusync_mlp_tail_splits(const cusync_mlp_t* mlp, int32_t* out4);

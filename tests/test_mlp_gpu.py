@@ -109,3 +109,39 @@ def test_output_rows_can_be_consumed_block_by_block(batch, max_ctas):
     with pytest.raises(L.CuSyncError):
         s2.wait_rows(0, 1, side)
     s2.destroy(); s.destroy()
+
+
+@pytest.mark.parametrize("batch", [64, 600, 1024])
+def test_input_rows_can_arrive_while_the_layer_runs(batch):
+    # x_rows: the first GEMM waits per 128-row tile of X on a semaphore that the caller's stream writes behind the
+    # copy that brings those rows (stream memory operations: neither needs an SM).  The rows come from pinned host
+    # memory on a stream that first idles for a while, so the layer is running, on poisoned X, well before they
+    # land.  A tile multiplied too early would carry NaN.
+    dev = torch.device("cuda")
+    x, w1, w2, v = M.make_inputs("gpt3", batch, dev, seed=6)
+    x_host = x.cpu().pin_memory()
+    ref = M.MLPShard("gpt3", batch, x.clone(), w1, w2, v, policy="rowsync")
+    ref.run_stream_ordered(torch.cuda.current_stream()); torch.cuda.synchronize()
+    s = M.MLPShard("gpt3", batch, x, w1, w2, v, policy="rowsync", x_rows=True, post_rows=True)
+    ps, cs_, feed = torch.cuda.Stream(priority=-1), torch.cuda.Stream(), torch.cuda.Stream()
+    tiles = (batch + 127) // 128
+    for it in range(1, 4):
+        x.fill_(float("nan")); s.y.fill_(float("nan")); torch.cuda.synchronize()
+        with torch.cuda.stream(feed):
+            torch.cuda._sleep(1_000_000)            # about half a millisecond before the first row arrives
+        for first in reversed(range(tiles)) if it == 2 else range(tiles):   # any order will do
+            r0, r1 = first * 128, min(batch, (first + 1) * 128)
+            with torch.cuda.stream(feed):
+                x[r0:r1].copy_(x_host[r0:r1], non_blocking=True)
+            s.post_x_rows(first, 1, feed)
+        s.run_cusync(ps, cs_)
+        torch.cuda.synchronize()
+        assert s.status_codes() == (0, 0)
+        assert not torch.isnan(s.y.float()).any()
+        # (split-K batches add their slices in arrival order: equal up to fp32 rounding, not bit for bit)
+        assert torch.allclose(s.y.float(), ref.y.float(), rtol=1e-2, atol=1e-3)
+        if s.split_k1 == 1 and s.split_k2 == 1:
+            assert torch.equal(s.y, ref.y)
+    with pytest.raises(L.CuSyncError):
+        ref.post_x_rows(0, 1, feed)
+    s.destroy(); ref.destroy()
