@@ -274,8 +274,37 @@ cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
               const uint32_t idx = cusync::eval::tileIndex(st.in_policy, static_cast<uint32_t>(m_off),
                                                            static_cast<uint32_t>(k_off), st.prod_grid.x,
                                                            st.prod_grid.y);
+              // Probe first: the tile's own semaphore and the next producer tiles along K are read with
+              // independent relaxed loads (one memory round trip for all of them); only if the tile's own is
+              // not there yet does the thread go on to wait for it.  How far the finished prefix reaches is
+              // remembered, so later K-blocks skip the wait.  One fence makes the relaxed loads acquiring.
+              uint32_t vals[kLookahead];
+              uint32_t v_first = 0;
+              if (sync_stride) {
+                // TileSync / Conv2DTileSync number the producer tiles of a row with a constant step along K
+                // (both orders are affine in the column), so one more evaluation gives every later index
+                // without its integer divisions; the wrapping policies are evaluated one by one.
+                const bool affine = st.in_policy.kind == CUSYNC_POLICY_TILESYNC ||
+                                    st.in_policy.kind == CUSYNC_POLICY_CONV2DTILESYNC;
+                uint32_t step = 0;
+                if (affine && static_cast<uint32_t>(k_off) + sync_stride < static_cast<uint32_t>(p.k))
+                  step = cusync::eval::tileIndex(st.in_policy, static_cast<uint32_t>(m_off),
+                                                 static_cast<uint32_t>(k_off) + sync_stride, st.prod_grid.x,
+                                                 st.prod_grid.y) - idx;
+                v_first = cusync::loadRelaxed(st.sems_wait + idx);
+#pragma unroll
+                for (int j = 0; j < kLookahead; j++) {
+                  const uint32_t kk = static_cast<uint32_t>(k_off) + (j + 1) * sync_stride;
+                  vals[j] = kk < static_cast<uint32_t>(p.k)
+                                ? cusync::loadRelaxed(st.sems_wait + (affine ? idx + (j + 1) * step
+                                      : cusync::eval::tileIndex(st.in_policy, static_cast<uint32_t>(m_off), kk,
+                                                                st.prod_grid.x, st.prod_grid.y)))
+                                : 0u;
+                }
+              }
+              const bool probed_ready = sync_stride != 0 && v_first >= wait_target;
               uint32_t seen = 0;
-              if (!cusync::spinUntilAtLeast(st.sems_wait + idx, wait_target, st.timeout_ns, &seen)) {
+              if (!probed_ready && !cusync::spinUntilAtLeast(st.sems_wait + idx, wait_target, st.timeout_ns, &seen)) {
                 bars->abort = 1u;
                 cusync::recordTimeout(st.status, 1u, static_cast<uint32_t>(m_off), static_cast<uint32_t>(k_off), tz,
                                       idx, seen, wait_target);
@@ -283,22 +312,13 @@ cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                 break;
               }
               if (sync_stride) {
-                uint32_t vals[kLookahead];
-#pragma unroll
-                for (int j = 0; j < kLookahead; j++) {
-                  const uint32_t kk = static_cast<uint32_t>(k_off) + (j + 1) * sync_stride;
-                  vals[j] = kk < static_cast<uint32_t>(p.k)
-                                ? cusync::loadRelaxed(st.sems_wait + cusync::eval::tileIndex(st.in_policy,
-                                      static_cast<uint32_t>(m_off), kk, st.prod_grid.x, st.prod_grid.y))
-                                : 0u;
-                }
                 uint32_t ahead = 0;
 #pragma unroll
                 for (int j = 0; j < kLookahead; j++) {
                   if (ahead == static_cast<uint32_t>(j) && vals[j] >= wait_target) ahead++;
                 }
                 ready_end = static_cast<uint32_t>(k_off) + (ahead + 1) * sync_stride;
-                if (ahead) __threadfence();
+                if (ahead || probed_ready) cusync::fenceAcqRel();
               }
               fence_proxy_async();
             }

@@ -19,7 +19,7 @@ constexpr int kThreads = 384;
 constexpr int kEpilogueWarps = 8;    // two per TMEM lane quarter: keeps every scheduler fed during the epilogue
 constexpr int kSchedSlots = 8;
 constexpr int kEpilogueWarp0 = 4;
-constexpr int kLookahead = 8;       // semaphores probed ahead of a consumer wait
+constexpr int kLookahead = 32;      // semaphores probed ahead of a consumer wait (a whole row of producer tiles here)
 constexpr int kStoreCols = 64;      // columns per TMA store box (128 bytes)
 constexpr uint32_t kSmemLimit = 232448;  // 227 KB
 
