@@ -19,6 +19,7 @@ ERROR_NAMES = ["CuSyncErrorNotProducer", "CuSyncErrorNotConsumer", "CuSyncErrorN
                "CuSyncErrorExceedsStaticScratch"]
 
 OPT_NONE, OPT_NO_ATOMIC_ADD, OPT_AVOID_WAIT_KERNEL, OPT_AVOID_CUSTOM_ORDER, OPT_REORDER_TILE_LOADS = 0, 1, 2, 4, 8
+OPT_STREAM_WAIT = 16
 ORDER_IDENTITY, ORDER_TRANSPOSE_XY, ORDER_GROUPED_ROWS = 0, 1, 2
 
 

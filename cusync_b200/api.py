@@ -23,6 +23,7 @@ class Optimizations:
     AvoidWaitKernel = L.OPT_AVOID_WAIT_KERNEL
     AvoidCustomOrder = L.OPT_AVOID_CUSTOM_ORDER
     ReorderTileLoads = L.OPT_REORDER_TILE_LOADS
+    StreamWait = L.OPT_STREAM_WAIT          # addition: the wait before a dependent launch without a kernel
 
 
 class IdentityOrder:

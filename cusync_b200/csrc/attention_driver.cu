@@ -82,7 +82,8 @@ int cusync_attn_block_create(cusync_attn_block_t** out, const cusync_attn_block_
 
   int rc = CUSYNC_SUCCESS;
   for (int i = 0; i < 3 && rc == CUSYNC_SUCCESS; i++) {
-    rc = cusync_stage_create(&b->stages[i], grids[i], ts, orders[i], in[i], outp[i], CUSYNC_OPT_NONE);
+    // (the waits before the dependent stages are stream memory operations, not kernel launches)
+    rc = cusync_stage_create(&b->stages[i], grids[i], ts, orders[i], in[i], outp[i], CUSYNC_OPT_STREAM_WAIT);
     if (rc == CUSYNC_SUCCESS)
       rc = cusync_stage_create(&b->plain_stages[i], grids[i], ts, orders[i], &none, &none, CUSYNC_OPT_NONE);
   }

@@ -72,19 +72,24 @@ int cusync_conv_chain_create(cusync_conv_chain_t** out, const cusync_conv_chain_
 
   int sms = cusync_b200_sm_count();
   if (sms <= 0) sms = 148;
-  // Left to choose, small chains (at most two tiles per SM and convolution) share the device: each synchronised
-  // convolution gets sms / num_convs persistent blocks, so that every stage is resident from the start and the
-  // chain runs as a pipeline over the semaphores, with no wait kernels (the reference's AvoidWaitKernel case,
-  // cusync.h:61-62).  Larger chains give every convolution the whole device (measured faster from about ten
-  // images of 56 x 56 on); the next stage then becomes resident as the previous one's blocks retire.
+  // Left to choose, a chain whose stages all fit on the device at once, and a small chain of three or more
+  // convolutions (at most two tiles per SM and convolution), share the device: each synchronised convolution gets
+  // sms / num_convs persistent blocks, so that every stage is resident from the start and the chain runs as a
+  // pipeline over the semaphores, with no waits before the launches (the reference's AvoidWaitKernel case,
+  // cusync.h:61-62; measured +19 % on four convolutions of eight 56 x 56 images).  Other chains give every
+  // convolution the whole device (measured faster for two convolutions from eight images on); the next stage then
+  // becomes resident as the previous one's blocks retire.
   const uint32_t tiles = grid.x * grid.y;
   const uint32_t share = static_cast<uint32_t>(sms / d.num_convs) > 0 ? static_cast<uint32_t>(sms / d.num_convs) : 1u;
   const uint32_t cap = d.max_ctas > 0 ? static_cast<uint32_t>(d.max_ctas)
-                                      : (tiles <= 2u * static_cast<uint32_t>(sms) ? share : static_cast<uint32_t>(sms));
+                                      : (tiles * d.num_convs <= static_cast<uint32_t>(sms) ||
+                                                 (d.num_convs >= 3 && tiles <= 2u * static_cast<uint32_t>(sms))
+                                             ? share : static_cast<uint32_t>(sms));
   const uint32_t blocks = tiles < cap ? tiles : cap;
   c->sync_ctas = static_cast<int>(cap);
   c->wait_kernels = static_cast<uint64_t>(blocks) * d.num_convs > static_cast<uint64_t>(sms);
-  const int opts = c->wait_kernels ? CUSYNC_OPT_NONE : CUSYNC_OPT_AVOID_WAIT_KERNEL;
+  // (where a wait is needed it is a stream memory operation, not a kernel launch: these kernels are short)
+  const int opts = c->wait_kernels ? CUSYNC_OPT_STREAM_WAIT : CUSYNC_OPT_AVOID_WAIT_KERNEL;
 
   int rc = CUSYNC_SUCCESS;
   for (int i = 0; i < c->num && rc == CUSYNC_SUCCESS; i++)

@@ -110,6 +110,9 @@ int cusync_mlp_create(cusync_mlp_t** out, const cusync_mlp_desc_t* desc) {
   none.tile_m = none.tile_n = 1;
   // NoAtomicAdd only where each semaphore has one poster (mlp.cu:9-14).
   int opts = d.opts;
+  // Short chains (up to four row tiles) take the wait before the second GEMM as a stream memory operation
+  // rather than a kernel launch: measured two points of gain at B <= 256 and nothing either way above.
+  if (tiles_m <= 4) opts |= CUSYNC_OPT_STREAM_WAIT;
   if (d.policy == CUSYNC_POLICY_ROWSYNC) opts &= ~CUSYNC_OPT_NO_ATOMIC_ADD;
   cusync_dim3_t ts = {1, 1, 1};
   const int order1 = d.group_rows1 > 1 ? CUSYNC_ORDER_GROUPED(d.group_rows1) : CUSYNC_ORDER_TRANSPOSE_XY;

@@ -264,6 +264,10 @@ int cusync_stage_invoke_wait_kernel(cusync_stage_t* s, cusync_stream_t stream) {
   if (s == nullptr) return CUSYNC_ERROR_NOT_INITIALIZED;
   if (!s->is_producer) return CUSYNC_ERROR_NOT_PRODUCER;
   if (s->view.opts & CUSYNC_OPT_AVOID_WAIT_KERNEL) return CUSYNC_SUCCESS;
+  if (s->launch_noted && (s->view.opts & CUSYNC_OPT_STREAM_WAIT)) {
+    const int rc = cusync_stream_wait_values(s->view.started + 1, 1, (uint32_t)s->blocks_launched, stream);
+    if (rc != CUSYNC_ERROR_UNSUPPORTED) return rc;
+  }
   if (s->launch_noted)   // persistent kernel: wait until every block of the launch is resident
     return cusync_wait_kernel(s->view.started + 1, (uint32_t)s->blocks_launched, stream, s->view.status,
                               s->view.timeout_ns);

@@ -73,7 +73,8 @@ enum Optimizations {
   NoAtomicAdd = CUSYNC_OPT_NO_ATOMIC_ADD,            // each semaphore has one poster: store instead of add
   AvoidWaitKernel = CUSYNC_OPT_AVOID_WAIT_KERNEL,    // all stages fit one wave: no wait kernel
   AvoidCustomOrder = CUSYNC_OPT_AVOID_CUSTOM_ORDER,  // take blockIdx instead of a ticket
-  ReorderTileLoads = CUSYNC_OPT_REORDER_TILE_LOADS   // load independent operands before waiting
+  ReorderTileLoads = CUSYNC_OPT_REORDER_TILE_LOADS,  // load independent operands before waiting
+  StreamWait = CUSYNC_OPT_STREAM_WAIT                // addition: invokeWaitKernel as a stream memory operation
 };
 
 namespace detail {

@@ -51,7 +51,10 @@ enum {
   CUSYNC_OPT_NO_ATOMIC_ADD = 1,
   CUSYNC_OPT_AVOID_WAIT_KERNEL = 2,
   CUSYNC_OPT_AVOID_CUSTOM_ORDER = 4,
-  CUSYNC_OPT_REORDER_TILE_LOADS = 8
+  CUSYNC_OPT_REORDER_TILE_LOADS = 8,
+  CUSYNC_OPT_STREAM_WAIT = 16      /* addition: invokeWaitKernel becomes a stream memory operation
+                                      (cuStreamWaitValue32 on the "blocks started" word) instead of a kernel launch:
+                                      same condition, no launch, no SM, but no timeout record either */
 };
 
 /* Tile orders (src/include/cusync/tile-orders.h:50-76). */

@@ -139,7 +139,8 @@ def test_conv_chain_driver(n, h, w, c, convs, max_ctas):
     chain = cs.ConvChain(x, filters, relu=True, max_ctas=max_ctas)
     blocks = n * (h // (128 // w)) * (c // 64)
     sms = L.lib().cusync_b200_sm_count()
-    per_stage = min(blocks, max_ctas if max_ctas else (sms // convs if blocks <= 2 * sms else sms))
+    shared = blocks * convs <= sms or (convs >= 3 and blocks <= 2 * sms)
+    per_stage = min(blocks, max_ctas if max_ctas else (sms // convs if shared else sms))
     assert chain.uses_wait_kernels == (per_stage * convs > sms)
     streams = [torch.cuda.Stream(priority=-1)] + [torch.cuda.Stream() for _ in range(convs - 1)]
     for it in range(1, 4):
