@@ -191,7 +191,9 @@ CUSYNC_API int cusync_wait_kernel_range(uint32_t* semaphores, uint32_t count, ui
 /* The same wait without a kernel (the driver's stream memory operations, cuStreamWaitValue32 with GEQ): `stream`
  * holds until each of `count` semaphores has reached `value`.  A kernel needs room on an SM, and while the
  * persistent GEMM blocks are resident there is none, so a wait kernel enqueued behind them starts only when
- * they retire; this form does not depend on that.  Unbounded: no timeout record.  No counterpart. */
+ * they retire; this form does not depend on that.  Unbounded, no timeout record: wait only for values that
+ * work ALREADY SUBMITTED will write (streams can share a hardware queue, and a wait at its head keeps everything
+ * submitted later to that queue from being issued).  No counterpart. */
 CUSYNC_API int cusync_stream_wait_values(uint32_t* semaphores, uint32_t count, uint32_t value, cusync_stream_t stream);
 /* The posting counterpart (cuStreamWriteValue32): `stream` stores `value` into each of `count` semaphores once
  * everything enqueued on it before has completed - the way something that is not a kernel of this library (a

@@ -459,3 +459,33 @@ def test_link_error_codes():
     assert cs.CuSync.setProducerConsumerPair(prod, cons) == L.SUCCESS
     assert cons.invokeWaitKernel(None) == L.ERROR_NOT_PRODUCER
     prod.destroy(); cons.destroy()
+
+
+def test_stream_memory_operations_wait_and_post():
+    # cusync_stream_wait_values / cusync_stream_write_values: a stream holds until semaphores reach a value, and
+    # another stream's write releases it, without any kernel of the library.  The posting side is submitted
+    # first (behind a delay), as a stream wait must only wait for work that is already submitted: two streams
+    # may share a hardware queue, and a wait at its head would keep a later post from ever being issued.
+    sems = torch.zeros(4, dtype=torch.int32, device="cuda")
+    out = torch.zeros(1024, device="cuda")
+    a, b = torch.cuda.Stream(), torch.cuda.Stream()
+    torch.cuda.synchronize()
+    lib = L.lib()
+    with torch.cuda.stream(b):
+        torch.cuda._sleep(100_000_000)                     # some tens of milliseconds
+    assert lib.cusync_stream_write_values(sems.data_ptr(), 3, 3, b.cuda_stream) == L.SUCCESS
+    assert lib.cusync_stream_write_values(sems.data_ptr() + 12, 1, 5, b.cuda_stream) == L.SUCCESS   # >= counts
+    assert lib.cusync_stream_wait_values(sems.data_ptr(), 4, 3, a.cuda_stream) == L.SUCCESS
+    with torch.cuda.stream(a):
+        out.add_(1.0)
+    assert not a.query()                                   # held: the posts are still behind the delay
+    torch.cuda.synchronize()
+    assert (out == 1.0).all() and sems.tolist() == [3, 3, 3, 5]
+    assert lib.cusync_stream_wait_values(None, 1, 1, a.cuda_stream) == L.ERROR_NOT_INITIALIZED
+
+
+@pytest.mark.parametrize("policy", ["row", "tile"])
+def test_chain_with_the_wait_as_a_stream_operation(policy):
+    # Optimizations.StreamWait: invokeWaitKernel enqueues a stream wait on the producer's "blocks started" word
+    _chain(policy, 640, 1024, 512, 1024, 256, 256, iters=3, opts=cs.Optimizations.StreamWait, max_ctas=4, cta_pair=2)
+    _chain(policy, 256, 1024, 1024, 1024, 128, 128, iters=2, opts=cs.Optimizations.StreamWait)
