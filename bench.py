@@ -170,7 +170,22 @@ def time_steps(step_fn, start_stream, end_stream, steps, warmup, barrier):
     return total, per
 
 
+def _watchdog(seconds):
+    """Ends the process if the run is still going after `seconds`: a stream that waits for a value nobody writes
+    (a chain that gave up on a bounded wait upstream) must not keep the device busy."""
+    import threading
+
+    def bail():
+        sys.stderr.write("bench.py: no result after %d s, giving up\n" % seconds)
+        sys.stderr.flush()
+        os._exit(3)
+    t = threading.Timer(seconds, bail)
+    t.daemon = True
+    t.start()
+
+
 def main():
+    _watchdog(1500)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)

@@ -14,6 +14,13 @@ def pytest_configure(config):
 
 
 def pytest_collection_modifyitems(config, items):
+    # A GPU test that waits for something that never comes must end the run, not sit on the device: with the
+    # timeout plug-in present every GPU test gets a wall-clock limit enforced from a watchdog thread (a signal
+    # would not interrupt a blocked synchronize).
+    if config.pluginmanager.hasplugin("timeout"):
+        for item in items:
+            if "gpu" in item.keywords and item.get_closest_marker("timeout") is None:
+                item.add_marker(pytest.mark.timeout(300, method="thread"))
     try:
         import torch
         has_gpu = torch.cuda.is_available()
