@@ -148,6 +148,7 @@ bool select_kernel(int tile_n, bool dual, KernelEntry* out) {
     switch (tile_n) {
       case 64:  *out = entry<64, false>(); return true;
       case 128: *out = entry<128, false>(); return true;
+      case 192: *out = entry<192, false>(); return true;
       case 256: *out = entry<256, false>(); return true;
       default: return false;
     }

@@ -207,7 +207,9 @@ struct Cfg {
           ? 8
           : ((int)kSmemLimit - 1024 - kStagingBytes - kBarrierBytes) / kStageBytes;
   static constexpr int kAccCols = BN * kNumB;               // fp32 columns per accumulator buffer
-  static constexpr int kTmemCols = 2 * kAccCols < 32 ? 32 : 2 * kAccCols;
+  // two accumulator buffers, rounded up to a power of two (tcgen05.alloc's granularity)
+  static constexpr int kTmemCols = 2 * kAccCols <= 32 ? 32 : 2 * kAccCols <= 64 ? 64 : 2 * kAccCols <= 128 ? 128
+                                   : 2 * kAccCols <= 256 ? 256 : 512;
   static constexpr uint32_t kSmemBytes = 1024 + kStages * kStageBytes + kStagingBytes + kBarrierBytes;
   static_assert(kTmemCols <= 512, "accumulators exceed tensor memory");
   static_assert((kTmemCols & (kTmemCols - 1)) == 0, "TMEM columns must be a power of two");

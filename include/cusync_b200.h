@@ -229,7 +229,7 @@ typedef struct cusync_gemm_desc {
   void* d; int64_t ldd;            /* row-major [m,n] */
   int32_t b_layout;
   int32_t epilogue;
-  int32_t tile_n;                  /* 0 = choose; else 32, 64, 128 or 256.  Tile M is 128. */
+  int32_t tile_n;                  /* 0 = choose; else 64, 128, 192 or 256.  Tile M is 128. */
   int32_t max_ctas;                /* 0 = one per SM */
   int32_t split_k;                 /* K slices per output tile (the stage grid's z): 0 = choose, 1 = none.  Slices add
                                       their parts into an fp32 workspace owned by the plan; the last one to arrive applies

@@ -58,6 +58,8 @@ def _gemm(a, b, epi=L.EPILOGUE_NONE, tile_n=0, b_layout=L.B_ROW_MAJOR_KN, max_ct
     (129, 72, 136, 64),        # N and K barely over one granule
     (512, 2752, 1024, 128),    # LLaMA ffn width: 21.5 tiles of 128
     (1024, 2048, 1024, 256),
+    (512, 1536, 1024, 192),    # 192-wide tiles: three 64-column chunks, accumulators 384 of 512 TMEM columns
+    (300, 1000, 520, 192),     # ... with ragged edges
 ])
 @pytest.mark.parametrize("layout", [L.B_ROW_MAJOR_KN, L.B_ROW_MAJOR_NK])
 def test_gemm_matches_oracle(M, N, K, tile_n, layout):
