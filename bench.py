@@ -364,13 +364,19 @@ def main():
     yh = torch.empty((args.batch, M.GPT3_HIDDEN), dtype=torch.half).pin_memory()
 
     # One GPU: the result goes back to the host in row blocks, each behind the RowSync semaphores of its 128-row
-    # tiles of the second GEMM (post_rows), so the device-to-host copy overlaps that GEMM.
+    # tiles of the second GEMM (post_rows), so the device-to-host copy overlaps that GEMM.  Each GEMM gets half of
+    # the SMs here: a persistent kernel that holds every SM while it waits for rows of X keeps the second GEMM
+    # from becoming resident, and with it the first rows of Y from leaving while the last rows of X arrive.  The
+    # step is bound by the PCIe link, not by the GEMMs, so halving their rate costs nothing.
     e2e_shard = shard
     d2h_blocks = 4
     if world == 1 and args.batch >= 512:
+        d2h_blocks = max(4, min(8, args.batch // 256))
+        e2e_ctas = torch.cuda.get_device_properties(dev).multi_processor_count // 4 * 2
         e2e_shard = M.MLPShard("gpt3", args.batch, shard.x, shard.w1, shard.w2, None, policy=args.policy, post_rows=True,
-                               x_rows=True)
-    d2h, h2d = torch.cuda.Stream(), torch.cuda.Stream()
+                               x_rows=True, max_ctas=e2e_ctas, group_rows2=2)
+    d2h, h2d, post = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+    landed = [torch.cuda.Event() for _ in range(d2h_blocks)]
 
     def e2e_step():
         ps.wait_stream(cs)
@@ -380,12 +386,17 @@ def main():
             # X comes in row blocks on its own stream, each followed by the post of its RowSync semaphores; the
             # first GEMM is launched right away and takes the rows as they land (x_rows)
             h2d.wait_stream(ps)
+            post.wait_stream(ps)
             for first in range(0, tiles, per):
                 n = min(per, tiles - first)
                 r0, r1 = first * 128, min(args.batch, (first + n) * 128)
                 with torch.cuda.stream(h2d):
                     e2e_shard.x[r0:r1].copy_(xh[r0:r1], non_blocking=True)
-                e2e_shard.post_x_rows(first, n, h2d)
+                # the post goes to a stream of its own behind an event, so that the copies stay back to back
+                ev = landed[first // per]
+                ev.record(h2d)
+                post.wait_event(ev)
+                e2e_shard.post_x_rows(first, n, post)
         else:
             with torch.cuda.stream(ps):
                 e2e_shard.x.copy_(xh, non_blocking=True)

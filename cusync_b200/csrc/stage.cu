@@ -75,6 +75,51 @@ bool policy_ok(const cusync_policy_t* p) {
   return true;
 }
 
+// Several semaphores go to the stream as ONE batched operation (cuStreamBatchMemOp) where the driver has it:
+// every separate stream memory operation is a submission of its own and a bubble between the copies or kernels
+// around it.
+typedef CUresult (*StreamBatchFn)(CUstream, unsigned int, CUstreamBatchMemOpParams*, unsigned int);
+constexpr uint32_t kBatchOps = 64;
+
+int stream_values(bool wait, uint32_t* semaphores, uint32_t count, uint32_t value, cusync_stream_t stream) {
+  if (semaphores == nullptr || count == 0) return CUSYNC_ERROR_NOT_INITIALIZED;
+  static StreamValueFn wait_fn = stream_value_fn("cuStreamWaitValue32");
+  static StreamValueFn write_fn = stream_value_fn("cuStreamWriteValue32");
+  static StreamBatchFn batch_fn = reinterpret_cast<StreamBatchFn>(stream_value_fn("cuStreamBatchMemOp"));
+  StreamValueFn fn = wait ? wait_fn : write_fn;
+  if (!fn) return CUSYNC_ERROR_UNSUPPORTED;
+  CUstream cs = reinterpret_cast<CUstream>(stream);
+  uint32_t done = 0;
+  if (batch_fn && count > 1) {
+    CUstreamBatchMemOpParams ops[kBatchOps];
+    while (done < count) {
+      const uint32_t n = count - done < kBatchOps ? count - done : kBatchOps;
+      memset(ops, 0, sizeof(CUstreamBatchMemOpParams) * n);
+      for (uint32_t i = 0; i < n; i++) {
+        const CUdeviceptr addr = reinterpret_cast<CUdeviceptr>(semaphores + done + i);
+        if (wait) {
+          ops[i].waitValue.operation = CU_STREAM_MEM_OP_WAIT_VALUE_32;
+          ops[i].waitValue.address = addr;
+          ops[i].waitValue.value = value;
+          ops[i].waitValue.flags = CU_STREAM_WAIT_VALUE_GEQ;
+        } else {
+          ops[i].writeValue.operation = CU_STREAM_MEM_OP_WRITE_VALUE_32;
+          ops[i].writeValue.address = addr;
+          ops[i].writeValue.value = value;
+          ops[i].writeValue.flags = CU_STREAM_WRITE_VALUE_DEFAULT;
+        }
+      }
+      if (batch_fn(cs, n, ops, 0) != CUDA_SUCCESS) break;   // fall back to single operations for the rest
+      done += n;
+    }
+  }
+  for (uint32_t i = done; i < count; i++)
+    if (fn(cs, reinterpret_cast<CUdeviceptr>(semaphores + i), value,
+           wait ? CU_STREAM_WAIT_VALUE_GEQ : CU_STREAM_WRITE_VALUE_DEFAULT) != CUDA_SUCCESS)
+      return CUSYNC_ERROR_CUDA;
+  return CUSYNC_SUCCESS;
+}
+
 }  // namespace
 
 extern "C" {
@@ -239,25 +284,11 @@ int cusync_wait_kernel_range(uint32_t* semaphores, uint32_t count, uint32_t give
 }
 
 int cusync_stream_wait_values(uint32_t* semaphores, uint32_t count, uint32_t value, cusync_stream_t stream) {
-  if (semaphores == nullptr || count == 0) return CUSYNC_ERROR_NOT_INITIALIZED;
-  static StreamValueFn fn = stream_value_fn("cuStreamWaitValue32");
-  if (!fn) return CUSYNC_ERROR_UNSUPPORTED;
-  for (uint32_t i = 0; i < count; i++)
-    if (fn(reinterpret_cast<CUstream>(stream), reinterpret_cast<CUdeviceptr>(semaphores + i), value,
-           CU_STREAM_WAIT_VALUE_GEQ) != CUDA_SUCCESS)
-      return CUSYNC_ERROR_CUDA;
-  return CUSYNC_SUCCESS;
+  return stream_values(true, semaphores, count, value, stream);
 }
 
 int cusync_stream_write_values(uint32_t* semaphores, uint32_t count, uint32_t value, cusync_stream_t stream) {
-  if (semaphores == nullptr || count == 0) return CUSYNC_ERROR_NOT_INITIALIZED;
-  static StreamValueFn fn = stream_value_fn("cuStreamWriteValue32");
-  if (!fn) return CUSYNC_ERROR_UNSUPPORTED;
-  for (uint32_t i = 0; i < count; i++)
-    if (fn(reinterpret_cast<CUstream>(stream), reinterpret_cast<CUdeviceptr>(semaphores + i), value,
-           CU_STREAM_WRITE_VALUE_DEFAULT) != CUDA_SUCCESS)
-      return CUSYNC_ERROR_CUDA;
-  return CUSYNC_SUCCESS;
+  return stream_values(false, semaphores, count, value, stream);
 }
 
 int cusync_stage_invoke_wait_kernel(cusync_stage_t* s, cusync_stream_t stream) {

@@ -193,7 +193,8 @@ CUSYNC_API int cusync_wait_kernel_range(uint32_t* semaphores, uint32_t count, ui
  * persistent GEMM blocks are resident there is none, so a wait kernel enqueued behind them starts only when
  * they retire; this form does not depend on that.  Unbounded, no timeout record: wait only for values that
  * work ALREADY SUBMITTED will write (streams can share a hardware queue, and a wait at its head keeps everything
- * submitted later to that queue from being issued).  No counterpart. */
+ * submitted later to that queue from being issued).  More than one semaphore goes to the stream as one batched
+ * operation (cuStreamBatchMemOp, up to 64 per batch) where the driver offers it.  No counterpart. */
 CUSYNC_API int cusync_stream_wait_values(uint32_t* semaphores, uint32_t count, uint32_t value, cusync_stream_t stream);
 /* The posting counterpart (cuStreamWriteValue32): `stream` stores `value` into each of `count` semaphores once
  * everything enqueued on it before has completed - the way something that is not a kernel of this library (a

@@ -484,6 +484,13 @@ def test_stream_memory_operations_wait_and_post():
     torch.cuda.synchronize()
     assert (out == 1.0).all() and sems.tolist() == [3, 3, 3, 5]
     assert lib.cusync_stream_wait_values(None, 1, 1, a.cuda_stream) == L.ERROR_NOT_INITIALIZED
+    # more semaphores than one batched operation carries: posted first, then waited for
+    many = torch.zeros(150, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    assert lib.cusync_stream_write_values(many.data_ptr(), 150, 7, b.cuda_stream) == L.SUCCESS
+    assert lib.cusync_stream_wait_values(many.data_ptr(), 150, 7, b.cuda_stream) == L.SUCCESS
+    torch.cuda.synchronize()
+    assert many.tolist() == [7] * 150
 
 
 @pytest.mark.parametrize("policy", ["row", "tile"])
