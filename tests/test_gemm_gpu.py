@@ -480,9 +480,10 @@ def test_stream_memory_operations_wait_and_post():
     assert lib.cusync_stream_wait_values(sems.data_ptr(), 4, 3, a.cuda_stream) == L.SUCCESS
     with torch.cuda.stream(a):
         out.add_(1.0)
-    assert not a.query()                                   # held: the posts are still behind the delay
+        seen = sems.clone()                                # what the stream sees once its wait lets it through
     torch.cuda.synchronize()
     assert (out == 1.0).all() and sems.tolist() == [3, 3, 3, 5]
+    assert seen.tolist() == [3, 3, 3, 5]                   # held until every post had landed
     assert lib.cusync_stream_wait_values(None, 1, 1, a.cuda_stream) == L.ERROR_NOT_INITIALIZED
     # more semaphores than one batched operation carries: posted first, then waited for
     many = torch.zeros(150, dtype=torch.int32, device="cuda")
