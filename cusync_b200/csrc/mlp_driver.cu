@@ -5,6 +5,7 @@
 // grid/sync set-up :1026-1062, runBaselineGPT3 :411-491, runCuSyncGPT3 :645-716).
 #include <cstring>
 #include <new>
+#include <vector>
 
 #include "common.cuh"
 
@@ -13,6 +14,7 @@ struct cusync_mlp {
   int tile_n1, tile_n2;
   int split_k1, split_k2;
   cusync_stage_t* input;        // x_rows: producer-only stage standing for whatever brings X, posted by the caller
+  std::vector<uint32_t> x_posted;  // x_rows: per 128-row tile of X, the run its latest post was for
   cusync_stage_t* prod;
   cusync_stage_t* cons;
   cusync_gemm_plan_t* sync1;    // producer GEMM with its stage
@@ -124,6 +126,7 @@ int cusync_mlp_create(cusync_mlp_t** out, const cusync_mlp_desc_t* desc) {
     rows_in.tile_m = 128; rows_in.tile_n = 1; rows_in.wait_value = 1; rows_in.post_value = 1;
     const cusync_dim3_t grid0 = {1, tiles_m, 1};
     rc = cusync_stage_create(&m->input, grid0, ts, CUSYNC_ORDER_TRANSPOSE_XY, &none, &rows_in, CUSYNC_OPT_NONE);
+    if (rc == CUSYNC_SUCCESS) m->x_posted.assign(tiles_m, cusync_stage_iter(m->input) - 1u);
   }
   if (rc == CUSYNC_SUCCESS)
     rc = cusync_stage_create(&m->prod, grid1, ts, order1, &rows_in, &sync, opts & ~(d.x_rows ? CUSYNC_OPT_NO_ATOMIC_ADD : 0));
@@ -228,8 +231,19 @@ int cusync_mlp_post_x_rows(cusync_mlp_t* m, uint32_t first_tile, uint32_t num_ti
   cusync_stage_view_t v;
   cusync_stage_get_view(m->input, &v);
   if (num_tiles == 0 || first_tile + num_tiles > v.grid.y) return CUSYNC_ERROR_INVALID_ARGUMENT;
-  // the value of the coming run: run r waits for its row semaphores to reach r
-  return cusync_stream_write_values(v.sems_post + first_tile, num_tiles, v.iter, stream);
+  // Run r waits for its row semaphores to reach r, and every tile is posted once per run: the j-th post of a
+  // tile is the one for run j, whether it is enqueued before or after that run's launch.
+  int rc = CUSYNC_SUCCESS;
+  uint32_t t = first_tile;
+  while (t < first_tile + num_tiles && rc == CUSYNC_SUCCESS) {
+    uint32_t n = 1;
+    const uint32_t value = m->x_posted[t] + 1u;
+    while (t + n < first_tile + num_tiles && m->x_posted[t + n] + 1u == value) n++;
+    rc = cusync_stream_write_values(v.sems_post + t, n, value, stream);
+    if (rc == CUSYNC_SUCCESS) for (uint32_t i = 0; i < n; i++) m->x_posted[t + i] = value;
+    t += n;
+  }
+  return rc;
 }
 
 int cusync_mlp_wait_rows(cusync_mlp_t* m, uint32_t first_tile, uint32_t num_tiles, cusync_stream_t stream) {

@@ -53,8 +53,9 @@ class MLPShard:
                 "run_cusync")
 
     def post_x_rows(self, first_tile, num_tiles, stream):
-        """x_rows=True: the 128-row tiles [first_tile, first_tile + num_tiles) of x are complete, for the NEXT
-        run_cusync, once what `stream` holds so far has run; call for every tile before each run_cusync."""
+        """x_rows=True: the 128-row tiles [first_tile, first_tile + num_tiles) of x are complete once what `stream`
+        holds so far has run; call once per tile and run_cusync (the j-th post of a tile feeds the j-th run),
+        before or after that run's launch."""
         L.check(L.lib().cusync_mlp_post_x_rows(self._h, first_tile, num_tiles, _stream_ptr(stream)), "post_x_rows")
 
     def wait_rows(self, first_tile, num_tiles, stream):

@@ -488,10 +488,12 @@ CUSYNC_API int cusync_mlp_set_trace(cusync_mlp_t* mlp, void* trace1, uint32_t ca
 /* Configuration in use: out[0..5] = tile_n1, tile_n2, ctas1, ctas2, split_k1, split_k2. */
 CUSYNC_API int cusync_mlp_config(const cusync_mlp_t* mlp, int32_t* out6);
 /* With desc.x_rows: enqueues on `stream` the post (a stream memory operation, no kernel) for the 128-row tiles
- * [first_tile, first_tile + num_tiles) of X for the NEXT run_cusync; what was enqueued on `stream` before (the copy
- * that brings those rows) is complete when the first GEMM sees the post.  Call it for every row tile before each
- * run_cusync; the stream may well execute it after the GEMM has started.  The copy itself must not need an SM
- * either (a host-to-device cudaMemcpyAsync does not; a copy kernel might wait for the GEMM's blocks to retire). */
+ * [first_tile, first_tile + num_tiles) of X; what was enqueued on `stream` before (the copy that brings those
+ * rows) is complete when the first GEMM sees the post.  Call it once per row tile and run_cusync: the j-th post of
+ * a tile is the one the j-th run_cusync waits for, whether it is enqueued before that run's launch or after it
+ * (launching first lets the GEMMs be resident when the first rows land; their waits are bounded, so rows that
+ * never come end in a timeout record, not a hang).  The copy itself must not need an SM (a host-to-device
+ * cudaMemcpyAsync does not; a copy kernel might wait for the GEMM's blocks to retire). */
 CUSYNC_API int cusync_mlp_post_x_rows(cusync_mlp_t* mlp, uint32_t first_tile, uint32_t num_tiles, cusync_stream_t stream);
 /* With desc.post_rows: makes `stream` wait (a stream memory operation, no kernel) for the 128-row tiles
  * [first_tile, first_tile + num_tiles) of Y as written by the most recent run_cusync (call it after that
