@@ -127,14 +127,21 @@ def test_input_rows_can_arrive_while_the_layer_runs(batch):
     tiles = (batch + 127) // 128
     for it in range(1, 4):
         x.fill_(float("nan")); s.y.fill_(float("nan")); torch.cuda.synchronize()
-        with torch.cuda.stream(feed):
-            torch.cuda._sleep(1_000_000)            # about half a millisecond before the first row arrives
+        # Third run: the layer is launched BEFORE its rows are even submitted (the posts count per tile, so either
+        # order feeds the same run).  No delay kernel then: it would need an SM that the waiting GEMM holds.
+        launch_first = it == 3
+        if launch_first:
+            s.run_cusync(ps, cs_)
+        else:
+            with torch.cuda.stream(feed):
+                torch.cuda._sleep(1_000_000)        # about half a millisecond before the first row arrives
         for first in reversed(range(tiles)) if it == 2 else range(tiles):   # any order will do
             r0, r1 = first * 128, min(batch, (first + 1) * 128)
             with torch.cuda.stream(feed):
                 x[r0:r1].copy_(x_host[r0:r1], non_blocking=True)
             s.post_x_rows(first, 1, feed)
-        s.run_cusync(ps, cs_)
+        if not launch_first:
+            s.run_cusync(ps, cs_)
         torch.cuda.synchronize()
         assert s.status_codes() == (0, 0)
         assert not torch.isnan(s.y.float()).any()
