@@ -29,6 +29,26 @@ UNIT = "us"
 SWEEP_BATCHES = [1, 64, 256, 512, 1024, 2048]
 
 
+_RESULT_FD = None
+
+
+def claim_stdout():
+    """Keeps the process's stdout for the result line alone: libraries that write to file descriptor 1 (NCCL's
+    version banner) go to stderr from here on."""
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
+
+
+def emit(line):
+    data = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(data.decode()); sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, data)
+
+
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -125,7 +145,7 @@ def run_reference(args, rank, world):
             "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port",
                              "sample": "%d of %d rows through both GEMMs, scaled to the full batch" % (sample, args.batch)},
             "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def workload_config(args, shard):
@@ -202,6 +222,7 @@ def main():
     ap.add_argument("--no-sweep", action="store_true", help="skip the per-batch table")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
+    claim_stdout()
     args.warmup = max(args.warmup, 3) if args.impl == "cusync" else args.warmup
 
     rank = int(os.environ.get("RANK", "0"))
@@ -571,7 +592,7 @@ def main():
         line["cpu_baseline"] = {"value": us, "unit": UNIT, "cores": threads, "kind": "port",
                                 "sample": "%d of %d rows through both GEMMs (%.1f s), scaled to the full batch"
                                           % (sample, args.batch, spent)}
-    print(json.dumps(line), flush=True)
+    emit(line)
     group.close()
 
 
