@@ -2,8 +2,9 @@
  * CPU oracle for the CuSync hot path -- see cusync_oracle.h.
  * TEST INFRASTRUCTURE ONLY; never linked into the product library.
  * Parity pinning is described in the header: integer side pinned to the
- * reference's own policy code and test known-answers; GELU / SiLU*mul / ReLU /
- * softmax: parity unpinned (no reference test covers them).
+ * reference's own policy code and test known-answers; arithmetic side pinned
+ * to CUTLASS's host reference kernels and activation functors (the decode
+ * attention's softmax alone stays unpinned: the reference has none).
  */
 #include "cusync_oracle.h"
 

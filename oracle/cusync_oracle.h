@@ -13,8 +13,15 @@
  * tile-order code (compiled for the host from the reference headers, see
  * oracle/Makefile target `_ref`) and to the known answers of the reference's
  * tests (tests/simple-test.cu:83-96, src/examples/twoMatMuls/matrixMul.cu:235-272).
- * GELU, SiLU*mul, ReLU, softmax: parity unpinned -- no reference test checks
- * them; the definitions below are the sole authority.
+ * The arithmetic side is pinned to NVIDIA CUTLASS's host reference kernels, the
+ * code the reference's drivers check their GPU kernels against
+ * (cutlass::reference::host::Conv2dFprop, src/ml-bench/volta_conv2d/resnet.cu:706-720;
+ * the CUTLASS host GEMM; the GELU / SiLu / ReLu functors of its epilogues):
+ * oracle/cutlass_host_ref.cpp wraps them and tests/test_oracle_cutlass_pin.py
+ * compares bit patterns (GEMM, GELU, ReLU, convolution: bit-exact; SiLU*mul:
+ * within one half-precision ulp).  The softmax of the decode-attention stage
+ * has no counterpart in the reference (its attention.cu has no softmax):
+ * parity unpinned for that one function; it is checked against float64 numpy.
  */
 #ifndef CUSYNC_ORACLE_H
 #define CUSYNC_ORACLE_H
