@@ -135,6 +135,7 @@ SIGNATURES = {
     "cusync_gemm_run": (_i, [_vp, _vp]),
     "cusync_gemm_plan_tail_split": (_i, [_vp]),
     "cusync_gemm_run_noalloc": (_i, [C.POINTER(GemmDesc), _vp]),
+    "cusync_gemm_noalloc_read_status": (_i, [C.POINTER(Status)]),
     "cusync_gemm_plan_set_trace": (_i, [_vp, _vp, _u32]),
     "cusync_gemm_plan_num_ctas": (_u32, [_vp]),
     "cusync_conv2d_tile_rows": (_i, [C.c_int32]),

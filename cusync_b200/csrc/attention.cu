@@ -86,7 +86,12 @@ cusync_attn_decode_kernel(const AttnParams p) {
       s_flag = ok;
     }
     __syncthreads();
-    if (!s_flag) return;      // bounded wait expired: leave without touching the output
+    if (!s_flag) {            // bounded wait expired: leave without touching the output ...
+      // ... and without posting: release what waits on this stage without a bound of its own
+      if (p.is_producer)
+        cusync::releaseWaitersOnAbort(st.sems_post, st.grid.x * st.grid.y * st.grid.z, tid, blockDim.x);
+      return;
+    }
   }
 
   // ---- query ----------------------------------------------------------------------------------

@@ -18,6 +18,7 @@ struct cusync_attn_block {
   cusync_attn_plan_t* attn[2];
   cusync_gemm_plan_t* proj[2];
   int tile_n1, tile_n3, split1, split3, kv_splits;
+  RunOrder order;                     // run r + 1 starts after run r has finished (qkv and attn_out are reused)
 };
 
 namespace {
@@ -32,6 +33,7 @@ void destroy_all(cusync_attn_block* b) {
     if (b->stages[i]) cusync_stage_destroy(b->stages[i]);
     if (b->plain_stages[i]) cusync_stage_destroy(b->plain_stages[i]);
   }
+  b->order.destroy();
   delete b;
 }
 
@@ -114,6 +116,7 @@ int cusync_attn_block_create(cusync_attn_block_t** out, const cusync_attn_block_
     g.tile_n = b->tile_n3; g.split_k = b->split3; g.stage = st[2];
     rc = cusync_gemm_plan_create(&b->proj[arm], &g);
   }
+  if (rc == CUSYNC_SUCCESS && !b->order.create()) { (void)cudaGetLastError(); rc = CUSYNC_ERROR_CUDA; }
   if (rc != CUSYNC_SUCCESS) { destroy_all(b); return rc; }
   *out = b;
   return CUSYNC_SUCCESS;
@@ -135,11 +138,14 @@ int cusync_attn_block_run_stream_ordered(cusync_attn_block_t* b, cusync_stream_t
 
 int cusync_attn_block_run_cusync(cusync_attn_block_t* b, const cusync_stream_t* streams) {
   if (!b || !streams) return CUSYNC_ERROR_NOT_INITIALIZED;
+  if (!b->order.begin(streams[0])) { (void)cudaGetLastError(); return CUSYNC_ERROR_CUDA; }
   int rc = cusync_gemm_run(b->qkv[0], streams[0]);
   if (rc == CUSYNC_SUCCESS) rc = cusync_stage_invoke_wait_kernel(b->stages[0], streams[1]);
   if (rc == CUSYNC_SUCCESS) rc = cusync_attn_run(b->attn[0], streams[1]);
   if (rc == CUSYNC_SUCCESS) rc = cusync_stage_invoke_wait_kernel(b->stages[1], streams[2]);
   if (rc == CUSYNC_SUCCESS) rc = cusync_gemm_run(b->proj[0], streams[2]);
+  if (rc != CUSYNC_SUCCESS) return rc;
+  if (!b->order.end(streams[2])) { (void)cudaGetLastError(); rc = CUSYNC_ERROR_CUDA; }
   for (int i = 0; i < 3; i++) cusync_stage_increment_iter(b->stages[i]);
   return rc;
 }

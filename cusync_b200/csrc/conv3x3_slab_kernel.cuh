@@ -439,6 +439,9 @@ cusync_conv3x3_slab_kernel(const __grid_constant__ CUtensorMap tmX, const __grid
   // Teardown (normal and abort paths alike).
   tc_fence_before();
   __syncthreads();
+  // A block that gave up does not post its tiles: release what waits on this stage without a bound of its own.
+  if (bars->abort != 0u && p.is_producer)
+    cusync::releaseWaitersOnAbort(st.sems_post, st.grid.x * st.grid.y * st.grid.z, threadIdx.x, blockDim.x);
   if (warp == 2) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kSlabStages * kSlabBN);

@@ -22,6 +22,7 @@ struct cusync_conv_chain {
   int sync_ctas;                            // blocks per synchronised convolution
   bool wait_kernels;                        // false: every stage fits on the device at once
   cudaEvent_t fork;                         // orders the resets of a replayable run before every stage
+  RunOrder order;                           // run r + 1 starts after run r has finished (activations are reused)
 };
 
 namespace {
@@ -33,6 +34,7 @@ void destroy_all(cusync_conv_chain* c) {
     if (c->stages[i]) cusync_stage_destroy(c->stages[i]);
   }
   if (c->fork) cudaEventDestroy(c->fork);
+  c->order.destroy();
   delete c;
 }
 
@@ -115,6 +117,7 @@ int cusync_conv_chain_create(cusync_conv_chain_t** out, const cusync_conv_chain_
     c->fork = nullptr;
     rc = CUSYNC_ERROR_CUDA;
   }
+  if (rc == CUSYNC_SUCCESS && !c->order.create()) { (void)cudaGetLastError(); rc = CUSYNC_ERROR_CUDA; }
   if (rc != CUSYNC_SUCCESS) { destroy_all(c); return rc; }
   *out = c;
   return CUSYNC_SUCCESS;
@@ -136,11 +139,14 @@ int cusync_conv_chain_run_stream_ordered(cusync_conv_chain_t* c, cusync_stream_t
 int cusync_conv_chain_run_cusync(cusync_conv_chain_t* c, const cusync_stream_t* streams) {
   if (!c || !streams) return CUSYNC_ERROR_NOT_INITIALIZED;
   int rc = CUSYNC_SUCCESS;
+  if (!c->order.begin(streams[0])) { (void)cudaGetLastError(); return CUSYNC_ERROR_CUDA; }
   for (int i = 0; i < c->num && rc == CUSYNC_SUCCESS; i++) {
     // a dependent convolution is launched only once every block of its producer is resident
     if (i > 0 && c->wait_kernels) rc = cusync_stage_invoke_wait_kernel(c->stages[i - 1], streams[i]);
     if (rc == CUSYNC_SUCCESS) rc = cusync_conv2d_run(c->sync[i], streams[i]);
   }
+  if (rc != CUSYNC_SUCCESS) return rc;
+  if (!c->order.end(streams[c->num - 1])) { (void)cudaGetLastError(); rc = CUSYNC_ERROR_CUDA; }
   for (int i = 0; i < c->num; i++) cusync_stage_increment_iter(c->stages[i]);
   return rc;
 }

@@ -144,11 +144,16 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           // Consumer wait, at the load of the dependent A K-block.
           if (p.is_consumer) {
             const uint32_t tz = kb == kb_begin ? 1u : 0u;
+            // A K slice (split-K) may begin in the middle of a producer tile: its first K block is a sync point
+            // of the K-walking policies as well, on the tile that contains it.
             if (static_cast<uint32_t>(k_off) >= ready_end &&
-                cusync::eval::isSync(st.in_policy, static_cast<uint32_t>(k_off), tz)) {
+                (cusync::eval::isSync(st.in_policy, static_cast<uint32_t>(k_off), tz) || (tz && sync_stride))) {
               const uint32_t idx = cusync::eval::tileIndex(st.in_policy, static_cast<uint32_t>(m_off),
                                                            static_cast<uint32_t>(k_off), st.prod_grid.x,
                                                            st.prod_grid.y);
+              // K offset at which the producer tile holding k_off begins
+              const uint32_t k_sync = sync_stride ? static_cast<uint32_t>(k_off) / sync_stride * sync_stride
+                                                  : static_cast<uint32_t>(k_off);
               uint32_t seen = 0;
               // Probe first: the tile's own semaphore and the next producer tiles along K are read with
               // independent relaxed loads (one memory round trip for all of them); only if the tile's own is
@@ -163,14 +168,14 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 const bool affine = st.in_policy.kind == CUSYNC_POLICY_TILESYNC ||
                                     st.in_policy.kind == CUSYNC_POLICY_CONV2DTILESYNC;
                 uint32_t step = 0;
-                if (affine && static_cast<uint32_t>(k_off) + sync_stride < static_cast<uint32_t>(p.k))
+                if (affine && k_sync + sync_stride < static_cast<uint32_t>(p.k))
                   step = cusync::eval::tileIndex(st.in_policy, static_cast<uint32_t>(m_off),
-                                                 static_cast<uint32_t>(k_off) + sync_stride, st.prod_grid.x,
+                                                 k_sync + sync_stride, st.prod_grid.x,
                                                  st.prod_grid.y) - idx;
                 v_first = cusync::loadRelaxed(st.sems_wait + idx);
 #pragma unroll
                 for (int j = 0; j < kLookahead; j++) {
-                  const uint32_t kk = static_cast<uint32_t>(k_off) + (j + 1) * sync_stride;
+                  const uint32_t kk = k_sync + (j + 1) * sync_stride;
                   vals[j] = kk < static_cast<uint32_t>(p.k)
                                 ? cusync::loadRelaxed(st.sems_wait + (affine ? idx + (j + 1) * step
                                       : cusync::eval::tileIndex(st.in_policy, static_cast<uint32_t>(m_off), kk,
@@ -216,7 +221,7 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 for (int j = 0; j < kLookahead; j++) {
                   if (ahead == static_cast<uint32_t>(j) && vals[j] >= wait_target) ahead++;
                 }
-                ready_end = static_cast<uint32_t>(k_off) + (ahead + 1) * sync_stride;
+                ready_end = k_sync + (ahead + 1) * sync_stride;
                 if (ahead || probed_ready) cusync::fenceAcqRel();
               }
               // A 3x3 stencil also reads the image rows just above and below the tile: they belong to
@@ -506,6 +511,9 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   // Teardown (normal and abort paths alike).
   tc_fence_before();
   __syncthreads();
+  // A block that gave up does not post its tiles: release what waits on this stage without a bound of its own.
+  if (bars->abort != 0u && p.is_producer)
+    cusync::releaseWaitersOnAbort(st.sems_post, st.grid.x * st.grid.y * st.grid.z, threadIdx.x, blockDim.x);
   if (warp == 2) {
     tc_fence_after();
     tmem_dealloc(tmem_base, C::kTmemCols);

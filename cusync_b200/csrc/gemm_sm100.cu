@@ -325,6 +325,36 @@ int build_maps(cusync_gemm_plan* pl) {
   return ok ? CUSYNC_SUCCESS : CUSYNC_ERROR_CUDA;
 }
 
+// The library kernels evaluate a stage's policies with THEIR tile shape: tile_m rows (128, or the pixels of a
+// convolution tile) by tile_n columns, K walked in 64-element blocks.  A policy built for another shape would
+// index semaphores the stage does not have (a producer posting past the end of its array) or cover fewer rows
+// than a block loads (a consumer reading rows nobody has waited for).  Checked once, on the host.
+int check_stage_policies(const cusync_stage_view_t& v, uint32_t tile_m, uint32_t tile_n, uint32_t k_extent, bool conv) {
+  const cusync_policy_t& out = v.out_policy;
+  if (out.kind != CUSYNC_POLICY_NOSYNC && out.kind != CUSYNC_POLICY_CUSTOM) {
+    const uint64_t num_sems = static_cast<uint64_t>(v.grid.x) * v.grid.y * v.grid.z;
+    for (uint32_t y = 0; y < v.grid.y; y++)
+      for (uint32_t x = 0; x < v.grid.x; x++)
+        if (cusync::eval::tileIndex(out, y * tile_m, x * tile_n, v.grid.x, v.grid.y) >= num_sems)
+          return CUSYNC_ERROR_INVALID_ARGUMENT;
+  }
+  const cusync_policy_t& in = v.in_policy;
+  if (in.kind != CUSYNC_POLICY_NOSYNC && in.kind != CUSYNC_POLICY_CUSTOM) {
+    // a block waits on the semaphore of its first row: the producer's row tiles must be whole multiples of it
+    if (conv ? in.tile_m != tile_m : in.tile_m % tile_m != 0) return CUSYNC_ERROR_INVALID_ARGUMENT;
+    const bool walks_k = in.kind == CUSYNC_POLICY_TILESYNC || in.kind == CUSYNC_POLICY_STRIDEDTILESYNC ||
+                         in.kind == CUSYNC_POLICY_CONV2DTILESYNC;
+    if (walks_k && (conv ? in.tile_n != static_cast<uint32_t>(kBlockK) : in.tile_n % kBlockK != 0))
+      return CUSYNC_ERROR_INVALID_ARGUMENT;
+    const uint64_t prod_sems = static_cast<uint64_t>(v.prod_grid.x) * v.prod_grid.y * v.prod_grid.z;
+    for (uint32_t y = 0; y < v.grid.y; y++)
+      for (uint32_t k = 0; k < k_extent; k += kBlockK)
+        if (cusync::eval::tileIndex(in, y * tile_m, k, v.prod_grid.x, v.prod_grid.y) >= prod_sems)
+          return CUSYNC_ERROR_INVALID_ARGUMENT;
+  }
+  return CUSYNC_SUCCESS;
+}
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // ---------------------------------------------------------------------------
@@ -387,7 +417,43 @@ int noalloc_scratch_for_current_device(NoAllocScratch** out) {
   return CUSYNC_SUCCESS;
 }
 
+// The opt-in to more than 48 KB of dynamic shared memory is a property of (kernel, device): set once, not per call.
+int noalloc_allow_large_smem(const KernelEntry& k) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoAllocMaxDevices) { (void)cudaGetLastError(); return CUSYNC_ERROR_CUDA; }
+  constexpr int kKernels = 8;
+  static KernelFn done_fn[kNoAllocMaxDevices][kKernels] = {};
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  for (int i = 0; i < kKernels; i++) {
+    if (done_fn[dev][i] == k.fn) return CUSYNC_SUCCESS;
+    if (done_fn[dev][i] == nullptr) {
+      if (cudaFuncSetAttribute(reinterpret_cast<const void*>(k.fn), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(k.smem)) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return CUSYNC_ERROR_CUDA;
+      }
+      done_fn[dev][i] = k.fn;
+      return CUSYNC_SUCCESS;
+    }
+  }
+  return CUSYNC_ERROR_CUDA;   // more kernel instantiations than select_kernel offers: cannot happen
+}
+
 }  // namespace
+
+// The timeout record of the allocation-free entry point lives in its static array (no stage owns it): copies
+// it to the host.  Synchronous with respect to the device's work; allocates nothing.
+extern "C" int cusync_gemm_noalloc_read_status(cusync_status_t* out) {
+  if (out == nullptr) return CUSYNC_ERROR_INVALID_ARGUMENT;
+  NoAllocScratch* scratch = nullptr;
+  const int rc = noalloc_scratch_for_current_device(&scratch);
+  if (rc != CUSYNC_SUCCESS) return rc;
+  if (cudaMemcpy(out, &scratch->words[8], sizeof(cusync_status_t), cudaMemcpyDeviceToHost) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return CUSYNC_ERROR_CUDA;
+  }
+  return CUSYNC_SUCCESS;
+}
 
 extern "C" int cusync_gemm_run_noalloc(const cusync_gemm_desc_t* desc, cusync_stream_t stream) {
   if (desc == nullptr) return CUSYNC_ERROR_INVALID_ARGUMENT;
@@ -404,6 +470,9 @@ extern "C" int cusync_gemm_run_noalloc(const cusync_gemm_desc_t* desc, cusync_st
     return CUSYNC_ERROR_UNSUPPORTED;
   if (d.lda % 8 || d.ldb % 8 || d.ldd % 8 || d.lda < d.k || d.ldd < d.n) return CUSYNC_ERROR_UNSUPPORTED;
   if (d.b_layout == CUSYNC_B_ROW_MAJOR_NK ? d.ldb < d.k : d.ldb < d.n) return CUSYNC_ERROR_UNSUPPORTED;
+  // Only the one-CTA-per-tile kernel without K slices runs here: the other forms need a workspace or a
+  // schedule of their own, which the plan-based path allocates.  Asking for them is refused, not ignored.
+  if (d.split_k > 1 || d.cta_pair == 2 || d.tail_split > 1) return CUSYNC_ERROR_UNSUPPORTED;
 
   cusync_gemm_plan pl;                       // on the stack: tensor maps travel as kernel parameters
   std::memset(&pl, 0, sizeof(pl));
@@ -432,11 +501,8 @@ extern "C" int cusync_gemm_run_noalloc(const cusync_gemm_desc_t* desc, cusync_st
   if (rc != CUSYNC_SUCCESS) return rc;
   rc = build_maps(&pl);
   if (rc != CUSYNC_SUCCESS) return rc;
-  if (cudaFuncSetAttribute(reinterpret_cast<const void*>(pl.kernel.fn), cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           static_cast<int>(pl.kernel.smem)) != cudaSuccess) {
-    (void)cudaGetLastError();
-    return CUSYNC_ERROR_CUDA;
-  }
+  rc = noalloc_allow_large_smem(pl.kernel);
+  if (rc != CUSYNC_SUCCESS) return rc;
 
   cusync_stage_view_t& v = p.stage;          // a NoSync stage view over the static scratch
   v.grid = cusync_dim3_t{static_cast<uint32_t>(p.tiles_n), static_cast<uint32_t>(p.tiles_m), 1};
@@ -575,6 +641,14 @@ int cusync_gemm_plan_create(cusync_gemm_plan_t** out, const cusync_gemm_desc_t* 
     if (pl->own_stage) cusync_stage_destroy(pl->own_stage);
     delete pl;
     return CUSYNC_ERROR_NOT_INITIALIZED;   // consumer not wired to a producer yet
+  }
+  {
+    const int prc = check_stage_policies(view, kBlockM, static_cast<uint32_t>(pl->tile_n), static_cast<uint32_t>(d.k), false);
+    if (prc != CUSYNC_SUCCESS) {
+      if (pl->own_stage) cusync_stage_destroy(pl->own_stage);
+      delete pl;
+      return prc;
+    }
   }
 
   uint32_t cap = d.max_ctas > 0 ? static_cast<uint32_t>(d.max_ctas) : static_cast<uint32_t>(sms);
@@ -725,6 +799,8 @@ int cusync_conv2d_plan_create(cusync_conv2d_plan_t** out, const cusync_conv2d_de
     rc = CUSYNC_ERROR_INVALID_ARGUMENT;
   else if (view.in_policy.kind != CUSYNC_POLICY_NOSYNC && view.sems_wait == nullptr)
     rc = CUSYNC_ERROR_NOT_INITIALIZED;
+  if (rc == CUSYNC_SUCCESS)
+    rc = check_stage_policies(view, static_cast<uint32_t>(rows * d.w), 64u, static_cast<uint32_t>(9 * d.c), true);
   int sms = cusync_b200_sm_count();
   if (sms <= 0) sms = 148;
   const uint32_t cap = d.max_ctas > 0 ? static_cast<uint32_t>(d.max_ctas) : static_cast<uint32_t>(sms);

@@ -23,6 +23,7 @@ struct cusync_mlp {
   cusync_gemm_plan_t* plain2;
   cusync_stage_t* plain_stage1; // NoSync stages carrying the two tile orders for the baseline
   cusync_stage_t* plain_stage2;
+  RunOrder order;               // run r + 1 starts after run r has finished (H and Y are reused)
 };
 
 namespace {
@@ -64,6 +65,7 @@ void destroy_all(cusync_mlp* m) {
   if (m->cons) cusync_stage_destroy(m->cons);
   if (m->plain_stage1) cusync_stage_destroy(m->plain_stage1);
   if (m->plain_stage2) cusync_stage_destroy(m->plain_stage2);
+  m->order.destroy();
   delete m;
 }
 
@@ -154,6 +156,7 @@ int cusync_mlp_create(cusync_mlp_t** out, const cusync_mlp_desc_t* desc) {
   if (rc == CUSYNC_SUCCESS) { fill_gemm1(d, m->tile_n1, m->split_k1, d.tail_split_plain1, m->plain_stage1, &g); rc = cusync_gemm_plan_create(&m->plain1, &g); }
   if (rc == CUSYNC_SUCCESS) rc = cusync_stage_create(&m->plain_stage2, grid2, ts, order2, &none, &none, CUSYNC_OPT_NONE);
   if (rc == CUSYNC_SUCCESS) { fill_gemm2(d, m->tile_n2, m->split_k2, d.tail_split_plain2, m->plain_stage2, &g); rc = cusync_gemm_plan_create(&m->plain2, &g); }
+  if (rc == CUSYNC_SUCCESS && !m->order.create()) { (void)cudaGetLastError(); rc = CUSYNC_ERROR_CUDA; }
   if (rc != CUSYNC_SUCCESS) { destroy_all(m); return rc; }
   *out = m;
   return CUSYNC_SUCCESS;
@@ -180,9 +183,13 @@ int cusync_mlp_run_single(cusync_mlp_t* m, int which, cusync_stream_t stream) {
 
 int cusync_mlp_run_cusync(cusync_mlp_t* m, cusync_stream_t producer_stream, cusync_stream_t consumer_stream) {
   if (!m) return CUSYNC_ERROR_NOT_INITIALIZED;
+  // The next run's first GEMM overwrites H, which this run's second GEMM reads: runs are ordered one after the other.
+  if (!m->order.begin(producer_stream)) { (void)cudaGetLastError(); return CUSYNC_ERROR_CUDA; }
   int rc = cusync_gemm_run(m->sync1, producer_stream);
   if (rc == CUSYNC_SUCCESS) rc = cusync_stage_invoke_wait_kernel(m->prod, consumer_stream);
   if (rc == CUSYNC_SUCCESS) rc = cusync_gemm_run(m->sync2, consumer_stream);
+  if (rc != CUSYNC_SUCCESS) return rc;      // nothing counted: the stages stay at this run's iteration
+  if (!m->order.end(consumer_stream)) { (void)cudaGetLastError(); rc = CUSYNC_ERROR_CUDA; }
   if (m->input) cusync_stage_increment_iter(m->input);
   cusync_stage_increment_iter(m->prod);
   cusync_stage_increment_iter(m->cons);

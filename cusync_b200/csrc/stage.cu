@@ -37,6 +37,23 @@ __global__ void waitKernel(const uint32_t* sem, uint32_t value, uint32_t* status
     cusync::recordTimeout(status, 3u, 0, 0, 0, 0, seen, value);
 }
 
+// The same for a counter that wraps (the 32-bit "blocks started" word counts every block of every run): done
+// when the counter has reached `value` in the cyclic sense the driver's stream waits use,
+// (int32_t)(*counter - value) >= 0.
+__global__ void waitCounterKernel(const uint32_t* counter, uint32_t value, uint32_t* status, uint64_t timeout_ns) {
+  if (threadIdx.x != 0) return;
+  const uint64_t t0 = cusync::globalTimerNs();
+  const uint64_t bound = timeout_ns ? timeout_ns : cusync::kDefaultSpinTimeoutNs;
+  uint32_t backoff = 32;
+  while (true) {
+    const uint32_t v = cusync::loadAcquire(counter);
+    if (static_cast<int32_t>(v - value) >= 0) return;
+    if (cusync::globalTimerNs() - t0 > bound) { cusync::recordTimeout(status, 3u, 0, 0, 0, 0, v, value); return; }
+    __nanosleep(backoff);
+    if (backoff < 1024) backoff <<= 1;
+  }
+}
+
 // One thread per semaphore of a contiguous range; the kernel ends when every one has reached `value`.
 __global__ void waitRangeKernel(const uint32_t* sems, uint32_t count, uint32_t value, uint32_t* status,
                                 uint64_t timeout_ns) {
@@ -295,13 +312,18 @@ int cusync_stage_invoke_wait_kernel(cusync_stage_t* s, cusync_stream_t stream) {
   if (s == nullptr) return CUSYNC_ERROR_NOT_INITIALIZED;
   if (!s->is_producer) return CUSYNC_ERROR_NOT_PRODUCER;
   if (s->view.opts & CUSYNC_OPT_AVOID_WAIT_KERNEL) return CUSYNC_SUCCESS;
+  // The device counter is 32 bits wide and wraps; both forms below compare cyclically against the low 32 bits
+  // of the host's running total.
+  const uint32_t launched = static_cast<uint32_t>(s->blocks_launched & 0xffffffffull);
   if (s->launch_noted && (s->view.opts & CUSYNC_OPT_STREAM_WAIT)) {
-    const int rc = cusync_stream_wait_values(s->view.started + 1, 1, (uint32_t)s->blocks_launched, stream);
+    const int rc = cusync_stream_wait_values(s->view.started + 1, 1, launched, stream);
     if (rc != CUSYNC_ERROR_UNSUPPORTED) return rc;
   }
-  if (s->launch_noted)   // persistent kernel: wait until every block of the launch is resident
-    return cusync_wait_kernel(s->view.started + 1, (uint32_t)s->blocks_launched, stream, s->view.status,
-                              s->view.timeout_ns);
+  if (s->launch_noted) {  // persistent kernel: wait until every block of the launch is resident
+    waitCounterKernel<<<1, 1, 0, (cudaStream_t)stream>>>(s->view.started + 1, launched, s->view.status,
+                                                         s->view.timeout_ns);
+    return cudaGetLastError() == cudaSuccess ? CUSYNC_SUCCESS : CUSYNC_ERROR_CUDA;
+  }
   return cusync_wait_kernel(s->view.started, s->view.iter, stream, s->view.status, s->view.timeout_ns);
 }
 

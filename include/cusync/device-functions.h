@@ -64,6 +64,20 @@ CUSYNC_DEVICE void recordTimeout(uint32_t* status, uint32_t where, uint32_t tx, 
   }
 }
 
+// Bit a block sets in every semaphore of its stage when it gives up (a bounded wait expired), so that nothing
+// downstream waits for posts that will not come: a ">= value" comparison is then satisfied, the plain unsigned
+// one of spinUntilAtLeast as well as the cyclic one of the driver's stream memory operations
+// ((int32_t)(*addr - value) >= 0), as long as counts stay below 2^30.  Work released this way reads unfinished
+// data: the host finds CUSYNC_ERROR_TIMEOUT in the stage's status and has to reset the chain's stages.
+static constexpr uint32_t kAbortedSemaphoreBit = 0x40000000u;
+
+// Called by all `nthreads` threads of a block on its abort path; `sems` may be null (not a producer).
+CUSYNC_DEVICE void releaseWaitersOnAbort(uint32_t* sems, uint32_t count, uint32_t tid, uint32_t nthreads) {
+  if (sems == nullptr) return;
+  for (uint32_t i = tid; i < count; i += nthreads) atomicOr(sems + i, kAbortedSemaphoreBit);
+  __threadfence();
+}
+
 // Spin until *sem >= expected.  Returns false (after recording why) when the
 // bound expires.  Called by ONE thread; the caller broadcasts the outcome.
 CUSYNC_DEVICE bool spinUntilAtLeast(const uint32_t* sem, uint32_t expected, uint64_t timeoutNs,

@@ -288,8 +288,16 @@ CUSYNC_API int cusync_gemm_plan_tail_split(const cusync_gemm_plan_t* plan);
  * caches it; make that first call outside any stream capture.  All calls on a device share the one
  * array, which keeps the last call's contents: each call re-arms it on `stream` before its kernel,
  * so calls issued to one stream are safe back to back, while calls that can overlap on the GPU
- * (different streams, no dependency) race on it and must be serialised by the caller. */
+ * (different streams, no dependency) race on it and must be serialised by the caller.
+ *
+ * It runs the one-CTA-per-tile kernel without K slices: desc->split_k > 1, desc->cta_pair == 2 and
+ * desc->tail_split > 1 are refused with CUSYNC_ERROR_UNSUPPORTED (those forms need a workspace or a schedule
+ * that only the plan-based path allocates); 0 and 1 are accepted. */
 CUSYNC_API int cusync_gemm_run_noalloc(const cusync_gemm_desc_t* desc, cusync_stream_t stream);
+/* The timeout record of the most recent cusync_gemm_run_noalloc on the current device (it lives in the same
+ * fixed array, so no stage handle gives access to it): code 0 when every bounded wait inside the kernel
+ * completed.  A synchronous device-to-host copy of 32 bytes; allocates nothing.  No counterpart in the reference. */
+CUSYNC_API int cusync_gemm_noalloc_read_status(cusync_status_t* out);
 
 /* Optional per-tile timeline, the only profiling hook beyond CUDA events: with a device buffer of
  * 8 * capacity_tiles 64-bit words set, every tile writes, at index 8 * ticket (CTA-pair kernel:

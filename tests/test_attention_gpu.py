@@ -60,6 +60,8 @@ def test_config4_attention_block_chain(B, S):
     blk = AttentionBlock(x, w_qkv, kc, vc, w_o, heads)
     streams = (torch.cuda.Stream(priority=-1), torch.cuda.Stream(), torch.cuda.Stream())
     qkv_ref = o.gemm_f16(x.cpu().numpy(), w_qkv.cpu().numpy())
+    # the oracle's own chain end to end: projection -> attention over the cache -> projection
+    y_ref = o.gemm_f16(_oracle_attention(qkv_ref, kc.cpu().numpy(), vc.cpu().numpy(), heads), w_o.cpu().numpy())
     torch.cuda.synchronize()
     for it in range(1, 4):
         blk.qkv.fill_(float("nan")); blk.o.fill_(float("nan")); blk.y.fill_(float("nan"))   # poison
@@ -72,6 +74,8 @@ def test_config4_attention_block_chain(B, S):
         o_gpu = blk.o.cpu().numpy()
         assert o.max_rel_err(o_gpu, _oracle_attention(qkv, kc.cpu().numpy(), vc.cpu().numpy(), heads)) <= TOL
         assert o.max_rel_err(blk.y.cpu().numpy(), o.gemm_f16(o_gpu, w_o.cpu().numpy())) <= TOL
+        # ... and the final output against the oracle's full chain, at the same tolerance
+        assert o.max_rel_err(blk.y.cpu().numpy(), y_ref) <= TOL
         # semaphores: three per row panel of the QKV stage (Q, K, V thirds), each reaching its 6 column tiles;
         # one per row panel of the attention stage
         tiles_m = (B + 127) // 128

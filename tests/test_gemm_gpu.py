@@ -499,3 +499,123 @@ def test_chain_with_the_wait_as_a_stream_operation(policy):
     # Optimizations.StreamWait: invokeWaitKernel enqueues a stream wait on the producer's "blocks started" word
     _chain(policy, 640, 1024, 512, 1024, 256, 256, iters=3, opts=cs.Optimizations.StreamWait, max_ctas=4, cta_pair=2)
     _chain(policy, 256, 1024, 1024, 1024, 128, 128, iters=2, opts=cs.Optimizations.StreamWait)
+
+
+def test_strided_tile_sync_chain_of_the_unfused_llama_layer():
+    # The reference's LLaMA chain (mlp.cu:103-109, 762-792): the first GEMM writes [X W1 | X V] side by side
+    # (N = 2 d) and posts StridedSync<TransposeXY, d, TM, TN, 2>: column tiles j and j + d / TN share semaphore j,
+    # which reaches 2 per run; the second GEMM reads the first d columns through the leading dimension 2 d and
+    # waits for 2.  d = 2816 as in the reference, 128-wide producer tiles: 44 column tiles, 22 semaphores per row.
+    M, K1, d, N2, TN = 300, 512, 2816, 768, 128
+    a = _rand((M, K1), 80, dist="normal")
+    w1v = _rand((K1, 2 * d), 81, scale=0.05, dist="normal")
+    w2 = _rand((d, N2), 82, scale=0.03, dist="normal")
+    buf = torch.empty((M, 2 * d), device="cuda", dtype=torch.half)
+    y = torch.empty((M, N2), device="cuda", dtype=torch.half)
+    grid1 = cs.gemm_tiled_shape(M, 2 * d, 128, TN)
+    grid2 = cs.gemm_tiled_shape(M, N2, 128, 256)
+    assert grid1 == (44, 3, 1)
+    sync = cs.StridedTileSync(cs.TransposeXYOrder, d, 128, TN, 2)
+    prod = cs.CuStage(cs.TransposeXYOrder, grid1, (1, 1, 1), cs.NoSync(), sync)     # two posters per semaphore: atomics
+    cons = cs.CuStage(cs.TransposeXYOrder, grid2, (1, 1, 1), sync, cs.NoSync())
+    assert cs.CuSync.setProducerConsumerPair(prod, cons) == L.SUCCESS
+    g1, g2 = cs.Gemm(), cs.Gemm()
+    # few blocks, so that the second GEMM really waits for column tiles of both halves
+    assert g1.initialize(cs.GemmArguments(prod, (M, 2 * d, K1), a, w1v, buf, tile_n=TN, max_ctas=8,
+                                          split_k_slices=1)) == L.SUCCESS
+    assert g2.initialize(cs.GemmArguments(cons, (M, N2, d), buf[:, :d], w2, y, tile_n=256, max_ctas=8,
+                                          split_k_slices=1, cta_pair=1)) == L.SUCCESS
+    ref1 = o.gemm_f16(a.cpu().numpy(), w1v.cpu().numpy())
+    yref = o.gemm_f16(np.ascontiguousarray(ref1[:, :d]), w2.cpu().numpy())
+    opol = o.policy(o.STRIDEDSYNC, o.ORDER_TRANSPOSE_XY, 128, TN, 0, 0, p0=d, p1=2)
+    ps, cst = torch.cuda.Stream(priority=-1), torch.cuda.Stream()
+    torch.cuda.synchronize()
+    for it in range(1, 4):
+        buf.fill_(float("nan")); y.fill_(float("nan")); torch.cuda.synchronize()
+        assert g1.run(True, None, ps) == L.SUCCESS
+        assert prod.invokeWaitKernel(cst) == L.SUCCESS
+        assert g2.run(True, None, cst) == L.SUCCESS
+        torch.cuda.synchronize()
+        assert prod.status().code == 0 and cons.status().code == 0
+        assert o.max_rel_err(buf.cpu().numpy(), ref1) <= TOL
+        assert o.max_rel_err(y.cpu().numpy(), yref) <= TOL
+        sems = prod.semaphores().reshape(3, 44)
+        assert (sems[:, :22] == 2 * it).all() and (sems[:, 22:] == 0).all()
+        exp, oob = o.producer_semaphores(opol, grid1, 128, TN, 0, it)
+        assert oob == 0 and (prod.semaphores() == exp).all()
+        prod.incrementIter(); cons.incrementIter()
+    g1.destroy(); g2.destroy(); prod.destroy(); cons.destroy()
+
+
+@pytest.mark.parametrize("kernel", ["split_k", "tail_split"])
+def test_consumer_k_slices_that_begin_inside_a_producer_tile_wait_for_it(kernel):
+    # TileSync, producer tiles 256 wide, consumer K = 1024 cut into three slices: the slices begin at K offsets
+    # 0, 384 and 768, the second one in the middle of producer tile 1.  Its first K block has to wait for that
+    # tile although 384 is not a multiple of the producer's tile width.  The producer is slow (long K, few
+    # blocks) and H is poisoned, so a slice that read ahead would put NaN into Y.
+    M, K1, N1, N2 = 512, 8192, 1024, 1024
+    a = _rand((M, K1), 90, dist="normal", scale=0.5)
+    w1 = _rand((K1, N1), 91, scale=0.02, dist="normal")
+    w2 = _rand((N1, N2), 92, scale=0.03, dist="normal")
+    h = torch.empty((M, N1), device="cuda", dtype=torch.half)
+    y = torch.empty((M, N2), device="cuda", dtype=torch.half)
+    split = 3 if kernel == "split_k" else 1
+    grid1 = cs.gemm_tiled_shape(M, N1, 128, 256)
+    grid2 = cs.gemm_tiled_shape(M, N2, 128, 256, split)
+    sync = cs.TileSync(cs.TransposeXYOrder, 128, 256)
+    prod = cs.CuStage(cs.TransposeXYOrder, grid1, (1, 1, 1), cs.NoSync(), sync)
+    cons = cs.CuStage(cs.TransposeXYOrder, grid2, (1, 1, 1), sync, cs.NoSync())
+    assert cs.CuSync.setProducerConsumerPair(prod, cons) == L.SUCCESS
+    g1, g2 = cs.Gemm(), cs.Gemm()
+    assert g1.initialize(cs.GemmArguments(prod, (M, N1, K1), a, w1, h, tile_n=256, max_ctas=4, cta_pair=1,
+                                          split_k_slices=1)) == L.SUCCESS
+    if kernel == "split_k":     # one CTA per tile, three K slices per tile
+        assert g2.initialize(cs.GemmArguments(cons, (M, N2, N1), h, w2, y, tile_n=256, max_ctas=12, cta_pair=1,
+                                              split_k_slices=3)) == L.SUCCESS
+    else:                       # CTA pairs: 8 pair tiles on 3 clusters, the 2 left over cut into 3 slices each
+        assert g2.initialize(cs.GemmArguments(cons, (M, N2, N1), h, w2, y, tile_n=256, max_ctas=6, cta_pair=2,
+                                              split_k_slices=1, tail_split=3)) == L.SUCCESS
+        assert g2.tail_split() == 3
+    href = o.gemm_f16(a.cpu().numpy(), w1.cpu().numpy())
+    yref = o.gemm_f16(href, w2.cpu().numpy())
+    ps, cst = torch.cuda.Stream(priority=-1), torch.cuda.Stream()
+    torch.cuda.synchronize()
+    for it in range(1, 4):
+        h.fill_(float("nan")); y.fill_(float("nan")); torch.cuda.synchronize()
+        assert g1.run(True, None, ps) == L.SUCCESS
+        assert prod.invokeWaitKernel(cst) == L.SUCCESS
+        assert g2.run(True, None, cst) == L.SUCCESS
+        torch.cuda.synchronize()
+        assert prod.status().code == 0 and cons.status().code == 0
+        assert not torch.isnan(y.float()).any()
+        assert o.max_rel_err(y.cpu().numpy(), yref) <= TOL
+        assert (prod.semaphores() == it).all()
+        prod.incrementIter(); cons.incrementIter()
+    g1.destroy(); g2.destroy(); prod.destroy(); cons.destroy()
+
+
+def test_policies_built_for_another_tile_shape_are_refused():
+    a = _rand((256, 512), 95); b = _rand((512, 512), 96)
+    d = torch.empty((256, 512), device="cuda", dtype=torch.half)
+    g = cs.Gemm()
+    # producer: 128-wide policy tiles on a 256-wide kernel tile would post past the end of the semaphore array
+    st = cs.CuStage(cs.TransposeXYOrder, (2, 2, 1), (1, 1, 1), cs.NoSync(), cs.TileSync(cs.TransposeXYOrder, 128, 128))
+    assert g.initialize(cs.GemmArguments(st, (256, 512, 512), a, b, d, tile_n=256, cta_pair=1,
+                                         split_k_slices=1)) == L.ERROR_INVALID_ARGUMENT
+    st.destroy()
+    # consumer: a block loads 128 rows but a 64-row policy tile covers only the first half of them
+    narrow = cs.TileSync(cs.TransposeXYOrder, 64, 128)
+    prod = cs.CuStage(cs.TransposeXYOrder, (4, 4, 1), (1, 1, 1), cs.NoSync(), narrow)
+    cons = cs.CuStage(cs.TransposeXYOrder, (2, 2, 1), (1, 1, 1), narrow, cs.NoSync())
+    assert cs.CuSync.setProducerConsumerPair(prod, cons) == L.SUCCESS
+    assert g.initialize(cs.GemmArguments(cons, (256, 512, 512), a, b, d, tile_n=256, cta_pair=1,
+                                         split_k_slices=1)) == L.ERROR_INVALID_ARGUMENT
+    prod.destroy(); cons.destroy()
+    # consumer: policy tiles that are not whole 64-element K blocks
+    odd = cs.TileSync(cs.TransposeXYOrder, 128, 96)
+    prod = cs.CuStage(cs.TransposeXYOrder, (6, 2, 1), (1, 1, 1), cs.NoSync(), odd)
+    cons = cs.CuStage(cs.TransposeXYOrder, (2, 2, 1), (1, 1, 1), odd, cs.NoSync())
+    assert cs.CuSync.setProducerConsumerPair(prod, cons) == L.SUCCESS
+    assert g.initialize(cs.GemmArguments(cons, (256, 512, 512), a, b, d, tile_n=256, cta_pair=1,
+                                         split_k_slices=1)) == L.ERROR_INVALID_ARGUMENT
+    prod.destroy(); cons.destroy()

@@ -82,6 +82,24 @@ def test_noalloc_dual_gemm_after_a_plain_one():
     torch.cuda.synchronize()
     expect = _plan_based(a, b1, L.EPILOGUE_SILU_MUL_DUAL, 64, b2)
     assert o.max_rel_err(d.cpu().numpy(), expect.cpu().numpy()) <= TOL
+    ref = o.gemm_dual_silu_mul_f16(a.cpu().numpy(), b1.cpu().numpy(), b2.cpu().numpy())
+    assert o.max_rel_err(d.cpu().numpy(), ref) <= TOL
+    # the call left no timeout record in the static array
+    status = L.Status()
+    assert L.lib().cusync_gemm_noalloc_read_status(C.byref(status)) == L.SUCCESS
+    assert status.code == 0
+
+
+def test_noalloc_refuses_the_kernel_forms_it_does_not_run():
+    stream = torch.cuda.current_stream().cuda_stream
+    a = _rand((512, 256), 7); b = _rand((256, 512), 8, 0.1)
+    d = torch.zeros((512, 512), device="cuda", dtype=torch.half)
+    for split_k, cta_pair, tail_split in ((2, 0, 0), (0, 2, 0), (0, 0, 2)):
+        desc = L.GemmDesc(512, 512, 256, a.data_ptr(), 256, b.data_ptr(), 512, None, d.data_ptr(), 512,
+                          L.B_ROW_MAJOR_KN, L.EPILOGUE_NONE, 256, 0, split_k, cta_pair, tail_split, None)
+        assert L.lib().cusync_gemm_run_noalloc(C.byref(desc), stream) == L.ERROR_UNSUPPORTED
+    torch.cuda.synchronize()
+    assert (d == 0).all()
 
 
 def test_noalloc_refuses_more_tiles_than_its_scratch_and_stage_handles():
