@@ -265,8 +265,7 @@ def main():
     shard = build(args.batch, args.policy)
 
     def cusync_step():
-        # a step may not overwrite H while the previous consumer still reads it
-        ps.wait_stream(cs)
+        # (the driver orders a run after the previous one: a step may not overwrite H while it is still read)
         shard.run_cusync(ps, cs)
         if overlap_reduce:
             group.all_reduce_rows_overlapped(shard, comm, args.reduce_chunks)
@@ -453,7 +452,6 @@ def main():
                 s = build(b, pol)
 
                 def c_step(s=s):
-                    ps.wait_stream(cs)
                     s.run_cusync(ps, cs)
 
                 def o_step(s=s):
@@ -466,8 +464,16 @@ def main():
                 row[pol + "_gain_pct"] = round(100.0 - c_us / o_us * 100.0, 2)
                 row["tile_n"] = [s.tile_n1, s.tile_n2]
                 row["split_k"] = [s.split_k1, s.split_k2]
+                row["single_grid"] = s.single_grid
                 if s.status_codes() != (0, 0):
                     row["error"] = "bounded wait expired"
+                if s.single_grid and pol == "rowsync":
+                    # the reference-shaped form of the same layer: one launch per GEMM and a wait kernel
+                    x2 = s.x; s.destroy()
+                    s = M.MLPShard("gpt3", b, x2, s.w1, s.w2, None, policy=pol, single_grid=1)
+                    c_per, o_per = interleaved(lambda s=s: s.run_cusync(ps, cs), (ps, cs),
+                                               lambda s=s: s.run_stream_ordered(cs), (cs, cs), 20, 5)
+                    row["rowsync_two_launches_us"] = round(statistics.median(c_per) * 1000, 2)
                 s.destroy()
             # context only, as in the reference's tables (their "torch" column): the same layer through the vendor
             # library, y = gelu(x @ w1) @ w2 on one stream (cuBLAS GEMMs + an elementwise kernel), timed alike
@@ -582,7 +588,9 @@ def main():
             "layer_frac_of_sustained_peak": shard.flops() / (ms_per_step * 1e-3) / 1e12 / peaks["tflops_sustained"],
             "roofline": roofline,
             "e2e": {"value": e2e_us, "unit": UNIT, "h2d_bytes_per_step": io_bytes, "d2h_bytes_per_step": io_bytes},
-            "gpu_launches": 3 * args.steps,
+            "gpu_launches": (1 if shard.single_grid else 3) * args.steps,
+            "launch_form": ("one persistent grid for both GEMMs" if shard.single_grid
+                            else "one launch per GEMM and a wait kernel"),
             "clocks": clocks,
             "per_batch": table,
             "other_workloads": extras}

@@ -97,9 +97,21 @@ class MlpDesc(C.Structure):
                 ("split_k1", C.c_int32), ("split_k2", C.c_int32), ("max_ctas", C.c_int32), ("cta_pair", C.c_int32), ("group_rows2", C.c_int32),
                 ("tail_split_sync1", C.c_int32), ("tail_split_sync2", C.c_int32),
                 ("tail_split_plain1", C.c_int32), ("tail_split_plain2", C.c_int32), ("group_rows1", C.c_int32),
-                ("x_rows", C.c_int32), ("post_rows", C.c_int32),
+                ("x_rows", C.c_int32), ("single_grid", C.c_int32), ("post_rows", C.c_int32),
                 ("x", C.c_void_p), ("w1", C.c_void_p), ("v", C.c_void_p), ("w2", C.c_void_p),
                 ("h", C.c_void_p), ("y", C.c_void_p)]
+
+
+class AllReduceDesc(C.Structure):
+    _fields_ = [("rank", C.c_int32), ("world", C.c_int32), ("rows", C.c_int32), ("cols", C.c_int32),
+                ("ld", C.c_int64), ("tile_rows", C.c_int32), ("num_ctas", C.c_int32),
+                ("buffers", C.POINTER(C.c_void_p)), ("flags", C.POINTER(C.c_void_p)),
+                ("multicast_buffer", C.c_void_p), ("multicast_flags", C.c_void_p), ("timeout_ns", C.c_uint64)]
+
+
+class MlpChoice(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("policy", "single_grid", "stream_wait", "group_rows1", "group_rows2",
+                                         "tile_n1", "tile_n2", "split_k1", "split_k2")]
 
 
 MLP_GPT3, MLP_LLAMA = 0, 1
@@ -134,6 +146,11 @@ SIGNATURES = {
     "cusync_gemm_plan_update": (_i, [_vp, _vp, _vp, _vp, _vp]),
     "cusync_gemm_run": (_i, [_vp, _vp]),
     "cusync_gemm_plan_tail_split": (_i, [_vp]),
+    "cusync_gemm_run_chain": (_i, [_vp, _vp, _vp]),
+    "cusync_gemm_chain_supported": (_i, [_vp, _vp]),
+    "cusync_gemm_chain_prepare": (_i, []),
+    "cusync_mlp_uses_single_grid": (_i, [_vp]),
+    "cusync_mlp_choose_config": (_i, [C.c_int32] * 4 + [C.POINTER(MlpChoice)]),
     "cusync_gemm_run_noalloc": (_i, [C.POINTER(GemmDesc), _vp]),
     "cusync_gemm_noalloc_read_status": (_i, [C.POINTER(Status)]),
     "cusync_gemm_plan_set_trace": (_i, [_vp, _vp, _u32]),
@@ -173,6 +190,13 @@ SIGNATURES = {
     "cusync_mlp_tail_splits": (_i, [_vp, C.POINTER(C.c_int32)]),
     "cusync_mlp_wait_rows": (_i, [_vp, _u32, _u32, _vp]),
     "cusync_mlp_post_x_rows": (_i, [_vp, _u32, _u32, _vp]),
+    "cusync_allreduce_flag_words": (_u32, [C.c_int32, C.c_int32]),
+    "cusync_allreduce_plan_create": (_i, [C.POINTER(_vp), C.POINTER(AllReduceDesc)]),
+    "cusync_allreduce_plan_destroy": (_i, [_vp]),
+    "cusync_allreduce_run": (_i, [_vp, _vp, _u32, _vp]),
+    "cusync_allreduce_read_status": (_i, [_vp, C.POINTER(Status)]),
+    "cusync_allreduce_plan_num_ctas": (_u32, [_vp]),
+    "cusync_mlp_run_cusync_allreduce": (_i, [_vp, _vp, _vp, _vp, _vp]),
     "cusync_b200_version": (C.c_char_p, []),
     "cusync_b200_sm_count": (_i, []),
 }

@@ -274,6 +274,11 @@ class Gemm:
     def run(self, overlap=True, unused=None, stream=None):
         return L.lib().cusync_gemm_run(self._plan, _stream_ptr(stream))
 
+    @staticmethod
+    def run_chain(first, second, stream=None):
+        """Both GEMMs as one persistent grid (cusync_gemm_run_chain): `second` consumes what `first` produces."""
+        return L.lib().cusync_gemm_run_chain(first._plan, second._plan, _stream_ptr(stream))
+
     def num_ctas(self):
         return L.lib().cusync_gemm_plan_num_ctas(self._plan)
 

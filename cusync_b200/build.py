@@ -11,7 +11,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 LIB = os.path.join(HERE, "libcusync_b200.so")
-SOURCES = ["stage.cu", "gemm_sm100.cu", "mlp_driver.cu", "attention.cu", "conv_driver.cu", "attention_driver.cu"]
+SOURCES = ["stage.cu", "gemm_sm100.cu", "mlp_driver.cu", "attention.cu", "conv_driver.cu", "attention_driver.cu", "allreduce.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]

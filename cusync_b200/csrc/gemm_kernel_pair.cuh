@@ -128,10 +128,18 @@ struct PairCfg {
   static_assert(kSmemBytes <= kSmemLimit, "shared memory over budget");
 };
 
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
-cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                        const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmWS,
-                        const GemmParams p) {
+// The kernel body serves one GEMM (kChain = false) or a chain of two dependent GEMMs run by ONE persistent grid
+// (kChain = true): the work units of the first GEMM take the tickets [0, units of GEMM 0), those of the second
+// the tickets after them, from one shared counter.  A pair that finds no unit of the first GEMM left goes
+// straight on to units of the second, whose waits on the first GEMM's semaphores are the usual ones; no second
+// launch, no wait kernel, and no pair sits idle while the first GEMM's last round runs.  It cannot deadlock:
+// every pair of the grid is resident, tickets are drawn in order, a pair works through its tickets in order,
+// and a unit only ever waits for units with lower tickets.
+template <bool kChain>
+__device__ __forceinline__ void pair_kernel_body(const CUtensorMap* mA0, const CUtensorMap* mB0, const CUtensorMap* mD0,
+                                                 const CUtensorMap* mWS0, const CUtensorMap* mA1, const CUtensorMap* mB1,
+                                                 const CUtensorMap* mD1, const CUtensorMap* mWS1, const GemmParams& p0,
+                                                 const GemmParams& p1) {
   using C = PairCfg;
   constexpr int BN = kPairBN;
   extern __shared__ uint8_t smem_raw[];
@@ -144,8 +152,10 @@ cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();          // 0 = leader: draws tickets, issues the MMAs
   const bool leader = rank == 0;
-  const cusync_stage_view_t& st = p.stage;
-  WaitCtx ctx{&bars->abort, st.status, 2 * st.timeout_ns + 1000000000ull};
+  // Bounded barrier waits record into the first GEMM's stage.
+  WaitCtx ctx{&bars->abort, p0.stage.status, 2 * p0.stage.timeout_ns + 1000000000ull};
+  const uint32_t units0 = static_cast<uint32_t>(p0.num_pairs);
+  const uint32_t total_units = units0 + (kChain ? static_cast<uint32_t>(p1.num_pairs) : 0u);
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < C::kStages; i++) { mbar_init(&bars->full[i], 1); mbar_init(&bars->empty[i], 1); }
@@ -164,12 +174,18 @@ cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     bars->abort = 0u;
     fence_barrier_init();
     fence_proxy_async_smem();
-    if (p.is_producer) {
-      if (blockIdx.x == 0) cusync::storeRelease(st.started, st.iter);
-      cusync::addRelease(st.started + 1, 1u);
+    for (int gi = 0; gi < (kChain ? 2 : 1); gi++) {
+      const GemmParams& pg = gi ? p1 : p0;
+      if (pg.is_producer) {
+        if (blockIdx.x == 0) cusync::storeRelease(pg.stage.started, pg.stage.iter);
+        cusync::addRelease(pg.stage.started + 1, 1u);
+      }
     }
   }
-  if (warp == 0 && lane == 0) { prefetch_tensormap(&tmA); prefetch_tensormap(&tmB); prefetch_tensormap(&tmD); }
+  if (warp == 0 && lane == 0) {
+    prefetch_tensormap(mA0); prefetch_tensormap(mB0); prefetch_tensormap(mD0);
+    if (kChain) { prefetch_tensormap(mA1); prefetch_tensormap(mB1); prefetch_tensormap(mD1); }
+  }
   if (warp == 2) {
     tmem_alloc_pair(&bars->tmem_base, C::kTmemCols);
     tmem_relinquish_pair();
@@ -192,34 +208,31 @@ cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     if (lane == 0) {
       uint32_t fills = 0, sched_it = 0;
       bool ok = true;
-      const uint32_t total_draws = static_cast<uint32_t>(p.num_pairs) + gridDim.x / 2;
-      const uint32_t wait_target = p.is_consumer ? st.iter * cusync::eval::waitValue(st.in_policy) : 0u;
-      uint32_t sync_stride = 0;
-      if (p.is_consumer) {
-        const int kind = st.in_policy.kind;
-        if (kind == CUSYNC_POLICY_TILESYNC || kind == CUSYNC_POLICY_STRIDEDTILESYNC) sync_stride = st.in_policy.tile_n;
-        else if (kind == CUSYNC_POLICY_CONV2DTILESYNC) sync_stride = st.in_policy.tile_n * st.in_policy.p0;
-      }
+      const uint32_t total_draws = total_units + gridDim.x / 2;
+      uint32_t* const ticket_counter = p0.stage.tile_counter;     // one counter for the whole chain
       const uint32_t peer_sched_tile0 = map_to_cta(smem_u32(&bars->sched_tile[0][0]), 1);
       const uint32_t peer_sched_time0 = map_to_cta(smem_u32(&bars->sched_time[0]), 1);
       const uint32_t peer_sched_full0 = map_to_cta(smem_u32(&bars->sched_full[0]), 1);
       while (ok) {
         const uint32_t slot = sched_it % kSchedSlots, sph = (sched_it / kSchedSlots) & 1u;
-        int32_t tn, tpm, valid, tz_slice = 0, nslices = 1;
+        int32_t tn, tpm, valid, tz_slice = 0, nslices = 1, gi = 0;
         if (leader) {
           if (!mbar_wait_cluster(&bars->sched_empty[slot], sph ^ 1u, ctx)) { ok = false; break; }
-          const uint32_t ticket = atomicAdd(st.tile_counter, 1u);
-          if (ticket == total_draws - 1u) atomicExch(st.tile_counter, 0u);   // last draw of the launch
-          valid = ticket < static_cast<uint32_t>(p.num_pairs) ? 1 : 0;
+          const uint32_t drawn = atomicAdd(ticket_counter, 1u);
+          if (drawn == total_draws - 1u) atomicExch(ticket_counter, 0u);   // last draw of the launch
+          valid = drawn < total_units ? 1 : 0;
+          gi = (kChain && drawn >= units0) ? 1 : 0;
+          const uint32_t ticket = gi ? drawn - units0 : drawn;              // index in that GEMM's own schedule
           PairUnit t = {0, 0, 1u << 16, 0};
-          if (valid) t = p.pair_order[ticket];
+          if (valid) t = (gi ? p1 : p0).pair_order[ticket];
           tn = static_cast<int32_t>(t.x); tpm = static_cast<int32_t>(t.y);
           tz_slice = static_cast<int32_t>(t.slice_of & 0xffffu); nslices = static_cast<int32_t>(t.slice_of >> 16);
-          const unsigned long long now = p.trace ? cusync::globalTimerNs() : 0ull;
+          const unsigned long long now = (p0.trace || (kChain && p1.trace)) ? cusync::globalTimerNs() : 0ull;
           bars->sched_tile[slot][0] = tn; bars->sched_tile[slot][1] = tpm;
           bars->sched_tile[slot][2] = valid; bars->sched_tile[slot][3] = static_cast<int32_t>(ticket);
           bars->sched_tile[slot][4] = tz_slice; bars->sched_tile[slot][5] = nslices;
           bars->sched_tile[slot][6] = static_cast<int32_t>(t.ws_tile);
+          bars->sched_tile[slot][7] = gi;
           bars->sched_time[slot] = now;
           // the same record into the peer's ring, then signal both
           const uint32_t pt = peer_sched_tile0 + slot * 32;
@@ -227,6 +240,7 @@ cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
           st_cluster_u32(pt + 8, static_cast<uint32_t>(valid)); st_cluster_u32(pt + 12, ticket);
           st_cluster_u32(pt + 16, static_cast<uint32_t>(tz_slice)); st_cluster_u32(pt + 20, static_cast<uint32_t>(nslices));
           st_cluster_u32(pt + 24, t.ws_tile);
+          st_cluster_u32(pt + 28, static_cast<uint32_t>(gi));
           st_cluster_u32(peer_sched_time0 + slot * 8, static_cast<uint32_t>(now));
           st_cluster_u32(peer_sched_time0 + slot * 8 + 4, static_cast<uint32_t>(now >> 32));
           mbar_arrive(&bars->sched_full[slot]);
@@ -235,11 +249,24 @@ cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
           if (!mbar_wait_cluster(&bars->sched_full[slot], sph, ctx)) { ok = false; break; }
           tn = bars->sched_tile[slot][0]; tpm = bars->sched_tile[slot][1]; valid = bars->sched_tile[slot][2];
           tz_slice = bars->sched_tile[slot][4]; nslices = bars->sched_tile[slot][5];
+          gi = kChain ? bars->sched_tile[slot][7] : 0;
           mbar_arrive_cluster(leader_sched_empty0 + slot * 8);
         }
         sched_it++;
         if (!valid) break;
 
+        // The GEMM this unit belongs to: its parameters, stage and tensor maps.
+        const GemmParams& p = gi ? p1 : p0;
+        const cusync_stage_view_t& st = p.stage;
+        const CUtensorMap* const tmA = gi ? mA1 : mA0;
+        const CUtensorMap* const tmB = gi ? mB1 : mB0;
+        const uint32_t wait_target = p.is_consumer ? st.iter * cusync::eval::waitValue(st.in_policy) : 0u;
+        uint32_t sync_stride = 0;
+        if (p.is_consumer) {
+          const int kind = st.in_policy.kind;
+          if (kind == CUSYNC_POLICY_TILESYNC || kind == CUSYNC_POLICY_STRIDEDTILESYNC) sync_stride = st.in_policy.tile_n;
+          else if (kind == CUSYNC_POLICY_CONV2DTILESYNC) sync_stride = st.in_policy.tile_n * st.in_policy.p0;
+        }
         const int n_off = tn * BN;
         const int m_off = tpm * (2 * kBlockM) + static_cast<int>(rank) * kBlockM;   // this CTA's 128 rows
         const int nb_off = n_off + static_cast<int>(rank) * (BN / 2);               // this CTA's half of B
@@ -261,8 +288,8 @@ cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
           const int k_base = kb * kPairBlockK;
           // B half: one 3-D box.  [k,n] weights: {64 columns, 128 k rows, 2 column chunks};
           // [n,k] weights: {64 k, 128 n rows, 2 k chunks}.
-          if (p.b_kmajor) tma_load_3d_pair(sb, &tmB, full_addr, 0, nb_off, k_base / 64);
-          else            tma_load_3d_pair(sb, &tmB, full_addr, 0, k_base, nb_off / 64);
+          if (p.b_kmajor) tma_load_3d_pair(sb, tmB, full_addr, 0, nb_off, k_base / 64);
+          else            tma_load_3d_pair(sb, tmB, full_addr, 0, k_base, nb_off / 64);
           // The stage spans two 64-deep K chunks; each may open a new producer tile.
 #pragma unroll 1
           for (int sub = 0; sub < kPairBlockK / kBlockK && ok; sub++) {
@@ -330,7 +357,7 @@ cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
           }
           // A: {64 k, 128 rows, 2 k chunks}.  Issued on the abort path too, so that the armed barrier
           // completes and the drain below terminates.
-          tma_load_3d_pair(sa, &tmA, full_addr, 0, m_off, k_base / 64);
+          tma_load_3d_pair(sa, tmA, full_addr, 0, m_off, k_base / 64);
           fills++;
           if (!ok) break;
         }
@@ -366,10 +393,6 @@ cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     // MMA issuer (leader only)
     // =====================================================================
     if (lane == 0 && leader) {
-      // instruction descriptor: M = 256 across the pair, N = 256
-      const uint32_t idesc = (1u << 4) | ((p.b_kmajor ? 0u : 1u) << 16) | (static_cast<uint32_t>(BN >> 3) << 17) |
-                             (static_cast<uint32_t>((2 * kBlockM) >> 4) << 24);
-      const uint32_t b_lbo = p.b_lbo, b_sbo = p.b_sbo, b_kstep = p.b_kstep;
       uint32_t drains = 0, sched_it = 0, acc_it = 0;
       bool ok = true, issued = false;
       while (ok) {
@@ -379,9 +402,14 @@ cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         const uint32_t ticket = static_cast<uint32_t>(bars->sched_tile[slot][3]);
         const int slice = bars->sched_tile[slot][4];
         const int nslices = bars->sched_tile[slot][5];
+        const GemmParams& p = (kChain && bars->sched_tile[slot][7]) ? p1 : p0;
         mbar_arrive(&bars->sched_empty[slot]);
         sched_it++;
         if (!valid) break;
+        // instruction descriptor: M = 256 across the pair, N = 256
+        const uint32_t idesc = (1u << 4) | ((p.b_kmajor ? 0u : 1u) << 16) | (static_cast<uint32_t>(BN >> 3) << 17) |
+                               (static_cast<uint32_t>((2 * kBlockM) >> 4) << 24);
+        const uint32_t b_lbo = p.b_lbo, b_sbo = p.b_sbo, b_kstep = p.b_kstep;
         const uint32_t acc = acc_it & 1u, aph = (acc_it >> 1) & 1u;
         const long long t_tile0 = p.trace ? clock64() : 0;
         if (!mbar_wait_cluster(&bars->tmem_empty[acc], aph ^ 1u, ctx)) { ok = false; break; }
@@ -452,11 +480,16 @@ cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
       const uint32_t slice = static_cast<uint32_t>(bars->sched_tile[slot][4]);
       const uint32_t ticket = static_cast<uint32_t>(bars->sched_tile[slot][3]);
       const unsigned long long t_draw = bars->sched_time[slot];
+      const int gi = kChain ? bars->sched_tile[slot][7] : 0;
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(leader_sched_empty0 + slot * 8);
       sched_it++;
       if (!valid) break;
       const uint32_t acc = acc_it & 1u, aph = (acc_it >> 1) & 1u;
+      const GemmParams& p = gi ? p1 : p0;
+      const cusync_stage_view_t& st = p.stage;
+      const CUtensorMap* const tmD = gi ? mD1 : mD0;
+      const CUtensorMap* const tmWS = gi ? mWS1 : mWS0;
       if (!mbar_wait_cluster(&bars->tmem_full[acc], aph, ctx)) { ok = false; break; }
       tc_fence_after();
       const unsigned long long t_mma_done = p.trace ? cusync::globalTimerNs() : 0ull;
@@ -468,12 +501,12 @@ cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         // One K slice of the tile: add it to the workspace; the pair that brings the last slice finalises.
         // `post` is also used by unsplit tiles, the two split-K barriers only here: separate phase counters.
         bool last = false;
-        ok = splitk_epilogue<BN>(p, &tmWS, buf, bars, ctx, t_row, n_off, m_off, quarter, half, ew, lane, post_it & 1u,
+        ok = splitk_epilogue<BN>(p, tmWS, buf, bars, ctx, t_row, n_off, m_off, quarter, half, ew, lane, post_it & 1u,
                                  split_it & 1u, nslices, nullptr, leader_tmem_empty0 + acc * 8,
                                  static_cast<__half*>(p.d), p.ldd, &last,
                                  reinterpret_cast<float4*>(p.splitk_ws) + static_cast<size_t>(ws_slot) * kPairSlotVec4 +
                                      rank * (kPairSlotVec4 / 2),
-                                 slice, &tmD);
+                                 slice, tmD);
         acc_it++;
         if (ew == 0 && lane == 0) {
           if (!mbar_wait(&bars->splitk_done, split_it & 1u, ctx)) ok = false;
@@ -498,7 +531,7 @@ cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         }
         continue;
       }
-      epilogue_store_rows<BN, false>(p, &tmD, buf, t_row, n_off, m_off + quarter * 32, half, lane);
+      epilogue_store_rows<BN, false>(p, tmD, buf, t_row, n_off, m_off + quarter * 32, half, lane);
 
       tc_fence_before();
       __syncwarp();
@@ -543,13 +576,35 @@ cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
   tc_fence_before();
   __syncthreads();
   // A block that gave up does not post its tiles: release what waits on this stage without a bound of its own.
-  if (bars->abort != 0u && p.is_producer)
-    cusync::releaseWaitersOnAbort(st.sems_post, st.grid.x * st.grid.y * st.grid.z, threadIdx.x, blockDim.x);
+  if (bars->abort != 0u) {
+    for (int gi = 0; gi < (kChain ? 2 : 1); gi++) {
+      const cusync_stage_view_t& sg = (gi ? p1 : p0).stage;
+      if ((gi ? p1 : p0).is_producer)
+        cusync::releaseWaitersOnAbort(sg.sems_post, sg.grid.x * sg.grid.y * sg.grid.z, threadIdx.x, blockDim.x);
+    }
+  }
   cluster_sync_all();
   if (warp == 2) {
     tc_fence_after();
     tmem_dealloc_pair(tmem_base, C::kTmemCols);
   }
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                        const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmWS,
+                        const GemmParams p) {
+  pair_kernel_body<false>(&tmA, &tmB, &tmD, &tmWS, &tmA, &tmB, &tmD, &tmWS, p, p);
+}
+
+// Two dependent GEMMs (both on CTA pairs) in one persistent grid; see pair_kernel_body.
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+cusync_gemm_pair_chain_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmB0,
+                              const __grid_constant__ CUtensorMap tmD0, const __grid_constant__ CUtensorMap tmWS0,
+                              const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1,
+                              const __grid_constant__ CUtensorMap tmD1, const __grid_constant__ CUtensorMap tmWS1,
+                              const __grid_constant__ GemmParams p0, const __grid_constant__ GemmParams p1) {
+  pair_kernel_body<true>(&tmA0, &tmB0, &tmD0, &tmWS0, &tmA1, &tmB1, &tmD1, &tmWS1, p0, p1);
 }
 
 }  // namespace

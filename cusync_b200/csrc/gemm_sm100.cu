@@ -743,6 +743,48 @@ int cusync_gemm_run(cusync_gemm_plan_t* pl, cusync_stream_t stream) {
   return cudaGetLastError() == cudaSuccess ? CUSYNC_SUCCESS : CUSYNC_ERROR_CUDA;
 }
 
+// Two dependent GEMMs in one persistent grid (both on the CTA-pair kernel).
+int cusync_gemm_chain_supported(const cusync_gemm_plan_t* first, const cusync_gemm_plan_t* second) {
+  return first && second && first->pair && second->pair && !first->conv_slab && !second->conv_slab ? 1 : 0;
+}
+
+// Loads the chain kernel and opts it in to its shared-memory size, once.  Called when a chain is set up (the
+// MLP driver's create) and again, as a no-op, by every run: the first run must not be the one that loads the
+// kernel, since a load can wait for kernels that are already running (an all-reduce kernel beside the chain).
+int cusync_gemm_chain_prepare(void) {
+  static bool attr_set = false;
+  if (attr_set) return CUSYNC_SUCCESS;
+  if (cudaFuncSetAttribute(reinterpret_cast<const void*>(cusync_gemm_pair_chain_kernel),
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(PairCfg::kSmemBytes)) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return CUSYNC_ERROR_CUDA;
+  }
+  attr_set = true;
+  return CUSYNC_SUCCESS;
+}
+
+int cusync_gemm_run_chain(cusync_gemm_plan_t* first, cusync_gemm_plan_t* second, cusync_stream_t stream) {
+  if (!first || !second) return CUSYNC_ERROR_NOT_INITIALIZED;
+  if (!cusync_gemm_chain_supported(first, second)) return CUSYNC_ERROR_UNSUPPORTED;
+  if (cusync_gemm_chain_prepare() != CUSYNC_SUCCESS) return CUSYNC_ERROR_CUDA;
+  GemmParams p0 = first->params, p1 = second->params;
+  cusync_stage_get_view(first->stage, &p0.stage);
+  cusync_stage_get_view(second->stage, &p1.stage);
+  p0.is_producer = p0.stage.out_policy.kind != CUSYNC_POLICY_NOSYNC;
+  p0.is_consumer = p0.stage.in_policy.kind != CUSYNC_POLICY_NOSYNC;
+  p1.is_producer = p1.stage.out_policy.kind != CUSYNC_POLICY_NOSYNC;
+  p1.is_consumer = p1.stage.in_policy.kind != CUSYNC_POLICY_NOSYNC;
+  // The grid: as many pairs as either plan may use, and no more than there are work units.
+  uint32_t ctas = first->num_ctas > second->num_ctas ? first->num_ctas : second->num_ctas;
+  const uint32_t units = static_cast<uint32_t>(p0.num_pairs) + static_cast<uint32_t>(p1.num_pairs);
+  if (ctas > 2 * units) ctas = 2 * units;
+  if (p0.is_producer) cusync_stage_note_launch(first->stage, ctas);
+  if (p1.is_producer) cusync_stage_note_launch(second->stage, ctas);
+  cusync_gemm_pair_chain_kernel<<<ctas, kThreads, PairCfg::kSmemBytes, reinterpret_cast<cudaStream_t>(stream)>>>(
+      first->tmA, first->tmB, first->tmD, first->tmWS, second->tmA, second->tmB, second->tmD, second->tmWS, p0, p1);
+  return cudaGetLastError() == cudaSuccess ? CUSYNC_SUCCESS : CUSYNC_ERROR_CUDA;
+}
+
 // ---------------------------------------------------------------------------
 // 3x3 convolution (implicit GEMM on the same kernel)
 // ---------------------------------------------------------------------------

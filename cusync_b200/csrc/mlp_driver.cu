@@ -24,9 +24,36 @@ struct cusync_mlp {
   cusync_stage_t* plain_stage1; // NoSync stages carrying the two tile orders for the baseline
   cusync_stage_t* plain_stage2;
   RunOrder order;               // run r + 1 starts after run r has finished (H and Y are reused)
+  bool single_grid;             // run_cusync launches both synchronised GEMMs as one persistent grid
+  cudaEvent_t joined;           // single grid: lets the consumer stream wait for the launch on the producer stream
+  cudaEvent_t reduced;          // overlapped all-reduce: lets the consumer stream wait for the reducer
 };
 
 namespace {
+
+// What run_cusync does when the caller leaves the choice open, by model and batch range: the role of the
+// reference's per-GPU tuning table (src/ml-bench/transformer/tile_sizes_db.py, applied by eval_mlp.py:141-210),
+// which picks tile shapes, split-K and the AvoidWaitKernel / AvoidCustomOrder / ReorderTileLoads switches per
+// batch.  Here tile shape and K slices follow from cusync_gemm_default_tile_n / _split_k; the table adds the
+// policy, the launch form and the tile orders.  Rows come from interleaved A/B sweeps on B200 (every
+// combination against the same stream-ordered layer): RowSync beats TileSync at every batch of both models;
+// one persistent grid pays from about twelve row tiles on (+1.5 to +2 points at B = 2048, nothing at 1024, a
+// loss at 512 where the first GEMM is a single round); walking the tiles in groups of rows pays from eight row
+// tiles on.
+struct ConfigRow { int model; int max_batch; int policy; int single_grid; int group_rows1; int group_rows2; };
+const ConfigRow kConfigTable[] = {
+    {CUSYNC_MLP_GPT3, 512, CUSYNC_POLICY_ROWSYNC, 1, 1, 1},
+    {CUSYNC_MLP_GPT3, 1536, CUSYNC_POLICY_ROWSYNC, 1, 4, 4},
+    {CUSYNC_MLP_GPT3, 0x7fffffff, CUSYNC_POLICY_ROWSYNC, 2, 4, 8},
+    {CUSYNC_MLP_LLAMA, 896, CUSYNC_POLICY_ROWSYNC, 1, 1, 1},
+    {CUSYNC_MLP_LLAMA, 0x7fffffff, CUSYNC_POLICY_ROWSYNC, 1, 1, 4},
+};
+
+const ConfigRow* config_row(int model, int batch) {
+  for (const ConfigRow& r : kConfigTable)
+    if (r.model == model && batch <= r.max_batch) return &r;
+  return nullptr;
+}
 
 void fill_gemm1(const cusync_mlp_desc_t& d, int tile_n, int split_k, int tail_split, cusync_stage_t* stage,
                 cusync_gemm_desc_t* g) {
@@ -66,6 +93,8 @@ void destroy_all(cusync_mlp* m) {
   if (m->plain_stage1) cusync_stage_destroy(m->plain_stage1);
   if (m->plain_stage2) cusync_stage_destroy(m->plain_stage2);
   m->order.destroy();
+  if (m->joined) cudaEventDestroy(m->joined);
+  if (m->reduced) cudaEventDestroy(m->reduced);
   delete m;
 }
 
@@ -76,17 +105,29 @@ extern "C" {
 int cusync_mlp_create(cusync_mlp_t** out, const cusync_mlp_desc_t* desc) {
   if (!out || !desc) return CUSYNC_ERROR_INVALID_ARGUMENT;
   *out = nullptr;
-  const cusync_mlp_desc_t& d = *desc;
-  if (d.model != CUSYNC_MLP_GPT3 && d.model != CUSYNC_MLP_LLAMA) return CUSYNC_ERROR_INVALID_ARGUMENT;
-  if (d.batch <= 0 || d.hidden <= 0 || d.ffn <= 0) return CUSYNC_ERROR_INVALID_ARGUMENT;
-  if (!d.x || !d.w1 || !d.w2 || !d.h || !d.y || (d.model == CUSYNC_MLP_LLAMA && !d.v))
+  const cusync_mlp_desc_t& d0 = *desc;
+  if (d0.model != CUSYNC_MLP_GPT3 && d0.model != CUSYNC_MLP_LLAMA) return CUSYNC_ERROR_INVALID_ARGUMENT;
+  if (d0.batch <= 0 || d0.hidden <= 0 || d0.ffn <= 0) return CUSYNC_ERROR_INVALID_ARGUMENT;
+  if (!d0.x || !d0.w1 || !d0.w2 || !d0.h || !d0.y || (d0.model == CUSYNC_MLP_LLAMA && !d0.v))
     return CUSYNC_ERROR_INVALID_ARGUMENT;
-  if (d.policy != CUSYNC_POLICY_ROWSYNC && d.policy != CUSYNC_POLICY_TILESYNC) return CUSYNC_ERROR_INVALID_ARGUMENT;
+  if (d0.policy != 0 && d0.policy != CUSYNC_POLICY_ROWSYNC && d0.policy != CUSYNC_POLICY_TILESYNC)
+    return CUSYNC_ERROR_INVALID_ARGUMENT;
+  if (d0.single_grid < 0 || d0.single_grid > 2 || d0.group_rows1 < 0 || d0.group_rows2 < 0) return CUSYNC_ERROR_INVALID_ARGUMENT;
+  cusync_mlp_choice_t choice;
+  if (cusync_mlp_choose_config(d0.model, d0.batch, d0.hidden, d0.ffn, &choice) != CUSYNC_SUCCESS)
+    return CUSYNC_ERROR_INVALID_ARGUMENT;
 
   cusync_mlp* m = new (std::nothrow) cusync_mlp();
   if (!m) return CUSYNC_ERROR_CUDA;
   std::memset(m, 0, sizeof(*m));
-  m->desc = d;
+  m->desc = *desc;
+  // whatever the caller left open (0) comes from the table
+  cusync_mlp_desc_t& dd = m->desc;
+  if (dd.policy == 0) dd.policy = choice.policy;
+  if (dd.group_rows1 == 0) dd.group_rows1 = choice.group_rows1;
+  if (dd.group_rows2 == 0) dd.group_rows2 = choice.group_rows2;
+  const int single_grid_wanted = dd.single_grid ? dd.single_grid : choice.single_grid;
+  const cusync_mlp_desc_t& d = m->desc;
   const int epi1 = d.model == CUSYNC_MLP_LLAMA ? CUSYNC_EPILOGUE_SILU_MUL_DUAL : CUSYNC_EPILOGUE_GELU_ERF;
   m->tile_n1 = d.tile_n1 ? d.tile_n1 : cusync_gemm_default_tile_n(d.batch, d.ffn, d.hidden, epi1);
   m->tile_n2 = d.tile_n2 ? d.tile_n2 : cusync_gemm_default_tile_n(d.batch, d.hidden, d.ffn, CUSYNC_EPILOGUE_NONE);
@@ -136,7 +177,7 @@ int cusync_mlp_create(cusync_mlp_t** out, const cusync_mlp_desc_t* desc) {
   // Consumer tile order: left to choose, batches of at least 8 row tiles take their tiles in groups of 4 rows
   // (row fastest inside a group), which re-reads W2 once per group instead of once per row; measured 4 % faster
   // at B = 1024 and 2048, neutral below.
-  const int group2 = d.group_rows2 > 1 ? d.group_rows2 : (d.group_rows2 == 0 && tiles_m >= 8 ? 4 : 0);
+  const int group2 = d.group_rows2 > 1 ? d.group_rows2 : 0;
   const int order2 = group2 > 1 ? CUSYNC_ORDER_GROUPED(group2) : CUSYNC_ORDER_TRANSPOSE_XY;
   // post_rows: the consumer publishes Y by 128-row tile as well (RowSync counting its column tiles)
   cusync_policy_t rows_out = none;
@@ -157,6 +198,20 @@ int cusync_mlp_create(cusync_mlp_t** out, const cusync_mlp_desc_t* desc) {
   if (rc == CUSYNC_SUCCESS) rc = cusync_stage_create(&m->plain_stage2, grid2, ts, order2, &none, &none, CUSYNC_OPT_NONE);
   if (rc == CUSYNC_SUCCESS) { fill_gemm2(d, m->tile_n2, m->split_k2, d.tail_split_plain2, m->plain_stage2, &g); rc = cusync_gemm_plan_create(&m->plain2, &g); }
   if (rc == CUSYNC_SUCCESS && !m->order.create()) { (void)cudaGetLastError(); rc = CUSYNC_ERROR_CUDA; }
+  if (rc == CUSYNC_SUCCESS) {
+    {
+      const bool can = cusync_gemm_chain_supported(m->sync1, m->sync2) != 0;
+      if (d.single_grid == 2 && !can) rc = CUSYNC_ERROR_UNSUPPORTED;      // asked for outright
+      m->single_grid = can && single_grid_wanted == 2;
+      if (m->single_grid && cusync_gemm_chain_prepare() != CUSYNC_SUCCESS) rc = CUSYNC_ERROR_CUDA;
+      if (rc == CUSYNC_SUCCESS && m->single_grid &&
+          cudaEventCreateWithFlags(&m->joined, cudaEventDisableTiming) != cudaSuccess) {
+        (void)cudaGetLastError();
+        m->joined = nullptr;
+        rc = CUSYNC_ERROR_CUDA;
+      }
+    }
+  }
   if (rc != CUSYNC_SUCCESS) { destroy_all(m); return rc; }
   *out = m;
   return CUSYNC_SUCCESS;
@@ -181,20 +236,71 @@ int cusync_mlp_run_single(cusync_mlp_t* m, int which, cusync_stream_t stream) {
   return cusync_gemm_run(which == 1 ? m->plain1 : m->plain2, stream);
 }
 
+namespace {
+int run_cusync_impl(cusync_mlp_t* m, cusync_allreduce_plan_t* reducer, cusync_stream_t producer_stream,
+                    cusync_stream_t consumer_stream, cusync_stream_t reduce_stream);
+}
+
 int cusync_mlp_run_cusync(cusync_mlp_t* m, cusync_stream_t producer_stream, cusync_stream_t consumer_stream) {
+  return run_cusync_impl(m, nullptr, producer_stream, consumer_stream, nullptr);
+}
+
+int cusync_mlp_run_cusync_allreduce(cusync_mlp_t* m, cusync_allreduce_plan_t* reducer, cusync_stream_t producer_stream,
+                                    cusync_stream_t consumer_stream, cusync_stream_t reduce_stream) {
+  if (!m || !reducer) return CUSYNC_ERROR_NOT_INITIALIZED;
+  if (!m->desc.post_rows) return CUSYNC_ERROR_NOT_PRODUCER;      // the second GEMM has to publish its rows
+  return run_cusync_impl(m, reducer, producer_stream, consumer_stream, reduce_stream);
+}
+
+namespace {
+int run_cusync_impl(cusync_mlp_t* m, cusync_allreduce_plan_t* reducer, cusync_stream_t producer_stream,
+                    cusync_stream_t consumer_stream, cusync_stream_t reduce_stream) {
   if (!m) return CUSYNC_ERROR_NOT_INITIALIZED;
   // The next run's first GEMM overwrites H, which this run's second GEMM reads: runs are ordered one after the other.
   if (!m->order.begin(producer_stream)) { (void)cudaGetLastError(); return CUSYNC_ERROR_CUDA; }
-  int rc = cusync_gemm_run(m->sync1, producer_stream);
-  if (rc == CUSYNC_SUCCESS) rc = cusync_stage_invoke_wait_kernel(m->prod, consumer_stream);
-  if (rc == CUSYNC_SUCCESS) rc = cusync_gemm_run(m->sync2, consumer_stream);
+  int rc;
+  if (reducer) {
+    // The reducer goes out first, so that it is resident on its SMs before the persistent GEMM blocks take the
+    // rest; it waits, tile by tile, for this run's RowSync posts of the second GEMM.
+    if (!m->order.begin(reduce_stream)) { (void)cudaGetLastError(); return CUSYNC_ERROR_CUDA; }
+    cusync_stage_view_t v;
+    cusync_stage_get_view(m->cons, &v);
+    rc = cusync_allreduce_run(reducer, v.sems_post, v.iter * v.grid.x, reduce_stream);
+    if (rc != CUSYNC_SUCCESS) return rc;
+  }
+  if (m->single_grid) {
+    // One persistent grid for both GEMMs on the producer stream; the consumer stream, where callers expect the
+    // layer's result, waits for it through an event.
+    rc = cusync_gemm_run_chain(m->sync1, m->sync2, producer_stream);
+    if (rc == CUSYNC_SUCCESS &&
+        (cudaEventRecord(m->joined, reinterpret_cast<cudaStream_t>(producer_stream)) != cudaSuccess ||
+         cudaStreamWaitEvent(reinterpret_cast<cudaStream_t>(consumer_stream), m->joined, 0) != cudaSuccess)) {
+      (void)cudaGetLastError();
+      rc = CUSYNC_ERROR_CUDA;
+    }
+  } else {
+    rc = cusync_gemm_run(m->sync1, producer_stream);
+    if (rc == CUSYNC_SUCCESS) rc = cusync_stage_invoke_wait_kernel(m->prod, consumer_stream);
+    if (rc == CUSYNC_SUCCESS) rc = cusync_gemm_run(m->sync2, consumer_stream);
+  }
   if (rc != CUSYNC_SUCCESS) return rc;      // nothing counted: the stages stay at this run's iteration
+  if (reducer) {                            // the layer's result is complete once the reducer has finished
+    if (!m->reduced) {
+      if (cudaEventCreateWithFlags(&m->reduced, cudaEventDisableTiming) != cudaSuccess) { (void)cudaGetLastError(); return CUSYNC_ERROR_CUDA; }
+    }
+    if (cudaEventRecord(m->reduced, reinterpret_cast<cudaStream_t>(reduce_stream)) != cudaSuccess ||
+        cudaStreamWaitEvent(reinterpret_cast<cudaStream_t>(consumer_stream), m->reduced, 0) != cudaSuccess) {
+      (void)cudaGetLastError();
+      rc = CUSYNC_ERROR_CUDA;
+    }
+  }
   if (!m->order.end(consumer_stream)) { (void)cudaGetLastError(); rc = CUSYNC_ERROR_CUDA; }
   if (m->input) cusync_stage_increment_iter(m->input);
   cusync_stage_increment_iter(m->prod);
   cusync_stage_increment_iter(m->cons);
   return rc;
 }
+}  // namespace
 
 int cusync_mlp_update_io(cusync_mlp_t* m, const void* x, void* y) {
   if (!m) return CUSYNC_ERROR_NOT_INITIALIZED;
@@ -267,6 +373,25 @@ int cusync_mlp_wait_rows(cusync_mlp_t* m, uint32_t first_tile, uint32_t num_tile
     rc = cusync_wait_kernel_range(v.sems_post + first_tile, num_tiles, runs * v.grid.x, stream, v.status, v.timeout_ns);
   return rc;
 }
+
+int cusync_mlp_choose_config(int32_t model, int32_t batch, int32_t hidden, int32_t ffn, cusync_mlp_choice_t* out) {
+  if (!out || batch <= 0 || hidden <= 0 || ffn <= 0) return CUSYNC_ERROR_INVALID_ARGUMENT;
+  const ConfigRow* row = config_row(model, batch);
+  if (!row) return CUSYNC_ERROR_INVALID_ARGUMENT;
+  const int epi1 = model == CUSYNC_MLP_LLAMA ? CUSYNC_EPILOGUE_SILU_MUL_DUAL : CUSYNC_EPILOGUE_GELU_ERF;
+  out->policy = row->policy;
+  out->single_grid = row->single_grid;
+  out->group_rows1 = row->group_rows1;
+  out->group_rows2 = row->group_rows2;
+  out->tile_n1 = cusync_gemm_default_tile_n(batch, ffn, hidden, epi1);
+  out->tile_n2 = cusync_gemm_default_tile_n(batch, hidden, ffn, CUSYNC_EPILOGUE_NONE);
+  out->split_k1 = cusync_gemm_default_split_k(batch, ffn, hidden, epi1, out->tile_n1, 0);
+  out->split_k2 = cusync_gemm_default_split_k(batch, hidden, ffn, CUSYNC_EPILOGUE_NONE, out->tile_n2, 0);
+  out->stream_wait = (batch + 127) / 128 <= 4 ? 1 : 0;
+  return CUSYNC_SUCCESS;
+}
+
+int cusync_mlp_uses_single_grid(const cusync_mlp_t* m) { return m && m->single_grid ? 1 : 0; }
 
 int cusync_mlp_tail_splits(const cusync_mlp_t* m, int32_t* out4) {
   if (!m || !out4) return CUSYNC_ERROR_NOT_INITIALIZED;

@@ -80,6 +80,21 @@ StreamValueFn stream_value_fn(const char* name) {
   return reinterpret_cast<StreamValueFn>(sym);
 }
 
+// With lazy module loading the first launch of a kernel loads it onto the device, and that load can wait for
+// kernels that are already running.  A wait kernel is launched exactly when a persistent producer (or an
+// all-reduce kernel spinning on semaphores) is running, so its first launch would stall the host until that
+// kernel ends: load the wait kernels when the first stage is created instead.
+void preload_wait_kernels() {
+  static bool done = false;
+  if (done) return;
+  cudaFuncAttributes a;
+  (void)cudaFuncGetAttributes(&a, waitKernel);
+  (void)cudaFuncGetAttributes(&a, waitCounterKernel);
+  (void)cudaFuncGetAttributes(&a, waitRangeKernel);
+  (void)cudaGetLastError();
+  done = true;
+}
+
 bool policy_ok(const cusync_policy_t* p) {
   if (p == nullptr) return true;
   if (p->kind < CUSYNC_POLICY_NOSYNC || p->kind > CUSYNC_POLICY_CUSTOM) return false;
@@ -171,6 +186,7 @@ int cusync_stage_create(cusync_stage_t** out, cusync_dim3_t grid, cusync_dim3_t 
   s->is_producer = s->view.out_policy.kind != CUSYNC_POLICY_NOSYNC;
   s->view.timeout_ns = cusync::kDefaultSpinTimeoutNs;
   if (cudaGetDevice(&s->device) != cudaSuccess) { delete s; return CUSYNC_ERROR_CUDA; }
+  preload_wait_kernels();
 
   // Schedule buffer: slot blockIndex(grid, block) holds block (x, y, z).  The
   // reference's two orders linearise the launch grid x-fastest; the grouped

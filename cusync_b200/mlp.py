@@ -17,23 +17,36 @@ LLAMA_HIDDEN = 8192
 LLAMA_FFN_REFERENCE = ((8192 // 3 + 127) // 128) * 128  # 2816, mlp.cu:247-250
 LLAMA_FFN = 2752                                        # 65.2B model: 22016 / 8
 
-POLICIES = {"rowsync": L.POLICY_ROWSYNC, "tilesync": L.POLICY_TILESYNC}
+POLICIES = {"rowsync": L.POLICY_ROWSYNC, "tilesync": L.POLICY_TILESYNC, "auto": 0}
+
+
+def choose_config(model, batch, hidden=None, ffn=None):
+    """What the library picks for a layer left to its choice (cusync_mlp_choose_config), as a dict."""
+    gpt3 = model == "gpt3"
+    hidden = hidden or (GPT3_HIDDEN if gpt3 else LLAMA_HIDDEN)
+    ffn = ffn or (GPT3_FFN if gpt3 else LLAMA_FFN)
+    c = L.MlpChoice()
+    L.check(L.lib().cusync_mlp_choose_config(L.MLP_GPT3 if gpt3 else L.MLP_LLAMA, batch, hidden, ffn, C.byref(c)),
+            "cusync_mlp_choose_config")
+    return {n: getattr(c, n) for n, _ in L.MlpChoice._fields_}
 
 
 class MLPShard:
     """x[B,H] -> y[B,H] through W1 (and V) [H,F] and W2 [F,H]; fp16, fp32 accumulate."""
 
     def __init__(self, model, batch, x, w1, w2, v=None, policy="rowsync", opts=0, tile_n1=0, tile_n2=0, max_ctas=0,
-                 group_rows2=0, cta_pair=0, split_k1=0, split_k2=0, tail_split=(0, 0, 0, 0), post_rows=False, group_rows1=0, x_rows=False):
+                 group_rows2=0, cta_pair=0, split_k1=0, split_k2=0, tail_split=(0, 0, 0, 0), post_rows=False, group_rows1=0, x_rows=False, single_grid=0, y=None):
         import torch
         self.model = L.MLP_GPT3 if model == "gpt3" else L.MLP_LLAMA
         self.batch, self.hidden, self.ffn = batch, w1.shape[0], w1.shape[1]
         assert x.shape == (batch, self.hidden) and w2.shape == (self.ffn, self.hidden)
         self.x, self.w1, self.w2, self.v = x, w1, w2, v
         self.h = torch.empty((batch, self.ffn), device=x.device, dtype=torch.half)
-        self.y = torch.empty((batch, self.hidden), device=x.device, dtype=torch.half)
+        # y may be the caller's (e.g. symmetric memory that an all-reduce kernel of another rank can reach)
+        self.y = y if y is not None else torch.empty((batch, self.hidden), device=x.device, dtype=torch.half)
+        assert self.y.shape == (batch, self.hidden) and self.y.is_contiguous()
         d = L.MlpDesc(self.model, batch, self.hidden, self.ffn, POLICIES[policy], opts, tile_n1, tile_n2, split_k1,
-                      split_k2, max_ctas, cta_pair, group_rows2, tail_split[0], tail_split[1], tail_split[2], tail_split[3], group_rows1, 1 if x_rows else 0, 1 if post_rows else 0,
+                      split_k2, max_ctas, cta_pair, group_rows2, tail_split[0], tail_split[1], tail_split[2], tail_split[3], group_rows1, 1 if x_rows else 0, single_grid, 1 if post_rows else 0,
                       x.data_ptr(), w1.data_ptr(), v.data_ptr() if v is not None else None, w2.data_ptr(),
                       self.h.data_ptr(), self.y.data_ptr())
         self._h = C.c_void_p()
@@ -44,6 +57,7 @@ class MLPShard:
         ts = (C.c_int32 * 4)()
         L.lib().cusync_mlp_tail_splits(self._h, ts)
         self.tail_splits = tuple(ts)   # (synchronised GEMM 1, 2, stream-ordered GEMM 1, 2)
+        self.single_grid = bool(L.lib().cusync_mlp_uses_single_grid(self._h))
 
     def run_stream_ordered(self, stream):
         L.check(L.lib().cusync_mlp_run_stream_ordered(self._h, _stream_ptr(stream)), "run_stream_ordered")
@@ -51,6 +65,12 @@ class MLPShard:
     def run_cusync(self, producer_stream, consumer_stream):
         L.check(L.lib().cusync_mlp_run_cusync(self._h, _stream_ptr(producer_stream), _stream_ptr(consumer_stream)),
                 "run_cusync")
+
+    def run_cusync_allreduce(self, reducer, producer_stream, consumer_stream, reduce_stream):
+        """One layer with its all-reduce overlapped (post_rows=True): `reducer` is a tp.RowAllReduce over self.y."""
+        L.check(L.lib().cusync_mlp_run_cusync_allreduce(self._h, reducer._plan, _stream_ptr(producer_stream),
+                                                        _stream_ptr(consumer_stream), _stream_ptr(reduce_stream)),
+                "run_cusync_allreduce")
 
     def post_x_rows(self, first_tile, num_tiles, stream):
         """x_rows=True: the 128-row tiles [first_tile, first_tile + num_tiles) of x are complete once what `stream`

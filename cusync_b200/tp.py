@@ -22,6 +22,76 @@ def shard_mlp_weights(w1, w2, v, parts, rank):
     return w1[:, b:e].contiguous(), w2[b:e, :].contiguous(), (v[:, b:e].contiguous() if v is not None else None)
 
 
+class RowAllReduce:
+    """The all-reduce kernel that runs beside the producing GEMM (cusync_allreduce_*): owns the output matrix
+    `y` [rows, cols] fp16 and the flag words, in memory every rank's kernel can reach.  With more than one rank
+    that is torch's symmetric memory (one process per GPU; peer mappings and, where the NVSwitch offers it, a
+    multicast address, both set up by a rendezvous over the process group); with one rank plain device memory.
+    torch only provides the memory; the reduction is this library's kernel."""
+
+    def __init__(self, group, rows, cols, device, num_ctas=8, multicast=True, timeout_ns=0):
+        import ctypes as C
+        import torch
+        from . import _lib as L
+        self.rows, self.cols, self.world, self.rank = rows, cols, group.world, group.rank
+        words = int(L.lib().cusync_allreduce_flag_words(rows, 128))
+        self.uses_multicast = False
+        if group.world > 1:
+            import torch.distributed._symmetric_memory as symm_mem
+            self.y = symm_mem.empty((rows, cols), dtype=torch.half, device=device)
+            self.flags = symm_mem.empty((max(words, 64),), dtype=torch.int32, device=device)
+            self.flags.zero_()
+            hy = symm_mem.rendezvous(self.y, group.dist.group.WORLD)
+            hf = symm_mem.rendezvous(self.flags, group.dist.group.WORLD)
+            self._handles = (hy, hf)
+            bufs, flags = list(hy.buffer_ptrs), list(hf.buffer_ptrs)
+            mc_y = int(hy.multicast_ptr) if multicast and hy.has_multicast_support(device.type, device.index) else 0
+            mc_f = int(hf.multicast_ptr) if mc_y else 0
+            if not (mc_y and mc_f):
+                mc_y = mc_f = 0
+            self.uses_multicast = bool(mc_y)
+            torch.cuda.synchronize(device)
+            group.barrier()                 # every rank's flags are zero before any rank's kernel can signal
+        else:
+            self.y = torch.empty((rows, cols), dtype=torch.half, device=device)
+            self.flags = torch.zeros((max(words, 64),), dtype=torch.int32, device=device)
+            bufs, flags, mc_y, mc_f = [self.y.data_ptr()], [self.flags.data_ptr()], 0, 0
+        self._bufs = (C.c_void_p * len(bufs))(*bufs)
+        self._flags = (C.c_void_p * len(flags))(*flags)
+        d = L.AllReduceDesc(group.rank, group.world, rows, cols, cols, 128, num_ctas, self._bufs, self._flags,
+                            mc_y or None, mc_f or None, int(timeout_ns))
+        self._plan = C.c_void_p()
+        L.check(L.lib().cusync_allreduce_plan_create(C.byref(self._plan), C.byref(d)), "cusync_allreduce_plan_create")
+        self.num_ctas = int(L.lib().cusync_allreduce_plan_num_ctas(self._plan))
+
+    def run(self, stream, row_semaphores=None, value=0):
+        """The all-reduce alone: the matrix is taken as complete when the kernel starts, unless semaphores are given."""
+        from . import _lib as L
+        from .api import _stream_ptr
+        L.check(L.lib().cusync_allreduce_run(self._plan, row_semaphores, value, _stream_ptr(stream)), "cusync_allreduce_run")
+
+    def status(self):
+        import ctypes as C
+        from . import _lib as L
+        st = L.Status()
+        L.lib().cusync_allreduce_read_status(self._plan, C.byref(st))
+        return st
+
+    def status_code(self):
+        return self.status().code
+
+    def describe_status(self):
+        st = self.status()
+        return "code %d where %d tile_x %d sem_index %d seen %d expected %d" % (
+            st.code, st.where, st.tile_x, st.sem_index, st.seen, st.expected)
+
+    def destroy(self):
+        from . import _lib as L
+        if self._plan:
+            L.lib().cusync_allreduce_plan_destroy(self._plan)
+            self._plan = None
+
+
 class TensorParallelGroup:
     """World of the layer's ranks.  backend "nccl" on GPUs (NVLink/NVSwitch), "gloo" for the CPU tests."""
 

@@ -267,6 +267,20 @@ CUSYNC_API int cusync_gemm_plan_update(cusync_gemm_plan_t* plan, const void* a, 
                             const void* b2, void* d);
 /* run(bool overlap, int*, cudaStream_t) (gemm/device/cusyncgemm.h:525-563). */
 CUSYNC_API int cusync_gemm_run(cusync_gemm_plan_t* plan, cusync_stream_t stream);
+/* Two dependent GEMMs launched as ONE persistent grid: the blocks draw the work units of `first`, then those of
+ * `second`, from one ticket counter, so a block that finds no unit of the first GEMM left goes straight on to
+ * units of the second (whose waits on the first's semaphores are the usual ones) instead of idling until a second
+ * launch can become resident.  Stages, policies, semaphore counts and results are those of two cusync_gemm_run
+ * calls; no wait kernel is needed.  The second plan's stage should be the consumer of the first's (or wait for
+ * nothing).  Both plans must run the CTA-pair kernel (cusync_gemm_chain_supported), else
+ * CUSYNC_ERROR_UNSUPPORTED.  The reference always launches one kernel per GEMM
+ * (src/ml-bench/transformer/mlp.cu:691-712); this is what its overlap of the producer's last wave turns into
+ * when every kernel is persistent and holds a whole SM per block. */
+CUSYNC_API int cusync_gemm_run_chain(cusync_gemm_plan_t* first, cusync_gemm_plan_t* second, cusync_stream_t stream);
+CUSYNC_API int cusync_gemm_chain_supported(const cusync_gemm_plan_t* first, const cusync_gemm_plan_t* second);
+/* Loads the one-grid kernel ahead of its first run (a first launch that has to load its kernel can stall behind
+ * kernels already running on the device).  Optional; cusync_gemm_run_chain does it otherwise. */
+CUSYNC_API int cusync_gemm_chain_prepare(void);
 /* K slices the plan uses for the tiles of its last partial wave (1 = none). */
 CUSYNC_API int cusync_gemm_plan_tail_split(const cusync_gemm_plan_t* plan);
 /* Allocation-free GEMM.  It has no counterpart in the reference.
@@ -449,19 +463,25 @@ enum { CUSYNC_MLP_GPT3 = 0, CUSYNC_MLP_LLAMA = 1 };
 typedef struct cusync_mlp_desc {
   int32_t model;                 /* CUSYNC_MLP_* */
   int32_t batch, hidden, ffn;
-  int32_t policy;                /* CUSYNC_POLICY_ROWSYNC or CUSYNC_POLICY_TILESYNC between the two GEMMs */
+  int32_t policy;                /* CUSYNC_POLICY_ROWSYNC or CUSYNC_POLICY_TILESYNC between the two GEMMs; 0 = choose
+                                    (cusync_mlp_choose_config) */
   int32_t opts;                  /* CUSYNC_OPT_* applied to both stages */
   int32_t tile_n1, tile_n2;      /* 0 = choose */
   int32_t split_k1, split_k2;    /* 0 = choose (mlp.cu's --split-k1 / --split-k2) */
   int32_t max_ctas;              /* 0 = one per SM */
   int32_t cta_pair;              /* as cusync_gemm_desc_t.cta_pair, for both GEMMs */
-  int32_t group_rows2;           /* the consumer's tile order: 0 = choose, 1 = plain, n > 1 = CUSYNC_ORDER_GROUPED(n) */
+  int32_t group_rows2;           /* the consumer's tile order: 0 = choose (cusync_mlp_choose_config), 1 = plain,
+                                    n > 1 = CUSYNC_ORDER_GROUPED(n) */
   int32_t tail_split_sync1, tail_split_sync2;    /* cusync_gemm_desc_t.tail_split of the two synchronised GEMMs ... */
   int32_t tail_split_plain1, tail_split_plain2;  /* ... and of the two stream-ordered ones: 0 = choose, 1 = none */
-  int32_t group_rows1;           /* the producer's tile order: 0 or 1 = plain, n > 1 = CUSYNC_ORDER_GROUPED(n) */
+  int32_t group_rows1;           /* the producer's tile order, like group_rows2 */
   int32_t x_rows;                /* 1: X arrives in row blocks while the layer runs (e.g. host-to-device copies on
                                     another stream): the first GEMM of run_cusync waits, per 128-row tile, on a RowSync
                                     semaphore that the caller posts with cusync_mlp_post_x_rows once per run */
+  int32_t single_grid;           /* run_cusync launches both GEMMs as one persistent grid (cusync_gemm_run_chain) on the
+                                    producer stream and lets the consumer stream wait for it: 0 = choose
+                                    (cusync_mlp_choose_config, and only where both GEMMs run the CTA-pair kernel), 1 = never (one launch per GEMM and a wait
+                                    kernel, as mlp.cu:691-712), 2 = required (else cusync_mlp_create fails) */
   int32_t post_rows;             /* 1: the second GEMM of run_cusync is a producer too: it posts RowSync semaphores, one
                                     per 128-row tile of Y, counting its column tiles, so that whatever consumes Y (the
                                     all-reduce of a tensor-parallel layer) can start row block by row block
@@ -507,8 +527,73 @@ CUSYNC_API int cusync_mlp_post_x_rows(cusync_mlp_t* mlp, uint32_t first_tile, ui
  * [first_tile, first_tile + num_tiles) of Y as written by the most recent run_cusync (call it after that
  * run_cusync).  Work enqueued on `stream` afterwards sees those rows complete. */
 CUSYNC_API int cusync_mlp_wait_rows(cusync_mlp_t* mlp, uint32_t first_tile, uint32_t num_tiles, cusync_stream_t stream);
+/* What the library picks for a layer when the descriptor leaves it open: the role of the reference's tuning
+ * table src/ml-bench/transformer/tile_sizes_db.py as applied by eval_mlp.py:141-210 (tile shapes, split-K and the
+ * optimisation switches per model and batch).  A pure host function: needs no device. */
+typedef struct cusync_mlp_choice {
+  int32_t policy;                /* CUSYNC_POLICY_ROWSYNC or CUSYNC_POLICY_TILESYNC */
+  int32_t single_grid;           /* 1 = one launch per GEMM and a wait, 2 = one persistent grid */
+  int32_t stream_wait;           /* 1 = the wait before the second launch is a stream memory operation */
+  int32_t group_rows1, group_rows2;
+  int32_t tile_n1, tile_n2, split_k1, split_k2;
+} cusync_mlp_choice_t;
+CUSYNC_API int cusync_mlp_choose_config(int32_t model, int32_t batch, int32_t hidden, int32_t ffn, cusync_mlp_choice_t* out);
+/* 1 when run_cusync launches both GEMMs as one persistent grid. */
+CUSYNC_API int cusync_mlp_uses_single_grid(const cusync_mlp_t* mlp);
 /* Tail splits in use: out[0..3] = synchronised GEMM 1, 2, stream-ordered GEMM 1, 2. */
 CUSYNC_API int cusync_mlp_tail_splits(const cusync_mlp_t* mlp, int32_t* out4);
+
+/* ---- all-reduce beside the producing GEMM (tensor-parallel layers) -------- */
+
+/* Sum all-reduce, in place, of the fp16 matrix Y[rows, cols] that every rank of a tensor-parallel group holds a
+ * partial copy of: the one exchange step of the sharded MLP / attention layer.  The reference times this
+ * collective on its own and runs it after the layer (src/ml-bench/transformer/allreduce_times.py:11-35); here it
+ * is a small persistent kernel that runs BESIDE the GEMM producing Y and takes the matrix by 128-row tile as the
+ * GEMM's RowSync semaphores publish them (cusync_mlp_desc_t.post_rows), so only the last tiles' exchange is left
+ * once the GEMM ends.  Rank r sums rows [r, r + 1) * tile_rows / world of every tile over all ranks (fp32
+ * accumulation, one rounding to fp16) and writes the sums into every rank's copy: through the NVSwitch
+ * (multimem.ld_reduce / multimem.st on multicast addresses) when such addresses are given, else with plain peer
+ * loads (summed in rank order) and peer stores.  Every rank must run its plan equally often.
+ *
+ * Memory comes from the caller and must be peer-accessible (one process per GPU: symmetric / IPC-mapped
+ * memory): buffers[w] / flags[w] are rank w's matrix and flag words AS MAPPED INTO THIS PROCESS
+ * (buffers[rank] is the local one); flags need cusync_allreduce_flag_words() uint32 each, zeroed once before
+ * the first run; multicast_* are the NVLS multicast addresses of the same two allocations, or both NULL.
+ * Launch it BEFORE the GEMMs of the run (it must be resident while they run; give the GEMMs max_ctas =
+ * SMs - num_ctas) on a stream of its own. */
+typedef struct cusync_allreduce_desc {
+  int32_t rank, world;             /* world <= 8 */
+  int32_t rows, cols;              /* cols a multiple of 8 */
+  int64_t ld;                      /* row pitch in elements, the same on every rank */
+  int32_t tile_rows;               /* 0 = 128 */
+  int32_t num_ctas;                /* 0 = choose (8); even: blocks are launched in pairs that fill whole TPCs */
+  void* const* buffers;            /* [world] */
+  uint32_t* const* flags;          /* [world] */
+  void* multicast_buffer;
+  uint32_t* multicast_flags;
+  uint64_t timeout_ns;             /* 0 = default bound of every wait inside the kernel */
+} cusync_allreduce_desc_t;
+
+typedef struct cusync_allreduce_plan cusync_allreduce_plan_t;
+
+CUSYNC_API uint32_t cusync_allreduce_flag_words(int32_t rows, int32_t tile_rows);
+CUSYNC_API int cusync_allreduce_plan_create(cusync_allreduce_plan_t** out, const cusync_allreduce_desc_t* desc);
+CUSYNC_API int cusync_allreduce_plan_destroy(cusync_allreduce_plan_t* plan);
+/* One all-reduce.  row_semaphores: this rank's per-tile semaphores (one per tile_rows rows), a tile being complete
+ * when its semaphore has reached `value`; NULL = the matrix is complete when the kernel starts (stream order). */
+CUSYNC_API int cusync_allreduce_run(cusync_allreduce_plan_t* plan, const uint32_t* row_semaphores, uint32_t value,
+                                    cusync_stream_t stream);
+/* Timeout record: where = 1 the local producer never published a tile, 2 another rank did not, 3 the final
+ * handshake.  After a timeout the flag words have to be zeroed on every rank and the plans recreated. */
+CUSYNC_API int cusync_allreduce_read_status(const cusync_allreduce_plan_t* plan, cusync_status_t* out);
+CUSYNC_API uint32_t cusync_allreduce_plan_num_ctas(const cusync_allreduce_plan_t* plan);
+
+/* One layer of a tensor-parallel MLP shard with its all-reduce overlapped: the reducer goes to reduce_stream
+ * first, then run_cusync's GEMMs (created with post_rows), and consumer_stream ends up waiting for both.  The
+ * sharded driver of mlp.cu (:243-251 shapes) plus the collective the reference leaves to its caller. */
+CUSYNC_API int cusync_mlp_run_cusync_allreduce(cusync_mlp_t* mlp, cusync_allreduce_plan_t* reducer,
+                                               cusync_stream_t producer_stream, cusync_stream_t consumer_stream,
+                                               cusync_stream_t reduce_stream);
 
 /* Library / device information. */
 CUSYNC_API const char* cusync_b200_version(void);

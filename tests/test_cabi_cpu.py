@@ -149,3 +149,32 @@ def test_grouped_rows_order_is_a_bijection_with_rows_fastest():
         assert first_group == [(0, y, 0) for y in range(min(rows, gy))]
         if gx > 1:
             assert seen[min(rows, gy)] == (1, 0, 0)
+
+
+def test_mlp_config_table_is_total_and_consistent():
+    # cusync_mlp_choose_config is a pure host function (the role of the reference's tile_sizes_db.py): every batch
+    # from 1 to 4096 of both models gets a row, with a policy the drivers implement, a launch form, tile orders
+    # that divide into the row tiles they cover, and tile shapes / K slices the kernels instantiate.
+    from cusync_b200 import mlp as M
+    from cusync_b200 import _lib as L
+    for model in ("gpt3", "llama"):
+        prev = None
+        changes = 0
+        for batch in range(1, 4097):
+            c = M.choose_config(model, batch)
+            assert c["policy"] in (L.POLICY_ROWSYNC, L.POLICY_TILESYNC)
+            assert c["single_grid"] in (1, 2)
+            assert c["group_rows1"] >= 1 and c["group_rows2"] >= 1
+            assert c["tile_n1"] in (64, 128, 192, 256) and c["tile_n2"] in (64, 128, 192, 256)
+            assert 1 <= c["split_k1"] <= 16 and 1 <= c["split_k2"] <= 16
+            if c["single_grid"] == 2:      # one grid needs both GEMMs on CTA pairs: more than two row tiles, 256-wide tiles
+                assert batch > 256 and c["tile_n1"] == 256 and c["tile_n2"] == 256 and model == "gpt3"
+            assert c["stream_wait"] == (1 if (batch + 127) // 128 <= 4 else 0)
+            key = (c["policy"], c["single_grid"], c["group_rows1"], c["group_rows2"])
+            if prev is not None and key != prev:
+                changes += 1
+            prev = key
+        assert changes <= 4          # a handful of batch ranges, not a row per batch
+    bad = L.MlpChoice()
+    assert L.lib().cusync_mlp_choose_config(7, 64, 12288, 6144, C.byref(bad)) == L.ERROR_INVALID_ARGUMENT
+    assert L.lib().cusync_mlp_choose_config(0, 0, 12288, 6144, C.byref(bad)) == L.ERROR_INVALID_ARGUMENT

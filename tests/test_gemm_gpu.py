@@ -278,7 +278,7 @@ def test_linearity_at_full_gpt3_width():
 
 
 def _chain(policy_name, M, N1, K1, N2, tile_n1, tile_n2, iters, opts=0, epi1=L.EPILOGUE_NONE, max_ctas=0,
-           wait_kernel=True, seed=20, cta_pair=0, tail_split=0):
+           wait_kernel=True, seed=20, cta_pair=0, tail_split=0, single_grid=False):
     a = _rand((M, K1), seed, dist="normal")
     w1 = _rand((K1, N1), seed + 1, scale=0.03, dist="normal")
     w2 = _rand((N1, N2), seed + 2, scale=0.03, dist="normal")
@@ -312,10 +312,13 @@ def _chain(policy_name, M, N1, K1, N2, tile_n1, tile_n2, iters, opts=0, epi1=L.E
         # poison: a consumer that reads ahead of its producer sees NaN
         h.fill_(float("nan")); y.fill_(float("nan"))
         torch.cuda.synchronize()
-        assert g1.run(True, None, ps) == L.SUCCESS
-        if wait_kernel:
-            assert prod.invokeWaitKernel(cst) == L.SUCCESS
-        assert g2.run(True, None, cst) == L.SUCCESS
+        if single_grid:
+            assert cs.Gemm.run_chain(g1, g2, ps) == L.SUCCESS
+        else:
+            assert g1.run(True, None, ps) == L.SUCCESS
+            if wait_kernel:
+                assert prod.invokeWaitKernel(cst) == L.SUCCESS
+            assert g2.run(True, None, cst) == L.SUCCESS
         torch.cuda.synchronize()
         assert prod.status().code == 0 and cons.status().code == 0
         assert o.max_rel_err(h.cpu().numpy(), href) <= TOL
@@ -619,3 +622,27 @@ def test_policies_built_for_another_tile_shape_are_refused():
     assert g.initialize(cs.GemmArguments(cons, (256, 512, 512), a, b, d, tile_n=256, cta_pair=1,
                                          split_k_slices=1)) == L.ERROR_INVALID_ARGUMENT
     prod.destroy(); cons.destroy()
+
+
+@pytest.mark.parametrize("policy", ["row", "tile"])
+def test_chain_as_one_persistent_grid(policy):
+    # cusync_gemm_run_chain: both GEMMs in one grid of CTA pairs drawing from one ticket counter.  Few clusters,
+    # so pairs go from producer units straight on to consumer units and really wait; odd row-tile count;
+    # with and without tail splits; three runs (the shared counter re-arms itself).
+    _chain(policy, 640, 1024, 512, 1024, 256, 256, iters=3, max_ctas=4, cta_pair=2, single_grid=True)
+    _chain(policy, 512, 1536, 1024, 768, 256, 256, iters=2, epi1=L.EPILOGUE_GELU_ERF, cta_pair=2, single_grid=True)
+    _chain(policy, 768, 1024, 2048, 1024, 256, 256, iters=2, max_ctas=10, cta_pair=2, tail_split=4,
+           epi1=L.EPILOGUE_GELU_ERF, single_grid=True)
+    _chain(policy, 1024, 2048, 1024, 2048, 256, 256, iters=2, opts=L.OPT_NO_ATOMIC_ADD if policy == "tile" else 0,
+           cta_pair=2, single_grid=True)
+
+
+def test_one_grid_chain_refuses_kernels_it_cannot_combine():
+    a = _rand((256, 256), 97); b = _rand((256, 256), 98)
+    d1 = torch.empty((256, 256), device="cuda", dtype=torch.half)
+    d2 = torch.empty((256, 256), device="cuda", dtype=torch.half)
+    g1, g2 = cs.Gemm(), cs.Gemm()
+    assert g1.initialize(cs.GemmArguments(None, (256, 256, 256), a, b, d1, tile_n=256, cta_pair=2)) == L.SUCCESS
+    assert g2.initialize(cs.GemmArguments(None, (256, 256, 256), d1, b, d2, tile_n=128, cta_pair=1)) == L.SUCCESS
+    assert cs.Gemm.run_chain(g1, g2, torch.cuda.current_stream()) == L.ERROR_UNSUPPORTED
+    g1.destroy(); g2.destroy()
