@@ -6,10 +6,12 @@ tensor-parallel shard, as a chain of two tile-synchronised GEMMs.
     python bench.py --impl reference ...          # the CPU host-reference path, timed on the host cores
 
 A step is one MLP layer over one batch of synthetic input (X ~ N(0,1),
-weights ~ N(0,0.02), seeded): producer GEMM (+GELU) on one stream, wait kernel
-and consumer GEMM on another, semaphores between them; with N > 1 GPUs an NCCL
-all-reduce of the [B, 12288] output follows on the consumer stream.  One JSON
-line is printed by rank 0.  Time-like metric: microseconds per layer.
+weights ~ N(0,0.02), seeded): producer GEMM (+GELU) and consumer GEMM
+synchronised tile by tile through semaphores (one launch each with a wait
+kernel, or one persistent grid for both, as the library's table picks); with
+N > 1 GPUs the sum all-reduce of the [B, 12288] output runs as this library's
+kernel beside the second GEMM (--reduce nccl: NCCL's all-reduce after it).
+One JSON line is printed by rank 0.  Time-like metric: microseconds per layer.
 """
 import argparse
 import json
@@ -64,13 +66,13 @@ class ClockSampler:
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index):
-        self.index, self.rows, self.proc = index, [], None
+    def __init__(self, index, period_ms=100):
+        self.index, self.rows, self.proc, self.period_ms = index, [], None, period_ms
 
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", str(self.period_ms)],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -105,12 +107,22 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def host_threads():
+    """Threads the CPU arm uses: every core this process may run on (a launcher such as torchrun exports
+    OMP_NUM_THREADS=1 to its workers, which is not what a host-side baseline should inherit)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def cpu_reference_us(batch, sample_rows, hidden, ffn):
     """The CPU host-reference path (oracle restatement of ref_cpumatmul + GELU) on `sample_rows` rows of the
     layer, all host threads; returns (microseconds scaled to `batch` rows, threads, seconds spent)."""
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import numpy as np
     import oracle_lib as o
+    o.set_num_threads(host_threads())
     rng = np.random.default_rng(0)
     x = rng.standard_normal((sample_rows, hidden), dtype=np.float32).astype(np.float16)
     w1 = (rng.standard_normal((hidden, ffn), dtype=np.float32) * 0.02).astype(np.float16)
@@ -126,24 +138,29 @@ def cpu_reference_us(batch, sample_rows, hidden, ffn):
 def run_reference(args, rank, world):
     """--impl reference: the reference's CPU check path for this layer, on the host cores.  Its CUTLASS GPU
     kernels cannot be built (un-vendored, un-pinned CUTLASS submodule), so the CPU path is the oracle's
-    restatement of ref_cpumatmul (kind "port")."""
+    restatement of ref_cpumatmul (kind "port").  Rank 0 alone runs it; a step is a bounded sample of the layer
+    (512 of its rows through both GEMMs, scaled to the batch) and at most three steps are timed, so the arm ends
+    within a minute whatever --steps says."""
     if rank != 0:
         return
+    os.environ["OMP_NUM_THREADS"] = str(host_threads())
     from cusync_b200 import mlp as M
     hidden, ffn = M.GPT3_HIDDEN, M.GPT3_FFN
-    sample = min(args.batch, 1024)
+    sample = min(args.batch, 512)
+    steps, warmup = min(args.steps, 3), min(args.warmup, 1)
     times = []
-    for i in range(args.warmup + args.steps):
+    for i in range(warmup + steps):
         us, threads, _ = cpu_reference_us(args.batch, sample, hidden, ffn)
-        if i >= args.warmup:
+        if i >= warmup:
             times.append(us)
     val = statistics.mean(times)
     line = {"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": val / 1000.0, "higher_is_better": False,
+            "steps": steps, "warmup": warmup, "ms_per_step": val / 1000.0, "higher_is_better": False,
             "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": workload_config(args, None),
             "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port",
-                             "sample": "%d of %d rows through both GEMMs, scaled to the full batch" % (sample, args.batch)},
+                             "sample": "%d of %d rows through both GEMMs, scaled to the full batch; %d timed steps"
+                                       % (sample, args.batch, steps)},
             "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     emit(line)
 
@@ -153,10 +170,11 @@ def workload_config(args, shard):
                        "* W2[6144,12288]" % args.batch,
            "batch": args.batch, "policy": args.policy,
            "l2": "inputs larger than L2 (302 MB of weights per step vs 126 MB L2); no explicit flush",
-           "all_reduce": ("NCCL sum of Y[B,12288] fp16 across ranks" + (
-               "; overlapped arm: %d row blocks, each behind the RowSync semaphores of its 128-row tiles of the "
-               "second GEMM (%d of 148 SMs to the GEMMs)" % (args.reduce_chunks, args.gemm_ctas) if args.gpus > 1 and args.batch >= 512 and args.reduce == "overlapped" else ""))
-                         if args.gpus > 1 else "none (1 GPU)"}
+           "all_reduce": (("sum of Y[B,12288] fp16 across ranks by this library's kernel beside the second GEMM "
+                           "(%d blocks; the GEMMs use the other SMs)" % args.reduce_ctas
+                           if getattr(args, "reduce", "overlapped") == "overlapped"
+                           else "NCCL sum of Y[B,12288] fp16 across ranks, after the layer")
+                          if args.gpus > 1 else "none (1 GPU)")}
     if shard is not None:
         cfg.update({"tile_m": 128, "tile_n1": shard.tile_n1, "tile_n2": shard.tile_n2,
                     "ctas1": shard.ctas1, "ctas2": shard.ctas2, "split_k1": shard.split_k1, "split_k2": shard.split_k2,
@@ -204,6 +222,19 @@ def _watchdog(seconds):
     t.start()
 
 
+def load_traffic(kernel_key, batch):
+    """dram__bytes_read.sum + dram__bytes_write.sum of one launch, as captured with ncu (bytes), or None."""
+    path = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    try:
+        table = json.load(open(path))
+    except (OSError, ValueError):
+        return None
+    for key, per_batch in table.items():
+        if key.startswith(kernel_key) and isinstance(per_batch, dict):
+            return per_batch.get(str(batch))
+    return None
+
+
 def main():
     _watchdog(1500)
     ap = argparse.ArgumentParser()
@@ -211,15 +242,13 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--batch", type=int, default=2048)
-    ap.add_argument("--policy", default="rowsync", choices=["rowsync", "tilesync"])
+    ap.add_argument("--policy", default="rowsync", choices=["rowsync", "tilesync", "auto"])
     ap.add_argument("--impl", default="cusync", choices=["cusync", "reference"])
-    ap.add_argument("--reduce", choices=("overlapped", "after"), default="after",
-                    help="multi-GPU: all-reduce Y after the second GEMM (default, the faster one here: NCCL needs "
-                         "more SMs for full NVLink bandwidth than the GEMMs can spare), or in row blocks behind "
-                         "the second GEMM's tiles")
-    ap.add_argument("--reduce-chunks", type=int, default=REDUCE_CHUNKS, help="row blocks of the overlapped all-reduce")
-    ap.add_argument("--gemm-ctas", type=int, default=128, help="blocks the GEMMs use when the all-reduce is overlapped")
-    ap.add_argument("--no-sweep", action="store_true", help="skip the per-batch table")
+    ap.add_argument("--reduce", choices=("overlapped", "nccl"), default="overlapped",
+                    help="multi-GPU: the all-reduce of Y as this library's kernel beside the second GEMM (default), "
+                         "or NCCL's all-reduce after the layer")
+    ap.add_argument("--reduce-ctas", type=int, default=8, help="blocks of the overlapped all-reduce kernel")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the per-batch table and the other workloads")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     claim_stdout()
@@ -242,46 +271,84 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     group = tp.TensorParallelGroup("nccl", dev)
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
 
     def barrier():
         group.barrier()
 
+    def reduce_max(v):
+        return group.max_over_ranks(v)
+
     peaks = load_peaks()
     ps = torch.cuda.Stream(priority=-1)   # producer: high priority, launched first
     cs = torch.cuda.Stream(priority=0)
+    rs = torch.cuda.Stream(priority=0)    # multi-GPU: the all-reduce kernel that runs beside the GEMMs
+    overlap_reduce = world > 1 and args.reduce == "overlapped"
 
-    comm = torch.cuda.Stream(priority=0)  # multi-GPU: the row-block all-reduces of the overlapped arm
-    # Multi-GPU: the second GEMM also posts its output by 128-row tile, so that the all-reduce runs block by
-    # block behind it; 20 SMs are left to the collective's kernels (128 blocks: 192 and 384 pair tiles are
-    # whole rounds of 64 pairs, so the GEMMs lose nothing at B = 2048).
-    overlap_reduce = world > 1 and args.batch >= 512 and args.reduce == "overlapped"
+    class Layer:
+        """One tensor-parallel layer of `model` at `batch`: the synchronised chain with its all-reduce (this
+        library's kernel beside the GEMMs, or NCCL after them) and the same kernels stream-ordered with NCCL."""
 
-    def build(batch, policy):
-        x, w1, w2, v = M.make_inputs("gpt3", batch, dev, seed=rank)
-        if overlap_reduce:
-            return M.MLPShard("gpt3", batch, x, w1, w2, v, policy=policy, post_rows=True, max_ctas=args.gemm_ctas)
-        return M.MLPShard("gpt3", batch, x, w1, w2, v, policy=policy)
+        def __init__(self, model, batch, policy, seed):
+            x, w1, w2, v = M.make_inputs(model, batch, dev, seed=seed)
+            self.model, self.batch = model, batch
+            self.reducer = None
+            if overlap_reduce:
+                self.reducer = tp.RowAllReduce(group, batch, x.shape[1], dev, num_ctas=args.reduce_ctas)
+                self.shard = M.MLPShard(model, batch, x, w1, w2, v, policy=policy, post_rows=True,
+                                        max_ctas=sms - self.reducer.num_ctas, y=self.reducer.y)
+                # the stream-ordered arm keeps the whole device and its own output
+                self.base = M.MLPShard(model, batch, x, w1, w2, v, policy=policy, single_grid=1)
+            else:
+                self.shard = M.MLPShard(model, batch, x, w1, w2, v, policy=policy)
+                self.base = self.shard
 
-    shard = build(args.batch, args.policy)
+        def cusync_step(self):
+            if self.reducer is not None:
+                self.shard.run_cusync_allreduce(self.reducer, ps, cs, rs)
+            else:
+                self.shard.run_cusync(ps, cs)
+                if world > 1:
+                    with torch.cuda.stream(cs):
+                        group.all_reduce_sum(self.shard.y)
 
-    def cusync_step():
-        # (the driver orders a run after the previous one: a step may not overwrite H while it is still read)
-        shard.run_cusync(ps, cs)
-        if overlap_reduce:
-            group.all_reduce_rows_overlapped(shard, comm, args.reduce_chunks)
-            cs.wait_stream(comm)
-        elif world > 1:
-            with torch.cuda.stream(cs):
-                group.all_reduce_sum(shard.y)
+        def chain_only_step(self):
+            """The layer without its all-reduce (what one GPU runs)."""
+            self.base.run_cusync(ps, cs)
 
-    def ordered_step():
-        shard.run_stream_ordered(cs)
-        if world > 1:
-            with torch.cuda.stream(cs):
-                group.all_reduce_sum(shard.y)
+        def ordered_step(self):
+            self.base.run_stream_ordered(cs)
+            if world > 1:
+                with torch.cuda.stream(cs):
+                    group.all_reduce_sum(self.base.y)
 
-    def reduce_max(v):
-        return group.max_over_ranks(v)
+        def check(self):
+            """The overlapped all-reduce gives what NCCL's all-reduce of the same partial outputs gives, up to the
+            order of the sum: this library's kernel adds the ranks' fp16 values in fp32 and rounds once."""
+            if self.reducer is None:
+                return None
+            self.cusync_step(); torch.cuda.synchronize(); barrier()
+            self.ordered_step(); torch.cuda.synchronize(); barrier()
+            ref, got = self.base.y.float(), self.shard.y.float()
+            err = (got - ref).abs().max().item() / max(ref.abs().max().item(), 1e-6)
+            if not err <= 4e-3:
+                raise SystemExit("overlapped all-reduce differs from NCCL's: %.3e of max|Y|" % err)
+            return err
+
+        def status_ok(self):
+            ok = self.shard.status_codes() == (0, 0)
+            return ok and (self.reducer is None or self.reducer.status_code() == 0)
+
+        def destroy(self):
+            if self.base is not self.shard:
+                self.base.destroy()
+            self.shard.destroy()
+            if self.reducer is not None:
+                self.reducer.destroy()
+
+    layer = Layer("gpt3", args.batch, args.policy, seed=rank)
+    shard = layer.shard
+    reduce_err = layer.check()
 
     def interleaved(step_a, a_streams, step_b, b_streams, n, warm):
         """Alternates the two arms step by step, so clock and power drift hits both alike.
@@ -289,11 +356,12 @@ def main():
         for _ in range(warm):
             step_a(); step_b()
         torch.cuda.synchronize()
+        barrier()
         ev = []
         for _ in range(n):
             pair = []
             for fn, (s0, s1) in ((step_a, a_streams), (step_b, b_streams)):
-                s0.wait_stream(cs); s0.wait_stream(ps)
+                s0.wait_stream(cs); s0.wait_stream(ps); s0.wait_stream(rs)
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record(s0); fn(); e1.record(s1)
                 pair.append((e0, e1))
@@ -301,82 +369,146 @@ def main():
         torch.cuda.synchronize()
         return [p[0][0].elapsed_time(p[0][1]) for p in ev], [p[1][0].elapsed_time(p[1][1]) for p in ev]
 
-    if overlap_reduce:
-        # the block-wise reduction must give what one all-reduce of the whole output gives
-        cusync_step(); torch.cuda.synchronize()
-        y_blocks = shard.y.clone()
-        ordered_step(); torch.cuda.synchronize()
-        if not torch.equal(y_blocks, shard.y):
-            raise SystemExit("row-block all-reduce differs from the whole-matrix all-reduce")
+    def med_us(ms_list):
+        return reduce_max(statistics.median(ms_list) * 1000.0)
 
     # ---- headline: overlapped chain ------------------------------------------------------------
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    total_ms, per_ms = time_steps(cusync_step, ps, cs, args.steps, args.warmup, barrier)
+    total_ms, per_ms = time_steps(layer.cusync_step, ps, cs, args.steps, args.warmup, barrier)
     total_ms = reduce_max(total_ms)
     ms_per_step = total_ms / args.steps
-    codes = shard.status_codes()
-    if codes != (0, 0):
-        raise SystemExit("a bounded wait expired during the timed region: %r" % (codes,))
+    if not layer.status_ok():
+        raise SystemExit("a bounded wait expired during the timed region")
 
     # ---- same kernels serialised by stream order --------------------------------------------
-    ord_total, ord_per = time_steps(ordered_step, cs, cs, args.steps, args.warmup, barrier)
+    ord_total, ord_per = time_steps(layer.ordered_step, cs, cs, args.steps, args.warmup, barrier)
     ord_ms = reduce_max(ord_total) / args.steps
     # ... and both arms interleaved step by step (the fair comparison under clock drift)
-    il_c, il_o = interleaved(cusync_step, (ps, cs), ordered_step, (cs, cs), args.steps, 3)
-    il_c_us, il_o_us = statistics.median(il_c) * 1000.0, statistics.median(il_o) * 1000.0
+    il_c, il_o = interleaved(layer.cusync_step, (ps, cs), layer.ordered_step, (cs, cs), args.steps, 3)
+    il_c_us, il_o_us = med_us(il_c), med_us(il_o)
 
-    # ---- per-kernel durations (stream-ordered, events on the launching stream) ----------------
+    # ---- multi-GPU: the layer without its all-reduce, and the all-reduce alone ---------------------------
+    multi = None
+    if world > 1:
+        def chain_vs_layer():
+            c_per, l_per = interleaved(layer.chain_only_step, (ps, cs), layer.cusync_step, (ps, cs), args.steps, 3)
+            return med_us(c_per), med_us(l_per)
+
+        def allreduce_alone(buf, n):
+            """The isolated collective on the layer's output buffer: barrier, then n back-to-back all-reduces
+            between one pair of events (the protocol of allreduce_times.py:13-28)."""
+            for _ in range(3):
+                with torch.cuda.stream(cs):
+                    group.all_reduce_sum(buf)
+            torch.cuda.synchronize(); barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            with torch.cuda.stream(cs):
+                e0.record(cs)
+                for _ in range(n):
+                    group.all_reduce_sum(buf)
+                e1.record(cs)
+            torch.cuda.synchronize()
+            return reduce_max(e0.elapsed_time(e1) / n * 1000.0)
+
+        def own_allreduce_alone(reducer, n):
+            if reducer is None:
+                return None
+            for _ in range(3):
+                reducer.run(rs)
+            torch.cuda.synchronize(); barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(rs)
+            for _ in range(n):
+                reducer.run(rs)
+            e1.record(rs)
+            torch.cuda.synchronize()
+            return reduce_max(e0.elapsed_time(e1) / n * 1000.0)
+
+        chain_us, layer_us = chain_vs_layer()
+        # the round-1 form for comparison: the synchronised chain on the whole device, NCCL's all-reduce after it
+        def nccl_after_step():
+            layer.base.run_cusync(ps, cs)
+            with torch.cuda.stream(cs):
+                group.all_reduce_sum(layer.base.y)
+        na_per, _ = interleaved(nccl_after_step, (ps, cs), layer.ordered_step, (cs, cs), args.steps, 3)
+        multi = {"layer_without_allreduce_us": chain_us, "layer_with_allreduce_us": layer_us,
+                 "cusync_chain_then_nccl_allreduce_us": med_us(na_per),
+                 "allreduce_alone_us": allreduce_alone(layer.base.y, 20),
+                 "own_allreduce_kernel_alone_us": own_allreduce_alone(layer.reducer, 20),
+                 "allreduce_form": ("this library's kernel beside the second GEMM: %d blocks, %s, GEMMs on %d of %d SMs"
+                                    % (layer.reducer.num_ctas,
+                                       "multimem.ld_reduce / multimem.st through the NVSwitch" if layer.reducer.uses_multicast
+                                       else "peer loads and stores", sms - layer.reducer.num_ctas, sms))
+                                   if layer.reducer is not None else "NCCL all-reduce after the layer",
+                 "overlapped_vs_nccl_max_err_of_max": reduce_err, "per_batch": []}
+        if not args.no_sweep:
+            for b in SWEEP_BATCHES:
+                lb = Layer("gpt3", b, args.policy, seed=rank)
+                lb.check()
+                c_per, l_per = interleaved(lb.chain_only_step, (ps, cs), lb.cusync_step, (ps, cs), 20, 3)
+                l2_per, o_per = interleaved(lb.cusync_step, (ps, cs), lb.ordered_step, (cs, cs), 20, 3)
+                multi["per_batch"].append({
+                    "batch": b, "layer_without_allreduce_us": round(med_us(c_per), 2),
+                    "layer_with_allreduce_us": round(med_us(l_per), 2),
+                    "stream_ordered_with_nccl_us": round(med_us(o_per), 2),
+                    "gain_pct": round(100.0 - med_us(l2_per) / med_us(o_per) * 100.0, 2),
+                    "allreduce_alone_us": round(allreduce_alone(lb.base.y, 20), 2),
+                    "own_allreduce_kernel_alone_us": (round(own_allreduce_alone(lb.reducer, 20), 2)
+                                                      if lb.reducer is not None else None)})
+                if not lb.status_ok():
+                    multi["per_batch"][-1]["error"] = "bounded wait expired"
+                lb.destroy()
+
+    # ---- per-kernel durations: each GEMM alone and both in a row, back to back between ONE pair of events ----
+    base = layer.base
     flops2 = 2.0 * args.batch * M.GPT3_FFN * M.GPT3_HIDDEN
-    evs = []
-    for i in range(args.warmup + args.steps):     # back to back, like the timed region: no host sync in between
-        e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+    loop_n = max(200, args.steps)
+
+    def loop_ms(fn, n):
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(cs)
-        shard.run_single(1, cs)
+        for _ in range(n):
+            fn()
         e1.record(cs)
-        shard.run_single(2, cs)
-        e2.record(cs)
-        if i >= args.warmup:
-            evs.append((e0, e1, e2))
-    torch.cuda.synchronize()
-    g1 = [a.elapsed_time(b) for a, b, _ in evs]
-    g2 = [b.elapsed_time(c) for _, b, c in evs]
-    t1_ms, t2_bracketed_ms = statistics.mean(g1), statistics.mean(g2)
-    # The consumer GEMM alone, `steps` launches back to back between ONE pair of events: the average launch
-    # duration without an event record (a submission and a pipeline drain of its own) around every launch.
-    for _ in range(args.warmup):
-        shard.run_single(2, cs)
-    l0, l1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    l0.record(cs)
-    for _ in range(args.steps):
-        shard.run_single(2, cs)
-    l1.record(cs)
-    torch.cuda.synchronize()
-    t2_ms = l0.elapsed_time(l1) / args.steps
-    # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the consumer GEMM, from the ncu captures
-    # summarised in profiles/cusync_gemm_pair_kernel_gpt3_mlp.md (bytes; None where no capture exists)
-    traffic = {512: 222.6e6, 2048: 688.9e6}.get(args.batch)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    kernel_clock = ClockSampler(local_rank, period_ms=20)
+    if rank == 0:
+        kernel_clock.start()
+    t2_ms = loop_ms(lambda: base.run_single(2, cs), loop_n)
+    t1_ms = loop_ms(lambda: base.run_single(1, cs), loop_n)
+    t12_ms = loop_ms(lambda: base.run_stream_ordered(cs), loop_n)
+    kclk = kernel_clock.stop() if rank == 0 else {"sm_mhz": None}
+    traffic = load_traffic("cusync_gemm_pair_kernel GEMM2", args.batch) if args.batch > 256 else None
     tensor_bound = args.batch >= 256
     kernel_name = ("cusync_gemm_pair_kernel (GEMM2, the consumer)" if args.batch > 256
                    else "cusync_gemm_kernel<%d,0> (GEMM2, the consumer)" % shard.tile_n2)
+    mhz = kclk.get("sm_mhz")
+    timing = {"launch_ms": t2_ms, "gemm1_ms": t1_ms, "both_in_a_row_ms": t12_ms,
+              "sum_of_the_two_over_both_in_a_row": (t1_ms + t2_ms) / t12_ms,
+              "launches_per_loop": loop_n, "sm_mhz_during_loops": mhz,
+              "launch_ms_x_mhz": t2_ms * mhz if mhz else None,
+              "how": "each figure = %d launches back to back between one pair of events on the launching stream; the "
+                     "three loops run one after the other under one clock sampler" % loop_n}
     if tensor_bound:
         achieved = flops2 / (t2_ms * 1e-3) / 1e12
-        peak = peaks["tflops_sustained"]
-        roofline = {"bound": "tensor", "kernel": kernel_name,
-                    "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                    "peak_kind": "%s sustained bf16/fp16 cuBLAS" % peaks["source"],
-                    "frac_of_burst_peak": achieved / peaks["tflops_burst"], "traffic": traffic,
-                    "launch_ms": t2_ms, "launch_ms_event_bracketed": t2_bracketed_ms, "gemm1_ms": t1_ms,
-                    "how": "launch_ms = consumer GEMM alone, steps launches back to back between one pair of events",
+        roofline = {"bound": "tensor", "kernel": kernel_name, "achieved": achieved, "peak": peaks["tflops_burst"],
+                    "unit": "TFLOP/s", "frac": achieved / peaks["tflops_burst"],
+                    "peak_kind": "%s burst bf16/fp16 cuBLAS figure (the kernel is timed alone)" % peaks["source"],
+                    "frac_of_sustained_peak": achieved / peaks["tflops_sustained"], "traffic": traffic,
                     "gemm1_tflops": flops2 / (t1_ms * 1e-3) / 1e12}
     else:
         bytes2 = 2.0 * (M.GPT3_FFN * M.GPT3_HIDDEN + args.batch * (M.GPT3_FFN + M.GPT3_HIDDEN))
         achieved = bytes2 / (t2_ms * 1e-3) / 1e9
-        roofline = {"bound": "hbm", "kernel": kernel_name,
-                    "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
-                    "peak_kind": "%s copy bandwidth" % peaks["source"], "traffic": traffic, "launch_ms": t2_ms,
-                    "launch_ms_event_bracketed": t2_bracketed_ms, "gemm1_ms": t1_ms}
+        roofline = {"bound": "hbm", "kernel": kernel_name, "achieved": achieved, "peak": peaks["hbm_gbs"],
+                    "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                    "peak_kind": "%s copy bandwidth" % peaks["source"], "traffic": traffic}
+    roofline.update(timing)
 
     # ---- end to end through the C ABI with host buffers ---------------------------------------
     xh = torch.empty((args.batch, M.GPT3_HIDDEN), dtype=torch.half).pin_memory()
@@ -388,25 +520,34 @@ def main():
     # the SMs here: a persistent kernel that holds every SM while it waits for rows of X keeps the second GEMM
     # from becoming resident, and with it the first rows of Y from leaving while the last rows of X arrive.  The
     # step is bound by the PCIe link, not by the GEMMs, so halving their rate costs nothing.
-    e2e_shard = shard
+    e2e_shard, e2e_reducer = shard, None
     d2h_blocks = 4
-    if world == 1 and args.batch >= 512:
+    row_blocks = args.batch >= 512
+    if row_blocks:
         d2h_blocks = max(4, min(8, args.batch // 256))
-        e2e_ctas = torch.cuda.get_device_properties(dev).multi_processor_count // 4 * 2
-        e2e_shard = M.MLPShard("gpt3", args.batch, shard.x, shard.w1, shard.w2, None, policy=args.policy, post_rows=True,
-                               x_rows=True, max_ctas=e2e_ctas, group_rows2=2)
+        if world == 1:
+            e2e_ctas = sms // 4 * 2
+            e2e_shard = M.MLPShard("gpt3", args.batch, shard.x, shard.w1, shard.w2, None, policy=args.policy,
+                                   post_rows=True, x_rows=True, max_ctas=e2e_ctas, group_rows2=2, single_grid=1)
+        else:
+            # N > 1: X still arrives in row blocks behind semaphores; Y leaves once the all-reduce has finished
+            if overlap_reduce:
+                e2e_reducer = tp.RowAllReduce(group, args.batch, M.GPT3_HIDDEN, dev, num_ctas=args.reduce_ctas)
+            e2e_shard = M.MLPShard("gpt3", args.batch, shard.x, shard.w1, shard.w2, None, policy=args.policy,
+                                   post_rows=True, x_rows=True,
+                                   max_ctas=sms - (e2e_reducer.num_ctas if e2e_reducer else 0),
+                                   y=e2e_reducer.y if e2e_reducer else None)
     d2h, h2d, post = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
     landed = [torch.cuda.Event() for _ in range(d2h_blocks)]
 
     def e2e_step():
-        ps.wait_stream(cs)
         tiles = (args.batch + 127) // 128
         per = (tiles + d2h_blocks - 1) // d2h_blocks
-        if e2e_shard is not shard:
+        if row_blocks:
             # X comes in row blocks on its own stream, each followed by the post of its RowSync semaphores; the
             # first GEMM is launched right away and takes the rows as they land (x_rows)
-            h2d.wait_stream(ps)
-            post.wait_stream(ps)
+            h2d.wait_stream(cs)
+            post.wait_stream(cs)
             for first in range(0, tiles, per):
                 n = min(per, tiles - first)
                 r0, r1 = first * 128, min(args.batch, (first + n) * 128)
@@ -420,8 +561,11 @@ def main():
         else:
             with torch.cuda.stream(ps):
                 e2e_shard.x.copy_(xh, non_blocking=True)
-        e2e_shard.run_cusync(ps, cs)
-        if e2e_shard is not shard:
+        if e2e_reducer is not None:
+            e2e_shard.run_cusync_allreduce(e2e_reducer, ps, cs, rs)
+        else:
+            e2e_shard.run_cusync(ps, cs)
+        if row_blocks and world == 1:
             for first in range(0, tiles, per):
                 n = min(per, tiles - first)
                 e2e_shard.wait_rows(first, n, d2h)
@@ -431,7 +575,8 @@ def main():
             cs.wait_stream(d2h)
         else:
             with torch.cuda.stream(cs):
-                group.all_reduce_sum(e2e_shard.y)
+                if world > 1 and e2e_reducer is None:
+                    group.all_reduce_sum(e2e_shard.y)
                 yh.copy_(e2e_shard.y, non_blocking=True)
 
     e2e_total, _ = time_steps(e2e_step, ps, cs, args.steps, args.warmup, barrier)
@@ -441,6 +586,8 @@ def main():
         if not torch.equal(yh, e2e_shard.y.cpu()):
             raise SystemExit("end-to-end result on the host differs from the device result")
         e2e_shard.destroy()
+        if e2e_reducer is not None:
+            e2e_reducer.destroy()
     io_bytes = args.batch * M.GPT3_HIDDEN * 2
 
     # ---- per-batch table ------------------------------------------------------------------------
@@ -449,7 +596,7 @@ def main():
         for b in SWEEP_BATCHES:
             row = {"batch": b}
             for pol in ("rowsync", "tilesync"):
-                s = build(b, pol)
+                s = M.MLPShard("gpt3", b, *M.make_inputs("gpt3", b, dev, seed=rank), policy=pol)
 
                 def c_step(s=s):
                     s.run_cusync(ps, cs)
@@ -506,9 +653,7 @@ def main():
             for pol in ("rowsync", "tilesync"):
                 sh = M.MLPShard("llama", b, x, w1, w2, v, policy=pol)
 
-                def c_step(sh=sh):
-                    ps.wait_stream(cs); sh.run_cusync(ps, cs)
-                r = ab(c_step, lambda sh=sh: sh.run_stream_ordered(cs))
+                r = ab(lambda sh=sh: sh.run_cusync(ps, cs), lambda sh=sh: sh.run_stream_ordered(cs))
                 r.update({"batch": b, "policy": pol, "tile_n": [sh.tile_n1, sh.tile_n2],
                           "split_k": [sh.split_k1, sh.split_k2]})
                 rows.append(r); sh.destroy()
@@ -523,7 +668,7 @@ def main():
             chain = lib_.ConvChain(xin, [f1, f2], relu=True)     # cusync_conv_chain_*: the resnet.cu flow in C
 
             def c_step():
-                ps.wait_stream(cs); chain.run_cusync([ps, cs])
+                chain.run_cusync([ps, cs])
 
             def o_step():
                 chain.run_stream_ordered(cs)
@@ -542,7 +687,7 @@ def main():
         side = [torch.cuda.Stream(), torch.cuda.Stream()]
 
         def c4_step():
-            ps.wait_stream(cs); chain.run_cusync([ps, side[0], side[1], cs])
+            chain.run_cusync([ps, side[0], side[1], cs])
 
         def o4_step():
             chain.run_stream_ordered(cs)
@@ -562,10 +707,52 @@ def main():
             blk = AttentionBlock(xin, wqkv, kc, vc, wo, 12)     # cusync_attn_block_*: the attention.cu flow in C
 
             def c_step():
-                ps.wait_stream(s3); blk.run((ps, cs, s3)); cs.wait_stream(s3)
+                blk.run((ps, cs, s3)); cs.wait_stream(s3)
             r = ab(c_step, lambda: blk.run_stream_ordered(cs))
             r.update({"batch": b, "context": seq, "config": blk.config})
             rows.append(r); blk.destroy()
+        extras["gpt3_attention_block"] = rows
+    if not args.no_sweep and world > 1:
+        # the other sharded workloads at N GPUs: LLaMA MLP shard (config 3) with the overlapped all-reduce, and the
+        # attention block (config 4: 12 of 96 heads per rank) with NCCL's all-reduce of its output after the chain
+        from cusync_b200.attention import AttentionBlock
+        s3 = torch.cuda.Stream()
+        rows = []
+        for b in (64, 512, 2048):
+            lb = Layer("llama", b, "rowsync", seed=rank)
+            lb.check()
+            c_per, o_per = interleaved(lb.cusync_step, (ps, cs), lb.ordered_step, (cs, cs), 20, 3)
+            n_per, l_per = interleaved(lb.chain_only_step, (ps, cs), lb.cusync_step, (ps, cs), 20, 3)
+            rows.append({"batch": b, "cusync_us": round(med_us(c_per), 2), "stream_ordered_us": round(med_us(o_per), 2),
+                         "gain_pct": round(100.0 - med_us(c_per) / med_us(o_per) * 100.0, 2),
+                         "layer_without_allreduce_us": round(med_us(n_per), 2), "ok": lb.status_ok()})
+            lb.destroy()
+        extras["llama_mlp"] = rows
+        rows = []
+        for b, seq in ((1, 2048), (4, 2048)):
+            g = torch.Generator(device=dev).manual_seed(7 + rank)
+            xin = torch.randn((b, 12288), generator=g, device=dev).half()
+            wqkv = (torch.randn((12288, 4608), generator=g, device=dev) * 0.02).half()
+            wo = (torch.randn((1536, 12288), generator=g, device=dev) * 0.02).half()
+            kc = torch.randn((b, seq, 12, 128), generator=g, device=dev).half()
+            vc = torch.randn((b, seq, 12, 128), generator=g, device=dev).half()
+            blk = AttentionBlock(xin, wqkv, kc, vc, wo, 12)
+
+            def c_step():
+                blk.run((ps, cs, s3)); cs.wait_stream(s3)
+                with torch.cuda.stream(cs):
+                    group.all_reduce_sum(blk.y)
+
+            def o_step():
+                blk.run_stream_ordered(cs)
+                with torch.cuda.stream(cs):
+                    group.all_reduce_sum(blk.y)
+            c_per, o_per = interleaved(c_step, (ps, cs), o_step, (cs, cs), 20, 3)
+            rows.append({"batch": b, "context": seq, "cusync_us": round(med_us(c_per), 2),
+                         "stream_ordered_us": round(med_us(o_per), 2),
+                         "gain_pct": round(100.0 - med_us(c_per) / med_us(o_per) * 100.0, 2),
+                         "all_reduce": "NCCL, after the output projection"})
+            blk.destroy()
         extras["gpt3_attention_block"] = rows
     clocks = sampler.stop() if rank == 0 else None
 
@@ -592,6 +779,7 @@ def main():
             "launch_form": ("one persistent grid for both GEMMs" if shard.single_grid
                             else "one launch per GEMM and a wait kernel"),
             "clocks": clocks,
+            "multi_gpu": multi,
             "per_batch": table,
             "other_workloads": extras}
     if not args.no_cpu:

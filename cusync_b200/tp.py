@@ -45,8 +45,8 @@ class RowAllReduce:
             hf = symm_mem.rendezvous(self.flags, group.dist.group.WORLD)
             self._handles = (hy, hf)
             bufs, flags = list(hy.buffer_ptrs), list(hf.buffer_ptrs)
-            mc_y = int(hy.multicast_ptr) if multicast and hy.has_multicast_support(device.type, device.index) else 0
-            mc_f = int(hf.multicast_ptr) if mc_y else 0
+            mc_y = int(hy.multicast_ptr or 0) if multicast else 0     # 0 where the box offers no NVLS multicast
+            mc_f = int(hf.multicast_ptr or 0) if mc_y else 0
             if not (mc_y and mc_f):
                 mc_y = mc_f = 0
             self.uses_multicast = bool(mc_y)

@@ -181,6 +181,14 @@ uint16_t orc_float_to_half(float f) {
   _Float16 v = (_Float16)f; uint16_t h; memcpy(&h, &v, 2); return h;
 }
 
+void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 int orc_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

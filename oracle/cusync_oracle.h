@@ -141,6 +141,8 @@ double orc_max_rel_err_f16(size_t n, const uint16_t* got, const uint16_t* ref,
 
 /* Number of OpenMP threads the arithmetic functions will use. */
 int orc_num_threads(void);
+/* Threads the OpenMP loops use from now on (a launcher may have exported OMP_NUM_THREADS=1). */
+void orc_set_num_threads(int n);
 
 #ifdef __cplusplus
 }

@@ -81,6 +81,8 @@ def lib():
     L.orc_max_rel_err_f16.restype = C.c_double
     L.orc_max_rel_err_f16.argtypes = [C.c_size_t, vp, vp, C.c_double]
     L.orc_num_threads.restype = i32
+    L.orc_set_num_threads.restype = None
+    L.orc_set_num_threads.argtypes = [i32]
     _lib = L
     return L
 
@@ -183,6 +185,10 @@ def check_final_output(y_gpu, y_oracle, y_exact, what, tol=1e-2):
           % (what, e_gpu, e_orc, direct))
     assert e_gpu <= max(tol, 1.25 * e_orc + 1e-3), (e_gpu, e_orc)
     assert max_rel_err(y_gpu, y_oracle, floor_frac=5e-2) <= tol
+
+
+def set_num_threads(n):
+    lib().orc_set_num_threads(int(n))
 
 
 def num_threads():
