@@ -172,7 +172,7 @@ def workload_config(args, shard):
            "l2": "inputs larger than L2 (302 MB of weights per step vs 126 MB L2); no explicit flush",
            "all_reduce": (("sum of Y[B,12288] fp16 across ranks by this library's kernel beside the second GEMM "
                            "(%d blocks; the GEMMs use the other SMs)" % args.reduce_ctas
-                           if getattr(args, "reduce", "overlapped") == "overlapped"
+                           if getattr(args, "reduce", "overlapped") == "overlapped" and args.batch >= 512
                            else "NCCL sum of Y[B,12288] fp16 across ranks, after the layer")
                           if args.gpus > 1 else "none (1 GPU)")}
     if shard is not None:
@@ -247,7 +247,9 @@ def main():
     ap.add_argument("--reduce", choices=("overlapped", "nccl"), default="overlapped",
                     help="multi-GPU: the all-reduce of Y as this library's kernel beside the second GEMM (default), "
                          "or NCCL's all-reduce after the layer")
-    ap.add_argument("--reduce-ctas", type=int, default=8, help="blocks of the overlapped all-reduce kernel")
+    ap.add_argument("--reduce-ctas", type=int, default=0,
+                    help="blocks of the overlapped all-reduce kernel (0 = choose: 8 at 2 ranks, 4 from 4 ranks on; a "
+                         "rank reduces 1/N of the matrix, so fewer SMs keep up as N grows)")
     ap.add_argument("--no-sweep", action="store_true", help="skip the per-batch table and the other workloads")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
@@ -284,6 +286,11 @@ def main():
     cs = torch.cuda.Stream(priority=0)
     rs = torch.cuda.Stream(priority=0)    # multi-GPU: the all-reduce kernel that runs beside the GEMMs
     overlap_reduce = world > 1 and args.reduce == "overlapped"
+    if args.reduce_ctas <= 0:
+        args.reduce_ctas = 8 if world <= 2 else 4
+    # Below four row tiles the all-reduce cannot start before the second GEMM is all but done: nothing to overlap,
+    # and NCCL's all-reduce after the layer is the better form.
+    OVERLAP_MIN_BATCH = 512
 
     class Layer:
         """One tensor-parallel layer of `model` at `batch`: the synchronised chain with its all-reduce (this
@@ -293,7 +300,7 @@ def main():
             x, w1, w2, v = M.make_inputs(model, batch, dev, seed=seed)
             self.model, self.batch = model, batch
             self.reducer = None
-            if overlap_reduce:
+            if overlap_reduce and batch >= OVERLAP_MIN_BATCH:
                 self.reducer = tp.RowAllReduce(group, batch, x.shape[1], dev, num_ctas=args.reduce_ctas)
                 self.shard = M.MLPShard(model, batch, x, w1, w2, v, policy=policy, post_rows=True,
                                         max_ctas=sms - self.reducer.num_ctas, y=self.reducer.y)
@@ -531,7 +538,7 @@ def main():
                                    post_rows=True, x_rows=True, max_ctas=e2e_ctas, group_rows2=2, single_grid=1)
         else:
             # N > 1: X still arrives in row blocks behind semaphores; Y leaves once the all-reduce has finished
-            if overlap_reduce:
+            if overlap_reduce and args.batch >= OVERLAP_MIN_BATCH:
                 e2e_reducer = tp.RowAllReduce(group, args.batch, M.GPT3_HIDDEN, dev, num_ctas=args.reduce_ctas)
             e2e_shard = M.MLPShard("gpt3", args.batch, shard.x, shard.w1, shard.w2, None, policy=args.policy,
                                    post_rows=True, x_rows=True,

@@ -26,8 +26,8 @@
 namespace {
 
 constexpr int kMaxWorld = 8;
-constexpr int kWorkerThreads = 512;
-constexpr int kThreads = kWorkerThreads + 32;     // + one watcher warp (active in block 0 only)
+constexpr int kThreads = 1024;                    // block 0: 31 worker warps + the watcher warp; other blocks: 32 worker warps
+constexpr int kWatcherWarp = kThreads / 32 - 1;
 constexpr int kFlagHeader = 8;                    // [0] done counter, [1..7] spare; then one ready counter per row tile
 
 struct ArParams {
@@ -108,6 +108,7 @@ __device__ __forceinline__ void add8(float (&acc)[8], uint4 v) {
   }
 }
 
+template <bool kMulticast>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) cusync_allreduce_rows_kernel(const ArParams p) {
   __shared__ volatile uint32_t s_abort;
   if (threadIdx.x == 0) s_abort = 0u;
@@ -115,9 +116,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) cusync_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint32_t* const my_flags = p.flags[p.rank];
 
-  if (warp == kWorkerThreads / 32) {
-    // ---- watcher (block 0): publish this rank's finished row tiles to every rank ----------------------
-    if (blockIdx.x != 0) return;
+  if (blockIdx.x == 0 && warp == kWatcherWarp) {
+    // ---- watcher: publish this rank's finished row tiles to every rank -------------------------------
     for (int t = lane; t < p.num_tiles; t += 32) {
       if (p.row_sems) {
         uint32_t seen = 0;
@@ -129,7 +129,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) cusync_
         }
       }
       fence_sys();        // the producer's stores (acquired at gpu scope) before the system-scope signal
-      if (p.mc_flags) multimem_red_add_release_sys(p.mc_flags + kFlagHeader + t, 1u);
+      if (kMulticast) multimem_red_add_release_sys(p.mc_flags + kFlagHeader + t, 1u);
       else
         for (int w = 0; w < p.world; w++) red_add_release_sys(p.flags[(p.rank + w) % p.world] + kFlagHeader + t, 1u);
     }
@@ -138,8 +138,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) cusync_
 
   // ---- workers ---------------------------------------------------------------------------------------
   const int vec_per_row = p.cols / 8;
-  const uint32_t worker = blockIdx.x * kWorkerThreads + threadIdx.x;
-  const uint32_t num_workers = gridDim.x * kWorkerThreads;
+  const uint32_t workers0 = kThreads - 32;                      // block 0 gives one warp to the watcher
+  const uint32_t block_workers = blockIdx.x == 0 ? workers0 : static_cast<uint32_t>(kThreads);
+  const uint32_t worker = blockIdx.x == 0 ? threadIdx.x : workers0 + (blockIdx.x - 1) * kThreads + threadIdx.x;
+  const uint32_t num_workers = workers0 + (gridDim.x - 1) * kThreads;
+  const bool contiguous = p.ld == p.cols;
   bool ok = true;
   for (int t = 0; t < p.num_tiles && ok; t++) {
     // all ranks have published tile t
@@ -162,20 +165,27 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) cusync_
     const int r_begin = row0 + static_cast<int>(static_cast<long long>(rows_in) * p.rank / p.world);
     const int r_end = row0 + static_cast<int>(static_cast<long long>(rows_in) * (p.rank + 1) / p.world);
     const uint32_t vecs = static_cast<uint32_t>(r_end - r_begin) * static_cast<uint32_t>(vec_per_row);
-    if (p.mc_buf) {
-      constexpr int kUnroll = 4;
+    if (kMulticast) {
+      // Latency-bound: a multimem.ld_reduce is a round trip through the switch of a few microseconds, so every
+      // thread keeps eight of them in flight (128 KB per block) before it turns to the stores.
+      constexpr int kUnroll = 8;
+      __half* const slice = p.mc_buf + static_cast<size_t>(r_begin) * p.ld;
       for (uint32_t base = worker; base < vecs; base += num_workers * kUnroll) {
         uint4 v[kUnroll];
-        size_t off[kUnroll];
 #pragma unroll
         for (int u = 0; u < kUnroll; u++) {
           const uint32_t i = base + u * num_workers;
-          off[u] = static_cast<size_t>(r_begin + i / vec_per_row) * p.ld + static_cast<size_t>(i % vec_per_row) * 8;
-          if (i < vecs) v[u] = multimem_ld_reduce_f16x8(p.mc_buf + off[u]);
+          if (i < vecs)
+            v[u] = multimem_ld_reduce_f16x8(contiguous ? slice + static_cast<size_t>(i) * 8
+                                                        : slice + static_cast<size_t>(i / vec_per_row) * p.ld + (i % vec_per_row) * 8);
         }
 #pragma unroll
-        for (int u = 0; u < kUnroll; u++)
-          if (base + u * num_workers < vecs) multimem_st_f16x8(p.mc_buf + off[u], v[u]);
+        for (int u = 0; u < kUnroll; u++) {
+          const uint32_t i = base + u * num_workers;
+          if (i < vecs)
+            multimem_st_f16x8(contiguous ? slice + static_cast<size_t>(i) * 8
+                                         : slice + static_cast<size_t>(i / vec_per_row) * p.ld + (i % vec_per_row) * 8, v[u]);
+        }
       }
     } else {
       for (uint32_t i = worker; i < vecs; i += num_workers) {
@@ -200,9 +210,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) cusync_
   }
   // ---- every rank's stores are in place before any rank's kernel ends -----------------------------------
   fence_sys();
-  asm volatile("bar.sync 1, %0;" ::"n"(kWorkerThreads) : "memory");
+  asm volatile("bar.sync 1, %0;" ::"r"(block_workers) : "memory");
   if (threadIdx.x == 0) {
-    if (p.mc_flags) multimem_red_add_release_sys(p.mc_flags, 1u);
+    if (kMulticast) multimem_red_add_release_sys(p.mc_flags, 1u);
     else
       for (int w = 0; w < p.world; w++) red_add_release_sys(p.flags[(p.rank + w) % p.world], 1u);
     const uint32_t expected = p.epoch * static_cast<uint32_t>(p.world) * gridDim.x;
@@ -264,7 +274,8 @@ int cusync_allreduce_plan_create(cusync_allreduce_plan_t** out, const cusync_all
   p.status = pl->status;
   // Load the kernel now: its launches come while other persistent kernels may be running (see stage.cu).
   cudaFuncAttributes attr;
-  if (cudaFuncGetAttributes(&attr, cusync_allreduce_rows_kernel) != cudaSuccess) (void)cudaGetLastError();
+  if (cudaFuncGetAttributes(&attr, cusync_allreduce_rows_kernel<true>) != cudaSuccess) (void)cudaGetLastError();
+  if (cudaFuncGetAttributes(&attr, cusync_allreduce_rows_kernel<false>) != cudaSuccess) (void)cudaGetLastError();
   *out = pl;
   return CUSYNC_SUCCESS;
 }
@@ -281,7 +292,8 @@ int cusync_allreduce_run(cusync_allreduce_plan_t* pl, const uint32_t* row_semaph
   ArParams p = pl->params;
   p.row_sems = row_semaphores;
   p.sem_target = value;
-  cusync_allreduce_rows_kernel<<<pl->num_ctas, kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+  if (p.mc_buf) cusync_allreduce_rows_kernel<true><<<pl->num_ctas, kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+  else          cusync_allreduce_rows_kernel<false><<<pl->num_ctas, kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
   if (cudaGetLastError() != cudaSuccess) return CUSYNC_ERROR_CUDA;
   pl->params.epoch += 1;         // counted only when the launch went out: every rank must run equally often
   return CUSYNC_SUCCESS;

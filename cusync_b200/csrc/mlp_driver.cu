@@ -125,7 +125,9 @@ int cusync_mlp_create(cusync_mlp_t** out, const cusync_mlp_desc_t* desc) {
   cusync_mlp_desc_t& dd = m->desc;
   if (dd.policy == 0) dd.policy = choice.policy;
   if (dd.group_rows1 == 0) dd.group_rows1 = choice.group_rows1;
-  if (dd.group_rows2 == 0) dd.group_rows2 = choice.group_rows2;
+  // post_rows: whoever consumes Y (an all-reduce beside the GEMM, a copy) wants its rows to complete one after
+  // the other, not a whole group at once at the end: pair-row groups unless the caller says otherwise
+  if (dd.group_rows2 == 0) dd.group_rows2 = dd.post_rows ? 2 : choice.group_rows2;
   const int single_grid_wanted = dd.single_grid ? dd.single_grid : choice.single_grid;
   const cusync_mlp_desc_t& d = m->desc;
   const int epi1 = d.model == CUSYNC_MLP_LLAMA ? CUSYNC_EPILOGUE_SILU_MUL_DUAL : CUSYNC_EPILOGUE_GELU_ERF;
@@ -262,7 +264,17 @@ int run_cusync_impl(cusync_mlp_t* m, cusync_allreduce_plan_t* reducer, cusync_st
   if (reducer) {
     // The reducer goes out first, so that it is resident on its SMs before the persistent GEMM blocks take the
     // rest; it waits, tile by tile, for this run's RowSync posts of the second GEMM.
-    if (!m->order.begin(reduce_stream)) { (void)cudaGetLastError(); return CUSYNC_ERROR_CUDA; }
+    // ... but not before the point the producer stream has reached: whatever the caller put there (the previous
+    // layer, a copy) must not find some of the SMs taken by a kernel that only spins
+    if (!m->reduced && cudaEventCreateWithFlags(&m->reduced, cudaEventDisableTiming) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return CUSYNC_ERROR_CUDA;
+    }
+    if (cudaEventRecord(m->reduced, reinterpret_cast<cudaStream_t>(producer_stream)) != cudaSuccess ||
+        cudaStreamWaitEvent(reinterpret_cast<cudaStream_t>(reduce_stream), m->reduced, 0) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return CUSYNC_ERROR_CUDA;
+    }
     cusync_stage_view_t v;
     cusync_stage_get_view(m->cons, &v);
     rc = cusync_allreduce_run(reducer, v.sems_post, v.iter * v.grid.x, reduce_stream);
@@ -285,9 +297,6 @@ int run_cusync_impl(cusync_mlp_t* m, cusync_allreduce_plan_t* reducer, cusync_st
   }
   if (rc != CUSYNC_SUCCESS) return rc;      // nothing counted: the stages stay at this run's iteration
   if (reducer) {                            // the layer's result is complete once the reducer has finished
-    if (!m->reduced) {
-      if (cudaEventCreateWithFlags(&m->reduced, cudaEventDisableTiming) != cudaSuccess) { (void)cudaGetLastError(); return CUSYNC_ERROR_CUDA; }
-    }
     if (cudaEventRecord(m->reduced, reinterpret_cast<cudaStream_t>(reduce_stream)) != cudaSuccess ||
         cudaStreamWaitEvent(reinterpret_cast<cudaStream_t>(consumer_stream), m->reduced, 0) != cudaSuccess) {
       (void)cudaGetLastError();
