@@ -197,6 +197,11 @@ SIGNATURES = {
     "cusync_allreduce_read_status": (_i, [_vp, C.POINTER(Status)]),
     "cusync_allreduce_plan_num_ctas": (_u32, [_vp]),
     "cusync_mlp_run_cusync_allreduce": (_i, [_vp, _vp, _vp, _vp, _vp]),
+    "cusync_tp_unique_id": (_i, [_vp]),
+    "cusync_tp_comm_create": (_i, [C.POINTER(_vp), C.c_int32, C.c_int32, _vp]),
+    "cusync_tp_comm_destroy": (_i, [_vp]),
+    "cusync_tp_all_reduce": (_i, [_vp, _vp, _u64, _vp]),
+    "cusync_tp_layer_run": (_i, [_vp, _vp, _vp, _vp, _u64, _vp, _vp, _vp]),
     "cusync_b200_version": (C.c_char_p, []),
     "cusync_b200_sm_count": (_i, []),
 }

@@ -11,7 +11,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 LIB = os.path.join(HERE, "libcusync_b200.so")
-SOURCES = ["stage.cu", "gemm_sm100.cu", "mlp_driver.cu", "attention.cu", "conv_driver.cu", "attention_driver.cu", "allreduce.cu"]
+SOURCES = ["stage.cu", "gemm_sm100.cu", "mlp_driver.cu", "attention.cu", "conv_driver.cu", "attention_driver.cu", "allreduce.cu", "tp_driver.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
@@ -51,7 +51,7 @@ def build(force=False, verbose=False):
         if p.returncode != 0:
             raise RuntimeError("nvcc failed on %s:\n%s" % (src, out.decode()))
     subprocess.check_call([NVCC, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB, *objs,
-                           "-Xcompiler", "-fPIC"])
+                           "-Xcompiler", "-fPIC", "-ldl"])
     return LIB
 
 

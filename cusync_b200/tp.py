@@ -92,6 +92,45 @@ class RowAllReduce:
             self._plan = None
 
 
+class NativeComm:
+    """The NCCL communicator of the C ABI (cusync_tp_comm_*): created from a unique id that rank 0 draws and the
+    process group hands round; cusync_tp_layer_run then runs a layer and its ncclAllReduce without Python's help."""
+
+    def __init__(self, group):
+        import ctypes as C
+        from . import _lib as L
+        self.group = group
+        uid = (C.c_char * 128)()
+        if group.rank == 0 and group.world > 1:
+            L.check(L.lib().cusync_tp_unique_id(uid), "cusync_tp_unique_id")
+        if group.world > 1:
+            box = [bytes(uid)]
+            group.dist.broadcast_object_list(box, src=0)
+            uid = (C.c_char * 128).from_buffer_copy(box[0])
+        self._h = C.c_void_p()
+        L.check(L.lib().cusync_tp_comm_create(C.byref(self._h), group.world, group.rank, uid), "cusync_tp_comm_create")
+
+    def all_reduce(self, tensor, stream):
+        from . import _lib as L
+        from .api import _stream_ptr
+        L.check(L.lib().cusync_tp_all_reduce(self._h, tensor.data_ptr(), tensor.numel(), _stream_ptr(stream)),
+                "cusync_tp_all_reduce")
+
+    def layer_run(self, shard, producer_stream, consumer_stream, reducer=None, reduce_stream=None):
+        """One layer of `shard` with its all-reduce (cusync_tp_layer_run)."""
+        from . import _lib as L
+        from .api import _stream_ptr
+        L.check(L.lib().cusync_tp_layer_run(shard._h, self._h, reducer._plan if reducer is not None else None,
+                                            shard.y.data_ptr(), shard.y.numel(), _stream_ptr(producer_stream),
+                                            _stream_ptr(consumer_stream), _stream_ptr(reduce_stream)), "cusync_tp_layer_run")
+
+    def destroy(self):
+        from . import _lib as L
+        if self._h:
+            L.lib().cusync_tp_comm_destroy(self._h)
+            self._h = None
+
+
 class TensorParallelGroup:
     """World of the layer's ranks.  backend "nccl" on GPUs (NVLink/NVSwitch), "gloo" for the CPU tests."""
 

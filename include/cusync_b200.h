@@ -595,6 +595,30 @@ CUSYNC_API int cusync_mlp_run_cusync_allreduce(cusync_mlp_t* mlp, cusync_allredu
                                                cusync_stream_t producer_stream, cusync_stream_t consumer_stream,
                                                cusync_stream_t reduce_stream);
 
+/* ---- tensor-parallel layer (one process per GPU) ------------------------- */
+
+/* The sharded layer with its collective below the C ABI: rank r of `world` holds the r-th column slice of W1 (and
+ * V) and the r-th row slice of W2 (the shard shapes of src/ml-bench/transformer/mlp.cu:243-251), X is replicated,
+ * and the layer ends with the sum all-reduce of Y over the ranks, the collective the reference times on its own
+ * (allreduce_times.py:11-35).  cusync_tp_layer_run runs one layer of a cusync_mlp_t either
+ *   - with `reducer`: the all-reduce kernel of this library beside the second GEMM
+ *     (cusync_mlp_run_cusync_allreduce; the shard was created with post_rows and Y is the reducer's matrix), or
+ *   - without: cusync_mlp_run_cusync, then ncclAllReduce(sum, fp16, in place) of y[0 .. y_count) on
+ *     consumer_stream over `comm` (nothing when the communicator has one rank).
+ * The NCCL communicator is created here: rank 0 calls cusync_tp_unique_id and hands the 128 bytes to every rank by
+ * whatever channel the application has (a file, a socket, another library's broadcast); then every rank calls
+ * cusync_tp_comm_create with its device current.  NCCL is taken from the process's libnccl.so.2 at run time:
+ * CUSYNC_ERROR_UNSUPPORTED where there is none. */
+typedef struct cusync_tp_comm cusync_tp_comm_t;
+CUSYNC_API int cusync_tp_unique_id(void* out128);
+CUSYNC_API int cusync_tp_comm_create(cusync_tp_comm_t** out, int32_t world, int32_t rank, const void* unique_id128);
+CUSYNC_API int cusync_tp_comm_destroy(cusync_tp_comm_t* comm);
+/* ncclAllReduce(sum) of `count` fp16 values in place on `stream`. */
+CUSYNC_API int cusync_tp_all_reduce(cusync_tp_comm_t* comm, void* buffer, uint64_t count, cusync_stream_t stream);
+CUSYNC_API int cusync_tp_layer_run(cusync_mlp_t* mlp, cusync_tp_comm_t* comm, cusync_allreduce_plan_t* reducer, void* y,
+                                   uint64_t y_count, cusync_stream_t producer_stream, cusync_stream_t consumer_stream,
+                                   cusync_stream_t reduce_stream);
+
 /* Library / device information. */
 CUSYNC_API const char* cusync_b200_version(void);
 CUSYNC_API int cusync_b200_sm_count(void);

@@ -65,6 +65,21 @@ def main():
         scale = ref.y.float().abs().max().item()
         err = (over.y.float() - ref.y.float()).abs().max().item()
         assert err <= 4e-3 * scale, (run, err, scale)          # two fp16 roundings of sums ordered differently
+    # the same two forms through the C ABI's own driver and communicator (cusync_tp_*): NCCL is called from C
+    comm = tp.NativeComm(g)
+    plain = M.MLPShard("gpt3", batch, x, w1, w2, None, policy="rowsync")
+    for run in range(2):
+        plain.y.fill_(float("nan")); over.y.fill_(float("nan")); torch.cuda.synchronize(); g.barrier()
+        comm.layer_run(plain, ps, cs)
+        comm.layer_run(over, ps, cs, reducer=ar, reduce_stream=rs)
+        torch.cuda.synchronize(); g.barrier()
+        assert torch.equal(plain.y, ref.y)                       # same kernels, same NCCL all-reduce
+        err = (over.y.float() - ref.y.float()).abs().max().item()
+        assert err <= 4e-3 * ref.y.float().abs().max().item()
+    t = torch.full((1000,), float(g.rank + 1), device=dev, dtype=torch.half)
+    comm.all_reduce(t, torch.cuda.current_stream()); torch.cuda.synchronize()
+    assert (t == sum(range(1, g.world + 1))).all()
+    plain.destroy(); comm.destroy()
     over.destroy(); ref.destroy(); ar.destroy()
     print("TP_WORKER_OK %d" % g.rank, flush=True)
     g.close()
