@@ -235,6 +235,44 @@ def load_traffic(kernel_key, batch):
     return None
 
 
+def overlap_timeline(shard, ps, cs):
+    """What the consumer GEMM's tiles do while the producer's last tiles still run, from one traced run of the
+    synchronised layer (the per-tile timeline of the CTA-pair kernels): the evidence a profiler cannot give,
+    since it serialises the two kernels."""
+    import numpy as np
+    for _ in range(3):
+        shard.run_cusync(ps, cs)
+    t1, t2 = shard.traced_run(ps, cs)
+    g1, g2 = t1[0::2], t2[0::2]                  # the leader CTA's record of every work unit
+    g1, g2 = g1[g1[:, 0] > 0], g2[g2[:, 0] > 0]
+    if len(g1) == 0 or len(g2) == 0:
+        return None
+    t0 = int(g1[:, 0].min())
+    p_last_draw, p_end = int(g1[:, 0].max()), int(g1[:, 2].max())
+    early = g2[g2[:, 0] < p_end]
+    late = g2[g2[:, 0] >= p_end]
+
+    def part(rs):
+        if len(rs) == 0:
+            return None
+        cyc = float(rs[:, 6].sum())
+        return {"units": int(len(rs)), "mma_thread_cycles_per_unit": round(cyc / len(rs)),
+                "waiting_for_operands_pct": round(100.0 * float(rs[:, 4].sum()) / cyc, 1),
+                "waiting_for_accumulator_pct": round(100.0 * float(rs[:, 7].sum()) / cyc, 1),
+                "loader_waiting_for_ring_slot_pct": round(100.0 * float(rs[:, 5].sum()) / cyc, 1),
+                "wall_us_per_unit": round(float((rs[:, 2] - rs[:, 0]).mean()) / 1e3, 1)}
+    return {"launch_form": "one persistent grid" if shard.single_grid else "one launch per GEMM and a wait kernel",
+            "producer_units": int(len(g1)), "consumer_units": int(len(g2)),
+            "producer_last_draw_us": round((p_last_draw - t0) / 1e3, 1), "producer_end_us": round((p_end - t0) / 1e3, 1),
+            "consumer_first_draw_us": round((int(g2[:, 0].min()) - t0) / 1e3, 1),
+            "consumer_end_us": round((int(g2[:, 2].max()) - t0) / 1e3, 1),
+            "consumer_units_drawn_before_producer_end": int(len(early)),
+            "consumer_units_finished_before_producer_end": int((g2[:, 2] < p_end).sum()),
+            "pairs_on_consumer_units_before_producer_end": int(len(np.unique(early[:, 3] & 0xffffffff))),
+            "producer": part(g1), "consumer_drawn_before_producer_end": part(early),
+            "consumer_drawn_after_producer_end": part(late)}
+
+
 def main():
     _watchdog(1500)
     ap = argparse.ArgumentParser()
@@ -252,6 +290,8 @@ def main():
                          "rank reduces 1/N of the matrix, so fewer SMs keep up as N grows)")
     ap.add_argument("--no-sweep", action="store_true", help="skip the per-batch table and the other workloads")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--timeline", action="store_true",
+                    help="add `overlap_timeline`: one traced run of the layer in both launch forms (per-tile timeline)")
     args = ap.parse_args()
     claim_stdout()
     args.warmup = max(args.warmup, 3) if args.impl == "cusync" else args.warmup
@@ -467,6 +507,14 @@ def main():
                 if not lb.status_ok():
                     multi["per_batch"][-1]["error"] = "bounded wait expired"
                 lb.destroy()
+
+    timeline = None
+    if args.timeline and world == 1 and args.batch > 256:
+        timeline = []
+        for sg in (2, 1):
+            ts = M.MLPShard("gpt3", args.batch, shard.x, shard.w1, shard.w2, None, policy=args.policy, single_grid=sg)
+            timeline.append(overlap_timeline(ts, ps, cs))
+            ts.destroy()
 
     # ---- per-kernel durations: each GEMM alone and both in a row, back to back between ONE pair of events ----
     base = layer.base
@@ -787,6 +835,7 @@ def main():
                             else "one launch per GEMM and a wait kernel"),
             "clocks": clocks,
             "multi_gpu": multi,
+            "overlap_timeline": timeline,
             "per_batch": table,
             "other_workloads": extras}
     if not args.no_cpu:

@@ -156,6 +156,7 @@ SIGNATURES = {
     "cusync_gemm_plan_set_trace": (_i, [_vp, _vp, _u32]),
     "cusync_gemm_plan_num_ctas": (_u32, [_vp]),
     "cusync_conv2d_tile_rows": (_i, [C.c_int32]),
+    "cusync_conv2d_tile_rows_hw": (_i, [C.c_int32, C.c_int32]),
     "cusync_conv2d_plan_create": (_i, [C.POINTER(_vp), C.POINTER(Conv2dDesc)]),
     "cusync_conv2d_plan_destroy": (_i, [_vp]),
     "cusync_conv2d_run": (_i, [_vp, _vp]),

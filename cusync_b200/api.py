@@ -298,7 +298,7 @@ class Conv2dProblemSize:
         self.n, self.h, self.w, self.c, self.k, self.r, self.s, self.pad, self.stride = n, h, w, c, k, r, s, pad, stride
 
     def tile_rows(self):
-        return L.lib().cusync_conv2d_tile_rows(self.w)
+        return L.lib().cusync_conv2d_tile_rows_hw(self.h, self.w)
 
     def grid(self):
         """Stage grid (N tiles, M tiles, 1) of the implicit GEMM."""

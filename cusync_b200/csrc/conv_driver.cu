@@ -50,8 +50,8 @@ int cusync_conv_chain_create(cusync_conv_chain_t** out, const cusync_conv_chain_
   if (d.n <= 0 || d.h <= 0 || d.w <= 0 || d.channels <= 0) return CUSYNC_ERROR_INVALID_ARGUMENT;
   for (int i = 0; i < d.num_convs; i++)
     if (!d.filters[i] || !d.activations[i] || !d.activations[i + 1]) return CUSYNC_ERROR_INVALID_ARGUMENT;
-  const int rows = cusync_conv2d_tile_rows(d.w);
-  if (rows == 0 || d.h % rows || d.channels % 64) return CUSYNC_ERROR_UNSUPPORTED;
+  const int rows = cusync_conv2d_tile_rows_hw(d.h, d.w);
+  if (rows == 0 || d.channels % 64) return CUSYNC_ERROR_UNSUPPORTED;
 
   cusync_conv_chain* c = new (std::nothrow) cusync_conv_chain();
   if (!c) return CUSYNC_ERROR_CUDA;

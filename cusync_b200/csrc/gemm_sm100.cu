@@ -793,6 +793,16 @@ int cusync_conv2d_tile_rows(int32_t w) {
   return kBlockM / w;     // whole image rows per 128-pixel M tile
 }
 
+int cusync_conv2d_tile_rows_hw(int32_t h, int32_t w) {
+  // the most whole image rows whose pixels fit the 128-row MMA AND that divide the image height, so that no tile
+  // straddles two images (14 x 14: 7 rows = 98 pixels; 7 x 7: the whole image, 49 pixels)
+  int rows = cusync_conv2d_tile_rows(w);
+  if (rows == 0 || h <= 0) return 0;
+  if (rows > h) rows = h;
+  while (h % rows) rows--;
+  return rows;
+}
+
 int cusync_conv2d_plan_create(cusync_conv2d_plan_t** out, const cusync_conv2d_desc_t* desc) {
   if (out == nullptr || desc == nullptr) return CUSYNC_ERROR_INVALID_ARGUMENT;
   *out = nullptr;
@@ -802,8 +812,8 @@ int cusync_conv2d_plan_create(cusync_conv2d_plan_t** out, const cusync_conv2d_de
   if (d.epilogue != CUSYNC_EPILOGUE_NONE && d.epilogue != CUSYNC_EPILOGUE_RELU) return CUSYNC_ERROR_INVALID_ARGUMENT;
   if (d.r != 3 || d.s != 3 || d.stride != 1 || d.pad != 1) return CUSYNC_ERROR_UNSUPPORTED;
   // channels in whole 64-element K chunks / 64-wide N tiles; an M tile is whole image rows
-  const int rows = cusync_conv2d_tile_rows(d.w);
-  if (d.c % 64 || d.k % 64 || rows == 0 || d.h % rows) return CUSYNC_ERROR_UNSUPPORTED;
+  const int rows = cusync_conv2d_tile_rows_hw(d.h, d.w);
+  if (d.c % 64 || d.k % 64 || rows == 0) return CUSYNC_ERROR_UNSUPPORTED;
   if (!aligned16(d.x) || !aligned16(d.filter) || !aligned16(d.y)) return CUSYNC_ERROR_UNSUPPORTED;
 
   cusync_gemm_plan* pl = new (std::nothrow) cusync_gemm_plan();

@@ -94,6 +94,27 @@ class MLPShard:
         if y is not None:
             self.y = y
 
+    def traced_run(self, producer_stream, consumer_stream):
+        """One run_cusync with the per-tile timeline switched on (cusync_mlp_set_trace).  Returns two int64 arrays
+        [records, 8], one per GEMM; the CTA-pair kernels write record 2 * ticket + rank: {globaltimer at the ticket
+        draw, at the end of the tile's MMAs, after its stores and post, SM id << 32 | block, cycles the MMA thread
+        waited for operands, cycles the loader waited for a free ring slot, cycles of the tile in the MMA thread,
+        of which waiting for a free accumulator} (the cycle counts in the leader's records only)."""
+        import torch
+        cap1 = 2 * ((self.batch + 255) // 256) * ((self.ffn + self.tile_n1 - 1) // self.tile_n1) * max(self.split_k1, 1)
+        cap2 = 2 * ((self.batch + 255) // 256) * ((self.hidden + self.tile_n2 - 1) // self.tile_n2) * max(self.split_k2, 1)
+        cap1, cap2 = max(cap1, 2 * self.ctas1), max(cap2, 2 * self.ctas2)
+        t1 = torch.zeros((cap1, 8), dtype=torch.int64, device=self.x.device)
+        t2 = torch.zeros((cap2, 8), dtype=torch.int64, device=self.x.device)
+        torch.cuda.synchronize()
+        L.check(L.lib().cusync_mlp_set_trace(self._h, t1.data_ptr(), cap1, t2.data_ptr(), cap2), "cusync_mlp_set_trace")
+        try:
+            self.run_cusync(producer_stream, consumer_stream)
+            torch.cuda.synchronize()
+        finally:
+            L.lib().cusync_mlp_set_trace(self._h, None, 0, None, 0)
+        return t1.cpu().numpy(), t2.cpu().numpy()
+
     def _stage_status(self, which):
         s = L.Status()
         L.lib().cusync_stage_read_status(L.lib().cusync_mlp_stage(self._h, which), C.byref(s))

@@ -31,9 +31,9 @@ struct Conv2dProblemSize {
 };
 
 // Output pixels per M tile (whole image rows) and the stage grid (N tiles, M tiles, 1) of the implicit GEMM.
-inline int conv2dTileM(const Conv2dProblemSize& p) { return cusync_conv2d_tile_rows(p.W) * p.W; }
+inline int conv2dTileM(const Conv2dProblemSize& p) { return cusync_conv2d_tile_rows_hw(p.H, p.W) * p.W; }
 inline dim3 conv2dGridShape(const Conv2dProblemSize& p) {
-  const int rows = cusync_conv2d_tile_rows(p.W);
+  const int rows = cusync_conv2d_tile_rows_hw(p.H, p.W);
   return dim3(p.K / 64, rows > 0 ? p.N * (p.H / rows) : 0, 1);
 }
 
@@ -65,8 +65,8 @@ class Conv2dFprop {
     if (a.epilogue.alpha != 1.0f || a.epilogue.beta != 0.0f) return Status::kErrorNotSupported;
     if (p.N <= 0 || p.H <= 0 || p.W <= 0 || p.C <= 0 || p.K <= 0) return Status::kErrorInvalidProblem;
     if (p.R != 3 || p.S != 3 || p.pad != 1 || p.stride != 1 || p.C % 64 || p.K % 64) return Status::kErrorNotSupported;
-    const int rows = cusync_conv2d_tile_rows(p.W);
-    if (rows == 0 || p.H % rows) return Status::kErrorNotSupported;
+    const int rows = cusync_conv2d_tile_rows_hw(p.H, p.W);
+    if (rows == 0) return Status::kErrorNotSupported;
     return Status::kSuccess;
   }
 

@@ -332,10 +332,10 @@ CUSYNC_API uint32_t cusync_gemm_plan_num_ctas(const cusync_gemm_plan_t* plan);
  * convolution of cutlass::conv::device::CuSyncImplicitGemmConvolution
  * (conv/device/cusyncimplicit_gemm_convolution.h:51-319) as the reference's resnet.cu / vgg.cu drive it.
  * Implicit GEMM [n*h*w, 9c] x [9c, k]: the K walk is channel-chunk outermost, filter tap innermost, as
- * Conv2DTileSync assumes (policies.h:160-210).  An M tile is cusync_conv2d_tile_rows(w) whole image rows
+ * Conv2DTileSync assumes (policies.h:160-210).  An M tile is cusync_conv2d_tile_rows_hw(h, w) whole image rows
  * (w <= 128), an N tile 64 output channels; the stage grid is (k / 64, n * h / rows, 1).  A consumer
  * convolution also waits for the producer tiles holding the image rows just above and below its own.
- * Supported: r = s = 3, stride 1, pad 1, c and k multiples of 64, h a multiple of the tile rows. */
+ * Supported: r = s = 3, stride 1, pad 1, c and k multiples of 64. */
 typedef struct cusync_conv2d_desc {
   int32_t n, h, w, c, k;
   int32_t r, s, stride, pad;
@@ -350,7 +350,11 @@ typedef struct cusync_conv2d_desc {
 
 typedef struct cusync_gemm_plan cusync_conv2d_plan_t;
 
-CUSYNC_API int cusync_conv2d_tile_rows(int32_t w);
+CUSYNC_API int cusync_conv2d_tile_rows(int32_t w);          /* floor(128 / w): the most image rows a tile can hold */
+/* Image rows per M tile for an h x w image: the largest divisor of h that is at most floor(128 / w), so that
+ * tiles never straddle two images (56 x 56: 2; 28 x 28: 4; 14 x 14: 7; 7 x 7: 7, the layer sizes of
+ * src/ml-bench/volta_conv2d/eval_resnet.py:12-17).  0 when w > 128. */
+CUSYNC_API int cusync_conv2d_tile_rows_hw(int32_t h, int32_t w);
 /* can_implement + initialize (conv/device/cusyncimplicit_gemm_convolution.h:100-265). */
 CUSYNC_API int cusync_conv2d_plan_create(cusync_conv2d_plan_t** out, const cusync_conv2d_desc_t* desc);
 CUSYNC_API int cusync_conv2d_plan_destroy(cusync_conv2d_plan_t* plan);

@@ -28,6 +28,9 @@ def _inputs(n, h, w, c, k, seed):
     (3, 28, 28, 64, 128),     # four image rows per tile, two N tiles
     (1, 8, 32, 128, 64),      # two channel chunks: 18 K blocks
     (2, 2, 128, 64, 64),      # one image row per tile
+    (2, 14, 14, 256, 256),    # 14 x 14 layer (eval_resnet.py:12-17): 7 of the 9 rows that would fit, so tiles end with the image
+    (3, 7, 7, 512, 128),      # 7 x 7 layer: one image (49 pixels) per tile, 72 K blocks
+    (1, 5, 56, 64, 64),       # odd height: one image row per tile although two would fit
 ])
 @pytest.mark.parametrize("relu", [False, True])
 def test_conv3x3_matches_oracle(n, h, w, c, k, relu):
@@ -79,7 +82,6 @@ def test_conv_refuses_unsupported_shapes():
     conv = cs.Conv2dFprop()
     assert conv.initialize(None, cs.Conv2dProblemSize(1, 56, 56, 64, 64, r=5, s=5), x, f, y) == L.ERROR_UNSUPPORTED
     assert conv.initialize(None, cs.Conv2dProblemSize(1, 56, 56, 48, 64), x, f, y) == L.ERROR_UNSUPPORTED
-    assert conv.initialize(None, cs.Conv2dProblemSize(1, 55, 56, 64, 64), x, f, y) == L.ERROR_UNSUPPORTED   # h % 2
     assert conv.initialize(None, cs.Conv2dProblemSize(1, 8, 200, 64, 64), x, f, y) == L.ERROR_UNSUPPORTED   # w > 128
 
 
@@ -130,6 +132,10 @@ def test_config5_conv_chain_with_conv2dtilesync(n, max_ctas):
     (8, 56, 56, 64, 2, 0),     # config 5, N = 8: wait kernel before the consumer
     (2, 28, 28, 64, 4, 6),     # vgg.cu-style chain of four, few blocks per stage, general-shape kernel rows
     (1, 8, 32, 128, 3, 0),     # two channel chunks: the implicit-GEMM path between the stages
+    (4, 28, 28, 128, 2, 0),    # the reference's other layer sizes (eval_resnet.py:12-17, 497-498): 128 channels, 28 x 28
+    (4, 14, 14, 256, 2, 0),    # 256 channels, 14 x 14
+    (8, 7, 7, 512, 2, 0),      # 512 channels, 7 x 7
+    (2, 14, 14, 256, 4, 0),    # vgg.cu-style chain of four at 256 channels (vgg.cu:104-119)
 ])
 def test_conv_chain_driver(n, h, w, c, convs, max_ctas):
     # cusync_conv_chain_*: the library's own driver for the chain (resnet.cu / vgg.cu flow)
@@ -137,7 +143,7 @@ def test_conv_chain_driver(n, h, w, c, convs, max_ctas):
     x = torch.randn((n, h, w, c), generator=g).half().cuda()
     filters = [(torch.randn((c, 3, 3, c), generator=g) * (2.0 / (9 * c)) ** 0.5).half().cuda() for _ in range(convs)]
     chain = cs.ConvChain(x, filters, relu=True, max_ctas=max_ctas)
-    blocks = n * (h // (128 // w)) * (c // 64)
+    blocks = n * (h // L.lib().cusync_conv2d_tile_rows_hw(h, w)) * (c // 64)
     sms = L.lib().cusync_b200_sm_count()
     shared = blocks * convs <= sms or (convs >= 3 and blocks <= 2 * sms)
     per_stage = min(blocks, max_ctas if max_ctas else (sms // convs if shared else sms))
