@@ -172,7 +172,7 @@ def workload_config(args, shard):
            "l2": "inputs larger than L2 (302 MB of weights per step vs 126 MB L2); no explicit flush",
            "all_reduce": (("sum of Y[B,12288] fp16 across ranks by this library's kernel beside the second GEMM "
                            "(%d blocks; the GEMMs use the other SMs)" % args.reduce_ctas
-                           if getattr(args, "reduce", "overlapped") == "overlapped" and args.batch >= 512
+                           if getattr(args, "reduce", "overlapped") == "overlapped" and args.batch >= 1024
                            else "NCCL sum of Y[B,12288] fp16 across ranks, after the layer")
                           if args.gpus > 1 else "none (1 GPU)")}
     if shard is not None:
@@ -242,11 +242,17 @@ def overlap_timeline(shard, ps, cs):
     import numpy as np
     for _ in range(3):
         shard.run_cusync(ps, cs)
-    t1, t2 = shard.traced_run(ps, cs)
-    g1, g2 = t1[0::2], t2[0::2]                  # the leader CTA's record of every work unit
-    g1, g2 = g1[g1[:, 0] > 0], g2[g2[:, 0] > 0]
-    if len(g1) == 0 or len(g2) == 0:
-        return None
+    best = None
+    for _ in range(3):                           # the quickest of three traced runs (the clock drifts between runs)
+        t1, t2 = shard.traced_run(ps, cs)
+        a, b = t1[0::2], t2[0::2]                # the leader CTA's record of every work unit
+        a, b = a[a[:, 0] > 0], b[b[:, 0] > 0]
+        if len(a) == 0 or len(b) == 0:
+            return None
+        span = int(b[:, 2].max()) - int(a[:, 0].min())
+        if best is None or span < best[0]:
+            best = (span, a, b)
+    g1, g2 = best[1], best[2]
     t0 = int(g1[:, 0].min())
     p_last_draw, p_end = int(g1[:, 0].max()), int(g1[:, 2].max())
     early = g2[g2[:, 0] < p_end]
@@ -286,10 +292,12 @@ def main():
                     help="multi-GPU: the all-reduce of Y as this library's kernel beside the second GEMM (default), "
                          "or NCCL's all-reduce after the layer")
     ap.add_argument("--reduce-ctas", type=int, default=0,
-                    help="blocks of the overlapped all-reduce kernel (0 = choose: 8 at 2 ranks, 4 from 4 ranks on; a "
-                         "rank reduces 1/N of the matrix, so fewer SMs keep up as N grows)")
+                    help="blocks of the overlapped all-reduce kernel (0 = choose: 4, which leaves the GEMMs 72 SM pairs: "
+                         "the 576 pair tiles of the B = 2048 layer are then exactly eight rounds)")
     ap.add_argument("--no-sweep", action="store_true", help="skip the per-batch table and the other workloads")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--group-rows1", type=int, default=0, help="tile order of the first GEMM (0 = the library's table)")
+    ap.add_argument("--group-rows2", type=int, default=0, help="tile order of the second GEMM (0 = the library's table)")
     ap.add_argument("--timeline", action="store_true",
                     help="add `overlap_timeline`: one traced run of the layer in both launch forms (per-tile timeline)")
     args = ap.parse_args()
@@ -327,10 +335,12 @@ def main():
     rs = torch.cuda.Stream(priority=0)    # multi-GPU: the all-reduce kernel that runs beside the GEMMs
     overlap_reduce = world > 1 and args.reduce == "overlapped"
     if args.reduce_ctas <= 0:
-        args.reduce_ctas = 8 if world <= 2 else 4
-    # Below four row tiles the all-reduce cannot start before the second GEMM is all but done: nothing to overlap,
-    # and NCCL's all-reduce after the layer is the better form.
-    OVERLAP_MIN_BATCH = 512
+        args.reduce_ctas = 4
+    # The all-reduce kernel hides behind the second GEMM where that GEMM runs longer than the exchange takes on a
+    # few SMs: the GPT-3 shard from eight row tiles on (measured on 2 GPUs: +4.6 % at B = 1024, +10 % at 2048, -1 %
+    # at 512).  Elsewhere (small batches; the LLaMA shard, whose second GEMM is short) NCCL's all-reduce after
+    # the layer is the better form.
+    OVERLAP_MIN_BATCH = 1024
 
     class Layer:
         """One tensor-parallel layer of `model` at `batch`: the synchronised chain with its all-reduce (this
@@ -340,14 +350,15 @@ def main():
             x, w1, w2, v = M.make_inputs(model, batch, dev, seed=seed)
             self.model, self.batch = model, batch
             self.reducer = None
-            if overlap_reduce and batch >= OVERLAP_MIN_BATCH:
+            if overlap_reduce and batch >= OVERLAP_MIN_BATCH and model == "gpt3":
                 self.reducer = tp.RowAllReduce(group, batch, x.shape[1], dev, num_ctas=args.reduce_ctas)
                 self.shard = M.MLPShard(model, batch, x, w1, w2, v, policy=policy, post_rows=True,
                                         max_ctas=sms - self.reducer.num_ctas, y=self.reducer.y)
                 # the stream-ordered arm keeps the whole device and its own output
                 self.base = M.MLPShard(model, batch, x, w1, w2, v, policy=policy, single_grid=1)
             else:
-                self.shard = M.MLPShard(model, batch, x, w1, w2, v, policy=policy)
+                self.shard = M.MLPShard(model, batch, x, w1, w2, v, policy=policy, group_rows1=args.group_rows1,
+                                        group_rows2=args.group_rows2)
                 self.base = self.shard
 
         def cusync_step(self):
@@ -734,6 +745,22 @@ def main():
             chain.destroy()
         extras["resnet_conv3x3_chain_conv2dtilesync"] = rows
 
+        # the reference's other layer sizes (eval_resnet.py:12-17, 497-498): 128 / 256 / 512 channels on
+        # 28x28 / 14x14 / 7x7 images, two convolutions, general implicit-GEMM kernel
+        rows = []
+        for c, hw_ in ((128, 28), (256, 14), (512, 7)):
+            for n in (8, 32):
+                g = torch.Generator(device=dev).manual_seed(c + n)
+                xin = torch.randn((n, hw_, hw_, c), generator=g, device=dev).half()
+                fs = [(torch.randn((c, 3, 3, c), generator=g, device=dev) * (2.0 / (9 * c)) ** 0.5).half() for _ in range(2)]
+                chain = lib_.ConvChain(xin, fs, relu=True)
+                r = ab(lambda chain=chain: chain.run_cusync([ps, cs]), lambda chain=chain: chain.run_stream_ordered(cs))
+                r.update({"channels": c, "image": hw_, "images": n, "wait_kernel": chain.uses_wait_kernels,
+                          "tflops": round(2 * 2.0 * n * hw_ * hw_ * c * 9 * c / (r["cusync_us"] * 1e-6) / 1e12, 1)})
+                rows.append(r)
+                chain.destroy()
+        extras["resnet_conv3x3_chain_other_layers"] = rows
+
         # vgg.cu-style chain of four 64-channel convolutions, one stream per convolution
         g = torch.Generator(device=dev).manual_seed(44)
         xin = torch.randn((8, 56, 56, 64), generator=g, device=dev).half()
@@ -767,6 +794,25 @@ def main():
             r.update({"batch": b, "context": seq, "config": blk.config})
             rows.append(r); blk.destroy()
         extras["gpt3_attention_block"] = rows
+        # the attention block in the prompt phase, as the reference runs it (attention.cu:272-276, seqlen = 0):
+        # XQKV = X Wqkv; S = Q K^T; O = S V; Y = O Wo, four GEMMs on four streams.  X ~ N(0, 0.1^2) keeps O in fp16.
+        from cusync_b200.attention import PromptAttentionBlock
+        s4 = torch.cuda.Stream()
+        rows = []
+        for b in (512, 1024, 2048):
+            g = torch.Generator(device=dev).manual_seed(9)
+            xin = (torch.randn((b, 12288), generator=g, device=dev) * 0.1).half()
+            wqkv = (torch.randn((12288, 4608), generator=g, device=dev) * 0.02).half()
+            wo = (torch.randn((1536, 12288), generator=g, device=dev) * 0.02).half()
+            blk = PromptAttentionBlock(xin, wqkv, wo, 12)
+
+            def c_step(blk=blk):
+                blk.run((ps, s3, s4, cs))
+            r = ab(c_step, lambda blk=blk: blk.run_stream_ordered(cs))
+            r.update({"batch": b, "tflops": round(blk.flops() / (r["cusync_us"] * 1e-6) / 1e12, 1),
+                      "ok": blk.status_codes() == (0, 0, 0, 0)})
+            rows.append(r); blk.destroy()
+        extras["gpt3_attention_prompt_phase"] = rows
     if not args.no_sweep and world > 1:
         # the other sharded workloads at N GPUs: LLaMA MLP shard (config 3) with the overlapped all-reduce, and the
         # attention block (config 4: 12 of 96 heads per rank) with NCCL's all-reduce of its output after the chain

@@ -62,7 +62,9 @@ class GemmDesc(C.Structure):
                 ("b2", C.c_void_p),
                 ("d", C.c_void_p), ("ldd", C.c_int64),
                 ("b_layout", C.c_int32), ("epilogue", C.c_int32), ("tile_n", C.c_int32), ("max_ctas", C.c_int32),
-                ("split_k", C.c_int32), ("cta_pair", C.c_int32), ("tail_split", C.c_int32), ("stage", C.c_void_p)]
+                ("split_k", C.c_int32), ("cta_pair", C.c_int32), ("tail_split", C.c_int32), ("stage", C.c_void_p),
+                ("b_stage", C.c_void_p), ("b_sem_first", C.c_uint32), ("b_sem_stride", C.c_uint32),
+                ("b_sem_value", C.c_uint32)]
 
 
 class Conv2dDesc(C.Structure):
@@ -89,6 +91,13 @@ class AttnBlockDesc(C.Structure):
                 ("out_features", C.c_int32), ("model_hidden", C.c_int32), ("kv_splits", C.c_int32),
                 ("x", C.c_void_p), ("w_qkv", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p),
                 ("w_o", C.c_void_p), ("qkv", C.c_void_p), ("attn_out", C.c_void_p), ("y", C.c_void_p)]
+
+
+class AttnPromptDesc(C.Structure):
+    _fields_ = [("batch", C.c_int32), ("hidden", C.c_int32), ("heads", C.c_int32), ("out_features", C.c_int32),
+                ("model_hidden", C.c_int32),
+                ("x", C.c_void_p), ("w_qkv", C.c_void_p), ("w_o", C.c_void_p),
+                ("qkv", C.c_void_p), ("s", C.c_void_p), ("o", C.c_void_p), ("y", C.c_void_p)]
 
 
 class MlpDesc(C.Structure):
@@ -179,6 +188,11 @@ SIGNATURES = {
     "cusync_attn_block_run_cusync": (_i, [_vp, C.POINTER(_vp)]),
     "cusync_attn_block_stage": (_vp, [_vp, _i]),
     "cusync_attn_block_config": (_i, [_vp, C.POINTER(C.c_int32)]),
+    "cusync_attn_prompt_create": (_i, [C.POINTER(_vp), C.POINTER(AttnPromptDesc)]),
+    "cusync_attn_prompt_destroy": (_i, [_vp]),
+    "cusync_attn_prompt_run_stream_ordered": (_i, [_vp, _vp]),
+    "cusync_attn_prompt_run_cusync": (_i, [_vp, C.POINTER(_vp)]),
+    "cusync_attn_prompt_stage": (_vp, [_vp, _i]),
     "cusync_mlp_create": (_i, [C.POINTER(_vp), C.POINTER(MlpDesc)]),
     "cusync_mlp_destroy": (_i, [_vp]),
     "cusync_mlp_run_stream_ordered": (_i, [_vp, _vp]),

@@ -101,3 +101,46 @@ class AttentionBlock:
         if self._h:
             L.lib().cusync_attn_block_destroy(self._h)
             self._h = C.c_void_p()
+
+
+class PromptAttentionBlock:
+    """The attention block in the prompt phase, as the reference runs it (attention.cu:272-276 with seqlen = 0):
+    XQKV = X Wqkv; S = Q K^T; O = S V; Y = O Wo, four dependent GEMMs without softmax or heads, each on its own
+    stream behind a wait kernel (cusync_attn_prompt_*).  x[B, H], w_qkv[H, 3 * heads * 128], w_o[heads * 128, out]."""
+
+    def __init__(self, x, w_qkv, w_o, heads, model_hidden=12288):
+        import torch
+        self.batch, self.hidden, self.heads = x.shape[0], x.shape[1], heads
+        hd = heads * HEAD_DIM
+        assert w_qkv.shape == (self.hidden, 3 * hd) and w_o.shape[0] == hd
+        dev = x.device
+        self.qkv = torch.empty((self.batch, 3 * hd), device=dev, dtype=torch.half)
+        self.s = torch.empty((self.batch, self.batch), device=dev, dtype=torch.half)
+        self.o = torch.empty((self.batch, hd), device=dev, dtype=torch.half)
+        self.y = torch.empty((self.batch, w_o.shape[1]), device=dev, dtype=torch.half)
+        self.x, self.w_qkv, self.w_o = x, w_qkv, w_o
+        d = L.AttnPromptDesc(self.batch, self.hidden, heads, w_o.shape[1], model_hidden, x.data_ptr(), w_qkv.data_ptr(),
+                             w_o.data_ptr(), self.qkv.data_ptr(), self.s.data_ptr(), self.o.data_ptr(), self.y.data_ptr())
+        self._h = C.c_void_p()
+        L.check(L.lib().cusync_attn_prompt_create(C.byref(self._h), C.byref(d)), "cusync_attn_prompt_create")
+        self.stages = [_StageRef(L.lib().cusync_attn_prompt_stage(self._h, i)) for i in range(4)]
+
+    def flops(self):
+        hd = self.heads * HEAD_DIM
+        return 2.0 * self.batch * (self.hidden * 3 * hd + 2 * self.batch * hd + hd * self.y.shape[1])
+
+    def run(self, streams):
+        """Four streams, a wait kernel before each dependent GEMM (attention.cu:792-811)."""
+        arr = (C.c_void_p * 4)(*[_stream_ptr(s) for s in streams])
+        L.check(L.lib().cusync_attn_prompt_run_cusync(self._h, C.cast(arr, C.POINTER(C.c_void_p))), "run_cusync")
+
+    def run_stream_ordered(self, stream):
+        L.check(L.lib().cusync_attn_prompt_run_stream_ordered(self._h, _stream_ptr(stream)), "run_stream_ordered")
+
+    def status_codes(self):
+        return tuple(st.status().code for st in self.stages)
+
+    def destroy(self):
+        if self._h:
+            L.lib().cusync_attn_prompt_destroy(self._h)
+            self._h = C.c_void_p()

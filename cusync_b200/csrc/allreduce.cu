@@ -26,8 +26,9 @@
 namespace {
 
 constexpr int kMaxWorld = 8;
-constexpr int kThreads = 1024;                    // block 0: 31 worker warps + the watcher warp; other blocks: 32 worker warps
-constexpr int kWatcherWarp = kThreads / 32 - 1;
+constexpr int kWorkers = 480;                     // worker threads per block
+constexpr int kThreads = kWorkers + 32;           // ... plus one more warp: the watcher (it has work in block 0 only)
+constexpr int kWatcherWarp = kWorkers / 32;
 constexpr int kFlagHeader = 8;                    // [0] done counter, [1..7] spare; then one ready counter per row tile
 
 struct ArParams {
@@ -70,6 +71,22 @@ __device__ __forceinline__ void multimem_st_f16x8(void* mc, uint4 v) {
                "r"(v.z), "r"(v.w)
                : "memory");
 }
+// The same two, executed only where `on` holds (a predicated instruction, not a branch around it).
+__device__ __forceinline__ void multimem_ld_reduce_f16x8_if(bool on, const void* mc, uint4& v) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %5, 0;\n\t"
+      "@p multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];\n\t}"
+      : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w)
+      : "l"(mc), "r"(on ? 1u : 0u)
+      : "memory");
+}
+__device__ __forceinline__ void multimem_st_f16x8_if(bool on, void* mc, const uint4& v) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %5, 0;\n\t"
+      "@p multimem.st.relaxed.sys.global.v4.f16x2 [%0], {%1, %2, %3, %4};\n\t}"
+      ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "r"(on ? 1u : 0u)
+      : "memory");
+}
 __device__ __forceinline__ uint4 ld_relaxed_sys_v4(const void* p) {
   uint4 v;
   asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
@@ -108,6 +125,45 @@ __device__ __forceinline__ void add8(float (&acc)[8], uint4 v) {
   }
 }
 
+// In-switch sum of `vecs` 16-byte pieces starting at the multicast address `base`, written back to every rank.
+// Rounds of one chunk of kUnroll * kWorkers pieces per block; what is left after the last full round is shared
+// out equally among the blocks and done in one more pass.  Inside a chunk a thread's pieces are kWorkers pieces
+// apart, a compile-time distance, so that one base register serves all of its kUnroll loads in flight.
+constexpr int kUnroll = 24;
+constexpr uint32_t kChunkVecs = kUnroll * kWorkers;
+__device__ __forceinline__ void multicast_reduce_span(__half* base, uint32_t vecs, uint32_t block, uint32_t blocks,
+                                                      uint32_t tid) {
+  const uint32_t full_rounds = vecs / (blocks * kChunkVecs);
+  for (uint32_t r = 0; r < full_rounds; r++) {
+    __half* const p0 = base + (static_cast<size_t>(r * blocks + block) * kChunkVecs + tid) * 8;
+    uint4 v[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; u++) v[u] = multimem_ld_reduce_f16x8(p0 + static_cast<size_t>(u) * kWorkers * 8);
+#pragma unroll
+    for (int u = 0; u < kUnroll; u++) multimem_st_f16x8(p0 + static_cast<size_t>(u) * kWorkers * 8, v[u]);
+  }
+  const uint32_t rest0 = full_rounds * blocks * kChunkVecs;
+  if (rest0 == vecs) return;
+  // the rest (fewer than `blocks` chunks): an equal share per block, at most one chunk, whole groups of kWorkers
+  const uint32_t share = ((vecs - rest0 + blocks - 1) / blocks + kWorkers - 1) / kWorkers * kWorkers;
+  const uint32_t begin = rest0 + block * share;
+  const uint32_t end = begin + share < vecs ? begin + share : vecs;
+  if (begin >= end) return;
+  __half* const p0 = base + (static_cast<size_t>(begin) + tid) * 8;
+  const uint32_t mine = begin + tid < end ? (end - begin - tid + kWorkers - 1) / kWorkers : 0u;   // this thread's pieces
+  // (predicated instructions in straight-line code: loads and stores keep fixed registers, which branches
+  // around the individual pieces did not)
+  uint4 v[kUnroll];
+#pragma unroll
+  for (int u = 0; u < kUnroll; u++) {
+    v[u] = make_uint4(0u, 0u, 0u, 0u);
+    multimem_ld_reduce_f16x8_if(static_cast<uint32_t>(u) < mine, p0 + static_cast<size_t>(u) * kWorkers * 8, v[u]);
+  }
+#pragma unroll
+  for (int u = 0; u < kUnroll; u++)
+    multimem_st_f16x8_if(static_cast<uint32_t>(u) < mine, p0 + static_cast<size_t>(u) * kWorkers * 8, v[u]);
+}
+
 template <bool kMulticast>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) cusync_allreduce_rows_kernel(const ArParams p) {
   __shared__ volatile uint32_t s_abort;
@@ -135,13 +191,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) cusync_
     }
     return;
   }
+  if (warp == kWatcherWarp) return;      // the extra warp of the other blocks has nothing to do
 
   // ---- workers ---------------------------------------------------------------------------------------
   const int vec_per_row = p.cols / 8;
-  const uint32_t workers0 = kThreads - 32;                      // block 0 gives one warp to the watcher
-  const uint32_t block_workers = blockIdx.x == 0 ? workers0 : static_cast<uint32_t>(kThreads);
-  const uint32_t worker = blockIdx.x == 0 ? threadIdx.x : workers0 + (blockIdx.x - 1) * kThreads + threadIdx.x;
-  const uint32_t num_workers = workers0 + (gridDim.x - 1) * kThreads;
+  const uint32_t block_workers = kWorkers;
+  const uint32_t worker = blockIdx.x * kWorkers + threadIdx.x;
+  const uint32_t num_workers = gridDim.x * kWorkers;
   const bool contiguous = p.ld == p.cols;
   bool ok = true;
   for (int t = 0; t < p.num_tiles && ok; t++) {
@@ -167,26 +223,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) cusync_
     const uint32_t vecs = static_cast<uint32_t>(r_end - r_begin) * static_cast<uint32_t>(vec_per_row);
     if (kMulticast) {
       // Latency-bound: a multimem.ld_reduce is a round trip through the switch of a few microseconds, so every
-      // thread keeps eight of them in flight (128 KB per block) before it turns to the stores.
-      constexpr int kUnroll = 8;
+      // thread of the 512 keeps 24 of them in flight (192 KB per block: most of the register file) before it
+      // turns to the stores.  A matrix with padded rows is walked row by row.
       __half* const slice = p.mc_buf + static_cast<size_t>(r_begin) * p.ld;
-      for (uint32_t base = worker; base < vecs; base += num_workers * kUnroll) {
-        uint4 v[kUnroll];
-#pragma unroll
-        for (int u = 0; u < kUnroll; u++) {
-          const uint32_t i = base + u * num_workers;
-          if (i < vecs)
-            v[u] = multimem_ld_reduce_f16x8(contiguous ? slice + static_cast<size_t>(i) * 8
-                                                        : slice + static_cast<size_t>(i / vec_per_row) * p.ld + (i % vec_per_row) * 8);
-        }
-#pragma unroll
-        for (int u = 0; u < kUnroll; u++) {
-          const uint32_t i = base + u * num_workers;
-          if (i < vecs)
-            multimem_st_f16x8(contiguous ? slice + static_cast<size_t>(i) * 8
-                                         : slice + static_cast<size_t>(i / vec_per_row) * p.ld + (i % vec_per_row) * 8, v[u]);
-        }
-      }
+      const int spans = contiguous ? 1 : r_end - r_begin;
+      const uint32_t span_vecs = contiguous ? vecs : static_cast<uint32_t>(vec_per_row);
+      for (int r = 0; r < spans; r++)
+        multicast_reduce_span(slice + static_cast<size_t>(r) * p.ld, span_vecs, blockIdx.x, gridDim.x, threadIdx.x);
     } else {
       for (uint32_t i = worker; i < vecs; i += num_workers) {
         const size_t off = static_cast<size_t>(r_begin + i / vec_per_row) * p.ld + static_cast<size_t>(i % vec_per_row) * 8;
@@ -264,7 +307,7 @@ int cusync_allreduce_plan_create(cusync_allreduce_plan_t** out, const cusync_all
   if ((p.mc_buf == nullptr) != (p.mc_flags == nullptr)) { delete pl; return CUSYNC_ERROR_INVALID_ARGUMENT; }
   p.timeout_ns = d.timeout_ns ? d.timeout_ns : cusync::kDefaultSpinTimeoutNs;
   p.epoch = 1;
-  pl->num_ctas = d.num_ctas ? d.num_ctas : 8;
+  pl->num_ctas = d.num_ctas ? d.num_ctas : 4;
   if (cudaMalloc(&pl->status, 8 * sizeof(uint32_t)) != cudaSuccess || cudaMemset(pl->status, 0, 8 * sizeof(uint32_t)) != cudaSuccess) {
     (void)cudaGetLastError();
     cudaFree(pl->status);

@@ -5,6 +5,8 @@
 // stage on its own stream, a wait kernel before every dependent stage, incrementIter at the end).  Unlike the
 // reference's chain, the middle stage is a real attention with heads and an fp32 softmax over a K/V cache.
 // Host-only code over the library's own C ABI.
+#include <cuda_fp16.h>
+
 #include <cstring>
 #include <new>
 
@@ -148,6 +150,158 @@ int cusync_attn_block_run_cusync(cusync_attn_block_t* b, const cusync_stream_t* 
   if (!b->order.end(streams[2])) { (void)cudaGetLastError(); rc = CUSYNC_ERROR_CUDA; }
   for (int i = 0; i < 3; i++) cusync_stage_increment_iter(b->stages[i]);
   return rc;
+}
+
+// ---- prompt phase: the reference's four-GEMM chain ---------------------------------------------------------
+// attention.cu:272-276 for seqlen = 0 and a batch of 512 to 2048 prompt tokens: XQKV = X Wqkv; S = Q K^T;
+// O = S V; Y = O Wo, with Q, K, V the three thirds of XQKV's columns and no softmax (the reference has none,
+// attention.cu:445-509).  Four stages on four streams, a wait kernel before each dependent one (:792-811).
+// What the reference's policies leave open is closed here: S = Q K^T also reads K rows that OTHER row panels of
+// the first GEMM produce, and O = S V reads all of V; both B operands are waited for through the first stage's
+// ConsecutiveSync semaphores (cusync_gemm_desc_t.b_stage).
+struct cusync_attn_prompt {
+  cusync_attn_prompt_desc_t desc;
+  cusync_stage_t* stages[4];
+  cusync_stage_t* plain_stages[4];
+  cusync_gemm_plan_t* gemm[2][4];     // [0] synchronised, [1] stream-ordered
+  RunOrder order;
+};
+
+namespace {
+void destroy_prompt(cusync_attn_prompt* b) {
+  for (int arm = 0; arm < 2; arm++)
+    for (int i = 0; i < 4; i++)
+      if (b->gemm[arm][i]) cusync_gemm_plan_destroy(b->gemm[arm][i]);
+  for (int i = 0; i < 4; i++) {
+    if (b->stages[i]) cusync_stage_destroy(b->stages[i]);
+    if (b->plain_stages[i]) cusync_stage_destroy(b->plain_stages[i]);
+  }
+  b->order.destroy();
+  delete b;
+}
+}  // namespace
+
+int cusync_attn_prompt_create(cusync_attn_prompt_t** out, const cusync_attn_prompt_desc_t* desc) {
+  if (!out || !desc) return CUSYNC_ERROR_INVALID_ARGUMENT;
+  *out = nullptr;
+  const cusync_attn_prompt_desc_t& d = *desc;
+  if (d.batch <= 0 || d.hidden <= 0 || d.heads <= 0 || d.out_features <= 0 || d.model_hidden <= 0) return CUSYNC_ERROR_INVALID_ARGUMENT;
+  if (!d.x || !d.w_qkv || !d.w_o || !d.qkv || !d.s || !d.o || !d.y) return CUSYNC_ERROR_INVALID_ARGUMENT;
+  const int hd = d.heads * 128;               // columns of each of Q, K, V in this shard
+  constexpr int kTile = 256;
+  // the CTA-pair kernels (256-column tiles) carry the chain: more than two row tiles, thirds in whole tiles,
+  // and the ConsecutiveSync group (H / 8 / tile) equal to the tiles of one third
+  if (d.batch <= 256 || d.batch % 64 || hd % kTile || d.model_hidden / 8 != hd) return CUSYNC_ERROR_UNSUPPORTED;
+
+  cusync_attn_prompt* b = new (std::nothrow) cusync_attn_prompt();
+  if (!b) return CUSYNC_ERROR_CUDA;
+  std::memset(b, 0, sizeof(*b));
+  b->desc = d;
+  const uint32_t tiles_m = static_cast<uint32_t>((d.batch + 127) / 128);
+  const uint32_t third_tiles = static_cast<uint32_t>(hd / kTile);
+  const uint32_t s_tiles = static_cast<uint32_t>((d.batch + kTile - 1) / kTile);
+  const cusync_dim3_t grids[4] = {{3 * third_tiles, tiles_m, 1}, {s_tiles, tiles_m, 1}, {third_tiles, tiles_m, 1},
+                                  {static_cast<uint32_t>((d.out_features + kTile - 1) / kTile), tiles_m, 1}};
+  const cusync_dim3_t ts = {1, 1, 1};
+  cusync_policy_t none, thirds, rows_s, rows_o;
+  std::memset(&none, 0, sizeof(none));
+  none.tile_m = none.tile_n = 1;
+  // ConsecutiveSync<TransposeXYOrder, H, 128, 256> (attention.cu:51-70, 105-110)
+  std::memset(&thirds, 0, sizeof(thirds));
+  thirds.kind = CUSYNC_POLICY_CONSECUTIVETILESYNC; thirds.order = CUSYNC_ORDER_TRANSPOSE_XY;
+  thirds.tile_m = 128; thirds.tile_n = kTile; thirds.p0 = static_cast<uint32_t>(d.model_hidden);
+  // RowSync<128>: a row panel of S / of O is complete when all of its column tiles are (Sync2 / Sync1, :113-117)
+  std::memset(&rows_s, 0, sizeof(rows_s));
+  rows_s.kind = CUSYNC_POLICY_ROWSYNC; rows_s.order = CUSYNC_ORDER_TRANSPOSE_XY;
+  rows_s.tile_m = 128; rows_s.tile_n = kTile; rows_s.wait_value = s_tiles; rows_s.post_value = 1;
+  rows_o = rows_s;
+  rows_o.wait_value = third_tiles;
+  const cusync_policy_t* in[4] = {&none, &thirds, &rows_s, &rows_o};
+  const cusync_policy_t* outp[4] = {&thirds, &rows_s, &rows_o, &none};
+  int rc = CUSYNC_SUCCESS;
+  for (int i = 0; i < 4 && rc == CUSYNC_SUCCESS; i++) {
+    rc = cusync_stage_create(&b->stages[i], grids[i], ts, CUSYNC_ORDER_TRANSPOSE_XY, in[i], outp[i], CUSYNC_OPT_NONE);
+    if (rc == CUSYNC_SUCCESS)
+      rc = cusync_stage_create(&b->plain_stages[i], grids[i], ts, CUSYNC_ORDER_TRANSPOSE_XY, &none, &none, CUSYNC_OPT_NONE);
+  }
+  for (int i = 0; i < 3 && rc == CUSYNC_SUCCESS; i++) rc = cusync_stage_link(b->stages[i], b->stages[i + 1]);
+
+  // Semaphore of (row block r, third t) of the first stage: first + r * stride
+  const uint32_t gx0 = grids[0].x, gy0 = grids[0].y;
+  const uint32_t k_first = cusync::eval::tileIndex(thirds, 0, static_cast<uint32_t>(hd), gx0, gy0);
+  const uint32_t v_first = cusync::eval::tileIndex(thirds, 0, static_cast<uint32_t>(2 * hd), gx0, gy0);
+  const uint32_t stride = tiles_m > 1 ? cusync::eval::tileIndex(thirds, 128, static_cast<uint32_t>(hd), gx0, gy0) - k_first : 1;
+  const __half* qkv = static_cast<const __half*>(d.qkv);
+
+  for (int arm = 0; arm < 2 && rc == CUSYNC_SUCCESS; arm++) {
+    cusync_stage_t* const* st = arm == 0 ? b->stages : b->plain_stages;
+    cusync_gemm_desc_t g;
+    // XQKV = X Wqkv
+    std::memset(&g, 0, sizeof(g));
+    g.m = d.batch; g.n = 3 * hd; g.k = d.hidden;
+    g.a = d.x; g.lda = d.hidden; g.b = d.w_qkv; g.ldb = 3 * hd; g.d = d.qkv; g.ldd = 3 * hd;
+    g.b_layout = CUSYNC_B_ROW_MAJOR_KN; g.tile_n = kTile; g.split_k = 1; g.cta_pair = 2; g.stage = st[0];
+    rc = cusync_gemm_plan_create(&b->gemm[arm][0], &g);
+    if (rc != CUSYNC_SUCCESS) break;
+    // S = Q K^T: A = the Q third of XQKV, B = the K third read as an [n, k] matrix
+    std::memset(&g, 0, sizeof(g));
+    g.m = d.batch; g.n = d.batch; g.k = hd;
+    g.a = qkv; g.lda = 3 * hd; g.b = qkv + hd; g.ldb = 3 * hd; g.d = d.s; g.ldd = d.batch;
+    g.b_layout = CUSYNC_B_ROW_MAJOR_NK; g.tile_n = kTile; g.split_k = 1; g.cta_pair = 2; g.stage = st[1];
+    if (arm == 0) { g.b_stage = b->stages[0]; g.b_sem_first = k_first; g.b_sem_stride = stride; g.b_sem_value = third_tiles; }
+    rc = cusync_gemm_plan_create(&b->gemm[arm][1], &g);
+    if (rc != CUSYNC_SUCCESS) break;
+    // O = S V: B = the V third of XQKV, a [k, n] matrix whose k runs over the tokens
+    std::memset(&g, 0, sizeof(g));
+    g.m = d.batch; g.n = hd; g.k = d.batch;
+    g.a = d.s; g.lda = d.batch; g.b = qkv + 2 * hd; g.ldb = 3 * hd; g.d = d.o; g.ldd = hd;
+    g.b_layout = CUSYNC_B_ROW_MAJOR_KN; g.tile_n = kTile; g.split_k = 1; g.cta_pair = 2; g.stage = st[2];
+    if (arm == 0) { g.b_stage = b->stages[0]; g.b_sem_first = v_first; g.b_sem_stride = stride; g.b_sem_value = third_tiles; }
+    rc = cusync_gemm_plan_create(&b->gemm[arm][2], &g);
+    if (rc != CUSYNC_SUCCESS) break;
+    // Y = O Wo
+    std::memset(&g, 0, sizeof(g));
+    g.m = d.batch; g.n = d.out_features; g.k = hd;
+    g.a = d.o; g.lda = hd; g.b = d.w_o; g.ldb = d.out_features; g.d = d.y; g.ldd = d.out_features;
+    g.b_layout = CUSYNC_B_ROW_MAJOR_KN; g.tile_n = kTile; g.split_k = 1; g.cta_pair = 2; g.stage = st[3];
+    rc = cusync_gemm_plan_create(&b->gemm[arm][3], &g);
+  }
+  if (rc == CUSYNC_SUCCESS && !b->order.create()) { (void)cudaGetLastError(); rc = CUSYNC_ERROR_CUDA; }
+  if (rc != CUSYNC_SUCCESS) { destroy_prompt(b); return rc; }
+  *out = b;
+  return CUSYNC_SUCCESS;
+}
+
+int cusync_attn_prompt_destroy(cusync_attn_prompt_t* b) {
+  if (!b) return CUSYNC_ERROR_NOT_INITIALIZED;
+  destroy_prompt(b);
+  return CUSYNC_SUCCESS;
+}
+
+int cusync_attn_prompt_run_stream_ordered(cusync_attn_prompt_t* b, cusync_stream_t stream) {
+  if (!b) return CUSYNC_ERROR_NOT_INITIALIZED;
+  int rc = CUSYNC_SUCCESS;
+  for (int i = 0; i < 4 && rc == CUSYNC_SUCCESS; i++) rc = cusync_gemm_run(b->gemm[1][i], stream);
+  return rc;
+}
+
+int cusync_attn_prompt_run_cusync(cusync_attn_prompt_t* b, const cusync_stream_t* streams) {
+  if (!b || !streams) return CUSYNC_ERROR_NOT_INITIALIZED;
+  if (!b->order.begin(streams[0])) { (void)cudaGetLastError(); return CUSYNC_ERROR_CUDA; }
+  int rc = CUSYNC_SUCCESS;
+  for (int i = 0; i < 4 && rc == CUSYNC_SUCCESS; i++) {
+    if (i > 0) rc = cusync_stage_invoke_wait_kernel(b->stages[i - 1], streams[i]);
+    if (rc == CUSYNC_SUCCESS) rc = cusync_gemm_run(b->gemm[0][i], streams[i]);
+  }
+  if (rc != CUSYNC_SUCCESS) return rc;
+  if (!b->order.end(streams[3])) { (void)cudaGetLastError(); rc = CUSYNC_ERROR_CUDA; }
+  for (int i = 0; i < 4; i++) cusync_stage_increment_iter(b->stages[i]);
+  return rc;
+}
+
+cusync_stage_t* cusync_attn_prompt_stage(cusync_attn_prompt_t* b, int which) {
+  if (!b || which < 0 || which > 3) return nullptr;
+  return b->stages[which];
 }
 
 cusync_stage_t* cusync_attn_block_stage(cusync_attn_block_t* b, int which) {

@@ -283,9 +283,26 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap* mA0, const C
           uint8_t* sa = ring + s * C::kStageBytes;
           uint8_t* sb = sa + C::kABytes;
           const uint32_t full_addr = leader_full0 + s * 8;
+          const int k_base = kb * kPairBlockK;
+          // A B operand that an earlier stage produces (the K^T and V operands of the attention GEMMs) is waited
+          // for by 128-row blocks of the B matrix: this CTA's 128 n rows once per unit, or the stage's 128 k rows.
+          if (p.b_sems != nullptr && (!p.b_kmajor || kb == kb_begin)) {
+            const uint32_t block = static_cast<uint32_t>(p.b_kmajor ? nb_off : k_base) / kBlockM;
+            const uint32_t bidx = p.b_sem_first + block * p.b_sem_stride;
+            const uint32_t target = st.iter * p.b_sem_value;
+            const bool in_range = p.b_kmajor ? nb_off < p.n : k_base < p.k;
+            uint32_t seen = 0;
+            if (in_range && !cusync::spinUntilAtLeast(p.b_sems + bidx, target, st.timeout_ns, &seen)) {
+              bars->abort = 1u;
+              cusync::recordTimeout(st.status, 1u, static_cast<uint32_t>(m_off), static_cast<uint32_t>(k_base), 3u, bidx,
+                                    seen, target);
+              ok = false;
+              break;              // nothing of this stage is armed yet
+            }
+            fence_proxy_async();
+          }
           // The leader's barrier collects the bytes of both CTAs.
           if (leader) mbar_expect_tx(&bars->full[s], 2 * C::kStageBytes);
-          const int k_base = kb * kPairBlockK;
           // B half: one 3-D box.  [k,n] weights: {64 columns, 128 k rows, 2 column chunks};
           // [n,k] weights: {64 k, 128 n rows, 2 k chunks}.
           if (p.b_kmajor) tma_load_3d_pair(sb, tmB, full_addr, 0, nb_off, k_base / 64);

@@ -458,7 +458,7 @@ extern "C" int cusync_gemm_noalloc_read_status(cusync_status_t* out) {
 extern "C" int cusync_gemm_run_noalloc(const cusync_gemm_desc_t* desc, cusync_stream_t stream) {
   if (desc == nullptr) return CUSYNC_ERROR_INVALID_ARGUMENT;
   const cusync_gemm_desc_t& d = *desc;
-  if (d.stage != nullptr) return CUSYNC_ERROR_INVALID_ARGUMENT;   // stages own allocated memory
+  if (d.stage != nullptr || d.b_stage != nullptr) return CUSYNC_ERROR_INVALID_ARGUMENT;   // stages own allocated memory
   if (d.m <= 0 || d.n <= 0 || d.k <= 0 || d.a == nullptr || d.b == nullptr || d.d == nullptr)
     return CUSYNC_ERROR_INVALID_ARGUMENT;
   if (d.epilogue < CUSYNC_EPILOGUE_NONE || d.epilogue > CUSYNC_EPILOGUE_SILU_MUL_DUAL)
@@ -582,12 +582,17 @@ int cusync_gemm_plan_create(cusync_gemm_plan_t** out, const cusync_gemm_desc_t* 
   if (d.cta_pair == 2 && !pair_ok) { delete pl; return CUSYNC_ERROR_UNSUPPORTED; }
   pl->pair = d.cta_pair == 2 || (d.cta_pair == 0 && pair_ok && pair_by_default(d.m, pl->tile_n, dual));
   if (pl->pair) pl->kernel = KernelEntry{nullptr, PairCfg::kSmemBytes};
+  // A produced B operand is waited for by the CTA-pair kernel's loader only, one wait per unit or ring stage.
+  if (d.b_stage != nullptr && (!pl->pair || d.split_k > 1 || d.tail_split > 1 || d.b_sem_value == 0)) {
+    delete pl;
+    return CUSYNC_ERROR_UNSUPPORTED;
+  }
 
   int sms = cusync_b200_sm_count();
   if (sms <= 0) sms = 148;
   if (d.split_k < 0 || d.split_k > 64 || (dual && d.split_k > 1)) { delete pl; return CUSYNC_ERROR_UNSUPPORTED; }
   if (d.tail_split < 0 || d.tail_split > 16) { delete pl; return CUSYNC_ERROR_INVALID_ARGUMENT; }
-  pl->split_k = d.split_k > 0 ? d.split_k : auto_split_k(d.m, d.n, d.k, pl->tile_n, dual, pl->pair, sms);
+  pl->split_k = d.split_k > 0 ? d.split_k : d.b_stage ? 1 : auto_split_k(d.m, d.n, d.k, pl->tile_n, dual, pl->pair, sms);
 
   GemmParams& p = pl->params;
   p.m = d.m; p.n = d.n; p.k = d.k;
@@ -731,6 +736,17 @@ int cusync_gemm_run(cusync_gemm_plan_t* pl, cusync_stream_t stream) {
   p.is_producer = p.stage.out_policy.kind != CUSYNC_POLICY_NOSYNC;
   p.is_consumer = p.stage.in_policy.kind != CUSYNC_POLICY_NOSYNC;
   if (p.is_producer) cusync_stage_note_launch(pl->stage, pl->num_ctas);
+  if (pl->desc.b_stage != nullptr) {
+    cusync_stage_view_t bv;
+    cusync_stage_get_view(pl->desc.b_stage, &bv);
+    if (bv.sems_post == nullptr) return CUSYNC_ERROR_NOT_PRODUCER;
+    // every index the kernel can form must be one of the producer's semaphores
+    const uint64_t blocks = (static_cast<uint64_t>(p.b_kmajor ? p.n : p.k) + kBlockM - 1) / kBlockM;
+    const uint64_t last = pl->desc.b_sem_first + (blocks - 1) * pl->desc.b_sem_stride;
+    if (last >= static_cast<uint64_t>(bv.grid.x) * bv.grid.y * bv.grid.z) return CUSYNC_ERROR_INVALID_ARGUMENT;
+    p.b_sems = bv.sems_post;
+    p.b_sem_first = pl->desc.b_sem_first; p.b_sem_stride = pl->desc.b_sem_stride; p.b_sem_value = pl->desc.b_sem_value;
+  }
   if (pl->conv_slab)
     cusync_conv3x3_slab_kernel<<<pl->num_ctas, kThreads, kSlabSmemBytes, reinterpret_cast<cudaStream_t>(stream)>>>(
         pl->tmA, pl->tmB, p);

@@ -191,6 +191,11 @@ struct GemmParams {
   int32_t num_pairs;
   unsigned long long* trace;       // optional per-tile timeline: 4 words per ticket (see cusync_gemm_plan_set_trace)
   uint32_t trace_capacity;
+  // B operand produced by an earlier stage (CTA-pair kernel): rows [128 r, 128 r + 128) of the B matrix as given
+  // (n rows of [n,k], k rows of [k,n]) are complete when b_sems[b_sem_first + r * b_sem_stride] has reached
+  // iter * b_sem_value.  Null: B holds weights and is never waited for.
+  const uint32_t* b_sems;
+  uint32_t b_sem_first, b_sem_stride, b_sem_value;
   cusync_stage_view_t stage;   // by-value copy, like params_.custage in the reference
 };
 

@@ -245,6 +245,14 @@ typedef struct cusync_gemm_desc {
                                       (today: none, it measured slower), 1 = none, 2..16 = forced.  The stage grid is unchanged (z = 1); a split tile
                                       posts once, from the pair that adds its last slice. */
   cusync_stage_t* stage;           /* NULL = no tile synchronisation (stream-ordered use) */
+  /* A B operand that is itself the output of an earlier stage of the chain (the K^T and V operands of the
+   * attention GEMMs S = Q K^T and O = S V, src/ml-bench/transformer/attention.cu:272-276, whose policies wait for
+   * the A operand only).  b_stage is that producer stage (NULL = B holds weights, never waited for); rows
+   * [128 r, 128 r + 128) of the B matrix as given (n rows of a [n,k] B, k rows of a [k,n] B) are complete when the
+   * producer's semaphore b_sem_first + r * b_sem_stride has reached b_sem_value times the run counter.  CTA-pair
+   * kernel only (else CUSYNC_ERROR_UNSUPPORTED); not with K slices. */
+  cusync_stage_t* b_stage;
+  uint32_t b_sem_first, b_sem_stride, b_sem_value;
 } cusync_gemm_desc_t;
 
 typedef struct cusync_gemm_plan cusync_gemm_plan_t;
@@ -454,6 +462,35 @@ CUSYNC_API cusync_stage_t* cusync_attn_block_stage(cusync_attn_block_t* block, i
 /* Configuration in use: out[0..4] = tile_n of the two GEMMs, their K slices, key-range splits of the attention. */
 CUSYNC_API int cusync_attn_block_config(const cusync_attn_block_t* block, int32_t* out5);
 
+/* The same block in the prompt phase, as the reference runs it (attention.cu:272-276 with seqlen = 0 and a
+ * batch of 512 to 2048 tokens; numbers in results/attention-results-gpt-3-cuda-12.2): four dependent GEMMs,
+ *   XQKV = X Wqkv;  S = Q K^T;  O = S V;  Y = O Wo
+ * with Q, K, V the three thirds of XQKV's columns and no softmax or heads (attention.cu:445-509), each on its own
+ * stream behind a wait kernel (:792-811).  Stage typing: ConsecutiveSync out of the first GEMM, RowSync between the
+ * others (the STRIDEDSYNC configuration, :105-118).  The reference's policies wait for A operands only; here
+ * S = Q K^T also waits for the K rows of the column tile it computes and O = S V for the V rows of each K block
+ * (cusync_gemm_desc_t.b_stage).  x[batch, hidden], w_qkv[hidden, 3 * heads * 128], w_o[heads * 128, out_features];
+ * intermediates qkv[batch, 3 * heads * 128], s[batch, batch], o[batch, heads * 128]; all row-major fp16 on the
+ * device, caller-owned.  batch > 256 and a multiple of 64; model_hidden = 8 * heads * 128.  Without a softmax the
+ * values grow with every GEMM: inputs must be scaled so that O stays inside fp16 (the reference skips its own
+ * check of this chain for that reason, attention.cu:512-515). */
+typedef struct cusync_attn_prompt_desc {
+  int32_t batch, hidden, heads, out_features, model_hidden;
+  const void* x; const void* w_qkv; const void* w_o;
+  void* qkv; void* s; void* o; void* y;
+} cusync_attn_prompt_desc_t;
+
+typedef struct cusync_attn_prompt cusync_attn_prompt_t;
+
+CUSYNC_API int cusync_attn_prompt_create(cusync_attn_prompt_t** out, const cusync_attn_prompt_desc_t* desc);
+CUSYNC_API int cusync_attn_prompt_destroy(cusync_attn_prompt_t* block);
+/* The four GEMMs back to back on one stream (runAttentionBaseline, attention.cu:557-704). */
+CUSYNC_API int cusync_attn_prompt_run_stream_ordered(cusync_attn_prompt_t* block, cusync_stream_t stream);
+/* runAttentionCuSync, one iteration (attention.cu:706-833).  streams: [4]. */
+CUSYNC_API int cusync_attn_prompt_run_cusync(cusync_attn_prompt_t* block, const cusync_stream_t* streams);
+/* Stage handles (0 = XQKV, 1 = S, 2 = O, 3 = Y) for inspection. */
+CUSYNC_API cusync_stage_t* cusync_attn_prompt_stage(cusync_attn_prompt_t* block, int which);
+
 /* ---- MLP driver ---------------------------------------------------------- */
 
 enum { CUSYNC_MLP_GPT3 = 0, CUSYNC_MLP_LLAMA = 1 };
@@ -570,7 +607,7 @@ typedef struct cusync_allreduce_desc {
   int32_t rows, cols;              /* cols a multiple of 8 */
   int64_t ld;                      /* row pitch in elements, the same on every rank */
   int32_t tile_rows;               /* 0 = 128 */
-  int32_t num_ctas;                /* 0 = choose (8); even: blocks are launched in pairs that fill whole TPCs */
+  int32_t num_ctas;                /* 0 = choose (4); even: blocks are launched in pairs that fill whole TPCs */
   void* const* buffers;            /* [world] */
   uint32_t* const* flags;          /* [world] */
   void* multicast_buffer;

@@ -8,7 +8,7 @@ import pytest
 import oracle_lib as o
 import cusync_b200 as cs
 from cusync_b200 import _lib as L
-from cusync_b200.attention import AttentionBlock, DecodeAttention
+from cusync_b200.attention import AttentionBlock, DecodeAttention, PromptAttentionBlock
 
 torch = pytest.importorskip("torch")
 pytestmark = pytest.mark.gpu
@@ -123,3 +123,60 @@ def test_attention_wait_times_out():
     assert st.code == L.ERROR_TIMEOUT and st.expected == 1 and st.seen == 0
     assert (out == 0).all()
     a.destroy(); prod.destroy(); mid.destroy()
+
+
+@pytest.mark.parametrize("B", [512, 1024])
+def test_prompt_phase_attention_chain_of_four_gemms(B):
+    # attention.cu:272-276 with seqlen = 0: XQKV = X Wqkv; S = Q K^T; O = S V; Y = O Wo (no softmax), four stages
+    # on four streams.  Every stage is compared with the oracle fed with what the GPU produced before it, and the
+    # final output with the oracle's own chain.  Inputs are scaled down (X ~ N(0, 0.1^2)) so that O stays inside
+    # fp16: the reference skips its check of this chain because its inputs overflow (attention.cu:512-515).
+    heads, H = 12, 12288
+    hd = heads * 128
+    x = _randn((B, H), 20, 0.1)
+    w_qkv = _randn((H, 3 * hd), 21, 0.02)
+    w_o = _randn((hd, H), 22, 0.02)
+    blk = PromptAttentionBlock(x, w_qkv, w_o, heads)
+    streams = [torch.cuda.Stream(priority=-1)] + [torch.cuda.Stream() for _ in range(3)]
+    rows = np.arange(0, B, B // 64)                # 64 sampled rows through the row-wise stages
+    qkv_ref = o.gemm_f16(x.cpu().numpy(), w_qkv.cpu().numpy())
+    s_ref = o.gemm_f16(qkv_ref[rows, :hd], np.ascontiguousarray(qkv_ref[:, hd:2 * hd].T))
+    o_ref = o.gemm_f16(s_ref, np.ascontiguousarray(qkv_ref[:, 2 * hd:]))
+    y_ref = o.gemm_f16(o_ref, w_o.cpu().numpy())
+    f = lambda t: t.cpu().numpy().astype(np.float64)
+    qkv64 = f(x) @ f(w_qkv)
+    y_exact = (((qkv64[rows, :hd] @ qkv64[:, hd:2 * hd].T) @ qkv64[:, 2 * hd:]) @ f(w_o)).astype(np.float16)
+    tiles_m = B // 128
+    torch.cuda.synchronize()
+    for it in range(1, 4):
+        for t in (blk.qkv, blk.s, blk.o, blk.y):
+            t.fill_(float("nan"))                  # a stage that reads ahead of its producer sees NaN
+        torch.cuda.synchronize()
+        blk.run(streams)
+        torch.cuda.synchronize()
+        assert blk.status_codes() == (0, 0, 0, 0)
+        qkv = blk.qkv.cpu().numpy()
+        assert o.max_rel_err(qkv, qkv_ref) <= TOL
+        s_gpu = blk.s.cpu().numpy()
+        assert not np.isnan(s_gpu.astype(np.float32)).any()
+        assert o.max_rel_err(s_gpu[rows], o.gemm_f16(qkv[rows, :hd], np.ascontiguousarray(qkv[:, hd:2 * hd].T))) <= TOL
+        o_gpu = blk.o.cpu().numpy()
+        assert not np.isnan(o_gpu.astype(np.float32)).any()
+        assert o.max_rel_err(o_gpu[rows], o.gemm_f16(s_gpu[rows], np.ascontiguousarray(qkv[:, 2 * hd:]))) <= TOL
+        y_gpu = blk.y.cpu().numpy()
+        assert not np.isnan(y_gpu.astype(np.float32)).any()
+        assert o.max_rel_err(y_gpu[rows], o.gemm_f16(o_gpu[rows], w_o.cpu().numpy())) <= TOL
+        o.check_final_output(y_gpu[rows], y_ref, y_exact, "prompt attention B=%d run %d" % (B, it), TOL)
+        # semaphores: ConsecutiveSync counts the six column tiles of each third of a row panel; RowSync counts the
+        # column tiles of S (B / 256) and of O (6)
+        assert (blk.stages[0].semaphores()[:3 * tiles_m] == 6 * it).all()
+        assert (blk.stages[1].semaphores()[:tiles_m] == (B // 256) * it).all()
+        assert (blk.stages[2].semaphores()[:tiles_m] == 6 * it).all()
+    y_sync = blk.y.clone()
+    blk.y.fill_(float("nan"))
+    blk.run_stream_ordered(torch.cuda.current_stream())
+    torch.cuda.synchronize()
+    assert torch.equal(blk.y, y_sync)
+    blk.destroy()
+    with pytest.raises(L.CuSyncError):
+        PromptAttentionBlock(x[:256].contiguous(), w_qkv, w_o, heads)      # needs more than two row tiles
