@@ -71,19 +71,27 @@ __device__ __forceinline__ void multimem_st_f16x8(void* mc, uint4 v) {
                "r"(v.z), "r"(v.w)
                : "memory");
 }
-// The same two, executed only where `on` holds (a predicated instruction, not a branch around it).
+// The same two, executed only where `on` holds.  The condition lives inside the statement (a branch over the one
+// instruction), so the compiler sees straight-line code with fixed registers.  A guard predicate on the
+// instruction itself was not enough: `@p multimem.st` was observed to store with p false.
 __device__ __forceinline__ void multimem_ld_reduce_f16x8_if(bool on, const void* mc, uint4& v) {
+  // (outputs only: the registers are cleared inside the statement, then loaded where the condition holds)
   asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %5, 0;\n\t"
-      "@p multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];\n\t}"
-      : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w)
+      "{\n\t.reg .pred p;\n\t.reg .b64 a;\n\tsetp.eq.u32 p, %5, 0;\n\tmov.b64 a, %4;\n\t"   // inputs read before any output is written
+      "mov.b32 %0, 0;\n\tmov.b32 %1, 0;\n\tmov.b32 %2, 0;\n\tmov.b32 %3, 0;\n\t"
+      "@p bra SKIP_LD;\n\t"
+      "multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [a];\n\t"
+      "SKIP_LD:\n\t}"
+      : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
       : "l"(mc), "r"(on ? 1u : 0u)
       : "memory");
 }
 __device__ __forceinline__ void multimem_st_f16x8_if(bool on, void* mc, const uint4& v) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %5, 0;\n\t"
-      "@p multimem.st.relaxed.sys.global.v4.f16x2 [%0], {%1, %2, %3, %4};\n\t}"
+      "{\n\t.reg .pred p;\n\tsetp.eq.u32 p, %5, 0;\n\t"
+      "@p bra SKIP_ST;\n\t"
+      "multimem.st.relaxed.sys.global.v4.f16x2 [%0], {%1, %2, %3, %4};\n\t"
+      "SKIP_ST:\n\t}"
       ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "r"(on ? 1u : 0u)
       : "memory");
 }
@@ -151,12 +159,11 @@ __device__ __forceinline__ void multicast_reduce_span(__half* base, uint32_t vec
   if (begin >= end) return;
   __half* const p0 = base + (static_cast<size_t>(begin) + tid) * 8;
   const uint32_t mine = begin + tid < end ? (end - begin - tid + kWorkers - 1) / kWorkers : 0u;   // this thread's pieces
-  // (predicated instructions in straight-line code: loads and stores keep fixed registers, which branches
-  // around the individual pieces did not)
+  // (the conditions are inside the asm statements: for the compiler this is straight-line code with fixed
+  // registers, which C++ branches around the individual pieces were not)
   uint4 v[kUnroll];
 #pragma unroll
   for (int u = 0; u < kUnroll; u++) {
-    v[u] = make_uint4(0u, 0u, 0u, 0u);
     multimem_ld_reduce_f16x8_if(static_cast<uint32_t>(u) < mine, p0 + static_cast<size_t>(u) * kWorkers * 8, v[u]);
   }
 #pragma unroll
