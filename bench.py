@@ -596,17 +596,37 @@ def main():
             e2e_shard = M.MLPShard("gpt3", args.batch, shard.x, shard.w1, shard.w2, None, policy=args.policy,
                                    post_rows=True, x_rows=True, max_ctas=e2e_ctas, group_rows2=2, single_grid=1)
         else:
-            # N > 1: X still arrives in row blocks behind semaphores; Y leaves once the all-reduce has finished
+            # N > 1: X is replicated over the ranks and Y is the same on all of them after the all-reduce, so the job
+            # moves each of them over PCIe ONCE: rank r fetches rows [r, r + 1) * B / N of X from the host, an
+            # all-gather over NVLink completes X everywhere, and rank r returns its B / N rows of Y.
             if overlap_reduce and args.batch >= OVERLAP_MIN_BATCH:
                 e2e_reducer = tp.RowAllReduce(group, args.batch, M.GPT3_HIDDEN, dev, num_ctas=args.reduce_ctas)
             e2e_shard = M.MLPShard("gpt3", args.batch, shard.x, shard.w1, shard.w2, None, policy=args.policy,
-                                   post_rows=True, x_rows=True,
+                                   post_rows=e2e_reducer is not None,
                                    max_ctas=sms - (e2e_reducer.num_ctas if e2e_reducer else 0),
                                    y=e2e_reducer.y if e2e_reducer else None)
     d2h, h2d, post = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
     landed = [torch.cuda.Event() for _ in range(d2h_blocks)]
 
+    share = args.batch // world if args.batch % world == 0 else 0     # rows of X and of Y this rank moves (N > 1)
+
+    def e2e_step_sharded():
+        r0, r1 = rank * share, (rank + 1) * share
+        with torch.cuda.stream(ps):
+            e2e_shard.x[r0:r1].copy_(xh[r0:r1], non_blocking=True)
+            group.all_gather_rows(e2e_shard.x, share)
+        if e2e_reducer is not None:
+            e2e_shard.run_cusync_allreduce(e2e_reducer, ps, cs, rs)
+        else:
+            e2e_shard.run_cusync(ps, cs)
+            with torch.cuda.stream(cs):
+                group.all_reduce_sum(e2e_shard.y)
+        with torch.cuda.stream(cs):
+            yh[r0:r1].copy_(e2e_shard.y[r0:r1], non_blocking=True)
+
     def e2e_step():
+        if world > 1 and share > 0 and row_blocks:
+            return e2e_step_sharded()
         tiles = (args.batch + 127) // 128
         per = (tiles + d2h_blocks - 1) // d2h_blocks
         if row_blocks:
@@ -649,12 +669,13 @@ def main():
     e2e_us = reduce_max(e2e_total) / args.steps * 1000.0
     if e2e_shard is not shard:
         torch.cuda.synchronize()
-        if not torch.equal(yh, e2e_shard.y.cpu()):
+        lo, hi = (rank * share, (rank + 1) * share) if (world > 1 and share > 0) else (0, args.batch)
+        if not torch.equal(yh[lo:hi], e2e_shard.y[lo:hi].cpu()):
             raise SystemExit("end-to-end result on the host differs from the device result")
         e2e_shard.destroy()
         if e2e_reducer is not None:
             e2e_reducer.destroy()
-    io_bytes = args.batch * M.GPT3_HIDDEN * 2
+    io_bytes = args.batch * M.GPT3_HIDDEN * 2       # whole job: at N > 1 every rank moves 1 / N of it each way
 
     # ---- per-batch table ------------------------------------------------------------------------
     table = []

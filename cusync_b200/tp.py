@@ -169,6 +169,15 @@ class TensorParallelGroup:
                 with torch.cuda.stream(comm_stream):
                     self.dist.all_reduce(shard.y[first * 128:min(shard.batch, (first + n) * 128)])
 
+    def all_gather_rows(self, full, rows_per_rank):
+        """Every rank holds rows [rank, rank + 1) * rows_per_rank of `full`; afterwards every rank holds all of it
+        (in place, on the current stream): how a replicated input reaches the ranks when each of them fetched
+        one share of it from the host."""
+        if self.world > 1:
+            mine = full[self.rank * rows_per_rank:(self.rank + 1) * rows_per_rank]
+            self.dist.all_gather_into_tensor(full[:self.world * rows_per_rank], mine)
+        return full
+
     def barrier(self):
         if self.world > 1:
             self.dist.barrier()
