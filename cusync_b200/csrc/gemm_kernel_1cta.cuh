@@ -461,6 +461,13 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         }
         post_it++;
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (p.trace && ew == 0 && lane == 0 && ticket < p.trace_capacity) {
+          uint32_t smid;
+          asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+          unsigned long long* rec = p.trace + 8ull * ticket;
+          rec[0] = t_draw; rec[1] = t_mma_done; rec[2] = cusync::globalTimerNs();
+          rec[3] = (static_cast<unsigned long long>(smid) << 32) | blockIdx.x;
+        }
         continue;
       }
       epilogue_store_rows<BN, DUAL>(p, &tmD, buf, t_row, n_off, m_off + quarter * 32, half, lane);
