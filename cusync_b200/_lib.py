@@ -166,6 +166,7 @@ SIGNATURES = {
     "cusync_gemm_plan_num_ctas": (_u32, [_vp]),
     "cusync_conv2d_tile_rows": (_i, [C.c_int32]),
     "cusync_conv2d_tile_rows_hw": (_i, [C.c_int32, C.c_int32]),
+    "cusync_conv2d_default_tile_n": (_i, [C.c_int32] * 5),
     "cusync_conv2d_plan_create": (_i, [C.POINTER(_vp), C.POINTER(Conv2dDesc)]),
     "cusync_conv2d_plan_destroy": (_i, [_vp]),
     "cusync_conv2d_run": (_i, [_vp, _vp]),

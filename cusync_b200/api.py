@@ -300,9 +300,13 @@ class Conv2dProblemSize:
     def tile_rows(self):
         return L.lib().cusync_conv2d_tile_rows_hw(self.h, self.w)
 
+    def tile_n(self):
+        """Output channels per N tile: the TileN argument of the sync policies."""
+        return L.lib().cusync_conv2d_default_tile_n(self.n, self.h, self.w, self.c, self.k)
+
     def grid(self):
         """Stage grid (N tiles, M tiles, 1) of the implicit GEMM."""
-        return (self.k // 64, self.n * self.h // max(self.tile_rows(), 1), 1)
+        return (self.k // max(self.tile_n(), 1), self.n * self.h // max(self.tile_rows(), 1), 1)
 
     def tile_m(self):
         """Output pixels per M tile: the TileM argument of the sync policies."""

@@ -59,8 +59,11 @@ int cusync_conv_chain_create(cusync_conv_chain_t** out, const cusync_conv_chain_
   c->desc = d;
   c->num = d.num_convs;
 
-  // Every convolution has the same tile grid: (K / 64, N * H / rows, 1); tiles are rows * W pixels by 64 channels.
-  const cusync_dim3_t grid = {static_cast<uint32_t>(d.channels / 64), static_cast<uint32_t>(d.n * (d.h / rows)), 1};
+  // Every convolution has the same tile grid: (K / tile_n, N * H / rows, 1); tiles are rows * W pixels by tile_n
+  // channels (64 for the 64-channel layer, 64 to 256 otherwise).
+  const int tile_n = cusync_conv2d_default_tile_n(d.n, d.h, d.w, d.channels, d.channels);
+  if (tile_n <= 0) return CUSYNC_ERROR_UNSUPPORTED;
+  const cusync_dim3_t grid = {static_cast<uint32_t>(d.channels / tile_n), static_cast<uint32_t>(d.n * (d.h / rows)), 1};
   const cusync_dim3_t ts = {1, 1, 1};
   const uint32_t tile_m = static_cast<uint32_t>(rows * d.w);
   cusync_policy_t none, post, wait;
@@ -68,7 +71,7 @@ int cusync_conv_chain_create(cusync_conv_chain_t** out, const cusync_conv_chain_
   none.tile_m = none.tile_n = 1;
   std::memset(&post, 0, sizeof(post));
   post.kind = CUSYNC_POLICY_TILESYNC; post.order = CUSYNC_ORDER_TRANSPOSE_XY;
-  post.tile_m = tile_m; post.tile_n = 64; post.wait_value = 1; post.post_value = 1;
+  post.tile_m = tile_m; post.tile_n = static_cast<uint32_t>(tile_n); post.wait_value = 1; post.post_value = 1;
   wait = post;
   wait.kind = CUSYNC_POLICY_CONV2DTILESYNC; wait.p0 = 9;          // R * S (resnet.cu:113-116)
 

@@ -344,8 +344,8 @@ int check_stage_policies(const cusync_stage_view_t& v, uint32_t tile_m, uint32_t
     if (conv ? in.tile_m != tile_m : in.tile_m % tile_m != 0) return CUSYNC_ERROR_INVALID_ARGUMENT;
     const bool walks_k = in.kind == CUSYNC_POLICY_TILESYNC || in.kind == CUSYNC_POLICY_STRIDEDTILESYNC ||
                          in.kind == CUSYNC_POLICY_CONV2DTILESYNC;
-    if (walks_k && (conv ? in.tile_n != static_cast<uint32_t>(kBlockK) : in.tile_n % kBlockK != 0))
-      return CUSYNC_ERROR_INVALID_ARGUMENT;
+    // (a convolution's K walk is channel chunks of 64 outermost: producer tiles are whole chunks wide)
+    if (walks_k && in.tile_n % kBlockK != 0) return CUSYNC_ERROR_INVALID_ARGUMENT;
     const uint64_t prod_sems = static_cast<uint64_t>(v.prod_grid.x) * v.prod_grid.y * v.prod_grid.z;
     for (uint32_t y = 0; y < v.grid.y; y++)
       for (uint32_t k = 0; k < k_extent; k += kBlockK)
@@ -819,6 +819,30 @@ int cusync_conv2d_tile_rows_hw(int32_t h, int32_t w) {
   return rows;
 }
 
+int cusync_conv2d_default_tile_n(int32_t n, int32_t h, int32_t w, int32_t c, int32_t k) {
+  (void)c;
+  const int rows = cusync_conv2d_tile_rows_hw(h, w);
+  if (rows <= 0 || n <= 0 || k <= 0 || k % 64) return 0;
+  if (k == 64) return 64;
+  int sms = cusync_b200_sm_count();
+  if (sms <= 0) sms = 148;
+  const long long tiles_m = static_cast<long long>(n) * (h / rows);
+  // Rounds of tiles on the device times the time of one tile: a K block costs the issuing thread about the same
+  // whatever the tile's width up to 128 columns and a quarter more at 256 (then the tensor pipe is the longer
+  // pole), and wider tiles re-read the input pixels less often.
+  const int widths[3] = {256, 128, 64};
+  const double unit_time[3] = {1.25, 1.05, 1.0};
+  int best = 64;
+  double best_cost = 1e30;
+  for (int i = 0; i < 3; i++) {
+    if (k % widths[i]) continue;
+    const long long units = tiles_m * (k / widths[i]);
+    const double cost = static_cast<double>((units + sms - 1) / sms) * unit_time[i];
+    if (cost < best_cost - 1e-9) { best_cost = cost; best = widths[i]; }
+  }
+  return best;
+}
+
 int cusync_conv2d_plan_create(cusync_conv2d_plan_t** out, const cusync_conv2d_desc_t* desc) {
   if (out == nullptr || desc == nullptr) return CUSYNC_ERROR_INVALID_ARGUMENT;
   *out = nullptr;
@@ -835,13 +859,18 @@ int cusync_conv2d_plan_create(cusync_conv2d_plan_t** out, const cusync_conv2d_de
   cusync_gemm_plan* pl = new (std::nothrow) cusync_gemm_plan();
   if (!pl) return CUSYNC_ERROR_CUDA;
   std::memset(pl, 0, sizeof(*pl));
-  pl->tile_n = 64;
+  pl->tile_n = cusync_conv2d_default_tile_n(d.n, d.h, d.w, d.c, d.k);
   pl->split_k = 1;
-  pl->kernel = KernelEntry{cusync_gemm_kernel<64, false, true>, Cfg<64, false>::kSmemBytes};
+  switch (pl->tile_n) {
+    case 256: pl->kernel = KernelEntry{cusync_gemm_kernel<256, false, true>, Cfg<256, false>::kSmemBytes}; break;
+    case 128: pl->kernel = KernelEntry{cusync_gemm_kernel<128, false, true>, Cfg<128, false>::kSmemBytes}; break;
+    default:  pl->tile_n = 64;
+              pl->kernel = KernelEntry{cusync_gemm_kernel<64, false, true>, Cfg<64, false>::kSmemBytes}; break;
+  }
   GemmParams& p = pl->params;
   p.m = d.n * d.h * d.w; p.n = d.k; p.k = 9 * d.c;
   p.d = d.y; p.ldd = d.k;
-  p.tiles_n = d.k / 64;
+  p.tiles_n = d.k / pl->tile_n;
   p.conv_n = d.n; p.conv_h = d.h; p.conv_w = d.w; p.conv_c = d.c;
   p.conv_rows = rows; p.conv_tiles_per_image = d.h / rows;
   p.tiles_m = d.n * p.conv_tiles_per_image;
@@ -868,7 +897,8 @@ int cusync_conv2d_plan_create(cusync_conv2d_plan_t** out, const cusync_conv2d_de
   else if (view.in_policy.kind != CUSYNC_POLICY_NOSYNC && view.sems_wait == nullptr)
     rc = CUSYNC_ERROR_NOT_INITIALIZED;
   if (rc == CUSYNC_SUCCESS)
-    rc = check_stage_policies(view, static_cast<uint32_t>(rows * d.w), 64u, static_cast<uint32_t>(9 * d.c), true);
+    rc = check_stage_policies(view, static_cast<uint32_t>(rows * d.w), static_cast<uint32_t>(pl->tile_n),
+                              static_cast<uint32_t>(9 * d.c), true);
   int sms = cusync_b200_sm_count();
   if (sms <= 0) sms = 148;
   const uint32_t cap = d.max_ctas > 0 ? static_cast<uint32_t>(d.max_ctas) : static_cast<uint32_t>(sms);
@@ -885,7 +915,7 @@ int cusync_conv2d_plan_create(cusync_conv2d_plan_t** out, const cusync_conv2d_de
     bool ok = (pl->conv_slab ? make_map_nhwc(&pl->tmA, d.x, d.n, d.h, d.w, d.c, static_cast<uint32_t>(rows + 2),
                                              static_cast<uint32_t>(d.w + 2))
                              : make_map_nhwc(&pl->tmA, d.x, d.n, d.h, d.w, d.c, static_cast<uint32_t>(rows))) &&
-              make_map(&pl->tmB, d.filter, d.k, 9ull * d.c, 9ull * d.c, kBlockK, 64);
+              make_map(&pl->tmB, d.filter, d.k, 9ull * d.c, 9ull * d.c, kBlockK, static_cast<uint32_t>(pl->tile_n));
     pl->tmB2 = pl->tmB; pl->tmD = pl->tmB; pl->tmWS = pl->tmB;      // unused by the convolution path
     if (!ok) rc = CUSYNC_ERROR_CUDA;
   }

@@ -8,7 +8,8 @@
 //   conv.params_.custage.incrementIter();
 //
 // CUTLASS types are replaced by small PODs; tensors are NHWC / KRSC fp16 device pointers.  The stage grid is
-// conv2dGridShape(problem) and the policies take TileM = conv2dTileM(problem), TileN = 64.
+// conv2dGridShape(problem) and the policies take TileM = conv2dTileM(problem), TileN = conv2dTileN(problem)
+// (64 for a 64-channel layer).
 #pragma once
 
 #include <cuda_runtime_api.h>
@@ -32,9 +33,11 @@ struct Conv2dProblemSize {
 
 // Output pixels per M tile (whole image rows) and the stage grid (N tiles, M tiles, 1) of the implicit GEMM.
 inline int conv2dTileM(const Conv2dProblemSize& p) { return cusync_conv2d_tile_rows_hw(p.H, p.W) * p.W; }
+inline int conv2dTileN(const Conv2dProblemSize& p) { return cusync_conv2d_default_tile_n(p.N, p.H, p.W, p.C, p.K); }
 inline dim3 conv2dGridShape(const Conv2dProblemSize& p) {
   const int rows = cusync_conv2d_tile_rows_hw(p.H, p.W);
-  return dim3(p.K / 64, rows > 0 ? p.N * (p.H / rows) : 0, 1);
+  const int tile_n = cusync_conv2d_default_tile_n(p.N, p.H, p.W, p.C, p.K);
+  return dim3(tile_n > 0 ? p.K / tile_n : 0, rows > 0 ? p.N * (p.H / rows) : 0, 1);
 }
 
 template <typename CuStageT, int EpilogueKind = EpilogueNone>

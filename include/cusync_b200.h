@@ -341,7 +341,8 @@ CUSYNC_API uint32_t cusync_gemm_plan_num_ctas(const cusync_gemm_plan_t* plan);
  * (conv/device/cusyncimplicit_gemm_convolution.h:51-319) as the reference's resnet.cu / vgg.cu drive it.
  * Implicit GEMM [n*h*w, 9c] x [9c, k]: the K walk is channel-chunk outermost, filter tap innermost, as
  * Conv2DTileSync assumes (policies.h:160-210).  An M tile is cusync_conv2d_tile_rows_hw(h, w) whole image rows
- * (w <= 128), an N tile 64 output channels; the stage grid is (k / 64, n * h / rows, 1).  A consumer
+ * (w <= 128), an N tile cusync_conv2d_default_tile_n(...) output channels; the stage grid is
+ * (k / tile_n, n * h / rows, 1).  A consumer
  * convolution also waits for the producer tiles holding the image rows just above and below its own.
  * Supported: r = s = 3, stride 1, pad 1, c and k multiples of 64. */
 typedef struct cusync_conv2d_desc {
@@ -363,6 +364,11 @@ CUSYNC_API int cusync_conv2d_tile_rows(int32_t w);          /* floor(128 / w): t
  * tiles never straddle two images (56 x 56: 2; 28 x 28: 4; 14 x 14: 7; 7 x 7: 7, the layer sizes of
  * src/ml-bench/volta_conv2d/eval_resnet.py:12-17).  0 when w > 128. */
 CUSYNC_API int cusync_conv2d_tile_rows_hw(int32_t h, int32_t w);
+/* Output channels per N tile the library picks for a layer: 64, 128 or 256 (a divisor of k), by the rounds of
+ * tiles the layer makes on the device; 64 for k = 64.  The stage grid is (k / tile_n, n * h / rows, 1) and the
+ * policies of a chain take TileN = tile_n (the reference fixes its tile shape at compile time,
+ * src/ml-bench/volta_conv2d/resnet.cu:95-105, and tunes it per layer in eval_resnet.py:18-60). */
+CUSYNC_API int cusync_conv2d_default_tile_n(int32_t n, int32_t h, int32_t w, int32_t c, int32_t k);
 /* can_implement + initialize (conv/device/cusyncimplicit_gemm_convolution.h:100-265). */
 CUSYNC_API int cusync_conv2d_plan_create(cusync_conv2d_plan_t** out, const cusync_conv2d_desc_t* desc);
 CUSYNC_API int cusync_conv2d_plan_destroy(cusync_conv2d_plan_t* plan);
@@ -373,8 +379,8 @@ CUSYNC_API uint32_t cusync_conv2d_plan_num_ctas(const cusync_conv2d_plan_t* plan
 /* A chain of 3x3 convolutions with equal channel counts, the workload of
  * src/ml-bench/volta_conv2d/resnet.cu (two convolutions) and vgg.cu (up to four):
  * activations[0] -> conv(filters[0]) -> activations[1] -> ... -> activations[num_convs], NHWC fp16 on the device,
- * caller-owned; ReLU after every convolution when `relu` is set.  Stage i posts TileSync<rows * w, 64> and stage
- * i + 1 waits with Conv2DTileSync<3, 3, rows * w, 64> (resnet.cu:107-116). */
+ * caller-owned; ReLU after every convolution when `relu` is set.  Stage i posts TileSync<rows * w, tile_n> and stage
+ * i + 1 waits with Conv2DTileSync<3, 3, rows * w, tile_n> (resnet.cu:107-116). */
 typedef struct cusync_conv_chain_desc {
   int32_t num_convs;               /* 2..8 */
   int32_t n, h, w, channels;

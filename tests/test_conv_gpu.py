@@ -31,6 +31,8 @@ def _inputs(n, h, w, c, k, seed):
     (2, 14, 14, 256, 256),    # 14 x 14 layer (eval_resnet.py:12-17): 7 of the 9 rows that would fit, so tiles end with the image
     (3, 7, 7, 512, 128),      # 7 x 7 layer: one image (49 pixels) per tile, 72 K blocks
     (1, 5, 56, 64, 64),       # odd height: one image row per tile although two would fit
+    (32, 14, 14, 256, 256),   # 64 M tiles: the library takes 128-channel N tiles (two rounds of 64-wide ones otherwise)
+    (32, 28, 28, 128, 256),   # 224 M tiles: 256-channel N tiles
 ])
 @pytest.mark.parametrize("relu", [False, True])
 def test_conv3x3_matches_oracle(n, h, w, c, k, relu):
@@ -38,6 +40,8 @@ def test_conv3x3_matches_oracle(n, h, w, c, k, relu):
     y = torch.full((n, h, w, k), float("nan"), device="cuda", dtype=torch.half)
     conv = cs.Conv2dFprop()
     prob = cs.Conv2dProblemSize(n, h, w, c, k)
+    if n == 32:
+        assert prob.tile_n() == (128 if h == 14 else 256) and prob.grid()[0] == k // prob.tile_n()
     assert conv.initialize(None, prob, x, f, y, L.EPILOGUE_RELU if relu else L.EPILOGUE_NONE) == L.SUCCESS
     assert conv.run(torch.cuda.current_stream()) == L.SUCCESS
     torch.cuda.synchronize()
@@ -136,6 +140,8 @@ def test_config5_conv_chain_with_conv2dtilesync(n, max_ctas):
     (4, 14, 14, 256, 2, 0),    # 256 channels, 14 x 14
     (8, 7, 7, 512, 2, 0),      # 512 channels, 7 x 7
     (2, 14, 14, 256, 4, 0),    # vgg.cu-style chain of four at 256 channels (vgg.cu:104-119)
+    (32, 14, 14, 256, 2, 0),   # N tiles of 128 channels: Conv2DTileSync over producer tiles two channel chunks wide
+    (40, 14, 14, 256, 2, 0),   # N tiles of 256 channels (80 M tiles: one round instead of two)
 ])
 def test_conv_chain_driver(n, h, w, c, convs, max_ctas):
     # cusync_conv_chain_*: the library's own driver for the chain (resnet.cu / vgg.cu flow)
@@ -143,7 +149,9 @@ def test_conv_chain_driver(n, h, w, c, convs, max_ctas):
     x = torch.randn((n, h, w, c), generator=g).half().cuda()
     filters = [(torch.randn((c, 3, 3, c), generator=g) * (2.0 / (9 * c)) ** 0.5).half().cuda() for _ in range(convs)]
     chain = cs.ConvChain(x, filters, relu=True, max_ctas=max_ctas)
-    blocks = n * (h // L.lib().cusync_conv2d_tile_rows_hw(h, w)) * (c // 64)
+    tile_n = L.lib().cusync_conv2d_default_tile_n(n, h, w, c, c)
+    assert tile_n == {32: 128, 40: 256}.get(n, 64)
+    blocks = n * (h // L.lib().cusync_conv2d_tile_rows_hw(h, w)) * (c // tile_n)
     sms = L.lib().cusync_b200_sm_count()
     shared = blocks * convs <= sms or (convs >= 3 and blocks <= 2 * sms)
     per_stage = min(blocks, max_ctas if max_ctas else (sms // convs if shared else sms))
