@@ -139,7 +139,7 @@ template <bool kChain>
 __device__ __forceinline__ void pair_kernel_body(const CUtensorMap* mA0, const CUtensorMap* mB0, const CUtensorMap* mD0,
                                                  const CUtensorMap* mWS0, const CUtensorMap* mA1, const CUtensorMap* mB1,
                                                  const CUtensorMap* mD1, const CUtensorMap* mWS1, const GemmParams& p0,
-                                                 const GemmParams& p1) {
+                                                 const GemmParams& p1, const CUtensorMap* mB2_0, const CUtensorMap* mB2_1) {
   using C = PairCfg;
   constexpr int BN = kPairBN;
   extern __shared__ uint8_t smem_raw[];
@@ -267,9 +267,13 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap* mA0, const C
           if (kind == CUSYNC_POLICY_TILESYNC || kind == CUSYNC_POLICY_STRIDEDTILESYNC) sync_stride = st.in_policy.tile_n;
           else if (kind == CUSYNC_POLICY_CONV2DTILESYNC) sync_stride = st.in_policy.tile_n * st.in_policy.p0;
         }
-        const int n_off = tn * BN;
+        // Dual GEMM (SiLU(A B) (.) (A B2)): the pair's 256-column MMA is [A B | A B2] of ONE 128-column output tile;
+        // the leader CTA supplies the B half, its peer the B2 half, each the tile's own 128 columns.
+        const bool dual = p.epilogue == CUSYNC_EPILOGUE_SILU_MUL_DUAL;
+        const CUtensorMap* const tmBr = dual && rank ? (gi ? mB2_1 : mB2_0) : tmB;
+        const int n_off = dual ? tn * (BN / 2) : tn * BN;
         const int m_off = tpm * (2 * kBlockM) + static_cast<int>(rank) * kBlockM;   // this CTA's 128 rows
-        const int nb_off = n_off + static_cast<int>(rank) * (BN / 2);               // this CTA's half of B
+        const int nb_off = dual ? n_off : n_off + static_cast<int>(rank) * (BN / 2);   // this CTA's half of B
         uint32_t ready_end = 0;
         long long wait_empty = 0;
         const int kb_per_slice = (p.num_k_blocks + nslices - 1) / nslices;
@@ -305,8 +309,8 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap* mA0, const C
           if (leader) mbar_expect_tx(&bars->full[s], 2 * C::kStageBytes);
           // B half: one 3-D box.  [k,n] weights: {64 columns, 128 k rows, 2 column chunks};
           // [n,k] weights: {64 k, 128 n rows, 2 k chunks}.
-          if (p.b_kmajor) tma_load_3d_pair(sb, tmB, full_addr, 0, nb_off, k_base / 64);
-          else            tma_load_3d_pair(sb, tmB, full_addr, 0, k_base, nb_off / 64);
+          if (p.b_kmajor) tma_load_3d_pair(sb, tmBr, full_addr, 0, nb_off, k_base / 64);
+          else            tma_load_3d_pair(sb, tmBr, full_addr, 0, k_base, nb_off / 64);
           // The stage spans two 64-deep K chunks; each may open a new producer tile.
 #pragma unroll 1
           for (int sub = 0; sub < kPairBlockK / kBlockK && ok; sub++) {
@@ -510,7 +514,8 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap* mA0, const C
       if (!mbar_wait_cluster(&bars->tmem_full[acc], aph, ctx)) { ok = false; break; }
       tc_fence_after();
       const unsigned long long t_mma_done = p.trace ? cusync::globalTimerNs() : 0ull;
-      const int n_off = tile_n * BN;
+      const bool dual = p.epilogue == CUSYNC_EPILOGUE_SILU_MUL_DUAL;       // a 128-column output tile from both halves
+      const int n_off = dual ? tile_n * (BN / 2) : tile_n * BN;
       const int m_off = pair_m * (2 * kBlockM) + static_cast<int>(rank) * kBlockM;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * C::kAccCols;
 
@@ -548,7 +553,8 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap* mA0, const C
         }
         continue;
       }
-      epilogue_store_rows<BN, false>(p, tmD, buf, t_row, n_off, m_off + quarter * 32, half, lane);
+      if (dual) epilogue_store_rows<BN / 2, true>(p, tmD, buf, t_row, n_off, m_off + quarter * 32, half, lane);
+      else      epilogue_store_rows<BN, false>(p, tmD, buf, t_row, n_off, m_off + quarter * 32, half, lane);
 
       tc_fence_before();
       __syncwarp();
@@ -610,8 +616,8 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap* mA0, const C
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 cusync_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                         const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmWS,
-                        const GemmParams p) {
-  pair_kernel_body<false>(&tmA, &tmB, &tmD, &tmWS, &tmA, &tmB, &tmD, &tmWS, p, p);
+                        const __grid_constant__ CUtensorMap tmB2, const GemmParams p) {
+  pair_kernel_body<false>(&tmA, &tmB, &tmD, &tmWS, &tmA, &tmB, &tmD, &tmWS, p, p, &tmB2, &tmB2);
 }
 
 // Two dependent GEMMs (both on CTA pairs) in one persistent grid; see pair_kernel_body.
@@ -620,8 +626,9 @@ cusync_gemm_pair_chain_kernel(const __grid_constant__ CUtensorMap tmA0, const __
                               const __grid_constant__ CUtensorMap tmD0, const __grid_constant__ CUtensorMap tmWS0,
                               const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1,
                               const __grid_constant__ CUtensorMap tmD1, const __grid_constant__ CUtensorMap tmWS1,
+                              const __grid_constant__ CUtensorMap tmB2_0, const __grid_constant__ CUtensorMap tmB2_1,
                               const __grid_constant__ GemmParams p0, const __grid_constant__ GemmParams p1) {
-  pair_kernel_body<true>(&tmA0, &tmB0, &tmD0, &tmWS0, &tmA1, &tmB1, &tmD1, &tmWS1, p0, p1);
+  pair_kernel_body<true>(&tmA0, &tmB0, &tmD0, &tmWS0, &tmA1, &tmB1, &tmD1, &tmWS1, p0, p1, &tmB2_0, &tmB2_1);
 }
 
 }  // namespace

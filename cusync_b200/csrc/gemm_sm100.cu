@@ -210,7 +210,8 @@ int auto_split_k(int m, int n, int k, int tile_n, bool dual, bool pair, int sms)
 // From three row tiles on: with two (M <= 256) the one-CTA kernel's 128-row tiles give twice the work units,
 // which measured 9 % faster on the GPT-3 MLP shard at M = 256.
 bool pair_by_default(int m, int tile_n, bool dual) {
-  return !dual && tile_n == kPairBN && m > 2 * kBlockM;
+  // (the dual GEMM on CTA pairs computes 128-column output tiles: its 256-column MMA is [A B | A B2])
+  return tile_n == (dual ? kPairBN / 2 : kPairBN) && m > 2 * kBlockM;
 }
 
 // Pair mode: schedule over 256-row pair tiles (the stage's order applied to the pair grid), and the
@@ -304,6 +305,10 @@ int build_maps(cusync_gemm_plan* pl) {
     if (d.b_layout == CUSYNC_B_ROW_MAJOR_NK) okp = okp && make_map_chunked(&pl->tmB, d.b, d.n, d.k, d.ldb, kPairBN / 2, kPairBlockK / 64);
     else                                     okp = okp && make_map_chunked(&pl->tmB, d.b, d.k, d.n, d.ldb, kPairBlockK, kPairBN / 2 / 64);
     pl->tmB2 = pl->tmB;
+    if (dual) {
+      if (d.b_layout == CUSYNC_B_ROW_MAJOR_NK) okp = okp && make_map_chunked(&pl->tmB2, d.b2, d.n, d.k, d.ldb, kPairBN / 2, kPairBlockK / 64);
+      else                                     okp = okp && make_map_chunked(&pl->tmB2, d.b2, d.k, d.n, d.ldb, kPairBlockK, kPairBN / 2 / 64);
+    }
     okp = okp && make_map(&pl->tmD, d.d, d.m, d.n, d.ldd, kStoreCols, 32);
     return okp ? CUSYNC_SUCCESS : CUSYNC_ERROR_CUDA;
   }
@@ -577,7 +582,7 @@ int cusync_gemm_plan_create(cusync_gemm_plan_t** out, const cusync_gemm_desc_t* 
   if (d.cta_pair < 0 || d.cta_pair > 2) { delete pl; return CUSYNC_ERROR_INVALID_ARGUMENT; }
   // The pair kernel fetches operands in 64-element chunks of whole rows: K, and N of [k,n] weights, must be
   // multiples of 64 (a ragged last chunk would read past the end of a row).
-  const bool pair_ok = !dual && pl->tile_n == kPairBN && d.k % 64 == 0 &&
+  const bool pair_ok = pl->tile_n == (dual ? kPairBN / 2 : kPairBN) && d.k % 64 == 0 &&
                        (d.b_layout == CUSYNC_B_ROW_MAJOR_NK || d.n % 64 == 0);
   if (d.cta_pair == 2 && !pair_ok) { delete pl; return CUSYNC_ERROR_UNSUPPORTED; }
   pl->pair = d.cta_pair == 2 || (d.cta_pair == 0 && pair_ok && pair_by_default(d.m, pl->tile_n, dual));
@@ -752,7 +757,7 @@ int cusync_gemm_run(cusync_gemm_plan_t* pl, cusync_stream_t stream) {
         pl->tmA, pl->tmB, p);
   else if (pl->pair)
     cusync_gemm_pair_kernel<<<pl->num_ctas, kThreads, pl->kernel.smem, reinterpret_cast<cudaStream_t>(stream)>>>(
-        pl->tmA, pl->tmB, pl->tmD, pl->tmWS, p);
+        pl->tmA, pl->tmB, pl->tmD, pl->tmWS, pl->tmB2, p);
   else
     pl->kernel.fn<<<pl->num_ctas, kThreads, pl->kernel.smem, reinterpret_cast<cudaStream_t>(stream)>>>(
         pl->tmA, pl->tmB, pl->tmB2, pl->tmD, pl->tmWS, p);
@@ -797,7 +802,8 @@ int cusync_gemm_run_chain(cusync_gemm_plan_t* first, cusync_gemm_plan_t* second,
   if (p0.is_producer) cusync_stage_note_launch(first->stage, ctas);
   if (p1.is_producer) cusync_stage_note_launch(second->stage, ctas);
   cusync_gemm_pair_chain_kernel<<<ctas, kThreads, PairCfg::kSmemBytes, reinterpret_cast<cudaStream_t>(stream)>>>(
-      first->tmA, first->tmB, first->tmD, first->tmWS, second->tmA, second->tmB, second->tmD, second->tmWS, p0, p1);
+      first->tmA, first->tmB, first->tmD, first->tmWS, second->tmA, second->tmB, second->tmD, second->tmWS,
+      first->tmB2, second->tmB2, p0, p1);
   return cudaGetLastError() == cudaSuccess ? CUSYNC_SUCCESS : CUSYNC_ERROR_CUDA;
 }
 

@@ -237,8 +237,10 @@ typedef struct cusync_gemm_desc {
                                       the epilogue, stores and posts (serial split-K of gemm/kernel/cusyncgemm.h:374-392,
                                       without its ordering of the slices).  Not with CUSYNC_EPILOGUE_SILU_MUL_DUAL. */
   int32_t cta_pair;                /* 0 = choose; 1 = one CTA per 128 x tile_n tile; 2 = CTA pairs (tcgen05
-                                      cta_group::2): two CTAs share a 256 x 256 tile, each loading half of B.
-                                      Needs tile_n 256 and a single B operand.  Semaphores stay per 128-row tile. */
+                                      cta_group::2): two CTAs share a 256 x 256 tile, each loading half of B
+                                      (tile_n 256), or, for CUSYNC_EPILOGUE_SILU_MUL_DUAL, a 256 x 128 output tile whose
+                                      MMA is [A B | A B2], one CTA loading B and the other B2 (tile_n 128).
+                                      Semaphores stay per 128-row tile. */
   int32_t tail_split;              /* CTA-pair kernel without uniform split-K: K slices for the tiles of the last,
                                       partial wave, so that the tail occupies every SM pair (the remedy the reference
                                       gets from Stream-K, src/ml-bench/transformer/mlp.cu:137-207).  0 = choose

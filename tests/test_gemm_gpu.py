@@ -108,6 +108,25 @@ def test_cta_pair_gemm_matches_oracle(M, N, K, layout):
     assert o.max_rel_err(d.cpu().numpy(), ref) <= TOL
 
 
+@pytest.mark.parametrize("M,N,K,max_ctas", [(256, 256, 128, 0), (640, 2752, 256, 0), (1024, 1280, 1024, 6), (2048, 2752, 512, 0)])
+@pytest.mark.parametrize("layout", [L.B_ROW_MAJOR_KN, L.B_ROW_MAJOR_NK])
+def test_dual_gemm_silu_mul_on_cta_pairs(M, N, K, max_ctas, layout):
+    # The fused SwiGLU GEMM on CTA pairs: the pair's 256-column MMA is [A B | A B2] of one 128-column output tile (the
+    # leader CTA loads the B half, its peer the B2 half); the epilogue stores SiLU(A B) (.) (A B2).  N = 2752 (LLaMA's
+    # ffn shard) ends in a ragged tile; M = 640 is an odd number of row tiles; few clusters and repeated runs.
+    a = _rand((M, K), 60, dist="normal")
+    b = _rand((K, N), 61, scale=0.05, dist="normal")
+    b2 = _rand((K, N), 62, scale=0.05, dist="normal")
+    d, n = _gemm(a, b, epi=L.EPILOGUE_SILU_MUL_DUAL, tile_n=128, b_layout=layout, b2=b2, cta_pair=2, max_ctas=max_ctas,
+                 runs=2)
+    assert n % 2 == 0
+    ref = o.gemm_dual_silu_mul_f16(a.cpu().numpy(), b.cpu().numpy(), b2.cpu().numpy())
+    assert o.max_rel_err(d.cpu().numpy(), ref) <= TOL
+    # the same numbers as the one-CTA kernel gives (same K walk per element)
+    d1, _ = _gemm(a, b, epi=L.EPILOGUE_SILU_MUL_DUAL, tile_n=128, b_layout=layout, b2=b2, cta_pair=1)
+    assert torch.equal(d, d1)
+
+
 def test_cta_pair_gemm_epilogue_and_few_clusters():
     a = _rand((1024, 512), 52, dist="normal")
     b = _rand((512, 2048), 53, scale=0.05, dist="normal")
