@@ -408,24 +408,37 @@ def main():
     shard = layer.shard
     reduce_err = layer.check()
 
-    def interleaved(step_a, a_streams, step_b, b_streams, n, warm):
-        """Alternates the two arms step by step, so clock and power drift hits both alike.
-        Returns the per-step millisecond lists of A and B."""
+    side_streams = []          # every further stream an arm launches on registers here
+
+    def interleaved_arms(arms, n, warm):
+        """Alternates the arms [(step, (first stream, last stream)), ...] step by step, so clock and power drift
+        hits all alike.  Before every step all streams meet: the arm's first stream waits for everything
+        enqueued so far and every other stream waits for that point, so that no kernel of a step (a consumer on a
+        side stream, say) can become resident while the previous step of another arm still runs.
+        Returns one per-step millisecond list per arm."""
+        streams = [ps, cs, rs] + side_streams
         for _ in range(warm):
-            step_a(); step_b()
+            for fn, _ in arms:
+                fn()
         torch.cuda.synchronize()
         barrier()
-        ev = []
+        ev = [[] for _ in arms]
         for _ in range(n):
-            pair = []
-            for fn, (s0, s1) in ((step_a, a_streams), (step_b, b_streams)):
-                s0.wait_stream(cs); s0.wait_stream(ps); s0.wait_stream(rs)
+            for i, (fn, (s0, s1)) in enumerate(arms):
+                for s in streams:
+                    if s is not s0:
+                        s0.wait_stream(s)
+                for s in streams:
+                    if s is not s0:
+                        s.wait_stream(s0)
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record(s0); fn(); e1.record(s1)
-                pair.append((e0, e1))
-            ev.append(pair)
+                ev[i].append((e0, e1))
         torch.cuda.synchronize()
-        return [p[0][0].elapsed_time(p[0][1]) for p in ev], [p[1][0].elapsed_time(p[1][1]) for p in ev]
+        return [[a.elapsed_time(b) for a, b in e] for e in ev]
+
+    def interleaved(step_a, a_streams, step_b, b_streams, n, warm):
+        return interleaved_arms([(step_a, a_streams), (step_b, b_streams)], n, warm)
 
     def med_us(ms_list):
         return reduce_max(statistics.median(ms_list) * 1000.0)
@@ -696,6 +709,12 @@ def main():
                 row[pol + "_us"] = round(c_us, 2)
                 row[pol + "_stream_ordered_us"] = round(o_us, 2)
                 row[pol + "_gain_pct"] = round(100.0 - c_us / o_us * 100.0, 2)
+                if pol == "rowsync":
+                    # the two synchronised launches on ONE stream, the consumer a programmatic dependent launch
+                    d_per, o2_per = interleaved(lambda s=s: s.run_dependent(cs), (cs, cs), o_step, (cs, cs), 20, 5)
+                    row["rowsync_dependent_launch_us"] = round(statistics.median(d_per) * 1000, 2)
+                    row["rowsync_dependent_launch_gain_pct"] = round(
+                        100.0 - statistics.median(d_per) / statistics.median(o2_per) * 100.0, 2)
                 row["tile_n"] = [s.tile_n1, s.tile_n2]
                 row["split_k"] = [s.split_k1, s.split_k2]
                 row["single_grid"] = s.single_grid
@@ -727,12 +746,21 @@ def main():
         import cusync_b200 as lib_
         from cusync_b200.attention import AttentionBlock
         s3 = torch.cuda.Stream()
+        side_streams.append(s3)
 
-        def ab(c_step, o_step):
-            c_per, o_per = interleaved(c_step, (ps, cs), o_step, (cs, cs), 20, 5)
-            c_us, o_us = statistics.median(c_per) * 1000, statistics.median(o_per) * 1000
-            return {"cusync_us": round(c_us, 2), "stream_ordered_us": round(o_us, 2),
-                    "gain_pct": round(100.0 - c_us / o_us * 100.0, 2)}
+        def ab(c_step, o_step, d_step=None):
+            """Stream form (the reference's: one stream per stage) against the stream-ordered arm and, where
+            given, the one-stream form whose dependent stages are programmatic dependent launches."""
+            arms = [(c_step, (ps, cs)), (o_step, (cs, cs))] + ([(d_step, (cs, cs))] if d_step else [])
+            per = interleaved_arms(arms, 20, 5)
+            c_us, o_us = statistics.median(per[0]) * 1000, statistics.median(per[1]) * 1000
+            r = {"cusync_us": round(c_us, 2), "stream_ordered_us": round(o_us, 2),
+                 "gain_pct": round(100.0 - c_us / o_us * 100.0, 2)}
+            if d_step:
+                d_us = statistics.median(per[2]) * 1000
+                r["dependent_launch_us"] = round(d_us, 2)
+                r["dependent_launch_gain_pct"] = round(100.0 - d_us / o_us * 100.0, 2)
+            return r
 
         rows = []
         for b in (1, 64, 512, 2048):     # config 3: LLaMA 65B MLP shard, fused SwiGLU dual GEMM, ffn 2752
@@ -740,7 +768,8 @@ def main():
             for pol in ("rowsync", "tilesync"):
                 sh = M.MLPShard("llama", b, x, w1, w2, v, policy=pol)
 
-                r = ab(lambda sh=sh: sh.run_cusync(ps, cs), lambda sh=sh: sh.run_stream_ordered(cs))
+                r = ab(lambda sh=sh: sh.run_cusync(ps, cs), lambda sh=sh: sh.run_stream_ordered(cs),
+                       (lambda sh=sh: sh.run_dependent(cs)) if pol == "rowsync" else None)
                 r.update({"batch": b, "policy": pol, "tile_n": [sh.tile_n1, sh.tile_n2],
                           "split_k": [sh.split_k1, sh.split_k2]})
                 rows.append(r); sh.destroy()
@@ -759,7 +788,7 @@ def main():
 
             def o_step():
                 chain.run_stream_ordered(cs)
-            r = ab(c_step, o_step)
+            r = ab(c_step, o_step, lambda: chain.run_dependent(cs))
             r["images"] = n
             r["wait_kernel"] = chain.uses_wait_kernels
             rows.append(r)
@@ -775,7 +804,8 @@ def main():
                 xin = torch.randn((n, hw_, hw_, c), generator=g, device=dev).half()
                 fs = [(torch.randn((c, 3, 3, c), generator=g, device=dev) * (2.0 / (9 * c)) ** 0.5).half() for _ in range(2)]
                 chain = lib_.ConvChain(xin, fs, relu=True)
-                r = ab(lambda chain=chain: chain.run_cusync([ps, cs]), lambda chain=chain: chain.run_stream_ordered(cs))
+                r = ab(lambda chain=chain: chain.run_cusync([ps, cs]), lambda chain=chain: chain.run_stream_ordered(cs),
+                       lambda chain=chain: chain.run_dependent(cs))
                 r.update({"channels": c, "image": hw_, "images": n, "wait_kernel": chain.uses_wait_kernels,
                           "tflops": round(2 * 2.0 * n * hw_ * hw_ * c * 9 * c / (r["cusync_us"] * 1e-6) / 1e12, 1)})
                 rows.append(r)
@@ -788,13 +818,14 @@ def main():
         fs = [(torch.randn((64, 3, 3, 64), generator=g, device=dev) * (2.0 / 576) ** 0.5).half() for _ in range(4)]
         chain = lib_.ConvChain(xin, fs, relu=True)
         side = [torch.cuda.Stream(), torch.cuda.Stream()]
+        side_streams.extend(side)
 
         def c4_step():
             chain.run_cusync([ps, side[0], side[1], cs])
 
         def o4_step():
             chain.run_stream_ordered(cs)
-        r = ab(c4_step, o4_step)
+        r = ab(c4_step, o4_step, lambda: chain.run_dependent(cs))
         r.update({"images": 8, "convs": 4})
         extras["vgg_conv3x3_chain_of_4"] = [r]
         chain.destroy()
@@ -811,7 +842,7 @@ def main():
 
             def c_step():
                 blk.run((ps, cs, s3)); cs.wait_stream(s3)
-            r = ab(c_step, lambda: blk.run_stream_ordered(cs))
+            r = ab(c_step, lambda: blk.run_stream_ordered(cs), lambda: blk.run_dependent(cs))
             r.update({"batch": b, "context": seq, "config": blk.config})
             rows.append(r); blk.destroy()
         extras["gpt3_attention_block"] = rows
@@ -819,6 +850,7 @@ def main():
         # XQKV = X Wqkv; S = Q K^T; O = S V; Y = O Wo, four GEMMs on four streams.  X ~ N(0, 0.1^2) keeps O in fp16.
         from cusync_b200.attention import PromptAttentionBlock
         s4 = torch.cuda.Stream()
+        side_streams.append(s4)
         rows = []
         for b in (512, 1024, 2048):
             g = torch.Generator(device=dev).manual_seed(9)
@@ -829,7 +861,7 @@ def main():
 
             def c_step(blk=blk):
                 blk.run((ps, s3, s4, cs))
-            r = ab(c_step, lambda blk=blk: blk.run_stream_ordered(cs))
+            r = ab(c_step, lambda blk=blk: blk.run_stream_ordered(cs), lambda blk=blk: blk.run_dependent(cs))
             r.update({"batch": b, "tflops": round(blk.flops() / (r["cusync_us"] * 1e-6) / 1e12, 1),
                       "ok": blk.status_codes() == (0, 0, 0, 0)})
             rows.append(r); blk.destroy()
@@ -839,6 +871,7 @@ def main():
         # attention block (config 4: 12 of 96 heads per rank) with NCCL's all-reduce of its output after the chain
         from cusync_b200.attention import AttentionBlock
         s3 = torch.cuda.Stream()
+        side_streams.append(s3)
         rows = []
         for b in (64, 512, 2048):
             lb = Layer("llama", b, "rowsync", seed=rank)

@@ -154,6 +154,7 @@ SIGNATURES = {
     "cusync_gemm_plan_destroy": (_i, [_vp]),
     "cusync_gemm_plan_update": (_i, [_vp, _vp, _vp, _vp, _vp]),
     "cusync_gemm_run": (_i, [_vp, _vp]),
+    "cusync_gemm_run_dependent": (_i, [_vp, _vp]),
     "cusync_gemm_plan_tail_split": (_i, [_vp]),
     "cusync_gemm_run_chain": (_i, [_vp, _vp, _vp]),
     "cusync_gemm_chain_supported": (_i, [_vp, _vp]),
@@ -170,11 +171,13 @@ SIGNATURES = {
     "cusync_conv2d_plan_create": (_i, [C.POINTER(_vp), C.POINTER(Conv2dDesc)]),
     "cusync_conv2d_plan_destroy": (_i, [_vp]),
     "cusync_conv2d_run": (_i, [_vp, _vp]),
+    "cusync_conv2d_run_dependent": (_i, [_vp, _vp]),
     "cusync_conv2d_plan_num_ctas": (_u32, [_vp]),
     "cusync_conv_chain_create": (_i, [C.POINTER(_vp), C.POINTER(ConvChainDesc)]),
     "cusync_conv_chain_destroy": (_i, [_vp]),
     "cusync_conv_chain_run_stream_ordered": (_i, [_vp, _vp]),
     "cusync_conv_chain_run_cusync": (_i, [_vp, C.POINTER(_vp)]),
+    "cusync_conv_chain_run_dependent": (_i, [_vp, _vp]),
     "cusync_conv_chain_run_cusync_replayable": (_i, [_vp, C.POINTER(_vp)]),
     "cusync_conv_chain_stage": (_vp, [_vp, _i]),
     "cusync_conv_chain_uses_wait_kernels": (_i, [_vp]),
@@ -183,21 +186,25 @@ SIGNATURES = {
     "cusync_attn_plan_destroy": (_i, [_vp]),
     "cusync_attn_plan_splits": (_i, [_vp]),
     "cusync_attn_run": (_i, [_vp, _vp]),
+    "cusync_attn_run_dependent": (_i, [_vp, _vp]),
     "cusync_attn_block_create": (_i, [C.POINTER(_vp), C.POINTER(AttnBlockDesc)]),
     "cusync_attn_block_destroy": (_i, [_vp]),
     "cusync_attn_block_run_stream_ordered": (_i, [_vp, _vp]),
     "cusync_attn_block_run_cusync": (_i, [_vp, C.POINTER(_vp)]),
+    "cusync_attn_block_run_dependent": (_i, [_vp, _vp]),
     "cusync_attn_block_stage": (_vp, [_vp, _i]),
     "cusync_attn_block_config": (_i, [_vp, C.POINTER(C.c_int32)]),
     "cusync_attn_prompt_create": (_i, [C.POINTER(_vp), C.POINTER(AttnPromptDesc)]),
     "cusync_attn_prompt_destroy": (_i, [_vp]),
     "cusync_attn_prompt_run_stream_ordered": (_i, [_vp, _vp]),
     "cusync_attn_prompt_run_cusync": (_i, [_vp, C.POINTER(_vp)]),
+    "cusync_attn_prompt_run_dependent": (_i, [_vp, _vp]),
     "cusync_attn_prompt_stage": (_vp, [_vp, _i]),
     "cusync_mlp_create": (_i, [C.POINTER(_vp), C.POINTER(MlpDesc)]),
     "cusync_mlp_destroy": (_i, [_vp]),
     "cusync_mlp_run_stream_ordered": (_i, [_vp, _vp]),
     "cusync_mlp_run_cusync": (_i, [_vp, _vp, _vp]),
+    "cusync_mlp_run_dependent": (_i, [_vp, _vp]),
     "cusync_mlp_run_single": (_i, [_vp, _i, _vp]),
     "cusync_mlp_update_io": (_i, [_vp, _vp, _vp]),
     "cusync_mlp_stage": (_vp, [_vp, _i]),

@@ -274,6 +274,11 @@ class Gemm:
     def run(self, overlap=True, unused=None, stream=None):
         return L.lib().cusync_gemm_run(self._plan, _stream_ptr(stream))
 
+    def run_dependent(self, stream=None):
+        """The launch as a programmatic dependent of the kernel ahead of it in `stream` (consumers only): resident
+        once every block of that kernel is, with no wait kernel or second stream."""
+        return L.lib().cusync_gemm_run_dependent(self._plan, _stream_ptr(stream))
+
     @staticmethod
     def run_chain(first, second, stream=None):
         """Both GEMMs as one persistent grid (cusync_gemm_run_chain): `second` consumes what `first` produces."""
@@ -331,6 +336,9 @@ class Conv2dFprop:
 
     def run(self, stream=None):
         return L.lib().cusync_conv2d_run(self._plan, _stream_ptr(stream))
+
+    def run_dependent(self, stream=None):
+        return L.lib().cusync_conv2d_run_dependent(self._plan, _stream_ptr(stream))
 
     def num_ctas(self):
         return L.lib().cusync_conv2d_plan_num_ctas(self._plan)

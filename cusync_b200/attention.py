@@ -28,6 +28,9 @@ class DecodeAttention:
     def run(self, stream=None):
         return L.lib().cusync_attn_run(self._plan, _stream_ptr(stream))
 
+    def run_dependent(self, stream=None):
+        return L.lib().cusync_attn_run_dependent(self._plan, _stream_ptr(stream))
+
     def destroy(self):
         if self._plan:
             L.lib().cusync_attn_plan_destroy(self._plan)
@@ -94,6 +97,10 @@ class AttentionBlock:
     def run_stream_ordered(self, stream):
         L.check(L.lib().cusync_attn_block_run_stream_ordered(self._h, _stream_ptr(stream)), "run_stream_ordered")
 
+    def run_dependent(self, stream):
+        """The synchronised stages on one stream, each dependent one a programmatic dependent launch."""
+        L.check(L.lib().cusync_attn_block_run_dependent(self._h, _stream_ptr(stream)), "run_dependent")
+
     def status_codes(self):
         return tuple(st.status().code for st in (self.s1, self.s2, self.s3))
 
@@ -136,6 +143,10 @@ class PromptAttentionBlock:
 
     def run_stream_ordered(self, stream):
         L.check(L.lib().cusync_attn_prompt_run_stream_ordered(self._h, _stream_ptr(stream)), "run_stream_ordered")
+
+    def run_dependent(self, stream):
+        """The four synchronised GEMMs on one stream, GEMMs 2 to 4 as programmatic dependent launches."""
+        L.check(L.lib().cusync_attn_prompt_run_dependent(self._h, _stream_ptr(stream)), "run_dependent")
 
     def status_codes(self):
         return tuple(st.status().code for st in self.stages)

@@ -40,6 +40,10 @@ class ConvChain:
         arr = (C.c_void_p * len(streams))(*[_stream_ptr(s) for s in streams])
         L.check(L.lib().cusync_conv_chain_run_cusync(self._h, C.cast(arr, C.POINTER(C.c_void_p))), "run_cusync")
 
+    def run_dependent(self, stream):
+        """The synchronised convolutions on one stream, each dependent one a programmatic dependent launch."""
+        L.check(L.lib().cusync_conv_chain_run_dependent(self._h, _stream_ptr(stream)), "run_dependent")
+
     def run_cusync_replayable(self, streams):
         """Reset + run, for recording into a CUDA graph captured on streams[0]; the caller joins the streams."""
         arr = (C.c_void_p * len(streams))(*[_stream_ptr(s) for s in streams])

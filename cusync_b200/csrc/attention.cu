@@ -59,6 +59,7 @@ cusync_attn_decode_kernel(const AttnParams p) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const cusync_stage_view_t& st = p.stage;
 
+  cusync::allowDependentLaunch();       // this block is resident: a dependent consumer may be launched
   if (tid == 0 && p.is_producer) {
     // "started" words for the wait kernel of the next stage
     if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) cusync::storeRelease(st.started, st.iter);
@@ -377,7 +378,22 @@ int cusync_attn_plan_destroy(cusync_attn_plan_t* pl) {
 
 int cusync_attn_plan_splits(const cusync_attn_plan_t* pl) { return pl ? pl->splits : 0; }
 
-int cusync_attn_run(cusync_attn_plan_t* pl, cusync_stream_t stream) {
+namespace {
+int attn_launch(cusync_attn_plan_t* pl, cusync_stream_t stream, bool dependent);
+}
+
+int cusync_attn_run(cusync_attn_plan_t* pl, cusync_stream_t stream) { return attn_launch(pl, stream, false); }
+
+int cusync_attn_run_dependent(cusync_attn_plan_t* pl, cusync_stream_t stream) {
+  if (!pl) return CUSYNC_ERROR_NOT_INITIALIZED;
+  cusync_stage_view_t v;
+  cusync_stage_get_view(pl->stage, &v);
+  if (v.in_policy.kind == CUSYNC_POLICY_NOSYNC) return CUSYNC_ERROR_NOT_CONSUMER;
+  return attn_launch(pl, stream, true);
+}
+
+namespace {
+int attn_launch(cusync_attn_plan_t* pl, cusync_stream_t stream, bool dependent) {
   if (!pl) return CUSYNC_ERROR_NOT_INITIALIZED;
   AttnParams p = pl->params;
   cusync_stage_get_view(pl->stage, &p.stage);
@@ -385,8 +401,17 @@ int cusync_attn_run(cusync_attn_plan_t* pl, cusync_stream_t stream) {
   p.is_consumer = p.stage.in_policy.kind != CUSYNC_POLICY_NOSYNC;
   dim3 grid(pl->desc.heads, pl->desc.batch, pl->splits);
   if (p.is_producer) cusync_stage_note_launch(pl->stage, grid.x * grid.y * grid.z);
+  if (dependent) {
+    if (launchDependent(cusync_attn_decode_kernel, grid, dim3(kAttnThreads), pl->smem,
+                        reinterpret_cast<cudaStream_t>(stream), p) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return CUSYNC_ERROR_CUDA;
+    }
+    return CUSYNC_SUCCESS;
+  }
   cusync_attn_decode_kernel<<<grid, kAttnThreads, pl->smem, reinterpret_cast<cudaStream_t>(stream)>>>(p);
   return cudaGetLastError() == cudaSuccess ? CUSYNC_SUCCESS : CUSYNC_ERROR_CUDA;
 }
+}  // namespace
 
 }  // extern "C"

@@ -152,6 +152,19 @@ int cusync_attn_block_run_cusync(cusync_attn_block_t* b, const cusync_stream_t* 
   return rc;
 }
 
+int cusync_attn_block_run_dependent(cusync_attn_block_t* b, cusync_stream_t stream) {
+  if (!b) return CUSYNC_ERROR_NOT_INITIALIZED;
+  // One stream: each dependent stage is launched as a programmatic dependent of the stage ahead of it.
+  if (!b->order.begin(stream)) { (void)cudaGetLastError(); return CUSYNC_ERROR_CUDA; }
+  int rc = cusync_gemm_run(b->qkv[0], stream);
+  if (rc == CUSYNC_SUCCESS) rc = cusync_attn_run_dependent(b->attn[0], stream);
+  if (rc == CUSYNC_SUCCESS) rc = cusync_gemm_run_dependent(b->proj[0], stream);
+  if (rc != CUSYNC_SUCCESS) return rc;
+  if (!b->order.end(stream)) { (void)cudaGetLastError(); rc = CUSYNC_ERROR_CUDA; }
+  for (int i = 0; i < 3; i++) cusync_stage_increment_iter(b->stages[i]);
+  return rc;
+}
+
 // ---- prompt phase: the reference's four-GEMM chain ---------------------------------------------------------
 // attention.cu:272-276 for seqlen = 0 and a batch of 512 to 2048 prompt tokens: XQKV = X Wqkv; S = Q K^T;
 // O = S V; Y = O Wo, with Q, K, V the three thirds of XQKV's columns and no softmax (the reference has none,
@@ -295,6 +308,18 @@ int cusync_attn_prompt_run_cusync(cusync_attn_prompt_t* b, const cusync_stream_t
   }
   if (rc != CUSYNC_SUCCESS) return rc;
   if (!b->order.end(streams[3])) { (void)cudaGetLastError(); rc = CUSYNC_ERROR_CUDA; }
+  for (int i = 0; i < 4; i++) cusync_stage_increment_iter(b->stages[i]);
+  return rc;
+}
+
+int cusync_attn_prompt_run_dependent(cusync_attn_prompt_t* b, cusync_stream_t stream) {
+  if (!b) return CUSYNC_ERROR_NOT_INITIALIZED;
+  if (!b->order.begin(stream)) { (void)cudaGetLastError(); return CUSYNC_ERROR_CUDA; }
+  int rc = CUSYNC_SUCCESS;
+  for (int i = 0; i < 4 && rc == CUSYNC_SUCCESS; i++)
+    rc = i == 0 ? cusync_gemm_run(b->gemm[0][i], stream) : cusync_gemm_run_dependent(b->gemm[0][i], stream);
+  if (rc != CUSYNC_SUCCESS) return rc;
+  if (!b->order.end(stream)) { (void)cudaGetLastError(); rc = CUSYNC_ERROR_CUDA; }
   for (int i = 0; i < 4; i++) cusync_stage_increment_iter(b->stages[i]);
   return rc;
 }

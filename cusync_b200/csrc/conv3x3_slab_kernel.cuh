@@ -83,6 +83,7 @@ cusync_conv3x3_slab_kernel(const __grid_constant__ CUtensorMap tmX, const __grid
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
+  cusync::allowDependentLaunch();      // this block is resident: a dependent consumer may be launched
 
   if (warp == 0) {
     // =====================================================================

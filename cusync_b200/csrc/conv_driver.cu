@@ -142,7 +142,12 @@ int cusync_conv_chain_run_stream_ordered(cusync_conv_chain_t* c, cusync_stream_t
 int cusync_conv_chain_run_cusync(cusync_conv_chain_t* c, const cusync_stream_t* streams) {
   if (!c || !streams) return CUSYNC_ERROR_NOT_INITIALIZED;
   int rc = CUSYNC_SUCCESS;
-  if (!c->order.begin(streams[0])) { (void)cudaGetLastError(); return CUSYNC_ERROR_CUDA; }
+  // Every stream waits for the previous run, not only the first: without wait kernels a dependent convolution
+  // would otherwise start while the previous run (which may have gone to other streams: run_dependent) still
+  // draws tiles from the same stage.
+  for (int i = 0; i < c->num; i++)
+    if (i == 0 || streams[i] != streams[0])
+      if (!c->order.begin(streams[i])) { (void)cudaGetLastError(); return CUSYNC_ERROR_CUDA; }
   for (int i = 0; i < c->num && rc == CUSYNC_SUCCESS; i++) {
     // a dependent convolution is launched only once every block of its producer is resident
     if (i > 0 && c->wait_kernels) rc = cusync_stage_invoke_wait_kernel(c->stages[i - 1], streams[i]);
@@ -150,6 +155,20 @@ int cusync_conv_chain_run_cusync(cusync_conv_chain_t* c, const cusync_stream_t* 
   }
   if (rc != CUSYNC_SUCCESS) return rc;
   if (!c->order.end(streams[c->num - 1])) { (void)cudaGetLastError(); rc = CUSYNC_ERROR_CUDA; }
+  for (int i = 0; i < c->num; i++) cusync_stage_increment_iter(c->stages[i]);
+  return rc;
+}
+
+int cusync_conv_chain_run_dependent(cusync_conv_chain_t* c, cusync_stream_t stream) {
+  if (!c) return CUSYNC_ERROR_NOT_INITIALIZED;
+  // One stream: convolution i + 1 is launched as a programmatic dependent of convolution i, so it becomes
+  // resident once every block of convolution i is, and waits for its tiles through the semaphores.
+  int rc = CUSYNC_SUCCESS;
+  if (!c->order.begin(stream)) { (void)cudaGetLastError(); return CUSYNC_ERROR_CUDA; }
+  for (int i = 0; i < c->num && rc == CUSYNC_SUCCESS; i++)
+    rc = i == 0 ? cusync_conv2d_run(c->sync[i], stream) : cusync_conv2d_run_dependent(c->sync[i], stream);
+  if (rc != CUSYNC_SUCCESS) return rc;
+  if (!c->order.end(stream)) { (void)cudaGetLastError(); rc = CUSYNC_ERROR_CUDA; }
   for (int i = 0; i < c->num; i++) cusync_stage_increment_iter(c->stages[i]);
   return rc;
 }

@@ -57,6 +57,7 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
+  cusync::allowDependentLaunch();      // this block is resident: a dependent consumer may be launched
 
   if (warp == 0) {
     // =====================================================================

@@ -195,6 +195,7 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap* mA0, const C
   cluster_sync_all();            // the peer's barriers are initialised before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
+  cusync::allowDependentLaunch();      // this pair is resident: a dependent consumer may be launched
 
   // Cluster addresses of the leader's barriers that the peer signals.
   const uint32_t leader_full0 = map_to_cta(smem_u32(&bars->full[0]), 0);

@@ -734,7 +734,23 @@ int cusync_gemm_plan_set_trace(cusync_gemm_plan_t* pl, void* device_buffer, uint
   return CUSYNC_SUCCESS;
 }
 
-int cusync_gemm_run(cusync_gemm_plan_t* pl, cusync_stream_t stream) {
+namespace {
+int gemm_launch(cusync_gemm_plan_t* pl, cusync_stream_t stream, bool dependent);
+}
+
+int cusync_gemm_run(cusync_gemm_plan_t* pl, cusync_stream_t stream) { return gemm_launch(pl, stream, false); }
+
+int cusync_gemm_run_dependent(cusync_gemm_plan_t* pl, cusync_stream_t stream) {
+  if (!pl) return CUSYNC_ERROR_NOT_INITIALIZED;
+  // Only a consumer may start before the kernel ahead of it has finished: its semaphore waits order the reads.
+  cusync_stage_view_t v;
+  cusync_stage_get_view(pl->stage, &v);
+  if (v.in_policy.kind == CUSYNC_POLICY_NOSYNC && pl->desc.b_stage == nullptr) return CUSYNC_ERROR_NOT_CONSUMER;
+  return gemm_launch(pl, stream, true);
+}
+
+namespace {
+int gemm_launch(cusync_gemm_plan_t* pl, cusync_stream_t stream, bool dependent) {
   if (!pl) return CUSYNC_ERROR_NOT_INITIALIZED;
   GemmParams p = pl->params;
   cusync_stage_get_view(pl->stage, &p.stage);   // picks up the current iter
@@ -752,17 +768,31 @@ int cusync_gemm_run(cusync_gemm_plan_t* pl, cusync_stream_t stream) {
     p.b_sems = bv.sems_post;
     p.b_sem_first = pl->desc.b_sem_first; p.b_sem_stride = pl->desc.b_sem_stride; p.b_sem_value = pl->desc.b_sem_value;
   }
+  const cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dependent) {
+    cudaError_t e;
+    if (pl->conv_slab)
+      e = launchDependent(cusync_conv3x3_slab_kernel, dim3(pl->num_ctas), dim3(kThreads), kSlabSmemBytes, st,
+                          pl->tmA, pl->tmB, p);
+    else if (pl->pair)
+      e = launchDependent(cusync_gemm_pair_kernel, dim3(pl->num_ctas), dim3(kThreads), pl->kernel.smem, st,
+                          pl->tmA, pl->tmB, pl->tmD, pl->tmWS, pl->tmB2, p);
+    else
+      e = launchDependent(pl->kernel.fn, dim3(pl->num_ctas), dim3(kThreads), pl->kernel.smem, st,
+                          pl->tmA, pl->tmB, pl->tmB2, pl->tmD, pl->tmWS, p);
+    if (e != cudaSuccess) { (void)cudaGetLastError(); return CUSYNC_ERROR_CUDA; }
+    return CUSYNC_SUCCESS;
+  }
   if (pl->conv_slab)
-    cusync_conv3x3_slab_kernel<<<pl->num_ctas, kThreads, kSlabSmemBytes, reinterpret_cast<cudaStream_t>(stream)>>>(
-        pl->tmA, pl->tmB, p);
+    cusync_conv3x3_slab_kernel<<<pl->num_ctas, kThreads, kSlabSmemBytes, st>>>(pl->tmA, pl->tmB, p);
   else if (pl->pair)
-    cusync_gemm_pair_kernel<<<pl->num_ctas, kThreads, pl->kernel.smem, reinterpret_cast<cudaStream_t>(stream)>>>(
+    cusync_gemm_pair_kernel<<<pl->num_ctas, kThreads, pl->kernel.smem, st>>>(
         pl->tmA, pl->tmB, pl->tmD, pl->tmWS, pl->tmB2, p);
   else
-    pl->kernel.fn<<<pl->num_ctas, kThreads, pl->kernel.smem, reinterpret_cast<cudaStream_t>(stream)>>>(
-        pl->tmA, pl->tmB, pl->tmB2, pl->tmD, pl->tmWS, p);
+    pl->kernel.fn<<<pl->num_ctas, kThreads, pl->kernel.smem, st>>>(pl->tmA, pl->tmB, pl->tmB2, pl->tmD, pl->tmWS, p);
   return cudaGetLastError() == cudaSuccess ? CUSYNC_SUCCESS : CUSYNC_ERROR_CUDA;
 }
+}  // namespace
 
 // Two dependent GEMMs in one persistent grid (both on the CTA-pair kernel).
 int cusync_gemm_chain_supported(const cusync_gemm_plan_t* first, const cusync_gemm_plan_t* second) {
@@ -945,6 +975,9 @@ int cusync_conv2d_plan_create(cusync_conv2d_plan_t** out, const cusync_conv2d_de
 
 int cusync_conv2d_plan_destroy(cusync_conv2d_plan_t* pl) { return cusync_gemm_plan_destroy(pl); }
 int cusync_conv2d_run(cusync_conv2d_plan_t* pl, cusync_stream_t stream) { return cusync_gemm_run(pl, stream); }
+int cusync_conv2d_run_dependent(cusync_conv2d_plan_t* pl, cusync_stream_t stream) {
+  return cusync_gemm_run_dependent(pl, stream);
+}
 uint32_t cusync_conv2d_plan_num_ctas(const cusync_conv2d_plan_t* pl) { return pl ? pl->num_ctas : 0; }
 
 }  // extern "C"

@@ -311,6 +311,21 @@ int run_cusync_impl(cusync_mlp_t* m, cusync_allreduce_plan_t* reducer, cusync_st
 }
 }  // namespace
 
+int cusync_mlp_run_dependent(cusync_mlp_t* m, cusync_stream_t stream) {
+  if (!m) return CUSYNC_ERROR_NOT_INITIALIZED;
+  // One stream: the second GEMM is a programmatic dependent of the first, resident as soon as every block of the
+  // first is, and ordered against its writes by the semaphores.  No second stream, wait kernel or event.
+  if (!m->order.begin(stream)) { (void)cudaGetLastError(); return CUSYNC_ERROR_CUDA; }
+  int rc = cusync_gemm_run(m->sync1, stream);
+  if (rc == CUSYNC_SUCCESS) rc = cusync_gemm_run_dependent(m->sync2, stream);
+  if (rc != CUSYNC_SUCCESS) return rc;
+  if (!m->order.end(stream)) { (void)cudaGetLastError(); rc = CUSYNC_ERROR_CUDA; }
+  if (m->input) cusync_stage_increment_iter(m->input);
+  cusync_stage_increment_iter(m->prod);
+  cusync_stage_increment_iter(m->cons);
+  return rc;
+}
+
 int cusync_mlp_update_io(cusync_mlp_t* m, const void* x, void* y) {
   if (!m) return CUSYNC_ERROR_NOT_INITIALIZED;
   int rc = CUSYNC_SUCCESS;

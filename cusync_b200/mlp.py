@@ -66,6 +66,10 @@ class MLPShard:
         L.check(L.lib().cusync_mlp_run_cusync(self._h, _stream_ptr(producer_stream), _stream_ptr(consumer_stream)),
                 "run_cusync")
 
+    def run_dependent(self, stream):
+        """The two synchronised GEMMs on one stream, the second a programmatic dependent launch of the first."""
+        L.check(L.lib().cusync_mlp_run_dependent(self._h, _stream_ptr(stream)), "run_dependent")
+
     def run_cusync_allreduce(self, reducer, producer_stream, consumer_stream, reduce_stream):
         """One layer with its all-reduce overlapped (post_rows=True): `reducer` is a tp.RowAllReduce over self.y."""
         L.check(L.lib().cusync_mlp_run_cusync_allreduce(self._h, reducer._plan, _stream_ptr(producer_stream),

@@ -43,6 +43,13 @@ CUSYNC_DEVICE void storeRelease(uint32_t* addr, uint32_t value) {
   asm volatile("st.release.gpu.global.u32 [%0], %1;" :: "l"(addr), "r"(value) : "memory");
 }
 
+// Tells the device that kernels launched behind this one as programmatic dependents (the launch attribute
+// "programmatic stream serialization") may start: they do once every block of this grid has said so or has
+// exited, which is to say once every block of this grid is resident or done.  That is the guarantee the
+// reference's wait kernel gives a consumer (cusync_device_defs.h:78-83, waitKernel), given by the launch
+// hardware instead of a polling kernel.  Without such a dependent behind the grid it does nothing.
+CUSYNC_DEVICE void allowDependentLaunch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 CUSYNC_DEVICE uint64_t globalTimerNs() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));

@@ -277,6 +277,16 @@ CUSYNC_API int cusync_gemm_plan_update(cusync_gemm_plan_t* plan, const void* a, 
                             const void* b2, void* d);
 /* run(bool overlap, int*, cudaStream_t) (gemm/device/cusyncgemm.h:525-563). */
 CUSYNC_API int cusync_gemm_run(cusync_gemm_plan_t* plan, cusync_stream_t stream);
+/* The same launch as a programmatic dependent of the kernel ahead of it in `stream` (launch attribute
+ * "programmatic stream serialization"): the GEMM becomes resident as soon as EVERY block of that kernel is resident
+ * or done, not when it has finished, and is ordered against its producer's writes by its semaphore waits alone.
+ * This is what the reference obtains with a second stream and CuStage::invokeWaitKernel (cusync.h:277-283,
+ * waitKernel in cusync_device_defs.h:78-83) - the consumer must not take the SMs before the producer's blocks
+ * have them - done by the launch hardware: one stream, no polling kernel, no events, and the consumer's launch
+ * latency and prologue run under the producer.  The plan must be a consumer (an input policy, or b_stage), else
+ * CUSYNC_ERROR_NOT_CONSUMER; the kernel ahead must be one of this library's GEMM, convolution or attention
+ * kernels (they release their dependents as soon as they run; behind any other kernel the launch is stream-ordered). */
+CUSYNC_API int cusync_gemm_run_dependent(cusync_gemm_plan_t* plan, cusync_stream_t stream);
 /* Two dependent GEMMs launched as ONE persistent grid: the blocks draw the work units of `first`, then those of
  * `second`, from one ticket counter, so a block that finds no unit of the first GEMM left goes straight on to
  * units of the second (whose waits on the first's semaphores are the usual ones) instead of idling until a second
@@ -376,6 +386,8 @@ CUSYNC_API int cusync_conv2d_plan_create(cusync_conv2d_plan_t** out, const cusyn
 CUSYNC_API int cusync_conv2d_plan_destroy(cusync_conv2d_plan_t* plan);
 /* run(stream) (conv/device/cusyncimplicit_gemm_convolution.h:283-297). */
 CUSYNC_API int cusync_conv2d_run(cusync_conv2d_plan_t* plan, cusync_stream_t stream);
+/* As cusync_gemm_run_dependent: the convolution starts once every block of the kernel ahead of it is resident. */
+CUSYNC_API int cusync_conv2d_run_dependent(cusync_conv2d_plan_t* plan, cusync_stream_t stream);
 CUSYNC_API uint32_t cusync_conv2d_plan_num_ctas(const cusync_conv2d_plan_t* plan);
 
 /* A chain of 3x3 convolutions with equal channel counts, the workload of
@@ -404,6 +416,10 @@ CUSYNC_API int cusync_conv_chain_run_stream_ordered(cusync_conv_chain_t* chain, 
 /* runCuSync, one iteration: convolution i on streams[i], each dependent one behind a wait kernel unless all
  * stages fit on the device at once, then incrementIter on every stage (resnet.cu:560-590).  streams: [num_convs]. */
 CUSYNC_API int cusync_conv_chain_run_cusync(cusync_conv_chain_t* chain, const cusync_stream_t* streams);
+/* The same iteration on ONE stream: every dependent convolution is launched with cusync_conv2d_run_dependent, so
+ * it becomes resident once all blocks of the convolution ahead of it are, with no wait kernel, stream or event
+ * between them.  Same stages, semaphore counts and results as run_cusync. */
+CUSYNC_API int cusync_conv_chain_run_dependent(cusync_conv_chain_t* chain, cusync_stream_t stream);
 /* The same work in a form that can be recorded once and replayed (a CUDA graph captured on streams[0]; no
  * counterpart in the reference): resets every stage (semaphores zero, iteration 1) on streams[0], makes the other
  * streams wait for the resets, then launches as run_cusync does, without incrementIter.  The caller joins
@@ -441,6 +457,8 @@ CUSYNC_API int cusync_attn_plan_create(cusync_attn_plan_t** out, const cusync_at
 CUSYNC_API int cusync_attn_plan_destroy(cusync_attn_plan_t* plan);
 CUSYNC_API int cusync_attn_plan_splits(const cusync_attn_plan_t* plan);
 CUSYNC_API int cusync_attn_run(cusync_attn_plan_t* plan, cusync_stream_t stream);
+/* As cusync_gemm_run_dependent: the attention kernel starts once every block of the kernel ahead of it is resident. */
+CUSYNC_API int cusync_attn_run_dependent(cusync_attn_plan_t* plan, cusync_stream_t stream);
 
 /* The whole attention block of one tensor-parallel shard, the workload of src/ml-bench/transformer/attention.cu:
  * qkv = x * w_qkv; attn_out = attention(qkv, caches); y = attn_out * w_o.  x[batch, hidden], w_qkv[hidden, 3 * heads
@@ -465,6 +483,9 @@ CUSYNC_API int cusync_attn_block_run_stream_ordered(cusync_attn_block_t* block, 
 /* runAttentionCuSync, one iteration (attention.cu:792-833): stage i on streams[i], a wait kernel before each
  * dependent stage, incrementIter on all three afterwards.  streams: [3]. */
 CUSYNC_API int cusync_attn_block_run_cusync(cusync_attn_block_t* block, const cusync_stream_t* streams);
+/* The same on ONE stream, each dependent stage launched as a programmatic dependent of the stage ahead of it
+ * (cusync_gemm_run_dependent, cusync_attn_run_dependent). */
+CUSYNC_API int cusync_attn_block_run_dependent(cusync_attn_block_t* block, cusync_stream_t stream);
 /* Stage handles (0 = QKV projection, 1 = attention, 2 = output projection) for inspection. */
 CUSYNC_API cusync_stage_t* cusync_attn_block_stage(cusync_attn_block_t* block, int which);
 /* Configuration in use: out[0..4] = tile_n of the two GEMMs, their K slices, key-range splits of the attention. */
@@ -496,6 +517,8 @@ CUSYNC_API int cusync_attn_prompt_destroy(cusync_attn_prompt_t* block);
 CUSYNC_API int cusync_attn_prompt_run_stream_ordered(cusync_attn_prompt_t* block, cusync_stream_t stream);
 /* runAttentionCuSync, one iteration (attention.cu:706-833).  streams: [4]. */
 CUSYNC_API int cusync_attn_prompt_run_cusync(cusync_attn_prompt_t* block, const cusync_stream_t* streams);
+/* The same on ONE stream, GEMMs 2 to 4 launched with cusync_gemm_run_dependent. */
+CUSYNC_API int cusync_attn_prompt_run_dependent(cusync_attn_prompt_t* block, cusync_stream_t stream);
 /* Stage handles (0 = XQKV, 1 = S, 2 = O, 3 = Y) for inspection. */
 CUSYNC_API cusync_stage_t* cusync_attn_prompt_stage(cusync_attn_prompt_t* block, int which);
 
@@ -553,6 +576,10 @@ CUSYNC_API int cusync_mlp_run_stream_ordered(cusync_mlp_t* mlp, cusync_stream_t 
  * incrementIter on both stages (mlp.cu:691-712). */
 CUSYNC_API int cusync_mlp_run_cusync(cusync_mlp_t* mlp, cusync_stream_t producer_stream,
                                      cusync_stream_t consumer_stream);
+/* The same two synchronised launches on ONE stream, the consumer GEMM as a programmatic dependent of the producer
+ * (cusync_gemm_run_dependent) in place of the second stream and the wait kernel.  Never the one-grid form; same
+ * stages, semaphore counts and results as run_cusync. */
+CUSYNC_API int cusync_mlp_run_dependent(cusync_mlp_t* mlp, cusync_stream_t stream);
 /* One of the two un-synchronised kernels alone (1 = first GEMM, 2 = second), for per-kernel timing
  * (the reference's baseline prints both, mlp.cu:463-488). */
 CUSYNC_API int cusync_mlp_run_single(cusync_mlp_t* mlp, int which, cusync_stream_t stream);
