@@ -709,7 +709,7 @@ def main():
                 row[pol + "_us"] = round(c_us, 2)
                 row[pol + "_stream_ordered_us"] = round(o_us, 2)
                 row[pol + "_gain_pct"] = round(100.0 - c_us / o_us * 100.0, 2)
-                if pol == "rowsync":
+                if pol == "rowsync" and not s.single_grid:
                     # the two synchronised launches on ONE stream, the consumer a programmatic dependent launch
                     d_per, o2_per = interleaved(lambda s=s: s.run_dependent(cs), (cs, cs), o_step, (cs, cs), 20, 5)
                     row["rowsync_dependent_launch_us"] = round(statistics.median(d_per) * 1000, 2)
@@ -724,9 +724,14 @@ def main():
                     # the reference-shaped form of the same layer: one launch per GEMM and a wait kernel
                     x2 = s.x; s.destroy()
                     s = M.MLPShard("gpt3", b, x2, s.w1, s.w2, None, policy=pol, single_grid=1)
-                    c_per, o_per = interleaved(lambda s=s: s.run_cusync(ps, cs), (ps, cs),
-                                               lambda s=s: s.run_stream_ordered(cs), (cs, cs), 20, 5)
+                    c_per, o_per, d_per = interleaved_arms([(lambda s=s: s.run_cusync(ps, cs), (ps, cs)),
+                                                            (lambda s=s: s.run_stream_ordered(cs), (cs, cs)),
+                                                            (lambda s=s: s.run_dependent(cs), (cs, cs))], 20, 5)
+                    o2 = statistics.median(o_per)
                     row["rowsync_two_launches_us"] = round(statistics.median(c_per) * 1000, 2)
+                    row["rowsync_two_launches_gain_pct"] = round(100.0 - statistics.median(c_per) / o2 * 100.0, 2)
+                    row["rowsync_dependent_launch_us"] = round(statistics.median(d_per) * 1000, 2)
+                    row["rowsync_dependent_launch_gain_pct"] = round(100.0 - statistics.median(d_per) / o2 * 100.0, 2)
                 s.destroy()
             # context only, as in the reference's tables (their "torch" column): the same layer through the vendor
             # library, y = gelu(x @ w1) @ w2 on one stream (cuBLAS GEMMs + an elementwise kernel), timed alike

@@ -101,6 +101,13 @@ class Conv2dFprop {
     return rc == CUSYNC_SUCCESS ? Status::kSuccess : Status::kErrorInternal;
   }
   Status operator()(cudaStream_t stream = nullptr) { return run(stream); }
+  // The launch as a programmatic dependent of the producer kernel ahead of it in `stream` (consumers only).
+  Status runDependent(cudaStream_t stream = nullptr) {
+    if (plan_ == nullptr) return Status::kErrorInternal;
+    if (params_.custage.handle()) cusync_stage_set_iter(params_.custage.handle(), params_.custage.currentIter());
+    int rc = cusync_conv2d_run_dependent(plan_, reinterpret_cast<cusync_stream_t>(stream));
+    return rc == CUSYNC_SUCCESS ? Status::kSuccess : Status::kErrorInternal;
+  }
 
   uint32_t numCtas() const { return cusync_conv2d_plan_num_ctas(plan_); }
   void destroy() { if (plan_) { cusync_conv2d_plan_destroy(plan_); plan_ = nullptr; } }

@@ -134,6 +134,14 @@ class Gemm {
     return run(stream);
   }
   Status operator()(cudaStream_t stream = nullptr) { return run(stream); }
+  // The launch as a programmatic dependent of the producer kernel ahead of it in `stream`: in place of
+  // prod.invokeWaitKernel(consumer_stream) and a second stream.  Consumers only.
+  Status runDependent(cudaStream_t stream = nullptr) {
+    if (plan_ == nullptr) return Status::kErrorInternal;
+    if (params_.custage.handle()) cusync_stage_set_iter(params_.custage.handle(), params_.custage.currentIter());
+    int rc = cusync_gemm_run_dependent(plan_, reinterpret_cast<cusync_stream_t>(stream));
+    return rc == CUSYNC_SUCCESS ? Status::kSuccess : Status::kErrorInternal;
+  }
 
   uint32_t numCtas() const { return cusync_gemm_plan_num_ctas(plan_); }
   void destroy() { if (plan_) { cusync_gemm_plan_destroy(plan_); plan_ = nullptr; } }
