@@ -150,7 +150,7 @@ cusync_conv3x3_slab_kernel(const __grid_constant__ CUtensorMap tmX, const __grid
           ready[j] = j < static_cast<int>(group) && base + j < num_tiles && v[j][0] >= wait_target &&
                      v[j][1] >= wait_target && v[j][2] >= wait_target;
         cusync::fenceAcqRel();
-        fence_proxy_async();     // acquire (generic proxy) before the TMA reads (async proxy)
+        fence_proxy_async_global();     // acquire (generic proxy) before the TMA reads (async proxy)
       };
 
       // Pipeline: group 0 is being loaded, group 1 has its tickets (schedule entries and probes follow while
@@ -209,7 +209,7 @@ cusync_conv3x3_slab_kernel(const __grid_constant__ CUtensorMap tmX, const __grid
                 ok = false;
               }
             }
-            fence_proxy_async();
+            fence_proxy_async_global();
           }
           const long long lc1 = p.trace ? clock64() : 0;
           const uint32_t slot = sched_it % kSchedSlots, sph = (sched_it / kSchedSlots) & 1u;

@@ -156,58 +156,110 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
               const uint32_t k_sync = sync_stride ? static_cast<uint32_t>(k_off) / sync_stride * sync_stride
                                                   : static_cast<uint32_t>(k_off);
               uint32_t seen = 0;
-              // Probe first: the tile's own semaphore and the next producer tiles along K are read with
-              // independent relaxed loads (one memory round trip for all of them); only if the tile's own is
-              // not there yet does the thread go on to wait for it.  How far the finished prefix reaches is
-              // remembered, so later K-blocks skip the wait.  One fence makes the relaxed loads acquiring.
-              uint32_t vals[kLookahead];
-              uint32_t v_first = 0;
-              if (sync_stride) {
-                // TileSync / Conv2DTileSync number the producer tiles of a row with a constant step along K
-                // (both orders are affine in the column), so one more evaluation gives every later index
-                // without its integer divisions; the wrapping policies are evaluated one by one.
-                const bool affine = st.in_policy.kind == CUSYNC_POLICY_TILESYNC ||
-                                    st.in_policy.kind == CUSYNC_POLICY_CONV2DTILESYNC;
-                uint32_t step = 0;
-                if (affine && k_sync + sync_stride < static_cast<uint32_t>(p.k))
-                  step = cusync::eval::tileIndex(st.in_policy, static_cast<uint32_t>(m_off),
-                                                 k_sync + sync_stride, st.prod_grid.x,
-                                                 st.prod_grid.y) - idx;
-                v_first = cusync::loadRelaxed(st.sems_wait + idx);
-#pragma unroll
-                for (int j = 0; j < kLookahead; j++) {
-                  const uint32_t kk = k_sync + (j + 1) * sync_stride;
-                  vals[j] = kk < static_cast<uint32_t>(p.k)
-                                ? cusync::loadRelaxed(st.sems_wait + (affine ? idx + (j + 1) * step
-                                      : cusync::eval::tileIndex(st.in_policy, static_cast<uint32_t>(m_off), kk,
-                                                                st.prod_grid.x, st.prod_grid.y)))
-                                : 0u;
-                }
-              }
-              const bool probed_ready = sync_stride != 0 && v_first >= wait_target;
-              // Convolution: the tile's own semaphore and those of its two halo neighbours are probed
-              // together first (one memory round trip instead of three); only what is still missing is
-              // then waited for.
-              bool conv_all_ready = false;
+              bool wait_ok = true;
               if (CONV) {
+                // A 3x3 stencil reads, besides the tile's own producer tile, the image rows just above and below
+                // it: they belong to the neighbouring producer tiles of the same image, which the reference's
+                // policy does not wait for (it relies on tile order).  All three are needed at EVERY channel
+                // chunk of the K walk.  One probe covers this chunk and the ones after it: the three rows'
+                // semaphores of up to kConvProbe chunks are read with independent relaxed loads (one memory round
+                // trip for all), one fence makes them acquiring, and ready_end remembers how far all three rows
+                // were finished, so the later chunks of the tile pass without touching memory.
+                constexpr int kConvProbe = 8;
                 const int tin = static_cast<int>(t.y) % p.conv_tiles_per_image;
                 const int span = p.conv_rows * p.conv_w;
-                const uint32_t i_up = tin > 0 ? cusync::eval::tileIndex(st.in_policy, static_cast<uint32_t>(m_off - span),
-                                                    static_cast<uint32_t>(k_off), st.prod_grid.x, st.prod_grid.y) : idx;
-                const uint32_t i_dn = tin + 1 < p.conv_tiles_per_image
-                                          ? cusync::eval::tileIndex(st.in_policy, static_cast<uint32_t>(m_off + span),
-                                                static_cast<uint32_t>(k_off), st.prod_grid.x, st.prod_grid.y) : idx;
-                const uint32_t v0 = cusync::loadRelaxed(st.sems_wait + idx);
-                const uint32_t v1 = cusync::loadRelaxed(st.sems_wait + i_up);
-                const uint32_t v2 = cusync::loadRelaxed(st.sems_wait + i_dn);
-                conv_all_ready = v0 >= wait_target && v1 >= wait_target && v2 >= wait_target;
-                if (conv_all_ready) __threadfence();
+                const bool has_up = tin > 0, has_dn = tin + 1 < p.conv_tiles_per_image;
+                const uint32_t i_up = has_up ? cusync::eval::tileIndex(st.in_policy, static_cast<uint32_t>(m_off - span),
+                                                   static_cast<uint32_t>(k_off), st.prod_grid.x, st.prod_grid.y) : idx;
+                const uint32_t i_dn = has_dn ? cusync::eval::tileIndex(st.in_policy, static_cast<uint32_t>(m_off + span),
+                                                   static_cast<uint32_t>(k_off), st.prod_grid.x, st.prod_grid.y) : idx;
+                // the tile orders are affine in the column: one more evaluation per row gives its step along K
+                uint32_t step = 0, step_up = 0, step_dn = 0;
+                if (k_sync + sync_stride < static_cast<uint32_t>(p.k)) {
+                  const uint32_t kn = k_sync + sync_stride;
+                  step = cusync::eval::tileIndex(st.in_policy, static_cast<uint32_t>(m_off), kn, st.prod_grid.x,
+                                                 st.prod_grid.y) - idx;
+                  step_up = has_up ? cusync::eval::tileIndex(st.in_policy, static_cast<uint32_t>(m_off - span), kn,
+                                                             st.prod_grid.x, st.prod_grid.y) - i_up : step;
+                  step_dn = has_dn ? cusync::eval::tileIndex(st.in_policy, static_cast<uint32_t>(m_off + span), kn,
+                                                             st.prod_grid.x, st.prod_grid.y) - i_dn : step;
+                }
+                uint32_t v[kConvProbe][3];
+#pragma unroll
+                for (int j = 0; j < kConvProbe; j++) {
+                  const bool in = k_sync + static_cast<uint32_t>(j) * sync_stride < static_cast<uint32_t>(p.k);
+                  v[j][0] = in ? cusync::loadRelaxed(st.sems_wait + idx + j * step) : 0u;
+                  v[j][1] = in ? cusync::loadRelaxed(st.sems_wait + i_up + j * step_up) : 0u;
+                  v[j][2] = in ? cusync::loadRelaxed(st.sems_wait + i_dn + j * step_dn) : 0u;
+                }
+                uint32_t chunks_ready = 0;
+#pragma unroll
+                for (int j = 0; j < kConvProbe; j++) {
+                  if (chunks_ready == static_cast<uint32_t>(j) && v[j][0] >= wait_target && v[j][1] >= wait_target &&
+                      v[j][2] >= wait_target)
+                    chunks_ready++;
+                }
+                if (chunks_ready == 0) {
+                  // this chunk is not there yet: wait (bounded) for the tile itself and its two neighbours
+                  const uint32_t need[3] = {idx, i_up, i_dn};
+                  for (int e = 0; e < 3 && wait_ok; e++) {
+                    if (!cusync::spinUntilAtLeast(st.sems_wait + need[e], wait_target, st.timeout_ns, &seen)) {
+                      cusync::recordTimeout(st.status, 1u, static_cast<uint32_t>(m_off), static_cast<uint32_t>(k_off),
+                                            e == 0 ? tz : 2u, need[e], seen, wait_target);
+                      wait_ok = false;
+                    }
+                  }
+                  chunks_ready = 1;
+                } else {
+                  cusync::fenceAcqRel();
+                }
+                ready_end = k_sync + chunks_ready * sync_stride;
+              } else {
+                // Probe first: the tile's own semaphore and the next producer tiles along K are read with
+                // independent relaxed loads (one memory round trip for all of them); only if the tile's own is
+                // not there yet does the thread go on to wait for it.  How far the finished prefix reaches is
+                // remembered, so later K-blocks skip the wait.  One fence makes the relaxed loads acquiring.
+                uint32_t vals[kLookahead];
+                uint32_t v_first = 0;
+                if (sync_stride) {
+                  // TileSync numbers the producer tiles of a row with a constant step along K (the orders are
+                  // affine in the column), so one more evaluation gives every later index without its integer
+                  // divisions; the wrapping policies are evaluated one by one.
+                  const bool affine = st.in_policy.kind == CUSYNC_POLICY_TILESYNC;
+                  uint32_t step = 0;
+                  if (affine && k_sync + sync_stride < static_cast<uint32_t>(p.k))
+                    step = cusync::eval::tileIndex(st.in_policy, static_cast<uint32_t>(m_off),
+                                                   k_sync + sync_stride, st.prod_grid.x,
+                                                   st.prod_grid.y) - idx;
+                  v_first = cusync::loadRelaxed(st.sems_wait + idx);
+#pragma unroll
+                  for (int j = 0; j < kLookahead; j++) {
+                    const uint32_t kk = k_sync + (j + 1) * sync_stride;
+                    vals[j] = kk < static_cast<uint32_t>(p.k)
+                                  ? cusync::loadRelaxed(st.sems_wait + (affine ? idx + (j + 1) * step
+                                        : cusync::eval::tileIndex(st.in_policy, static_cast<uint32_t>(m_off), kk,
+                                                                  st.prod_grid.x, st.prod_grid.y)))
+                                  : 0u;
+                  }
+                }
+                const bool probed_ready = sync_stride != 0 && v_first >= wait_target;
+                if (!probed_ready && !cusync::spinUntilAtLeast(st.sems_wait + idx, wait_target, st.timeout_ns, &seen)) {
+                  cusync::recordTimeout(st.status, 1u, static_cast<uint32_t>(m_off), static_cast<uint32_t>(k_off), tz,
+                                        idx, seen, wait_target);
+                  wait_ok = false;
+                }
+                if (wait_ok && sync_stride) {
+                  uint32_t ahead = 0;
+#pragma unroll
+                  for (int j = 0; j < kLookahead; j++) {
+                    if (ahead == static_cast<uint32_t>(j) && vals[j] >= wait_target) ahead++;
+                  }
+                  ready_end = k_sync + (ahead + 1) * sync_stride;
+                  if (ahead || probed_ready) cusync::fenceAcqRel();
+                }
               }
-              if (!conv_all_ready && !probed_ready &&
-                  !cusync::spinUntilAtLeast(st.sems_wait + idx, wait_target, st.timeout_ns, &seen)) {
+              if (!wait_ok) {
                 bars->abort = 1u;
-                cusync::recordTimeout(st.status, 1u, static_cast<uint32_t>(m_off), static_cast<uint32_t>(k_off), tz,
-                                      idx, seen, wait_target);
                 // The stage was armed: give it its A bytes anyway so the
                 // barrier completes and the drain below terminates.
                 if (CONV) tma_load_4d(sa, &tmA, &bars->full[s], chunk * kBlockK, tap % 3 - 1, h0 + tap / 3 - 1, img);
@@ -216,42 +268,8 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 ok = false;
                 break;
               }
-              if (sync_stride) {
-                uint32_t ahead = 0;
-#pragma unroll
-                for (int j = 0; j < kLookahead; j++) {
-                  if (ahead == static_cast<uint32_t>(j) && vals[j] >= wait_target) ahead++;
-                }
-                ready_end = k_sync + (ahead + 1) * sync_stride;
-                if (ahead || probed_ready) cusync::fenceAcqRel();
-              }
-              // A 3x3 stencil also reads the image rows just above and below the tile: they belong to
-              // the neighbouring producer tiles of the same image, which the reference's policy does
-              // not wait for (it relies on tile order); wait for them as well.
-              if (CONV && !conv_all_ready) {
-                bool halo_ok = true;
-                for (int dm = -1; dm <= 1 && halo_ok; dm += 2) {
-                  const int nb = static_cast<int>(t.y) % p.conv_tiles_per_image + dm;
-                  if (nb < 0 || nb >= p.conv_tiles_per_image) continue;
-                  const uint32_t nidx = cusync::eval::tileIndex(
-                      st.in_policy, static_cast<uint32_t>(m_off + dm * p.conv_rows * p.conv_w),
-                      static_cast<uint32_t>(k_off), st.prod_grid.x, st.prod_grid.y);
-                  if (!cusync::spinUntilAtLeast(st.sems_wait + nidx, wait_target, st.timeout_ns, &seen)) {
-                    bars->abort = 1u;
-                    cusync::recordTimeout(st.status, 1u, static_cast<uint32_t>(m_off), static_cast<uint32_t>(k_off), 2u,
-                                          nidx, seen, wait_target);
-                    halo_ok = false;
-                  }
-                }
-                if (!halo_ok) {
-                  tma_load_4d(sa, &tmA, &bars->full[s], chunk * kBlockK, tap % 3 - 1, h0 + tap / 3 - 1, img);
-                  fills++;
-                  ok = false;
-                  break;
-                }
-              }
               // Order the acquire (generic proxy) before the TMA read (async proxy).
-              fence_proxy_async();
+              fence_proxy_async_global();
             }
           }
           // Convolution: the box {64 channels, W pixels, conv_rows rows, 1 image} shifted by the tap; the

@@ -304,7 +304,7 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap* mA0, const C
               ok = false;
               break;              // nothing of this stage is armed yet
             }
-            fence_proxy_async();
+            fence_proxy_async_global();
           }
           // The leader's barrier collects the bytes of both CTAs.
           if (leader) mbar_expect_tx(&bars->full[s], 2 * C::kStageBytes);
@@ -373,7 +373,7 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap* mA0, const C
                 ready_end = k_sync + (ahead + 1) * sync_stride;
                 if (ahead || probed_ready) cusync::fenceAcqRel();
               }
-              fence_proxy_async();
+              fence_proxy_async_global();
             }
           }
           }
