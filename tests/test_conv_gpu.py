@@ -131,6 +131,54 @@ def test_config5_conv_chain_with_conv2dtilesync(n, max_ctas):
     c1.destroy(); c2.destroy(); prod.destroy(); cons.destroy()
 
 
+def test_a_consumer_tile_waits_for_its_halo_neighbours_at_every_channel_chunk():
+    # 128 channels in producer tiles of 64: two channel chunks along the consumer's K walk.  The host stands in for
+    # the producer and posts every semaphore but ONE, the second chunk of row tile 3.  The consumer tiles of rows
+    # 2, 3 and 4 all read image rows of that producer tile (own rows or halo), so all three must give up (bounded
+    # wait) without writing; the other rows complete.  A consumer that only looked at its neighbours' first chunk
+    # would write rows 2 and 4 from unfinished input.
+    import ctypes as C
+    n, h, w, c = 1, 28, 28, 128
+    x, f = _inputs(n, h, w, c, c, 77)
+    y = torch.full((n, h, w, c), float("nan"), device="cuda", dtype=torch.half)
+    prob = cs.Conv2dProblemSize(n, h, w, c, c)
+    grid, tile_m, tile_n = prob.grid(), prob.tile_m(), prob.tile_n()
+    assert grid == (2, 7, 1) and tile_m == 112 and tile_n == 64
+    prod = cs.CuStage(cs.TransposeXYOrder, grid, (1, 1, 1), cs.NoSync(), cs.TileSync(cs.TransposeXYOrder, tile_m, tile_n))
+    cons = cs.CuStage(cs.TransposeXYOrder, grid, (1, 1, 1), cs.Conv2DTileSync(cs.TransposeXYOrder, 3, 3, tile_m, tile_n),
+                      cs.NoSync())
+    assert cs.CuSync.setProducerConsumerPair(prod, cons) == L.SUCCESS
+    cons.set_timeout_ns(30e6)
+    conv = cs.Conv2dFprop()
+    assert conv.initialize(cons, prob, x, f, y, L.EPILOGUE_RELU, 0) == L.SUCCESS
+    # which semaphore the producer tile (row tile 3, chunk 1) posts: row offset 3 * tile_m, column offset tile_n
+    opol = o.policy(o.TILESYNC, o.ORDER_TRANSPOSE_XY, tile_m, tile_n, 1, 1)
+    missing = int(o.consumer_tile_waits(opol, grid, 3 * tile_m, 2 * tile_n, tile_n, 1)[0][1])
+    view = L.StageView()
+    assert L.lib().cusync_stage_get_view(prod._h, C.byref(view)) == L.SUCCESS
+    count = grid[0] * grid[1]
+    stream = torch.cuda.current_stream()
+    for i in range(count):
+        if i != missing:
+            assert L.lib().cusync_stream_write_values(C.c_void_p(view.sems_post + 4 * i), 1, 1,
+                                                      C.c_void_p(stream.cuda_stream)) == L.SUCCESS
+    assert conv.run(stream) == L.SUCCESS
+    torch.cuda.synchronize()
+    st = cons.status()
+    assert st.code == L.ERROR_TIMEOUT and st.sem_index == missing and st.expected == 1 and st.seen == 0
+    ref = o.conv2d_3x3_nhwc_f16(x.cpu().numpy(), f.cpu().numpy(), True)
+    got = y.float().cpu().numpy()
+    rows = h // 7                                   # image rows per tile
+    for t in range(7):
+        part = got[0, t * rows:(t + 1) * rows]
+        if t in (2, 3, 4):
+            assert np.isnan(part).all(), "row tile %d was written although its input was not complete" % t
+        else:
+            assert not np.isnan(part).any()
+            assert o.max_rel_err(part.astype(np.float16), ref[0, t * rows:(t + 1) * rows]) <= TOL
+    conv.destroy(); prod.destroy(); cons.destroy()
+
+
 @pytest.mark.parametrize("n,h,w,c,convs,max_ctas", [
     (1, 56, 56, 64, 2, 0),     # config 5, N = 1: both grids resident at once, no wait kernel
     (8, 56, 56, 64, 2, 0),     # config 5, N = 8: wait kernel before the consumer
