@@ -171,7 +171,7 @@ def workload_config(args, shard):
            "batch": args.batch, "policy": args.policy,
            "l2": "inputs larger than L2 (302 MB of weights per step vs 126 MB L2); no explicit flush",
            "all_reduce": (("sum of Y[B,12288] fp16 across ranks by this library's kernel beside the second GEMM "
-                           "(%d blocks; the GEMMs use the other SMs)" % args.reduce_ctas
+                           "(%d blocks; the GEMMs use the other SMs)" % (args.reduce_ctas if args.reduce_ctas > 0 else 4)
                            if getattr(args, "reduce", "overlapped") == "overlapped" and args.batch >= 1024
                            else "NCCL sum of Y[B,12288] fp16 across ranks, after the layer")
                           if args.gpus > 1 else "none (1 GPU)")}
