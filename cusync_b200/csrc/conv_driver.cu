@@ -77,19 +77,21 @@ int cusync_conv_chain_create(cusync_conv_chain_t** out, const cusync_conv_chain_
 
   int sms = cusync_b200_sm_count();
   if (sms <= 0) sms = 148;
-  // Left to choose, a chain whose stages all fit on the device at once, and a small chain of three or more
-  // convolutions (at most two tiles per SM and convolution), share the device: each synchronised convolution gets
-  // sms / num_convs persistent blocks, so that every stage is resident from the start and the chain runs as a
-  // pipeline over the semaphores, with no waits before the launches (the reference's AvoidWaitKernel case,
-  // cusync.h:61-62; measured +19 % on four convolutions of eight 56 x 56 images).  Other chains give every
-  // convolution the whole device (measured faster for two convolutions from eight images on); the next stage then
-  // becomes resident as the previous one's blocks retire.
+  // Left to choose, every synchronised convolution gets the whole device, except in chains of three or more
+  // 64-channel convolutions (the slab kernel), where each gets half of it: two adjacent stages are then resident
+  // together and run as a pipeline over the semaphores, and a stage's tiles spread over more rounds (224 tiles are
+  // 3.03 rounds of 74 blocks but 1.51, run as 2, of 148).  Measured with all streams meeting before every step,
+  // eight 56 x 56 x 64 images, four convolutions: 41 us with half the device per stage, 45.5 us with all of it,
+  // 49 us with a quarter each, against 44.4 us stream-ordered; two images 32 / 33-39 / 35-40 against 39 us.  Chains
+  // of the general kernel (128 channels and more) and chains of two convolutions measured best on the whole device.
+  // Where the blocks of all stages fit on the device at once no wait is needed before a launch (the reference's
+  // AvoidWaitKernel case, cusync.h:61-62); otherwise the next stage becomes resident as the previous one's blocks
+  // retire.
   const uint32_t tiles = grid.x * grid.y;
-  const uint32_t share = static_cast<uint32_t>(sms / d.num_convs) > 0 ? static_cast<uint32_t>(sms / d.num_convs) : 1u;
+  const bool slab = d.channels == 64;
   const uint32_t cap = d.max_ctas > 0 ? static_cast<uint32_t>(d.max_ctas)
-                                      : (tiles * d.num_convs <= static_cast<uint32_t>(sms) ||
-                                                 (d.num_convs >= 3 && tiles <= 2u * static_cast<uint32_t>(sms))
-                                             ? share : static_cast<uint32_t>(sms));
+                                      : (slab && d.num_convs >= 3 ? static_cast<uint32_t>(sms > 1 ? sms / 2 : 1)
+                                                                  : static_cast<uint32_t>(sms));
   const uint32_t blocks = tiles < cap ? tiles : cap;
   c->sync_ctas = static_cast<int>(cap);
   c->wait_kernels = static_cast<uint64_t>(blocks) * d.num_convs > static_cast<uint64_t>(sms);

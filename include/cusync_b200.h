@@ -399,8 +399,9 @@ typedef struct cusync_conv_chain_desc {
   int32_t num_convs;               /* 2..8 */
   int32_t n, h, w, channels;
   int32_t relu;
-  int32_t max_ctas;                /* blocks per convolution; 0 = choose: the synchronised convolutions of a small
-                                      chain share the SMs equally (all stages resident at once), otherwise one per SM */
+  int32_t max_ctas;                /* blocks per convolution; 0 = choose: one per SM, or one per two SMs for each
+                                      synchronised convolution of a chain of three or more 64-channel convolutions
+                                      (two adjacent stages resident together) */
   const void* const* filters;      /* [num_convs] pointers to [channels, 3, 3, channels] */
   void* const* activations;        /* [num_convs + 1] pointers to [n, h, w, channels] */
 } cusync_conv_chain_desc_t;

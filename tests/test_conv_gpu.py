@@ -201,8 +201,8 @@ def test_conv_chain_driver(n, h, w, c, convs, max_ctas):
     assert tile_n == {32: 128, 40: 256}.get(n, 64)
     blocks = n * (h // L.lib().cusync_conv2d_tile_rows_hw(h, w)) * (c // tile_n)
     sms = L.lib().cusync_b200_sm_count()
-    shared = blocks * convs <= sms or (convs >= 3 and blocks <= 2 * sms)
-    per_stage = min(blocks, max_ctas if max_ctas else (sms // convs if shared else sms))
+    # left to choose: half of the device per stage in chains of three or more 64-channel convolutions, else all of it
+    per_stage = min(blocks, max_ctas if max_ctas else (sms // 2 if (c == 64 and convs >= 3) else sms))
     assert chain.uses_wait_kernels == (per_stage * convs > sms)
     streams = [torch.cuda.Stream(priority=-1)] + [torch.cuda.Stream() for _ in range(convs - 1)]
     for it in range(1, 4):
