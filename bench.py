@@ -498,7 +498,7 @@ def main():
             return reduce_max(e0.elapsed_time(e1) / n * 1000.0)
 
         chain_us, layer_us = chain_vs_layer()
-        # the round-1 form for comparison: the synchronised chain on the whole device, NCCL's all-reduce after it
+        # for comparison: the synchronised chain on the whole device, NCCL's all-reduce after it
         def nccl_after_step():
             layer.base.run_cusync(ps, cs)
             with torch.cuda.stream(cs):
