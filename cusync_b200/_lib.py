@@ -52,7 +52,8 @@ class StageView(C.Structure):
                 ("in_policy", Policy), ("out_policy", Policy),
                 ("tile_order", C.c_void_p), ("tile_counter", C.c_void_p), ("started", C.c_void_p),
                 ("sems_post", C.c_void_p), ("sems_wait", C.c_void_p), ("status", C.c_void_p),
-                ("timeout_ns", C.c_uint64)]
+                ("timeout_ns", C.c_uint64),
+                ("prod_finished", C.c_void_p), ("prod_finish_target", C.c_uint32), ("reserved2", C.c_uint32)]
 
 
 class GemmDesc(C.Structure):

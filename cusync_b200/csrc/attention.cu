@@ -89,8 +89,11 @@ cusync_attn_decode_kernel(const AttnParams p) {
     __syncthreads();
     if (!s_flag) {            // bounded wait expired: leave without touching the output ...
       // ... and without posting: release what waits on this stage without a bound of its own
-      if (p.is_producer)
+      if (p.is_producer) {
         cusync::releaseWaitersOnAbort(st.sems_post, st.grid.x * st.grid.y * st.grid.z, tid, blockDim.x);
+        __syncthreads();
+        if (tid == 0) cusync::countBlockFinished(st.started);
+      }
       return;
     }
   }
@@ -262,6 +265,7 @@ cusync_attn_decode_kernel(const AttnParams p) {
         else                                    cusync::addRelease(st.sems_post + idx, pv);
       }
     }
+    if (tid == 0) cusync::countBlockFinished(st.started);     // after this block's post, if it had one
   }
 }
 

@@ -134,7 +134,18 @@ cusync_conv3x3_slab_kernel(const __grid_constant__ CUtensorMap tmX, const __grid
       // Probes the dependencies of a group of tiles with relaxed loads (all in flight together), then ONE fence
       // makes them acquiring: the fence is the expensive part (over a thousand cycles here) and is paid once
       // per group, a tile ahead of need.  ready[j] tells whether tile j may be loaded without waiting.
+      // Once the producer kernel of this run has finished altogether there is nothing left to probe.
+      bool prod_done = false;
       auto probe_group = [&](uint32_t base, const uint32_t* ys, bool* ready) {
+        if (!prod_done && cusync::producerFinished(st.prod_finished, st.prod_finish_target)) {
+          prod_done = true;
+          fence_proxy_async_global();     // the acquire (generic proxy) before every later TMA read (async proxy)
+        }
+        if (prod_done) {
+#pragma unroll
+          for (int j = 0; j < kSlabGroup; j++) ready[j] = true;
+          return;
+        }
         uint32_t v[kSlabGroup][3];
 #pragma unroll
         for (int j = 0; j < kSlabGroup; j++) {
@@ -429,7 +440,7 @@ cusync_conv3x3_slab_kernel(const __grid_constant__ CUtensorMap tmX, const __grid
         const uint32_t m_off = static_cast<uint32_t>(tile_m * p.conv_rows * p.conv_w);
         const uint32_t idx = cusync::eval::tileIndex(st.out_policy, m_off, 0u, st.grid.x, st.grid.y);
         const uint32_t pv = cusync::eval::postValue(st.out_policy);
-        cusync::fenceAcqRel();
+        // (the release below is the fence: no separate one)
         if (st.opts & CUSYNC_OPT_NO_ATOMIC_ADD) cusync::storeRelease(st.sems_post + idx, pv * st.iter);
         else                                    cusync::addRelease(st.sems_post + idx, pv);
         mbar_arrive(&bars->sched_empty[slot]);      // only now may the slot (and its post barrier) be reused
@@ -443,6 +454,8 @@ cusync_conv3x3_slab_kernel(const __grid_constant__ CUtensorMap tmX, const __grid
   // A block that gave up does not post its tiles: release what waits on this stage without a bound of its own.
   if (bars->abort != 0u && p.is_producer)
     cusync::releaseWaitersOnAbort(st.sems_post, st.grid.x * st.grid.y * st.grid.z, threadIdx.x, blockDim.x);
+  // every post of this block happened before the barrier above: the block counts itself finished
+  if (p.is_producer && threadIdx.x == 0) cusync::countBlockFinished(st.started);
   if (warp == 2) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kSlabStages * kSlabBN);

@@ -66,6 +66,9 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     if (lane == 0) {
       uint32_t fills = 0, sched_it = 0;
       bool ok = true;
+      // Once the producer kernel of this run has finished altogether there is nothing left to wait for: the
+      // tiles that follow skip their semaphore probes (checked once per tile until it is so).
+      bool prod_done = false;
       const uint32_t total_draws = static_cast<uint32_t>(p.num_tiles) + gridDim.x;
       const uint32_t wait_target = p.is_consumer ? st.iter * cusync::eval::waitValue(st.in_policy) : 0u;
       // Distance along K between two sync points of the input policy (0: it syncs once per tile).
@@ -107,6 +110,10 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                                                                            : p.num_k_blocks;
         uint32_t ready_end = 0;   // K offset below which this tile's producer tiles are known finished
         long long wait_empty = 0;
+        if (p.is_consumer && !prod_done && cusync::producerFinished(st.prod_finished, st.prod_finish_target)) {
+          prod_done = true;
+          fence_proxy_async_global();     // the acquire (generic proxy) before every later TMA read (async proxy)
+        }
         for (int kb = kb_begin; kb < kb_end; kb++) {
           const uint32_t s = fills % C::kStages, ph = (fills / C::kStages) & 1u;
           const long long c0 = p.trace ? clock64() : 0;
@@ -143,7 +150,7 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             }
           }
           // Consumer wait, at the load of the dependent A K-block.
-          if (p.is_consumer) {
+          if (p.is_consumer && !prod_done) {
             const uint32_t tz = kb == kb_begin ? 1u : 0u;
             // A K slice (split-K) may begin in the middle of a producer tile: its first K block is a sync point
             // of the K-walking policies as well, on the tile that contains it.
@@ -429,9 +436,10 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         if (lane == 0) mbar_arrive(&bars->tmem_empty[acc]);
         acc_it++;
         if (p.is_producer) {
-          // every lane's stores are ordered before lane 0's fence by the warp barrier above
+          // Every lane's stores are ordered before lane 0's arrival by the warp barrier above, the arrival (a
+          // release) before the posting lane's wait (an acquire), and that lane's fence + release publish them
+          // device-wide (releases are cumulative): no device-wide fence per warp.
           if (lane == 0) {
-            __threadfence();
             // Epilogue warps run at their own pace: one that is a tile ahead must not arrive on `post`
             // while the previous tile's phase is still open (its arrival would close that phase early).
             if (!mbar_wait(&bars->post, (post_it & 1u) ^ 1u, ctx)) ok = false;
@@ -442,7 +450,7 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 const uint32_t idx = cusync::eval::tileIndex(st.out_policy, static_cast<uint32_t>(m_off),
                                                              static_cast<uint32_t>(n_off), st.grid.x, st.grid.y);
                 const uint32_t pv = cusync::eval::postValue(st.out_policy);
-                __threadfence();
+                // (the release below is the fence: no separate one, which costs the whole SM's stores a wait)
                 if (st.opts & CUSYNC_OPT_NO_ATOMIC_ADD) cusync::storeRelease(st.sems_post + idx, pv * st.iter);
                 else                                    cusync::addRelease(st.sems_post + idx, pv);
               }
@@ -502,8 +510,7 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         // on `post`; the first epilogue warp's lane collects the four arrivals
         // (bounded) and performs the single release.
         if (lane == 0) {
-          tma_store_wait_all();
-          __threadfence();
+          tma_store_wait_all();        // the bulk stores' writes are complete and visible to this thread
           // Epilogue warps run at their own pace: one that is a tile ahead must not arrive on `post`
           // while the previous tile's phase is still open (its arrival would close that phase early).
           if (!mbar_wait(&bars->post, (post_it & 1u) ^ 1u, ctx)) ok = false;
@@ -514,7 +521,7 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
               const uint32_t idx = cusync::eval::tileIndex(st.out_policy, static_cast<uint32_t>(m_off),
                                                            static_cast<uint32_t>(n_off), st.grid.x, st.grid.y);
               const uint32_t pv = cusync::eval::postValue(st.out_policy);
-              __threadfence();
+              cusync::fenceAcqRel();      // (one per tile of a GEMM: cheap; the tiles' writes came from bulk stores)
               if (st.opts & CUSYNC_OPT_NO_ATOMIC_ADD) cusync::storeRelease(st.sems_post + idx, pv * st.iter);
               else                                    cusync::addRelease(st.sems_post + idx, pv);
             }
@@ -540,6 +547,8 @@ cusync_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   // A block that gave up does not post its tiles: release what waits on this stage without a bound of its own.
   if (bars->abort != 0u && p.is_producer)
     cusync::releaseWaitersOnAbort(st.sems_post, st.grid.x * st.grid.y * st.grid.z, threadIdx.x, blockDim.x);
+  // every post of this block happened before the barrier above: the block counts itself finished
+  if (p.is_producer && threadIdx.x == 0) cusync::countBlockFinished(st.started);
   if (warp == 2) {
     tc_fence_after();
     tmem_dealloc(tmem_base, C::kTmemCols);

@@ -564,8 +564,7 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap* mA0, const C
 
       if (p.is_producer && m_off < p.m) {     // a pair's second half may lie past the last row tile
         if (lane == 0) {
-          tma_store_wait_all();
-          __threadfence();
+          tma_store_wait_all();        // the bulk stores' writes are complete and visible to this thread
           // Epilogue warps run at their own pace: one that is a tile ahead must not arrive on `post`
           // while the previous tile's phase is still open (its arrival would close that phase early).
           if (!mbar_wait(&bars->post, (post_it & 1u) ^ 1u, ctx)) ok = false;
@@ -576,7 +575,7 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap* mA0, const C
               const uint32_t idx = cusync::eval::tileIndex(st.out_policy, static_cast<uint32_t>(m_off),
                                                            static_cast<uint32_t>(n_off), st.grid.x, st.grid.y);
               const uint32_t pv = cusync::eval::postValue(st.out_policy);
-              __threadfence();
+              cusync::fenceAcqRel();
               if (st.opts & CUSYNC_OPT_NO_ATOMIC_ADD) cusync::storeRelease(st.sems_post + idx, pv * st.iter);
               else                                    cusync::addRelease(st.sems_post + idx, pv);
             }
@@ -606,6 +605,12 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap* mA0, const C
       if ((gi ? p1 : p0).is_producer)
         cusync::releaseWaitersOnAbort(sg.sems_post, sg.grid.x * sg.grid.y * sg.grid.z, threadIdx.x, blockDim.x);
     }
+  }
+  // every post of this block happened before the barrier above: the block counts itself finished in each stage
+  // it produced for
+  if (threadIdx.x == 0) {
+    if (p0.is_producer) cusync::countBlockFinished(p0.stage.started);
+    if (kChain && p1.is_producer) cusync::countBlockFinished(p1.stage.started);
   }
   cluster_sync_all();
   if (warp == 2) {

@@ -25,6 +25,12 @@ struct cusync_stage {
   uint64_t blocks_launched;      // persistent-kernel blocks launched over all runs
   bool     launch_noted;         // a persistent launch was noted for the current run
   int device;
+  // Producer <-> consumer links (cusync_stage_link), kept in both directions so that either side may be
+  // destroyed first: the producer tells its consumers when its launch of a run has been noted.
+  cusync_stage* producer;                 // consumer: the stage it waits on, or null
+  std::vector<cusync_stage*>* consumers;  // producer: stages linked to it (allocated on the first link)
+  uint32_t prod_target;                   // consumer: "blocks finished" count at which this run's producer is done
+  uint32_t prod_target_iter;              // consumer: the run that count belongs to (0: none)
 };
 
 namespace {
@@ -231,6 +237,16 @@ int cusync_stage_create(cusync_stage_t** out, cusync_dim3_t grid, cusync_dim3_t 
 
 int cusync_stage_destroy(cusync_stage_t* s) {
   if (s == nullptr) return CUSYNC_ERROR_NOT_INITIALIZED;
+  // undo the links in both directions
+  if (s->producer && s->producer->consumers) {
+    std::vector<cusync_stage*>& v = *s->producer->consumers;
+    for (size_t i = 0; i < v.size(); i++)
+      if (v[i] == s) { v.erase(v.begin() + i); break; }
+  }
+  if (s->consumers) {
+    for (cusync_stage* c : *s->consumers) { c->producer = nullptr; c->prod_target_iter = 0; }
+    delete s->consumers;
+  }
   cudaFree(s->view.tile_counter);
   cudaFree(s->view.tile_order);
   cudaFree(s->view.sems_post);   // owned by the producer; consumers only alias it
@@ -246,6 +262,17 @@ int cusync_stage_link(cusync_stage_t* prod, cusync_stage_t* cons) {
   cons->view.prod_grid = prod->view.grid;
   cons->view.sems_wait = prod->view.sems_post;
   cons->linked = true;
+  if (cons->producer != prod) {
+    if (cons->producer && cons->producer->consumers) {          // re-linked to another producer
+      std::vector<cusync_stage*>& v = *cons->producer->consumers;
+      for (size_t i = 0; i < v.size(); i++)
+        if (v[i] == cons) { v.erase(v.begin() + i); break; }
+    }
+    if (!prod->consumers) prod->consumers = new (std::nothrow) std::vector<cusync_stage*>();
+    if (prod->consumers) { prod->consumers->push_back(cons); cons->producer = prod; }
+    else cons->producer = nullptr;
+    cons->prod_target_iter = 0;
+  }
   return CUSYNC_SUCCESS;
 }
 
@@ -279,12 +306,22 @@ int cusync_stage_reset(cusync_stage_t* s, cusync_stream_t stream) {
   s->view.iter = 1;
   s->blocks_launched = 0;
   s->launch_noted = false;
+  s->prod_target_iter = 0;
+  if (s->consumers)
+    for (cusync_stage* c : *s->consumers) c->prod_target_iter = 0;
   return ok ? CUSYNC_SUCCESS : CUSYNC_ERROR_CUDA;
 }
 
 int cusync_stage_get_view(const cusync_stage_t* s, cusync_stage_view_t* out) {
   if (s == nullptr || out == nullptr) return CUSYNC_ERROR_NOT_INITIALIZED;
   *out = s->view;
+  // the producer's finish count, when its launch of this very run has been noted already
+  out->prod_finished = nullptr;
+  out->prod_finish_target = 0;
+  if (s->producer && s->prod_target_iter == s->view.iter && s->producer->view.iter == s->view.iter) {
+    out->prod_finished = s->producer->view.started + 2;
+    out->prod_finish_target = s->prod_target;
+  }
   return CUSYNC_SUCCESS;
 }
 
@@ -298,6 +335,11 @@ int cusync_stage_note_launch(cusync_stage_t* s, uint32_t num_blocks) {
   if (s == nullptr) return CUSYNC_ERROR_NOT_INITIALIZED;
   s->blocks_launched += num_blocks;
   s->launch_noted = true;
+  if (s->consumers)
+    for (cusync_stage* c : *s->consumers) {
+      c->prod_target = static_cast<uint32_t>(s->blocks_launched & 0xffffffffull);
+      c->prod_target_iter = s->view.iter;
+    }
   return CUSYNC_SUCCESS;
 }
 

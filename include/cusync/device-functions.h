@@ -50,6 +50,16 @@ CUSYNC_DEVICE void storeRelease(uint32_t* addr, uint32_t value) {
 // hardware instead of a polling kernel.  Without such a dependent behind the grid it does nothing.
 CUSYNC_DEVICE void allowDependentLaunch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// A producer block's last act: counts itself finished (after its posts) in the stage's third "started" word.
+CUSYNC_DEVICE void countBlockFinished(uint32_t* started) { addRelease(started + 2, 1u); }
+
+// Whether the producer kernel of this run has finished altogether: its "blocks finished" word has reached the
+// count the host computed when it launched the producer (a counter over all runs: wrapped difference).  An
+// acquire: when true, everything the producer wrote and posted is visible to this thread.
+CUSYNC_DEVICE bool producerFinished(const uint32_t* finished, uint32_t target) {
+  return finished != nullptr && static_cast<int32_t>(loadAcquire(finished) - target) >= 0;
+}
+
 CUSYNC_DEVICE uint64_t globalTimerNs() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));

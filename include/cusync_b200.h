@@ -115,12 +115,21 @@ typedef struct cusync_stage_view {
   cusync_policy_t out_policy;
   cusync_dim3_t*  tile_order;   /* [numTiles] schedule buffer */
   uint32_t*       tile_counter; /* ticket counter for tile_order */
-  uint32_t*       started;      /* [2]: [0] = iter stored by block 0 (reference protocol),
-                                   [1] = blocks started so far, all runs (persistent kernels) */
+  uint32_t*       started;      /* [3]: [0] = iter stored by block 0 (reference protocol),
+                                   [1] = blocks started so far, all runs (persistent kernels),
+                                   [2] = blocks finished so far, all runs: a producer block adds 1 after its last post */
   uint32_t*       sems_post;    /* semaphores this stage posts to (producer) */
   uint32_t*       sems_wait;    /* semaphores this stage waits on (consumer) */
   uint32_t*       status;       /* device copy of cusync_status_t */
   uint64_t        timeout_ns;   /* bound of every device-side spin */
+  /* Consumer: the producer's "blocks finished" word and the count it reaches when the producer kernel of THIS run
+   * has finished altogether (cusync_stage_note_launch of the producer writes it into its linked consumers).  A
+   * consumer block that finds the count reached need not look at the semaphores of its tiles any more: everything
+   * it could wait for is there.  Null when the producer's launch of this run was not noted before the consumer's
+   * view was taken (the consumer then checks every tile, as the reference does).  No counterpart. */
+  const uint32_t* prod_finished;
+  uint32_t        prod_finish_target;
+  uint32_t        reserved2;
 } cusync_stage_view_t;
 
 typedef struct cusync_stage cusync_stage_t;

@@ -131,6 +131,60 @@ def test_config5_conv_chain_with_conv2dtilesync(n, max_ctas):
     c1.destroy(); c2.destroy(); prod.destroy(); cons.destroy()
 
 
+@pytest.mark.parametrize("c", [64, 128])      # the slab kernel and the general kernel
+def test_consumer_skips_its_probes_once_the_producer_kernel_has_finished(c):
+    # The producer's blocks count themselves finished after their posts; a consumer block that finds the count of
+    # this run's producer launch reached knows that every tile is there and stops probing semaphores.  Shown by
+    # taking the semaphores away after the producer has finished: the consumer completes all the same.  In the next
+    # run, with no producer launched, the count of run 1 must NOT be taken for run 2's: the consumer times out.
+    import ctypes as C
+    n, h, w = 2, 28, 28
+    x, f1 = _inputs(n, h, w, c, c, 90)
+    _, f2 = _inputs(1, 4, 28, c, c, 91)
+    y1 = torch.empty((n, h, w, c), device="cuda", dtype=torch.half)
+    y2 = torch.full((n, h, w, c), float("nan"), device="cuda", dtype=torch.half)
+    prob = cs.Conv2dProblemSize(n, h, w, c, c)
+    grid, tile_m, tile_n = prob.grid(), prob.tile_m(), prob.tile_n()
+    prod = cs.CuStage(cs.TransposeXYOrder, grid, (1, 1, 1), cs.NoSync(), cs.TileSync(cs.TransposeXYOrder, tile_m, tile_n))
+    cons = cs.CuStage(cs.TransposeXYOrder, grid, (1, 1, 1), cs.Conv2DTileSync(cs.TransposeXYOrder, 3, 3, tile_m, tile_n),
+                      cs.NoSync())
+    assert cs.CuSync.setProducerConsumerPair(prod, cons) == L.SUCCESS
+    cons.set_timeout_ns(30e6)
+    c1, c2 = cs.Conv2dFprop(), cs.Conv2dFprop()
+    assert c1.initialize(prod, prob, x, f1, y1, L.EPILOGUE_RELU, 0) == L.SUCCESS
+    assert c2.initialize(cons, prob, y1, f2, y2, L.EPILOGUE_RELU, 0) == L.SUCCESS
+    stream = torch.cuda.current_stream()
+    sp = C.c_void_p(stream.cuda_stream)
+    view = L.StageView()
+    # before any producer launch the consumer has no count to look at
+    assert L.lib().cusync_stage_get_view(cons._h, C.byref(view)) == L.SUCCESS and not view.prod_finished
+    assert c1.run(stream) == L.SUCCESS
+    torch.cuda.synchronize()
+    assert L.lib().cusync_stage_get_view(cons._h, C.byref(view)) == L.SUCCESS
+    assert view.prod_finished and view.prod_finish_target == c1.num_ctas()
+    count = grid[0] * grid[1]
+    assert (prod.semaphores() == 1).all()
+    assert L.lib().cusync_stage_get_view(prod._h, C.byref(view)) == L.SUCCESS
+    assert L.lib().cusync_stream_write_values(C.c_void_p(view.sems_post), count, 0, sp) == L.SUCCESS   # take them away
+    assert c2.run(stream) == L.SUCCESS
+    torch.cuda.synchronize()
+    assert cons.status().code == 0
+    r1 = o.conv2d_3x3_nhwc_f16(x.cpu().numpy(), f1.cpu().numpy(), True)
+    assert o.max_rel_err(y1.cpu().numpy(), r1) <= TOL
+    assert o.max_rel_err(y2.cpu().numpy(), o.conv2d_3x3_nhwc_f16(y1.cpu().numpy(), f2.cpu().numpy(), True)) <= TOL
+    # run 2 without its producer: nothing to go by but the semaphores, which stay below 2
+    assert L.lib().cusync_stream_write_values(C.c_void_p(view.sems_post), count, 1, sp) == L.SUCCESS
+    prod.incrementIter(); cons.incrementIter()
+    assert L.lib().cusync_stage_get_view(cons._h, C.byref(view)) == L.SUCCESS and not view.prod_finished
+    y2.fill_(float("nan"))
+    assert c2.run(stream) == L.SUCCESS
+    torch.cuda.synchronize()
+    st = cons.status()
+    assert st.code == L.ERROR_TIMEOUT and st.expected == 2 and st.seen == 1
+    assert torch.isnan(y2.float()).all()
+    c1.destroy(); c2.destroy(); prod.destroy(); cons.destroy()
+
+
 def test_a_consumer_tile_waits_for_its_halo_neighbours_at_every_channel_chunk():
     # 128 channels in producer tiles of 64: two channel chunks along the consumer's K walk.  The host stands in for
     # the producer and posts every semaphore but ONE, the second chunk of row tile 3.  The consumer tiles of rows
