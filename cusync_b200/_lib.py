@@ -121,7 +121,7 @@ class AllReduceDesc(C.Structure):
 
 class MlpChoice(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("policy", "single_grid", "stream_wait", "group_rows1", "group_rows2",
-                                         "tile_n1", "tile_n2", "split_k1", "split_k2")]
+                                         "tile_n1", "tile_n2", "split_k1", "split_k2", "tail_split1")]
 
 
 MLP_GPT3, MLP_LLAMA = 0, 1

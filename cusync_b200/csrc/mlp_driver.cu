@@ -39,14 +39,21 @@ namespace {
 // combination against the same stream-ordered layer): RowSync beats TileSync at every batch of both models;
 // one persistent grid pays from about twelve row tiles on (+1.5 to +2 points at B = 2048, nothing at 1024, a
 // loss at 512 where the first GEMM is a single round); walking the tiles in groups of rows pays from eight row
-// tiles on.
-struct ConfigRow { int model; int max_batch; int policy; int single_grid; int group_rows1; int group_rows2; };
+// tiles on.  Re-measured with the dual GEMM on CTA pairs and the lighter post path: one persistent grid is level
+// with two launches at seven and eight row tiles and 2 to 4 % ahead from nine on (B = 1152 ... 1792); at seven and
+// eight row tiles the first GEMM's 96 pair tiles are one round of 74 and a tail of 22, and cutting the tail's tiles
+// into three K slices (66 units: one short round) brings the one-grid layer from 289-297 to 277-285 us at
+// B = 960 and 1024 (with two launches the same split is a loss).  tail_split1 is applied only where the tail's
+// units fit one round (see cusync_mlp_create).
+struct ConfigRow { int model; int max_batch; int policy; int single_grid; int group_rows1; int group_rows2; int tail_split1; };
 const ConfigRow kConfigTable[] = {
-    {CUSYNC_MLP_GPT3, 512, CUSYNC_POLICY_ROWSYNC, 1, 1, 1},
-    {CUSYNC_MLP_GPT3, 1536, CUSYNC_POLICY_ROWSYNC, 1, 4, 4},
-    {CUSYNC_MLP_GPT3, 0x7fffffff, CUSYNC_POLICY_ROWSYNC, 2, 4, 8},
-    {CUSYNC_MLP_LLAMA, 896, CUSYNC_POLICY_ROWSYNC, 1, 1, 1},
-    {CUSYNC_MLP_LLAMA, 0x7fffffff, CUSYNC_POLICY_ROWSYNC, 1, 1, 4},
+    {CUSYNC_MLP_GPT3, 512, CUSYNC_POLICY_ROWSYNC, 1, 1, 1, 0},
+    {CUSYNC_MLP_GPT3, 768, CUSYNC_POLICY_ROWSYNC, 1, 4, 4, 0},
+    {CUSYNC_MLP_GPT3, 1024, CUSYNC_POLICY_ROWSYNC, 2, 4, 4, 3},
+    {CUSYNC_MLP_GPT3, 1536, CUSYNC_POLICY_ROWSYNC, 2, 4, 4, 0},
+    {CUSYNC_MLP_GPT3, 0x7fffffff, CUSYNC_POLICY_ROWSYNC, 2, 4, 8, 0},
+    {CUSYNC_MLP_LLAMA, 896, CUSYNC_POLICY_ROWSYNC, 1, 1, 1, 0},
+    {CUSYNC_MLP_LLAMA, 0x7fffffff, CUSYNC_POLICY_ROWSYNC, 1, 1, 4, 0},
 };
 
 const ConfigRow* config_row(int model, int batch) {
@@ -129,6 +136,18 @@ int cusync_mlp_create(cusync_mlp_t** out, const cusync_mlp_desc_t* desc) {
   // the other, not a whole group at once at the end: pair-row groups unless the caller says otherwise
   if (dd.group_rows2 == 0) dd.group_rows2 = dd.post_rows ? 2 : choice.group_rows2;
   const int single_grid_wanted = dd.single_grid ? dd.single_grid : choice.single_grid;
+  // The table's K slices for the first GEMM's last partial round go with the table's launch form: only where the
+  // caller left both open, the form is one grid, and the tail's units fit one round of the SM pairs in use.
+  if (d0.single_grid == 0 && d0.tail_split_sync1 == 0 && choice.single_grid == 2 && choice.tail_split1 > 1 &&
+      choice.tile_n1 == 256 && dd.tile_n1 == 0 && dd.cta_pair != 1) {
+    int sms = cusync_b200_sm_count();
+    if (sms <= 0) sms = 148;
+    const int ctas = dd.max_ctas > 0 && dd.max_ctas < sms ? dd.max_ctas : sms;
+    const int pairs = ctas / 2;
+    const int units = ((dd.batch + 255) / 256) * ((dd.ffn + 255) / 256);
+    const int tail = pairs > 0 ? units % pairs : 0;
+    if (units > pairs && tail > 0 && tail * choice.tail_split1 <= pairs) dd.tail_split_sync1 = choice.tail_split1;
+  }
   const cusync_mlp_desc_t& d = m->desc;
   const int epi1 = d.model == CUSYNC_MLP_LLAMA ? CUSYNC_EPILOGUE_SILU_MUL_DUAL : CUSYNC_EPILOGUE_GELU_ERF;
   m->tile_n1 = d.tile_n1 ? d.tile_n1 : cusync_gemm_default_tile_n(d.batch, d.ffn, d.hidden, epi1);
@@ -407,6 +426,7 @@ int cusync_mlp_choose_config(int32_t model, int32_t batch, int32_t hidden, int32
   out->single_grid = row->single_grid;
   out->group_rows1 = row->group_rows1;
   out->group_rows2 = row->group_rows2;
+  out->tail_split1 = row->tail_split1;
   out->tile_n1 = cusync_gemm_default_tile_n(batch, ffn, hidden, epi1);
   out->tile_n2 = cusync_gemm_default_tile_n(batch, hidden, ffn, CUSYNC_EPILOGUE_NONE);
   out->split_k1 = cusync_gemm_default_split_k(batch, ffn, hidden, epi1, out->tile_n1, 0);

@@ -622,6 +622,9 @@ typedef struct cusync_mlp_choice {
   int32_t stream_wait;           /* 1 = the wait before the second launch is a stream memory operation */
   int32_t group_rows1, group_rows2;
   int32_t tile_n1, tile_n2, split_k1, split_k2;
+  int32_t tail_split1;           /* K slices for the tiles of the first GEMM's last partial round in the one-grid form
+                                    (0 = none); cusync_mlp_create applies it where the caller left single_grid and
+                                    tail_split_sync1 open and the tail's units fit one round of the SM pairs */
 } cusync_mlp_choice_t;
 CUSYNC_API int cusync_mlp_choose_config(int32_t model, int32_t batch, int32_t hidden, int32_t ffn, cusync_mlp_choice_t* out);
 /* 1 when run_cusync launches both GEMMs as one persistent grid. */

@@ -73,7 +73,11 @@ def main():
         comm.layer_run(plain, ps, cs)
         comm.layer_run(over, ps, cs, reducer=ar, reduce_stream=rs)
         torch.cuda.synchronize(); g.barrier()
-        assert torch.equal(plain.y, ref.y)                       # same kernels, same NCCL all-reduce
+        if plain.tail_splits[:2] == ref.tail_splits[2:]:
+            assert torch.equal(plain.y, ref.y)                   # same kernels, same NCCL all-reduce
+        else:                                                    # K slices in the last partial round of one arm only
+            perr = (plain.y.float() - ref.y.float()).abs().max().item()
+            assert perr <= 4e-3 * ref.y.float().abs().max().item()
         err = (over.y.float() - ref.y.float()).abs().max().item()
         assert err <= 4e-3 * ref.y.float().abs().max().item()
     t = torch.full((1000,), float(g.rank + 1), device=dev, dtype=torch.half)
