@@ -597,6 +597,8 @@ int cusync_gemm_plan_create(cusync_gemm_plan_t** out, const cusync_gemm_desc_t* 
   if (sms <= 0) sms = 148;
   if (d.split_k < 0 || d.split_k > 64 || (dual && d.split_k > 1)) { delete pl; return CUSYNC_ERROR_UNSUPPORTED; }
   if (d.tail_split < 0 || d.tail_split > 16) { delete pl; return CUSYNC_ERROR_INVALID_ARGUMENT; }
+  // (the K-sliced paths sum plain accumulators: no finaliser for the dual epilogue's two halves)
+  if (dual && d.tail_split > 1) { delete pl; return CUSYNC_ERROR_UNSUPPORTED; }
   pl->split_k = d.split_k > 0 ? d.split_k : d.b_stage ? 1 : auto_split_k(d.m, d.n, d.k, pl->tile_n, dual, pl->pair, sms);
 
   GemmParams& p = pl->params;

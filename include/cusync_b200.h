@@ -253,8 +253,10 @@ typedef struct cusync_gemm_desc {
   int32_t tail_split;              /* CTA-pair kernel without uniform split-K: K slices for the tiles of the last,
                                       partial wave, so that the tail occupies every SM pair (the remedy the reference
                                       gets from Stream-K, src/ml-bench/transformer/mlp.cu:137-207).  0 = choose
-                                      (today: none, it measured slower), 1 = none, 2..16 = forced.  The stage grid is unchanged (z = 1); a split tile
-                                      posts once, from the pair that adds its last slice. */
+                                      (none for a single launch: it measured slower; the MLP driver's table uses it
+                                      inside the one-grid layer), 1 = none, 2..16 = forced.  The stage grid is
+                                      unchanged (z = 1); a split tile posts once, from the pair that adds its last
+                                      slice.  Not with CUSYNC_EPILOGUE_SILU_MUL_DUAL (CUSYNC_ERROR_UNSUPPORTED). */
   cusync_stage_t* stage;           /* NULL = no tile synchronisation (stream-ordered use) */
   /* A B operand that is itself the output of an earlier stage of the chain (the K^T and V operands of the
    * attention GEMMs S = Q K^T and O = S V, src/ml-bench/transformer/attention.cu:272-276, whose policies wait for

@@ -125,6 +125,11 @@ def test_dual_gemm_silu_mul_on_cta_pairs(M, N, K, max_ctas, layout):
     # the same numbers as the one-CTA kernel gives (same K walk per element)
     d1, _ = _gemm(a, b, epi=L.EPILOGUE_SILU_MUL_DUAL, tile_n=128, b_layout=layout, b2=b2, cta_pair=1)
     assert torch.equal(d, d1)
+    # K slices (uniform or for the last partial round) have no finaliser for the two halves: refused
+    for kw in (dict(tail_split=2), dict(split_k_slices=2)):
+        g = cs.Gemm()
+        assert g.initialize(cs.GemmArguments(None, (M, N, K), a, b, d, ref_b2=b2, epilogue=L.EPILOGUE_SILU_MUL_DUAL,
+                                             tile_n=128, cta_pair=2, **kw)) == L.ERROR_UNSUPPORTED
 
 
 def test_cta_pair_gemm_epilogue_and_few_clusters():
