@@ -170,6 +170,10 @@ def test_mlp_config_table_is_total_and_consistent():
             if c["single_grid"] == 2:      # one grid needs both GEMMs on CTA pairs: more than two row tiles, 256-wide tiles
                 assert batch > 256 and c["tile_n1"] == 256 and c["tile_n2"] == 256 and model == "gpt3"
             assert c["stream_wait"] == (1 if (batch + 127) // 128 <= 4 else 0)
+            # K slices for the first GEMM's last partial round: only in the one-grid form, and only at seven and eight
+            # row tiles of the GPT-3 shard (96 pair tiles: one round of 74 and a tail of 22, 66 units in three slices)
+            assert c["tail_split1"] == (3 if (model == "gpt3" and 768 < batch <= 1024) else 0)
+            assert c["tail_split1"] == 0 or c["single_grid"] == 2
             key = (c["policy"], c["single_grid"], c["group_rows1"], c["group_rows2"])
             if prev is not None and key != prev:
                 changes += 1
