@@ -44,7 +44,9 @@ namespace {
 // eight row tiles the first GEMM's 96 pair tiles are one round of 74 and a tail of 22, and cutting the tail's tiles
 // into three K slices (66 units: one short round) brings the one-grid layer from 289-297 to 277-285 us at
 // B = 960 and 1024 (with two launches the same split is a loss).  tail_split1 is applied only where the tail's
-// units fit one round (see cusync_mlp_create).
+// units fit one round (see cusync_mlp_create).  LLaMA shard (the fused SwiGLU GEMM on CTA pairs): one grid is level
+// with two launches up to eight row tiles and 4 to 6 % ahead from nine on (B = 1152 ... 3072: 150 / 170 / 186 /
+// 242 / 373 us against 159 / 182 / 195 / 254 / 388 us at B = 1152 / 1280 / 1536 / 2048 / 3072).
 struct ConfigRow { int model; int max_batch; int policy; int single_grid; int group_rows1; int group_rows2; int tail_split1; };
 const ConfigRow kConfigTable[] = {
     {CUSYNC_MLP_GPT3, 512, CUSYNC_POLICY_ROWSYNC, 1, 1, 1, 0},
@@ -53,7 +55,8 @@ const ConfigRow kConfigTable[] = {
     {CUSYNC_MLP_GPT3, 1536, CUSYNC_POLICY_ROWSYNC, 2, 4, 4, 0},
     {CUSYNC_MLP_GPT3, 0x7fffffff, CUSYNC_POLICY_ROWSYNC, 2, 4, 8, 0},
     {CUSYNC_MLP_LLAMA, 896, CUSYNC_POLICY_ROWSYNC, 1, 1, 1, 0},
-    {CUSYNC_MLP_LLAMA, 0x7fffffff, CUSYNC_POLICY_ROWSYNC, 1, 1, 4, 0},
+    {CUSYNC_MLP_LLAMA, 1024, CUSYNC_POLICY_ROWSYNC, 1, 1, 4, 0},
+    {CUSYNC_MLP_LLAMA, 0x7fffffff, CUSYNC_POLICY_ROWSYNC, 2, 1, 4, 0},
 };
 
 const ConfigRow* config_row(int model, int batch) {

@@ -167,8 +167,9 @@ def test_mlp_config_table_is_total_and_consistent():
             assert c["group_rows1"] >= 1 and c["group_rows2"] >= 1
             assert c["tile_n1"] in (64, 128, 192, 256) and c["tile_n2"] in (64, 128, 192, 256)
             assert 1 <= c["split_k1"] <= 16 and 1 <= c["split_k2"] <= 16
-            if c["single_grid"] == 2:      # one grid needs both GEMMs on CTA pairs: more than two row tiles, 256-wide tiles
-                assert batch > 256 and c["tile_n1"] == 256 and c["tile_n2"] == 256 and model == "gpt3"
+            if c["single_grid"] == 2:      # one grid needs both GEMMs on CTA pairs: more than two row tiles, 256-wide
+                # tiles (128-wide output tiles for the fused SwiGLU GEMM, whose pair MMA is [X W1 | X V])
+                assert batch > 256 and c["tile_n1"] == (256 if model == "gpt3" else 128) and c["tile_n2"] == 256
             assert c["stream_wait"] == (1 if (batch + 127) // 128 <= 4 else 0)
             # K slices for the first GEMM's last partial round: only in the one-grid form, and only at seven and eight
             # row tiles of the GPT-3 shard (96 pair tiles: one round of 74 and a tail of 22, 66 units in three slices)

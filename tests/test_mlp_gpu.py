@@ -246,3 +246,29 @@ def test_single_grid_layer_equals_the_two_launch_layer(batch, max_ctas, policy):
         assert torch.equal(one.h, two.h) and torch.equal(one.y, two.y)
         assert (one.producer_semaphores() == two.producer_semaphores()).all()
     one.destroy(); two.destroy()
+
+
+@pytest.mark.parametrize("batch", [640, 2048])
+def test_llama_layer_as_one_grid_equals_the_two_launch_layer(batch):
+    # the fused SwiGLU GEMM on CTA pairs followed by the second GEMM, as ONE persistent grid (the table's choice from
+    # nine row tiles on) against one launch per GEMM: same H and Y bit for bit, same semaphore counts
+    dev = torch.device("cuda")
+    x, w1, w2, v = M.make_inputs("llama", batch, dev, seed=19)
+    one = M.MLPShard("llama", batch, x, w1, w2, v, policy="rowsync", single_grid=2)
+    two = M.MLPShard("llama", batch, x, w1, w2, v, policy="rowsync", single_grid=1)
+    assert one.single_grid and not two.single_grid
+    assert M.MLPShard("llama", 2048, *M.make_inputs("llama", 2048, dev, seed=1), policy="rowsync").single_grid
+    ps, cs_ = torch.cuda.Stream(priority=-1), torch.cuda.Stream()
+    for it in range(1, 4):
+        for s in (one, two):
+            s.h.fill_(float("nan")); s.y.fill_(float("nan"))
+        torch.cuda.synchronize()
+        one.run_cusync(ps, cs_)
+        cs_.synchronize()
+        assert not torch.isnan(one.y.float()).any()
+        two.run_cusync(ps, cs_)
+        torch.cuda.synchronize()
+        assert one.status_codes() == (0, 0) and two.status_codes() == (0, 0)
+        assert torch.equal(one.h, two.h) and torch.equal(one.y, two.y)
+        assert (one.producer_semaphores() == two.producer_semaphores()).all()
+    one.destroy(); two.destroy()
